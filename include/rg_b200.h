@@ -1,0 +1,204 @@
+/*
+ * rg_b200 — C ABI of the B200-native GGUF-quantized Llama session.
+ *
+ * This is the boundary a rustgrad CUDA session target binds through FFI.  Every entry point
+ * names the rustgrad interface it stands in for (paths relative to the rustgrad tree).  All
+ * pointers are plain host pointers unless a parameter is documented as a device pointer; no
+ * C++ or torch type crosses the boundary; every function returns an rg_status and never throws.
+ *
+ * Threading: a plan or session is driven by one host thread at a time (rustgrad sessions are
+ * `&mut self`, src/models/transformer/metal_generation.rs:1052).  Distinct sessions may be used
+ * from distinct threads.
+ */
+#ifndef RG_B200_H
+#define RG_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Typed, fail-closed statuses.  They fold rustgrad's error enums for this path:
+ * GgufErrorKind (src/gguf/mod.rs:70-134), LlamaModelError (src/models/transformer/model.rs:1073-1153),
+ * LlamaMetalStepError (src/models/transformer/metal_step.rs:161-170) and CudaError (src/cuda.rs:478-511). */
+typedef enum {
+  RG_OK = 0,
+  RG_INVALID_ARGUMENT = 1,
+  RG_UNSUPPORTED_TYPE = 2,      /* ggml type outside {F32, F16, Q4_0, Q8_0}; packed norm tensor */
+  RG_SHAPE_MISMATCH = 3,        /* tensor shape differs from the configuration's inventory */
+  RG_NON_FINITE_SCALE = 4,      /* a packed block carries an inf/NaN scale */
+  RG_TOKEN_OUT_OF_RANGE = 5,
+  RG_CONTEXT_EXHAUSTED = 6,
+  RG_NON_FINITE_LOGITS = 7,
+  RG_FRESH_SESSION_REQUIRED = 8,
+  RG_CUDA_ERROR = 9,
+  RG_NCCL_ERROR = 10,
+  RG_OUT_OF_MEMORY = 11,
+  RG_TIMEOUT = 12,              /* a bounded device-side wait gave up */
+  RG_POISONED = 13,             /* an earlier step could not be proven complete */
+  RG_MALFORMED_GGUF = 14,
+  RG_MISSING_TENSOR = 15,
+  RG_UNEXPECTED_TENSOR = 16,
+  RG_UNSUPPORTED_VARIANT = 17,  /* rope scaling, experts, partial rotary, biases, q/k norms */
+  RG_MISSING_METADATA = 18,
+  RG_EMPTY_PROMPT = 19,
+  RG_UNSUPPORTED_GEOMETRY = 20  /* a shape the sm_100a kernels do not cover (K % 256 != 0 for packed) */
+} rg_status;
+
+/* GGML tensor types on this path (src/gguf/tensor.rs:33-59). */
+enum { RG_TYPE_F32 = 0, RG_TYPE_F16 = 1, RG_TYPE_Q4_0 = 2, RG_TYPE_Q8_0 = 8 };
+
+/* Mirror of LlamaModelConfig (src/models/transformer/model.rs:109-121). */
+typedef struct {
+  int32_t n_layers;
+  int32_t d_model;
+  int32_t n_heads;
+  int32_t n_kv_heads;
+  int32_t head_dim;
+  int32_t ffn_dim;
+  int32_t vocab;
+  int32_t max_context;
+  float norm_eps;
+  double rope_theta;
+  int32_t eos_id; /* -1 = none */
+  int32_t eot_id; /* -1 = none */
+} rg_llama_config;
+
+/* Session options.  Zero-initialise, then set what differs.  (rustgrad has no config framework:
+ * builders and plain structs such as MetalPlanOptions; src/session/target.rs:165-213.) */
+typedef struct {
+  int32_t device;        /* CUDA ordinal of this process's GPU */
+  int32_t max_batch;     /* independent sequences decoded together; 0 -> 1 */
+  int32_t max_context;   /* KV positions per sequence; 0 -> config.max_context */
+  int32_t kv_f32;        /* 0: f16 KV cache; 1: f32 cache like the reference's (model.rs:879-922) */
+  int32_t tp_rank;       /* tensor-parallel rank of this process */
+  int32_t tp_world;      /* 0 or 1: single GPU */
+  uint8_t nccl_id[128];  /* rg_b200_nccl_unique_id() of rank 0, identical on every rank */
+  int32_t disable_graph; /* 1: launch decode kernels directly instead of replaying a CUDA graph */
+  int32_t disable_pdl;   /* 1: no programmatic dependent launch between kernels */
+  int32_t disable_fused_allreduce; /* 1: TP all-reduce through NCCL only */
+  int32_t reserved[8];
+} rg_options;
+
+/* Per-run evidence in the vocabulary of MetalDeviceRunReport
+ * (src/runtime/metal/session.rs:145-185) and BenchmarkMetrics (src/benchmark.rs:290-305). */
+typedef struct {
+  uint64_t kernel_launches;   /* kernels launched (graph nodes count once per replay) */
+  uint64_t graph_replays;
+  uint64_t h2d_calls, h2d_bytes;
+  uint64_t d2h_calls, d2h_bytes;
+  uint64_t weight_bytes;      /* packed bytes resident in HBM on this rank */
+  uint64_t kv_bytes;          /* KV cache bytes on this rank */
+  uint64_t fallback_count;    /* always 0: there is no CPU or library fallback */
+  float last_prefill_ms;      /* CUDA-event time of the last prefill call */
+  float last_decode_ms;       /* CUDA-event time of the last decode step */
+} rg_report;
+
+typedef struct rg_gguf rg_gguf;
+typedef struct rg_plan rg_plan;
+typedef struct rg_session rg_session;
+
+const char *rg_b200_version(void);
+const char *rg_b200_status_string(int32_t status);
+/* Detail of the most recent failure on the calling thread (CUDA/NCCL code and call site). */
+const char *rg_b200_last_error(void);
+
+/* Host-side fault injection for tests: the n-th next call of a wrapped CUDA entry ("malloc",
+ * "memcpy", "launch", "sync") fails; n < 0 disarms.  Stands where rustgrad's mock driver has its
+ * fail-after-N knobs (src/cuda.rs:5895-5960).  Never makes the GPU itself fault. */
+int32_t rg_b200_test_fail_after(const char *what, int32_t n);
+
+/* ---- GGUF container: replaces read_gguf / GgufFile (src/gguf/mod.rs:166-173,256-384,
+ * src/gguf/reader.rs:8-301).  The bytes are borrowed and must outlive the handle. ---- */
+int32_t rg_b200_gguf_open(const uint8_t *bytes, size_t len, rg_gguf **out);
+void rg_b200_gguf_close(rg_gguf *g);
+size_t rg_b200_gguf_tensor_count(const rg_gguf *g);
+/* dims are logical (outermost first), as GgufTensor::shape (src/gguf/reader.rs:144-146). */
+int32_t rg_b200_gguf_tensor_info(const rg_gguf *g, size_t index, const char **name, int32_t *ggml_type,
+                                 int32_t *rank, uint64_t dims[4], const uint8_t **data, size_t *nbytes);
+/* LlamaModelConfig::from_gguf (src/models/transformer/model.rs:126-298). */
+int32_t rg_b200_gguf_llama_config(const rg_gguf *g, rg_llama_config *out);
+
+/* ---- Plan: replaces LlamaModelState::bind (model.rs:352-529) + LlamaMetalPlan::from_workflow_on
+ * (metal_generation.rs:276-281).  Tensors are validated on the host before any device work and
+ * uploaded once, in their native block bytes, with no host dequantisation.  Unlike the Metal
+ * plan the upload happens per tensor at add time, so a 39 GB model never has two host copies. ---- */
+int32_t rg_b200_plan_create(const rg_llama_config *config, const rg_options *options, rg_plan **out);
+int32_t rg_b200_plan_add_tensor(rg_plan *plan, const char *name, int32_t ggml_type, uint64_t rows,
+                                uint64_t cols, const uint8_t *bytes, size_t nbytes);
+/* Binds every tensor of an open GGUF file (exact inventory, unexpected tensors rejected). */
+int32_t rg_b200_plan_from_gguf(const rg_gguf *g, const rg_options *options, rg_plan **out);
+/* Synthetic weights generated and quantized on the device: N(0, std) from a counter-based
+ * generator keyed by (seed, element index of the full tensor), so a tensor-parallel rank
+ * produces exactly its shard of the single-GPU tensor.  No counterpart in rustgrad (it has no
+ * encoder and no synthetic-model tool); exists so 8B/70B-shape models need no 39 GB host file.
+ * norm tensors: std is ignored and the value 1.0 is written. */
+int32_t rg_b200_plan_synth_tensor(rg_plan *plan, const char *name, int32_t ggml_type, uint64_t rows,
+                                  uint64_t cols, uint64_t seed, float std);
+/* Copies the rank-local packed bytes of a bound tensor back to the host (tests, checker input). */
+int32_t rg_b200_plan_tensor_nbytes(const rg_plan *plan, const char *name, size_t *nbytes);
+int32_t rg_b200_plan_read_tensor(const rg_plan *plan, const char *name, uint8_t *out, size_t nbytes);
+void rg_b200_plan_destroy(rg_plan *plan);
+
+/* ---- Session: replaces SessionTarget::prepare for the Llama plan
+ * (src/session/target.rs:13-18, metal_generation.rs:453-500,702-715).  Consumes the plan's device
+ * tensors; the plan handle stays valid only for rg_b200_plan_destroy. ---- */
+int32_t rg_b200_session_prepare(rg_plan *plan, rg_session **out);
+void rg_b200_session_destroy(rg_session *s);
+
+/* metal_generation.rs:837-882 */
+int32_t rg_b200_position(const rg_session *s, int32_t row);
+int32_t rg_b200_max_context(const rg_session *s);
+int32_t rg_b200_vocab_size(const rg_session *s);
+int32_t rg_b200_is_full(const rg_session *s);
+int32_t rg_b200_reset_sequence(rg_session *s);
+
+/* prefill_ids (metal_generation.rs:913-1047): appends n prompt tokens to sequence `row`;
+ * last_logits ([vocab], nullable) receives the logits of the final prompt token. */
+int32_t rg_b200_prefill(rg_session *s, int32_t row, const int32_t *ids, size_t n, float *last_logits);
+/* run_token (metal_generation.rs:1123-1138) generalised to `batch` rows (batch.rs:140-162):
+ * tokens[batch] in; logits [batch, vocab] and/or greedy ids [batch] out (either may be NULL).
+ * Rows 0..batch-1 advance by one position only when the whole step succeeds. */
+int32_t rg_b200_decode(rg_session *s, const int32_t *tokens, int32_t batch, float *logits, int32_t *greedy);
+/* generate_ids with greedy selection (generation.rs:106-160, metal_generation.rs:1052-1175):
+ * requires a fresh sequence, prefill then one-token steps, stops on EOS/EOT, the last token is
+ * not fed back.  out has room for max_new ids. */
+int32_t rg_b200_generate_greedy(rg_session *s, const int32_t *prompt, size_t n_prompt, size_t max_new,
+                                int32_t *out, size_t *n_out, int32_t *stopped);
+/* Device-resident greedy loop for rows 0..batch-1: `steps` replays of the decode graph with the
+ * selected token fed back on the device (the device-greedy session of
+ * metal_greedy_generation.rs:52-72).  first_tokens[batch] seeds it; out [steps, batch] (nullable)
+ * receives the ids after the last step.  gpu_ms (nullable) is the CUDA-event time of the loop. */
+int32_t rg_b200_decode_loop(rg_session *s, const int32_t *first_tokens, int32_t batch, int32_t steps,
+                            int32_t *out, float *gpu_ms);
+int32_t rg_b200_report(const rg_session *s, rg_report *out);
+/* cudaStream_t the session launches on (for CUDA-event timing by the caller). */
+void *rg_b200_session_stream(const rg_session *s);
+
+/* ---- Tensor parallel plumbing (replaces CudaCollectiveGroup, src/collective.rs:322-345,441). ---- */
+int32_t rg_b200_nccl_unique_id(uint8_t out[128]);
+
+/* ---- Operator-level entry points (host buffers in, host buffers out). ---- */
+/* QuantizedTensorData::dequantize_f32 (src/gguf/quantization/data.rs:415-428): bit-exact. */
+int32_t rg_b200_dequantize(int32_t device, int32_t ggml_type, const uint8_t *bytes, size_t elements, float *out);
+/* QuantizedMatmulPlan::execute (src/matmul/quantized.rs:126-182): activation f32 [m,k] x packed
+ * or dense [n,k] -> f32 [m,n].  m <= 8 runs the decode GEMV, larger m the prefill path. */
+int32_t rg_b200_qmatmul(int32_t device, int32_t ggml_type, const uint8_t *weight, uint64_t n, uint64_t k,
+                        const float *activation, uint64_t m, float *out);
+/* QuantizedRowGatherPlan::execute (src/gguf/quantization/row_gather.rs:149-226). */
+int32_t rg_b200_row_gather(int32_t device, int32_t ggml_type, const uint8_t *weight, uint64_t rows,
+                           uint64_t cols, const int64_t *indices, size_t count, float *out);
+
+/* Device-resident operator benchmark: weight uploaded once, `iters` launches timed with CUDA
+ * events on the library's stream; `rotate` distinct weight copies are cycled so that each launch
+ * reads HBM rather than L2.  kernel_ms receives the mean time of one launch. */
+int32_t rg_b200_qmatmul_bench(int32_t device, int32_t ggml_type, const uint8_t *weight, uint64_t n, uint64_t k,
+                              const float *activation, uint64_t m, int32_t rotate, int32_t iters,
+                              int32_t warmup, float *out, float *kernel_ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,107 @@
+"""ctypes binding of ``librg_b200.so`` (the C ABI of ``include/rg_b200.h``).
+
+Importing this module fails loudly when the CUDA library is missing: there is no CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+LIB_PATH = HERE / "librg_b200.so"
+
+
+class LlamaConfig(C.Structure):
+    _fields_ = [
+        ("n_layers", C.c_int32), ("d_model", C.c_int32), ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32),
+        ("head_dim", C.c_int32), ("ffn_dim", C.c_int32), ("vocab", C.c_int32), ("max_context", C.c_int32),
+        ("norm_eps", C.c_float), ("rope_theta", C.c_double), ("eos_id", C.c_int32), ("eot_id", C.c_int32),
+    ]
+
+
+class Options(C.Structure):
+    _fields_ = [
+        ("device", C.c_int32), ("max_batch", C.c_int32), ("max_context", C.c_int32), ("kv_f32", C.c_int32),
+        ("tp_rank", C.c_int32), ("tp_world", C.c_int32), ("nccl_id", C.c_uint8 * 128), ("disable_graph", C.c_int32),
+        ("disable_pdl", C.c_int32), ("disable_fused_allreduce", C.c_int32), ("reserved", C.c_int32 * 8),
+    ]
+
+
+class Report(C.Structure):
+    _fields_ = [
+        ("kernel_launches", C.c_uint64), ("graph_replays", C.c_uint64), ("h2d_calls", C.c_uint64),
+        ("h2d_bytes", C.c_uint64), ("d2h_calls", C.c_uint64), ("d2h_bytes", C.c_uint64), ("weight_bytes", C.c_uint64),
+        ("kv_bytes", C.c_uint64), ("fallback_count", C.c_uint64), ("last_prefill_ms", C.c_float),
+        ("last_decode_ms", C.c_float),
+    ]
+
+
+EXPORTS = [
+    "rg_b200_version", "rg_b200_status_string", "rg_b200_last_error", "rg_b200_test_fail_after", "rg_b200_gguf_open",
+    "rg_b200_gguf_close", "rg_b200_gguf_tensor_count", "rg_b200_gguf_tensor_info", "rg_b200_gguf_llama_config",
+    "rg_b200_plan_create", "rg_b200_plan_add_tensor", "rg_b200_plan_from_gguf", "rg_b200_plan_synth_tensor",
+    "rg_b200_plan_tensor_nbytes", "rg_b200_plan_read_tensor", "rg_b200_plan_destroy", "rg_b200_session_prepare",
+    "rg_b200_session_destroy", "rg_b200_position", "rg_b200_max_context", "rg_b200_vocab_size", "rg_b200_is_full",
+    "rg_b200_reset_sequence", "rg_b200_prefill", "rg_b200_decode", "rg_b200_generate_greedy", "rg_b200_decode_loop",
+    "rg_b200_report", "rg_b200_session_stream", "rg_b200_nccl_unique_id", "rg_b200_dequantize", "rg_b200_qmatmul",
+    "rg_b200_row_gather", "rg_b200_qmatmul_bench",
+]
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m rustgrad_b200.build` (nvcc, sm_100a). "
+            "rustgrad_b200 has no CPU fallback.")
+    L = C.CDLL(str(LIB_PATH))
+    vp, u8p, f32p, i32p = C.c_void_p, C.POINTER(C.c_uint8), C.POINTER(C.c_float), C.POINTER(C.c_int32)
+    L.rg_b200_version.restype = C.c_char_p
+    L.rg_b200_status_string.restype = C.c_char_p
+    L.rg_b200_status_string.argtypes = [C.c_int32]
+    L.rg_b200_last_error.restype = C.c_char_p
+    L.rg_b200_test_fail_after.argtypes = [C.c_char_p, C.c_int32]
+    L.rg_b200_gguf_open.argtypes = [u8p, C.c_size_t, C.POINTER(vp)]
+    L.rg_b200_gguf_close.restype = None
+    L.rg_b200_gguf_close.argtypes = [vp]
+    L.rg_b200_gguf_tensor_count.restype = C.c_size_t
+    L.rg_b200_gguf_tensor_count.argtypes = [vp]
+    L.rg_b200_gguf_tensor_info.argtypes = [vp, C.c_size_t, C.POINTER(C.c_char_p), i32p, i32p, C.POINTER(C.c_uint64),
+                                           C.POINTER(u8p), C.POINTER(C.c_size_t)]
+    L.rg_b200_gguf_llama_config.argtypes = [vp, C.POINTER(LlamaConfig)]
+    L.rg_b200_plan_create.argtypes = [C.POINTER(LlamaConfig), C.POINTER(Options), C.POINTER(vp)]
+    L.rg_b200_plan_add_tensor.argtypes = [vp, C.c_char_p, C.c_int32, C.c_uint64, C.c_uint64, u8p, C.c_size_t]
+    L.rg_b200_plan_from_gguf.argtypes = [vp, C.POINTER(Options), C.POINTER(vp)]
+    L.rg_b200_plan_synth_tensor.argtypes = [vp, C.c_char_p, C.c_int32, C.c_uint64, C.c_uint64, C.c_uint64, C.c_float]
+    L.rg_b200_plan_tensor_nbytes.argtypes = [vp, C.c_char_p, C.POINTER(C.c_size_t)]
+    L.rg_b200_plan_read_tensor.argtypes = [vp, C.c_char_p, u8p, C.c_size_t]
+    L.rg_b200_plan_destroy.restype = None
+    L.rg_b200_plan_destroy.argtypes = [vp]
+    L.rg_b200_session_prepare.argtypes = [vp, C.POINTER(vp)]
+    L.rg_b200_session_destroy.restype = None
+    L.rg_b200_session_destroy.argtypes = [vp]
+    L.rg_b200_position.argtypes = [vp, C.c_int32]
+    L.rg_b200_max_context.argtypes = [vp]
+    L.rg_b200_vocab_size.argtypes = [vp]
+    L.rg_b200_is_full.argtypes = [vp]
+    L.rg_b200_reset_sequence.argtypes = [vp]
+    L.rg_b200_prefill.argtypes = [vp, C.c_int32, i32p, C.c_size_t, f32p]
+    L.rg_b200_decode.argtypes = [vp, i32p, C.c_int32, f32p, i32p]
+    L.rg_b200_generate_greedy.argtypes = [vp, i32p, C.c_size_t, C.c_size_t, i32p, C.POINTER(C.c_size_t), i32p]
+    L.rg_b200_decode_loop.argtypes = [vp, i32p, C.c_int32, C.c_int32, i32p, f32p]
+    L.rg_b200_report.argtypes = [vp, C.POINTER(Report)]
+    L.rg_b200_session_stream.restype = vp
+    L.rg_b200_session_stream.argtypes = [vp]
+    L.rg_b200_nccl_unique_id.argtypes = [u8p]
+    L.rg_b200_dequantize.argtypes = [C.c_int32, C.c_int32, u8p, C.c_size_t, f32p]
+    L.rg_b200_qmatmul.argtypes = [C.c_int32, C.c_int32, u8p, C.c_uint64, C.c_uint64, f32p, C.c_uint64, f32p]
+    L.rg_b200_row_gather.argtypes = [C.c_int32, C.c_int32, u8p, C.c_uint64, C.c_uint64, C.POINTER(C.c_int64),
+                                     C.c_size_t, f32p]
+    L.rg_b200_qmatmul_bench.argtypes = [C.c_int32, C.c_int32, u8p, C.c_uint64, C.c_uint64, f32p, C.c_uint64, C.c_int32,
+                                        C.c_int32, C.c_int32, f32p, f32p]
+    _lib = L
+    return L

@@ -1,0 +1,119 @@
+// Host-callable launchers of the sm_100a kernels.  Internal to the library (not part of the C ABI).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace rg {
+
+struct LaunchCfg {
+  cudaStream_t stream = nullptr;
+  bool pdl = false;    // launch with programmatic stream serialization
+  int sm_count = 148;
+  int *status = nullptr;  // device status word (see rg_device.cuh)
+};
+
+enum GemvEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2 };
+
+// y = x . W^T for packed W given as up to three row segments that share K (virtual rows are the
+// concatenation).  EPI_SWIGLU pairs row r of segment 0 (gate) with row r of segment 1 (up) and
+// writes silu(gate) * up straight into the packed-activation buffer of the next GEMV.
+struct GemvArgs {
+  int type = 0;  // RG_TYPE_Q4_0 or RG_TYPE_Q8_0
+  const uint8_t *w[3] = {nullptr, nullptr, nullptr};
+  int seg_rows[3] = {0, 0, 0};
+  int nseg = 1;
+  int k = 0;               // multiple of 256
+  const void *xpack = nullptr;
+  int batch = 1;           // 1..8
+  int epi = EPI_STORE;
+  float *y = nullptr;      // EPI_STORE: y[b*ldy + row] = v;  EPI_RESIDUAL: y[b*ldy + row] += v
+  int ldy = 0;
+  void *ypack = nullptr;   // EPI_SWIGLU: packed output with K' = seg_rows[0]
+};
+cudaError_t launch_qgemv(const GemvArgs &a, const LaunchCfg &cfg);
+size_t xpack_bytes(int k, int batch);  // K rounded up to a whole 32-element block
+
+// Dense (F32/F16) weight GEMV for tensors the block formats cannot hold (K % 32 != 0) or that a
+// file stores dense.  x is plain f32 [batch, ldx]; same epilogues (EPI_SWIGLU unsupported).
+struct DenseGemvArgs {
+  int type = 0;  // RG_TYPE_F32 or RG_TYPE_F16
+  const uint8_t *w = nullptr;
+  int rows = 0, k = 0;
+  const float *x = nullptr;
+  int ldx = 0;
+  int batch = 1;
+  int epi = EPI_STORE;
+  float *y = nullptr;
+  int ldy = 0;
+};
+cudaError_t launch_dense_gemv(const DenseGemvArgs &a, const LaunchCfg &cfg);
+
+// f32 [batch, ldx] -> packed activations of K columns.
+cudaError_t launch_pack(const float *x, int ldx, int k, int batch, void *xpack, const LaunchCfg &cfg);
+// Packed activations -> f32 (used where a dense-weight GEMV follows a packed producer).
+cudaError_t launch_unpack(const void *xpack, int k, int batch, float *x, int ldx, const LaunchCfg &cfg);
+
+// Bit-exact block decode (src/gguf/quantization/blocks.rs:1244-1257,1493-1505).  status receives
+// DEV_NON_FINITE when a scale or a decoded value is not finite.
+cudaError_t launch_dequantize(int type, const uint8_t *bytes, size_t elements, float *out, const LaunchCfg &cfg);
+// Embedding row gather: out[c, :] = decode(row ids[c]); ids validated on the host beforehand.
+cudaError_t launch_row_gather(int type, const uint8_t *bytes, int cols, const int32_t *ids, int count, float *out, int ldo,
+                              const LaunchCfg &cfg);
+
+// RMSNorm of x[col, :d] with weight w, result written as packed activations (column c of
+// `cols`; col_map (nullable) selects source columns) and optionally as plain f32 (y, nullable).
+cudaError_t launch_rmsnorm_pack(const float *x, int ldx, const float *w, int d, float eps, int cols, const int32_t *col_map,
+                                void *xpack, float *y, int ldy, const LaunchCfg &cfg);
+
+// De-interleave + RoPE of q and k, KV-cache append.  qkv: [cols, qw + 2*kw] raw projections.
+// q_out: [cols, heads, hd] rotated.  Caches: [seqs, kv_heads, ctx, hd] (half or float).
+struct RopeArgs {
+  const float *qkv = nullptr;
+  int cols = 0, heads = 0, kv_heads = 0, hd = 0, ctx = 0;
+  const int32_t *col_seq = nullptr;  // sequence of each column
+  const int32_t *col_pos = nullptr;  // absolute position of each column
+  const float *cos_t = nullptr;      // [ctx, hd/2]
+  const float *sin_t = nullptr;
+  float *q_out = nullptr;
+  void *k_cache = nullptr, *v_cache = nullptr;
+  bool kv_f32 = false;
+};
+cudaError_t launch_rope_append(const RopeArgs &a, const LaunchCfg &cfg);
+
+// Split-context GQA attention for one new token per column, then the combine that writes the
+// packed activations of the output projection.  scratch: see attn_scratch_floats().
+struct AttnArgs {
+  const float *q = nullptr;  // [cols, heads, hd]
+  const void *k_cache = nullptr, *v_cache = nullptr;
+  bool kv_f32 = false;
+  int cols = 0, heads = 0, kv_heads = 0, hd = 0, ctx = 0;
+  const int32_t *col_seq = nullptr, *col_pos = nullptr;
+  float *scratch = nullptr;
+  void *out_pack = nullptr;  // packed [K = heads*hd], batch = cols
+  float *out_f32 = nullptr;  // optional plain copy [cols, heads*hd]
+};
+constexpr int ATTN_SPAN = 64;  // context positions per CTA of the split kernel
+size_t attn_scratch_floats(int cols, int heads, int hd, int ctx);
+cudaError_t launch_attention(const AttnArgs &a, const LaunchCfg &cfg);
+
+// Greedy selection per column with the reference's rules (generation.rs:260-287): lowest id wins
+// ties, any non-finite logit yields -1.  Also advances: next_tokens[c] = id, pos[c] += 1 when
+// advance is set.
+cudaError_t launch_argmax(const float *logits, int ld, int vocab, int cols, int32_t *out_ids, const LaunchCfg &cfg);
+cudaError_t launch_advance(const int32_t *ids, int32_t *tokens, int32_t *pos, int32_t *history, int32_t *step_counter,
+                           int cols, const LaunchCfg &cfg);
+
+// Synthetic tensors: counter-based N(0, std) then GGML quantization, all on the device.
+// row0/rows and col0/cols select the shard of the full [full_rows, full_cols] tensor.
+cudaError_t launch_synth(int type, uint8_t *out, uint64_t seed, float std, uint64_t full_cols, uint64_t row0, uint64_t rows,
+                         uint64_t col0, uint64_t cols, const LaunchCfg &cfg);
+cudaError_t launch_fill_f32(float *out, size_t n, float v, const LaunchCfg &cfg);
+// h = silu(g) * u for dense-weight gate/up projections (packed and/or plain output).
+cudaError_t launch_swiglu(const float *g, const float *u, int n, int ld, int batch, void *pack, float *out, int ldo,
+                          const LaunchCfg &cfg);
+// x[b, :n] += p[b, :n]
+cudaError_t launch_add_rows(float *x, int ldx, const float *p, int ldp, int n, int batch, const LaunchCfg &cfg);
+
+}  // namespace rg

@@ -1,0 +1,613 @@
+// The non-GEMV kernels of the decode step: block decode, embedding gather, RMSNorm (+ pack),
+// RoPE + KV append, split-context GQA attention + combine, greedy selection, dense-weight GEMV,
+// and the synthetic-tensor generator.  All are HBM/latency-bound SIMT kernels; each calls
+// pdl_wait() before touching step data so programmatic dependent launch stays transitive.
+#include <math.h>
+
+#include "../../include/rg_b200.h"
+#include "kernels.h"
+#include "rg_device.cuh"
+
+namespace rg {
+namespace {
+
+template <typename K, typename... Args>
+cudaError_t launch(K kernel, dim3 grid, dim3 block, size_t smem, const LaunchCfg &cfg, Args... args) {
+  cudaLaunchConfig_t lc{};
+  lc.gridDim = grid;
+  lc.blockDim = block;
+  lc.dynamicSmemBytes = smem;
+  lc.stream = cfg.stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = cfg.pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&lc, kernel, args...);
+}
+
+// ------------------------------------------------------------------------------ block decode
+// One element of a tensor in its GGML bytes; the f32 operation order is the reference's
+// (src/gguf/quantization/blocks.rs:1251-1254,1501-1503): (f32(nibble) - 8) * d, f32(int8) * d.
+__device__ __forceinline__ float decode_element(int type, const uint8_t *bytes, size_t e, bool *bad) {
+  if (type == RG_TYPE_F32) return reinterpret_cast<const float *>(bytes)[e];
+  if (type == RG_TYPE_F16) return half_bits_to_float(reinterpret_cast<const uint16_t *>(bytes)[e]);
+  const size_t blk = e >> 5;
+  const int lane = (int)(e & 31);
+  if (type == RG_TYPE_Q4_0) {
+    const uint8_t *b = bytes + blk * 18;
+    const float d = half_bits_to_float((uint32_t)b[0] | ((uint32_t)b[1] << 8));
+    const uint8_t packed = b[2 + (lane & 15)];
+    const int nib = (lane < 16) ? (packed & 0x0f) : (packed >> 4);
+    if (bad && !finite_f32(d)) *bad = true;
+    return __fmul_rn(__fsub_rn((float)nib, 8.0f), d);
+  }
+  const uint8_t *b = bytes + blk * 34;
+  const float d = half_bits_to_float((uint32_t)b[0] | ((uint32_t)b[1] << 8));
+  if (bad && !finite_f32(d)) *bad = true;
+  return __fmul_rn((float)(int8_t)b[2 + lane], d);
+}
+
+__global__ void dequantize_kernel(int type, const uint8_t *bytes, size_t n, float *out, int *status) {
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  bool bad = false;
+  const float v = decode_element(type, bytes, i, &bad);
+  out[i] = v;
+  if ((bad || !finite_f32(v)) && status) atomicExch(status, DEV_NON_FINITE);
+}
+
+__global__ void row_gather_kernel(int type, const uint8_t *bytes, int cols, const int32_t *ids, float *out, int ldo) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int c = blockIdx.x;
+  const size_t base = (size_t)ids[c] * (size_t)cols;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) out[(size_t)c * ldo + i] = decode_element(type, bytes, base + i, nullptr);
+}
+
+// ------------------------------------------------------------------------------ pack / unpack
+__global__ void pack_kernel(const float *x, int ldx, int k, int batch, __half *xpack) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.y;
+  if (i < k) xpack_store(xpack, 2 * batch, b, i, x[(size_t)b * ldx + i]);
+}
+__global__ void unpack_kernel(const __half *xpack, int k, int batch, float *x, int ldx) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.y;
+  if (i >= k) return;
+  const float hi = __half2float(xpack[xpack_half_index(2 * batch, i, 2 * b)]);
+  const float lo = __half2float(xpack[xpack_half_index(2 * batch, i, 2 * b + 1)]);
+  x[(size_t)b * ldx + i] = hi + lo * XPACK_LO_INV;
+}
+
+// ------------------------------------------------------------------------------ RMSNorm
+// y = (x * (1 / sqrt(mean(x^2) + eps))) * w with each step rounded to f32 like the reference
+// (src/models/transformer/layer.rs:423-443); only the order of the sum of squares differs.
+__global__ void rmsnorm_pack_kernel(const float *x, int ldx, const float *w, int d, float eps, int cols, const int32_t *col_map,
+                                    __half *xpack, float *y, int ldy) {
+  pdl_wait();
+  pdl_launch_dependents();
+  __shared__ float partial[32];
+  __shared__ float inv_s;
+  const int c = blockIdx.x;
+  const int src = col_map ? col_map[c] : c;
+  const float *xr = x + (size_t)src * ldx;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = (threadIdx.x < (blockDim.x >> 5)) ? partial[threadIdx.x] : 0.0f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) {
+      const float mean = __fdiv_rn(v, (float)d);
+      inv_s = __frcp_rn(__fsqrt_rn(__fadd_rn(mean, eps)));
+    }
+  }
+  __syncthreads();
+  const float inv = inv_s;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = __fmul_rn(__fmul_rn(xr[i], inv), w[i]);
+    if (xpack) xpack_store(xpack, 2 * cols, c, i, v);
+    if (y) y[(size_t)c * ldy + i] = v;
+  }
+}
+
+// ------------------------------------------------------------------------------ RoPE + KV append
+// De-interleave (src/models/transformer/layer.rs:481-525: out[j] = in[2j], out[half+j] = in[2j+1])
+// then split-half rotation (layer.rs:528-571) with every product and sum rounded separately.
+template <typename KV>
+__device__ __forceinline__ KV to_kv(float v);
+template <>
+__device__ __forceinline__ float to_kv<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half to_kv<__half>(float v) { return __float2half_rn(v); }
+
+template <typename KV>
+__global__ void rope_append_kernel(const float *qkv, int heads, int kv_heads, int hd, int ctx, const int32_t *col_seq,
+                                   const int32_t *col_pos, const float *cos_t, const float *sin_t, float *q_out, KV *k_cache,
+                                   KV *v_cache) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int c = blockIdx.x;
+  const int half = hd >> 1;
+  const int qw = heads * hd, kw = kv_heads * hd;
+  const int pos = col_pos[c], seq = col_seq[c];
+  const float *row = qkv + (size_t)c * (qw + 2 * kw);
+  const float *ct = cos_t + (size_t)pos * half, *st = sin_t + (size_t)pos * half;
+  const int rot_items = (heads + kv_heads) * half;
+  for (int it = threadIdx.x; it < rot_items; it += blockDim.x) {
+    const int h = it / half, i = it - h * half;
+    const float *src = row + (size_t)h * hd;  // q heads then k heads are contiguous in the row
+    const float x1 = src[2 * i], x2 = src[2 * i + 1];
+    const float cs = ct[i], sn = st[i];
+    const float y1 = __fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));
+    const float y2 = __fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn));
+    if (h < heads) {
+      float *dst = q_out + ((size_t)c * heads + h) * hd;
+      dst[i] = y1;
+      dst[half + i] = y2;
+    } else {
+      KV *dst = k_cache + (((size_t)seq * kv_heads + (h - heads)) * ctx + pos) * hd;
+      dst[i] = to_kv<KV>(y1);
+      dst[half + i] = to_kv<KV>(y2);
+    }
+  }
+  for (int it = threadIdx.x; it < kw; it += blockDim.x) {
+    const int h = it / hd, j = it - h * hd;
+    v_cache[(((size_t)seq * kv_heads + h) * ctx + pos) * hd + j] = to_kv<KV>(row[qw + kw + it]);
+  }
+}
+
+// ------------------------------------------------------------------------------ attention
+// Scratch per (column, head, split): [m, l, out[hd]].
+constexpr int ATT_THREADS = 128;
+constexpr int MAX_GROUP = 8;
+constexpr int MAX_HD = 128;
+
+__device__ __forceinline__ float kv_load(const float *p) { return *p; }
+__device__ __forceinline__ float kv_load(const __half *p) { return __half2float(*p); }
+
+// Softmax pieces follow src/ir/attention.rs:495-558: e = exp2((s - m) * log2(e)); the scores are
+// q.k / f32(sqrt(hd)) (attention.rs:1183-1188).  Query head h reads kv head h / (H/KV) (:1226-1240).
+template <typename KV>
+__global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(const float *q, const KV *k_cache, const KV *v_cache, int heads,
+                                                                 int kv_heads, int hd, int ctx, const int32_t *col_seq,
+                                                                 const int32_t *col_pos, float *scratch, int max_splits) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int split = blockIdx.x, kvh = blockIdx.y, c = blockIdx.z;
+  const int pos = col_pos[c];
+  const int p0 = split * ATTN_SPAN;
+  if (p0 > pos) return;
+  const int np = min(ATTN_SPAN, pos + 1 - p0);
+  const int group = heads / kv_heads;
+  const int seq = col_seq[c];
+  __shared__ float qs[MAX_GROUP][MAX_HD];
+  __shared__ float sc[MAX_GROUP][ATTN_SPAN];
+  __shared__ float ml[MAX_GROUP][2];
+  const int tid = threadIdx.x;
+  for (int i = tid; i < group * hd; i += ATT_THREADS) {
+    const int gq = i / hd, j = i - gq * hd;
+    qs[gq][j] = q[((size_t)c * heads + (size_t)kvh * group + gq) * hd + j];
+  }
+  __syncthreads();
+  const KV *kbase = k_cache + (((size_t)seq * kv_heads + kvh) * ctx + p0) * hd;
+  const KV *vbase = v_cache + (((size_t)seq * kv_heads + kvh) * ctx + p0) * hd;
+  const float inv_scale = (float)(1.0 / (1.0 / sqrt((double)hd)));
+  {
+    // two threads per position, each half of the head dimension
+    const int p = tid >> 1, part = tid & 1;
+    const int hh = hd >> 1;
+    float dots[MAX_GROUP];
+#pragma unroll
+    for (int gq = 0; gq < MAX_GROUP; ++gq) dots[gq] = 0.0f;
+    if (p < np) {
+      const KV *kr = kbase + (size_t)p * hd + part * hh;
+      for (int j = 0; j < hh; ++j) {
+        const float kv = kv_load(kr + j);
+#pragma unroll
+        for (int gq = 0; gq < MAX_GROUP; ++gq)
+          if (gq < group) dots[gq] = fmaf(qs[gq][part * hh + j], kv, dots[gq]);
+      }
+    }
+#pragma unroll
+    for (int gq = 0; gq < MAX_GROUP; ++gq) {
+      const float other = __shfl_xor_sync(0xffffffffu, dots[gq], 1);
+      if (gq < group && part == 0 && p < ATTN_SPAN) sc[gq][p] = (p < np) ? __fdiv_rn(dots[gq] + other, inv_scale) : -INFINITY;
+    }
+  }
+  __syncthreads();
+  {
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int gq = warp; gq < group; gq += ATT_THREADS / 32) {
+      const float s0 = sc[gq][lane], s1 = sc[gq][lane + 32];
+      const float m = warp_max(fmaxf(s0, s1));
+      const float e0 = (lane < np) ? exp2f(__fmul_rn(__fsub_rn(s0, m), 1.44269504088896340736f)) : 0.0f;
+      const float e1 = (lane + 32 < np) ? exp2f(__fmul_rn(__fsub_rn(s1, m), 1.44269504088896340736f)) : 0.0f;
+      sc[gq][lane] = e0;
+      sc[gq][lane + 32] = e1;
+      const float l = warp_sum(e0 + e1);
+      if (lane == 0) {
+        ml[gq][0] = m;
+        ml[gq][1] = l;
+      }
+    }
+  }
+  __syncthreads();
+  if (tid < hd) {
+    float out[MAX_GROUP];
+#pragma unroll
+    for (int gq = 0; gq < MAX_GROUP; ++gq) out[gq] = 0.0f;
+    for (int p = 0; p < np; ++p) {
+      const float v = kv_load(vbase + (size_t)p * hd + tid);
+#pragma unroll
+      for (int gq = 0; gq < MAX_GROUP; ++gq)
+        if (gq < group) out[gq] = fmaf(sc[gq][p], v, out[gq]);
+    }
+#pragma unroll
+    for (int gq = 0; gq < MAX_GROUP; ++gq)
+      if (gq < group) {
+        float *dst = scratch + (((size_t)c * heads + (size_t)kvh * group + gq) * max_splits + split) * (hd + 2);
+        if (tid == 0) {
+          dst[0] = ml[gq][0];
+          dst[1] = ml[gq][1];
+        }
+        dst[2 + tid] = out[gq];
+      }
+  }
+}
+
+__global__ void attn_combine_kernel(const float *scratch, int heads, int hd, const int32_t *col_pos, int max_splits, int cols,
+                                    __half *out_pack, float *out_f32) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int h = blockIdx.x, c = blockIdx.y, tid = threadIdx.x;
+  const int ns = col_pos[c] / ATTN_SPAN + 1;
+  const float *base = scratch + ((size_t)c * heads + h) * max_splits * (hd + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < ns; ++s) M = fmaxf(M, base[(size_t)s * (hd + 2)]);
+  float L = 0.0f, acc = 0.0f;
+  for (int s = 0; s < ns; ++s) {
+    const float *ps = base + (size_t)s * (hd + 2);
+    const float wgt = exp2f(__fmul_rn(__fsub_rn(ps[0], M), 1.44269504088896340736f));
+    L = fmaf(ps[1], wgt, L);
+    if (tid < hd) acc = fmaf(ps[2 + tid], wgt, acc);
+  }
+  if (tid < hd) {
+    const float v = __fmul_rn(acc, __frcp_rn(L));
+    const int k = h * hd + tid;
+    if (out_pack) xpack_store(out_pack, 2 * cols, c, k, v);
+    if (out_f32) out_f32[(size_t)c * heads * hd + k] = v;
+  }
+}
+
+// ------------------------------------------------------------------------------ greedy selection
+// src/models/transformer/generation.rs:260-287: strict '>' so the lowest id wins ties; any
+// non-finite logit is an error, reported as id -1 (the sentinel of metal_step.rs:964-987).
+__global__ void argmax_kernel(const float *logits, int ld, int vocab, int32_t *out_ids) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int c = blockIdx.x;
+  const float *row = logits + (size_t)c * ld;
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  int bad = 0;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = row[i];
+    if (!finite_f32(v)) bad = 1;
+    if (v > best || idx == 0x7fffffff) {
+      best = v;
+      idx = i;
+    }
+  }
+  __shared__ float sv[32];
+  __shared__ int si[32], sb[32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    bad |= __shfl_xor_sync(0xffffffffu, bad, o);
+    if (ov > best || (ov == best && oi < idx)) {
+      best = ov;
+      idx = oi;
+    }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    sv[warp] = best;
+    si[warp] = idx;
+    sb[warp] = bad;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    best = (lane < nw) ? sv[lane] : -INFINITY;
+    idx = (lane < nw) ? si[lane] : 0x7fffffff;
+    bad = (lane < nw) ? sb[lane] : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      bad |= __shfl_xor_sync(0xffffffffu, bad, o);
+      if (ov > best || (ov == best && oi < idx)) {
+        best = ov;
+        idx = oi;
+      }
+    }
+    if (lane == 0) out_ids[c] = bad ? -1 : idx;
+  }
+}
+
+__global__ void advance_kernel(const int32_t *ids, int32_t *tokens, int32_t *pos, int32_t *history, int32_t *step_counter,
+                               int cols) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int c = threadIdx.x;
+  const int step = *step_counter;
+  if (c < cols) {
+    const int id = ids[c];
+    tokens[c] = id < 0 ? 0 : id;
+    pos[c] += 1;
+    if (history) history[(size_t)step * cols + c] = id;
+  }
+  __syncthreads();
+  if (c == 0) *step_counter = step + 1;
+}
+
+// ------------------------------------------------------------------------------ dense GEMV
+template <typename W>
+__device__ __forceinline__ float w_load(const W *p);
+template <>
+__device__ __forceinline__ float w_load<float>(const float *p) { return *p; }
+template <>
+__device__ __forceinline__ float w_load<__half>(const __half *p) { return __half2float(*p); }
+
+template <typename W>
+__global__ void dense_gemv_kernel(const W *w, int rows, int k, const float *x, int ldx, int batch, int epi, float *y, int ldy) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= rows) return;
+  const W *wr = w + (size_t)row * k;
+  float acc[8];
+#pragma unroll
+  for (int b = 0; b < 8; ++b) acc[b] = 0.0f;
+  for (int i = lane; i < k; i += 32) {
+    const float wv = w_load<W>(wr + i);
+#pragma unroll
+    for (int b = 0; b < 8; ++b)
+      if (b < batch) acc[b] = fmaf(x[(size_t)b * ldx + i], wv, acc[b]);
+  }
+#pragma unroll
+  for (int b = 0; b < 8; ++b) {
+    if (b >= batch) break;
+    const float v = warp_sum(acc[b]);
+    if (lane == 0) {
+      float *dst = y + (size_t)b * ldy + row;
+      *dst = (epi == EPI_RESIDUAL) ? __fadd_rn(*dst, v) : v;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ synthetic tensors
+__device__ __forceinline__ uint64_t splitmix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+// Sum of sixteen 16-bit uniforms (Irwin-Hall, n = 16) centred and scaled to unit variance:
+// integer arithmetic up to one float multiply, so any host can reproduce it bit for bit.
+__device__ __forceinline__ float synth_normal(uint64_t seed, uint64_t element) {
+  uint32_t sum = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint64_t r = splitmix64(seed * 0xD1342543DE82EF95ull + element * 4 + i);
+    sum += (uint32_t)(r & 0xffff) + (uint32_t)((r >> 16) & 0xffff) + (uint32_t)((r >> 32) & 0xffff) + (uint32_t)(r >> 48);
+  }
+  return (float)((int)sum - 524280) * (1.0f / 75674.5234375f);
+}
+
+__global__ void synth_kernel(int type, uint8_t *out, uint64_t seed, float std, uint64_t full_cols, uint64_t row0, uint64_t rows,
+                             uint64_t col0, uint64_t cols) {
+  const uint64_t bpr = cols / 32;  // 32-element groups per local row (dense types use the same tiling)
+  const uint64_t gidx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gidx >= rows * bpr) return;
+  const uint64_t r = gidx / bpr, cb = gidx - r * bpr;
+  const uint64_t e0 = (row0 + r) * full_cols + col0 + cb * 32;
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(synth_normal(seed, e0 + i), std);
+  if (type == RG_TYPE_F32) {
+    float *o = reinterpret_cast<float *>(out) + gidx * 32;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) o[i] = v[i];
+  } else if (type == RG_TYPE_F16) {
+    __half *o = reinterpret_cast<__half *>(out) + gidx * 32;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) o[i] = __float2half_rn(v[i]);
+  } else if (type == RG_TYPE_Q8_0) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+    uint16_t *o = reinterpret_cast<uint16_t *>(out + gidx * 34);
+    o[0] = __half_as_ushort(__float2half_rn(d));
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int q0 = (int)roundf(__fmul_rn(v[2 * i], id)), q1 = (int)roundf(__fmul_rn(v[2 * i + 1], id));
+      o[1 + i] = (uint16_t)((q0 & 0xff) | ((q1 & 0xff) << 8));
+    }
+  } else {  // Q4_0
+    float amax = 0.0f, mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (amax < fabsf(v[i])) {
+        amax = fabsf(v[i]);
+        mx = v[i];
+      }
+    const float d = __fdiv_rn(mx, -8.0f);
+    const float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+    uint16_t *o = reinterpret_cast<uint16_t *>(out + gidx * 18);
+    o[0] = __half_as_ushort(__float2half_rn(d));
+    uint8_t q[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int qi = (int)__fadd_rn(__fmul_rn(v[i], id), 8.5f);
+      q[i] = (uint8_t)min(15, qi);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t b0 = q[2 * i] | (q[2 * i + 16] << 4), b1 = q[2 * i + 1] | (q[2 * i + 17] << 4);
+      o[1 + i] = (uint16_t)(b0 | (b1 << 8));
+    }
+  }
+}
+
+// Dense (F32/F16) synthetic tensor: one element per thread, any column count.
+__global__ void synth_dense_kernel(int type, uint8_t *out, uint64_t seed, float std, uint64_t full_cols, uint64_t row0,
+                                   uint64_t rows, uint64_t col0, uint64_t cols) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * cols) return;
+  const uint64_t r = i / cols, c = i - r * cols;
+  const float v = __fmul_rn(synth_normal(seed, (row0 + r) * full_cols + col0 + c), std);
+  if (type == RG_TYPE_F32)
+    reinterpret_cast<float *>(out)[i] = v;
+  else
+    reinterpret_cast<__half *>(out)[i] = __float2half_rn(v);
+}
+
+// h = silu(g) * u for dense-weight gate/up projections; written packed and/or plain.
+__global__ void swiglu_kernel(const float *g, const float *u, int n, int ld, int batch, __half *pack, float *out, int ldo) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+  if (i >= n) return;
+  const float h = swiglu(g[(size_t)b * ld + i], u[(size_t)b * ld + i]);
+  if (pack) xpack_store(pack, 2 * batch, b, i, h);
+  if (out) out[(size_t)b * ldo + i] = h;
+}
+
+// x[b, :] += partial[b, :] (residual add after a tensor-parallel all-reduce).
+__global__ void add_rows_kernel(float *x, int ldx, const float *p, int ldp, int n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+  if (i < n) x[(size_t)b * ldx + i] = __fadd_rn(x[(size_t)b * ldx + i], p[(size_t)b * ldp + i]);
+}
+
+__global__ void fill_kernel(float *out, size_t n, float v) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = v;
+}
+
+}  // namespace
+
+// ============================================================================== launchers
+cudaError_t launch_dequantize(int type, const uint8_t *bytes, size_t n, float *out, const LaunchCfg &cfg) {
+  if (n == 0) return cudaSuccess;
+  return launch(dequantize_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, cfg, type, bytes, n, out, cfg.status);
+}
+cudaError_t launch_row_gather(int type, const uint8_t *bytes, int cols, const int32_t *ids, int count, float *out, int ldo,
+                              const LaunchCfg &cfg) {
+  if (count == 0) return cudaSuccess;
+  return launch(row_gather_kernel, dim3(count), dim3(256), 0, cfg, type, bytes, cols, ids, out, ldo);
+}
+cudaError_t launch_pack(const float *x, int ldx, int k, int batch, void *xpack, const LaunchCfg &cfg) {
+  return launch(pack_kernel, dim3((k + 255) / 256, batch), dim3(256), 0, cfg, x, ldx, k, batch, static_cast<__half *>(xpack));
+}
+cudaError_t launch_unpack(const void *xpack, int k, int batch, float *x, int ldx, const LaunchCfg &cfg) {
+  return launch(unpack_kernel, dim3((k + 255) / 256, batch), dim3(256), 0, cfg, static_cast<const __half *>(xpack), k, batch, x,
+                ldx);
+}
+cudaError_t launch_rmsnorm_pack(const float *x, int ldx, const float *w, int d, float eps, int cols, const int32_t *col_map,
+                                void *xpack, float *y, int ldy, const LaunchCfg &cfg) {
+  return launch(rmsnorm_pack_kernel, dim3(cols), dim3(512), 0, cfg, x, ldx, w, d, eps, cols, col_map, static_cast<__half *>(xpack),
+                y, ldy);
+}
+cudaError_t launch_rope_append(const RopeArgs &a, const LaunchCfg &cfg) {
+  if (a.kv_f32)
+    return launch(rope_append_kernel<float>, dim3(a.cols), dim3(256), 0, cfg, a.qkv, a.heads, a.kv_heads, a.hd, a.ctx, a.col_seq,
+                  a.col_pos, a.cos_t, a.sin_t, a.q_out, static_cast<float *>(a.k_cache), static_cast<float *>(a.v_cache));
+  return launch(rope_append_kernel<__half>, dim3(a.cols), dim3(256), 0, cfg, a.qkv, a.heads, a.kv_heads, a.hd, a.ctx, a.col_seq,
+                a.col_pos, a.cos_t, a.sin_t, a.q_out, static_cast<__half *>(a.k_cache), static_cast<__half *>(a.v_cache));
+}
+size_t attn_scratch_floats(int cols, int heads, int hd, int ctx) {
+  const int splits = (ctx + ATTN_SPAN - 1) / ATTN_SPAN;
+  return (size_t)cols * heads * splits * (hd + 2);
+}
+cudaError_t launch_attention(const AttnArgs &a, const LaunchCfg &cfg) {
+  if (a.hd > MAX_HD || (a.hd & 1) || a.heads % a.kv_heads || a.heads / a.kv_heads > MAX_GROUP) return cudaErrorInvalidValue;
+  const int splits = (a.ctx + ATTN_SPAN - 1) / ATTN_SPAN;
+  cudaError_t e;
+  if (a.kv_f32)
+    e = launch(attn_split_kernel<float>, dim3(splits, a.kv_heads, a.cols), dim3(ATT_THREADS), 0, cfg, a.q,
+               static_cast<const float *>(a.k_cache), static_cast<const float *>(a.v_cache), a.heads, a.kv_heads, a.hd, a.ctx,
+               a.col_seq, a.col_pos, a.scratch, splits);
+  else
+    e = launch(attn_split_kernel<__half>, dim3(splits, a.kv_heads, a.cols), dim3(ATT_THREADS), 0, cfg, a.q,
+               static_cast<const __half *>(a.k_cache), static_cast<const __half *>(a.v_cache), a.heads, a.kv_heads, a.hd, a.ctx,
+               a.col_seq, a.col_pos, a.scratch, splits);
+  if (e != cudaSuccess) return e;
+  return launch(attn_combine_kernel, dim3(a.heads, a.cols), dim3(MAX_HD), 0, cfg, (const float *)a.scratch, a.heads, a.hd,
+                a.col_pos, splits, a.cols, static_cast<__half *>(a.out_pack), a.out_f32);
+}
+cudaError_t launch_argmax(const float *logits, int ld, int vocab, int cols, int32_t *out_ids, const LaunchCfg &cfg) {
+  return launch(argmax_kernel, dim3(cols), dim3(1024), 0, cfg, logits, ld, vocab, out_ids);
+}
+cudaError_t launch_advance(const int32_t *ids, int32_t *tokens, int32_t *pos, int32_t *history, int32_t *step_counter, int cols,
+                           const LaunchCfg &cfg) {
+  return launch(advance_kernel, dim3(1), dim3(32), 0, cfg, ids, tokens, pos, history, step_counter, cols);
+}
+cudaError_t launch_dense_gemv(const DenseGemvArgs &a, const LaunchCfg &cfg) {
+  if (a.batch < 1 || a.batch > 8 || a.epi == EPI_SWIGLU) return cudaErrorInvalidValue;
+  const dim3 grid((a.rows + 7) / 8), block(256);
+  if (a.type == RG_TYPE_F32)
+    return launch(dense_gemv_kernel<float>, grid, block, 0, cfg, reinterpret_cast<const float *>(a.w), a.rows, a.k, a.x, a.ldx,
+                  a.batch, a.epi, a.y, a.ldy);
+  if (a.type == RG_TYPE_F16)
+    return launch(dense_gemv_kernel<__half>, grid, block, 0, cfg, reinterpret_cast<const __half *>(a.w), a.rows, a.k, a.x, a.ldx,
+                  a.batch, a.epi, a.y, a.ldy);
+  return cudaErrorInvalidValue;
+}
+cudaError_t launch_synth(int type, uint8_t *out, uint64_t seed, float std, uint64_t full_cols, uint64_t row0, uint64_t rows,
+                         uint64_t col0, uint64_t cols, const LaunchCfg &cfg) {
+  LaunchCfg plain = cfg;
+  plain.pdl = false;
+  if (type == RG_TYPE_F32 || type == RG_TYPE_F16) {
+    const uint64_t n = rows * cols;
+    if (n == 0) return cudaSuccess;
+    return launch(synth_dense_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, plain, type, out, seed, std, full_cols,
+                  row0, rows, col0, cols);
+  }
+  if (cols % 32 || col0 % 32) return cudaErrorInvalidValue;
+  const uint64_t groups = rows * (cols / 32);
+  if (groups == 0) return cudaSuccess;
+  return launch(synth_kernel, dim3((unsigned)((groups + 127) / 128)), dim3(128), 0, plain, type, out, seed, std, full_cols, row0,
+                rows, col0, cols);
+}
+cudaError_t launch_swiglu(const float *g, const float *u, int n, int ld, int batch, void *pack, float *out, int ldo,
+                          const LaunchCfg &cfg) {
+  return launch(swiglu_kernel, dim3((n + 255) / 256, batch), dim3(256), 0, cfg, g, u, n, ld, batch, static_cast<__half *>(pack),
+                out, ldo);
+}
+cudaError_t launch_add_rows(float *x, int ldx, const float *p, int ldp, int n, int batch, const LaunchCfg &cfg) {
+  return launch(add_rows_kernel, dim3((n + 255) / 256, batch), dim3(256), 0, cfg, x, ldx, p, ldp, n);
+}
+cudaError_t launch_fill_f32(float *out, size_t n, float v, const LaunchCfg &cfg) {
+  if (n == 0) return cudaSuccess;
+  LaunchCfg plain = cfg;
+  plain.pdl = false;
+  return launch(fill_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, plain, out, n, v);
+}
+
+}  // namespace rg

@@ -1,0 +1,282 @@
+// Operator-level C ABI entry points: host buffers in, host buffers out, plus the device-resident
+// GEMV benchmark.  Each call uploads its inputs, runs the sm_100a kernels and reads the result
+// back; there is no CPU path behind any of them.
+#include <cuda_runtime.h>
+#include <string.h>
+
+#include <algorithm>
+#include <string>
+#include <vector>
+
+#include "../../include/rg_b200.h"
+#include "gguf.h"
+#include "kernels.h"
+
+namespace rg {
+extern thread_local std::string g_last_error;
+}
+using namespace rg;
+
+namespace {
+
+int32_t fail(int32_t status, const std::string &why) {
+  g_last_error = why;
+  return status;
+}
+
+#define OP_CUDA(expr)                                                                                   \
+  do {                                                                                                  \
+    cudaError_t e__ = (expr);                                                                           \
+    if (e__ != cudaSuccess)                                                                             \
+      return fail(e__ == cudaErrorMemoryAllocation ? RG_OUT_OF_MEMORY : RG_CUDA_ERROR,                  \
+                  std::string(#expr) + ": " + cudaGetErrorString(e__) + " (" + __FILE__ + ":" +         \
+                      std::to_string(__LINE__) + ")");                                                  \
+  } while (0)
+
+// Frees device buffers and the stream when an operator call returns, on every path.
+struct Scope {
+  std::vector<void *> bufs;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  ~Scope() {
+    for (void *p : bufs) cudaFree(p);
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    if (stream) cudaStreamDestroy(stream);
+  }
+  template <typename T>
+  cudaError_t alloc(T **p, size_t bytes) {
+    void *raw = nullptr;
+    cudaError_t e = cudaMalloc(&raw, bytes ? bytes : 16);
+    if (e == cudaSuccess) bufs.push_back(raw);
+    *p = static_cast<T *>(raw);
+    return e;
+  }
+};
+
+int32_t open_scope(int32_t device, Scope *sc, LaunchCfg *cfg, int **d_status) {
+  OP_CUDA(cudaSetDevice(device));
+  OP_CUDA(cudaStreamCreateWithFlags(&sc->stream, cudaStreamNonBlocking));
+  int sms = 148;
+  OP_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  OP_CUDA(sc->alloc(d_status, sizeof(int)));
+  OP_CUDA(cudaMemsetAsync(*d_status, 0, sizeof(int), sc->stream));
+  cfg->stream = sc->stream;
+  cfg->pdl = false;
+  cfg->sm_count = sms;
+  cfg->status = *d_status;
+  return RG_OK;
+}
+
+int32_t check_weight(int32_t type, uint64_t n, uint64_t k, size_t *nbytes) {
+  if (!block_elements(type)) return fail(RG_UNSUPPORTED_TYPE, "ggml type " + std::to_string(type) + " is not supported");
+  if (k % (uint64_t)block_elements(type)) return fail(RG_SHAPE_MISMATCH, "K is not a multiple of the block size");
+  *nbytes = (size_t)(n * (k / (uint64_t)block_elements(type)) * (uint64_t)block_bytes(type));
+  return RG_OK;
+}
+
+int32_t scan_scales(int32_t type, const uint8_t *bytes, size_t nbytes) {
+  if (type != RG_TYPE_Q4_0 && type != RG_TYPE_Q8_0) return RG_OK;
+  const size_t bb = (size_t)block_bytes(type);
+  for (size_t b = 0; b < nbytes / bb; ++b)
+    if (((bytes[b * bb + 1] >> 2) & 0x1f) == 0x1f) return fail(RG_NON_FINITE_SCALE, "block " + std::to_string(b));
+  return RG_OK;
+}
+
+// Launches y[m,n] = x[m,k] . W[n,k]^T in column chunks of at most eight activation rows.
+int32_t run_matmul(int32_t type, const uint8_t *d_w, uint64_t n, uint64_t k, const float *d_x, uint64_t m, float *d_y,
+                   void *d_pack, const LaunchCfg &cfg) {
+  const bool packed = (type == RG_TYPE_Q4_0 || type == RG_TYPE_Q8_0);
+  for (uint64_t m0 = 0; m0 < m; m0 += 8) {
+    const int batch = (int)std::min<uint64_t>(8, m - m0);
+    if (packed) {
+      OP_CUDA(launch_pack(d_x + m0 * k, (int)k, (int)k, batch, d_pack, cfg));
+      GemvArgs a;
+      a.type = type;
+      a.w[0] = d_w;
+      a.seg_rows[0] = (int)n;
+      a.nseg = 1;
+      a.k = (int)k;
+      a.xpack = d_pack;
+      a.batch = batch;
+      a.epi = EPI_STORE;
+      a.y = d_y + m0 * n;
+      a.ldy = (int)n;
+      OP_CUDA(launch_qgemv(a, cfg));
+    } else {
+      DenseGemvArgs a;
+      a.type = type;
+      a.w = d_w;
+      a.rows = (int)n;
+      a.k = (int)k;
+      a.x = d_x + m0 * k;
+      a.ldx = (int)k;
+      a.batch = batch;
+      a.epi = EPI_STORE;
+      a.y = d_y + m0 * n;
+      a.ldy = (int)n;
+      OP_CUDA(launch_dense_gemv(a, cfg));
+    }
+  }
+  return RG_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t rg_b200_dequantize(int32_t device, int32_t type, const uint8_t *bytes, size_t elements, float *out) {
+  if (!bytes || (!out && elements)) return fail(RG_INVALID_ARGUMENT, "null argument");
+  size_t nbytes;
+  int32_t rc = check_weight(type, 1, elements, &nbytes);
+  if (rc) return rc;
+  if (elements == 0) return RG_OK;
+  Scope sc;
+  LaunchCfg cfg;
+  int *d_status;
+  if ((rc = open_scope(device, &sc, &cfg, &d_status))) return rc;
+  uint8_t *d_in;
+  float *d_out;
+  OP_CUDA(sc.alloc(&d_in, nbytes));
+  OP_CUDA(sc.alloc(&d_out, elements * sizeof(float)));
+  OP_CUDA(cudaMemcpyAsync(d_in, bytes, nbytes, cudaMemcpyHostToDevice, sc.stream));
+  OP_CUDA(launch_dequantize(type, d_in, elements, d_out, cfg));
+  int status = 0;
+  OP_CUDA(cudaMemcpyAsync(out, d_out, elements * sizeof(float), cudaMemcpyDeviceToHost, sc.stream));
+  OP_CUDA(cudaMemcpyAsync(&status, d_status, sizeof(int), cudaMemcpyDeviceToHost, sc.stream));
+  OP_CUDA(cudaStreamSynchronize(sc.stream));
+  if (status == 2) return fail(RG_NON_FINITE_SCALE, "a block decodes to a non-finite value");
+  if (status) return fail(RG_CUDA_ERROR, "device status " + std::to_string(status));
+  return RG_OK;
+}
+
+int32_t rg_b200_qmatmul(int32_t device, int32_t type, const uint8_t *weight, uint64_t n, uint64_t k, const float *activation,
+                        uint64_t m, float *out) {
+  if (!weight || !activation || !out) return fail(RG_INVALID_ARGUMENT, "null argument");
+  size_t wbytes;
+  int32_t rc = check_weight(type, n, k, &wbytes);
+  if (rc) return rc;
+  if (n == 0 || m == 0) return RG_OK;
+  const bool packed = (type == RG_TYPE_Q4_0 || type == RG_TYPE_Q8_0);
+  if (k == 0) {  // empty contraction: zeros (src/matmul/quantized.rs:512-560)
+    memset(out, 0, sizeof(float) * m * n);
+    return RG_OK;
+  }
+  if (packed && k % 256) return fail(RG_UNSUPPORTED_GEOMETRY, "packed weights need K to be a multiple of 256");
+  if ((rc = scan_scales(type, weight, wbytes))) return rc;
+  Scope sc;
+  LaunchCfg cfg;
+  int *d_status;
+  if ((rc = open_scope(device, &sc, &cfg, &d_status))) return rc;
+  uint8_t *d_w, *d_pack;
+  float *d_x, *d_y;
+  OP_CUDA(sc.alloc(&d_w, wbytes));
+  OP_CUDA(sc.alloc(&d_x, sizeof(float) * m * k));
+  OP_CUDA(sc.alloc(&d_y, sizeof(float) * m * n));
+  OP_CUDA(sc.alloc(&d_pack, xpack_bytes((int)k, 8)));
+  OP_CUDA(cudaMemcpyAsync(d_w, weight, wbytes, cudaMemcpyHostToDevice, sc.stream));
+  OP_CUDA(cudaMemcpyAsync(d_x, activation, sizeof(float) * m * k, cudaMemcpyHostToDevice, sc.stream));
+  if ((rc = run_matmul(type, d_w, n, k, d_x, m, d_y, d_pack, cfg))) return rc;
+  int status = 0;
+  OP_CUDA(cudaMemcpyAsync(out, d_y, sizeof(float) * m * n, cudaMemcpyDeviceToHost, sc.stream));
+  OP_CUDA(cudaMemcpyAsync(&status, d_status, sizeof(int), cudaMemcpyDeviceToHost, sc.stream));
+  OP_CUDA(cudaStreamSynchronize(sc.stream));
+  if (status == 1) return fail(RG_TIMEOUT, "a bounded device-side wait gave up");
+  if (status) return fail(RG_CUDA_ERROR, "device status " + std::to_string(status));
+  return RG_OK;
+}
+
+int32_t rg_b200_row_gather(int32_t device, int32_t type, const uint8_t *weight, uint64_t rows, uint64_t cols,
+                           const int64_t *indices, size_t count, float *out) {
+  if (!weight || (!indices && count) || (!out && count)) return fail(RG_INVALID_ARGUMENT, "null argument");
+  size_t wbytes;
+  int32_t rc = check_weight(type, rows, cols, &wbytes);
+  if (rc) return rc;
+  // every index is validated before any decode (src/gguf/quantization/row_gather.rs:187-226)
+  std::vector<int32_t> ids(count);
+  for (size_t i = 0; i < count; ++i) {
+    if (indices[i] < 0 || (uint64_t)indices[i] >= rows) return fail(RG_TOKEN_OUT_OF_RANGE, "index " + std::to_string(indices[i]) + " at " + std::to_string(i));
+    ids[i] = (int32_t)indices[i];
+  }
+  if (count == 0 || cols == 0) return RG_OK;
+  if ((rc = scan_scales(type, weight, wbytes))) return rc;
+  Scope sc;
+  LaunchCfg cfg;
+  int *d_status;
+  if ((rc = open_scope(device, &sc, &cfg, &d_status))) return rc;
+  uint8_t *d_w;
+  int32_t *d_ids;
+  float *d_out;
+  OP_CUDA(sc.alloc(&d_w, wbytes));
+  OP_CUDA(sc.alloc(&d_ids, sizeof(int32_t) * count));
+  OP_CUDA(sc.alloc(&d_out, sizeof(float) * count * cols));
+  OP_CUDA(cudaMemcpyAsync(d_w, weight, wbytes, cudaMemcpyHostToDevice, sc.stream));
+  OP_CUDA(cudaMemcpyAsync(d_ids, ids.data(), sizeof(int32_t) * count, cudaMemcpyHostToDevice, sc.stream));
+  OP_CUDA(launch_row_gather(type, d_w, (int)cols, d_ids, (int)count, d_out, (int)cols, cfg));
+  OP_CUDA(cudaMemcpyAsync(out, d_out, sizeof(float) * count * cols, cudaMemcpyDeviceToHost, sc.stream));
+  OP_CUDA(cudaStreamSynchronize(sc.stream));
+  return RG_OK;
+}
+
+int32_t rg_b200_qmatmul_bench(int32_t device, int32_t type, const uint8_t *weight, uint64_t n, uint64_t k, const float *activation,
+                              uint64_t m, int32_t rotate, int32_t iters, int32_t warmup, float *out, float *kernel_ms) {
+  if (!weight || !activation || !kernel_ms) return fail(RG_INVALID_ARGUMENT, "null argument");
+  if (m < 1 || m > 8 || iters < 1 || rotate < 1) return fail(RG_INVALID_ARGUMENT, "m in 1..8, iters >= 1, rotate >= 1");
+  size_t wbytes;
+  int32_t rc = check_weight(type, n, k, &wbytes);
+  if (rc) return rc;
+  const bool packed = (type == RG_TYPE_Q4_0 || type == RG_TYPE_Q8_0);
+  if (!packed) return fail(RG_UNSUPPORTED_TYPE, "the benchmark covers packed weights");
+  if (k == 0 || k % 256) return fail(RG_UNSUPPORTED_GEOMETRY, "packed weights need K to be a multiple of 256");
+  Scope sc;
+  LaunchCfg cfg;
+  int *d_status;
+  if ((rc = open_scope(device, &sc, &cfg, &d_status))) return rc;
+  std::vector<uint8_t *> copies((size_t)rotate);
+  for (int r = 0; r < rotate; ++r) {
+    OP_CUDA(sc.alloc(&copies[(size_t)r], wbytes));
+    if (r == 0) OP_CUDA(cudaMemcpyAsync(copies[0], weight, wbytes, cudaMemcpyHostToDevice, sc.stream));
+    else OP_CUDA(cudaMemcpyAsync(copies[(size_t)r], copies[0], wbytes, cudaMemcpyDeviceToDevice, sc.stream));
+  }
+  float *d_x, *d_y;
+  uint8_t *d_pack;
+  OP_CUDA(sc.alloc(&d_x, sizeof(float) * m * k));
+  OP_CUDA(sc.alloc(&d_y, sizeof(float) * m * n));
+  OP_CUDA(sc.alloc(&d_pack, xpack_bytes((int)k, (int)m)));
+  OP_CUDA(cudaMemcpyAsync(d_x, activation, sizeof(float) * m * k, cudaMemcpyHostToDevice, sc.stream));
+  OP_CUDA(launch_pack(d_x, (int)k, (int)k, (int)m, d_pack, cfg));
+  GemvArgs a;
+  a.type = type;
+  a.seg_rows[0] = (int)n;
+  a.nseg = 1;
+  a.k = (int)k;
+  a.xpack = d_pack;
+  a.batch = (int)m;
+  a.epi = EPI_STORE;
+  a.y = d_y;
+  a.ldy = (int)n;
+  OP_CUDA(cudaEventCreate(&sc.e0));
+  OP_CUDA(cudaEventCreate(&sc.e1));
+  for (int i = 0; i < warmup; ++i) {
+    a.w[0] = copies[(size_t)(i % rotate)];
+    OP_CUDA(launch_qgemv(a, cfg));
+  }
+  OP_CUDA(cudaEventRecord(sc.e0, sc.stream));
+  for (int i = 0; i < iters; ++i) {
+    a.w[0] = copies[(size_t)((warmup + i) % rotate)];
+    OP_CUDA(launch_qgemv(a, cfg));
+  }
+  OP_CUDA(cudaEventRecord(sc.e1, sc.stream));
+  int status = 0;
+  if (out) OP_CUDA(cudaMemcpyAsync(out, d_y, sizeof(float) * m * n, cudaMemcpyDeviceToHost, sc.stream));
+  OP_CUDA(cudaMemcpyAsync(&status, d_status, sizeof(int), cudaMemcpyDeviceToHost, sc.stream));
+  OP_CUDA(cudaStreamSynchronize(sc.stream));
+  if (status == 1) return fail(RG_TIMEOUT, "a bounded device-side wait gave up");
+  if (status) return fail(RG_CUDA_ERROR, "device status " + std::to_string(status));
+  float ms = 0.0f;
+  OP_CUDA(cudaEventElapsedTime(&ms, sc.e0, sc.e1));
+  *kernel_ms = ms / (float)iters;
+  return RG_OK;
+}
+
+}  // extern "C"

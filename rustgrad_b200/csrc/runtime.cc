@@ -1,0 +1,1160 @@
+// Host runtime behind the C ABI: tensor binding with typed rejections, one-time upload of the
+// native GGML block bytes (sharded for tensor parallelism), the session with its fixed launch
+// sequence, CUDA-graph replay of the decode step, and transactional positions.
+//
+// It takes the place of rustgrad's CUDA plumbing for this model: src/cuda.rs (driver wrapper),
+// src/runtime/cuda_graph.rs (prepared graph replay), src/sharded_cuda_plan.rs /
+// src/sharded_cuda_execute.rs (static Megatron split instead of a general sharded plan).
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <atomic>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/rg_b200.h"
+#include "comm.h"
+#include "gguf.h"
+#include "kernels.h"
+
+namespace rg {
+
+// ------------------------------------------------------------------------------------------
+// Errors and host-side fault injection
+// ------------------------------------------------------------------------------------------
+thread_local std::string g_last_error;
+
+static int32_t fail(int32_t status, const std::string &why) {
+  g_last_error = why;
+  return status;
+}
+
+// Fail-after-N counters for the wrapped runtime calls, the host-side stand-in for the
+// fault knobs of rustgrad's mock driver (src/cuda.rs:5895-5960).  -1 = never fail.
+struct FaultKnobs {
+  std::atomic<int> malloc_after{-1}, memcpy_after{-1}, launch_after{-1}, sync_after{-1};
+};
+static FaultKnobs g_faults;
+
+static bool inject(std::atomic<int> &knob) {
+  int v = knob.load();
+  if (v < 0) return false;
+  if (v == 0) {
+    knob.store(-1);
+    return true;
+  }
+  knob.store(v - 1);
+  return false;
+}
+
+#define RG_CUDA(expr)                                                                                        \
+  do {                                                                                                       \
+    cudaError_t e__ = (expr);                                                                                \
+    if (e__ != cudaSuccess)                                                                                  \
+      return fail(e__ == cudaErrorMemoryAllocation ? RG_OUT_OF_MEMORY : RG_CUDA_ERROR,                       \
+                  std::string(#expr) + ": " + cudaGetErrorString(e__) + " (" + __FILE__ + ":" +              \
+                      std::to_string(__LINE__) + ")");                                                       \
+  } while (0)
+
+static cudaError_t x_malloc(void **p, size_t n) {
+  if (inject(g_faults.malloc_after)) return cudaErrorMemoryAllocation;
+  return cudaMalloc(p, n ? n : 16);
+}
+static cudaError_t x_memcpy_async(void *dst, const void *src, size_t n, cudaMemcpyKind kind, cudaStream_t s) {
+  if (inject(g_faults.memcpy_after)) return cudaErrorUnknown;
+  return cudaMemcpyAsync(dst, src, n, kind, s);
+}
+static cudaError_t x_sync(cudaStream_t s) {
+  if (inject(g_faults.sync_after)) return cudaErrorUnknown;
+  return cudaStreamSynchronize(s);
+}
+static cudaError_t x_launch(cudaError_t launched) {
+  if (inject(g_faults.launch_after)) return cudaErrorLaunchFailure;
+  return launched;
+}
+
+static bool env_flag(const char *name) {
+  const char *v = getenv(name);
+  return v && *v && strcmp(v, "0") != 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// Tensors
+// ------------------------------------------------------------------------------------------
+struct DevTensor {
+  int type = -1;          // -1: absent
+  uint64_t rows = 0, cols = 0;  // rank-local shape
+  uint8_t *d = nullptr;
+  size_t nbytes = 0;
+  bool packed() const { return type == RG_TYPE_Q4_0 || type == RG_TYPE_Q8_0; }
+};
+
+struct LayerW {
+  DevTensor attn_norm, q, k, v, o, ffn_norm, gate, up, down;
+};
+
+enum Split { SPLIT_NONE, SPLIT_ROWS, SPLIT_COLS };
+
+struct Slot {
+  DevTensor *t = nullptr;
+  uint64_t rows = 0, cols = 0;  // full shape
+  bool norm = false;
+  Split split = SPLIT_NONE;
+  bool ignored = false;  // rope_freqs.weight: validated, not used (as in the reference forward)
+};
+
+}  // namespace rg
+
+using namespace rg;
+
+struct rg_gguf {
+  Gguf g;
+};
+
+struct rg_plan {
+  rg_llama_config cfg{};
+  rg_options opt{};
+  int tp_rank = 0, tp_world = 1;
+  cudaStream_t stream = nullptr;
+  int *d_status = nullptr;
+  int sm_count = 148;
+  std::vector<LayerW> layers;
+  DevTensor token_embd, output_norm, output;
+  uint64_t weight_bytes = 0;
+  bool consumed = false;
+
+  ~rg_plan() {
+    if (!consumed) {
+      auto drop = [](DevTensor &t) {
+        if (t.d) cudaFree(t.d);
+        t.d = nullptr;
+      };
+      drop(token_embd);
+      drop(output_norm);
+      drop(output);
+      for (auto &l : layers)
+        for (DevTensor *t : {&l.attn_norm, &l.q, &l.k, &l.v, &l.o, &l.ffn_norm, &l.gate, &l.up, &l.down}) drop(*t);
+    }
+    if (d_status) cudaFree(d_status);
+    if (stream) cudaStreamDestroy(stream);
+  }
+};
+
+namespace rg {
+
+static bool find_slot(rg_plan *p, const std::string &name, Slot *s) {
+  const rg_llama_config &c = p->cfg;
+  const uint64_t d = c.d_model, f = c.ffn_dim, qw = (uint64_t)c.n_heads * c.head_dim, kw = (uint64_t)c.n_kv_heads * c.head_dim;
+  auto set = [&](DevTensor *t, uint64_t rows, uint64_t cols, bool norm, Split split) {
+    s->t = t;
+    s->rows = rows;
+    s->cols = cols;
+    s->norm = norm;
+    s->split = split;
+    return true;
+  };
+  if (name == "token_embd.weight") return set(&p->token_embd, c.vocab, d, false, SPLIT_NONE);
+  if (name == "output.weight") return set(&p->output, c.vocab, d, false, SPLIT_ROWS);
+  if (name == "output_norm.weight") return set(&p->output_norm, 1, d, true, SPLIT_NONE);
+  if (name == "rope_freqs.weight") {
+    s->ignored = true;
+    return set(nullptr, 1, (uint64_t)c.head_dim / 2, true, SPLIT_NONE);
+  }
+  int layer = -1, used = 0;
+  if (sscanf(name.c_str(), "blk.%d.%n", &layer, &used) != 1 || layer < 0 || layer >= c.n_layers) return false;
+  const std::string suffix = name.substr((size_t)used);
+  LayerW &L = p->layers[(size_t)layer];
+  if (suffix == "attn_norm.weight") return set(&L.attn_norm, 1, d, true, SPLIT_NONE);
+  if (suffix == "ffn_norm.weight") return set(&L.ffn_norm, 1, d, true, SPLIT_NONE);
+  if (suffix == "attn_q.weight") return set(&L.q, qw, d, false, SPLIT_ROWS);
+  if (suffix == "attn_k.weight") return set(&L.k, kw, d, false, SPLIT_ROWS);
+  if (suffix == "attn_v.weight") return set(&L.v, kw, d, false, SPLIT_ROWS);
+  if (suffix == "attn_output.weight") return set(&L.o, d, qw, false, SPLIT_COLS);
+  if (suffix == "ffn_gate.weight") return set(&L.gate, f, d, false, SPLIT_ROWS);
+  if (suffix == "ffn_up.weight") return set(&L.up, f, d, false, SPLIT_ROWS);
+  if (suffix == "ffn_down.weight") return set(&L.down, d, f, false, SPLIT_COLS);
+  return false;
+}
+
+// Shape/type checks shared by uploaded and synthesized tensors.  Computes the rank-local shard.
+static int32_t check_tensor(rg_plan *p, const std::string &name, int32_t type, uint64_t rows, uint64_t cols, Slot *slot,
+                            uint64_t *r0, uint64_t *lr, uint64_t *c0, uint64_t *lc) {
+  if (!find_slot(p, name, slot)) return fail(RG_UNEXPECTED_TENSOR, "unexpected tensor " + name);
+  if (!block_elements(type)) return fail(RG_UNSUPPORTED_TYPE, name + ": ggml type " + std::to_string(type) + " is not supported");
+  if (slot->norm && type != RG_TYPE_F32 && type != RG_TYPE_F16)
+    return fail(RG_UNSUPPORTED_TYPE, name + ": packed tensor where a dense vector is required");
+  if (rows != slot->rows || cols != slot->cols)
+    return fail(RG_SHAPE_MISMATCH, name + ": expected [" + std::to_string(slot->rows) + "," + std::to_string(slot->cols) +
+                                       "], got [" + std::to_string(rows) + "," + std::to_string(cols) + "]");
+  if (cols % (uint64_t)block_elements(type)) return fail(RG_SHAPE_MISMATCH, name + ": columns are not a multiple of the block size");
+  if (slot->t && slot->t->type >= 0) return fail(RG_INVALID_ARGUMENT, name + ": tensor bound twice");
+  const uint64_t W = (uint64_t)p->tp_world, R = (uint64_t)p->tp_rank;
+  *r0 = 0, *lr = rows, *c0 = 0, *lc = cols;
+  if (W > 1 && slot->split == SPLIT_ROWS) {
+    if (rows % W) return fail(RG_UNSUPPORTED_GEOMETRY, name + ": rows do not divide by the tensor-parallel world size");
+    *lr = rows / W;
+    *r0 = R * *lr;
+  } else if (W > 1 && slot->split == SPLIT_COLS) {
+    if (cols % (W * 32)) return fail(RG_UNSUPPORTED_GEOMETRY, name + ": columns do not split at block boundaries");
+    *lc = cols / W;
+    *c0 = R * *lc;
+  }
+  const bool is_packed = (type == RG_TYPE_Q4_0 || type == RG_TYPE_Q8_0);
+  if (is_packed && !slot->norm && name != "token_embd.weight" && (*lc % 256))
+    return fail(RG_UNSUPPORTED_GEOMETRY, name + ": packed projections need a (rank-local) K that is a multiple of 256");
+  if (is_packed && name == "token_embd.weight" && p->output.type < 0 && (*lc % 256))
+    ;  // a tied head over such an embedding is rejected at prepare
+  return RG_OK;
+}
+
+}  // namespace rg
+
+// ------------------------------------------------------------------------------------------
+// Session
+// ------------------------------------------------------------------------------------------
+static constexpr int MAXC = 8;  // columns per forward: decode batch or prefill chunk
+
+struct Ctrl {  // device control block, uploaded in one copy per host-driven step
+  int32_t tokens[MAXC];
+  int32_t pos[MAXC];
+  int32_t seq[MAXC];
+  int32_t logit_cols[MAXC];
+  int32_t step;
+  int32_t pad[3];
+};
+
+struct rg_session {
+  rg_llama_config cfg{};
+  rg_options opt{};
+  int tp_rank = 0, tp_world = 1;
+  int heads_l = 0, kv_l = 0, ffn_l = 0, vocab_l = 0;  // rank-local sizes
+  int max_batch = 1, ctx = 0;
+  bool kv_f32 = false, use_graph = true, use_pdl = true;
+  cudaStream_t stream = nullptr;
+  int sm_count = 148;
+  Comm comm;
+  std::vector<LayerW> layers;
+  DevTensor token_embd, output_norm, output;
+  const DevTensor *head = nullptr;
+  uint64_t weight_bytes = 0, kv_bytes = 0;
+  // device buffers
+  Ctrl *d_ctrl = nullptr;
+  int32_t *d_ids = nullptr, *d_history = nullptr;
+  int *d_status = nullptr;
+  float *x = nullptr, *xn_f32 = nullptr, *qkv = nullptr, *q_rot = nullptr, *attn_scratch = nullptr, *attn_f32 = nullptr;
+  float *partial = nullptr, *gate_f32 = nullptr, *up_f32 = nullptr, *h_f32 = nullptr, *logits = nullptr, *logits_l = nullptr;
+  void *xn_pack = nullptr, *attn_pack = nullptr, *h_pack = nullptr, *head_pack = nullptr;
+  float *cos_t = nullptr, *sin_t = nullptr;
+  std::vector<void *> k_cache, v_cache;
+  std::vector<void *> owned;  // everything to cudaFree
+  // pinned host staging
+  Ctrl *h_ctrl = nullptr;
+  int32_t *h_ids = nullptr;
+  int *h_status = nullptr;
+  float *h_logits = nullptr;
+  int history_cap = 0;
+  // state
+  std::vector<int32_t> position;
+  bool poisoned = false;
+  std::map<int, cudaGraphExec_t> graphs;  // by batch
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  rg_report report{};
+  uint64_t launches_in_step = 0;
+
+  ~rg_session() {
+    for (auto &g : graphs) cudaGraphExecDestroy(g.second);
+    for (void *p : owned) cudaFree(p);
+    if (h_ctrl) cudaFreeHost(h_ctrl);
+    if (h_ids) cudaFreeHost(h_ids);
+    if (h_status) cudaFreeHost(h_status);
+    if (h_logits) cudaFreeHost(h_logits);
+    if (ev0) cudaEventDestroy(ev0);
+    if (ev1) cudaEventDestroy(ev1);
+    comm_destroy(&comm);
+    if (stream) cudaStreamDestroy(stream);
+  }
+};
+
+namespace rg {
+
+template <typename T>
+static int32_t dalloc(rg_session *s, T **p, size_t count) {
+  void *raw = nullptr;
+  RG_CUDA(x_malloc(&raw, count * sizeof(T)));
+  s->owned.push_back(raw);
+  *p = static_cast<T *>(raw);
+  return RG_OK;
+}
+
+static LaunchCfg lcfg(rg_session *s) {
+  LaunchCfg c;
+  c.stream = s->stream;
+  c.pdl = s->use_pdl;
+  c.sm_count = s->sm_count;
+  c.status = s->d_status;
+  return c;
+}
+
+#define RG_LAUNCH(s, expr)                                                                     \
+  do {                                                                                         \
+    cudaError_t e__ = x_launch(expr);                                                          \
+    (s)->launches_in_step++;                                                                   \
+    if (e__ != cudaSuccess)                                                                    \
+      return fail(RG_CUDA_ERROR, std::string(#expr) + ": " + cudaGetErrorString(e__) + " (" +  \
+                                     __FILE__ + ":" + std::to_string(__LINE__) + ")");         \
+  } while (0)
+
+// y = W x for one projection given as `n` row segments sharing K.  Packed segments of one type go
+// out as a single fused launch; dense ones run the dense kernel segment by segment.
+static int32_t linear(rg_session *s, const DevTensor *const *w, int n, const void *in_pack, const float *in_f32, int ld_in,
+                      int batch, int epi, float *y, int ldy) {
+  bool all_packed = true;
+  for (int i = 0; i < n; ++i) all_packed = all_packed && w[i]->packed() && w[i]->type == w[0]->type;
+  if (all_packed) {
+    GemvArgs a;
+    a.type = w[0]->type;
+    a.nseg = n;
+    for (int i = 0; i < n; ++i) {
+      a.w[i] = w[i]->d;
+      a.seg_rows[i] = (int)w[i]->rows;
+    }
+    a.k = (int)w[0]->cols;
+    a.xpack = in_pack;
+    a.batch = batch;
+    a.epi = epi;
+    a.y = y;
+    a.ldy = ldy;
+    RG_LAUNCH(s, launch_qgemv(a, lcfg(s)));
+    return RG_OK;
+  }
+  int row0 = 0;
+  for (int i = 0; i < n; ++i) {
+    if (w[i]->packed()) {
+      GemvArgs a;
+      a.type = w[i]->type;
+      a.nseg = 1;
+      a.w[0] = w[i]->d;
+      a.seg_rows[0] = (int)w[i]->rows;
+      a.k = (int)w[i]->cols;
+      a.xpack = in_pack;
+      a.batch = batch;
+      a.epi = epi;
+      a.y = y + row0;
+      a.ldy = ldy;
+      RG_LAUNCH(s, launch_qgemv(a, lcfg(s)));
+    } else {
+      DenseGemvArgs a;
+      a.type = w[i]->type;
+      a.w = w[i]->d;
+      a.rows = (int)w[i]->rows;
+      a.k = (int)w[i]->cols;
+      a.x = in_f32;
+      a.ldx = ld_in;
+      a.batch = batch;
+      a.epi = epi;
+      a.y = y + row0;
+      a.ldy = ldy;
+      RG_LAUNCH(s, launch_dense_gemv(a, lcfg(s)));
+    }
+    row0 += (int)w[i]->rows;
+  }
+  return RG_OK;
+}
+
+static int32_t tp_reduce_add(rg_session *s, int ncols) {
+  const int d = s->cfg.d_model;
+  std::string err;
+  int32_t rc = comm_allreduce_sum_f32(&s->comm, s->partial, (size_t)ncols * d, s->stream, &err);
+  if (rc) return fail(rc, err);
+  LaunchCfg c = lcfg(s);
+  c.pdl = false;  // follows a library kernel
+  RG_LAUNCH(s, launch_add_rows(s->x, d, s->partial, d, d, ncols, c));
+  return RG_OK;
+}
+
+// One forward over `ncols` columns described by the device control block.  n_logit_cols columns
+// (indices in ctrl.logit_cols) get logits + greedy ids; 0 skips the head (non-final prefill chunk).
+static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance) {
+  const rg_llama_config &c = s->cfg;
+  const int d = c.d_model, hd = c.head_dim;
+  const int qw = s->heads_l * hd, kw = s->kv_l * hd, qkv_w = qw + 2 * kw;
+  Ctrl *ctl = s->d_ctrl;
+  LaunchCfg L = lcfg(s);
+  LaunchCfg first = L;
+  first.pdl = false;  // follows a memcpy, not a kernel
+  RG_LAUNCH(s, launch_row_gather(s->token_embd.type, s->token_embd.d, d, ctl->tokens, ncols, s->x, d, first));
+  for (int l = 0; l < c.n_layers; ++l) {
+    const LayerW &W = s->layers[(size_t)l];
+    const bool qkv_dense = !W.q.packed() || !W.k.packed() || !W.v.packed();
+    RG_LAUNCH(s, launch_rmsnorm_pack(s->x, d, reinterpret_cast<const float *>(W.attn_norm.d), d, c.norm_eps, ncols, nullptr,
+                                     s->xn_pack, qkv_dense ? s->xn_f32 : nullptr, d, L));
+    const DevTensor *qkvw[3] = {&W.q, &W.k, &W.v};
+    int32_t rc = linear(s, qkvw, 3, s->xn_pack, s->xn_f32, d, ncols, EPI_STORE, s->qkv, qkv_w);
+    if (rc) return rc;
+    RopeArgs ra;
+    ra.qkv = s->qkv;
+    ra.cols = ncols;
+    ra.heads = s->heads_l;
+    ra.kv_heads = s->kv_l;
+    ra.hd = hd;
+    ra.ctx = s->ctx;
+    ra.col_seq = ctl->seq;
+    ra.col_pos = ctl->pos;
+    ra.cos_t = s->cos_t;
+    ra.sin_t = s->sin_t;
+    ra.q_out = s->q_rot;
+    ra.k_cache = s->k_cache[(size_t)l];
+    ra.v_cache = s->v_cache[(size_t)l];
+    ra.kv_f32 = s->kv_f32;
+    RG_LAUNCH(s, launch_rope_append(ra, L));
+    AttnArgs aa;
+    aa.q = s->q_rot;
+    aa.k_cache = ra.k_cache;
+    aa.v_cache = ra.v_cache;
+    aa.kv_f32 = s->kv_f32;
+    aa.cols = ncols;
+    aa.heads = s->heads_l;
+    aa.kv_heads = s->kv_l;
+    aa.hd = hd;
+    aa.ctx = s->ctx;
+    aa.col_seq = ctl->seq;
+    aa.col_pos = ctl->pos;
+    aa.scratch = s->attn_scratch;
+    aa.out_pack = s->attn_pack;
+    aa.out_f32 = W.o.packed() ? nullptr : s->attn_f32;
+    RG_LAUNCH(s, launch_attention(aa, L));
+    s->launches_in_step++;  // split + combine
+    const DevTensor *ow[1] = {&W.o};
+    if (s->tp_world > 1) {
+      if ((rc = linear(s, ow, 1, s->attn_pack, s->attn_f32, qw, ncols, EPI_STORE, s->partial, d))) return rc;
+      if ((rc = tp_reduce_add(s, ncols))) return rc;
+    } else if ((rc = linear(s, ow, 1, s->attn_pack, s->attn_f32, qw, ncols, EPI_RESIDUAL, s->x, d))) {
+      return rc;
+    }
+    LaunchCfg after = L;
+    if (s->tp_world > 1) after.pdl = false;
+    const bool gu_dense = !W.gate.packed() || !W.up.packed() || W.gate.type != W.up.type;
+    RG_LAUNCH(s, launch_rmsnorm_pack(s->x, d, reinterpret_cast<const float *>(W.ffn_norm.d), d, c.norm_eps, ncols, nullptr,
+                                     s->xn_pack, gu_dense ? s->xn_f32 : nullptr, d, after));
+    if (!gu_dense) {
+      GemvArgs a;
+      a.type = W.gate.type;
+      a.nseg = 2;
+      a.w[0] = W.gate.d;
+      a.w[1] = W.up.d;
+      a.seg_rows[0] = a.seg_rows[1] = s->ffn_l;
+      a.k = d;
+      a.xpack = s->xn_pack;
+      a.batch = ncols;
+      a.epi = EPI_SWIGLU;
+      a.ypack = s->h_pack;
+      RG_LAUNCH(s, launch_qgemv(a, L));
+      if (!W.down.packed()) RG_LAUNCH(s, launch_unpack(s->h_pack, s->ffn_l, ncols, s->h_f32, s->ffn_l, L));
+    } else {
+      const DevTensor *gw[1] = {&W.gate}, *uw[1] = {&W.up};
+      if ((rc = linear(s, gw, 1, s->xn_pack, s->xn_f32, d, ncols, EPI_STORE, s->gate_f32, s->ffn_l))) return rc;
+      if ((rc = linear(s, uw, 1, s->xn_pack, s->xn_f32, d, ncols, EPI_STORE, s->up_f32, s->ffn_l))) return rc;
+      RG_LAUNCH(s, launch_swiglu(s->gate_f32, s->up_f32, s->ffn_l, s->ffn_l, ncols, s->h_pack, s->h_f32, s->ffn_l, L));
+    }
+    const DevTensor *dw[1] = {&W.down};
+    if (s->tp_world > 1) {
+      if ((rc = linear(s, dw, 1, s->h_pack, s->h_f32, s->ffn_l, ncols, EPI_STORE, s->partial, d))) return rc;
+      if ((rc = tp_reduce_add(s, ncols))) return rc;
+    } else if ((rc = linear(s, dw, 1, s->h_pack, s->h_f32, s->ffn_l, ncols, EPI_RESIDUAL, s->x, d))) {
+      return rc;
+    }
+  }
+  if (n_logit_cols > 0) {
+    LaunchCfg after = L;
+    if (s->tp_world > 1) after.pdl = false;
+    RG_LAUNCH(s, launch_rmsnorm_pack(s->x, d, reinterpret_cast<const float *>(s->output_norm.d), d, c.norm_eps, n_logit_cols,
+                                     ctl->logit_cols, s->head_pack, s->head->packed() ? nullptr : s->xn_f32, d, after));
+    const DevTensor *hw[1] = {s->head};
+    const bool split_head = s->tp_world > 1 && s->head == &s->output;
+    float *dst = split_head ? s->logits_l : s->logits;
+    const int ld = split_head ? s->vocab_l : c.vocab;
+    int32_t rc = linear(s, hw, 1, s->head_pack, s->xn_f32, d, n_logit_cols, EPI_STORE, dst, ld);
+    if (rc) return rc;
+    LaunchCfg am = L;
+    if (split_head) {
+      std::string err;
+      if ((rc = comm_group_start(&err))) return fail(rc, err);
+      for (int col = 0; col < n_logit_cols; ++col)
+        if ((rc = comm_allgather_f32(&s->comm, s->logits_l + (size_t)col * s->vocab_l, s->logits + (size_t)col * c.vocab,
+                                     (size_t)s->vocab_l, s->stream, &err)))
+          return fail(rc, err);
+      if ((rc = comm_group_end(&err))) return fail(rc, err);
+      am.pdl = false;
+    }
+    RG_LAUNCH(s, launch_argmax(s->logits, c.vocab, c.vocab, n_logit_cols, s->d_ids, am));
+    if (advance) RG_LAUNCH(s, launch_advance(s->d_ids, ctl->tokens, ctl->pos, s->d_history, &ctl->step, ncols, L));
+  }
+  return RG_OK;
+}
+
+// Captures the decode step for `batch` rows once and returns the executable graph.
+static int32_t decode_graph(rg_session *s, int batch, cudaGraphExec_t *out) {
+  auto it = s->graphs.find(batch);
+  if (it != s->graphs.end()) {
+    *out = it->second;
+    return RG_OK;
+  }
+  // Run every kernel once outside capture so lazy module loading and function attributes are
+  // done.  The run uses the control block already uploaded; what it writes (KV rows at the
+  // current positions, advanced control block) is rewritten by the upload and the replay below.
+  s->launches_in_step = 0;
+  int32_t warm = forward(s, batch, batch, true);
+  if (warm) return warm;
+  RG_CUDA(x_memcpy_async(s->d_ctrl, s->h_ctrl, sizeof(Ctrl), cudaMemcpyHostToDevice, s->stream));
+  RG_CUDA(cudaStreamSynchronize(s->stream));
+  RG_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+  s->launches_in_step = 0;
+  int32_t rc = forward(s, batch, batch, true);
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(s->stream, &graph);
+  if (rc) {
+    if (graph) cudaGraphDestroy(graph);
+    return rc;
+  }
+  if (e != cudaSuccess) return fail(RG_CUDA_ERROR, std::string("cudaStreamEndCapture: ") + cudaGetErrorString(e));
+  cudaGraphExec_t exec = nullptr;
+  e = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) return fail(RG_CUDA_ERROR, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
+  s->graphs[batch] = exec;
+  *out = exec;
+  return RG_OK;
+}
+
+static int32_t run_step(rg_session *s, int ncols, int n_logit_cols, bool advance, bool allow_graph) {
+  if (allow_graph && s->use_graph) {
+    cudaGraphExec_t exec;
+    int32_t rc = decode_graph(s, ncols, &exec);
+    if (rc) return rc;
+    if (inject(g_faults.launch_after)) return fail(RG_CUDA_ERROR, "injected graph launch failure");
+    RG_CUDA(cudaGraphLaunch(exec, s->stream));
+    s->report.graph_replays++;
+    s->report.kernel_launches += s->launches_in_step;
+    return RG_OK;
+  }
+  s->launches_in_step = 0;
+  int32_t rc = forward(s, ncols, n_logit_cols, advance);
+  s->report.kernel_launches += s->launches_in_step;
+  return rc;
+}
+
+static int32_t upload_ctrl(rg_session *s) {
+  RG_CUDA(x_memcpy_async(s->d_ctrl, s->h_ctrl, sizeof(Ctrl), cudaMemcpyHostToDevice, s->stream));
+  s->report.h2d_calls++;
+  s->report.h2d_bytes += sizeof(Ctrl);
+  return RG_OK;
+}
+
+// Reads back the status word and `n` greedy ids; maps device findings to typed statuses.
+static int32_t finish_step(rg_session *s, int n_ids, float *logits_out, int n_logit_rows) {
+  RG_CUDA(x_memcpy_async(s->h_status, s->d_status, sizeof(int), cudaMemcpyDeviceToHost, s->stream));
+  if (n_ids > 0) RG_CUDA(x_memcpy_async(s->h_ids, s->d_ids, sizeof(int32_t) * (size_t)n_ids, cudaMemcpyDeviceToHost, s->stream));
+  s->report.d2h_calls += 1 + (n_ids > 0);
+  s->report.d2h_bytes += sizeof(int) + sizeof(int32_t) * (size_t)n_ids;
+  if (logits_out && n_logit_rows > 0) {
+    const size_t bytes = sizeof(float) * (size_t)n_logit_rows * (size_t)s->cfg.vocab;
+    RG_CUDA(x_memcpy_async(s->h_logits, s->logits, bytes, cudaMemcpyDeviceToHost, s->stream));
+    s->report.d2h_calls++;
+    s->report.d2h_bytes += bytes;
+  }
+  cudaError_t e = x_sync(s->stream);
+  if (e != cudaSuccess) {
+    s->poisoned = true;  // completion cannot be proven (src/runtime/cuda_graph.rs:542-546)
+    return fail(RG_POISONED, std::string("stream synchronize: ") + cudaGetErrorString(e));
+  }
+  if (*s->h_status == 1) {
+    s->poisoned = true;
+    return fail(RG_TIMEOUT, "a bounded device-side wait gave up");
+  }
+  if (*s->h_status != 0) return fail(RG_CUDA_ERROR, "device status " + std::to_string(*s->h_status));
+  if (logits_out && n_logit_rows > 0) memcpy(logits_out, s->h_logits, sizeof(float) * (size_t)n_logit_rows * (size_t)s->cfg.vocab);
+  for (int i = 0; i < n_ids; ++i)
+    if (s->h_ids[i] < 0) return fail(RG_NON_FINITE_LOGITS, "non-finite logits in row " + std::to_string(i));
+  return RG_OK;
+}
+
+static int32_t check_live(const rg_session *s) {
+  if (!s) return fail(RG_INVALID_ARGUMENT, "null session");
+  if (s->poisoned) return fail(RG_POISONED, "session poisoned by an earlier failure");
+  return RG_OK;
+}
+
+}  // namespace rg
+
+// ==========================================================================================
+// C ABI
+// ==========================================================================================
+extern "C" {
+
+const char *rg_b200_version(void) { return "rg_b200 0.1 (sm_100a)"; }
+
+const char *rg_b200_status_string(int32_t st) {
+  static const char *names[] = {"OK", "INVALID_ARGUMENT", "UNSUPPORTED_TYPE", "SHAPE_MISMATCH", "NON_FINITE_SCALE",
+                                "TOKEN_OUT_OF_RANGE", "CONTEXT_EXHAUSTED", "NON_FINITE_LOGITS", "FRESH_SESSION_REQUIRED",
+                                "CUDA_ERROR", "NCCL_ERROR", "OUT_OF_MEMORY", "TIMEOUT", "POISONED", "MALFORMED_GGUF",
+                                "MISSING_TENSOR", "UNEXPECTED_TENSOR", "UNSUPPORTED_VARIANT", "MISSING_METADATA", "EMPTY_PROMPT",
+                                "UNSUPPORTED_GEOMETRY"};
+  if (st < 0 || st > 20) return "UNKNOWN";
+  return names[st];
+}
+
+const char *rg_b200_last_error(void) { return g_last_error.c_str(); }
+
+// Test hook: make the n-th next call of a wrapped CUDA entry fail ("malloc", "memcpy", "launch",
+// "sync"); n < 0 disarms.  Host-side fault injection in the manner of src/cuda.rs:5895-5960.
+int32_t rg_b200_test_fail_after(const char *what, int32_t n) {
+  if (!what) return RG_INVALID_ARGUMENT;
+  if (!strcmp(what, "malloc")) g_faults.malloc_after = n;
+  else if (!strcmp(what, "memcpy")) g_faults.memcpy_after = n;
+  else if (!strcmp(what, "launch")) g_faults.launch_after = n;
+  else if (!strcmp(what, "sync")) g_faults.sync_after = n;
+  else return RG_INVALID_ARGUMENT;
+  return RG_OK;
+}
+
+// ------------------------------------------------------------------------------ GGUF
+int32_t rg_b200_gguf_open(const uint8_t *bytes, size_t len, rg_gguf **out) {
+  if (!bytes || !out) return fail(RG_INVALID_ARGUMENT, "null argument");
+  auto g = std::make_unique<rg_gguf>();
+  std::string err;
+  int32_t rc = gguf_parse(bytes, len, &g->g, &err);
+  if (rc) return fail(rc, err);
+  *out = g.release();
+  return RG_OK;
+}
+void rg_b200_gguf_close(rg_gguf *g) { delete g; }
+size_t rg_b200_gguf_tensor_count(const rg_gguf *g) { return g ? g->g.tensors.size() : 0; }
+int32_t rg_b200_gguf_tensor_info(const rg_gguf *g, size_t index, const char **name, int32_t *type, int32_t *rank, uint64_t dims[4],
+                                 const uint8_t **data, size_t *nbytes) {
+  if (!g || index >= g->g.tensors.size()) return fail(RG_INVALID_ARGUMENT, "tensor index out of range");
+  const GgufTensorInfo &t = g->g.tensors[index];
+  if (name) *name = t.name.c_str();
+  if (type) *type = t.ggml_type;
+  if (rank) *rank = (int32_t)t.shape.size();
+  if (dims)
+    for (size_t i = 0; i < t.shape.size(); ++i) dims[i] = t.shape[i];
+  if (data) *data = g->g.bytes + t.offset;
+  if (nbytes) *nbytes = t.nbytes;
+  return RG_OK;
+}
+int32_t rg_b200_gguf_llama_config(const rg_gguf *g, rg_llama_config *out) {
+  if (!g || !out) return fail(RG_INVALID_ARGUMENT, "null argument");
+  std::string err;
+  int32_t rc = gguf_llama_config(g->g, out, &err);
+  return rc ? fail(rc, err) : RG_OK;
+}
+
+// ------------------------------------------------------------------------------ plan
+int32_t rg_b200_plan_create(const rg_llama_config *c, const rg_options *o, rg_plan **out) {
+  if (!c || !out) return fail(RG_INVALID_ARGUMENT, "null argument");
+  if (c->n_layers <= 0 || c->d_model <= 0 || c->n_heads <= 0 || c->n_kv_heads <= 0 || c->head_dim <= 0 || c->ffn_dim <= 0 ||
+      c->vocab <= 0 || c->max_context <= 0 || c->n_heads % c->n_kv_heads || !(c->norm_eps >= 0.0f) || !(c->rope_theta > 0.0))
+    return fail(RG_INVALID_ARGUMENT, "invalid model configuration");
+  if (c->head_dim > 128 || (c->head_dim & 1) || c->n_heads / c->n_kv_heads > 8)
+    return fail(RG_UNSUPPORTED_GEOMETRY, "head_dim must be even and <= 128, query heads per kv head <= 8");
+  auto p = std::make_unique<rg_plan>();
+  p->cfg = *c;
+  if (o) p->opt = *o;
+  p->tp_world = p->opt.tp_world > 1 ? p->opt.tp_world : 1;
+  p->tp_rank = p->tp_world > 1 ? p->opt.tp_rank : 0;
+  if (p->tp_rank < 0 || p->tp_rank >= p->tp_world) return fail(RG_INVALID_ARGUMENT, "tensor-parallel rank out of range");
+  if (p->tp_world > 1 && (c->n_heads % p->tp_world || c->n_kv_heads % p->tp_world || c->ffn_dim % p->tp_world))
+    return fail(RG_UNSUPPORTED_GEOMETRY, "heads, kv heads and ffn width must divide by the tensor-parallel world size");
+  if (p->opt.max_batch > MAXC) return fail(RG_UNSUPPORTED_GEOMETRY, "max_batch above 8 is not supported");
+  RG_CUDA(cudaSetDevice(p->opt.device));
+  int sms = 0;
+  RG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->opt.device));
+  p->sm_count = sms;
+  RG_CUDA(cudaStreamCreateWithFlags(&p->stream, cudaStreamNonBlocking));
+  RG_CUDA(x_malloc(reinterpret_cast<void **>(&p->d_status), sizeof(int)));
+  RG_CUDA(cudaMemsetAsync(p->d_status, 0, sizeof(int), p->stream));
+  p->layers.resize((size_t)c->n_layers);
+  *out = p.release();
+  return RG_OK;
+}
+
+int32_t rg_b200_plan_add_tensor(rg_plan *p, const char *name, int32_t type, uint64_t rows, uint64_t cols, const uint8_t *bytes,
+                                size_t nbytes) {
+  if (!p || !name || !bytes) return fail(RG_INVALID_ARGUMENT, "null argument");
+  if (p->consumed) return fail(RG_INVALID_ARGUMENT, "plan already prepared");
+  Slot slot;
+  uint64_t r0, lr, c0, lc;
+  int32_t rc = check_tensor(p, name, type, rows, cols, &slot, &r0, &lr, &c0, &lc);
+  if (rc) return rc;
+  const uint64_t be = (uint64_t)block_elements(type), bb = (uint64_t)block_bytes(type);
+  const uint64_t row_bytes = cols / be * bb;
+  if (nbytes != rows * row_bytes) return fail(RG_SHAPE_MISMATCH, std::string(name) + ": byte length does not match its geometry");
+  if (type == RG_TYPE_Q4_0 || type == RG_TYPE_Q8_0) {
+    // a non-finite scale is rejected before any device work (src/gguf/quantization/data.rs:325-327)
+    const uint64_t blocks = rows * cols / 32;
+    for (uint64_t b = 0; b < blocks; ++b) {
+      const uint8_t *blk = bytes + b * bb;
+      if (((blk[1] >> 2) & 0x1f) == 0x1f) return fail(RG_NON_FINITE_SCALE, std::string(name) + ": block " + std::to_string(b));
+    }
+  }
+  if (slot.ignored) return RG_OK;
+  RG_CUDA(cudaSetDevice(p->opt.device));
+  DevTensor t;
+  t.rows = lr;
+  t.cols = lc;
+  if (slot.norm) {
+    std::vector<float> v((size_t)cols);
+    if (type == RG_TYPE_F32) {
+      memcpy(v.data(), bytes, (size_t)cols * 4);
+    } else {
+      for (uint64_t i = 0; i < cols; ++i) {  // IEEE half -> float, exact (src/tensor/scalar.rs:110-135)
+        const uint16_t h = (uint16_t)(bytes[2 * i] | (bytes[2 * i + 1] << 8));
+        uint32_t sign = (uint32_t)(h & 0x8000u) << 16, exp = (h >> 10) & 0x1f, mant = h & 0x3ffu, o;
+        if (exp == 0) {
+          if (!mant) o = sign;
+          else {
+            int e = -14;
+            while (!(mant & 0x400u)) { mant <<= 1; --e; }
+            o = sign | ((uint32_t)(e + 127) << 23) | ((mant & 0x3ffu) << 13);
+          }
+        } else if (exp == 31) o = sign | 0x7f800000u | (mant << 13);
+        else o = sign | ((exp + 112u) << 23) | (mant << 13);
+        memcpy(&v[(size_t)i], &o, 4);
+      }
+    }
+    t.type = RG_TYPE_F32;
+    t.nbytes = (size_t)cols * 4;
+    RG_CUDA(x_malloc(reinterpret_cast<void **>(&t.d), t.nbytes));
+    RG_CUDA(cudaMemcpy(t.d, v.data(), t.nbytes, cudaMemcpyHostToDevice));
+  } else {
+    const uint64_t local_row_bytes = lc / be * bb;
+    t.type = type;
+    t.nbytes = (size_t)(lr * local_row_bytes);
+    RG_CUDA(x_malloc(reinterpret_cast<void **>(&t.d), t.nbytes));
+    const uint8_t *src = bytes + r0 * row_bytes + c0 / be * bb;
+    if (inject(g_faults.memcpy_after)) {
+      cudaFree(t.d);
+      return fail(RG_CUDA_ERROR, "injected upload failure");
+    }
+    cudaError_t e = cudaMemcpy2D(t.d, (size_t)local_row_bytes, src, (size_t)row_bytes, (size_t)local_row_bytes, (size_t)lr,
+                                 cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+      cudaFree(t.d);
+      return fail(RG_CUDA_ERROR, std::string("upload of ") + name + ": " + cudaGetErrorString(e));
+    }
+  }
+  p->weight_bytes += t.nbytes;
+  *slot.t = t;
+  return RG_OK;
+}
+
+int32_t rg_b200_plan_synth_tensor(rg_plan *p, const char *name, int32_t type, uint64_t rows, uint64_t cols, uint64_t seed,
+                                  float std) {
+  if (!p || !name) return fail(RG_INVALID_ARGUMENT, "null argument");
+  if (p->consumed) return fail(RG_INVALID_ARGUMENT, "plan already prepared");
+  Slot slot;
+  uint64_t r0, lr, c0, lc;
+  int32_t rc = check_tensor(p, name, type, rows, cols, &slot, &r0, &lr, &c0, &lc);
+  if (rc) return rc;
+  if (slot.ignored) return RG_OK;
+  RG_CUDA(cudaSetDevice(p->opt.device));
+  LaunchCfg cfg;
+  cfg.stream = p->stream;
+  DevTensor t;
+  t.rows = lr;
+  t.cols = lc;
+  if (slot.norm) {
+    t.type = RG_TYPE_F32;
+    t.nbytes = (size_t)cols * 4;
+    RG_CUDA(x_malloc(reinterpret_cast<void **>(&t.d), t.nbytes));
+    RG_CUDA(launch_fill_f32(reinterpret_cast<float *>(t.d), (size_t)cols, 1.0f, cfg));
+  } else {
+    t.type = type;
+    t.nbytes = (size_t)(lr * (lc / (uint64_t)block_elements(type)) * (uint64_t)block_bytes(type));
+    RG_CUDA(x_malloc(reinterpret_cast<void **>(&t.d), t.nbytes));
+    RG_CUDA(launch_synth(type, t.d, seed, std, cols, r0, lr, c0, lc, cfg));
+  }
+  RG_CUDA(cudaStreamSynchronize(p->stream));
+  p->weight_bytes += t.nbytes;
+  *slot.t = t;
+  return RG_OK;
+}
+
+int32_t rg_b200_plan_from_gguf(const rg_gguf *g, const rg_options *o, rg_plan **out) {
+  if (!g || !out) return fail(RG_INVALID_ARGUMENT, "null argument");
+  rg_llama_config cfg;
+  int32_t rc = rg_b200_gguf_llama_config(g, &cfg);
+  if (rc) return rc;
+  rg_plan *p = nullptr;
+  if ((rc = rg_b200_plan_create(&cfg, o, &p))) return rc;
+  for (const GgufTensorInfo &t : g->g.tensors) {
+    uint64_t rows = 1, cols = 0;
+    if (t.shape.size() == 1) cols = t.shape[0];
+    else if (t.shape.size() == 2) { rows = t.shape[0]; cols = t.shape[1]; }
+    else {
+      delete p;
+      return fail(RG_SHAPE_MISMATCH, t.name + ": rank " + std::to_string(t.shape.size()));
+    }
+    if ((rc = rg_b200_plan_add_tensor(p, t.name.c_str(), t.ggml_type, rows, cols, g->g.bytes + t.offset, t.nbytes))) {
+      delete p;
+      return rc;
+    }
+  }
+  *out = p;
+  return RG_OK;
+}
+
+static const DevTensor *plan_tensor(const rg_plan *p, const char *name) {
+  Slot s;
+  if (!find_slot(const_cast<rg_plan *>(p), name, &s) || !s.t || s.t->type < 0) return nullptr;
+  return s.t;
+}
+int32_t rg_b200_plan_tensor_nbytes(const rg_plan *p, const char *name, size_t *nbytes) {
+  if (!p || !name || !nbytes) return fail(RG_INVALID_ARGUMENT, "null argument");
+  const DevTensor *t = plan_tensor(p, name);
+  if (!t) return fail(RG_MISSING_TENSOR, std::string("tensor not bound: ") + name);
+  *nbytes = t->nbytes;
+  return RG_OK;
+}
+int32_t rg_b200_plan_read_tensor(const rg_plan *p, const char *name, uint8_t *out, size_t nbytes) {
+  if (!p || !name || !out) return fail(RG_INVALID_ARGUMENT, "null argument");
+  if (p->consumed) return fail(RG_INVALID_ARGUMENT, "plan already prepared");
+  const DevTensor *t = plan_tensor(p, name);
+  if (!t) return fail(RG_MISSING_TENSOR, std::string("tensor not bound: ") + name);
+  if (nbytes != t->nbytes) return fail(RG_INVALID_ARGUMENT, "buffer size differs from the tensor's byte length");
+  RG_CUDA(cudaSetDevice(p->opt.device));
+  RG_CUDA(cudaMemcpy(out, t->d, nbytes, cudaMemcpyDeviceToHost));
+  return RG_OK;
+}
+void rg_b200_plan_destroy(rg_plan *p) { delete p; }
+
+// ------------------------------------------------------------------------------ session
+int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
+  if (!p || !out) return fail(RG_INVALID_ARGUMENT, "null argument");
+  if (p->consumed) return fail(RG_INVALID_ARGUMENT, "plan already prepared");
+  const rg_llama_config &c = p->cfg;
+  // exact inventory (src/models/transformer/model.rs:384-455)
+  if (p->token_embd.type < 0) return fail(RG_MISSING_TENSOR, "token_embd.weight");
+  if (p->output_norm.type < 0) return fail(RG_MISSING_TENSOR, "output_norm.weight");
+  for (int l = 0; l < c.n_layers; ++l) {
+    LayerW &L = p->layers[(size_t)l];
+    const char *names[] = {"attn_norm", "attn_q", "attn_k", "attn_v", "attn_output", "ffn_norm", "ffn_gate", "ffn_up", "ffn_down"};
+    DevTensor *ts[] = {&L.attn_norm, &L.q, &L.k, &L.v, &L.o, &L.ffn_norm, &L.gate, &L.up, &L.down};
+    for (int i = 0; i < 9; ++i)
+      if (ts[i]->type < 0) return fail(RG_MISSING_TENSOR, "blk." + std::to_string(l) + "." + names[i] + ".weight");
+  }
+  const bool tied = p->output.type < 0;
+  if (tied && p->token_embd.packed() && (c.d_model % 256))
+    return fail(RG_UNSUPPORTED_GEOMETRY, "a packed tied head needs d_model to be a multiple of 256");
+  RG_CUDA(cudaSetDevice(p->opt.device));
+  auto s = std::make_unique<rg_session>();
+  s->cfg = c;
+  s->opt = p->opt;
+  s->tp_rank = p->tp_rank;
+  s->tp_world = p->tp_world;
+  s->heads_l = c.n_heads / s->tp_world;
+  s->kv_l = c.n_kv_heads / s->tp_world;
+  s->ffn_l = c.ffn_dim / s->tp_world;
+  s->vocab_l = (!tied && s->tp_world > 1) ? c.vocab / s->tp_world : c.vocab;
+  s->max_batch = p->opt.max_batch > 0 ? p->opt.max_batch : 1;
+  s->ctx = p->opt.max_context > 0 ? p->opt.max_context : c.max_context;
+  if (s->ctx > c.max_context) return fail(RG_INVALID_ARGUMENT, "max_context above the model's context length");
+  s->kv_f32 = p->opt.kv_f32 != 0;
+  s->use_graph = !p->opt.disable_graph && !env_flag("RG_B200_DISABLE_GRAPH");
+  s->use_pdl = !p->opt.disable_pdl && !env_flag("RG_B200_DISABLE_PDL");
+  s->sm_count = p->sm_count;
+  RG_CUDA(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
+  RG_CUDA(cudaEventCreate(&s->ev0));
+  RG_CUDA(cudaEventCreate(&s->ev1));
+  if (s->tp_world > 1) {
+    std::string err;
+    int32_t rc = comm_init(&s->comm, p->opt.nccl_id, s->tp_rank, s->tp_world, &err);
+    if (rc) return fail(rc, err);
+  }
+  const int d = c.d_model, hd = c.head_dim;
+  const int qw = s->heads_l * hd, kw = s->kv_l * hd;
+  int32_t rc;
+#define RG_TRY(e)            \
+  if ((rc = (e))) return rc;
+  RG_TRY(dalloc(s.get(), &s->d_ctrl, 1));
+  RG_TRY(dalloc(s.get(), &s->d_ids, MAXC));
+  s->history_cap = 8192;
+  RG_TRY(dalloc(s.get(), &s->d_history, (size_t)s->history_cap * MAXC));
+  RG_TRY(dalloc(s.get(), &s->d_status, 1));
+  RG_TRY(dalloc(s.get(), &s->x, (size_t)MAXC * d));
+  RG_TRY(dalloc(s.get(), &s->xn_f32, (size_t)MAXC * d));
+  RG_TRY(dalloc(s.get(), &s->qkv, (size_t)MAXC * (qw + 2 * kw)));
+  RG_TRY(dalloc(s.get(), &s->q_rot, (size_t)MAXC * qw));
+  RG_TRY(dalloc(s.get(), &s->attn_scratch, attn_scratch_floats(MAXC, s->heads_l, hd, s->ctx)));
+  RG_TRY(dalloc(s.get(), &s->attn_f32, (size_t)MAXC * qw));
+  RG_TRY(dalloc(s.get(), &s->partial, (size_t)MAXC * d));
+  RG_TRY(dalloc(s.get(), &s->gate_f32, (size_t)MAXC * s->ffn_l));
+  RG_TRY(dalloc(s.get(), &s->up_f32, (size_t)MAXC * s->ffn_l));
+  RG_TRY(dalloc(s.get(), &s->h_f32, (size_t)MAXC * s->ffn_l));
+  RG_TRY(dalloc(s.get(), &s->logits, (size_t)MAXC * c.vocab));
+  RG_TRY(dalloc(s.get(), &s->logits_l, (size_t)MAXC * s->vocab_l));
+  uint8_t *raw;
+  RG_TRY(dalloc(s.get(), &raw, xpack_bytes(d, MAXC)));
+  s->xn_pack = raw;
+  RG_TRY(dalloc(s.get(), &raw, xpack_bytes(qw, MAXC)));
+  s->attn_pack = raw;
+  RG_TRY(dalloc(s.get(), &raw, xpack_bytes(s->ffn_l, MAXC)));
+  s->h_pack = raw;
+  RG_TRY(dalloc(s.get(), &raw, xpack_bytes(d, MAXC)));
+  s->head_pack = raw;
+  // RoPE tables in f64 on the host, cast to f32 (src/models/transformer/layer.rs:541-556)
+  {
+    const int half = hd / 2;
+    std::vector<float> cs((size_t)s->ctx * half), sn((size_t)s->ctx * half);
+    for (int i = 0; i < half; ++i) {
+      const double freq = 1.0 / pow(c.rope_theta, (double)(2 * i) / (double)hd);
+      for (int pos = 0; pos < s->ctx; ++pos) {
+        const double ang = (double)pos * freq;
+        cs[(size_t)pos * half + i] = (float)cos(ang);
+        sn[(size_t)pos * half + i] = (float)sin(ang);
+      }
+    }
+    RG_TRY(dalloc(s.get(), &s->cos_t, cs.size()));
+    RG_TRY(dalloc(s.get(), &s->sin_t, sn.size()));
+    RG_CUDA(cudaMemcpy(s->cos_t, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice));
+    RG_CUDA(cudaMemcpy(s->sin_t, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice));
+  }
+  const size_t kv_elems = (size_t)s->max_batch * s->kv_l * s->ctx * hd;
+  const size_t kv_item = s->kv_f32 ? 4 : 2;
+  for (int l = 0; l < c.n_layers; ++l) {
+    uint8_t *k, *v;
+    RG_TRY(dalloc(s.get(), &k, kv_elems * kv_item));
+    RG_TRY(dalloc(s.get(), &v, kv_elems * kv_item));
+    RG_CUDA(cudaMemsetAsync(k, 0, kv_elems * kv_item, s->stream));
+    RG_CUDA(cudaMemsetAsync(v, 0, kv_elems * kv_item, s->stream));
+    s->k_cache.push_back(k);
+    s->v_cache.push_back(v);
+    s->kv_bytes += 2 * kv_elems * kv_item;
+  }
+  RG_CUDA(cudaMemsetAsync(s->d_status, 0, sizeof(int), s->stream));
+  RG_CUDA(cudaMemsetAsync(s->d_ctrl, 0, sizeof(Ctrl), s->stream));
+  RG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&s->h_ctrl), sizeof(Ctrl)));
+  RG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&s->h_ids), sizeof(int32_t) * (size_t)s->history_cap * MAXC));
+  RG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&s->h_status), sizeof(int)));
+  RG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&s->h_logits), sizeof(float) * (size_t)MAXC * c.vocab));
+  memset(s->h_ctrl, 0, sizeof(Ctrl));
+  RG_CUDA(cudaStreamSynchronize(s->stream));
+#undef RG_TRY
+  // take ownership of the weights
+  s->layers = p->layers;
+  s->token_embd = p->token_embd;
+  s->output_norm = p->output_norm;
+  s->output = p->output;
+  s->head = tied ? &s->token_embd : &s->output;
+  s->weight_bytes = p->weight_bytes;
+  auto own = [&](DevTensor &t) {
+    if (t.d) s->owned.push_back(t.d);
+  };
+  own(s->token_embd);
+  own(s->output_norm);
+  own(s->output);
+  for (auto &L : s->layers)
+    for (DevTensor *t : {&L.attn_norm, &L.q, &L.k, &L.v, &L.o, &L.ffn_norm, &L.gate, &L.up, &L.down}) own(*t);
+  p->consumed = true;
+  s->position.assign((size_t)s->max_batch, 0);
+  s->report.weight_bytes = s->weight_bytes;
+  s->report.kv_bytes = s->kv_bytes;
+  *out = s.release();
+  return RG_OK;
+}
+
+void rg_b200_session_destroy(rg_session *s) {
+  if (!s) return;
+  cudaSetDevice(s->opt.device);
+  cudaStreamSynchronize(s->stream);
+  delete s;
+}
+
+int32_t rg_b200_position(const rg_session *s, int32_t row) {
+  if (!s || row < 0 || row >= s->max_batch) return -1;
+  return s->position[(size_t)row];
+}
+int32_t rg_b200_max_context(const rg_session *s) { return s ? s->ctx : -1; }
+int32_t rg_b200_vocab_size(const rg_session *s) { return s ? s->cfg.vocab : -1; }
+int32_t rg_b200_is_full(const rg_session *s) {
+  if (!s) return -1;
+  for (int32_t p : s->position)
+    if (p >= s->ctx) return 1;
+  return 0;
+}
+// Rewinds every row to position 0.  The cache is not cleared: stale rows lie beyond the causal
+// horizon and each row is rewritten before it is read (metal_generation.rs:847-859).
+int32_t rg_b200_reset_sequence(rg_session *s) {
+  int32_t rc = check_live(s);
+  if (rc) return rc;
+  std::fill(s->position.begin(), s->position.end(), 0);
+  return RG_OK;
+}
+
+int32_t rg_b200_prefill(rg_session *s, int32_t row, const int32_t *ids, size_t n, float *last_logits) {
+  int32_t rc = check_live(s);
+  if (rc) return rc;
+  if (!ids) return fail(RG_INVALID_ARGUMENT, "null ids");
+  if (row < 0 || row >= s->max_batch) return fail(RG_INVALID_ARGUMENT, "row out of range");
+  if (n == 0) return fail(RG_EMPTY_PROMPT, "empty token list");
+  const int base = s->position[(size_t)row];
+  if ((size_t)base + n > (size_t)s->ctx) return fail(RG_CONTEXT_EXHAUSTED, "position " + std::to_string(base) + " + " + std::to_string(n) + " tokens exceeds " + std::to_string(s->ctx));
+  for (size_t i = 0; i < n; ++i)
+    if (ids[i] < 0 || ids[i] >= s->cfg.vocab) return fail(RG_TOKEN_OUT_OF_RANGE, "token " + std::to_string(ids[i]) + " at index " + std::to_string(i));
+  RG_CUDA(cudaSetDevice(s->opt.device));
+  RG_CUDA(cudaEventRecord(s->ev0, s->stream));
+  for (size_t done = 0; done < n;) {
+    const int chunk = (int)std::min<size_t>(MAXC, n - done);
+    const bool last = done + (size_t)chunk == n;
+    Ctrl *h = s->h_ctrl;
+    for (int i = 0; i < chunk; ++i) {
+      h->tokens[i] = ids[done + (size_t)i];
+      h->pos[i] = base + (int)done + i;
+      h->seq[i] = row;
+    }
+    h->logit_cols[0] = chunk - 1;
+    h->step = 0;
+    if ((rc = upload_ctrl(s))) return rc;
+    if ((rc = run_step(s, chunk, last ? 1 : 0, false, false))) return rc;
+    // the pinned control block is reused by the next chunk: wait for the upload to be consumed
+    if (!last) RG_CUDA(x_sync(s->stream));
+    done += (size_t)chunk;
+  }
+  RG_CUDA(cudaEventRecord(s->ev1, s->stream));
+  if ((rc = finish_step(s, 1, last_logits, last_logits ? 1 : 0))) return rc;
+  cudaEventElapsedTime(&s->report.last_prefill_ms, s->ev0, s->ev1);
+  s->position[(size_t)row] = base + (int)n;  // commit only after the whole call succeeded
+  return RG_OK;
+}
+
+int32_t rg_b200_decode(rg_session *s, const int32_t *tokens, int32_t batch, float *logits, int32_t *greedy) {
+  int32_t rc = check_live(s);
+  if (rc) return rc;
+  if (!tokens) return fail(RG_INVALID_ARGUMENT, "null tokens");
+  if (batch < 1 || batch > s->max_batch) return fail(RG_INVALID_ARGUMENT, "batch out of range");
+  for (int i = 0; i < batch; ++i) {
+    if (tokens[i] < 0 || tokens[i] >= s->cfg.vocab) return fail(RG_TOKEN_OUT_OF_RANGE, "token " + std::to_string(tokens[i]) + " in row " + std::to_string(i));
+    if (s->position[(size_t)i] >= s->ctx) return fail(RG_CONTEXT_EXHAUSTED, "row " + std::to_string(i) + " is at position " + std::to_string(s->position[(size_t)i]) + " of " + std::to_string(s->ctx));
+  }
+  RG_CUDA(cudaSetDevice(s->opt.device));
+  Ctrl *h = s->h_ctrl;
+  for (int i = 0; i < batch; ++i) {
+    h->tokens[i] = tokens[i];
+    h->pos[i] = s->position[(size_t)i];
+    h->seq[i] = i;
+    h->logit_cols[i] = i;
+  }
+  h->step = 0;
+  RG_CUDA(cudaEventRecord(s->ev0, s->stream));
+  if ((rc = upload_ctrl(s))) return rc;
+  if ((rc = run_step(s, batch, batch, true, true))) return rc;
+  RG_CUDA(cudaEventRecord(s->ev1, s->stream));
+  rc = finish_step(s, batch, logits, logits ? batch : 0);
+  if (rc && rc != RG_NON_FINITE_LOGITS) return rc;
+  cudaEventElapsedTime(&s->report.last_decode_ms, s->ev0, s->ev1);
+  if (rc) return rc;  // non-finite logits: position unchanged (metal_generation.rs:892-898)
+  if (greedy) memcpy(greedy, s->h_ids, sizeof(int32_t) * (size_t)batch);
+  for (int i = 0; i < batch; ++i) s->position[(size_t)i] += 1;
+  return RG_OK;
+}
+
+int32_t rg_b200_generate_greedy(rg_session *s, const int32_t *prompt, size_t n_prompt, size_t max_new, int32_t *out, size_t *n_out,
+                                int32_t *stopped) {
+  int32_t rc = check_live(s);
+  if (rc) return rc;
+  if (!n_out || !stopped || (!out && max_new)) return fail(RG_INVALID_ARGUMENT, "null output");
+  *n_out = 0;
+  *stopped = 0;
+  if (!prompt || n_prompt == 0) return fail(RG_EMPTY_PROMPT, "empty prompt");
+  if (s->position[0] != 0) return fail(RG_FRESH_SESSION_REQUIRED, "sequence 0 is at position " + std::to_string(s->position[0]));
+  if (n_prompt + max_new > (size_t)s->ctx) return fail(RG_CONTEXT_EXHAUSTED, std::to_string(n_prompt + max_new) + " tokens requested of " + std::to_string(s->ctx));
+  for (size_t i = 0; i < n_prompt; ++i)
+    if (prompt[i] < 0 || prompt[i] >= s->cfg.vocab) return fail(RG_TOKEN_OUT_OF_RANGE, "token " + std::to_string(prompt[i]) + " at index " + std::to_string(i));
+  if (max_new == 0) return RG_OK;
+  if ((rc = rg_b200_prefill(s, 0, prompt, n_prompt, nullptr))) return rc;
+  int32_t token = s->h_ids[0];
+  for (size_t step = 0; step < max_new; ++step) {
+    out[(*n_out)++] = token;
+    if (token == s->cfg.eos_id || token == s->cfg.eot_id) {
+      *stopped = 1;
+      break;
+    }
+    if (step + 1 < max_new) {
+      int32_t next;
+      if ((rc = rg_b200_decode(s, &token, 1, nullptr, &next))) return rc;
+      token = next;
+    }
+  }
+  return RG_OK;
+}
+
+int32_t rg_b200_decode_loop(rg_session *s, const int32_t *first, int32_t batch, int32_t steps, int32_t *out, float *gpu_ms) {
+  int32_t rc = check_live(s);
+  if (rc) return rc;
+  if (!first || batch < 1 || batch > s->max_batch || steps < 1) return fail(RG_INVALID_ARGUMENT, "bad arguments");
+  if (steps > s->history_cap) return fail(RG_INVALID_ARGUMENT, "steps above the history capacity of " + std::to_string(s->history_cap));
+  for (int i = 0; i < batch; ++i) {
+    if (first[i] < 0 || first[i] >= s->cfg.vocab) return fail(RG_TOKEN_OUT_OF_RANGE, "token in row " + std::to_string(i));
+    if (s->position[(size_t)i] + steps > s->ctx) return fail(RG_CONTEXT_EXHAUSTED, "row " + std::to_string(i));
+  }
+  RG_CUDA(cudaSetDevice(s->opt.device));
+  Ctrl *h = s->h_ctrl;
+  for (int i = 0; i < batch; ++i) {
+    h->tokens[i] = first[i];
+    h->pos[i] = s->position[(size_t)i];
+    h->seq[i] = i;
+    h->logit_cols[i] = i;
+  }
+  h->step = 0;
+  if ((rc = upload_ctrl(s))) return rc;
+  if (s->use_graph) {
+    cudaGraphExec_t exec;
+    if ((rc = decode_graph(s, batch, &exec))) return rc;  // capture outside the timed region
+  }
+  RG_CUDA(cudaEventRecord(s->ev0, s->stream));
+  for (int i = 0; i < steps; ++i)
+    if ((rc = run_step(s, batch, batch, true, true))) {
+      s->poisoned = true;
+      return rc;
+    }
+  RG_CUDA(cudaEventRecord(s->ev1, s->stream));
+  const size_t hist_bytes = sizeof(int32_t) * (size_t)steps * (size_t)batch;
+  RG_CUDA(x_memcpy_async(s->h_ids, s->d_history, hist_bytes, cudaMemcpyDeviceToHost, s->stream));
+  s->report.d2h_calls++;
+  s->report.d2h_bytes += hist_bytes;
+  rc = finish_step(s, 0, nullptr, 0);
+  if (rc) return rc;
+  float ms = 0.0f;
+  cudaEventElapsedTime(&ms, s->ev0, s->ev1);
+  if (gpu_ms) *gpu_ms = ms;
+  s->report.last_decode_ms = ms / (float)steps;
+  for (size_t i = 0; i < (size_t)steps * (size_t)batch; ++i)
+    if (s->h_ids[i] < 0) {
+      s->poisoned = true;  // later steps consumed a sentinel token; the cache content is unproven
+      return fail(RG_NON_FINITE_LOGITS, "non-finite logits at step " + std::to_string(i / (size_t)batch));
+    }
+  if (out) memcpy(out, s->h_ids, hist_bytes);
+  for (int i = 0; i < batch; ++i) s->position[(size_t)i] += steps;
+  return RG_OK;
+}
+
+int32_t rg_b200_report(const rg_session *s, rg_report *out) {
+  if (!s || !out) return fail(RG_INVALID_ARGUMENT, "null argument");
+  *out = s->report;
+  return RG_OK;
+}
+void *rg_b200_session_stream(const rg_session *s) { return s ? (void *)s->stream : nullptr; }
+
+int32_t rg_b200_nccl_unique_id(uint8_t out[128]) {
+  if (!out) return fail(RG_INVALID_ARGUMENT, "null argument");
+  std::string err;
+  int32_t rc = comm_unique_id(out, &err);
+  return rc ? fail(rc, err) : RG_OK;
+}
+
+}  // extern "C"

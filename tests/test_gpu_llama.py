@@ -1,0 +1,258 @@
+"""GPU parity of the Llama session against the CPU checker on seeded synthetic models.
+
+Bar (floating point): every logit within 1e-2 absolute and 1e-3 relative of the reference CPU
+path (|a-b| <= 1e-2 and |a-b| <= 1e-3 * max|logit|), identical greedy token sequences."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from rustgrad_b200 import quant, session, synth
+
+pytestmark = pytest.mark.gpu
+
+ATOL, RTOL = 1e-2, 1e-3
+
+
+def assert_logits_close(got, want):
+    diff = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert diff.max() <= ATOL, diff.max()
+    assert diff.max() <= RTOL * np.abs(want).max() + 1e-6, (diff.max(), np.abs(want).max())
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    """BASELINE config 1: 2 layers, d 256, 4 heads, ffn 688, vocab 512, Q8_0, tied head, as a GGUF file."""
+    cfg = dict(synth.TINY)
+    tensors = synth.build_tensors(cfg, seed=0, body_type=quant.Q8_0)
+    data = synth.gguf_bytes(cfg, tensors)
+    prompt = synth.prompt_ids(cfg, 16, seed=1)
+    return cfg, tensors, data, prompt
+
+
+def make_session(data, **kw):
+    target = session.CudaSessionTarget(**kw)
+    plan = session.LlamaCudaPlan.from_gguf_bytes(data, target)
+    return target.prepare(plan)
+
+
+def test_config1_logits_and_greedy_tokens_match_reference_cpu_path(tiny):
+    cfg, tensors, data, prompt = tiny
+    oracle = O.OracleModel(cfg, tensors, threads=1)
+    want_ids, _ = oracle.generate_greedy(prompt, 32, O.MODE_STRICT)
+    s = make_session(data, kv_f32=True)
+    gen = s.generate_ids(prompt, 32)
+    assert gen.generated_ids == want_ids
+    assert not gen.stopped and s.position() == 16 + 31
+    # logits of the prefill and of every decode step
+    oracle.reset()
+    s.reset_sequence()
+    assert_logits_close(s.prefill_ids(prompt), oracle.forward(prompt))
+    for tok in want_ids[:8]:
+        assert_logits_close(s.run_token(tok), oracle.forward([tok]))
+    assert s.report()["fallback_count"] == 0 and s.report()["kernel_launches"] > 0
+
+
+def test_f16_kv_cache_matches_checker_with_f16_cache(tiny):
+    cfg, tensors, data, prompt = tiny
+    oracle = O.OracleModel(cfg, tensors, kv_f16=True, threads=1)
+    s = make_session(data)  # f16 cache is the default
+    assert_logits_close(s.prefill_ids(prompt), oracle.forward(prompt))
+    for tok in (5, 77, 300):
+        assert_logits_close(s.run_token(tok), oracle.forward([tok]))
+
+
+def test_prefill_equals_token_steps_and_graph_equals_direct_launch(tiny):
+    cfg, tensors, data, prompt = tiny
+    a = make_session(data, kv_f32=True)
+    full = a.prefill_ids(prompt)
+    b = make_session(data, kv_f32=True, disable_graph=True, disable_pdl=True)
+    for tok in prompt[:-1]:
+        b.run_token(int(tok))
+    step = b.run_token(int(prompt[-1]))
+    assert np.abs(full - step).max() <= 1e-4
+    c = make_session(data, kv_f32=True)
+    for tok in prompt[:-1]:
+        c.run_token(int(tok))
+    assert np.array_equal(c.run_token(int(prompt[-1])), step)  # graph + PDL replay is bit-identical
+
+
+def test_batched_rows_decode_independently(tiny):
+    cfg, tensors, data, _ = tiny
+    rows = [synth.prompt_ids(cfg, 6, seed=10 + r) for r in range(3)]
+    s = make_session(data, max_batch=3, kv_f32=True)
+    oracles = [O.OracleModel(cfg, tensors, threads=1) for _ in rows]
+    firsts = []
+    for r, p in enumerate(rows):
+        lg = s.prefill_ids(p, row=r)
+        want = oracles[r].forward(p)
+        assert_logits_close(lg, want)
+        firsts.append(O.select_greedy(want))
+    toks = firsts
+    for _ in range(5):
+        logits, greedy = s.decode(toks, want_logits=True)
+        nxt = []
+        for r in range(3):
+            want = oracles[r].forward([toks[r]])
+            assert_logits_close(logits[r], want)
+            nxt.append(O.select_greedy(want))
+        assert greedy.tolist() == nxt
+        toks = nxt
+    assert [s.position(r) for r in range(3)] == [11, 11, 11]
+
+
+def test_device_resident_loop_equals_host_driven_generation(tiny):
+    cfg, tensors, data, prompt = tiny
+    s = make_session(data, kv_f32=True)
+    gen = s.generate_ids(prompt, 20)
+    t = make_session(data, kv_f32=True)
+    logits = t.prefill_ids(prompt)
+    first = int(np.argmax(logits))
+    assert first == gen.generated_ids[0]
+    ids, ms = t.decode_loop([first], 19)
+    assert ids[:, 0].tolist() == gen.generated_ids[1:]
+    assert ms > 0 and t.position() == 16 + 19
+
+
+def test_q4_0_body_with_explicit_q8_0_head():
+    cfg = synth.scaled(synth.TINY, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn_dim=1024, vocab=640, n_layers=3,
+                       rope_theta=500000.0)
+    tensors = synth.build_tensors(cfg, seed=6, body_type=quant.Q4_0, embed_type=quant.Q8_0, head_type=quant.Q8_0,
+                                  tied_head=False)
+    prompt = synth.prompt_ids(cfg, 13, seed=2)
+    oracle = O.OracleModel(cfg, tensors, threads=4)
+    want_ids, _ = oracle.generate_greedy(prompt, 16, O.MODE_STRICT)
+    s = session.LlamaCudaPlan.from_tensors(cfg, tensors, session.CudaSessionTarget(kv_f32=True)).prepare()
+    assert s.generate_ids(prompt, 16).generated_ids == want_ids
+    oracle.reset()
+    s.reset_sequence()
+    assert_logits_close(s.prefill_ids(prompt), oracle.forward(prompt))
+
+
+def test_stop_on_eos_and_last_token_not_fed_back(tiny):
+    cfg, tensors, data, prompt = tiny
+    s = make_session(data, kv_f32=True)
+    ids = s.generate_ids(prompt, 10).generated_ids
+    cfg2 = dict(cfg, eos_id=ids[3])
+    plan = session.LlamaCudaPlan.from_tensors(cfg2, tensors, session.CudaSessionTarget(kv_f32=True))
+    s2 = plan.prepare()
+    gen = s2.generate_ids(prompt, 10)
+    first = ids.index(ids[3])
+    assert gen.stopped and gen.generated_ids == ids[: first + 1]
+    assert s2.position() == 16 + first  # the stop token is never fed back
+
+
+def test_typed_failures_leave_the_session_unchanged(tiny):
+    cfg, tensors, data, prompt = tiny
+    s = make_session(data, kv_f32=True)
+    E = session
+    with pytest.raises(E.EmptyPrompt):
+        s.generate_ids([], 4)
+    with pytest.raises(E.TokenOutOfRange):
+        s.generate_ids([1, 512], 4)
+    with pytest.raises(E.TokenOutOfRange):
+        s.prefill_ids([-1])
+    with pytest.raises(E.ContextExhausted):
+        s.generate_ids(prompt, cfg["max_context"])
+    assert s.position() == 0
+    assert s.generate_ids(prompt, 0).generated_ids == []
+    s.prefill_ids(prompt)
+    with pytest.raises(E.FreshSessionRequired):
+        s.generate_ids(prompt, 2)
+    with pytest.raises(E.ContextExhausted):
+        s.prefill_ids([1] * (cfg["max_context"] - 15))
+    with pytest.raises(E.InvalidArgument):
+        s.decode([1, 2])  # batch above max_batch
+    assert s.position() == 16 and not s.is_full()
+    s.reset_sequence()
+    assert s.position() == 0
+    assert s.generate_ids(prompt, 3).generated_ids == make_session(data, kv_f32=True).generate_ids(prompt, 3).generated_ids
+
+
+def test_binding_rejections_precede_device_work(tiny):
+    cfg, tensors, _, _ = tiny
+    E = session
+    target = E.CudaSessionTarget()
+
+    def plan_with(change):
+        t = dict(tensors)
+        change(t)
+        return E.LlamaCudaPlan.from_tensors(cfg, t, target)
+
+    with pytest.raises(E.UnexpectedTensor):
+        plan_with(lambda t: t.update({"blk.0.attn_q.extra": t["blk.0.attn_q.weight"]}))
+    with pytest.raises(E.ShapeMismatch):
+        plan_with(lambda t: t.update({"blk.0.attn_k.weight": (quant.Q8_0, 128, 256, t["blk.0.attn_k.weight"][3][: 128 * 272])}))
+    with pytest.raises(E.UnsupportedType):
+        plan_with(lambda t: t.update({"output_norm.weight": (quant.Q8_0, 1, 256, np.zeros(272, np.uint8))}))
+    with pytest.raises(E.UnsupportedType):
+        plan_with(lambda t: t.update({"blk.1.ffn_up.weight": (12, 688, 256, np.zeros(688 * 144, np.uint8))}))
+
+    def poison(t):
+        kind, rows, cols, data = t["blk.1.ffn_gate.weight"]
+        data = data.copy()
+        data[34 * 5 + 1] = 0x7C
+        t["blk.1.ffn_gate.weight"] = (kind, rows, cols, data)
+
+    with pytest.raises(E.NonFiniteScale):
+        plan_with(poison)
+    missing = dict(tensors)
+    del missing["blk.1.ffn_norm.weight"]
+    with pytest.raises(E.MissingTensor):
+        E.LlamaCudaPlan.from_tensors(cfg, missing, target).prepare()
+    with pytest.raises(E.UnsupportedGeometry):  # packed K must be a multiple of 256
+        c2 = synth.scaled(cfg, d_model=128, n_heads=2, n_kv_heads=2)
+        E.LlamaCudaPlan.from_tensors(c2, synth.build_tensors(c2, 0), target)
+
+
+def test_host_injected_failures_are_typed_and_recoverable(tiny):
+    """Fault injection on the host side of the runtime (no GPU fault is ever provoked)."""
+    from rustgrad_b200 import _lib
+    cfg, tensors, data, prompt = tiny
+    L = _lib.load()
+    s = make_session(data, kv_f32=True, disable_graph=True)
+    s.prefill_ids(prompt[:4])
+    L.rg_b200_test_fail_after(b"launch", 5)
+    with pytest.raises(session.CudaError):
+        s.run_token(3)
+    assert s.position() == 4                      # position unchanged
+    logits = s.run_token(3)                       # retry succeeds
+    ref = make_session(data, kv_f32=True, disable_graph=True)
+    ref.prefill_ids(prompt[:4])
+    assert np.array_equal(logits, ref.run_token(3))
+    L.rg_b200_test_fail_after(b"sync", 0)
+    with pytest.raises(session.Poisoned):         # completion unprovable -> poisoned
+        s.run_token(4)
+    L.rg_b200_test_fail_after(b"sync", -1)
+    with pytest.raises(session.Poisoned):
+        s.run_token(4)
+    L.rg_b200_test_fail_after(b"malloc", 3)
+    with pytest.raises(session.OutOfMemory):
+        make_session(data)
+    L.rg_b200_test_fail_after(b"malloc", -1)
+    make_session(data).prefill_ids(prompt)
+
+
+def test_device_synthesized_weights_match_host_recipe():
+    """The device generator + GGML quantizer are reproducible on the host, bit for bit."""
+    cfg = synth.scaled(synth.TINY, n_layers=1, vocab=64)
+    plan = session.LlamaCudaPlan.empty(cfg, session.CudaSessionTarget())
+    for name, kind, rows, cols in (("blk.0.attn_q.weight", quant.Q4_0, 256, 256), ("blk.0.ffn_gate.weight", quant.Q8_0, 688, 256),
+                                   ("blk.0.ffn_down.weight", quant.F32, 256, 688), ("token_embd.weight", quant.F16, 64, 256)):
+        plan.synth_tensor(name, kind, rows, cols, seed=42, std=0.02)
+        got = plan.read_tensor(name)
+        e = np.arange(rows * cols, dtype=np.uint64)
+        total = np.zeros(rows * cols, dtype=np.uint64)
+        with np.errstate(over="ignore"):
+            for i in range(4):
+                z = np.uint64(42) * np.uint64(0xD1342543DE82EF95) + e * np.uint64(4) + np.uint64(i)
+                z = z + np.uint64(0x9E3779B97F4A7C15)
+                z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+                z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+                z = z ^ (z >> np.uint64(31))
+                for sh in (0, 16, 32, 48):
+                    total += (z >> np.uint64(sh)) & np.uint64(0xFFFF)
+        normal = (total.astype(np.int64) - 524280).astype(np.float32) * np.float32(1.0 / 75674.5234375)
+        w = (normal * np.float32(0.02)).astype(np.float32)
+        assert abs(float(normal.std()) - 1.0) < 0.02 and abs(float(normal.mean())) < 0.02
+        want = quant.encode(kind, w.reshape(rows, cols))
+        assert np.array_equal(got, want.reshape(-1)), name
