@@ -265,6 +265,11 @@ struct rg_session {
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   rg_report report{};
   uint64_t launches_in_step = 0;
+  // profiling pass: events recorded between kernel families while a step is captured
+  bool prof = false;
+  std::vector<cudaEvent_t> prof_events;
+  std::vector<int> prof_kinds;
+  size_t prof_used = 0;
 
   ~rg_session() {
     for (auto &g : graphs) cudaGraphExecDestroy(g.second);
@@ -275,6 +280,7 @@ struct rg_session {
     if (h_logits) cudaFreeHost(h_logits);
     if (ev0) cudaEventDestroy(ev0);
     if (ev1) cudaEventDestroy(ev1);
+    for (cudaEvent_t e : prof_events) cudaEventDestroy(e);
     comm_destroy(&comm);
     if (stream) cudaStreamDestroy(stream);
   }
@@ -309,12 +315,27 @@ static LaunchCfg lcfg(rg_session *s) {
                                      __FILE__ + ":" + std::to_string(__LINE__) + ")");         \
   } while (0)
 
+enum ProfKind { PROF_GEMV = 0, PROF_ATTN = 1, PROF_OTHER = 2, PROF_END = 3 };
+
+// Marks the start of a kernel family in the profiling pass (no-op otherwise).
+static void prof_mark(rg_session *s, int kind) {
+  if (!s->prof) return;
+  if (s->prof_used == s->prof_events.size()) {
+    cudaEvent_t e;
+    if (cudaEventCreate(&e) != cudaSuccess) return;
+    s->prof_events.push_back(e);
+  }
+  cudaEventRecord(s->prof_events[s->prof_used++], s->stream);
+  s->prof_kinds.push_back(kind);
+}
+
 // y = W x for one projection given as `n` row segments sharing K.  Packed segments of one type go
 // out as a single fused launch; dense ones run the dense kernel segment by segment.
 static int32_t linear(rg_session *s, const DevTensor *const *w, int n, const void *in_pack, const float *in_f32, int ld_in,
                       int batch, int epi, float *y, int ldy) {
   bool all_packed = true;
   for (int i = 0; i < n; ++i) all_packed = all_packed && w[i]->packed() && w[i]->type == w[0]->type;
+  prof_mark(s, PROF_GEMV);
   if (all_packed) {
     GemvArgs a;
     a.type = w[0]->type;
@@ -369,6 +390,7 @@ static int32_t linear(rg_session *s, const DevTensor *const *w, int n, const voi
 static int32_t tp_reduce_add(rg_session *s, int ncols) {
   const int d = s->cfg.d_model;
   std::string err;
+  prof_mark(s, PROF_OTHER);
   int32_t rc = comm_allreduce_sum_f32(&s->comm, s->partial, (size_t)ncols * d, s->stream, &err);
   if (rc) return fail(rc, err);
   LaunchCfg c = lcfg(s);
@@ -387,15 +409,18 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
   LaunchCfg L = lcfg(s);
   LaunchCfg first = L;
   first.pdl = false;  // follows a memcpy, not a kernel
+  prof_mark(s, PROF_OTHER);
   RG_LAUNCH(s, launch_row_gather(s->token_embd.type, s->token_embd.d, d, ctl->tokens, ncols, s->x, d, first));
   for (int l = 0; l < c.n_layers; ++l) {
     const LayerW &W = s->layers[(size_t)l];
     const bool qkv_dense = !W.q.packed() || !W.k.packed() || !W.v.packed();
+    prof_mark(s, PROF_OTHER);
     RG_LAUNCH(s, launch_rmsnorm_pack(s->x, d, reinterpret_cast<const float *>(W.attn_norm.d), d, c.norm_eps, ncols, nullptr,
                                      s->xn_pack, qkv_dense ? s->xn_f32 : nullptr, d, L));
     const DevTensor *qkvw[3] = {&W.q, &W.k, &W.v};
     int32_t rc = linear(s, qkvw, 3, s->xn_pack, s->xn_f32, d, ncols, EPI_STORE, s->qkv, qkv_w);
     if (rc) return rc;
+    prof_mark(s, PROF_ATTN);
     RopeArgs ra;
     ra.qkv = s->qkv;
     ra.cols = ncols;
@@ -439,9 +464,11 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
     LaunchCfg after = L;
     if (s->tp_world > 1) after.pdl = false;
     const bool gu_dense = !W.gate.packed() || !W.up.packed() || W.gate.type != W.up.type;
+    prof_mark(s, PROF_OTHER);
     RG_LAUNCH(s, launch_rmsnorm_pack(s->x, d, reinterpret_cast<const float *>(W.ffn_norm.d), d, c.norm_eps, ncols, nullptr,
                                      s->xn_pack, gu_dense ? s->xn_f32 : nullptr, d, after));
     if (!gu_dense) {
+      prof_mark(s, PROF_GEMV);
       GemvArgs a;
       a.type = W.gate.type;
       a.nseg = 2;
@@ -472,6 +499,7 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
   if (n_logit_cols > 0) {
     LaunchCfg after = L;
     if (s->tp_world > 1) after.pdl = false;
+    prof_mark(s, PROF_OTHER);
     RG_LAUNCH(s, launch_rmsnorm_pack(s->x, d, reinterpret_cast<const float *>(s->output_norm.d), d, c.norm_eps, n_logit_cols,
                                      ctl->logit_cols, s->head_pack, s->head->packed() ? nullptr : s->xn_f32, d, after));
     const DevTensor *hw[1] = {s->head};
@@ -491,9 +519,11 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
       if ((rc = comm_group_end(&err))) return fail(rc, err);
       am.pdl = false;
     }
+    prof_mark(s, PROF_OTHER);
     RG_LAUNCH(s, launch_argmax(s->logits, c.vocab, c.vocab, n_logit_cols, s->d_ids, am));
     if (advance) RG_LAUNCH(s, launch_advance(s->d_ids, ctl->tokens, ctl->pos, s->d_history, &ctl->step, ncols, L));
   }
+  prof_mark(s, PROF_END);
   return RG_OK;
 }
 
@@ -1139,6 +1169,90 @@ int32_t rg_b200_decode_loop(rg_session *s, const int32_t *first, int32_t batch, 
       return fail(RG_NON_FINITE_LOGITS, "non-finite logits at step " + std::to_string(i / (size_t)batch));
     }
   if (out) memcpy(out, s->h_ids, hist_bytes);
+  for (int i = 0; i < batch; ++i) s->position[(size_t)i] += steps;
+  return RG_OK;
+}
+
+int32_t rg_b200_decode_profile(rg_session *s, const int32_t *first, int32_t batch, int32_t steps, float out_ms[4],
+                               uint64_t out_marks[4]) {
+  int32_t rc = check_live(s);
+  if (rc) return rc;
+  if (!first || !out_ms || batch < 1 || batch > s->max_batch || steps < 1) return fail(RG_INVALID_ARGUMENT, "bad arguments");
+  for (int i = 0; i < batch; ++i) {
+    if (first[i] < 0 || first[i] >= s->cfg.vocab) return fail(RG_TOKEN_OUT_OF_RANGE, "token in row " + std::to_string(i));
+    if (s->position[(size_t)i] + steps > s->ctx) return fail(RG_CONTEXT_EXHAUSTED, "row " + std::to_string(i));
+  }
+  RG_CUDA(cudaSetDevice(s->opt.device));
+  Ctrl *h = s->h_ctrl;
+  for (int i = 0; i < batch; ++i) {
+    h->tokens[i] = first[i];
+    h->pos[i] = s->position[(size_t)i];
+    h->seq[i] = i;
+    h->logit_cols[i] = i;
+  }
+  h->step = 0;
+  if ((rc = upload_ctrl(s))) return rc;
+  // a step graph of its own: no programmatic overlap, so the events bound whole kernels
+  const bool saved_pdl = s->use_pdl;
+  s->use_pdl = false;
+  s->launches_in_step = 0;
+  rc = forward(s, batch, batch, true);  // loads every kernel before capture
+  if (!rc) {
+    cudaError_t e = x_memcpy_async(s->d_ctrl, s->h_ctrl, sizeof(Ctrl), cudaMemcpyHostToDevice, s->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s->stream);
+    if (e != cudaSuccess) rc = fail(RG_CUDA_ERROR, cudaGetErrorString(e));
+  }
+  cudaGraphExec_t exec = nullptr;
+  if (!rc) {
+    s->prof = true;
+    s->prof_used = 0;
+    s->prof_kinds.clear();
+    cudaError_t e = cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal);
+    if (e == cudaSuccess) {
+      rc = forward(s, batch, batch, true);
+      cudaGraph_t graph = nullptr;
+      e = cudaStreamEndCapture(s->stream, &graph);
+      if (e == cudaSuccess && !rc) e = cudaGraphInstantiate(&exec, graph, 0);
+      if (graph) cudaGraphDestroy(graph);
+    }
+    s->prof = false;
+    if (!rc && e != cudaSuccess) rc = fail(RG_CUDA_ERROR, std::string("profile graph: ") + cudaGetErrorString(e));
+  }
+  s->use_pdl = saved_pdl;
+  if (rc) {
+    if (exec) cudaGraphExecDestroy(exec);
+    return rc;
+  }
+  double sums[4] = {0, 0, 0, 0};
+  uint64_t marks[4] = {0, 0, 0, 0};
+  for (int it = 0; it < steps && !rc; ++it) {
+    cudaError_t e = cudaGraphLaunch(exec, s->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s->stream);
+    if (e != cudaSuccess) {
+      rc = fail(RG_CUDA_ERROR, std::string("profile replay: ") + cudaGetErrorString(e));
+      break;
+    }
+    for (size_t i = 0; i + 1 < s->prof_used; ++i) {
+      float ms = 0.0f;
+      if (cudaEventElapsedTime(&ms, s->prof_events[i], s->prof_events[i + 1]) != cudaSuccess) {
+        rc = fail(RG_CUDA_ERROR, "event timing inside a graph is unavailable");
+        break;
+      }
+      sums[s->prof_kinds[i]] += ms;
+      sums[3] += ms;
+      if (it == 0) marks[s->prof_kinds[i]]++;
+    }
+  }
+  cudaGraphExecDestroy(exec);
+  if (rc) {
+    s->poisoned = true;
+    return rc;
+  }
+  if ((rc = finish_step(s, 0, nullptr, 0))) return rc;
+  for (int k = 0; k < 4; ++k) {
+    out_ms[k] = (float)(sums[k] / steps);
+    if (out_marks) out_marks[k] = marks[k];
+  }
   for (int i = 0; i < batch; ++i) s->position[(size_t)i] += steps;
   return RG_OK;
 }
