@@ -1,0 +1,292 @@
+"""Decode-throughput benchmark of the GGUF-quantized Llama session (one JSON line on stdout).
+
+    python bench.py --gpus 1 --steps 256 --warmup 8
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference ...        # the CPU restatement of the reference path
+
+A step is one greedy decode step (one new token per row) of a seeded synthetic model:
+  * N = 1: Llama-3-8B shape, Q4_0 projections, Q8_0 embedding and head, f16 KV cache, batch 1,
+    decoded after a 2048-token prefill;
+  * N > 1: Llama-3-70B shape, all Q4_0, tensor-parallel over N GPUs (strong scaling).
+`value` times K replays of the decode graph with the selected token fed back on the device
+(inputs resident in HBM); `e2e` times K calls of the session's decode verb with host tokens in
+and host ids out.  The weights (4.5 GB / 39 GB) are far larger than L2, so every step reads HBM.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import numpy as np  # noqa: E402
+
+from rustgrad_b200 import quant, synth  # noqa: E402
+
+PREFILL = 2048
+# dram__bytes_read.sum + dram__bytes_write.sum of one qgemv launch on the gate/up shape, from the
+# ncu capture summarised in profiles/ (None until captured)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        peaks = json.loads(path.read_text())
+        return float(peaks["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def workload(n_gpus: int):
+    if n_gpus == 1:
+        return dict(name="llama3_8b_shape_q4_0_decode_b1", cfg=dict(synth.LLAMA_8B), seed=6, body=quant.Q4_0, embed=quant.Q8_0,
+                    head=quant.Q8_0)
+    return dict(name=f"llama3_70b_shape_q4_0_decode_b1_tp{n_gpus}", cfg=dict(synth.LLAMA_70B), seed=7, body=quant.Q4_0,
+                embed=quant.Q4_0, head=quant.Q4_0)
+
+
+def gemv_bytes_per_step(cfg: dict, wl: dict, tp: int, batch: int):
+    """Algorithmic bytes of the quantized GEMV launches of one decode step on one rank:
+    packed weight bytes + f32 activations in + f32 results out (N*K*18/32 + 4*B*K + 4*B*N)."""
+    d, f, hd = cfg["d_model"], cfg["ffn_dim"], cfg["head_dim"]
+    qw, kw = cfg["n_heads"] * hd // tp, cfg["n_kv_heads"] * hd // tp
+    fl = f // tp
+
+    def one(n, k, t):
+        return n * k * quant.BLOCK_BYTES[t] // 32 + 4 * batch * k + 4 * batch * n
+
+    body = wl["body"]
+    layer = one(qw + 2 * kw, d, body) + one(d, qw, body) + one(2 * fl, d, body) + one(d, fl, body)
+    head = one(cfg["vocab"] // tp, d, wl["head"])
+    launches = 4 * cfg["n_layers"] + 1
+    return cfg["n_layers"] * layer + head, launches
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device, self.proc = device, None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.device)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.summary = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.proc:
+            return
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            self.summary = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                            "samples": len(sm)}
+
+
+def cpu_reference_arm(args, wl, threads):
+    """Times the CPU restatement of the reference path on a bounded sample of the workload.
+
+    One decode token costs t_head + L * t_layer.  The sample runs the full-width model with 1 and
+    with 3 layers and an eighth of the vocabulary rows in embedding and head, takes
+    t_layer = (T3 - T1) / 2 and t_head = 8 * (T1 - t_layer), and scales to the model's layer count.
+    Weights come from the host generator (same distribution as the device generator); the context
+    is a 16-token prompt.
+    """
+    from oracle import oracle as O
+    cfg = wl["cfg"]
+    steps = max(1, min(args.steps, 3))
+    vocab_div = 8
+    sub3 = synth.scaled(cfg, n_layers=3, max_context=64, vocab=cfg["vocab"] // vocab_div)
+    tensors3 = synth.build_tensors(sub3, seed=wl["seed"], body_type=wl["body"], embed_type=wl["embed"], head_type=wl["head"],
+                                   tied_head=False)
+    times = {}
+    for layers in (1, 3):
+        sub = synth.scaled(sub3, n_layers=layers)
+        keep = {k: v for k, v in tensors3.items() if not k.startswith("blk.") or int(k.split(".")[1]) < layers}
+        m = O.OracleModel(sub, keep, kv_f16=True, threads=threads)
+        m.forward(synth.prompt_ids(sub, 16, seed=1), O.MODE_FAST)
+        m.forward([1], O.MODE_FAST)  # warm-up step
+        t0 = time.perf_counter()
+        for i in range(steps):
+            m.forward([2 + i], O.MODE_FAST)
+        times[layers] = (time.perf_counter() - t0) / steps
+        m.close()
+    t_layer = max((times[3] - times[1]) / 2.0, 1e-9)
+    t_head = max(times[1] - t_layer, 0.0) * vocab_div
+    t_token = t_head + cfg["n_layers"] * t_layer
+    sample = (f"{steps} decode steps each of a 1-layer and a 3-layer full-width model with vocab/{vocab_div} rows, "
+              f"scaled to {cfg['n_layers']} layers and the full vocabulary")
+    return 1.0 / t_token, t_token, sample
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--prefill", type=int, default=PREFILL)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    n = args.gpus
+    wl = workload(n)
+    cfg = wl["cfg"]
+    threads = os.cpu_count() or 1
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        tok_s, t_token, sample = cpu_reference_arm(args, wl, threads)
+        line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": n,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_token * 1e3, "higher_is_better": True,
+                "scaling": "weak" if n == 1 else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": wl["name"], "batch": 1, "context": 16},
+                "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+                "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    import torch
+    from rustgrad_b200 import session
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: rustgrad_b200 has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    nccl_id = b""
+    if n > 1:
+        if world != n:
+            raise SystemExit(f"--gpus {n} needs torchrun with {n} ranks (WORLD_SIZE={world})")
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        box = [session.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        nccl_id = box[0]
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    prefill = min(args.prefill, cfg["max_context"] - 2 * (args.steps + args.warmup) - 80)
+    target = session.CudaSessionTarget(device=local_rank, max_batch=1, tp_rank=rank if n > 1 else 0, tp_world=n, nccl_id=nccl_id)
+    plan = session.LlamaCudaPlan.synthetic(cfg, target, seed=wl["seed"], body_type=wl["body"], embed_type=wl["embed"],
+                                           head_type=wl["head"])
+    sess = target.prepare(plan)
+    prompt = synth.prompt_ids(cfg, prefill, seed=1)
+    logits = sess.prefill_ids(prompt)
+    first = int(np.argmax(logits))
+    prefill_ms = sess.report()["last_prefill_ms"]
+
+    # ---- device-resident loop: W warm-up steps, then exactly K timed steps
+    ids, _ = sess.decode_loop([first], args.warmup)
+    tok = int(ids[-1, 0])
+    r0 = sess.report()
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        ids, gpu_ms = sess.decode_loop([tok], args.steps)
+        torch.cuda.synchronize()
+    barrier()
+    r1 = sess.report()
+    tok = int(ids[-1, 0])
+    launches = r1["kernel_launches"] - r0["kernel_launches"]
+
+    # ---- end to end through the decode verb: host token in, host id out, every step
+    for _ in range(3):
+        _, g = sess.decode([tok])
+        tok = int(g[0])
+    r2 = sess.report()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        _, g = sess.decode([tok])
+        tok = int(g[0])
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    r3 = sess.report()
+
+    # ---- profiling pass: CUDA events between kernel families (serialized, no overlap)
+    prof = sess.decode_profile([tok], 16)
+    position = sess.position()
+
+    t = torch.tensor([gpu_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    gpu_ms, e2e_ms = float(t[0]), float(t[1])
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peaks()
+    gemv_bytes, gemv_launches = gemv_bytes_per_step(cfg, wl, n, 1)
+    gemv_ms = prof["gemv"]["ms_per_step"]
+    achieved = gemv_bytes / (gemv_ms * 1e-3) / 1e9 if gemv_ms > 0 else None
+    ms_per_step = gpu_ms / args.steps
+    line = {
+        "metric": "decode_tokens_per_s", "value": args.steps / (gpu_ms * 1e-3), "unit": "tokens/s", "n_gpus": n,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak" if n == 1 else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl["name"], "batch": 1, "prefill_tokens": prefill, "context_at_end": position,
+                   "kv_cache": "f16", "weights": "Q4_0 body, Q8_0 embedding+head" if n == 1 else "Q4_0",
+                   "parallelism": "single GPU" if n == 1 else f"tp{n}", "l2": "inputs larger than L2 (weights >> 126 MB)",
+                   "prefill_ms": prefill_ms},
+        "e2e": {"value": args.steps / (e2e_ms * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": (r3["h2d_bytes"] - r2["h2d_bytes"]) / args.steps,
+                "d2h_bytes_per_step": (r3["d2h_bytes"] - r2["d2h_bytes"]) / args.steps},
+        "gpu_launches": launches,
+        "clocks": clocks.summary,
+        "roofline": {"bound": "hbm", "kernel": "qgemv_kernel (all quantized GEMV launches of a step)", "achieved": achieved,
+                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak if achieved else None,
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "launches_per_step": gemv_launches,
+                     "algorithmic_bytes_per_step": gemv_bytes, "kernel_ms_per_step": gemv_ms,
+                     "step_bytes_over_step_time_gbs": (gemv_bytes / (ms_per_step * 1e-3) / 1e9)},
+        "profile_ms_per_step": {k: v["ms_per_step"] for k, v in prof.items()},
+    }
+    if n == 1 and not args.no_cpu_baseline:
+        tok_s, t_token, sample = cpu_reference_arm(args, wl, threads)
+        line["cpu_baseline"] = {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

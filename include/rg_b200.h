@@ -173,13 +173,14 @@ int32_t rg_b200_generate_greedy(rg_session *s, const int32_t *prompt, size_t n_p
  * receives the ids after the last step.  gpu_ms (nullable) is the CUDA-event time of the loop. */
 int32_t rg_b200_decode_loop(rg_session *s, const int32_t *first_tokens, int32_t batch, int32_t steps,
                             int32_t *out, float *gpu_ms);
-/* Profiling pass in the vocabulary of rustgrad's CUDA event recorder (src/cuda_profile.rs:15-60):
- * `steps` greedy decode steps replayed from a graph without programmatic overlap, CUDA events
- * between kernel families.  out_ms / out_marks: [0] quantized GEMV launches, [1] RoPE + KV append +
- * attention, [2] norms, embedding, selection and collectives, [3] whole step; milliseconds per step
- * and timed intervals per step.  Advances rows 0..batch-1 by `steps` like rg_b200_decode_loop. */
+/* Profiling pass in the vocabulary of rustgrad's CUDA event recorder (src/cuda_profile.rs:15-60).
+ * The launches of one decode step are replayed one kernel family at a time, serialized (no
+ * programmatic overlap), `steps` times between two CUDA events on the session's stream.
+ * out_ms / out_launches: [0] quantized GEMV launches, [1] RoPE + KV append + attention,
+ * [2] norms, embedding, selection and collectives, [3] their sum; milliseconds per step and
+ * kernels per step.  Positions are not advanced and nothing is committed. */
 int32_t rg_b200_decode_profile(rg_session *s, const int32_t *first_tokens, int32_t batch, int32_t steps,
-                               float out_ms[4], uint64_t out_marks[4]);
+                               float out_ms[4], uint64_t out_launches[4]);
 int32_t rg_b200_report(const rg_session *s, rg_report *out);
 /* cudaStream_t the session launches on (for CUDA-event timing by the caller). */
 void *rg_b200_session_stream(const rg_session *s);

@@ -265,11 +265,9 @@ struct rg_session {
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   rg_report report{};
   uint64_t launches_in_step = 0;
-  // profiling pass: events recorded between kernel families while a step is captured
-  bool prof = false;
-  std::vector<cudaEvent_t> prof_events;
-  std::vector<int> prof_kinds;
-  size_t prof_used = 0;
+  // profiling pass: only the kernel families in family_mask are launched
+  unsigned family_mask = 0xffffffffu;
+  int cur_kind = 0;
 
   ~rg_session() {
     for (auto &g : graphs) cudaGraphExecDestroy(g.second);
@@ -280,7 +278,6 @@ struct rg_session {
     if (h_logits) cudaFreeHost(h_logits);
     if (ev0) cudaEventDestroy(ev0);
     if (ev1) cudaEventDestroy(ev1);
-    for (cudaEvent_t e : prof_events) cudaEventDestroy(e);
     comm_destroy(&comm);
     if (stream) cudaStreamDestroy(stream);
   }
@@ -306,28 +303,22 @@ static LaunchCfg lcfg(rg_session *s) {
   return c;
 }
 
-#define RG_LAUNCH(s, expr)                                                                     \
-  do {                                                                                         \
-    cudaError_t e__ = x_launch(expr);                                                          \
-    (s)->launches_in_step++;                                                                   \
-    if (e__ != cudaSuccess)                                                                    \
-      return fail(RG_CUDA_ERROR, std::string(#expr) + ": " + cudaGetErrorString(e__) + " (" +  \
-                                     __FILE__ + ":" + std::to_string(__LINE__) + ")");         \
+#define RG_LAUNCH(s, expr)                                                                       \
+  do {                                                                                           \
+    if ((s)->family_mask & (1u << (s)->cur_kind)) {                                              \
+      cudaError_t e__ = x_launch(expr);                                                          \
+      (s)->launches_in_step++;                                                                   \
+      if (e__ != cudaSuccess)                                                                    \
+        return fail(RG_CUDA_ERROR, std::string(#expr) + ": " + cudaGetErrorString(e__) + " (" +  \
+                                       __FILE__ + ":" + std::to_string(__LINE__) + ")");         \
+    }                                                                                            \
   } while (0)
 
 enum ProfKind { PROF_GEMV = 0, PROF_ATTN = 1, PROF_OTHER = 2, PROF_END = 3 };
 
-// Marks the start of a kernel family in the profiling pass (no-op otherwise).
-static void prof_mark(rg_session *s, int kind) {
-  if (!s->prof) return;
-  if (s->prof_used == s->prof_events.size()) {
-    cudaEvent_t e;
-    if (cudaEventCreate(&e) != cudaSuccess) return;
-    s->prof_events.push_back(e);
-  }
-  cudaEventRecord(s->prof_events[s->prof_used++], s->stream);
-  s->prof_kinds.push_back(kind);
-}
+// Names the kernel family of the launches that follow; the profiling pass launches one family
+// at a time.
+static inline void prof_mark(rg_session *s, int kind) { s->cur_kind = kind; }
 
 // y = W x for one projection given as `n` row segments sharing K.  Packed segments of one type go
 // out as a single fused launch; dense ones run the dense kernel segment by segment.
@@ -391,6 +382,7 @@ static int32_t tp_reduce_add(rg_session *s, int ncols) {
   const int d = s->cfg.d_model;
   std::string err;
   prof_mark(s, PROF_OTHER);
+  if (!(s->family_mask & (1u << PROF_OTHER))) return RG_OK;
   int32_t rc = comm_allreduce_sum_f32(&s->comm, s->partial, (size_t)ncols * d, s->stream, &err);
   if (rc) return fail(rc, err);
   LaunchCfg c = lcfg(s);
@@ -453,7 +445,7 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
     aa.out_pack = s->attn_pack;
     aa.out_f32 = W.o.packed() ? nullptr : s->attn_f32;
     RG_LAUNCH(s, launch_attention(aa, L));
-    s->launches_in_step++;  // split + combine
+    if (s->family_mask & (1u << PROF_ATTN)) s->launches_in_step++;  // split + combine
     const DevTensor *ow[1] = {&W.o};
     if (s->tp_world > 1) {
       if ((rc = linear(s, ow, 1, s->attn_pack, s->attn_f32, qw, ncols, EPI_STORE, s->partial, d))) return rc;
@@ -509,7 +501,8 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
     int32_t rc = linear(s, hw, 1, s->head_pack, s->xn_f32, d, n_logit_cols, EPI_STORE, dst, ld);
     if (rc) return rc;
     LaunchCfg am = L;
-    if (split_head) {
+    prof_mark(s, PROF_OTHER);
+    if (split_head && (s->family_mask & (1u << PROF_OTHER))) {
       std::string err;
       if ((rc = comm_group_start(&err))) return fail(rc, err);
       for (int col = 0; col < n_logit_cols; ++col)
@@ -519,11 +512,9 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
       if ((rc = comm_group_end(&err))) return fail(rc, err);
       am.pdl = false;
     }
-    prof_mark(s, PROF_OTHER);
     RG_LAUNCH(s, launch_argmax(s->logits, c.vocab, c.vocab, n_logit_cols, s->d_ids, am));
     if (advance) RG_LAUNCH(s, launch_advance(s->d_ids, ctl->tokens, ctl->pos, s->d_history, &ctl->step, ncols, L));
   }
-  prof_mark(s, PROF_END);
   return RG_OK;
 }
 
@@ -1174,13 +1165,13 @@ int32_t rg_b200_decode_loop(rg_session *s, const int32_t *first, int32_t batch, 
 }
 
 int32_t rg_b200_decode_profile(rg_session *s, const int32_t *first, int32_t batch, int32_t steps, float out_ms[4],
-                               uint64_t out_marks[4]) {
+                               uint64_t out_launches[4]) {
   int32_t rc = check_live(s);
   if (rc) return rc;
   if (!first || !out_ms || batch < 1 || batch > s->max_batch || steps < 1) return fail(RG_INVALID_ARGUMENT, "bad arguments");
   for (int i = 0; i < batch; ++i) {
     if (first[i] < 0 || first[i] >= s->cfg.vocab) return fail(RG_TOKEN_OUT_OF_RANGE, "token in row " + std::to_string(i));
-    if (s->position[(size_t)i] + steps > s->ctx) return fail(RG_CONTEXT_EXHAUSTED, "row " + std::to_string(i));
+    if (s->position[(size_t)i] >= s->ctx) return fail(RG_CONTEXT_EXHAUSTED, "row " + std::to_string(i));
   }
   RG_CUDA(cudaSetDevice(s->opt.device));
   Ctrl *h = s->h_ctrl;
@@ -1192,69 +1183,52 @@ int32_t rg_b200_decode_profile(rg_session *s, const int32_t *first, int32_t batc
   }
   h->step = 0;
   if ((rc = upload_ctrl(s))) return rc;
-  // a step graph of its own: no programmatic overlap, so the events bound whole kernels
   const bool saved_pdl = s->use_pdl;
-  s->use_pdl = false;
+  s->use_pdl = false;  // serialized launches: every kernel runs alone
   s->launches_in_step = 0;
-  rc = forward(s, batch, batch, true);  // loads every kernel before capture
-  if (!rc) {
-    cudaError_t e = x_memcpy_async(s->d_ctrl, s->h_ctrl, sizeof(Ctrl), cudaMemcpyHostToDevice, s->stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(s->stream);
-    if (e != cudaSuccess) rc = fail(RG_CUDA_ERROR, cudaGetErrorString(e));
-  }
-  cudaGraphExec_t exec = nullptr;
-  if (!rc) {
-    s->prof = true;
-    s->prof_used = 0;
-    s->prof_kinds.clear();
+  rc = forward(s, batch, batch, false);  // loads every kernel before capture; nothing is committed
+  double total = 0.0;
+  for (int fam = 0; fam < 3 && !rc; ++fam) {
+    cudaGraphExec_t exec = nullptr;
+    s->family_mask = 1u << fam;
+    s->launches_in_step = 0;
     cudaError_t e = cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal);
     if (e == cudaSuccess) {
-      rc = forward(s, batch, batch, true);
+      rc = forward(s, batch, batch, false);
       cudaGraph_t graph = nullptr;
       e = cudaStreamEndCapture(s->stream, &graph);
       if (e == cudaSuccess && !rc) e = cudaGraphInstantiate(&exec, graph, 0);
       if (graph) cudaGraphDestroy(graph);
     }
-    s->prof = false;
+    s->family_mask = 0xffffffffu;
     if (!rc && e != cudaSuccess) rc = fail(RG_CUDA_ERROR, std::string("profile graph: ") + cudaGetErrorString(e));
-  }
-  s->use_pdl = saved_pdl;
-  if (rc) {
-    if (exec) cudaGraphExecDestroy(exec);
-    return rc;
-  }
-  double sums[4] = {0, 0, 0, 0};
-  uint64_t marks[4] = {0, 0, 0, 0};
-  for (int it = 0; it < steps && !rc; ++it) {
-    cudaError_t e = cudaGraphLaunch(exec, s->stream);
+    if (rc) {
+      if (exec) cudaGraphExecDestroy(exec);
+      break;
+    }
+    if (out_launches) out_launches[fam] = s->launches_in_step;
+    e = cudaGraphLaunch(exec, s->stream);  // warm replay
+    if (e == cudaSuccess) e = cudaEventRecord(s->ev0, s->stream);
+    for (int it = 0; it < steps && e == cudaSuccess; ++it) e = cudaGraphLaunch(exec, s->stream);
+    if (e == cudaSuccess) e = cudaEventRecord(s->ev1, s->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s->stream);
+    float ms = 0.0f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, s->ev0, s->ev1);
+    cudaGraphExecDestroy(exec);
     if (e != cudaSuccess) {
+      s->poisoned = true;
       rc = fail(RG_CUDA_ERROR, std::string("profile replay: ") + cudaGetErrorString(e));
       break;
     }
-    for (size_t i = 0; i + 1 < s->prof_used; ++i) {
-      float ms = 0.0f;
-      if (cudaEventElapsedTime(&ms, s->prof_events[i], s->prof_events[i + 1]) != cudaSuccess) {
-        rc = fail(RG_CUDA_ERROR, "event timing inside a graph is unavailable");
-        break;
-      }
-      sums[s->prof_kinds[i]] += ms;
-      sums[3] += ms;
-      if (it == 0) marks[s->prof_kinds[i]]++;
-    }
+    out_ms[fam] = ms / (float)steps;
+    total += out_ms[fam];
   }
-  cudaGraphExecDestroy(exec);
-  if (rc) {
-    s->poisoned = true;
-    return rc;
-  }
-  if ((rc = finish_step(s, 0, nullptr, 0))) return rc;
-  for (int k = 0; k < 4; ++k) {
-    out_ms[k] = (float)(sums[k] / steps);
-    if (out_marks) out_marks[k] = marks[k];
-  }
-  for (int i = 0; i < batch; ++i) s->position[(size_t)i] += steps;
-  return RG_OK;
+  s->family_mask = 0xffffffffu;
+  s->use_pdl = saved_pdl;
+  if (rc) return rc;
+  out_ms[3] = (float)total;
+  if (out_launches) out_launches[3] = out_launches[0] + out_launches[1] + out_launches[2];
+  return finish_step(s, 0, nullptr, 0);
 }
 
 int32_t rg_b200_report(const rg_session *s, rg_report *out) {

@@ -287,13 +287,13 @@ class LlamaCudaSession:
         return out, ms.value
 
     def decode_profile(self, first_tokens, steps: int) -> dict:
-        """CUDA-event time per step of each kernel family (serialized launches, no overlap)."""
+        """CUDA-event time per step of each kernel family replayed alone (serialized launches)."""
         t = np.ascontiguousarray(first_tokens, dtype=np.int32)
         ms = (C.c_float * 4)()
         marks = (C.c_uint64 * 4)()
         check(self._L.rg_b200_decode_profile(self._h, _i32(t), t.size, steps, ms, marks))
         keys = ("gemv", "attention", "other", "total")
-        return {k: {"ms_per_step": ms[i], "intervals_per_step": marks[i]} for i, k in enumerate(keys)}
+        return {k: {"ms_per_step": ms[i], "launches_per_step": marks[i]} for i, k in enumerate(keys)}
 
     def report(self) -> dict:
         r = Report()
