@@ -94,7 +94,8 @@ struct AttnArgs {
   void *out_pack = nullptr;  // packed [K = heads*hd], batch = cols
   float *out_f32 = nullptr;  // optional plain copy [cols, heads*hd]
 };
-constexpr int ATTN_SPAN = 64;  // context positions per CTA of the split kernel
+constexpr int ATTN_SPAN = 128;  // context positions per CTA of the split kernel
+bool attention_supported(int heads, int kv_heads, int hd);  // hd in {64,128}, heads/kv_heads in {1,2,4,8}
 size_t attn_scratch_floats(int cols, int heads, int hd, int ctx);
 cudaError_t launch_attention(const AttnArgs &a, const LaunchCfg &cfg);
 

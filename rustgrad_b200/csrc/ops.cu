@@ -166,101 +166,183 @@ __global__ void rope_append_kernel(const float *qkv, int heads, int kv_heads, in
 }
 
 // ------------------------------------------------------------------------------ attention
-// Scratch per (column, head, split): [m, l, out[hd]].
-constexpr int ATT_THREADS = 128;
-constexpr int MAX_GROUP = 8;
-constexpr int MAX_HD = 128;
-
-__device__ __forceinline__ float kv_load(const float *p) { return *p; }
-__device__ __forceinline__ float kv_load(const __half *p) { return __half2float(*p); }
-
+// Split-context decode attention.  One CTA per (context span, kv head, column) handles the G query
+// heads that share the kv head.  Scratch per (column, head, split): [m, l, out[hd]].
+//  phase 0: the span's K rows and V rows (each one contiguous range of the cache) are staged in
+//           shared memory by two bulk copies of the TMA engine, so no lane waits on DRAM in a loop.
+//  phase 1: scores.  16 lanes per position, each lane owns HD/16 dims of K (one 128-bit load for
+//           f16, hd 128) and the matching slice of every q head in registers; 4 shuffles per head.
+//  phase 2: per-head max / exp2 / sum over the span (one warp per head).
+//  phase 3: P.V.  A warp takes every 8th position, a lane owns HD/32 dims of V (coalesced row
+//           reads), G accumulators per dim; cross-warp sum in shared memory.
 // Softmax pieces follow src/ir/attention.rs:495-558: e = exp2((s - m) * log2(e)); the scores are
 // q.k / f32(sqrt(hd)) (attention.rs:1183-1188).  Query head h reads kv head h / (H/KV) (:1226-1240).
-template <typename KV>
+constexpr int ATT_THREADS = 256;
+constexpr int ATT_WARPS = ATT_THREADS / 32;
+constexpr int MAX_HD = 128;
+
+template <int N>
+__device__ __forceinline__ void kv_load_vec(const float *p, float (&v)[N]) {
+  if constexpr (N % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i) {
+      const float4 f = reinterpret_cast<const float4 *>(p)[i];
+      v[4 * i] = f.x, v[4 * i + 1] = f.y, v[4 * i + 2] = f.z, v[4 * i + 3] = f.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < N / 2; ++i) {
+      const float2 f = reinterpret_cast<const float2 *>(p)[i];
+      v[2 * i] = f.x, v[2 * i + 1] = f.y;
+    }
+  }
+}
+template <int N>
+__device__ __forceinline__ void kv_load_vec(const __half *p, float (&v)[N]) {
+  if constexpr (N == 8) {
+    const uint4 u = *reinterpret_cast<const uint4 *>(p);
+    const __half2 *h = reinterpret_cast<const __half2 *>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h[i]);
+      v[2 * i] = f.x, v[2 * i + 1] = f.y;
+    }
+  } else if constexpr (N == 4) {
+    const uint2 u = *reinterpret_cast<const uint2 *>(p);
+    const __half2 *h = reinterpret_cast<const __half2 *>(&u);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float2 f = __half22float2(h[i]);
+      v[2 * i] = f.x, v[2 * i + 1] = f.y;
+    }
+  } else {
+    static_assert(N == 2, "unsupported vector width");
+    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(p));
+    v[0] = f.x, v[1] = f.y;
+  }
+}
+
+template <typename KV, int G, int HD>
 __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(const float *q, const KV *k_cache, const KV *v_cache, int heads,
-                                                                 int kv_heads, int hd, int ctx, const int32_t *col_seq,
-                                                                 const int32_t *col_pos, float *scratch, int max_splits) {
+                                                                 int kv_heads, int ctx, const int32_t *col_seq,
+                                                                 const int32_t *col_pos, float *scratch, int max_splits,
+                                                                 int *status) {
   pdl_wait();
   pdl_launch_dependents();
+  constexpr int DPL = HD / 16;  // dims per lane, phase 1
+  constexpr int DV = HD / 32;   // dims per lane, phase 3
   const int split = blockIdx.x, kvh = blockIdx.y, c = blockIdx.z;
   const int pos = col_pos[c];
   const int p0 = split * ATTN_SPAN;
   if (p0 > pos) return;
   const int np = min(ATTN_SPAN, pos + 1 - p0);
-  const int group = heads / kv_heads;
   const int seq = col_seq[c];
-  __shared__ float qs[MAX_GROUP][MAX_HD];
-  __shared__ float sc[MAX_GROUP][ATTN_SPAN];
-  __shared__ float ml[MAX_GROUP][2];
-  const int tid = threadIdx.x;
-  for (int i = tid; i < group * hd; i += ATT_THREADS) {
-    const int gq = i / hd, j = i - gq * hd;
-    qs[gq][j] = q[((size_t)c * heads + (size_t)kvh * group + gq) * hd + j];
+  __shared__ __align__(16) float sc[ATTN_SPAN][G];
+  __shared__ float ml[G][2];
+  __shared__ __align__(16) float red[ATT_WARPS][G][HD];
+  __shared__ __align__(8) uint64_t bars[2];
+  __shared__ int dead_flag;
+  extern __shared__ __align__(128) uint8_t att_smem[];
+  KV *ks = reinterpret_cast<KV *>(att_smem);
+  KV *vs = ks + (size_t)ATTN_SPAN * HD;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    dead_flag = 0;
+    mbar_fence_init();
   }
   __syncthreads();
-  const KV *kbase = k_cache + (((size_t)seq * kv_heads + kvh) * ctx + p0) * hd;
-  const KV *vbase = v_cache + (((size_t)seq * kv_heads + kvh) * ctx + p0) * hd;
-  const float inv_scale = (float)(1.0 / (1.0 / sqrt((double)hd)));
+  if (tid == 0) {
+    const uint32_t bytes = (uint32_t)((size_t)np * HD * sizeof(KV));
+    mbar_expect_tx(&bars[0], bytes);
+    bulk_g2s(ks, k_cache + (((size_t)seq * kv_heads + kvh) * ctx + p0) * HD, bytes, &bars[0]);
+    mbar_expect_tx(&bars[1], bytes);
+    bulk_g2s(vs, v_cache + (((size_t)seq * kv_heads + kvh) * ctx + p0) * HD, bytes, &bars[1]);
+  }
+  const KV *kbase = ks, *vbase = vs;
+  const float inv_scale = (float)(1.0 / (1.0 / sqrt((double)HD)));
   {
-    // two threads per position, each half of the head dimension
-    const int p = tid >> 1, part = tid & 1;
-    const int hh = hd >> 1;
-    float dots[MAX_GROUP];
+    const int sub = lane & 15, hi = lane >> 4;
+    float qr[G][DPL];
 #pragma unroll
-    for (int gq = 0; gq < MAX_GROUP; ++gq) dots[gq] = 0.0f;
-    if (p < np) {
-      const KV *kr = kbase + (size_t)p * hd + part * hh;
-      for (int j = 0; j < hh; ++j) {
-        const float kv = kv_load(kr + j);
+    for (int g = 0; g < G; ++g)
 #pragma unroll
-        for (int gq = 0; gq < MAX_GROUP; ++gq)
-          if (gq < group) dots[gq] = fmaf(qs[gq][part * hh + j], kv, dots[gq]);
+      for (int i = 0; i < DPL; ++i) qr[g][i] = q[((size_t)c * heads + (size_t)kvh * G + g) * HD + sub * DPL + i];
+    mbar_wait_bounded(&bars[0], 0, &dead_flag, status);
+    for (int base = 0; base < np; base += 2 * ATT_WARPS) {
+      const int p = base + warp * 2 + hi;
+      float kv[DPL];
+      if (p < np) {
+        kv_load_vec<DPL>(kbase + (size_t)p * HD + sub * DPL, kv);
+      } else {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) kv[i] = 0.0f;
       }
-    }
 #pragma unroll
-    for (int gq = 0; gq < MAX_GROUP; ++gq) {
-      const float other = __shfl_xor_sync(0xffffffffu, dots[gq], 1);
-      if (gq < group && part == 0 && p < ATTN_SPAN) sc[gq][p] = (p < np) ? __fdiv_rn(dots[gq] + other, inv_scale) : -INFINITY;
+      for (int g = 0; g < G; ++g) {
+        float dot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) dot = fmaf(qr[g][i], kv[i], dot);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (sub == 0 && p < np) sc[p][g] = __fdiv_rn(dot, inv_scale);
+      }
     }
   }
   __syncthreads();
+  if (warp < G) {
+    const int g = warp;
+    float m = -INFINITY;
+    for (int p = lane; p < np; p += 32) m = fmaxf(m, sc[p][g]);
+    m = warp_max(m);
+    float l = 0.0f;
+    for (int p = lane; p < np; p += 32) {
+      const float e = exp2f(__fmul_rn(__fsub_rn(sc[p][g], m), 1.44269504088896340736f));
+      sc[p][g] = e;
+      l += e;
+    }
+    l = warp_sum(l);
+    if (lane == 0) {
+      ml[g][0] = m;
+      ml[g][1] = l;
+    }
+  }
+  __syncthreads();
+  mbar_wait_bounded(&bars[1], 0, &dead_flag, status);
   {
-    const int warp = tid >> 5, lane = tid & 31;
-    for (int gq = warp; gq < group; gq += ATT_THREADS / 32) {
-      const float s0 = sc[gq][lane], s1 = sc[gq][lane + 32];
-      const float m = warp_max(fmaxf(s0, s1));
-      const float e0 = (lane < np) ? exp2f(__fmul_rn(__fsub_rn(s0, m), 1.44269504088896340736f)) : 0.0f;
-      const float e1 = (lane + 32 < np) ? exp2f(__fmul_rn(__fsub_rn(s1, m), 1.44269504088896340736f)) : 0.0f;
-      sc[gq][lane] = e0;
-      sc[gq][lane + 32] = e1;
-      const float l = warp_sum(e0 + e1);
-      if (lane == 0) {
-        ml[gq][0] = m;
-        ml[gq][1] = l;
+    float acc[G][DV];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int i = 0; i < DV; ++i) acc[g][i] = 0.0f;
+    for (int p = warp; p < np; p += ATT_WARPS) {
+      float v[DV];
+      kv_load_vec<DV>(vbase + (size_t)p * HD + lane * DV, v);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float pr = sc[p][g];
+#pragma unroll
+        for (int i = 0; i < DV; ++i) acc[g][i] = fmaf(pr, v[i], acc[g][i]);
       }
     }
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int i = 0; i < DV; ++i) red[warp][g][lane * DV + i] = acc[g][i];
   }
   __syncthreads();
-  if (tid < hd) {
-    float out[MAX_GROUP];
+  for (int idx = tid; idx < G * HD; idx += ATT_THREADS) {
+    const int g = idx / HD, d = idx - g * HD;
+    float v = 0.0f;
 #pragma unroll
-    for (int gq = 0; gq < MAX_GROUP; ++gq) out[gq] = 0.0f;
-    for (int p = 0; p < np; ++p) {
-      const float v = kv_load(vbase + (size_t)p * hd + tid);
-#pragma unroll
-      for (int gq = 0; gq < MAX_GROUP; ++gq)
-        if (gq < group) out[gq] = fmaf(sc[gq][p], v, out[gq]);
+    for (int w = 0; w < ATT_WARPS; ++w) v += red[w][g][d];
+    float *dst = scratch + (((size_t)c * heads + (size_t)kvh * G + g) * max_splits + split) * (HD + 2);
+    dst[2 + d] = v;
+    if (d == 0) {
+      dst[0] = ml[g][0];
+      dst[1] = ml[g][1];
     }
-#pragma unroll
-    for (int gq = 0; gq < MAX_GROUP; ++gq)
-      if (gq < group) {
-        float *dst = scratch + (((size_t)c * heads + (size_t)kvh * group + gq) * max_splits + split) * (hd + 2);
-        if (tid == 0) {
-          dst[0] = ml[gq][0];
-          dst[1] = ml[gq][1];
-        }
-        dst[2 + tid] = out[gq];
-      }
   }
 }
 
@@ -545,18 +627,43 @@ size_t attn_scratch_floats(int cols, int heads, int hd, int ctx) {
   const int splits = (ctx + ATTN_SPAN - 1) / ATTN_SPAN;
   return (size_t)cols * heads * splits * (hd + 2);
 }
+template <typename KV, int G, int HD>
+static cudaError_t launch_attn_t(const AttnArgs &a, const LaunchCfg &cfg, int splits) {
+  constexpr size_t smem = 2 * (size_t)ATTN_SPAN * HD * sizeof(KV);
+  auto kernel = attn_split_kernel<KV, G, HD>;
+  static bool attr_done = false;  // per instantiation
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr_done = true;
+  }
+  return launch(kernel, dim3(splits, a.kv_heads, a.cols), dim3(ATT_THREADS), smem, cfg, a.q, static_cast<const KV *>(a.k_cache),
+                static_cast<const KV *>(a.v_cache), a.heads, a.kv_heads, a.ctx, a.col_seq, a.col_pos, a.scratch, splits,
+                cfg.status);
+}
+template <typename KV, int HD>
+static cudaError_t launch_attn_g(const AttnArgs &a, const LaunchCfg &cfg, int splits) {
+  switch (a.heads / a.kv_heads) {
+    case 1: return launch_attn_t<KV, 1, HD>(a, cfg, splits);
+    case 2: return launch_attn_t<KV, 2, HD>(a, cfg, splits);
+    case 4: return launch_attn_t<KV, 4, HD>(a, cfg, splits);
+    case 8: return launch_attn_t<KV, 8, HD>(a, cfg, splits);
+    default: return cudaErrorInvalidValue;
+  }
+}
+bool attention_supported(int heads, int kv_heads, int hd) {
+  if (kv_heads <= 0 || heads % kv_heads) return false;
+  const int g = heads / kv_heads;
+  return (hd == 64 || hd == 128) && (g == 1 || g == 2 || g == 4 || g == 8);
+}
 cudaError_t launch_attention(const AttnArgs &a, const LaunchCfg &cfg) {
-  if (a.hd > MAX_HD || (a.hd & 1) || a.heads % a.kv_heads || a.heads / a.kv_heads > MAX_GROUP) return cudaErrorInvalidValue;
+  if (!attention_supported(a.heads, a.kv_heads, a.hd)) return cudaErrorInvalidValue;
   const int splits = (a.ctx + ATTN_SPAN - 1) / ATTN_SPAN;
   cudaError_t e;
   if (a.kv_f32)
-    e = launch(attn_split_kernel<float>, dim3(splits, a.kv_heads, a.cols), dim3(ATT_THREADS), 0, cfg, a.q,
-               static_cast<const float *>(a.k_cache), static_cast<const float *>(a.v_cache), a.heads, a.kv_heads, a.hd, a.ctx,
-               a.col_seq, a.col_pos, a.scratch, splits);
+    e = a.hd == 128 ? launch_attn_g<float, 128>(a, cfg, splits) : launch_attn_g<float, 64>(a, cfg, splits);
   else
-    e = launch(attn_split_kernel<__half>, dim3(splits, a.kv_heads, a.cols), dim3(ATT_THREADS), 0, cfg, a.q,
-               static_cast<const __half *>(a.k_cache), static_cast<const __half *>(a.v_cache), a.heads, a.kv_heads, a.hd, a.ctx,
-               a.col_seq, a.col_pos, a.scratch, splits);
+    e = a.hd == 128 ? launch_attn_g<__half, 128>(a, cfg, splits) : launch_attn_g<__half, 64>(a, cfg, splits);
   if (e != cudaSuccess) return e;
   return launch(attn_combine_kernel, dim3(a.heads, a.cols), dim3(MAX_HD), 0, cfg, (const float *)a.scratch, a.heads, a.hd,
                 a.col_pos, splits, a.cols, static_cast<__half *>(a.out_pack), a.out_f32);

@@ -4,13 +4,15 @@
 // (src/models/transformer/layer.rs:445-448).
 //
 // Design (HBM-bound; nothing here is reshaped to chase tensor-core flops):
-//  * One persistent CTA per SM owns a contiguous slice of output rows; rows are dealt out evenly
-//    so the last wave is not short.
+//  * One persistent CTA per SM owns a contiguous slice of output rows (dealt out in 8-row units
+//    so the last wave is not short).
 //  * A producer warp streams [32 rows x KC blocks] of raw block bytes per stage into shared
-//    memory with the TMA engine's untiled bulk copy (row pieces are contiguous, 16-byte aligned
-//    because KC is a multiple of 8 blocks), 3-4 stages deep, >= 140 KB in flight per SM.  The
-//    matching slice of the packed activations rides in the same stage.
-//  * Eight consumer warps each take a K slice of the stage for all 32 rows.  A lane reads 4-byte
+//    memory with tiled 2-D TMA (`cp.async.bulk.tensor.2d`, one request per 8 rows; the weight
+//    matrix is described as [rows][row bytes / 8] 64-bit elements), 3-6 stages deep.  KC is chosen
+//    so that the dense box pitch is 12, 20 or 28 banks (mod 32): the eight rows a warp reads at
+//    the same K offset fall in distinct banks without padding.  The matching slice of the packed
+//    activations rides in the same stage as one untiled bulk copy.
+//  * Consumer warps each take block pairs of the stage for all 32 rows.  A lane reads 4-byte
 //    words of quant bytes (the 2-byte scale in front of every block makes half of them
 //    unaligned: two aligned words + funnel shift), expands nibbles / int8 to exact f16 integers
 //    with one logic op + one half2 subtract per two weights, and feeds them as the A operand of
@@ -24,6 +26,9 @@
 //    GEMV's packed activations.
 //  * Programmatic dependent launch: weight prefetch of the first stages is issued before the
 //    grid dependency wait, so it overlaps the tail of the previous kernel.
+//  * Every mbarrier wait is bounded; on expiry the kernel records a status and finishes.
+#include <cuda.h>
+
 #include "../../include/rg_b200.h"
 #include "kernels.h"
 #include "rg_device.cuh"
@@ -31,21 +36,23 @@
 namespace rg {
 namespace {
 
-constexpr int R = 32;   // weight rows per stage: two m16 tiles
-constexpr int CW = 8;   // consumer warps
-constexpr int MAX_STAGES = 4;
+constexpr int R = 32;     // weight rows per stage: two m16 tiles
+constexpr int BOXR = 8;   // rows per TMA box: BOXR * pitch is a multiple of 128 bytes (TMA destination alignment)
+constexpr int CW = 14;    // consumer warps
+constexpr int MAX_STAGES = 6;
 constexpr int THREADS = (CW + 1) * 32;
 constexpr int SMEM_LIMIT = 227 * 1024;
 
 template <int QT, int NT>
 struct Geo {
   static constexpr bool Q4 = (QT == RG_TYPE_Q4_0);
-  static constexpr int BB = Q4 ? 18 : 34;          // bytes per block
-  static constexpr int PAIR_WORDS = Q4 ? 9 : 17;   // 32-bit words per two blocks
-  static constexpr int KC = (Q4 ? 64 : 32) / NT;   // blocks per stage
-  static constexpr int RS = KC * BB + 16;          // padded row stride: bank = 4*row + word
-  static constexpr int PPW = KC / 2 / CW;          // block pairs per consumer warp per stage
-  static_assert(PPW >= 1, "stage too small for eight consumer warps");
+  static constexpr int BB = Q4 ? 18 : 34;         // bytes per block
+  static constexpr int PAIR_WORDS = Q4 ? 9 : 17;  // 32-bit words per two blocks
+  // blocks per stage; pitch = KC * BB bytes: 1008 (28 banks), 432 (12), 1360 (20), 816 (12)
+  static constexpr int KC = NT == 1 ? (Q4 ? 56 : 40) : 24;
+  static constexpr int RS = KC * BB;  // dense box pitch in shared memory
+  static_assert(RS % 16 == 0 && (BOXR * RS) % 128 == 0 && RS / 8 <= 256, "box inner extent must be 16-byte granular and <= 256 elements");
+  static_assert(((RS / 4) % 32) % 4 == 0 && ((RS / 4) % 32) % 8 != 0, "pitch must spread eight rows over distinct banks");
 };
 
 struct KParams {
@@ -65,12 +72,17 @@ struct KParams {
   int *status;
 };
 
+// Eight nibbles of one 32-bit word -> four half2 registers of exact integers (n - 8).
+// Low nibbles: (1024 | n) - 1032.  High nibbles stay in place: (1024 | 16 n) * (1/16) - 72, one
+// half2 FMA, so only the odd bytes need a shift.  5 logic ops + 4 half2 ops per 8 weights.
 __device__ __forceinline__ void unpack_q4(uint32_t q, uint32_t (&p)[4]) {
-  const uint32_t M = 0x000F000Fu, E = 0x64006400u, OFF = 0x64086408u;  // 1024 | n, minus 1032
-  p[0] = hsub2_u32((q & M) | E, OFF);
-  p[1] = hsub2_u32(((q >> 8) & M) | E, OFF);
-  p[2] = hsub2_u32(((q >> 4) & M) | E, OFF);
-  p[3] = hsub2_u32(((q >> 12) & M) | E, OFF);
+  const uint32_t MLO = 0x000F000Fu, MHI = 0x00F000F0u, E = 0x64006400u;
+  const uint32_t SUB = 0x64086408u, SIXTEENTH = 0x2C002C00u, NEG72 = 0xD480D480u;
+  const uint32_t qs = q >> 8;
+  p[0] = hsub2_u32((q & MLO) | E, SUB);
+  p[1] = hsub2_u32((qs & MLO) | E, SUB);
+  p[2] = hfma2_u32((q & MHI) | E, SIXTEENTH, NEG72);
+  p[3] = hfma2_u32((qs & MHI) | E, SIXTEENTH, NEG72);
 }
 __device__ __forceinline__ void unpack_q8(uint32_t q, uint32_t &p0, uint32_t &p1) {
   const uint32_t OFF = 0x64806480u;  // 1024 + 128
@@ -79,8 +91,62 @@ __device__ __forceinline__ void unpack_q8(uint32_t q, uint32_t &p0, uint32_t &p1
   p1 = hsub2_u32(prmt(u, 0x64646464u, 0x4341u), OFF);
 }
 
+// Explicit shared-memory loads with immediate offsets: one address register per block pair.
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1+%2];" : "=h"(v) : "r"(addr), "n"(OFF));
+  return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+// Row slot rs of a stage is shared row (rs >> 1) * 16 + (rs & 1) * 8 + g; `a` already points at
+// (row g, word t) of the block pair.
+template <int RS, int RSLOT>
+__device__ __forceinline__ void lds_q4_slot(uint32_t a, uint32_t (&w)[6]) {
+  constexpr int R0 = ((RSLOT >> 1) * 16 + (RSLOT & 1) * 8) * RS;
+  w[0] = lds32<R0>(a);
+  w[1] = lds32<R0 + 4>(a);
+  w[2] = lds32<R0 + 20>(a);
+}
+template <int RS, int RSLOT>
+__device__ __forceinline__ void lds_q8_slot(uint32_t a, uint32_t (&w)[6]) {
+  constexpr int R0 = ((RSLOT >> 1) * 16 + (RSLOT & 1) * 8) * RS;
+  w[0] = lds32<R0>(a);
+  w[1] = lds32<R0 + 4>(a);
+  w[2] = lds32<R0 + 16>(a);
+  w[3] = lds32<R0 + 20>(a);
+  w[4] = lds32<R0 + 36>(a);
+  w[5] = lds32<R0 + 52>(a);
+}
+template <int RS, int BB, int RSLOT>
+__device__ __forceinline__ void lds_scale_slot(uint32_t a, uint32_t (&sc)[2]) {
+  constexpr int R0 = ((RSLOT >> 1) * 16 + (RSLOT & 1) * 8) * RS;
+  sc[0] = lds16<R0>(a);
+  sc[1] = lds16<R0 + BB>(a);
+}
+
+__device__ __forceinline__ void tma_box_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
 template <int QT, int NT, int EPI>
-__global__ void __launch_bounds__(THREADS, 1) qgemv_kernel(const KParams P) {
+__global__ void __launch_bounds__(THREADS, 1)
+    qgemv_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
+                 const __grid_constant__ CUtensorMap map2, const KParams P) {
   using G = Geo<QT, NT>;
   constexpr bool PAIR = (EPI == EPI_SWIGLU);
   constexpr int GROUP_ROWS = PAIR ? 16 : 32;  // virtual rows per stage
@@ -90,9 +156,11 @@ __global__ void __launch_bounds__(THREADS, 1) qgemv_kernel(const KParams P) {
   volatile int *dead = reinterpret_cast<volatile int *>(empty + MAX_STAGES);
   float *red = reinterpret_cast<float *>(smem + 128);
   constexpr int RED_BYTES = CW * R * 4 * NT * 4;
+  static_assert(RED_BYTES % 128 == 0, "stage buffers must stay 128-byte aligned");
   uint8_t *stage0 = smem + 128 + RED_BYTES;
+  constexpr int W_STAGE_BYTES = R * G::RS;
   const int x_stage_bytes = G::KC * P.S * 64;
-  const int stage_bytes = R * G::RS + x_stage_bytes;
+  const int stage_bytes = (W_STAGE_BYTES + x_stage_bytes + 127) & ~127;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r_begin = blockIdx.x * P.rows_per_cta;
@@ -115,47 +183,60 @@ __global__ void __launch_bounds__(THREADS, 1) qgemv_kernel(const KParams P) {
 
   if (warp == CW) {
     // ------------------------------------------------------------------ producer
-    const size_t row_bytes = (size_t)P.kb * G::BB;
-    auto issue = [&](int u, bool do_w, bool do_x) {
-      const int stage = u % stages;
-      const int grp = u / n_chunks, c = u - grp * n_chunks;
+    // lane i < 4 moves box i: shared rows [8i, 8i+8) of the stage
+    auto issue = [&](int stage, int grp, int c, bool do_w, bool do_x) {
       const int nb = min(G::KC, P.kb - c * G::KC);
       const int vr0 = r_begin + grp * GROUP_ROWS;
-      const uint32_t wbytes = (uint32_t)(nb * G::BB), xbytes = (uint32_t)(nb * P.S * 64);
-      // shared row `lane` <- which weight row?
-      const uint8_t *src = nullptr;
-      int vrow = PAIR ? vr0 + (lane & 15) : vr0 + lane;
-      if (vrow < r_end) {
-        if (PAIR) {
-          src = P.w[lane >> 4] + (size_t)vrow * row_bytes;
-        } else {
-          int local = vrow, seg = 0;
-          while (seg + 1 < P.nseg && local >= P.seg_rows[seg]) {
-            local -= P.seg_rows[seg];
-            ++seg;
-          }
-          src = P.w[seg] + (size_t)local * row_bytes;
-        }
-        src += (size_t)c * G::KC * G::BB;
-      }
+      const uint32_t xbytes = (uint32_t)(nb * P.S * 64);
       uint8_t *sw = stage0 + (size_t)stage * stage_bytes;
       if (do_w) {
-        const int nvalid = __popc(__ballot_sync(0xffffffffu, src != nullptr));
-        if (lane == 0) mbar_expect_tx(&full[stage], (uint32_t)nvalid * wbytes + xbytes);
+        if (lane == 0) mbar_expect_tx(&full[stage], (uint32_t)W_STAGE_BYTES + xbytes);
         __syncwarp();
-        if (src) bulk_g2s(sw + lane * G::RS, src, wbytes, &full[stage]);
+        if (lane < R / BOXR) {
+          const CUtensorMap *map = &map0;
+          int row;
+          if (PAIR) {
+            map = (lane < 2) ? &map0 : &map1;
+            row = vr0 + (lane & 1) * BOXR;
+          } else {
+            row = vr0 + lane * BOXR;
+            if (P.nseg > 1 && row >= P.seg_rows[0]) {
+              row -= P.seg_rows[0];
+              map = &map1;
+              if (P.nseg > 2 && row >= P.seg_rows[1]) {
+                row -= P.seg_rows[1];
+                map = &map2;
+              }
+            }
+          }
+          // x coordinate in 8-byte elements; rows or bytes outside the tensor arrive as zeros
+          tma_box_2d(sw + lane * BOXR * G::RS, map, c * (G::RS / 8), row, &full[stage]);
+        }
       }
       if (do_x && lane == 0)
-        bulk_g2s(sw + R * G::RS, P.xpack + (size_t)c * G::KC * P.S * 64, xbytes, &full[stage]);
+        bulk_g2s(sw + W_STAGE_BYTES, P.xpack + (size_t)c * G::KC * P.S * 64, xbytes, &full[stage]);
     };
     const int pro = min(units, stages);
-    for (int u = 0; u < pro; ++u) issue(u, true, false);  // weights do not depend on earlier kernels
+    int grp = 0, c = 0;
+    auto next = [&]() {
+      if (++c == n_chunks) {
+        c = 0;
+        ++grp;
+      }
+    };
+    for (int u = 0; u < pro; ++u, next()) issue(u, grp, c, true, false);  // weights do not depend on earlier kernels
     pdl_wait();
-    for (int u = 0; u < pro; ++u) issue(u, false, true);
-    for (int u = pro; u < units; ++u) {
-      const int stage = u % stages, round = u / stages;
-      mbar_wait_bounded(&empty[stage], (uint32_t)((round - 1) & 1), dead, P.status);
-      issue(u, true, true);
+    grp = 0, c = 0;
+    for (int u = 0; u < pro; ++u, next()) issue(u, grp, c, false, true);
+    int stage = 0;
+    uint32_t phase = 0;  // parity of the consumers' release being waited for
+    for (int u = pro; u < units; ++u, next()) {
+      mbar_wait_bounded(&empty[stage], phase, dead, P.status);
+      issue(stage, grp, c, true, true);
+      if (++stage == stages) {
+        stage = 0;
+        phase ^= 1u;
+      }
     }
     return;
   }
@@ -171,61 +252,78 @@ __global__ void __launch_bounds__(THREADS, 1) qgemv_kernel(const KParams P) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[mt][j][i] = 0.0f;
 
+  // loop state kept incrementally: no integer division in the steady state
+  int stage = 0, c = 0, grp = 0;
+  uint32_t phase = 0;
+  const uint32_t smem_stage0 = smem_u32(stage0);
+  const uint32_t lane_w_off = (uint32_t)(g * G::RS + t * 4);  // (row g, word t) of pair 0
+  const uint32_t lane_s_off = (uint32_t)(g * G::RS);          // scale of (row g, pair 0)
   for (int u = 0; u < units; ++u) {
-    const int stage = u % stages;
-    const int grp = u / n_chunks, c = u - grp * n_chunks;
     const int nb = min(G::KC, P.kb - c * G::KC);
-    mbar_wait_bounded(&full[stage], (uint32_t)((u / stages) & 1), dead, P.status);
-    const uint8_t *sw = stage0 + (size_t)stage * stage_bytes;
-    const uint4 *sx = reinterpret_cast<const uint4 *>(sw + R * G::RS);
+    mbar_wait_bounded(&full[stage], phase, dead, P.status);
+    const uint32_t sw = smem_stage0 + (uint32_t)stage * (uint32_t)stage_bytes;
+    const uint32_t sx = sw + W_STAGE_BYTES;
 
-#pragma unroll
-    for (int i = 0; i < G::PPW; ++i) {
-      const int p = warp * G::PPW + i;
-      if (2 * p >= nb) break;
+    uint32_t aw = sw + lane_w_off + (uint32_t)warp * (2 * G::BB);
+    uint32_t as = sw + lane_s_off + (uint32_t)warp * (2 * G::BB);
+    for (int p = warp; 2 * p < nb; p += CW, aw += CW * 2 * G::BB, as += CW * 2 * G::BB) {
+      // ---- all shared loads of this block pair first (explicit ld.shared, immediate offsets)
+      uint32_t wq[4][6];
+      uint32_t sc[4][2];
+      if constexpr (G::Q4) {
+        lds_q4_slot<G::RS, 0>(aw, wq[0]);
+        lds_q4_slot<G::RS, 1>(aw, wq[1]);
+        lds_q4_slot<G::RS, 2>(aw, wq[2]);
+        lds_q4_slot<G::RS, 3>(aw, wq[3]);
+      } else {
+        lds_q8_slot<G::RS, 0>(aw, wq[0]);
+        lds_q8_slot<G::RS, 1>(aw, wq[1]);
+        lds_q8_slot<G::RS, 2>(aw, wq[2]);
+        lds_q8_slot<G::RS, 3>(aw, wq[3]);
+      }
+      lds_scale_slot<G::RS, G::BB, 0>(as, sc[0]);
+      lds_scale_slot<G::RS, G::BB, 1>(as, sc[1]);
+      lds_scale_slot<G::RS, G::BB, 2>(as, sc[2]);
+      lds_scale_slot<G::RS, G::BB, 3>(as, sc[3]);
       uint4 xe[NT], xo[NT];
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
         const int slot = 8 * j + g;
         if (slot < P.S) {
-          xe[j] = sx[((2 * p) * P.S + slot) * 4 + t];
-          xo[j] = sx[((2 * p + 1) * P.S + slot) * 4 + t];
+          const uint32_t ax = sx + (uint32_t)((((2 * p) * P.S + slot) * 4 + t) * 16);
+          xe[j] = lds128(ax);
+          xo[j] = lds128(ax + (uint32_t)(P.S * 64));
         } else {
           xe[j] = make_uint4(0, 0, 0, 0);
           xo[j] = make_uint4(0, 0, 0, 0);
         }
       }
+      // ---- expand and multiply
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
         uint32_t ae[2][4], ao[2][4];
         float de[2], dd[2];
 #pragma unroll
         for (int hs = 0; hs < 2; ++hs) {
-          const int row = mt * 16 + hs * 8 + g;
-          const uint32_t *wr = reinterpret_cast<const uint32_t *>(sw + row * G::RS) + p * G::PAIR_WORDS;
+          const int rs = mt * 2 + hs;
+          de[hs] = half_bits_to_float(sc[rs][0]);
+          dd[hs] = half_bits_to_float(sc[rs][1]);
           if (G::Q4) {
-            const uint32_t w0 = wr[t], w1 = wr[t + 1], w2 = wr[5 + t];
-            de[hs] = half_bits_to_float(__shfl_sync(0xffffffffu, w0, lane & ~3) & 0xffffu);
-            dd[hs] = half_bits_to_float(__shfl_sync(0xffffffffu, w1, lane | 3) >> 16);
-            unpack_q4(__funnelshift_r(w0, w1, 16), ae[hs]);
-            unpack_q4(w2, ao[hs]);
+            unpack_q4(__funnelshift_r(wq[rs][0], wq[rs][1], 16), ae[hs]);
+            unpack_q4(wq[rs][2], ao[hs]);
           } else {
-            const uint32_t w0 = wr[t], w1 = wr[t + 1], w2 = wr[4 + t], w3 = wr[5 + t];
-            const uint32_t w4 = wr[9 + t], w5 = wr[13 + t];
-            de[hs] = half_bits_to_float(__shfl_sync(0xffffffffu, w0, lane & ~3) & 0xffffu);
-            dd[hs] = half_bits_to_float(__shfl_sync(0xffffffffu, w3, lane | 3) >> 16);
-            unpack_q8(__funnelshift_r(w0, w1, 16), ae[hs][0], ae[hs][1]);
-            unpack_q8(__funnelshift_r(w2, w3, 16), ae[hs][2], ae[hs][3]);
-            unpack_q8(w4, ao[hs][0], ao[hs][1]);
-            unpack_q8(w5, ao[hs][2], ao[hs][3]);
+            unpack_q8(__funnelshift_r(wq[rs][0], wq[rs][1], 16), ae[hs][0], ae[hs][1]);
+            unpack_q8(__funnelshift_r(wq[rs][2], wq[rs][3], 16), ae[hs][2], ae[hs][3]);
+            unpack_q8(wq[rs][4], ao[hs][0], ao[hs][1]);
+            unpack_q8(wq[rs][5], ao[hs][2], ao[hs][3]);
           }
         }
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
-          float ce[4] = {0.f, 0.f, 0.f, 0.f}, co[4] = {0.f, 0.f, 0.f, 0.f};
-          mma_16816(ce, ae[0][0], ae[1][0], ae[0][1], ae[1][1], xe[j].x, xe[j].y);
+          float ce[4], co[4];
+          mma_16816_zero(ce, ae[0][0], ae[1][0], ae[0][1], ae[1][1], xe[j].x, xe[j].y);
           mma_16816(ce, ae[0][2], ae[1][2], ae[0][3], ae[1][3], xe[j].z, xe[j].w);
-          mma_16816(co, ao[0][0], ao[1][0], ao[0][1], ao[1][1], xo[j].x, xo[j].y);
+          mma_16816_zero(co, ao[0][0], ao[1][0], ao[0][1], ao[1][1], xo[j].x, xo[j].y);
           mma_16816(co, ao[0][2], ao[1][2], ao[0][3], ao[1][3], xo[j].z, xo[j].w);
           acc[mt][j][0] = fmaf(de[0], ce[0], acc[mt][j][0]);
           acc[mt][j][1] = fmaf(de[0], ce[1], acc[mt][j][1]);
@@ -279,7 +377,46 @@ __global__ void __launch_bounds__(THREADS, 1) qgemv_kernel(const KParams P) {
       }
       asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
     }
+    if (++c == n_chunks) {
+      c = 0;
+      ++grp;
+    }
+    if (++stage == stages) {
+      stage = 0;
+      phase ^= 1u;
+    }
   }
+}
+
+// cuTensorMapEncodeTiled resolved through the runtime, so the library needs no link to libcuda.
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+// Describes packed weights [rows][row_bytes] as a 2-D tensor of 8-byte elements with a
+// [BOXR rows][pitch bytes] box.
+cudaError_t make_map(CUtensorMap *map, const uint8_t *w, int rows, size_t row_bytes, int pitch) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return cudaErrorNotSupported;
+  const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 8), (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)(pitch / 8), (cuuint32_t)BOXR};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t *>(w), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
 template <int QT, int NT, int EPI>
@@ -306,16 +443,25 @@ cudaError_t launch_t(const GemvArgs &a, const LaunchCfg &cfg) {
   P.ypack = static_cast<__half *>(a.ypack);
   P.status = cfg.status;
   const int sms = cfg.sm_count > 0 ? cfg.sm_count : 148;
-  P.rows_per_cta = (P.n_rows + sms - 1) / sms;
-  if (P.rows_per_cta < 1) P.rows_per_cta = 1;
+  // rows are dealt out in box-height units so that no TMA box straddles two CTAs or two segments
+  const int units = (P.n_rows + BOXR - 1) / BOXR;
+  P.rows_per_cta = ((units + sms - 1) / sms) * BOXR;
   const int grid = (P.n_rows + P.rows_per_cta - 1) / P.rows_per_cta;
-  const int stage_bytes = R * G::RS + G::KC * P.S * 64;
+  const int stage_bytes = (R * G::RS + G::KC * P.S * 64 + 127) & ~127;
   const int fixed = 128 + CW * R * 4 * NT * 4;
   int stages = (SMEM_LIMIT - fixed) / stage_bytes;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages < 2) return cudaErrorInvalidConfiguration;
   P.stages = stages;
   const size_t smem = (size_t)fixed + (size_t)stages * stage_bytes;
+
+  alignas(64) CUtensorMap maps[3];
+  const size_t row_bytes = (size_t)P.kb * G::BB;
+  for (int i = 0; i < 3; ++i) {
+    const int src = i < a.nseg ? i : 0;
+    cudaError_t e = make_map(&maps[i], a.w[src], a.seg_rows[src], row_bytes, G::RS);
+    if (e != cudaSuccess) return e;
+  }
 
   auto kernel = qgemv_kernel<QT, NT, EPI>;
   static bool attr_done = false;  // per instantiation
@@ -334,7 +480,7 @@ cudaError_t launch_t(const GemvArgs &a, const LaunchCfg &cfg) {
   at[0].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = at;
   lc.numAttrs = cfg.pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&lc, kernel, P);
+  return cudaLaunchKernelEx(&lc, kernel, maps[0], maps[1], maps[2], P);
 }
 
 template <int QT, int NT>
@@ -354,6 +500,10 @@ size_t xpack_bytes(int k, int batch) { return (size_t)((k + 31) / 32 * 32) * (si
 cudaError_t launch_qgemv(const GemvArgs &a, const LaunchCfg &cfg) {
   if (a.k <= 0 || a.k % 256 || a.batch < 1 || a.batch > 8 || a.nseg < 1 || a.nseg > 3) return cudaErrorInvalidValue;
   if (a.epi == EPI_SWIGLU && (a.nseg != 2 || a.seg_rows[0] != a.seg_rows[1])) return cudaErrorInvalidValue;
+  for (int i = 0; i + 1 < a.nseg; ++i)
+    if (a.epi != EPI_SWIGLU && a.seg_rows[i] % BOXR) return cudaErrorInvalidValue;  // boxes may not straddle segments
+  for (int i = 0; i < a.nseg; ++i)
+    if ((reinterpret_cast<uintptr_t>(a.w[i]) & 15) != 0) return cudaErrorInvalidValue;
   const bool two = a.batch > 4;
   if (a.type == RG_TYPE_Q4_0) return two ? launch_e<RG_TYPE_Q4_0, 2>(a, cfg) : launch_e<RG_TYPE_Q4_0, 1>(a, cfg);
   if (a.type == RG_TYPE_Q8_0) return two ? launch_e<RG_TYPE_Q8_0, 2>(a, cfg) : launch_e<RG_TYPE_Q8_0, 1>(a, cfg);

@@ -681,8 +681,8 @@ int32_t rg_b200_plan_create(const rg_llama_config *c, const rg_options *o, rg_pl
   if (c->n_layers <= 0 || c->d_model <= 0 || c->n_heads <= 0 || c->n_kv_heads <= 0 || c->head_dim <= 0 || c->ffn_dim <= 0 ||
       c->vocab <= 0 || c->max_context <= 0 || c->n_heads % c->n_kv_heads || !(c->norm_eps >= 0.0f) || !(c->rope_theta > 0.0))
     return fail(RG_INVALID_ARGUMENT, "invalid model configuration");
-  if (c->head_dim > 128 || (c->head_dim & 1) || c->n_heads / c->n_kv_heads > 8)
-    return fail(RG_UNSUPPORTED_GEOMETRY, "head_dim must be even and <= 128, query heads per kv head <= 8");
+  if (!attention_supported(c->n_heads, c->n_kv_heads, c->head_dim))
+    return fail(RG_UNSUPPORTED_GEOMETRY, "head_dim must be 64 or 128 and query heads per kv head 1, 2, 4 or 8");
   auto p = std::make_unique<rg_plan>();
   p->cfg = *c;
   if (o) p->opt = *o;
