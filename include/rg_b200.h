@@ -199,6 +199,14 @@ int32_t rg_b200_qmatmul(int32_t device, int32_t ggml_type, const uint8_t *weight
 int32_t rg_b200_row_gather(int32_t device, int32_t ggml_type, const uint8_t *weight, uint64_t rows,
                            uint64_t cols, const int64_t *indices, size_t count, float *out);
 
+/* One decode token of scaled_dot_product_attention with GQA (src/ir/attention.rs:946-981,1157-1240;
+ * mask `col <= past + row` of src/models/transformer/layer.rs:374-380 for a single new row): q is
+ * [heads, head_dim] f32, already rotated; keys / values are caches [kv_heads, n_pos, head_dim] of
+ * f32 (kv_f32 != 0) or IEEE half; the token sits at position n_pos - 1 and attends to all n_pos
+ * positions.  out [heads, head_dim] f32. */
+int32_t rg_b200_attention_decode(int32_t device, const float *q, const void *keys, const void *values, int32_t heads,
+                                 int32_t kv_heads, int32_t head_dim, int32_t n_pos, int32_t kv_f32, float *out);
+
 /* Device-resident operator benchmark: weight uploaded once, `iters` launches timed with CUDA
  * events on the library's stream; `rotate` distinct weight copies are cycled so that each launch
  * reads HBM rather than L2.  kernel_ms receives the mean time of one launch. */

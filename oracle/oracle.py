@@ -79,6 +79,7 @@ def lib():
         L.rgo_select_greedy.argtypes = [f32p, C.c_int, i32p]
         L.rgo_generate_greedy.argtypes = [C.c_void_p, C.c_void_p, i32p, C.c_int, C.c_int, C.c_int, C.c_int, i32p,
                                           C.POINTER(C.c_int), C.POINTER(C.c_int)]
+        L.rgo_attention_decode.argtypes = [f32p, f32p, f32p, C.c_int, C.c_int, C.c_int, C.c_int, f32p]
         L.rgo_forward_f64.argtypes = [C.c_void_p, i32p, C.c_int, C.POINTER(C.c_double)]
         _lib = L
     return _lib
@@ -146,6 +147,19 @@ def dense_matmul_strict(weight: np.ndarray, activation: np.ndarray) -> np.ndarra
     a = np.ascontiguousarray(activation, dtype=np.float32).reshape(-1, w.shape[1])
     out = np.empty((a.shape[0], w.shape[0]), dtype=np.float32)
     lib().rgo_dense_matmul_strict(_f32(w), w.shape[0], w.shape[1], _f32(a), a.shape[0], _f32(out))
+    return out
+
+
+def attention_decode(q: np.ndarray, keys: np.ndarray, values: np.ndarray) -> np.ndarray:
+    """q [heads, hd]; keys/values [kv_heads, n_pos, hd] (f32) -> [heads, hd]."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    keys = np.ascontiguousarray(keys, dtype=np.float32)
+    values = np.ascontiguousarray(values, dtype=np.float32)
+    out = np.empty_like(q)
+    rc = lib().rgo_attention_decode(_f32(q), _f32(keys), _f32(values), q.shape[0], keys.shape[0], q.shape[1], keys.shape[1],
+                                    _f32(out))
+    if rc:
+        raise OracleError(rc, "attention_decode")
     return out
 
 

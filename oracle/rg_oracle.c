@@ -494,6 +494,23 @@ static void attend_row(const float *q, const float *keys, const float *values, i
   }
 }
 
+/* One new token's attention over caches laid out [kv_heads][n_pos][hd]; q is [heads][hd], already
+ * rotated.  src/ir/attention.rs:1157-1240 (GQA head mapping :1226-1240) via attend_row above. */
+int rgo_attention_decode(const float *q, const float *keys, const float *values, int heads, int kv_heads, int hd,
+                         int n_pos, float *out) {
+  if (!q || !keys || !values || !out || heads <= 0 || kv_heads <= 0 || heads % kv_heads || hd <= 0 || n_pos <= 0)
+    return RGO_ERR_ARG;
+  float *scores = (float *)malloc((size_t)n_pos * sizeof(float));
+  int group = heads / kv_heads;
+  for (int h = 0; h < heads; ++h) {
+    int kvh = h / group;
+    attend_row(q + (size_t)h * hd, keys + (size_t)kvh * n_pos * hd, values + (size_t)kvh * n_pos * hd, hd, n_pos - 1,
+               scores, out + (size_t)h * hd);
+  }
+  free(scores);
+  return RGO_OK;
+}
+
 static float round_f16(float v) { return rgo_f16_to_f32(rgo_f32_to_f16(v)); }
 
 int rgo_forward(const rgo_model *m, rgo_cache *cache, const int32_t *tokens, int S, int mode, int threads,

@@ -122,6 +122,11 @@ int rgo_generate_greedy(const rgo_model *model, rgo_cache *cache, const int32_t 
                         int n_prompt, int max_new, int mode, int threads, int32_t *out,
                         int *n_out, int *stopped);
 
+/* One decode token of src/ir/attention.rs:1157-1240: q [heads][hd] (rotated), caches
+ * [kv_heads][n_pos][hd], the token attends to all n_pos positions; out [heads][hd]. */
+int rgo_attention_decode(const float *q, const float *keys, const float *values, int heads, int kv_heads, int hd,
+                         int n_pos, float *out);
+
 /* Independent f64 forward (no f32 commits) used only to pin the strict mode, in the manner of
  * the in-test oracle of src/models/transformer/model_tests.rs:827-997.  Full sequence, no cache. */
 int rgo_forward_f64(const rgo_model *model, const int32_t *tokens, int n_tokens, double *logits);

@@ -218,6 +218,57 @@ int32_t rg_b200_row_gather(int32_t device, int32_t type, const uint8_t *weight, 
   return RG_OK;
 }
 
+int32_t rg_b200_attention_decode(int32_t device, const float *q, const void *keys, const void *values, int32_t heads,
+                                 int32_t kv_heads, int32_t head_dim, int32_t n_pos, int32_t kv_f32, float *out) {
+  if (!q || !keys || !values || !out) return fail(RG_INVALID_ARGUMENT, "null argument");
+  if (n_pos < 1) return fail(RG_INVALID_ARGUMENT, "n_pos must be at least 1");
+  if (heads < 1 || kv_heads < 1 || !attention_supported(heads, kv_heads, head_dim))
+    return fail(RG_UNSUPPORTED_GEOMETRY, "head_dim must be 64 or 128 and query heads per kv head 1, 2, 4 or 8");
+  Scope sc;
+  LaunchCfg cfg;
+  int *d_status;
+  int32_t rc;
+  if ((rc = open_scope(device, &sc, &cfg, &d_status))) return rc;
+  const size_t item = kv_f32 ? 4 : 2;
+  const size_t kv_bytes = (size_t)kv_heads * n_pos * head_dim * item, q_bytes = sizeof(float) * (size_t)heads * head_dim;
+  float *d_q, *d_out, *d_scratch;
+  uint8_t *d_k, *d_v;
+  int32_t *d_ctl;
+  OP_CUDA(sc.alloc(&d_q, q_bytes));
+  OP_CUDA(sc.alloc(&d_out, q_bytes));
+  OP_CUDA(sc.alloc(&d_k, kv_bytes));
+  OP_CUDA(sc.alloc(&d_v, kv_bytes));
+  OP_CUDA(sc.alloc(&d_ctl, 2 * sizeof(int32_t)));
+  OP_CUDA(sc.alloc(&d_scratch, sizeof(float) * attn_scratch_floats(1, heads, head_dim, n_pos)));
+  const int32_t ctl[2] = {0, n_pos - 1};  // sequence 0, position of the new token
+  OP_CUDA(cudaMemcpyAsync(d_q, q, q_bytes, cudaMemcpyHostToDevice, sc.stream));
+  OP_CUDA(cudaMemcpyAsync(d_k, keys, kv_bytes, cudaMemcpyHostToDevice, sc.stream));
+  OP_CUDA(cudaMemcpyAsync(d_v, values, kv_bytes, cudaMemcpyHostToDevice, sc.stream));
+  OP_CUDA(cudaMemcpyAsync(d_ctl, ctl, sizeof(ctl), cudaMemcpyHostToDevice, sc.stream));
+  AttnArgs a;
+  a.q = d_q;
+  a.k_cache = d_k;
+  a.v_cache = d_v;
+  a.kv_f32 = kv_f32 != 0;
+  a.cols = 1;
+  a.heads = heads;
+  a.kv_heads = kv_heads;
+  a.hd = head_dim;
+  a.ctx = n_pos;
+  a.col_seq = d_ctl;
+  a.col_pos = d_ctl + 1;
+  a.scratch = d_scratch;
+  a.out_f32 = d_out;
+  OP_CUDA(launch_attention(a, cfg));
+  int status = 0;
+  OP_CUDA(cudaMemcpyAsync(out, d_out, q_bytes, cudaMemcpyDeviceToHost, sc.stream));
+  OP_CUDA(cudaMemcpyAsync(&status, d_status, sizeof(int), cudaMemcpyDeviceToHost, sc.stream));
+  OP_CUDA(cudaStreamSynchronize(sc.stream));
+  if (status == 1) return fail(RG_TIMEOUT, "a bounded device-side wait gave up");
+  if (status) return fail(RG_CUDA_ERROR, "device status " + std::to_string(status));
+  return RG_OK;
+}
+
 int32_t rg_b200_qmatmul_bench(int32_t device, int32_t type, const uint8_t *weight, uint64_t n, uint64_t k, const float *activation,
                               uint64_t m, int32_t rotate, int32_t iters, int32_t warmup, float *out, float *kernel_ms) {
   if (!weight || !activation || !kernel_ms) return fail(RG_INVALID_ARGUMENT, "null argument");

@@ -330,6 +330,19 @@ def row_gather(ggml_type: int, weight, rows: int, cols: int, indices, device: in
     return out
 
 
+def attention_decode(q, keys, values, device: int = 0) -> np.ndarray:
+    """q [heads, hd] f32; keys/values [kv_heads, n_pos, hd] as float32 or float16 arrays -> [heads, hd]."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    if keys.dtype != values.dtype or keys.dtype not in (np.float32, np.float16):
+        raise TypeError("caches must both be float32 or both float16")
+    keys, values = np.ascontiguousarray(keys), np.ascontiguousarray(values)
+    out = np.empty_like(q)
+    check(_lib.load().rg_b200_attention_decode(device, _f32(q), keys.ctypes.data_as(C.c_void_p),
+                                               values.ctypes.data_as(C.c_void_p), q.shape[0], keys.shape[0], q.shape[1],
+                                               keys.shape[1], int(keys.dtype == np.float32), _f32(out)))
+    return out
+
+
 def qmatmul_bench(ggml_type: int, weight, n: int, k: int, activation, rotate: int, iters: int, warmup: int = 3,
                   device: int = 0):
     """Returns (output [m,n], mean kernel milliseconds) for weights resident in HBM."""

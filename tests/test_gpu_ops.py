@@ -149,3 +149,28 @@ def test_row_gather_is_bit_exact_and_preflights_indices():
                 session.row_gather(kind, data, rows, cols, bad)
             assert e.value.status == 5
         assert session.row_gather(kind, data, rows, cols, []).shape == (0, cols)
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd", [(4, 4, 64), (8, 2, 128), (32, 8, 128), (16, 2, 128)])
+@pytest.mark.parametrize("n_pos", [1, 31, 128, 129, 700])
+def test_decode_attention_matches_reference_softmax_composition(heads, kv_heads, hd, n_pos):
+    # tolerance: 1e-5 absolute on outputs that are convex combinations of N(0,1) values
+    rng = np.random.default_rng(heads * 1000 + n_pos)
+    q = rng.standard_normal((heads, hd)).astype(np.float32)
+    k = rng.standard_normal((kv_heads, n_pos, hd)).astype(np.float32)
+    v = rng.standard_normal((kv_heads, n_pos, hd)).astype(np.float32)
+    want = O.attention_decode(q, k, v)
+    got = session.attention_decode(q, k, v)
+    assert np.abs(got - want).max() <= 1e-5
+    k16, v16 = k.astype(np.float16), v.astype(np.float16)
+    want16 = O.attention_decode(q, k16.astype(np.float32), v16.astype(np.float32))
+    got16 = session.attention_decode(q, k16, v16)
+    assert np.abs(got16 - want16).max() <= 1e-5
+
+
+def test_decode_attention_rejects_unsupported_head_geometry():
+    q = np.zeros((6, 96), np.float32)
+    kv = np.zeros((2, 4, 96), np.float32)
+    with pytest.raises(session.RgError) as e:
+        session.attention_decode(q, kv, kv)
+    assert e.value.status == 20
