@@ -207,6 +207,25 @@ int32_t rg_b200_row_gather(int32_t device, int32_t ggml_type, const uint8_t *wei
 int32_t rg_b200_attention_decode(int32_t device, const float *q, const void *keys, const void *values, int32_t heads,
                                  int32_t kv_heads, int32_t head_dim, int32_t n_pos, int32_t kv_f32, float *out);
 
+/* The same decode attention for callers that must not allocate device memory: a runtime that
+ * carved up all of its HBM into its own arena at start-up, a serving loop that cannot afford the
+ * device-wide stall of a cudaMalloc, or code between the begin and end of a stream capture.  It
+ * has no counterpart in rustgrad (whose CUDA layer always draws scratch from its pooled
+ * allocator).  All pointers are DEVICE pointers owned by the caller: q [heads, head_dim] f32,
+ * caches [kv_heads, ctx, head_dim] (ctx = rows allocated per kv head, of which the first n_pos are
+ * used; the new token sits at n_pos - 1), out [heads, head_dim] f32.  The split-context partials
+ * live in a 4 MiB array inside the library image, held by every GPU that loads the library until
+ * the process ends; heads * ceil(ctx / 128) * (head_dim + 2) may not exceed 1 048 576 floats, and
+ * anything larger is refused with RG_UNSUPPORTED_GEOMETRY.  The call makes no cudaMalloc, cudaFree
+ * or other allocating call.  The first call on a device resolves the array's device address and
+ * prepares the kernels: make it before any stream capture.  Every call on a device shares the
+ * array, so calls whose kernels could overlap on the GPU must be ordered by the caller.  Work is
+ * enqueued on `stream` (a cudaStream_t, NULL for the default stream); with wait != 0 the call
+ * also synchronises the stream and reports a device-side time-out as RG_TIMEOUT. */
+int32_t rg_b200_attention_decode_noalloc(const float *q_dev, const void *keys_dev, const void *values_dev, int32_t heads,
+                                         int32_t kv_heads, int32_t head_dim, int32_t ctx, int32_t n_pos, int32_t kv_f32,
+                                         float *out_dev, void *stream, int32_t wait);
+
 /* Device-resident operator benchmark: weight uploaded once, `iters` launches timed with CUDA
  * events on the library's stream; `rotate` distinct weight copies are cycled so that each launch
  * reads HBM rather than L2.  kernel_ms receives the mean time of one launch. */

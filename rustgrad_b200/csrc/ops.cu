@@ -4,6 +4,9 @@
 // pdl_wait() before touching step data so programmatic dependent launch stays transitive.
 #include <math.h>
 
+#include <mutex>
+#include <string>
+
 #include "../../include/rg_b200.h"
 #include "kernels.h"
 #include "rg_device.cuh"
@@ -717,4 +720,111 @@ cudaError_t launch_fill_f32(float *out, size_t n, float v, const LaunchCfg &cfg)
   return launch(fill_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, plain, out, n, v);
 }
 
+// ------------------------------------------------------------------------------ no-allocation attention
+// Decode attention for callers that must not allocate device memory while they run: a host
+// runtime that hands out all of its HBM from its own arena at start-up (rustgrad's pooled CUDA
+// allocator is one), a latency-critical serving loop in which a cudaMalloc would stall the
+// device, or code running between the begin and end of a stream capture, where allocation calls
+// are not permitted.  The split-context partial results that the ordinary entry point keeps in a
+// cudaMalloc'ed buffer live here in a fixed array inside the library image instead.
+//
+// Limits and rules for users:
+//  * heads * ceil(ctx / 128) * (head_dim + 2) must not exceed RG_NOALLOC_SCRATCH_FLOATS
+//    (1 Mi floats = 4 MiB; e.g. 64 heads of 128 dims up to a context of 15 872 positions).
+//    Larger problems are refused with RG_UNSUPPORTED_GEOMETRY before anything is launched.
+//  * Every GPU that loads the library holds these 4 MiB until the process exits.
+//  * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
+//    prepares the kernels; make that first call outside any stream capture.
+//  * All calls on a device share the one array.  Two calls whose kernels may overlap on the GPU
+//    (different streams without an ordering between them) race on it; order them.  Nothing in
+//    the array has to start at zero: each call overwrites every partial it later reads, and the
+//    three control words in front of the partials are rewritten by a kernel at the start of each call.
+namespace {
+constexpr size_t NOALLOC_SCRATCH_FLOATS = size_t(1) << 20;
+constexpr size_t NOALLOC_HEADER_FLOATS = 64;  // control words: sequence, position, status
+static __device__ __align__(256) float g_noalloc_attn[NOALLOC_HEADER_FLOATS + NOALLOC_SCRATCH_FLOATS];
+
+__global__ void noalloc_header_kernel(int32_t *header, int32_t pos) {
+  header[0] = 0;    // the single sequence
+  header[1] = pos;  // position of the new token
+  header[2] = DEV_OK;
+}
+
+// The array's name is only a host-side handle; kernels need the device address, looked up once
+// per device with that device current.
+cudaError_t noalloc_base(float **out) {
+  static std::mutex mu;
+  static float *base[64] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!base[dev]) {
+    float *p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_noalloc_attn);
+    if (e != cudaSuccess) return e;
+    base[dev] = p;
+  }
+  *out = base[dev];
+  return cudaSuccess;
+}
+}  // namespace
+
+extern thread_local std::string g_last_error;
+
 }  // namespace rg
+
+extern "C" int32_t rg_b200_attention_decode_noalloc(const float *q_dev, const void *keys_dev, const void *values_dev, int32_t heads,
+                                                    int32_t kv_heads, int32_t head_dim, int32_t ctx, int32_t n_pos, int32_t kv_f32,
+                                                    float *out_dev, void *stream, int32_t wait) {
+  using namespace rg;
+  auto fail = [](int32_t status, const std::string &why) {
+    g_last_error = why;
+    return status;
+  };
+  if (!q_dev || !keys_dev || !values_dev || !out_dev) return fail(RG_INVALID_ARGUMENT, "null device pointer");
+  if (n_pos < 1 || ctx < n_pos) return fail(RG_INVALID_ARGUMENT, "need 1 <= n_pos <= ctx");
+  if (heads < 1 || kv_heads < 1 || !attention_supported(heads, kv_heads, head_dim))
+    return fail(RG_UNSUPPORTED_GEOMETRY, "head_dim must be 64 or 128 and query heads per kv head 1, 2, 4 or 8");
+  const size_t need = attn_scratch_floats(1, heads, head_dim, ctx);
+  if (need > NOALLOC_SCRATCH_FLOATS)
+    return fail(RG_UNSUPPORTED_GEOMETRY, "the allocation-free attention holds " + std::to_string(NOALLOC_SCRATCH_FLOATS) +
+                                             " scratch floats; heads * ceil(ctx / 128) * (head_dim + 2) = " +
+                                             std::to_string(need) + " is beyond that");
+  float *base = nullptr;
+  cudaError_t e = noalloc_base(&base);
+  if (e != cudaSuccess) return fail(RG_CUDA_ERROR, std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+  int32_t *header = reinterpret_cast<int32_t *>(base);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  noalloc_header_kernel<<<1, 1, 0, st>>>(header, n_pos - 1);
+  if ((e = cudaGetLastError()) != cudaSuccess) return fail(RG_CUDA_ERROR, std::string("header launch: ") + cudaGetErrorString(e));
+  LaunchCfg cfg;
+  cfg.stream = st;
+  cfg.pdl = false;
+  cfg.status = header + 2;
+  AttnArgs a;
+  a.q = q_dev;
+  a.k_cache = keys_dev;
+  a.v_cache = values_dev;
+  a.kv_f32 = kv_f32 != 0;
+  a.cols = 1;
+  a.heads = heads;
+  a.kv_heads = kv_heads;
+  a.hd = head_dim;
+  a.ctx = ctx;
+  a.col_seq = header;
+  a.col_pos = header + 1;
+  a.scratch = base + NOALLOC_HEADER_FLOATS;
+  a.out_f32 = out_dev;
+  if ((e = launch_attention(a, cfg)) != cudaSuccess) return fail(RG_CUDA_ERROR, std::string("attention launch: ") + cudaGetErrorString(e));
+  if (wait) {
+    int status = 0;
+    if ((e = cudaMemcpyAsync(&status, header + 2, sizeof(int), cudaMemcpyDeviceToHost, st)) != cudaSuccess ||
+        (e = cudaStreamSynchronize(st)) != cudaSuccess)
+      return fail(RG_CUDA_ERROR, std::string("synchronize: ") + cudaGetErrorString(e));
+    if (status == DEV_TIMEOUT) return fail(RG_TIMEOUT, "a bounded device-side wait gave up");
+    if (status) return fail(RG_CUDA_ERROR, "device status " + std::to_string(status));
+  }
+  return RG_OK;
+}
