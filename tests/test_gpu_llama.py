@@ -256,3 +256,32 @@ def test_device_synthesized_weights_match_host_recipe():
         assert abs(float(normal.std()) - 1.0) < 0.02 and abs(float(normal.mean())) < 0.02
         want = quant.encode(kind, w.reshape(rows, cols))
         assert np.array_equal(got, want.reshape(-1)), name
+
+
+def test_llama3_8b_width_model_matches_cpu_path_on_device_synthesized_weights():
+    """BASELINE config 4 at full width (d 4096, 32/8 heads of 128, ffn 14336, vocab 128256, Q4_0 body,
+    Q8_0 embedding + head, f16 KV) with 3 of the 32 layers, so the CPU checker finishes in seconds.
+    The weights are generated on the device and read back, so both sides see the same bytes."""
+    cfg = synth.scaled(synth.LLAMA_8B, n_layers=3, max_context=256)
+    target = session.CudaSessionTarget(max_context=256)
+    plan = session.LlamaCudaPlan.synthetic(cfg, target, seed=6)
+    tensors = {}
+    for name, rows, cols, is_norm in synth.tensor_inventory(cfg, tied_head=False):
+        kind = quant.F32 if is_norm else quant.Q8_0 if name in ("token_embd.weight", "output.weight") else quant.Q4_0
+        tensors[name] = (kind, rows, cols, plan.read_tensor(name))
+    s = plan.prepare()
+    oracle = O.OracleModel(cfg, tensors, kv_f16=True)
+    prompt = synth.prompt_ids(cfg, 24, seed=1)
+    want = oracle.forward(prompt, O.MODE_FAST)
+    got = s.prefill_ids(prompt)
+    assert_logits_close(got, want)
+    tok = O.select_greedy(want)
+    assert int(np.argmax(got)) == tok
+    for _ in range(4):
+        want = oracle.forward([tok], O.MODE_FAST)
+        logits, greedy = s.decode([tok], want_logits=True)
+        assert_logits_close(logits[0], want)
+        nxt = O.select_greedy(want)
+        top2 = np.sort(want)[-2:]
+        assert int(greedy[0]) == nxt or (top2[1] - top2[0]) < 1e-5, "greedy token differs beyond a numerical tie"
+        tok = nxt

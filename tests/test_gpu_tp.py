@@ -1,0 +1,74 @@
+"""Tensor-parallel session on 2 GPUs (one process per GPU, NCCL) against the CPU checker and the
+single-GPU session.  Skipped when fewer than two devices are visible."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from rustgrad_b200 import quant, synth
+
+pytestmark = pytest.mark.gpu
+
+CFG = synth.scaled(synth.TINY, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn_dim=1024, vocab=640, n_layers=2,
+                   rope_theta=500000.0)
+
+
+def free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    from rustgrad_b200 import session
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    box = [session.nccl_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    tensors = synth.build_tensors(CFG, seed=6, body_type=quant.Q4_0, embed_type=quant.Q8_0, head_type=quant.Q8_0, tied_head=False)
+    target = session.CudaSessionTarget(device=rank, kv_f32=True, tp_rank=rank, tp_world=world, nccl_id=box[0])
+    s = session.LlamaCudaPlan.from_tensors(CFG, tensors, target).prepare()
+    prompt = synth.prompt_ids(CFG, 11, seed=2)
+    logits = [s.prefill_ids(prompt)]
+    tok = int(np.argmax(logits[0]))
+    ids = [tok]
+    for _ in range(6):
+        lg, greedy = s.decode([tok], want_logits=True)
+        logits.append(lg[0])
+        tok = int(greedy[0])
+        ids.append(tok)
+    np.save(os.path.join(out_dir, f"logits{rank}.npy"), np.stack(logits))
+    np.save(os.path.join(out_dir, f"ids{rank}.npy"), np.array(ids))
+    dist.barrier()
+    s.close()
+    dist.destroy_process_group()
+
+
+def test_two_gpu_tensor_parallel_matches_single_gpu_and_cpu_path(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from oracle import oracle as O
+    from rustgrad_b200 import session
+    mp.spawn(worker, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
+    l0, l1 = np.load(tmp_path / "logits0.npy"), np.load(tmp_path / "logits1.npy")
+    i0, i1 = np.load(tmp_path / "ids0.npy"), np.load(tmp_path / "ids1.npy")
+    assert np.array_equal(l0, l1) and np.array_equal(i0, i1)  # every rank holds identical logits
+    tensors = synth.build_tensors(CFG, seed=6, body_type=quant.Q4_0, embed_type=quant.Q8_0, head_type=quant.Q8_0, tied_head=False)
+    oracle = O.OracleModel(CFG, tensors, threads=4)
+    prompt = synth.prompt_ids(CFG, 11, seed=2)
+    want = [oracle.forward(prompt)]
+    ids = [O.select_greedy(want[0])]
+    for _ in range(6):
+        want.append(oracle.forward([ids[-1]]))
+        ids.append(O.select_greedy(want[-1]))
+    assert i0.tolist() == ids
+    diff = np.abs(l0 - np.stack(want)).max()
+    assert diff <= 1e-2 and diff <= 1e-3 * np.abs(np.stack(want)).max() + 1e-6
+    single = session.LlamaCudaPlan.from_tensors(CFG, tensors, session.CudaSessionTarget(kv_f32=True)).prepare()
+    assert np.abs(single.prefill_ids(prompt) - l0[0]).max() <= 1e-4
