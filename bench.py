@@ -191,6 +191,8 @@ def main():
     dist = None
     nccl_id = b""
     if n > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
         if world != n:
             raise SystemExit(f"--gpus {n} needs torchrun with {n} ranks (WORLD_SIZE={world})")
         import torch.distributed as dist

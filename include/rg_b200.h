@@ -79,7 +79,7 @@ typedef struct {
   int32_t disable_graph; /* 1: launch decode kernels directly instead of replaying a CUDA graph */
   int32_t disable_pdl;   /* 1: no programmatic dependent launch between kernels */
   int32_t disable_fused_allreduce; /* 1: TP all-reduce through NCCL only */
-  int32_t reserved[8];
+  int32_t reserved[8];    /* reserved[0] == 1: never take the fused small-batch decode path */
 } rg_options;
 
 /* Per-run evidence in the vocabulary of MetalDeviceRunReport

@@ -35,6 +35,28 @@ struct GemvArgs {
 cudaError_t launch_qgemv(const GemvArgs &a, const LaunchCfg &cfg);
 size_t xpack_bytes(int k, int batch);  // K rounded up to a whole 32-element block
 
+// Integer tensor-core GEMV for batch 1..2 with the activations packed (and optionally
+// RMS-normalised) by the kernel's own prologue from plain f32 input.  Same segment / epilogue
+// conventions as GemvArgs, except that EPI_SWIGLU writes plain f32 to y.
+struct GemvI8Args {
+  int type = 0;  // RG_TYPE_Q4_0 or RG_TYPE_Q8_0
+  const uint8_t *w[3] = {nullptr, nullptr, nullptr};
+  int seg_rows[3] = {0, 0, 0};
+  int nseg = 1;
+  int k = 0;
+  const float *x = nullptr;  // [batch][ldx]
+  int ldx = 0;
+  const int32_t *col_map = nullptr;  // device array: source row of each batch column (nullable)
+  const float *norm_w = nullptr;     // RMSNorm weight [k]; nullptr = no normalisation
+  float eps = 0.0f;
+  int batch = 1;
+  int epi = EPI_STORE;
+  float *y = nullptr;
+  int ldy = 0;
+};
+bool qgemv_i8_supported(int k, int batch);
+cudaError_t launch_qgemv_i8(const GemvI8Args &a, const LaunchCfg &cfg);
+
 // Dense (F32/F16) weight GEMV for tensors the block formats cannot hold (K % 32 != 0) or that a
 // file stores dense.  x is plain f32 [batch, ldx]; same epilogues (EPI_SWIGLU unsupported).
 struct DenseGemvArgs {

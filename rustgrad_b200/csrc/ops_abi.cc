@@ -89,7 +89,22 @@ int32_t run_matmul(int32_t type, const uint8_t *d_w, uint64_t n, uint64_t k, con
   const bool packed = (type == RG_TYPE_Q4_0 || type == RG_TYPE_Q8_0);
   for (uint64_t m0 = 0; m0 < m; m0 += 8) {
     const int batch = (int)std::min<uint64_t>(8, m - m0);
-    if (packed) {
+    if (packed && qgemv_i8_supported((int)k, batch)) {
+      // batch 1..2: integer tensor-core kernel, packs the f32 activations in its own prologue
+      GemvI8Args a;
+      a.type = type;
+      a.w[0] = d_w;
+      a.seg_rows[0] = (int)n;
+      a.nseg = 1;
+      a.k = (int)k;
+      a.x = d_x + m0 * k;
+      a.ldx = (int)k;
+      a.batch = batch;
+      a.epi = EPI_STORE;
+      a.y = d_y + m0 * n;
+      a.ldy = (int)n;
+      OP_CUDA(launch_qgemv_i8(a, cfg));
+    } else if (packed) {
       OP_CUDA(launch_pack(d_x + m0 * k, (int)k, (int)k, batch, d_pack, cfg));
       GemvArgs a;
       a.type = type;
@@ -306,17 +321,32 @@ int32_t rg_b200_qmatmul_bench(int32_t device, int32_t type, const uint8_t *weigh
   a.epi = EPI_STORE;
   a.y = d_y;
   a.ldy = (int)n;
+  // batch 1..2 runs the integer tensor-core kernel (activations packed by its prologue)
+  const bool use_i8 = qgemv_i8_supported((int)k, (int)m);
+  GemvI8Args a8;
+  a8.type = type;
+  a8.seg_rows[0] = (int)n;
+  a8.nseg = 1;
+  a8.k = (int)k;
+  a8.x = d_x;
+  a8.ldx = (int)k;
+  a8.batch = (int)m;
+  a8.epi = EPI_STORE;
+  a8.y = d_y;
+  a8.ldy = (int)n;
+  auto launch_one = [&](const uint8_t *w) {
+    if (use_i8) {
+      a8.w[0] = w;
+      return launch_qgemv_i8(a8, cfg);
+    }
+    a.w[0] = w;
+    return launch_qgemv(a, cfg);
+  };
   OP_CUDA(cudaEventCreate(&sc.e0));
   OP_CUDA(cudaEventCreate(&sc.e1));
-  for (int i = 0; i < warmup; ++i) {
-    a.w[0] = copies[(size_t)(i % rotate)];
-    OP_CUDA(launch_qgemv(a, cfg));
-  }
+  for (int i = 0; i < warmup; ++i) OP_CUDA(launch_one(copies[(size_t)(i % rotate)]));
   OP_CUDA(cudaEventRecord(sc.e0, sc.stream));
-  for (int i = 0; i < iters; ++i) {
-    a.w[0] = copies[(size_t)((warmup + i) % rotate)];
-    OP_CUDA(launch_qgemv(a, cfg));
-  }
+  for (int i = 0; i < iters; ++i) OP_CUDA(launch_one(copies[(size_t)((warmup + i) % rotate)]));
   OP_CUDA(cudaEventRecord(sc.e1, sc.stream));
   int status = 0;
   if (out) OP_CUDA(cudaMemcpyAsync(out, d_y, sizeof(float) * m * n, cudaMemcpyDeviceToHost, sc.stream));

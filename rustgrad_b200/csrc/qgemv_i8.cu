@@ -1,0 +1,513 @@
+// Decode GEMV (batch 1..2) for Q4_0 / Q8_0 weights in their native GGML block bytes, integer
+// tensor-core variant.  Semantics: the per-layer linear of the Llama forward
+// (src/models/transformer/layer.rs:445-448) with the dequantised weight of
+// src/gguf/quantization/blocks.rs:1244-1257,1493-1505; RMSNorm of layer.rs:423-443 fused in front.
+//
+// Why a second GEMV kernel: the f16-MMA kernel (qgemv.cu) is bound by the instructions that expand
+// nibbles to f16, not by HBM.  Here the weights never leave the integer domain:
+//  * Q8_0 quants are already the s8 A operand of mma.sync.m16n8k32; Q4_0 nibbles become
+//    s8 values 16*(n-8) with one shift and two logic ops per 8 weights (xor 8 turns offset binary
+//    into two's complement, kept in the high nibble of each byte).  The natural byte order of a
+//    Q4_0 word (low nibbles = elements 4t..4t+3, high nibbles = 16+4t..) is exactly the A fragment.
+//  * The activation block (32 values) is converted once per CTA to 32-bit block fixed point,
+//    x = s_b * X with s_b a power of two and |X| < 2^30, and X is split into four signed base-256
+//    digits that sit in four B columns.  One MMA per (16 rows x 32 k) block gives four exact int32
+//    digit sums; (c0 + 256 c1) and (c2 + 256 c3) are converted to f32 and accumulated with the
+//    factor d * s_b.  Everything up to that conversion is exact, so the result carries the full
+//    f32 activation (relative 2^-30 of the block maximum) and f32 accumulation over blocks.
+//  * The packed activations stay resident in shared memory for the whole kernel, produced by the
+//    CTA itself in the prologue from the previous kernel's f32 output, optionally through RMSNorm:
+//    no separate normalisation / packing kernel, no activation traffic per stage.
+//  * Weight streaming is the same as in qgemv.cu: persistent CTA per SM, tiled 2-D TMA boxes of
+//    8 rows into a 3-6 stage mbarrier pipeline with bounded waits, bank-conflict-free pitch, weight
+//    prefetch issued before the grid dependency wait.
+#include <cuda.h>
+
+#include "../../include/rg_b200.h"
+#include "kernels.h"
+#include "rg_device.cuh"
+
+namespace rg {
+namespace {
+
+constexpr int R = 32;     // weight rows per stage: two m16 tiles
+constexpr int BOXR = 8;   // rows per TMA box
+constexpr int CW = 14;    // consumer warps
+constexpr int MAX_STAGES = 6;
+constexpr int THREADS = (CW + 1) * 32;
+constexpr int SMEM_LIMIT = 227 * 1024;
+
+template <int QT>
+struct Geo {
+  static constexpr bool Q4 = (QT == RG_TYPE_Q4_0);
+  static constexpr int BB = Q4 ? 18 : 34;
+  static constexpr int KC = Q4 ? 56 : 40;  // blocks per stage; pitch 1008 / 1360 bytes (28 / 20 banks)
+  static constexpr int RS = KC * BB;
+  static_assert(RS % 16 == 0 && (BOXR * RS) % 128 == 0 && RS / 8 <= 256, "TMA box geometry");
+};
+
+struct Params {
+  int seg_rows[3];
+  int nseg;
+  int n_rows;  // virtual rows (EPI_SWIGLU: rows of the gate matrix)
+  int kb;      // K / 32
+  const float *x;  // [cols][ldx] f32 input of the previous kernel
+  int ldx;
+  const int32_t *col_map;  // nullable: source row of each batch column
+  const float *norm_w;     // nullable: RMSNorm weight (prologue normalises when set)
+  float eps;
+  int batch;  // 1..2
+  float *y;
+  int ldy;
+  int rows_per_cta;
+  int stages;
+  int *status;
+};
+
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1+%2];" : "=h"(v) : "r"(addr), "n"(OFF));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float ldsf(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void tma_box_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+// D(16x8,s32) = A(16x32,s8,row) * B(32x8,s8,col)
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  const int z = 0;
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
+}
+// Q4_0 word -> s8 bytes 16*(n-8): low nibbles (elements 4t..) and high nibbles (elements 16+4t..)
+__device__ __forceinline__ void q4_to_s8(uint32_t q, uint32_t &lo, uint32_t &hi) {
+  lo = ((q << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
+  hi = (q & 0xF0F0F0F0u) ^ 0x80808080u;
+}
+
+// Row slot rs of a stage is shared row (rs >> 1) * 16 + (rs & 1) * 8 + g; `a` points at
+// (row g, word t) of the block pair, `s` at the pair's first scale of row g.
+template <int QT, int RSLOT>
+__device__ __forceinline__ void load_slot(uint32_t a, uint32_t s, uint32_t (&w)[6], uint32_t (&sc)[2]) {
+  using G = Geo<QT>;
+  constexpr int R0 = ((RSLOT >> 1) * 16 + (RSLOT & 1) * 8) * G::RS;
+  if constexpr (G::Q4) {
+    w[0] = lds32<R0>(a);
+    w[1] = lds32<R0 + 4>(a);
+    w[2] = lds32<R0 + 20>(a);
+  } else {
+    w[0] = lds32<R0>(a);
+    w[1] = lds32<R0 + 4>(a);
+    w[2] = lds32<R0 + 16>(a);
+    w[3] = lds32<R0 + 20>(a);
+    w[4] = lds32<R0 + 36>(a);
+    w[5] = lds32<R0 + 52>(a);
+  }
+  sc[0] = lds16<R0>(s);
+  sc[1] = lds16<R0 + G::BB>(s);
+}
+
+// A operands of the even and the odd block of a pair for one row slot: {k 0..15, k 16..31}
+template <int QT>
+__device__ __forceinline__ void expand(const uint32_t (&w)[6], uint32_t (&ae)[2], uint32_t (&ao)[2]) {
+  if constexpr (Geo<QT>::Q4) {
+    q4_to_s8(__funnelshift_r(w[0], w[1], 16), ae[0], ae[1]);
+    q4_to_s8(w[2], ao[0], ao[1]);
+  } else {
+    ae[0] = __funnelshift_r(w[0], w[1], 16);
+    ae[1] = __funnelshift_r(w[2], w[3], 16);
+    ao[0] = w[4];
+    ao[1] = w[5];
+  }
+}
+
+// Shared layout of the resident activations: digits then block scales.
+//   digit byte of element e of block kb, column c (= 4*batch + digit):
+//     ((kb * S + c) * 4 + t) * 8 + r * 4 + i,  e < 16: t = e/4, r = 0;  e >= 16: t = (e-16)/4, r = 1;  i = e%4
+//   scale of (block kb, batch b): float at kb * B + b
+__device__ __forceinline__ uint32_t digit_offset(int S, int kb, int c, int e) {
+  const int t = (e & 15) >> 2, r = e >> 4, i = e & 3;
+  return (uint32_t)((((kb * S + c) * 4 + t) * 8) + r * 4 + i);
+}
+
+template <int QT, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+    qgemv_i8_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
+                    const __grid_constant__ CUtensorMap map2, const Params P) {
+  using G = Geo<QT>;
+  constexpr bool PAIR = (EPI == EPI_SWIGLU);
+  constexpr int GROUP_ROWS = PAIR ? 16 : 32;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem);
+  uint64_t *empty = full + MAX_STAGES;
+  volatile int *dead = reinterpret_cast<volatile int *>(empty + MAX_STAGES);
+  float *red = reinterpret_cast<float *>(smem + 128);  // [CW][R][4]; also scratch of the prologue
+  constexpr int RED_BYTES = CW * R * 4 * 4;
+  static_assert(RED_BYTES % 128 == 0, "alignment");
+  const int S = 4 * P.batch;
+  const int xs_bytes = (P.kb * S * 32 + 127) & ~127;
+  const int sb_bytes = (P.kb * P.batch * 4 + 127) & ~127;
+  uint8_t *xs = smem + 128 + RED_BYTES;
+  float *sb = reinterpret_cast<float *>(xs + xs_bytes);
+  uint8_t *stage0 = xs + xs_bytes + sb_bytes;
+  constexpr int STAGE_BYTES = R * G::RS;
+  static_assert(STAGE_BYTES % 128 == 0, "alignment");
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r_begin = blockIdx.x * P.rows_per_cta;
+  const int r_end = min(P.n_rows, r_begin + P.rows_per_cta);
+  const int n_groups = (r_end > r_begin) ? (r_end - r_begin + GROUP_ROWS - 1) / GROUP_ROWS : 0;
+  const int n_chunks = (P.kb + G::KC - 1) / G::KC;
+  const int units = n_groups * n_chunks;
+  const int stages = P.stages;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], CW);
+    }
+    *dead = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+
+  if (warp == CW) {
+    // ------------------------------------------------------------------ producer (weights only:
+    // constant data, so it never waits for the previous kernel)
+    int grp = 0, c = 0, stage = 0, round = 0;
+    for (int u = 0; u < units; ++u) {
+      if (round > 0) mbar_wait_bounded(&empty[stage], (uint32_t)((round - 1) & 1), dead, P.status);
+      const int vr0 = r_begin + grp * GROUP_ROWS;
+      uint8_t *sw = stage0 + (size_t)stage * STAGE_BYTES;
+      if (lane == 0) mbar_expect_tx(&full[stage], (uint32_t)STAGE_BYTES);
+      __syncwarp();
+      if (lane < R / BOXR) {
+        const CUtensorMap *map = &map0;
+        int row;
+        if (PAIR) {
+          map = (lane < 2) ? &map0 : &map1;
+          row = vr0 + (lane & 1) * BOXR;
+        } else {
+          row = vr0 + lane * BOXR;
+          if (P.nseg > 1 && row >= P.seg_rows[0]) {
+            row -= P.seg_rows[0];
+            map = &map1;
+            if (P.nseg > 2 && row >= P.seg_rows[1]) {
+              row -= P.seg_rows[1];
+              map = &map2;
+            }
+          }
+        }
+        tma_box_2d(sw + lane * BOXR * G::RS, map, c * (G::RS / 8), row, &full[stage]);
+      }
+      if (++c == n_chunks) {
+        c = 0;
+        ++grp;
+      }
+      if (++stage == stages) {
+        stage = 0;
+        ++round;
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------------- consumers
+  pdl_wait();
+  const int ctid = threadIdx.x;  // 0 .. CW*32-1
+  // ---- prologue: (RMSNorm and) block fixed-point packing of the activations into shared memory
+  for (int b = 0; b < P.batch; ++b) {
+    const float *xr = P.x + (size_t)(P.col_map ? P.col_map[b] : b) * P.ldx;
+    float inv = 1.0f;
+    if (P.norm_w) {
+      // y = (x * (1 / sqrt(mean(x^2) + eps))) * w, every step rounded to f32 (layer.rs:423-443)
+      float ss = 0.0f;
+      for (int i = ctid; i < P.kb * 32; i += CW * 32) ss = fmaf(xr[i], xr[i], ss);
+      ss = warp_sum(ss);
+      if (lane == 0) red[warp] = ss;
+      asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+      float tot = 0.0f;
+#pragma unroll
+      for (int w = 0; w < CW; ++w) tot += red[w];
+      const float mean = __fdiv_rn(tot, (float)(P.kb * 32));
+      inv = __frcp_rn(__fsqrt_rn(__fadd_rn(mean, P.eps)));
+      asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+    }
+    for (int kb = warp; kb < P.kb; kb += CW) {
+      float v = xr[kb * 32 + lane];
+      if (P.norm_w) v = __fmul_rn(__fmul_rn(v, inv), P.norm_w[kb * 32 + lane]);
+      const float m = warp_max(fabsf(v));
+      const uint32_t E = __float_as_uint(m) >> 23;  // biased exponent of the block maximum (m >= 0)
+      float s = 0.0f;
+      int X = 0;
+      if (E >= 40u && E < 255u) {
+        s = __uint_as_float((E - 29u) << 23);                     // 2^(floor(log2 m) - 29)
+        X = __float2int_rn(v * __uint_as_float((283u - E) << 23));  // |X| < 2^30
+      } else if (E == 255u) {  // inf / NaN input must stay visible in the result
+        s = __uint_as_float(0x7fc00000u);
+        X = 1;
+      }
+      // four signed base-256 digits
+      const int d0 = (int)(int8_t)(X & 0xff);
+      const int x1 = (X - d0) >> 8;
+      const int d1 = (int)(int8_t)(x1 & 0xff);
+      const int x2 = (x1 - d1) >> 8;
+      const int d2 = (int)(int8_t)(x2 & 0xff);
+      const int d3 = (x2 - d2) >> 8;
+      xs[digit_offset(S, kb, 4 * b + 0, lane)] = (uint8_t)d0;
+      xs[digit_offset(S, kb, 4 * b + 1, lane)] = (uint8_t)d1;
+      xs[digit_offset(S, kb, 4 * b + 2, lane)] = (uint8_t)d2;
+      xs[digit_offset(S, kb, 4 * b + 3, lane)] = (uint8_t)d3;
+      if (lane == 0) sb[kb * P.batch + b] = s;
+    }
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+
+  const int g = lane >> 2, t = lane & 3;
+  const bool col_live = g < S;              // this lane's B column carries a digit
+  const int my_batch = t >> 1;              // batch of this lane's accumulator columns
+  const bool acc_live = my_batch < P.batch;
+  float acc[2][2];  // [m-tile][row g / row g+8]
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt) acc[mt][0] = acc[mt][1] = 0.0f;
+
+  int stage = 0, c = 0, grp = 0;
+  uint32_t phase = 0;
+  const uint32_t smem_stage0 = smem_u32(stage0);
+  const uint32_t xs_lane = smem_u32(xs) + (uint32_t)((g * 4 + t) * 8);
+  const uint32_t sb_lane = smem_u32(sb) + (uint32_t)(my_batch * 4);
+  const uint32_t lane_w_off = (uint32_t)(g * G::RS + t * 4);
+  const uint32_t lane_s_off = (uint32_t)(g * G::RS);
+  for (int u = 0; u < units; ++u) {
+    const int nb = min(G::KC, P.kb - c * G::KC);
+    mbar_wait_bounded(&full[stage], phase, dead, P.status);
+    const uint32_t sw = smem_stage0 + (uint32_t)stage * (uint32_t)STAGE_BYTES;
+    uint32_t aw = sw + lane_w_off + (uint32_t)warp * (2 * G::BB);
+    uint32_t as = sw + lane_s_off + (uint32_t)warp * (2 * G::BB);
+    int gb = c * G::KC + 2 * warp;  // global block index of the pair's even block
+    for (int p = warp; 2 * p < nb; p += CW, aw += CW * 2 * G::BB, as += CW * 2 * G::BB, gb += 2 * CW) {
+      uint32_t wq[4][6], sc[4][2];
+      load_slot<QT, 0>(aw, as, wq[0], sc[0]);
+      load_slot<QT, 1>(aw, as, wq[1], sc[1]);
+      load_slot<QT, 2>(aw, as, wq[2], sc[2]);
+      load_slot<QT, 3>(aw, as, wq[3], sc[3]);
+      uint2 xe = make_uint2(0, 0), xo = make_uint2(0, 0);
+      if (col_live) {
+        xe = lds64(xs_lane + (uint32_t)(gb * S * 32));
+        xo = lds64(xs_lane + (uint32_t)((gb + 1) * S * 32));
+      }
+      float se = 0.0f, so = 0.0f;
+      if (acc_live) {
+        se = ldsf(sb_lane + (uint32_t)(gb * P.batch * 4));
+        so = ldsf(sb_lane + (uint32_t)((gb + 1) * P.batch * 4));
+      }
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        uint32_t ae[2][2], ao[2][2];
+        expand<QT>(wq[mt * 2], ae[0], ao[0]);
+        expand<QT>(wq[mt * 2 + 1], ae[1], ao[1]);
+        int ce[4], co[4];
+        mma_s8(ce, ae[0][0], ae[1][0], ae[0][1], ae[1][1], xe.x, xe.y);
+        mma_s8(co, ao[0][0], ao[1][0], ao[0][1], ao[1][1], xo.x, xo.y);
+        // this lane's two columns are digit 2j and 2j+1 of one batch: fold them exactly
+        const float fe0 = (float)(ce[0] + (ce[1] << 8)), fe1 = (float)(ce[2] + (ce[3] << 8));
+        const float fo0 = (float)(co[0] + (co[1] << 8)), fo1 = (float)(co[2] + (co[3] << 8));
+        acc[mt][0] = fmaf(half_bits_to_float(sc[mt * 2][0]) * se, fe0, acc[mt][0]);
+        acc[mt][1] = fmaf(half_bits_to_float(sc[mt * 2 + 1][0]) * se, fe1, acc[mt][1]);
+        acc[mt][0] = fmaf(half_bits_to_float(sc[mt * 2][1]) * so, fo0, acc[mt][0]);
+        acc[mt][1] = fmaf(half_bits_to_float(sc[mt * 2 + 1][1]) * so, fo1, acc[mt][1]);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[stage]);
+
+    if (c == n_chunks - 1) {
+      // ---- cross-warp K reduction (fixed order) and epilogue for this row group
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int hs = 0; hs < 2; ++hs) {
+          red[(warp * R + mt * 16 + hs * 8 + g) * 4 + t] = acc[mt][hs];
+          acc[mt][hs] = 0.0f;
+        }
+      asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+      const int vr0 = r_begin + grp * GROUP_ROWS;
+      constexpr float A_SCALE = G::Q4 ? 0.0625f : 1.0f;  // Q4_0 operands were 16 * (n - 8)
+      for (int idx = ctid; idx < GROUP_ROWS * 2; idx += CW * 32) {
+        const int row = idx >> 1, b = idx & 1;
+        const int vrow = vr0 + row;
+        if (vrow >= r_end || b >= P.batch) continue;
+        auto total = [&](int rr) {
+          float lo = 0.0f, hi = 0.0f;
+#pragma unroll
+          for (int w = 0; w < CW; ++w) {
+            lo += red[(w * R + rr) * 4 + 2 * b];
+            hi += red[(w * R + rr) * 4 + 2 * b + 1];
+          }
+          return fmaf(hi, 65536.0f, lo) * A_SCALE;
+        };
+        const float v = total(row);
+        if (EPI == EPI_STORE) {
+          P.y[(size_t)b * P.ldy + vrow] = v;
+        } else if (EPI == EPI_RESIDUAL) {
+          float *dst = P.y + (size_t)b * P.ldy + vrow;
+          *dst = __fadd_rn(*dst, v);
+        } else {
+          P.y[(size_t)b * P.ldy + vrow] = swiglu(v, total(row + 16));
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+    }
+    if (++c == n_chunks) {
+      c = 0;
+      ++grp;
+    }
+    if (++stage == stages) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+cudaError_t make_map(CUtensorMap *map, const uint8_t *w, int rows, size_t row_bytes, int pitch) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return cudaErrorNotSupported;
+  const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 8), (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)(pitch / 8), (cuuint32_t)BOXR};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t *>(w), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+template <int QT, int EPI>
+cudaError_t launch_t(const GemvI8Args &a, const LaunchCfg &cfg) {
+  using G = Geo<QT>;
+  Params P{};
+  for (int i = 0; i < 3; ++i) P.seg_rows[i] = a.seg_rows[i];
+  P.nseg = a.nseg;
+  if (EPI == EPI_SWIGLU) {
+    P.n_rows = a.seg_rows[0];
+  } else {
+    P.n_rows = 0;
+    for (int i = 0; i < a.nseg; ++i) P.n_rows += a.seg_rows[i];
+  }
+  P.kb = a.k / 32;
+  P.x = a.x;
+  P.ldx = a.ldx;
+  P.col_map = a.col_map;
+  P.norm_w = a.norm_w;
+  P.eps = a.eps;
+  P.batch = a.batch;
+  P.y = a.y;
+  P.ldy = a.ldy;
+  P.status = cfg.status;
+  const int sms = cfg.sm_count > 0 ? cfg.sm_count : 148;
+  const int boxes = (P.n_rows + BOXR - 1) / BOXR;
+  P.rows_per_cta = ((boxes + sms - 1) / sms) * BOXR;
+  const int grid = (P.n_rows + P.rows_per_cta - 1) / P.rows_per_cta;
+  const int S = 4 * a.batch;
+  const int fixed = 128 + CW * R * 4 * 4 + ((P.kb * S * 32 + 127) & ~127) + ((P.kb * a.batch * 4 + 127) & ~127);
+  const int stage_bytes = R * G::RS;
+  int stages = (SMEM_LIMIT - fixed) / stage_bytes;
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  if (stages < 2) return cudaErrorInvalidConfiguration;
+  P.stages = stages;
+  const size_t smem = (size_t)fixed + (size_t)stages * stage_bytes;
+
+  alignas(64) CUtensorMap maps[3];
+  const size_t row_bytes = (size_t)P.kb * G::BB;
+  for (int i = 0; i < 3; ++i) {
+    const int src = i < a.nseg ? i : 0;
+    cudaError_t e = make_map(&maps[i], a.w[src], a.seg_rows[src], row_bytes, G::RS);
+    if (e != cudaSuccess) return e;
+  }
+  auto kernel = qgemv_i8_kernel<QT, EPI>;
+  static bool attr_done = false;  // per instantiation
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+    if (e != cudaSuccess) return e;
+    attr_done = true;
+  }
+  cudaLaunchConfig_t lc{};
+  lc.gridDim = dim3((unsigned)grid);
+  lc.blockDim = dim3(THREADS);
+  lc.dynamicSmemBytes = smem;
+  lc.stream = cfg.stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = cfg.pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&lc, kernel, maps[0], maps[1], maps[2], P);
+}
+
+template <int QT>
+cudaError_t launch_e(const GemvI8Args &a, const LaunchCfg &cfg) {
+  switch (a.epi) {
+    case EPI_STORE: return launch_t<QT, EPI_STORE>(a, cfg);
+    case EPI_RESIDUAL: return launch_t<QT, EPI_RESIDUAL>(a, cfg);
+    case EPI_SWIGLU: return launch_t<QT, EPI_SWIGLU>(a, cfg);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace
+
+bool qgemv_i8_supported(int k, int batch) {
+  // resident activations: digits (4 bytes per element and batch row) + block scales must leave
+  // room for at least three weight stages
+  return k > 0 && k % 256 == 0 && batch >= 1 && batch <= 2 && (size_t)k * 4 * batch <= 120 * 1024;
+}
+
+cudaError_t launch_qgemv_i8(const GemvI8Args &a, const LaunchCfg &cfg) {
+  if (!qgemv_i8_supported(a.k, a.batch) || a.nseg < 1 || a.nseg > 3 || !a.x || !a.y) return cudaErrorInvalidValue;
+  if (a.epi == EPI_SWIGLU && (a.nseg != 2 || a.seg_rows[0] != a.seg_rows[1])) return cudaErrorInvalidValue;
+  for (int i = 0; i + 1 < a.nseg; ++i)
+    if (a.epi != EPI_SWIGLU && a.seg_rows[i] % BOXR) return cudaErrorInvalidValue;
+  for (int i = 0; i < a.nseg; ++i)
+    if ((reinterpret_cast<uintptr_t>(a.w[i]) & 15) != 0) return cudaErrorInvalidValue;
+  if (a.type == RG_TYPE_Q4_0) return launch_e<RG_TYPE_Q4_0>(a, cfg);
+  if (a.type == RG_TYPE_Q8_0) return launch_e<RG_TYPE_Q8_0>(a, cfg);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace rg

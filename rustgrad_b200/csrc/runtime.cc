@@ -391,9 +391,147 @@ static int32_t tp_reduce_add(rg_session *s, int ncols) {
   return RG_OK;
 }
 
+// True when every projection of the model can run the integer tensor-core GEMV at this width.
+static bool small_batch_path(const rg_session *s, int ncols) {
+  if (ncols > 2 || s->opt.reserved[0] == 1) return false;  // reserved[0] == 1: force the general path (tests)
+  const int d = s->cfg.d_model, qw = s->heads_l * s->cfg.head_dim;
+  if (!qgemv_i8_supported(d, ncols) || !qgemv_i8_supported(qw, ncols) || !qgemv_i8_supported(s->ffn_l, ncols)) return false;
+  for (const LayerW &W : s->layers) {
+    if (!W.q.packed() || W.k.type != W.q.type || W.v.type != W.q.type || !W.o.packed() || !W.gate.packed() ||
+        W.up.type != W.gate.type || !W.down.packed())
+      return false;
+  }
+  return s->head->packed();
+}
+
+static int32_t gemv_i8(rg_session *s, const DevTensor *const *w, int n, const float *x, int ldx, const int32_t *col_map,
+                       const float *norm_w, int batch, int epi, float *y, int ldy, const LaunchCfg &L) {
+  GemvI8Args a;
+  a.type = w[0]->type;
+  a.nseg = n;
+  for (int i = 0; i < n; ++i) {
+    a.w[i] = w[i]->d;
+    a.seg_rows[i] = (int)w[i]->rows;
+  }
+  a.k = (int)w[0]->cols;
+  a.x = x;
+  a.ldx = ldx;
+  a.col_map = col_map;
+  a.norm_w = norm_w;
+  a.eps = s->cfg.norm_eps;
+  a.batch = batch;
+  a.epi = epi;
+  a.y = y;
+  a.ldy = ldy;
+  prof_mark(s, PROF_GEMV);
+  RG_LAUNCH(s, launch_qgemv_i8(a, L));
+  return RG_OK;
+}
+
+// Decode forward for one or two columns: RMSNorm and activation packing live in the GEMV
+// prologues, so a layer is seven launches (QKV, RoPE+append, attention split, combine, O, gate/up
+// with SwiGLU, down).
+static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool advance) {
+  const rg_llama_config &c = s->cfg;
+  const int d = c.d_model, hd = c.head_dim;
+  const int qw = s->heads_l * hd, kw = s->kv_l * hd, qkv_w = qw + 2 * kw;
+  Ctrl *ctl = s->d_ctrl;
+  LaunchCfg L = lcfg(s);
+  LaunchCfg plain = L;
+  plain.pdl = false;
+  const bool tp = s->tp_world > 1;
+  int32_t rc;
+  prof_mark(s, PROF_OTHER);
+  RG_LAUNCH(s, launch_row_gather(s->token_embd.type, s->token_embd.d, d, ctl->tokens, ncols, s->x, d, plain));
+  for (int l = 0; l < c.n_layers; ++l) {
+    const LayerW &W = s->layers[(size_t)l];
+    const DevTensor *qkvw[3] = {&W.q, &W.k, &W.v};
+    // the first GEMV of a layer follows a collective (library kernel) under tensor parallelism
+    if ((rc = gemv_i8(s, qkvw, 3, s->x, d, nullptr, reinterpret_cast<const float *>(W.attn_norm.d), ncols, EPI_STORE, s->qkv,
+                      qkv_w, (tp && l > 0) ? plain : L)))
+      return rc;
+    prof_mark(s, PROF_ATTN);
+    RopeArgs ra;
+    ra.qkv = s->qkv;
+    ra.cols = ncols;
+    ra.heads = s->heads_l;
+    ra.kv_heads = s->kv_l;
+    ra.hd = hd;
+    ra.ctx = s->ctx;
+    ra.col_seq = ctl->seq;
+    ra.col_pos = ctl->pos;
+    ra.cos_t = s->cos_t;
+    ra.sin_t = s->sin_t;
+    ra.q_out = s->q_rot;
+    ra.k_cache = s->k_cache[(size_t)l];
+    ra.v_cache = s->v_cache[(size_t)l];
+    ra.kv_f32 = s->kv_f32;
+    RG_LAUNCH(s, launch_rope_append(ra, L));
+    AttnArgs aa;
+    aa.q = s->q_rot;
+    aa.k_cache = ra.k_cache;
+    aa.v_cache = ra.v_cache;
+    aa.kv_f32 = s->kv_f32;
+    aa.cols = ncols;
+    aa.heads = s->heads_l;
+    aa.kv_heads = s->kv_l;
+    aa.hd = hd;
+    aa.ctx = s->ctx;
+    aa.col_seq = ctl->seq;
+    aa.col_pos = ctl->pos;
+    aa.scratch = s->attn_scratch;
+    aa.out_f32 = s->attn_f32;
+    RG_LAUNCH(s, launch_attention(aa, L));
+    if (s->family_mask & (1u << PROF_ATTN)) s->launches_in_step++;  // split + combine
+    const DevTensor *ow[1] = {&W.o};
+    if (tp) {
+      if ((rc = gemv_i8(s, ow, 1, s->attn_f32, qw, nullptr, nullptr, ncols, EPI_STORE, s->partial, d, L))) return rc;
+      if ((rc = tp_reduce_add(s, ncols))) return rc;
+    } else if ((rc = gemv_i8(s, ow, 1, s->attn_f32, qw, nullptr, nullptr, ncols, EPI_RESIDUAL, s->x, d, L))) {
+      return rc;
+    }
+    const DevTensor *guw[2] = {&W.gate, &W.up};
+    if ((rc = gemv_i8(s, guw, 2, s->x, d, nullptr, reinterpret_cast<const float *>(W.ffn_norm.d), ncols, EPI_SWIGLU, s->h_f32,
+                      s->ffn_l, tp ? plain : L)))
+      return rc;
+    const DevTensor *dw[1] = {&W.down};
+    if (tp) {
+      if ((rc = gemv_i8(s, dw, 1, s->h_f32, s->ffn_l, nullptr, nullptr, ncols, EPI_STORE, s->partial, d, L))) return rc;
+      if ((rc = tp_reduce_add(s, ncols))) return rc;
+    } else if ((rc = gemv_i8(s, dw, 1, s->h_f32, s->ffn_l, nullptr, nullptr, ncols, EPI_RESIDUAL, s->x, d, L))) {
+      return rc;
+    }
+  }
+  if (n_logit_cols > 0) {
+    const DevTensor *hw[1] = {s->head};
+    const bool split_head = tp && s->head == &s->output;
+    float *dst = split_head ? s->logits_l : s->logits;
+    const int ld = split_head ? s->vocab_l : c.vocab;
+    if ((rc = gemv_i8(s, hw, 1, s->x, d, ctl->logit_cols, reinterpret_cast<const float *>(s->output_norm.d), n_logit_cols,
+                      EPI_STORE, dst, ld, tp ? plain : L)))
+      return rc;
+    LaunchCfg am = L;
+    prof_mark(s, PROF_OTHER);
+    if (split_head && (s->family_mask & (1u << PROF_OTHER))) {
+      std::string err;
+      if ((rc = comm_group_start(&err))) return fail(rc, err);
+      for (int col = 0; col < n_logit_cols; ++col)
+        if ((rc = comm_allgather_f32(&s->comm, s->logits_l + (size_t)col * s->vocab_l, s->logits + (size_t)col * c.vocab,
+                                     (size_t)s->vocab_l, s->stream, &err)))
+          return fail(rc, err);
+      if ((rc = comm_group_end(&err))) return fail(rc, err);
+      am.pdl = false;
+    }
+    RG_LAUNCH(s, launch_argmax(s->logits, c.vocab, c.vocab, n_logit_cols, s->d_ids, am));
+    if (advance) RG_LAUNCH(s, launch_advance(s->d_ids, ctl->tokens, ctl->pos, s->d_history, &ctl->step, ncols, L));
+  }
+  return RG_OK;
+}
+
 // One forward over `ncols` columns described by the device control block.  n_logit_cols columns
 // (indices in ctrl.logit_cols) get logits + greedy ids; 0 skips the head (non-final prefill chunk).
 static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance) {
+  if (small_batch_path(s, ncols)) return forward_small(s, ncols, n_logit_cols, advance);
   const rg_llama_config &c = s->cfg;
   const int d = c.d_model, hd = c.head_dim;
   const int qw = s->heads_l * hd, kw = s->kv_l * hd, qkv_w = qw + 2 * kw;

@@ -82,6 +82,7 @@ class CudaSessionTarget:
     nccl_id: bytes = b""
     disable_graph: bool = False
     disable_pdl: bool = False
+    general_path_only: bool = False  # never take the fused small-batch decode path (tests)
     _opts: Options = field(default=None, repr=False)
 
     def options(self) -> Options:
@@ -89,6 +90,7 @@ class CudaSessionTarget:
         o.device, o.max_batch, o.max_context = self.device, self.max_batch, self.max_context
         o.kv_f32, o.tp_rank, o.tp_world = int(self.kv_f32), self.tp_rank, self.tp_world
         o.disable_graph, o.disable_pdl = int(self.disable_graph), int(self.disable_pdl)
+        o.reserved[0] = int(self.general_path_only)
         if self.tp_world > 1:
             if len(self.nccl_id) != 128:
                 raise InvalidArgument(1, "tensor parallelism needs the 128-byte NCCL id of rank 0")  # noqa: F821

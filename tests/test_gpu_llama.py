@@ -126,6 +126,14 @@ def test_q4_0_body_with_explicit_q8_0_head():
     oracle.reset()
     s.reset_sequence()
     assert_logits_close(s.prefill_ids(prompt), oracle.forward(prompt))
+    # the fused small-batch decode path (integer GEMV) and the general path agree step by step
+    g = session.LlamaCudaPlan.from_tensors(cfg, tensors, session.CudaSessionTarget(kv_f32=True, general_path_only=True)).prepare()
+    g.prefill_ids(prompt)
+    for tok in want_ids[:6]:
+        a, b, w = s.run_token(tok), g.run_token(tok), oracle.forward([tok])
+        assert_logits_close(a, w)
+        assert_logits_close(b, w)
+        assert np.abs(a - b).max() <= 1e-4
 
 
 def test_stop_on_eos_and_last_token_not_fed_back(tiny):
