@@ -35,13 +35,17 @@ constexpr int BOXR = 8;   // rows per TMA box
 constexpr int CW = 14;    // consumer warps
 constexpr int MAX_STAGES = 6;
 constexpr int THREADS = (CW + 1) * 32;
+// One CTA per SM.  (Letting two CTAs share an SM so that the next kernel could move in early under
+// programmatic dependent launch was measured slower: freed slots fill unevenly and some SMs end up
+// with two CTAs of the same kernel.)
 constexpr int SMEM_LIMIT = 227 * 1024;
+constexpr int SMEM_FULL = 227 * 1024;
 
 template <int QT>
 struct Geo {
   static constexpr bool Q4 = (QT == RG_TYPE_Q4_0);
   static constexpr int BB = Q4 ? 18 : 34;
-  static constexpr int KC = Q4 ? 56 : 40;  // blocks per stage; pitch 1008 / 1360 bytes (28 / 20 banks)
+  static constexpr int KC = Q4 ? 56 : 40;  // blocks per stage; pitch 1008 / 1360 bytes (28 / 20 banks mod 32)
   static constexpr int RS = KC * BB;
   static_assert(RS % 16 == 0 && (BOXR * RS) % 128 == 0 && RS / 8 <= 256, "TMA box geometry");
 };
@@ -244,7 +248,13 @@ __global__ void __launch_bounds__(THREADS, 1)
     if (P.norm_w) {
       // y = (x * (1 / sqrt(mean(x^2) + eps))) * w, every step rounded to f32 (layer.rs:423-443)
       float ss = 0.0f;
-      for (int i = ctid; i < P.kb * 32; i += CW * 32) ss = fmaf(xr[i], xr[i], ss);
+      for (int i = ctid; i < P.kb * 8; i += CW * 32) {
+        const float4 f = __ldg(reinterpret_cast<const float4 *>(xr) + i);
+        ss = fmaf(f.x, f.x, ss);
+        ss = fmaf(f.y, f.y, ss);
+        ss = fmaf(f.z, f.z, ss);
+        ss = fmaf(f.w, f.w, ss);
+      }
       ss = warp_sum(ss);
       if (lane == 0) red[warp] = ss;
       asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
@@ -255,32 +265,47 @@ __global__ void __launch_bounds__(THREADS, 1)
       inv = __frcp_rn(__fsqrt_rn(__fadd_rn(mean, P.eps)));
       asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
     }
-    for (int kb = warp; kb < P.kb; kb += CW) {
-      float v = xr[kb * 32 + lane];
-      if (P.norm_w) v = __fmul_rn(__fmul_rn(v, inv), P.norm_w[kb * 32 + lane]);
-      const float m = warp_max(fabsf(v));
+    // Eight lanes per block, four consecutive elements per lane (= one 32-bit word of each digit
+    // plane in the fragment layout); a warp converts four blocks per iteration.
+    const int quad = lane & 7;
+#pragma unroll 4
+    for (int kb = warp * 4 + (lane >> 3); kb < P.kb; kb += CW * 4) {
+      const float4 f = __ldg(reinterpret_cast<const float4 *>(xr + kb * 32) + quad);
+      float v[4] = {f.x, f.y, f.z, f.w};
+      if (P.norm_w) {
+        const float4 w = __ldg(reinterpret_cast<const float4 *>(P.norm_w + kb * 32) + quad);
+        v[0] = __fmul_rn(__fmul_rn(v[0], inv), w.x);
+        v[1] = __fmul_rn(__fmul_rn(v[1], inv), w.y);
+        v[2] = __fmul_rn(__fmul_rn(v[2], inv), w.z);
+        v[3] = __fmul_rn(__fmul_rn(v[3], inv), w.w);
+      }
+      float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+      if (!(fabsf(v[0] + v[1] + v[2] + v[3]) <= 3.0e38f)) m = __uint_as_float(0x7f800000u);  // fmaxf drops NaN: keep it visible
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
       const uint32_t E = __float_as_uint(m) >> 23;  // biased exponent of the block maximum (m >= 0)
       float s = 0.0f;
-      int X = 0;
+      uint32_t Y[4] = {0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u};
       if (E >= 40u && E < 255u) {
-        s = __uint_as_float((E - 29u) << 23);                     // 2^(floor(log2 m) - 29)
-        X = __float2int_rn(v * __uint_as_float((283u - E) << 23));  // |X| < 2^30
+        s = __uint_as_float((E - 29u) << 23);  // 2^(floor(log2 m) - 29), so |X| < 2^30
+        const float up = __uint_as_float((283u - E) << 23);
+        // X + 0x80808080 turns the four signed base-256 digits of X into unsigned bytes (digit + 128)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) Y[i] = (uint32_t)__float2int_rn(v[i] * up) + 0x80808080u;
       } else if (E == 255u) {  // inf / NaN input must stay visible in the result
         s = __uint_as_float(0x7fc00000u);
-        X = 1;
+        Y[0] = 0x80808081u;
       }
-      // four signed base-256 digits
-      const int d0 = (int)(int8_t)(X & 0xff);
-      const int x1 = (X - d0) >> 8;
-      const int d1 = (int)(int8_t)(x1 & 0xff);
-      const int x2 = (x1 - d1) >> 8;
-      const int d2 = (int)(int8_t)(x2 & 0xff);
-      const int d3 = (x2 - d2) >> 8;
-      xs[digit_offset(S, kb, 4 * b + 0, lane)] = (uint8_t)d0;
-      xs[digit_offset(S, kb, 4 * b + 1, lane)] = (uint8_t)d1;
-      xs[digit_offset(S, kb, 4 * b + 2, lane)] = (uint8_t)d2;
-      xs[digit_offset(S, kb, 4 * b + 3, lane)] = (uint8_t)d3;
-      if (lane == 0) sb[kb * P.batch + b] = s;
+      // 4x4 byte transpose: word d = digit d of the lane's four elements, then back to signed
+      const uint32_t t0 = prmt(Y[0], Y[1], 0x5140u), t1 = prmt(Y[2], Y[3], 0x5140u);
+      const uint32_t t2 = prmt(Y[0], Y[1], 0x7362u), t3 = prmt(Y[2], Y[3], 0x7362u);
+      uint32_t *dst = reinterpret_cast<uint32_t *>(xs + digit_offset(S, kb, 4 * b, quad * 4));
+      const int plane = 32 / 4;  // words between consecutive columns of a block
+      dst[0 * plane] = prmt(t0, t1, 0x5410u) ^ 0x80808080u;
+      dst[1 * plane] = prmt(t0, t1, 0x7632u) ^ 0x80808080u;
+      dst[2 * plane] = prmt(t2, t3, 0x5410u) ^ 0x80808080u;
+      dst[3 * plane] = prmt(t2, t3, 0x7632u) ^ 0x80808080u;
+      if (quad == 0) sb[kb * P.batch + b] = s;
     }
   }
   asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
@@ -448,6 +473,7 @@ cudaError_t launch_t(const GemvI8Args &a, const LaunchCfg &cfg) {
   const int fixed = 128 + CW * R * 4 * 4 + ((P.kb * S * 32 + 127) & ~127) + ((P.kb * a.batch * 4 + 127) & ~127);
   const int stage_bytes = R * G::RS;
   int stages = (SMEM_LIMIT - fixed) / stage_bytes;
+  if (stages < 3) stages = (SMEM_FULL - fixed) / stage_bytes;  // too large to share an SM: take it whole
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages < 2) return cudaErrorInvalidConfiguration;
   P.stages = stages;
@@ -463,7 +489,9 @@ cudaError_t launch_t(const GemvI8Args &a, const LaunchCfg &cfg) {
   auto kernel = qgemv_i8_kernel<QT, EPI>;
   static bool attr_done = false;  // per instantiation
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_FULL);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
