@@ -199,6 +199,14 @@ int32_t rg_b200_qmatmul(int32_t device, int32_t ggml_type, const uint8_t *weight
 int32_t rg_b200_row_gather(int32_t device, int32_t ggml_type, const uint8_t *weight, uint64_t rows,
                            uint64_t cols, const int64_t *indices, size_t count, float *out);
 
+/* The same product for many activation rows on the tcgen05 tensor cores (prefill): activations are
+ * rounded to bf16 and the weights are dequantised to bf16 tiles, accumulation is f32
+ * (the per-layer linear of src/models/transformer/layer.rs:445-448 for a whole prompt chunk).
+ * iters > 0 additionally repeats the launch `iters` times between CUDA events and stores the mean
+ * kernel time in kernel_ms (nullable). */
+int32_t rg_b200_qgemm(int32_t device, int32_t ggml_type, const uint8_t *weight, uint64_t n, uint64_t k,
+                      const float *activation, uint64_t m, int32_t iters, float *out, float *kernel_ms);
+
 /* One decode token of scaled_dot_product_attention with GQA (src/ir/attention.rs:946-981,1157-1240;
  * mask `col <= past + row` of src/models/transformer/layer.rs:374-380 for a single new row): q is
  * [heads, head_dim] f32, already rotated; keys / values are caches [kv_heads, n_pos, head_dim] of

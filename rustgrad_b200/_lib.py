@@ -44,7 +44,7 @@ EXPORTS = [
     "rg_b200_session_destroy", "rg_b200_position", "rg_b200_max_context", "rg_b200_vocab_size", "rg_b200_is_full",
     "rg_b200_reset_sequence", "rg_b200_prefill", "rg_b200_decode", "rg_b200_generate_greedy", "rg_b200_decode_loop", "rg_b200_decode_profile",
     "rg_b200_report", "rg_b200_session_stream", "rg_b200_nccl_unique_id", "rg_b200_dequantize", "rg_b200_qmatmul",
-    "rg_b200_row_gather", "rg_b200_qmatmul_bench", "rg_b200_attention_decode", "rg_b200_attention_decode_noalloc",
+    "rg_b200_row_gather", "rg_b200_qmatmul_bench", "rg_b200_qgemm", "rg_b200_attention_decode", "rg_b200_attention_decode_noalloc",
 ]
 
 _lib = None
@@ -102,6 +102,7 @@ def load() -> C.CDLL:
     L.rg_b200_qmatmul.argtypes = [C.c_int32, C.c_int32, u8p, C.c_uint64, C.c_uint64, f32p, C.c_uint64, f32p]
     L.rg_b200_row_gather.argtypes = [C.c_int32, C.c_int32, u8p, C.c_uint64, C.c_uint64, C.POINTER(C.c_int64),
                                      C.c_size_t, f32p]
+    L.rg_b200_qgemm.argtypes = [C.c_int32, C.c_int32, u8p, C.c_uint64, C.c_uint64, f32p, C.c_uint64, C.c_int32, f32p, f32p]
     L.rg_b200_attention_decode_noalloc.argtypes = [vp, vp, vp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                                    C.c_int32, vp, vp, C.c_int32]
     L.rg_b200_attention_decode.argtypes = [C.c_int32, f32p, vp, vp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,

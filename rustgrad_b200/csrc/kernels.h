@@ -57,6 +57,24 @@ struct GemvI8Args {
 bool qgemv_i8_supported(int k, int batch);
 cudaError_t launch_qgemv_i8(const GemvI8Args &a, const LaunchCfg &cfg);
 
+// tcgen05 GEMM for many tokens: out[m][n] = x[m][k] (bf16) . W[n][k]^T with W in Q4_0 / Q8_0 blocks
+// dequantised to bf16 tiles; f32 accumulation in TMEM.  splits > 1 divides K over blockIdx.z and
+// writes one partial result per split (split_stride floats apart) for a later reduction.
+struct QGemmArgs {
+  int type = 0;
+  const uint8_t *w = nullptr;
+  int n = 0, k = 0;
+  const void *x_bf16 = nullptr;  // [m][ldx] bf16, 16-byte aligned rows
+  int ldx = 0;
+  int m = 0;
+  float *out = nullptr;
+  int ldc = 0;
+  int splits = 1;
+  size_t split_stride = 0;
+};
+cudaError_t launch_qgemm_tc(const QGemmArgs &a, const LaunchCfg &cfg);
+cudaError_t launch_to_bf16(const float *x, int ldx, int k, int rows, void *y, int ldy, const LaunchCfg &cfg);
+
 // Dense (F32/F16) weight GEMV for tensors the block formats cannot hold (K % 32 != 0) or that a
 // file stores dense.  x is plain f32 [batch, ldx]; same epilogues (EPI_SWIGLU unsupported).
 struct DenseGemvArgs {

@@ -233,6 +233,60 @@ int32_t rg_b200_row_gather(int32_t device, int32_t type, const uint8_t *weight, 
   return RG_OK;
 }
 
+int32_t rg_b200_qgemm(int32_t device, int32_t type, const uint8_t *weight, uint64_t n, uint64_t k, const float *activation,
+                      uint64_t m, int32_t iters, float *out, float *kernel_ms) {
+  if (!weight || !activation || !out) return fail(RG_INVALID_ARGUMENT, "null argument");
+  if (type != RG_TYPE_Q4_0 && type != RG_TYPE_Q8_0) return fail(RG_UNSUPPORTED_TYPE, "the tensor-core GEMM takes Q4_0 or Q8_0 weights");
+  size_t wbytes;
+  int32_t rc = check_weight(type, n, k, &wbytes);
+  if (rc) return rc;
+  if (n == 0 || m == 0) return RG_OK;
+  if (k == 0 || k % 256) return fail(RG_UNSUPPORTED_GEOMETRY, "packed weights need K to be a multiple of 256");
+  if ((rc = scan_scales(type, weight, wbytes))) return rc;
+  Scope sc;
+  LaunchCfg cfg;
+  int *d_status;
+  if ((rc = open_scope(device, &sc, &cfg, &d_status))) return rc;
+  uint8_t *d_w, *d_xb;
+  float *d_x, *d_y;
+  OP_CUDA(sc.alloc(&d_w, wbytes));
+  OP_CUDA(sc.alloc(&d_x, sizeof(float) * m * k));
+  OP_CUDA(sc.alloc(&d_xb, 2 * m * k));
+  OP_CUDA(sc.alloc(&d_y, sizeof(float) * m * n));
+  OP_CUDA(cudaMemcpyAsync(d_w, weight, wbytes, cudaMemcpyHostToDevice, sc.stream));
+  OP_CUDA(cudaMemcpyAsync(d_x, activation, sizeof(float) * m * k, cudaMemcpyHostToDevice, sc.stream));
+  OP_CUDA(launch_to_bf16(d_x, (int)k, (int)k, (int)m, d_xb, (int)k, cfg));
+  QGemmArgs a;
+  a.type = type;
+  a.w = d_w;
+  a.n = (int)n;
+  a.k = (int)k;
+  a.x_bf16 = d_xb;
+  a.ldx = (int)k;
+  a.m = (int)m;
+  a.out = d_y;
+  a.ldc = (int)n;
+  OP_CUDA(launch_qgemm_tc(a, cfg));  // first launch also serves as warm-up
+  const int reps = iters > 0 ? iters : 0;
+  OP_CUDA(cudaEventCreate(&sc.e0));
+  OP_CUDA(cudaEventCreate(&sc.e1));
+  OP_CUDA(cudaEventRecord(sc.e0, sc.stream));
+  for (int i = 0; i < reps; ++i) OP_CUDA(launch_qgemm_tc(a, cfg));
+  OP_CUDA(cudaEventRecord(sc.e1, sc.stream));
+  int status = 0;
+  OP_CUDA(cudaMemcpyAsync(out, d_y, sizeof(float) * m * n, cudaMemcpyDeviceToHost, sc.stream));
+  OP_CUDA(cudaMemcpyAsync(&status, d_status, sizeof(int), cudaMemcpyDeviceToHost, sc.stream));
+  OP_CUDA(cudaStreamSynchronize(sc.stream));
+  if (status == 1) return fail(RG_TIMEOUT, "a bounded device-side wait gave up");
+  if (status) return fail(RG_CUDA_ERROR, "device status " + std::to_string(status));
+  if (kernel_ms) {
+    float ms = 0.0f;
+    OP_CUDA(cudaEventElapsedTime(&ms, sc.e0, sc.e1));
+    *kernel_ms = reps ? ms / (float)reps : 0.0f;
+  }
+  return RG_OK;
+}
+
 int32_t rg_b200_attention_decode(int32_t device, const float *q, const void *keys, const void *values, int32_t heads,
                                  int32_t kv_heads, int32_t head_dim, int32_t n_pos, int32_t kv_f32, float *out) {
   if (!q || !keys || !values || !out) return fail(RG_INVALID_ARGUMENT, "null argument");
