@@ -10,8 +10,10 @@
 //     the accumulator lives in TMEM (128 lanes x TN f32 columns).
 //   * warp 0: TMA producer of the activation tiles (tiled 2-D copy, 128-byte swizzle).
 //   * warp 1: allocates TMEM, issues tcgen05.mma from one thread, commits to mbarriers.
-//   * warps 2-5: one thread per weight row reads the row's two raw blocks of the stage from
-//     global memory (L2 resident across token tiles), expands nibbles to exact bf16 integers with
+//   * warp 0 also streams the raw block bytes of the 128 weight rows, 256 columns (8 blocks) at a
+//     time, into a small ring with a second tiled 2-D TMA map, so no thread waits on global memory.
+//   * warps 2-5: one thread per weight row reads the row's two raw blocks of the stage from that
+//     ring, expands nibbles to exact bf16 integers with
 //     the 128+n bit pattern and applies the block scale with one bf16x2 FMA per two weights, and
 //     writes the 128-byte row into the K-major / 128-byte-swizzled A tile; afterwards the same
 //     warps read the accumulator with tcgen05.ld and store it.
@@ -30,7 +32,8 @@ namespace {
 
 constexpr int TM = 128;     // weight rows per tile (MMA M)
 constexpr int KSTEP = 64;   // elements per stage (128 bytes of bf16: one swizzle row)
-constexpr int NS = 4;       // ring depth
+constexpr int RAW_STEPS = 4;  // 64-element stages per raw weight tile (256 columns = 8 blocks)
+constexpr int RAW_NS = 2;     // raw ring depth
 constexpr int THREADS = 192;
 constexpr int A_BYTES = TM * KSTEP * 2;
 
@@ -129,23 +132,29 @@ __device__ __forceinline__ void q8_block_to_bf16(uint32_t dbits16, const uint32_
 }
 
 template <int QT, int TN>
-__global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
+__global__ void __launch_bounds__(THREADS, 1)
+    qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const Params P) {
   constexpr bool Q4 = (QT == RG_TYPE_Q4_0);
   constexpr int BB = Q4 ? 18 : 34;
+  constexpr int NS = TN > 128 ? 3 : 4;  // operand ring depth
   constexpr int B_BYTES = TN * KSTEP * 2;
+  constexpr int RAW_ROW = 8 * BB;  // bytes of one weight row in a raw tile (144 / 272)
+  constexpr int RAW_BYTES = TM * RAW_ROW;
   constexpr int TMEM_COLS = TN < 32 ? 32 : TN;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t *a_ring = smem;
   uint8_t *b_ring = smem + NS * A_BYTES;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(b_ring + NS * B_BYTES);
-  uint64_t *b_full = bars, *a_full = bars + NS, *slot_free = bars + 2 * NS, *acc_done = bars + 3 * NS;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * NS + 1);
+  uint8_t *raw_ring = b_ring + NS * B_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(raw_ring + RAW_NS * RAW_BYTES);
+  uint64_t *b_full = bars, *a_full = bars + NS, *slot_free = bars + 2 * NS;
+  uint64_t *raw_full = bars + 3 * NS, *raw_free = raw_full + RAW_NS, *acc_done = raw_free + RAW_NS;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_done + 1);
   volatile int *dead = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * TM, tok0 = blockIdx.y * TN;
-  const int step0 = blockIdx.z * P.k_steps;
+  const int step0 = blockIdx.z * P.k_steps;  // k_steps is a multiple of RAW_STEPS
   const int nsteps = min(P.k_steps, P.k / KSTEP - step0);
 
   if (threadIdx.x == 0) {
@@ -153,6 +162,10 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(const __grid_const
       mbar_init(&b_full[s], 1);
       mbar_init(&a_full[s], 128);
       mbar_init(&slot_free[s], 1);
+    }
+    for (int s = 0; s < RAW_NS; ++s) {
+      mbar_init(&raw_full[s], 1);
+      mbar_init(&raw_free[s], 128);
     }
     mbar_init(acc_done, 1);
     *dead = 0;
@@ -171,9 +184,16 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(const __grid_const
   pdl_wait();
 
   if (warp == 0) {
-    // ---------------------------------------------------------------- activation tiles by TMA
+    // ---------------------------------------------------------------- TMA: raw weight tiles and activation tiles
     if (lane == 0) {
       for (int i = 0; i < nsteps; ++i) {
+        if (i % RAW_STEPS == 0) {
+          const int j = i / RAW_STEPS, rs = j % RAW_NS;
+          if (j >= RAW_NS) mbar_wait_bounded(&raw_free[rs], (uint32_t)((j / RAW_NS - 1) & 1), dead, P.status);
+          mbar_expect_tx(&raw_full[rs], (uint32_t)RAW_BYTES);
+          // x in 8-byte elements; rows beyond the tensor arrive as zeros (zero scale, zero weights)
+          tma_tile_2d(raw_ring + rs * RAW_BYTES, &wmap, ((step0 + i) / RAW_STEPS) * (RAW_ROW / 8), n0, &raw_full[rs]);
+        }
         const int slot = i % NS;
         if (i >= NS) mbar_wait_bounded(&slot_free[slot], (uint32_t)((i / NS - 1) & 1), dead, P.status);
         mbar_expect_tx(&b_full[slot], (uint32_t)B_BYTES);
@@ -201,51 +221,47 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(const __grid_const
   } else {
     // ---------------------------------------------------------------- dequantisation: one weight row per thread
     const int r = threadIdx.x - 64;  // 0..127
-    const int wrow = n0 + r;
-    const bool live = wrow < P.n;
-    const size_t row_bytes = (size_t)(P.k / 32) * BB;
-    const uint32_t *src = reinterpret_cast<const uint32_t *>(P.w + (size_t)(live ? wrow : 0) * row_bytes + (size_t)step0 * 2 * BB);
     constexpr int WORDS = 2 * BB / 4;  // 9 or 17 words per stage and row
-    uint32_t raw[WORDS];
-    auto load_raw = [&](int i) {
-#pragma unroll
-      for (int j = 0; j < WORDS; ++j) raw[j] = live ? __ldg(src + (size_t)i * WORDS + j) : 0u;
-    };
-    if (nsteps > 0) load_raw(0);
     for (int i = 0; i < nsteps; ++i) {
       const int slot = i % NS;
+      const int j = i / RAW_STEPS, rs = j % RAW_NS, sub = i % RAW_STEPS;
+      if (sub == 0) mbar_wait_bounded(&raw_full[rs], (uint32_t)((j / RAW_NS) & 1), dead, P.status);
+      const uint32_t *src = reinterpret_cast<const uint32_t *>(raw_ring + rs * RAW_BYTES + r * RAW_ROW + sub * 2 * BB);
+      uint32_t raw[WORDS];
+#pragma unroll
+      for (int w = 0; w < WORDS; ++w) raw[w] = src[w];
       uint32_t vals[32];  // 64 bf16 of this row and stage, in k order
       if (Q4) {
         // pair layout: [d0 | q0 (16 bytes)] [d1 | q1 (16 bytes)], 2-byte scale in front of each block
         uint32_t q0[4], q1[4], lo[16], hi[16];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          q0[j] = __funnelshift_r(raw[j], raw[j + 1], 16);
-          q1[j] = raw[5 + j];
+        for (int w = 0; w < 4; ++w) {
+          q0[w] = __funnelshift_r(raw[w], raw[w + 1], 16);
+          q1[w] = raw[5 + w];
         }
         q4_block_to_bf16(raw[0] & 0xffffu, q0, lo);
         q4_block_to_bf16(raw[4] >> 16, q1, hi);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          vals[j] = lo[j];
-          vals[16 + j] = hi[j];
+        for (int w = 0; w < 16; ++w) {
+          vals[w] = lo[w];
+          vals[16 + w] = hi[w];
         }
       } else {
         uint32_t q0[8], q1[8], lo[16], hi[16];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          q0[j] = __funnelshift_r(raw[j], raw[j + 1], 16);
-          q1[j] = raw[9 + j];
+        for (int w = 0; w < 8; ++w) {
+          q0[w] = __funnelshift_r(raw[w], raw[w + 1], 16);
+          q1[w] = raw[9 + w];
         }
         q8_block_to_bf16(raw[0] & 0xffffu, q0, lo);
         q8_block_to_bf16(raw[8] >> 16, q1, hi);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          vals[j] = lo[j];
-          vals[16 + j] = hi[j];
+        for (int w = 0; w < 16; ++w) {
+          vals[w] = lo[w];
+          vals[16 + w] = hi[w];
         }
       }
-      if (i + 1 < nsteps) load_raw(i + 1);  // next stage's bytes travel while this one is written
+      if (sub == RAW_STEPS - 1 || i + 1 == nsteps) mbar_arrive(&raw_free[rs]);  // raw bytes are in registers now
       if (i >= NS) mbar_wait_bounded(&slot_free[slot], (uint32_t)((i / NS - 1) & 1), dead, P.status);
       uint8_t *row_dst = a_ring + slot * A_BYTES + r * 128;
 #pragma unroll
@@ -265,6 +281,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(const __grid_const
     if (nsteps > 0) {
 #pragma unroll 1
       for (int c0 = 0; c0 < TN; c0 += 16) {
+        if (tok0 + c0 >= P.m) break;
         uint32_t v[16];
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
         asm volatile(
@@ -274,9 +291,9 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(const __grid_const
             : "r"(taddr));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int tok = tok0 + c0 + j;
-          if (tok < P.m && orow < P.n) out[(size_t)tok * P.ldc + orow] = __uint_as_float(v[j]);
+        for (int w = 0; w < 16; ++w) {
+          const int tok = tok0 + c0 + w;
+          if (tok < P.m && orow < P.n) out[(size_t)tok * P.ldc + orow] = __uint_as_float(v[w]);
         }
       }
     }
@@ -308,28 +325,44 @@ template <int QT, int TN>
 cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
   EncodeFn fn = encode_fn();
   if (!fn) return cudaErrorNotSupported;
-  alignas(64) CUtensorMap xmap;
-  const cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
-  const cuuint64_t strides[1] = {(cuuint64_t)a.ldx * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)KSTEP, (cuuint32_t)TN};
+  constexpr int BB = (QT == RG_TYPE_Q4_0) ? 18 : 34;
+  constexpr int NS = TN > 128 ? 3 : 4;
+  constexpr int RAW_ROW = 8 * BB;
+  alignas(64) CUtensorMap xmap, wmap;
   const cuuint32_t elem[2] = {1, 1};
-  if (fn(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(a.x_bf16), dims, strides, box, elem,
-         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return cudaErrorInvalidValue;
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
+    const cuuint64_t strides[1] = {(cuuint64_t)a.ldx * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)KSTEP, (cuuint32_t)TN};
+    if (fn(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(a.x_bf16), dims, strides, box, elem,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return cudaErrorInvalidValue;
+  }
+  {
+    const size_t row_bytes = (size_t)(a.k / 32) * BB;
+    const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 8), (cuuint64_t)a.n};
+    const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)(RAW_ROW / 8), (cuuint32_t)TM};
+    if (fn(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t *>(a.w), dims, strides, box, elem,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return cudaErrorInvalidValue;
+  }
   Params P{};
   P.w = a.w;
   P.n = a.n;
   P.k = a.k;
   P.m = a.m;
   const int total_steps = a.k / KSTEP;
-  const int splits = a.splits < 1 ? 1 : a.splits;
-  P.k_steps = (total_steps + splits - 1) / splits;
+  int splits = a.splits < 1 ? 1 : a.splits;
+  P.k_steps = ((total_steps / RAW_STEPS + splits - 1) / splits) * RAW_STEPS;  // whole raw tiles per split
+  splits = (total_steps + P.k_steps - 1) / P.k_steps;
   P.out = a.out;
   P.ldc = a.ldc;
   P.split_stride = a.split_stride;
   P.status = cfg.status;
-  constexpr size_t smem = 1024 + NS * (A_BYTES + TN * KSTEP * 2) + (3 * NS + 1) * 8 + 16;
+  constexpr size_t smem = 1024 + NS * (A_BYTES + TN * KSTEP * 2) + RAW_NS * TM * RAW_ROW + (3 * NS + 2 * RAW_NS + 1) * 8 + 16;
   auto kernel = qgemm_tc_kernel<QT, TN>;
   static bool attr_done = false;  // per instantiation
   if (!attr_done) {
@@ -347,11 +380,12 @@ cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
   at[0].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = at;
   lc.numAttrs = cfg.pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&lc, kernel, xmap, P);
+  return cudaLaunchKernelEx(&lc, kernel, xmap, wmap, P);
 }
 
 template <int QT>
 cudaError_t launch_n(const QGemmArgs &a, const LaunchCfg &cfg) {
+  if (a.m > 128) return launch_t<QT, 256>(a, cfg);
   if (a.m > 64) return launch_t<QT, 128>(a, cfg);
   if (a.m > 32) return launch_t<QT, 64>(a, cfg);
   if (a.m > 16) return launch_t<QT, 32>(a, cfg);
@@ -369,7 +403,7 @@ __global__ void to_bf16_kernel(const float *x, int ldx, int k, __nv_bfloat16 *y,
 
 cudaError_t launch_qgemm_tc(const QGemmArgs &a, const LaunchCfg &cfg) {
   if (!a.w || !a.x_bf16 || !a.out || a.m < 1 || a.n < 1 || a.k < KSTEP || a.k % 256) return cudaErrorInvalidValue;
-  if ((reinterpret_cast<uintptr_t>(a.x_bf16) & 15) || (a.ldx * 2) % 16 || (reinterpret_cast<uintptr_t>(a.w) & 3))
+  if ((reinterpret_cast<uintptr_t>(a.x_bf16) & 15) || (a.ldx * 2) % 16 || (reinterpret_cast<uintptr_t>(a.w) & 15))
     return cudaErrorInvalidValue;
   if (a.type == RG_TYPE_Q4_0) return launch_n<RG_TYPE_Q4_0>(a, cfg);
   if (a.type == RG_TYPE_Q8_0) return launch_n<RG_TYPE_Q8_0>(a, cfg);
