@@ -74,6 +74,10 @@ struct QGemmArgs {
 };
 cudaError_t launch_qgemm_tc(const QGemmArgs &a, const LaunchCfg &cfg);
 cudaError_t launch_to_bf16(const float *x, int ldx, int k, int rows, void *y, int ldy, const LaunchCfg &cfg);
+// RMSNorm of `rows` token rows to the bf16 GEMM operand; SwiGLU of (gate, up) rows to bf16.
+cudaError_t launch_rmsnorm_bf16(const float *x, int ldx, const float *w, int d, float eps, int rows, void *y, int ldy,
+                                const LaunchCfg &cfg);
+cudaError_t launch_swiglu_bf16(const float *g, const float *u, int n, int ld, int rows, void *y, int ldy, const LaunchCfg &cfg);
 
 // Dense (F32/F16) weight GEMV for tensors the block formats cannot hold (K % 32 != 0) or that a
 // file stores dense.  x is plain f32 [batch, ldx]; same epilogues (EPI_SWIGLU unsupported).

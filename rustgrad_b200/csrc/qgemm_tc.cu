@@ -12,7 +12,7 @@
 //   * warp 1: allocates TMEM, issues tcgen05.mma from one thread, commits to mbarriers.
 //   * warp 0 also streams the raw block bytes of the 128 weight rows, 256 columns (8 blocks) at a
 //     time, into a small ring with a second tiled 2-D TMA map, so no thread waits on global memory.
-//   * warps 2-5: one thread per weight row reads the row's two raw blocks of the stage from that
+//   * warps 2-9: two threads per weight row, each reads the row's two raw blocks of the stage from that
 //     ring, expands nibbles to exact bf16 integers with
 //     the 128+n bit pattern and applies the block scale with one bf16x2 FMA per two weights, and
 //     writes the 128-byte row into the K-major / 128-byte-swizzled A tile; afterwards the same
@@ -34,7 +34,7 @@ constexpr int TM = 128;     // weight rows per tile (MMA M)
 constexpr int KSTEP = 64;   // elements per stage (128 bytes of bf16: one swizzle row)
 constexpr int RAW_STEPS = 4;  // 64-element stages per raw weight tile (256 columns = 8 blocks)
 constexpr int RAW_NS = 2;     // raw ring depth
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;  // TMA warp, MMA warp, eight dequantisation / epilogue warps
 constexpr int A_BYTES = TM * KSTEP * 2;
 
 struct Params {
@@ -160,12 +160,12 @@ __global__ void __launch_bounds__(THREADS, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(&b_full[s], 1);
-      mbar_init(&a_full[s], 128);
+      mbar_init(&a_full[s], 256);
       mbar_init(&slot_free[s], 1);
     }
     for (int s = 0; s < RAW_NS; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_free[s], 128);
+      mbar_init(&raw_free[s], 256);
     }
     mbar_init(acc_done, 1);
     *dead = 0;
@@ -219,55 +219,43 @@ __global__ void __launch_bounds__(THREADS, 1)
       umma_commit(acc_done);
     }
   } else {
-    // ---------------------------------------------------------------- dequantisation: one weight row per thread
-    const int r = threadIdx.x - 64;  // 0..127
-    constexpr int WORDS = 2 * BB / 4;  // 9 or 17 words per stage and row
+    // ---------------------------------------------------------------- dequantisation: one block (half of a
+    // stage's 64 columns) of one weight row per thread, two threads per row
+    const int tdq = threadIdx.x - 64;            // 0..255
+    const int r = tdq & 127, half = tdq >> 7;    // row of the tile, even / odd block of the stage
+    constexpr int QW = Q4 ? 4 : 8;               // quant words per block
     for (int i = 0; i < nsteps; ++i) {
       const int slot = i % NS;
       const int j = i / RAW_STEPS, rs = j % RAW_NS, sub = i % RAW_STEPS;
       if (sub == 0) mbar_wait_bounded(&raw_full[rs], (uint32_t)((j / RAW_NS) & 1), dead, P.status);
+      // pair layout: [d0 | q0] [d1 | q1] with a 2-byte scale in front of each block: the even block's
+      // quants straddle word boundaries (funnel shift), the odd block's are word aligned
       const uint32_t *src = reinterpret_cast<const uint32_t *>(raw_ring + rs * RAW_BYTES + r * RAW_ROW + sub * 2 * BB);
-      uint32_t raw[WORDS];
+      uint32_t q[QW], dbits, vals[16];  // 32 bf16 of this block, in k order
+      if (half == 0) {
+        uint32_t raw[QW + 1];
 #pragma unroll
-      for (int w = 0; w < WORDS; ++w) raw[w] = src[w];
-      uint32_t vals[32];  // 64 bf16 of this row and stage, in k order
-      if (Q4) {
-        // pair layout: [d0 | q0 (16 bytes)] [d1 | q1 (16 bytes)], 2-byte scale in front of each block
-        uint32_t q0[4], q1[4], lo[16], hi[16];
+        for (int w = 0; w <= QW; ++w) raw[w] = src[w];
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          q0[w] = __funnelshift_r(raw[w], raw[w + 1], 16);
-          q1[w] = raw[5 + w];
-        }
-        q4_block_to_bf16(raw[0] & 0xffffu, q0, lo);
-        q4_block_to_bf16(raw[4] >> 16, q1, hi);
-#pragma unroll
-        for (int w = 0; w < 16; ++w) {
-          vals[w] = lo[w];
-          vals[16 + w] = hi[w];
-        }
+        for (int w = 0; w < QW; ++w) q[w] = __funnelshift_r(raw[w], raw[w + 1], 16);
+        dbits = raw[0] & 0xffffu;
       } else {
-        uint32_t q0[8], q1[8], lo[16], hi[16];
+        dbits = src[QW] >> 16;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) {
-          q0[w] = __funnelshift_r(raw[w], raw[w + 1], 16);
-          q1[w] = raw[9 + w];
-        }
-        q8_block_to_bf16(raw[0] & 0xffffu, q0, lo);
-        q8_block_to_bf16(raw[8] >> 16, q1, hi);
-#pragma unroll
-        for (int w = 0; w < 16; ++w) {
-          vals[w] = lo[w];
-          vals[16 + w] = hi[w];
-        }
+        for (int w = 0; w < QW; ++w) q[w] = src[QW + 1 + w];
+      }
+      if constexpr (Q4) {
+        q4_block_to_bf16(dbits, q, vals);
+      } else {
+        q8_block_to_bf16(dbits, q, vals);
       }
       if (sub == RAW_STEPS - 1 || i + 1 == nsteps) mbar_arrive(&raw_free[rs]);  // raw bytes are in registers now
       if (i >= NS) mbar_wait_bounded(&slot_free[slot], (uint32_t)((i / NS - 1) & 1), dead, P.status);
       uint8_t *row_dst = a_ring + slot * A_BYTES + r * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint4 chunk = make_uint4(vals[4 * c], vals[4 * c + 1], vals[4 * c + 2], vals[4 * c + 3]);
-        *reinterpret_cast<uint4 *>(row_dst + ((c ^ (r & 7)) << 4)) = chunk;
+        *reinterpret_cast<uint4 *>(row_dst + (((4 * half + c) ^ (r & 7)) << 4)) = chunk;
       }
       proxy_fence_async();  // generic-proxy stores must be visible to the tensor core's async reads
       mbar_arrive(&a_full[slot]);
@@ -280,7 +268,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     float *out = P.out + (size_t)blockIdx.z * P.split_stride;
     if (nsteps > 0) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < TN; c0 += 16) {
+      for (int c0 = (warp >= 6 ? 16 : 0); c0 < TN; c0 += 32) {  // two warps share a lane quarter
         if (tok0 + c0 >= P.m) break;
         uint32_t v[16];
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
@@ -399,7 +387,63 @@ __global__ void to_bf16_kernel(const float *x, int ldx, int k, __nv_bfloat16 *y,
   if (i < k) y[(size_t)row * ldy + i] = __float2bfloat16_rn(x[(size_t)row * ldx + i]);
 }
 
+// RMSNorm of one token row straight to the bf16 GEMM operand; f32 steps rounded like the
+// reference (src/models/transformer/layer.rs:423-443), then one rounding to bf16.
+__global__ void rmsnorm_bf16_kernel(const float *x, int ldx, const float *w, int d, float eps, __nv_bfloat16 *y, int ldy) {
+  pdl_wait();
+  pdl_launch_dependents();
+  __shared__ float partial[32];
+  __shared__ float inv_s;
+  const float *xr = x + (size_t)blockIdx.x * ldx;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = (threadIdx.x < (blockDim.x >> 5)) ? partial[threadIdx.x] : 0.0f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) inv_s = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(v, (float)d), eps)));
+  }
+  __syncthreads();
+  const float inv = inv_s;
+  for (int i = threadIdx.x; i < d; i += blockDim.x)
+    y[(size_t)blockIdx.x * ldy + i] = __float2bfloat16_rn(__fmul_rn(__fmul_rn(xr[i], inv), w[i]));
+}
+
+// h = silu(gate) * up (src/ir/elementwise.rs:6772-6830,7046-7050) to the bf16 operand of the down projection.
+__global__ void swiglu_bf16_kernel(const float *g, const float *u, int n, int ld, __nv_bfloat16 *y, int ldy) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x, row = blockIdx.y;
+  if (i < n) y[(size_t)row * ldy + i] = __float2bfloat16_rn(swiglu(g[(size_t)row * ld + i], u[(size_t)row * ld + i]));
+}
+
+template <typename K, typename... Args>
+cudaError_t launch_simple(K kernel, dim3 grid, dim3 block, const LaunchCfg &cfg, Args... args) {
+  cudaLaunchConfig_t lc{};
+  lc.gridDim = grid;
+  lc.blockDim = block;
+  lc.stream = cfg.stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = cfg.pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&lc, kernel, args...);
+}
+
 }  // namespace
+
+cudaError_t launch_rmsnorm_bf16(const float *x, int ldx, const float *w, int d, float eps, int rows, void *y, int ldy,
+                                const LaunchCfg &cfg) {
+  return launch_simple(rmsnorm_bf16_kernel, dim3((unsigned)rows), dim3(512), cfg, x, ldx, w, d, eps, static_cast<__nv_bfloat16 *>(y),
+                       ldy);
+}
+cudaError_t launch_swiglu_bf16(const float *g, const float *u, int n, int ld, int rows, void *y, int ldy, const LaunchCfg &cfg) {
+  return launch_simple(swiglu_bf16_kernel, dim3((unsigned)((n + 255) / 256), (unsigned)rows), dim3(256), cfg, g, u, n, ld,
+                       static_cast<__nv_bfloat16 *>(y), ldy);
+}
 
 cudaError_t launch_qgemm_tc(const QGemmArgs &a, const LaunchCfg &cfg) {
   if (!a.w || !a.x_bf16 || !a.out || a.m < 1 || a.n < 1 || a.k < KSTEP || a.k % 256) return cudaErrorInvalidValue;

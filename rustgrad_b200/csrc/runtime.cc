@@ -217,13 +217,15 @@ static int32_t check_tensor(rg_plan *p, const std::string &name, int32_t type, u
 // ------------------------------------------------------------------------------------------
 // Session
 // ------------------------------------------------------------------------------------------
-static constexpr int MAXC = 8;  // columns per forward: decode batch or prefill chunk
+static constexpr int MAXC = 8;    // columns of the GEMV paths: decode batch <= 8, short prefill tails
+static constexpr int WMAX = 256;  // columns of the tensor-core path: prefill chunk, decode batch 9..32
+static constexpr int BMAX = 32;   // independent sequences per session
 
 struct Ctrl {  // device control block, uploaded in one copy per host-driven step
-  int32_t tokens[MAXC];
-  int32_t pos[MAXC];
-  int32_t seq[MAXC];
-  int32_t logit_cols[MAXC];
+  int32_t tokens[WMAX];
+  int32_t pos[WMAX];
+  int32_t seq[WMAX];
+  int32_t logit_cols[BMAX];
   int32_t step;
   int32_t pad[3];
 };
@@ -249,6 +251,8 @@ struct rg_session {
   float *x = nullptr, *xn_f32 = nullptr, *qkv = nullptr, *q_rot = nullptr, *attn_scratch = nullptr, *attn_f32 = nullptr;
   float *partial = nullptr, *gate_f32 = nullptr, *up_f32 = nullptr, *h_f32 = nullptr, *logits = nullptr, *logits_l = nullptr;
   void *xn_pack = nullptr, *attn_pack = nullptr, *h_pack = nullptr, *head_pack = nullptr;
+  void *xb = nullptr;  // bf16 operand of the tensor-core path: [WMAX][max(d, qw, ffn_l)]
+  int xb_ld = 0;
   float *cos_t = nullptr, *sin_t = nullptr;
   std::vector<void *> k_cache, v_cache;
   std::vector<void *> owned;  // everything to cudaFree
@@ -528,10 +532,153 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
   return RG_OK;
 }
 
+// True when every projection can run the tensor-core GEMM (packed, K a multiple of 256).
+static bool wide_path_ok(const rg_session *s) {
+  if (s->opt.reserved[0] == 1) return false;
+  for (const LayerW &W : s->layers)
+    for (const DevTensor *t : {&W.q, &W.k, &W.v, &W.o, &W.gate, &W.up, &W.down})
+      if (!t->packed() || t->cols % 256) return false;
+  return s->head->packed() && s->head->cols % 256 == 0;
+}
+
+static int32_t gemm_tc(rg_session *s, const DevTensor &w, int m, float *out, int ldc, const LaunchCfg &L) {
+  QGemmArgs a;
+  a.type = w.type;
+  a.w = w.d;
+  a.n = (int)w.rows;
+  a.k = (int)w.cols;
+  a.x_bf16 = s->xb;
+  a.ldx = s->xb_ld;
+  a.m = m;
+  a.out = out;
+  a.ldc = ldc;
+  prof_mark(s, PROF_GEMV);
+  RG_LAUNCH(s, launch_qgemm_tc(a, L));
+  return RG_OK;
+}
+
+// Forward for 9..256 columns (a prefill chunk, or decode of 9..32 rows): the projections run on
+// the tcgen05 tensor cores with bf16 operands; norms, RoPE, attention and residuals stay f32.
+static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool advance) {
+  const rg_llama_config &c = s->cfg;
+  const int d = c.d_model, hd = c.head_dim;
+  const int qw = s->heads_l * hd, kw = s->kv_l * hd, qkv_w = qw + 2 * kw;
+  Ctrl *ctl = s->d_ctrl;
+  LaunchCfg L = lcfg(s);
+  LaunchCfg plain = L;
+  plain.pdl = false;
+  const bool tp = s->tp_world > 1;
+  int32_t rc;
+  prof_mark(s, PROF_OTHER);
+  RG_LAUNCH(s, launch_row_gather(s->token_embd.type, s->token_embd.d, d, ctl->tokens, ncols, s->x, d, plain));
+  for (int l = 0; l < c.n_layers; ++l) {
+    const LayerW &W = s->layers[(size_t)l];
+    prof_mark(s, PROF_OTHER);
+    RG_LAUNCH(s, launch_rmsnorm_bf16(s->x, d, reinterpret_cast<const float *>(W.attn_norm.d), d, c.norm_eps, ncols, s->xb,
+                                     s->xb_ld, (tp && l > 0) ? plain : L));
+    if ((rc = gemm_tc(s, W.q, ncols, s->qkv, qkv_w, L))) return rc;
+    if ((rc = gemm_tc(s, W.k, ncols, s->qkv + qw, qkv_w, L))) return rc;
+    if ((rc = gemm_tc(s, W.v, ncols, s->qkv + qw + kw, qkv_w, L))) return rc;
+    prof_mark(s, PROF_ATTN);
+    RopeArgs ra;
+    ra.qkv = s->qkv;
+    ra.cols = ncols;
+    ra.heads = s->heads_l;
+    ra.kv_heads = s->kv_l;
+    ra.hd = hd;
+    ra.ctx = s->ctx;
+    ra.col_seq = ctl->seq;
+    ra.col_pos = ctl->pos;
+    ra.cos_t = s->cos_t;
+    ra.sin_t = s->sin_t;
+    ra.q_out = s->q_rot;
+    ra.k_cache = s->k_cache[(size_t)l];
+    ra.v_cache = s->v_cache[(size_t)l];
+    ra.kv_f32 = s->kv_f32;
+    RG_LAUNCH(s, launch_rope_append(ra, L));
+    AttnArgs aa;
+    aa.q = s->q_rot;
+    aa.k_cache = ra.k_cache;
+    aa.v_cache = ra.v_cache;
+    aa.kv_f32 = s->kv_f32;
+    aa.cols = ncols;
+    aa.heads = s->heads_l;
+    aa.kv_heads = s->kv_l;
+    aa.hd = hd;
+    aa.ctx = s->ctx;
+    aa.col_seq = ctl->seq;
+    aa.col_pos = ctl->pos;
+    aa.scratch = s->attn_scratch;
+    aa.out_f32 = s->attn_f32;
+    RG_LAUNCH(s, launch_attention(aa, L));
+    if (s->family_mask & (1u << PROF_ATTN)) s->launches_in_step++;  // split + combine
+    RG_LAUNCH(s, launch_to_bf16(s->attn_f32, qw, qw, ncols, s->xb, s->xb_ld, L));
+    if ((rc = gemm_tc(s, W.o, ncols, s->partial, d, L))) return rc;
+    if (tp) {
+      if ((rc = tp_reduce_add(s, ncols))) return rc;
+    } else {
+      prof_mark(s, PROF_OTHER);
+      RG_LAUNCH(s, launch_add_rows(s->x, d, s->partial, d, d, ncols, L));
+    }
+    prof_mark(s, PROF_OTHER);
+    RG_LAUNCH(s, launch_rmsnorm_bf16(s->x, d, reinterpret_cast<const float *>(W.ffn_norm.d), d, c.norm_eps, ncols, s->xb,
+                                     s->xb_ld, tp ? plain : L));
+    if ((rc = gemm_tc(s, W.gate, ncols, s->gate_f32, s->ffn_l, L))) return rc;
+    if ((rc = gemm_tc(s, W.up, ncols, s->up_f32, s->ffn_l, L))) return rc;
+    prof_mark(s, PROF_OTHER);
+    RG_LAUNCH(s, launch_swiglu_bf16(s->gate_f32, s->up_f32, s->ffn_l, s->ffn_l, ncols, s->xb, s->xb_ld, L));
+    if ((rc = gemm_tc(s, W.down, ncols, s->partial, d, L))) return rc;
+    if (tp) {
+      if ((rc = tp_reduce_add(s, ncols))) return rc;
+    } else {
+      prof_mark(s, PROF_OTHER);
+      RG_LAUNCH(s, launch_add_rows(s->x, d, s->partial, d, d, ncols, L));
+    }
+  }
+  if (n_logit_cols > 0) {
+    const bool split_head = tp && s->head == &s->output;
+    float *dst = split_head ? s->logits_l : s->logits;
+    const int ld = split_head ? s->vocab_l : c.vocab;
+    if (n_logit_cols <= 2) {
+      // a prompt's last token: the integer GEMV with the final norm in its prologue
+      const DevTensor *hw[1] = {s->head};
+      if ((rc = gemv_i8(s, hw, 1, s->x, d, ctl->logit_cols, reinterpret_cast<const float *>(s->output_norm.d), n_logit_cols,
+                        EPI_STORE, dst, ld, tp ? plain : L)))
+        return rc;
+    } else {
+      // decode of many rows: logit column i is row i
+      prof_mark(s, PROF_OTHER);
+      RG_LAUNCH(s, launch_rmsnorm_bf16(s->x, d, reinterpret_cast<const float *>(s->output_norm.d), d, c.norm_eps, n_logit_cols,
+                                       s->xb, s->xb_ld, tp ? plain : L));
+      if ((rc = gemm_tc(s, *s->head, n_logit_cols, dst, ld, L))) return rc;
+    }
+    LaunchCfg am = L;
+    prof_mark(s, PROF_OTHER);
+    if (split_head && (s->family_mask & (1u << PROF_OTHER))) {
+      std::string err;
+      if ((rc = comm_group_start(&err))) return fail(rc, err);
+      for (int col = 0; col < n_logit_cols; ++col)
+        if ((rc = comm_allgather_f32(&s->comm, s->logits_l + (size_t)col * s->vocab_l, s->logits + (size_t)col * c.vocab,
+                                     (size_t)s->vocab_l, s->stream, &err)))
+          return fail(rc, err);
+      if ((rc = comm_group_end(&err))) return fail(rc, err);
+      am.pdl = false;
+    }
+    RG_LAUNCH(s, launch_argmax(s->logits, c.vocab, c.vocab, n_logit_cols, s->d_ids, am));
+    if (advance) RG_LAUNCH(s, launch_advance(s->d_ids, ctl->tokens, ctl->pos, s->d_history, &ctl->step, ncols, L));
+  }
+  return RG_OK;
+}
+
 // One forward over `ncols` columns described by the device control block.  n_logit_cols columns
 // (indices in ctrl.logit_cols) get logits + greedy ids; 0 skips the head (non-final prefill chunk).
 static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance) {
   if (small_batch_path(s, ncols)) return forward_small(s, ncols, n_logit_cols, advance);
+  if (ncols > MAXC) {
+    if (!wide_path_ok(s))
+      return fail(RG_UNSUPPORTED_GEOMETRY, "more than 8 columns need packed projections with K a multiple of 256");
+    return forward_wide(s, ncols, n_logit_cols, advance);
+  }
   const rg_llama_config &c = s->cfg;
   const int d = c.d_model, hd = c.head_dim;
   const int qw = s->heads_l * hd, kw = s->kv_l * hd, qkv_w = qw + 2 * kw;
@@ -829,7 +976,7 @@ int32_t rg_b200_plan_create(const rg_llama_config *c, const rg_options *o, rg_pl
   if (p->tp_rank < 0 || p->tp_rank >= p->tp_world) return fail(RG_INVALID_ARGUMENT, "tensor-parallel rank out of range");
   if (p->tp_world > 1 && (c->n_heads % p->tp_world || c->n_kv_heads % p->tp_world || c->ffn_dim % p->tp_world))
     return fail(RG_UNSUPPORTED_GEOMETRY, "heads, kv heads and ffn width must divide by the tensor-parallel world size");
-  if (p->opt.max_batch > MAXC) return fail(RG_UNSUPPORTED_GEOMETRY, "max_batch above 8 is not supported");
+  if (p->opt.max_batch > BMAX) return fail(RG_UNSUPPORTED_GEOMETRY, "max_batch above 32 is not supported");
   RG_CUDA(cudaSetDevice(p->opt.device));
   int sms = 0;
   RG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->opt.device));
@@ -1041,23 +1188,27 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
 #define RG_TRY(e)            \
   if ((rc = (e))) return rc;
   RG_TRY(dalloc(s.get(), &s->d_ctrl, 1));
-  RG_TRY(dalloc(s.get(), &s->d_ids, MAXC));
+  RG_TRY(dalloc(s.get(), &s->d_ids, BMAX));
   s->history_cap = 8192;
-  RG_TRY(dalloc(s.get(), &s->d_history, (size_t)s->history_cap * MAXC));
+  RG_TRY(dalloc(s.get(), &s->d_history, (size_t)s->history_cap * BMAX));
   RG_TRY(dalloc(s.get(), &s->d_status, 1));
-  RG_TRY(dalloc(s.get(), &s->x, (size_t)MAXC * d));
+  // per-column buffers are sized for the widest forward (a 256-token prefill chunk)
+  RG_TRY(dalloc(s.get(), &s->x, (size_t)WMAX * d));
   RG_TRY(dalloc(s.get(), &s->xn_f32, (size_t)MAXC * d));
-  RG_TRY(dalloc(s.get(), &s->qkv, (size_t)MAXC * (qw + 2 * kw)));
-  RG_TRY(dalloc(s.get(), &s->q_rot, (size_t)MAXC * qw));
-  RG_TRY(dalloc(s.get(), &s->attn_scratch, attn_scratch_floats(MAXC, s->heads_l, hd, s->ctx)));
-  RG_TRY(dalloc(s.get(), &s->attn_f32, (size_t)MAXC * qw));
-  RG_TRY(dalloc(s.get(), &s->partial, (size_t)MAXC * d));
-  RG_TRY(dalloc(s.get(), &s->gate_f32, (size_t)MAXC * s->ffn_l));
-  RG_TRY(dalloc(s.get(), &s->up_f32, (size_t)MAXC * s->ffn_l));
+  RG_TRY(dalloc(s.get(), &s->qkv, (size_t)WMAX * (qw + 2 * kw)));
+  RG_TRY(dalloc(s.get(), &s->q_rot, (size_t)WMAX * qw));
+  RG_TRY(dalloc(s.get(), &s->attn_scratch, attn_scratch_floats(WMAX, s->heads_l, hd, s->ctx)));
+  RG_TRY(dalloc(s.get(), &s->attn_f32, (size_t)WMAX * qw));
+  RG_TRY(dalloc(s.get(), &s->partial, (size_t)WMAX * d));
+  RG_TRY(dalloc(s.get(), &s->gate_f32, (size_t)WMAX * s->ffn_l));
+  RG_TRY(dalloc(s.get(), &s->up_f32, (size_t)WMAX * s->ffn_l));
   RG_TRY(dalloc(s.get(), &s->h_f32, (size_t)MAXC * s->ffn_l));
-  RG_TRY(dalloc(s.get(), &s->logits, (size_t)MAXC * c.vocab));
-  RG_TRY(dalloc(s.get(), &s->logits_l, (size_t)MAXC * s->vocab_l));
+  RG_TRY(dalloc(s.get(), &s->logits, (size_t)BMAX * c.vocab));
+  RG_TRY(dalloc(s.get(), &s->logits_l, (size_t)BMAX * s->vocab_l));
   uint8_t *raw;
+  s->xb_ld = std::max(d, std::max(qw, s->ffn_l));
+  RG_TRY(dalloc(s.get(), &raw, (size_t)WMAX * s->xb_ld * 2));
+  s->xb = raw;
   RG_TRY(dalloc(s.get(), &raw, xpack_bytes(d, MAXC)));
   s->xn_pack = raw;
   RG_TRY(dalloc(s.get(), &raw, xpack_bytes(qw, MAXC)));
@@ -1098,9 +1249,9 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   RG_CUDA(cudaMemsetAsync(s->d_status, 0, sizeof(int), s->stream));
   RG_CUDA(cudaMemsetAsync(s->d_ctrl, 0, sizeof(Ctrl), s->stream));
   RG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&s->h_ctrl), sizeof(Ctrl)));
-  RG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&s->h_ids), sizeof(int32_t) * (size_t)s->history_cap * MAXC));
+  RG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&s->h_ids), sizeof(int32_t) * (size_t)s->history_cap * BMAX));
   RG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&s->h_status), sizeof(int)));
-  RG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&s->h_logits), sizeof(float) * (size_t)MAXC * c.vocab));
+  RG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&s->h_logits), sizeof(float) * (size_t)BMAX * c.vocab));
   memset(s->h_ctrl, 0, sizeof(Ctrl));
   RG_CUDA(cudaStreamSynchronize(s->stream));
 #undef RG_TRY
@@ -1167,8 +1318,9 @@ int32_t rg_b200_prefill(rg_session *s, int32_t row, const int32_t *ids, size_t n
     if (ids[i] < 0 || ids[i] >= s->cfg.vocab) return fail(RG_TOKEN_OUT_OF_RANGE, "token " + std::to_string(ids[i]) + " at index " + std::to_string(i));
   RG_CUDA(cudaSetDevice(s->opt.device));
   RG_CUDA(cudaEventRecord(s->ev0, s->stream));
+  const bool wide_ok = wide_path_ok(s);  // prompt chunks of 256 tokens on the tensor cores
   for (size_t done = 0; done < n;) {
-    const int chunk = (int)std::min<size_t>(MAXC, n - done);
+    const int chunk = (int)std::min<size_t>(wide_ok ? WMAX : MAXC, n - done);
     const bool last = done + (size_t)chunk == n;
     Ctrl *h = s->h_ctrl;
     for (int i = 0; i < chunk; ++i) {
