@@ -79,7 +79,10 @@ typedef struct {
   int32_t disable_graph; /* 1: launch decode kernels directly instead of replaying a CUDA graph */
   int32_t disable_pdl;   /* 1: no programmatic dependent launch between kernels */
   int32_t disable_fused_allreduce; /* 1: TP all-reduce through NCCL only */
-  int32_t reserved[8];    /* reserved[0] == 1: never take the fused small-batch decode path */
+  int32_t reserved[8];    /* reserved[0] == 1: never take the fused small-batch decode path nor the
+                           * tensor-core path; reserved[1]: operand mode of the tensor-core path as
+                           * in rg_b200_qgemm, offset by one (0 = default = compensated half,
+                           * 1 = bf16, 2 = half, 3 = compensated half) */
 } rg_options;
 
 /* Per-run evidence in the vocabulary of MetalDeviceRunReport
@@ -200,12 +203,17 @@ int32_t rg_b200_row_gather(int32_t device, int32_t ggml_type, const uint8_t *wei
                            uint64_t cols, const int64_t *indices, size_t count, float *out);
 
 /* The same product for many activation rows on the tcgen05 tensor cores (prefill): activations are
- * rounded to bf16 and the weights are dequantised to bf16 tiles, accumulation is f32
- * (the per-layer linear of src/models/transformer/layer.rs:445-448 for a whole prompt chunk).
- * iters > 0 additionally repeats the launch `iters` times between CUDA events and stores the mean
- * kernel time in kernel_ms (nullable). */
+ * rounded to a 16-bit operand type and the weights are dequantised to tiles of that type,
+ * accumulation is f32 (the per-layer linear of src/models/transformer/layer.rs:445-448 for a whole
+ * prompt chunk).  operand_mode 0: bf16 operands (Q4_0 weights enter as bf16(bf16(d) * (n - 8)));
+ * 1: IEEE half operands (f16(d * (n - 8)); finite activations beyond +-65504 saturate);
+ * 2: compensated half, the session's default: each operand is split into f16 hi + f16 lo and three
+ * products per K step (hi.hi + hi.lo + lo.hi) give f32-grade accuracy at three times the
+ * tensor-core work.  iters > 0 additionally repeats the launch `iters` times between CUDA events
+ * and stores the mean kernel time in kernel_ms (nullable). */
 int32_t rg_b200_qgemm(int32_t device, int32_t ggml_type, const uint8_t *weight, uint64_t n, uint64_t k,
-                      const float *activation, uint64_t m, int32_t iters, float *out, float *kernel_ms);
+                      const float *activation, uint64_t m, int32_t operand_mode, int32_t iters, float *out,
+                      float *kernel_ms);
 
 /* One decode token of scaled_dot_product_attention with GQA (src/ir/attention.rs:946-981,1157-1240;
  * mask `col <= past + row` of src/models/transformer/layer.rs:374-380 for a single new row): q is

@@ -102,7 +102,8 @@ def load() -> C.CDLL:
     L.rg_b200_qmatmul.argtypes = [C.c_int32, C.c_int32, u8p, C.c_uint64, C.c_uint64, f32p, C.c_uint64, f32p]
     L.rg_b200_row_gather.argtypes = [C.c_int32, C.c_int32, u8p, C.c_uint64, C.c_uint64, C.POINTER(C.c_int64),
                                      C.c_size_t, f32p]
-    L.rg_b200_qgemm.argtypes = [C.c_int32, C.c_int32, u8p, C.c_uint64, C.c_uint64, f32p, C.c_uint64, C.c_int32, f32p, f32p]
+    L.rg_b200_qgemm.argtypes = [C.c_int32, C.c_int32, u8p, C.c_uint64, C.c_uint64, f32p, C.c_uint64, C.c_int32, C.c_int32,
+                                f32p, f32p]
     L.rg_b200_attention_decode_noalloc.argtypes = [vp, vp, vp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                                    C.c_int32, vp, vp, C.c_int32]
     L.rg_b200_attention_decode.argtypes = [C.c_int32, f32p, vp, vp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,

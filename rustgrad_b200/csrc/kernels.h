@@ -57,14 +57,20 @@ struct GemvI8Args {
 bool qgemv_i8_supported(int k, int batch);
 cudaError_t launch_qgemv_i8(const GemvI8Args &a, const LaunchCfg &cfg);
 
-// tcgen05 GEMM for many tokens: out[m][n] = x[m][k] (bf16) . W[n][k]^T with W in Q4_0 / Q8_0 blocks
-// dequantised to bf16 tiles; f32 accumulation in TMEM.  splits > 1 divides K over blockIdx.z and
-// writes one partial result per split (split_stride floats apart) for a later reduction.
+// tcgen05 GEMM for many tokens: out[m][n] = x[m][k] (16-bit) . W[n][k]^T with W in Q4_0 / Q8_0 blocks
+// dequantised to 16-bit tiles; f32 accumulation in TMEM.  Operand modes: bf16; IEEE half (more
+// mantissa, saturating activations); compensated half, where activations come as two planes
+// (hi = f16(x), lo = f16(x - hi)), the weights are split the same way in the kernel and three
+// products per K step give f32-grade accuracy.  splits > 1 divides K over blockIdx.z and writes one
+// partial result per split (split_stride floats apart) for a later reduction.
+enum QGemmMode { QGEMM_BF16 = 0, QGEMM_F16 = 1, QGEMM_F16X3 = 2 };
 struct QGemmArgs {
   int type = 0;
   const uint8_t *w = nullptr;
   int n = 0, k = 0;
-  const void *x_bf16 = nullptr;  // [m][ldx] bf16, 16-byte aligned rows
+  const void *x16 = nullptr;     // [m][ldx] bf16 or f16, 16-byte aligned rows
+  const void *x16_lo = nullptr;  // QGEMM_F16X3: the low plane, same shape
+  int mode = QGEMM_BF16;
   int ldx = 0;
   int m = 0;
   float *out = nullptr;
@@ -73,11 +79,17 @@ struct QGemmArgs {
   size_t split_stride = 0;
 };
 cudaError_t launch_qgemm_tc(const QGemmArgs &a, const LaunchCfg &cfg);
-cudaError_t launch_to_bf16(const float *x, int ldx, int k, int rows, void *y, int ldy, const LaunchCfg &cfg);
-// RMSNorm of `rows` token rows to the bf16 GEMM operand; SwiGLU of (gate, up) rows to bf16.
-cudaError_t launch_rmsnorm_bf16(const float *x, int ldx, const float *w, int d, float eps, int rows, void *y, int ldy,
-                                const LaunchCfg &cfg);
-cudaError_t launch_swiglu_bf16(const float *g, const float *u, int n, int ld, int rows, void *y, int ldy, const LaunchCfg &cfg);
+// Destination of the f32 -> operand conversions: lo is written only for f16 operands and may be null.
+struct Operand16 {
+  void *hi = nullptr, *lo = nullptr;
+  int ld = 0;
+  bool f16 = false;
+};
+cudaError_t launch_to16(const float *x, int ldx, int k, int rows, const Operand16 &y, const LaunchCfg &cfg);
+// RMSNorm of `rows` token rows to the 16-bit GEMM operand; SwiGLU of (gate, up) rows likewise.
+cudaError_t launch_rmsnorm16(const float *x, int ldx, const float *w, int d, float eps, int rows, const Operand16 &y,
+                             const LaunchCfg &cfg);
+cudaError_t launch_swiglu16(const float *g, const float *u, int n, int ld, int rows, const Operand16 &y, const LaunchCfg &cfg);
 
 // Dense (F32/F16) weight GEMV for tensors the block formats cannot hold (K % 32 != 0) or that a
 // file stores dense.  x is plain f32 [batch, ldx]; same epilogues (EPI_SWIGLU unsupported).

@@ -234,7 +234,7 @@ int32_t rg_b200_row_gather(int32_t device, int32_t type, const uint8_t *weight, 
 }
 
 int32_t rg_b200_qgemm(int32_t device, int32_t type, const uint8_t *weight, uint64_t n, uint64_t k, const float *activation,
-                      uint64_t m, int32_t iters, float *out, float *kernel_ms) {
+                      uint64_t m, int32_t operand_mode, int32_t iters, float *out, float *kernel_ms) {
   if (!weight || !activation || !out) return fail(RG_INVALID_ARGUMENT, "null argument");
   if (type != RG_TYPE_Q4_0 && type != RG_TYPE_Q8_0) return fail(RG_UNSUPPORTED_TYPE, "the tensor-core GEMM takes Q4_0 or Q8_0 weights");
   size_t wbytes;
@@ -251,17 +251,25 @@ int32_t rg_b200_qgemm(int32_t device, int32_t type, const uint8_t *weight, uint6
   float *d_x, *d_y;
   OP_CUDA(sc.alloc(&d_w, wbytes));
   OP_CUDA(sc.alloc(&d_x, sizeof(float) * m * k));
-  OP_CUDA(sc.alloc(&d_xb, 2 * m * k));
+  if (operand_mode < 0 || operand_mode > 2) return fail(RG_INVALID_ARGUMENT, "operand_mode must be 0, 1 or 2");
+  OP_CUDA(sc.alloc(&d_xb, 4 * m * k));  // hi and lo planes
   OP_CUDA(sc.alloc(&d_y, sizeof(float) * m * n));
   OP_CUDA(cudaMemcpyAsync(d_w, weight, wbytes, cudaMemcpyHostToDevice, sc.stream));
   OP_CUDA(cudaMemcpyAsync(d_x, activation, sizeof(float) * m * k, cudaMemcpyHostToDevice, sc.stream));
-  OP_CUDA(launch_to_bf16(d_x, (int)k, (int)k, (int)m, d_xb, (int)k, cfg));
+  Operand16 op;
+  op.hi = d_xb;
+  op.lo = operand_mode == QGEMM_F16X3 ? d_xb + 2 * m * k : nullptr;
+  op.ld = (int)k;
+  op.f16 = operand_mode != QGEMM_BF16;
+  OP_CUDA(launch_to16(d_x, (int)k, (int)k, (int)m, op, cfg));
   QGemmArgs a;
   a.type = type;
   a.w = d_w;
   a.n = (int)n;
   a.k = (int)k;
-  a.x_bf16 = d_xb;
+  a.x16 = d_xb;
+  a.x16_lo = op.lo;
+  a.mode = operand_mode;
   a.ldx = (int)k;
   a.m = (int)m;
   a.out = d_y;

@@ -1,27 +1,33 @@
 // Prefill / wide-batch GEMM on the 5th-generation tensor cores:
-//   C[M][N] (f32) = X[M][K] (bf16) * W[N][K]^T,  W in native Q4_0 / Q8_0 GGML blocks.
+//   C[M][N] (f32) = X[M][K] (16-bit) * W[N][K]^T,  W in native Q4_0 / Q8_0 GGML blocks.
 // Semantics: the layer linears of the Llama forward for many tokens at once
 // (src/models/transformer/layer.rs:445-448, src/backend/cpu.rs:3484-3532 on the dequantised
-// weight of src/models/transformer/model.rs:982-995), with bf16 operands and f32 accumulation.
+// weight of src/models/transformer/model.rs:982-995), with 16-bit operands and f32 accumulation.
 //
 // One CTA computes a [128 weight rows] x [TN tokens] tile over a K range:
 //   * MMA M = 128 weight rows (the dequantised tile is the A operand), MMA N = TN tokens (the
 //     activation tile is the B operand), K = 16 per tcgen05.mma, four per 64-element stage;
 //     the accumulator lives in TMEM (128 lanes x TN f32 columns).
-//   * warp 0: TMA producer of the activation tiles (tiled 2-D copy, 128-byte swizzle).
+//   * warp 0: TMA producer.  Activation tiles come as tiled 2-D copies with the 128-byte swizzle;
+//     the raw block bytes of the 128 weight rows, 256 columns (8 blocks) at a time, come through
+//     a second tiled 2-D map into a small ring, so no thread waits on global memory.
 //   * warp 1: allocates TMEM, issues tcgen05.mma from one thread, commits to mbarriers.
-//   * warp 0 also streams the raw block bytes of the 128 weight rows, 256 columns (8 blocks) at a
-//     time, into a small ring with a second tiled 2-D TMA map, so no thread waits on global memory.
-//   * warps 2-9: two threads per weight row, each reads the row's two raw blocks of the stage from that
-//     ring, expands nibbles to exact bf16 integers with
-//     the 128+n bit pattern and applies the block scale with one bf16x2 FMA per two weights, and
-//     writes the 128-byte row into the K-major / 128-byte-swizzled A tile; afterwards the same
-//     warps read the accumulator with tcgen05.ld and store it.
-//   * Four-stage ring with bounded mbarrier waits; a time-out records a status and the kernel
-//     still frees its TMEM and exits.
-// The weight scale enters as bf16(d): the A operand is bf16(bf16(d) * (n - 8)).
+//   * warps 2-9: two threads per weight row; each expands one block per stage (nibbles to exact
+//     16-bit integers by bit pattern, one packed subtract and one packed multiply by the block
+//     scale per two weights) and writes its half of the 128-byte row into the K-major,
+//     128-byte-swizzled A tile; afterwards the same warps read the accumulator with tcgen05.ld
+//     and store it.
+//   * Operand rings of 3-4 stages with bounded mbarrier waits; a time-out records a status and
+//     the kernel still frees its TMEM and exits.
+// Operand modes: bf16 (weights enter as bf16(bf16(d) * (n - 8)) for Q4_0), f16 (weights enter as
+// f16(d * (n - 8))), and compensated f16, where every operand is the sum of two halves
+// (hi = f16(v), lo = f16(v - hi)) and each K step issues hi.hi + hi.lo + lo.hi into the same
+// accumulator: the dropped lo.lo term is 2^-22 of the product, so the result has f32-grade accuracy
+// at three times the tensor-core work.  The session uses the compensated mode because logits must
+// stay within 1e-3 of the reference's f32 arithmetic.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "../../include/rg_b200.h"
 #include "kernels.h"
@@ -30,19 +36,18 @@
 namespace rg {
 namespace {
 
-constexpr int TM = 128;     // weight rows per tile (MMA M)
-constexpr int KSTEP = 64;   // elements per stage (128 bytes of bf16: one swizzle row)
+constexpr int TM = 128;       // weight rows per tile (MMA M)
+constexpr int KSTEP = 64;     // elements per stage (128 bytes: one swizzle row)
 constexpr int RAW_STEPS = 4;  // 64-element stages per raw weight tile (256 columns = 8 blocks)
 constexpr int RAW_NS = 2;     // raw ring depth
 constexpr int THREADS = 320;  // TMA warp, MMA warp, eight dequantisation / epilogue warps
 constexpr int A_BYTES = TM * KSTEP * 2;
 
 struct Params {
-  const uint8_t *w;
-  int n, k;       // weight rows, columns
-  int m;          // tokens
-  int k_begin_steps, k_steps;  // this launch covers steps [blockIdx.z * k_steps, ...) of k / 64
-  float *out;     // [splits][m][ldc] when split-K, else [m][ldc]
+  int n, k;     // weight rows, columns
+  int m;        // tokens
+  int k_steps;  // 64-element steps per split (blockIdx.z), a multiple of RAW_STEPS
+  float *out;   // [splits][m][ldc] when split-K, else [m][ldc]
   int ldc;
   size_t split_stride;
   int *status;
@@ -67,11 +72,12 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;                        // layout: 128-byte swizzle
   return d;
 }
-// Instruction descriptor: f32 accumulate, bf16 A and B, both K-major, shape M x N.
-__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+// Instruction descriptor: f32 accumulate, A and B both f16 (format 0) or both bf16 (format 1),
+// both K-major, shape M x N.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n, bool f16) {
+  return (1u << 4) | ((f16 ? 0u : 1u) << 7) | ((f16 ? 0u : 1u) << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_16bit(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
@@ -85,39 +91,66 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void proxy_fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
+template <bool F16>
+__device__ __forceinline__ uint32_t sub2(uint32_t a, uint32_t b) {
   uint32_t d;
-  asm("sub.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  if constexpr (F16) {
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  } else {
+    asm("sub.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  }
   return d;
 }
-__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+template <bool F16>
+__device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
   uint32_t d;
-  asm("mul.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  if constexpr (F16) {
+    asm("mul.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  } else {
+    asm("mul.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  }
   return d;
 }
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+template <bool F16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   uint32_t d;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  if constexpr (F16) {
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  } else {
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  }
   return d;
+}
+template <bool F16>
+__device__ __forceinline__ uint16_t to16(float v) {
+  if constexpr (F16) {
+    // finite values beyond the f16 range saturate; infinities and NaN pass through unchanged
+    if (fabsf(v) > 65504.0f && fabsf(v) < __int_as_float(0x7f800000)) v = copysignf(65504.0f, v);
+    return __half_as_ushort(__float2half_rn(v));
+  } else {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+  }
 }
 
-// One Q4_0 block (scale + 16 quant bytes given as four words) -> 32 bf16 in element order:
+// One Q4_0 block (scale + 16 quant bytes given as four words) -> 32 values in element order:
 // out[0..7] = elements 0..15 (low nibbles), out[8..15] = elements 16..31 (high nibbles).
-__device__ __forceinline__ void q4_block_to_bf16(uint32_t dbits16, const uint32_t (&q)[4], uint32_t (&out)[16]) {
-  const float d = half_bits_to_float(dbits16);
-  const uint32_t d2 = pack_bf16x2(d, d);
-  const uint32_t M = 0x000F000Fu, E = 0x43004300u, OFF = 0x43084308u;  // bf16 128 + n, minus 136: exact n - 8
+// Bit patterns: f16 0x6400 | n = 1024 + n, bf16 0x4300 | n = 128 + n; the subtraction gives n - 8 exactly.
+template <bool F16>
+__device__ __forceinline__ void q4_block_to_16(uint32_t dbits16, const uint32_t (&q)[4], uint32_t (&out)[16]) {
+  const uint32_t d2 = F16 ? (dbits16 | (dbits16 << 16)) : pack2<false>(half_bits_to_float(dbits16), half_bits_to_float(dbits16));
+  const uint32_t M = 0x000F000Fu, E = F16 ? 0x64006400u : 0x43004300u, OFF = F16 ? 0x64086408u : 0x43084308u;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const uint32_t w = prmt(q[i], 0u, 0x3120u);  // bytes (b0, b2, b1, b3): adjacent elements share a mask
-    out[2 * i] = bf16x2_mul(bf16x2_sub((w & M) | E, OFF), d2);              // elements 4i, 4i+1
-    out[2 * i + 1] = bf16x2_mul(bf16x2_sub(((w >> 8) & M) | E, OFF), d2);   // elements 4i+2, 4i+3
-    out[8 + 2 * i] = bf16x2_mul(bf16x2_sub(((w >> 4) & M) | E, OFF), d2);   // elements 16+4i, 16+4i+1
-    out[8 + 2 * i + 1] = bf16x2_mul(bf16x2_sub(((w >> 12) & M) | E, OFF), d2);
+    out[2 * i] = mul2<F16>(sub2<F16>((w & M) | E, OFF), d2);              // elements 4i, 4i+1
+    out[2 * i + 1] = mul2<F16>(sub2<F16>(((w >> 8) & M) | E, OFF), d2);   // elements 4i+2, 4i+3
+    out[8 + 2 * i] = mul2<F16>(sub2<F16>(((w >> 4) & M) | E, OFF), d2);   // elements 16+4i, 16+4i+1
+    out[8 + 2 * i + 1] = mul2<F16>(sub2<F16>(((w >> 12) & M) | E, OFF), d2);
   }
 }
-// One Q8_0 block (eight words of int8) -> 32 bf16.
-__device__ __forceinline__ void q8_block_to_bf16(uint32_t dbits16, const uint32_t (&q)[8], uint32_t (&out)[16]) {
+// One Q8_0 block (eight words of int8) -> 32 values.
+template <bool F16>
+__device__ __forceinline__ void q8_block_to_16(uint32_t dbits16, const uint32_t (&q)[8], uint32_t (&out)[16]) {
   const float d = half_bits_to_float(dbits16);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -126,26 +159,74 @@ __device__ __forceinline__ void q8_block_to_bf16(uint32_t dbits16, const uint32_
     const float v1 = __uint_as_float(0x4B000000u | ((u >> 8) & 0xffu)) - 8388736.0f;
     const float v2 = __uint_as_float(0x4B000000u | ((u >> 16) & 0xffu)) - 8388736.0f;
     const float v3 = __uint_as_float(0x4B000000u | (u >> 24)) - 8388736.0f;
-    out[2 * i] = pack_bf16x2(v0 * d, v1 * d);
-    out[2 * i + 1] = pack_bf16x2(v2 * d, v3 * d);
+    out[2 * i] = pack2<F16>(v0 * d, v1 * d);
+    out[2 * i + 1] = pack2<F16>(v2 * d, v3 * d);
   }
 }
 
-template <int QT, int TN>
+// Compensated operands: hi = f16(w), lo = f16(w - hi) with w = d * q exact in f32 (Q8_0) or through a
+// fused multiply-add (Q4_0: q * d - hi is exact before its single rounding).
+__device__ __forceinline__ void q4_block_split(uint32_t dbits16, const uint32_t (&q)[4], uint32_t (&hi)[16], uint32_t (&lo)[16]) {
+  const uint32_t d2 = dbits16 | (dbits16 << 16);
+  const uint32_t M = 0x000F000Fu, E = 0x64006400u, OFF = 0x64086408u;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t w = prmt(q[i], 0u, 0x3120u);
+    const uint32_t n[4] = {w & M, (w >> 8) & M, (w >> 4) & M, (w >> 12) & M};
+    const int slot[4] = {2 * i, 2 * i + 1, 8 + 2 * i, 8 + 2 * i + 1};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t qf = sub2<true>(n[j] | E, OFF);
+      const uint32_t h = mul2<true>(qf, d2);
+      uint32_t l;
+      asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(l) : "r"(qf), "r"(d2), "r"(h ^ 0x80008000u));
+      hi[slot[j]] = h;
+      lo[slot[j]] = l;
+    }
+  }
+}
+__device__ __forceinline__ void split_pair(float v0, float v1, uint32_t &hi, uint32_t &lo) {
+  const __half2 h = __floats2half2_rn(v0, v1);
+  const float2 hf = __half22float2(h);
+  const __half2 l = __floats2half2_rn(v0 - hf.x, v1 - hf.y);
+  hi = *reinterpret_cast<const uint32_t *>(&h);
+  lo = *reinterpret_cast<const uint32_t *>(&l);
+}
+__device__ __forceinline__ void q8_block_split(uint32_t dbits16, const uint32_t (&q)[8], uint32_t (&hi)[16], uint32_t (&lo)[16]) {
+  const float d = half_bits_to_float(dbits16);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t u = q[i] ^ 0x80808080u;
+    const float v0 = __uint_as_float(0x4B000000u | (u & 0xffu)) - 8388736.0f;
+    const float v1 = __uint_as_float(0x4B000000u | ((u >> 8) & 0xffu)) - 8388736.0f;
+    const float v2 = __uint_as_float(0x4B000000u | ((u >> 16) & 0xffu)) - 8388736.0f;
+    const float v3 = __uint_as_float(0x4B000000u | (u >> 24)) - 8388736.0f;
+    split_pair(v0 * d, v1 * d, hi[2 * i], lo[2 * i]);
+    split_pair(v2 * d, v3 * d, hi[2 * i + 1], lo[2 * i + 1]);
+  }
+}
+
+__host__ __device__ constexpr int ring_depth(int tn, bool comp) { return comp ? (tn >= 128 ? 2 : 3) : (tn > 128 ? 3 : 4); }
+
+template <int QT, int TN, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
-    qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const Params P) {
+    qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap xlo_map,
+                    const __grid_constant__ CUtensorMap wmap, const Params P) {
   constexpr bool Q4 = (QT == RG_TYPE_Q4_0);
+  constexpr bool F16 = MODE != QGEMM_BF16, COMP = MODE == QGEMM_F16X3;
+  constexpr int NPL = COMP ? 2 : 1;  // operand planes per stage: hi (and lo)
   constexpr int BB = Q4 ? 18 : 34;
-  constexpr int NS = TN > 128 ? 3 : 4;  // operand ring depth
+  constexpr int NS = ring_depth(TN, COMP);  // operand ring depth
   constexpr int B_BYTES = TN * KSTEP * 2;
+  constexpr int A_STAGE = NPL * A_BYTES, B_STAGE = NPL * B_BYTES;
   constexpr int RAW_ROW = 8 * BB;  // bytes of one weight row in a raw tile (144 / 272)
   constexpr int RAW_BYTES = TM * RAW_ROW;
   constexpr int TMEM_COLS = TN < 32 ? 32 : TN;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t *a_ring = smem;
-  uint8_t *b_ring = smem + NS * A_BYTES;
-  uint8_t *raw_ring = b_ring + NS * B_BYTES;
+  uint8_t *b_ring = smem + NS * A_STAGE;
+  uint8_t *raw_ring = b_ring + NS * B_STAGE;
   uint64_t *bars = reinterpret_cast<uint64_t *>(raw_ring + RAW_NS * RAW_BYTES);
   uint64_t *b_full = bars, *a_full = bars + NS, *slot_free = bars + 2 * NS;
   uint64_t *raw_full = bars + 3 * NS, *raw_free = raw_full + RAW_NS, *acc_done = raw_free + RAW_NS;
@@ -154,7 +235,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * TM, tok0 = blockIdx.y * TN;
-  const int step0 = blockIdx.z * P.k_steps;  // k_steps is a multiple of RAW_STEPS
+  const int step0 = blockIdx.z * P.k_steps;
   const int nsteps = min(P.k_steps, P.k / KSTEP - step0);
 
   if (threadIdx.x == 0) {
@@ -196,24 +277,33 @@ __global__ void __launch_bounds__(THREADS, 1)
         }
         const int slot = i % NS;
         if (i >= NS) mbar_wait_bounded(&slot_free[slot], (uint32_t)((i / NS - 1) & 1), dead, P.status);
-        mbar_expect_tx(&b_full[slot], (uint32_t)B_BYTES);
-        tma_tile_2d(b_ring + slot * B_BYTES, &xmap, (step0 + i) * KSTEP, tok0, &b_full[slot]);
+        mbar_expect_tx(&b_full[slot], (uint32_t)B_STAGE);
+        tma_tile_2d(b_ring + slot * B_STAGE, &xmap, (step0 + i) * KSTEP, tok0, &b_full[slot]);
+        if constexpr (COMP) tma_tile_2d(b_ring + slot * B_STAGE + B_BYTES, &xlo_map, (step0 + i) * KSTEP, tok0, &b_full[slot]);
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(TM, TN);
+      constexpr uint32_t idesc = umma_idesc(TM, TN, F16);
       for (int i = 0; i < nsteps; ++i) {
         const int slot = i % NS;
         const uint32_t ph = (uint32_t)((i / NS) & 1);
         mbar_wait_bounded(&a_full[slot], ph, dead, P.status);
         mbar_wait_bounded(&b_full[slot], ph, dead, P.status);
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(a_ring + slot * A_BYTES), b_addr = smem_u32(b_ring + slot * B_BYTES);
+        const uint32_t a_addr = smem_u32(a_ring + slot * A_STAGE), b_addr = smem_u32(b_ring + slot * B_STAGE);
 #pragma unroll
-        for (int kk = 0; kk < KSTEP / 16; ++kk)
-          umma_bf16(tmem_base, umma_desc(a_addr + kk * 32), umma_desc(b_addr + kk * 32), idesc, (i > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < KSTEP / 16; ++kk) {
+          const uint64_t a_hi = umma_desc(a_addr + kk * 32), b_hi = umma_desc(b_addr + kk * 32);
+          if constexpr (COMP) {  // the small terms first, then hi.hi
+            umma_16bit(tmem_base, a_hi, umma_desc(b_addr + B_BYTES + kk * 32), idesc, (i > 0 || kk > 0) ? 1u : 0u);
+            umma_16bit(tmem_base, umma_desc(a_addr + A_BYTES + kk * 32), b_hi, idesc, 1u);
+            umma_16bit(tmem_base, a_hi, b_hi, idesc, 1u);
+          } else {
+            umma_16bit(tmem_base, a_hi, b_hi, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+        }
         umma_commit(&slot_free[slot]);  // the slot may be rewritten once these MMAs have read it
       }
       umma_commit(acc_done);
@@ -221,9 +311,9 @@ __global__ void __launch_bounds__(THREADS, 1)
   } else {
     // ---------------------------------------------------------------- dequantisation: one block (half of a
     // stage's 64 columns) of one weight row per thread, two threads per row
-    const int tdq = threadIdx.x - 64;            // 0..255
-    const int r = tdq & 127, half = tdq >> 7;    // row of the tile, even / odd block of the stage
-    constexpr int QW = Q4 ? 4 : 8;               // quant words per block
+    const int tdq = threadIdx.x - 64;          // 0..255
+    const int r = tdq & 127, half = tdq >> 7;  // row of the tile, even / odd block of the stage
+    constexpr int QW = Q4 ? 4 : 8;             // quant words per block
     for (int i = 0; i < nsteps; ++i) {
       const int slot = i % NS;
       const int j = i / RAW_STEPS, rs = j % RAW_NS, sub = i % RAW_STEPS;
@@ -231,7 +321,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       // pair layout: [d0 | q0] [d1 | q1] with a 2-byte scale in front of each block: the even block's
       // quants straddle word boundaries (funnel shift), the odd block's are word aligned
       const uint32_t *src = reinterpret_cast<const uint32_t *>(raw_ring + rs * RAW_BYTES + r * RAW_ROW + sub * 2 * BB);
-      uint32_t q[QW], dbits, vals[16];  // 32 bf16 of this block, in k order
+      uint32_t q[QW], dbits, vals[16];  // 32 values of this block, in k order
       if (half == 0) {
         uint32_t raw[QW + 1];
 #pragma unroll
@@ -244,18 +334,29 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
         for (int w = 0; w < QW; ++w) q[w] = src[QW + 1 + w];
       }
-      if constexpr (Q4) {
-        q4_block_to_bf16(dbits, q, vals);
+      uint32_t lows[COMP ? 16 : 1];
+      if constexpr (COMP) {
+        if constexpr (Q4) {
+          q4_block_split(dbits, q, vals, lows);
+        } else {
+          q8_block_split(dbits, q, vals, lows);
+        }
+      } else if constexpr (Q4) {
+        q4_block_to_16<F16>(dbits, q, vals);
       } else {
-        q8_block_to_bf16(dbits, q, vals);
+        q8_block_to_16<F16>(dbits, q, vals);
       }
       if (sub == RAW_STEPS - 1 || i + 1 == nsteps) mbar_arrive(&raw_free[rs]);  // raw bytes are in registers now
       if (i >= NS) mbar_wait_bounded(&slot_free[slot], (uint32_t)((i / NS - 1) & 1), dead, P.status);
-      uint8_t *row_dst = a_ring + slot * A_BYTES + r * 128;
+      uint8_t *row_dst = a_ring + slot * A_STAGE + r * 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint4 chunk = make_uint4(vals[4 * c], vals[4 * c + 1], vals[4 * c + 2], vals[4 * c + 3]);
         *reinterpret_cast<uint4 *>(row_dst + (((4 * half + c) ^ (r & 7)) << 4)) = chunk;
+        if constexpr (COMP) {
+          chunk = make_uint4(lows[4 * c], lows[4 * c + 1], lows[4 * c + 2], lows[4 * c + 3]);
+          *reinterpret_cast<uint4 *>(row_dst + A_BYTES + (((4 * half + c) ^ (r & 7)) << 4)) = chunk;
+        }
       }
       proxy_fence_async();  // generic-proxy stores must be visible to the tensor core's async reads
       mbar_arrive(&a_full[slot]);
@@ -309,24 +410,27 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-template <int QT, int TN>
+template <int QT, int TN, int MODE>
 cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
   EncodeFn fn = encode_fn();
   if (!fn) return cudaErrorNotSupported;
+  constexpr bool F16 = MODE != QGEMM_BF16, COMP = MODE == QGEMM_F16X3;
   constexpr int BB = (QT == RG_TYPE_Q4_0) ? 18 : 34;
-  constexpr int NS = TN > 128 ? 3 : 4;
+  constexpr int NS = ring_depth(TN, COMP);
+  constexpr int NPL = COMP ? 2 : 1;
   constexpr int RAW_ROW = 8 * BB;
-  alignas(64) CUtensorMap xmap, wmap;
+  alignas(64) CUtensorMap xmap, xlo_map, wmap;
   const cuuint32_t elem[2] = {1, 1};
-  {
+  for (int plane = 0; plane < NPL; ++plane) {
     const cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
     const cuuint64_t strides[1] = {(cuuint64_t)a.ldx * 2};
     const cuuint32_t box[2] = {(cuuint32_t)KSTEP, (cuuint32_t)TN};
-    if (fn(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(a.x_bf16), dims, strides, box, elem,
-           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    if (fn(plane ? &xlo_map : &xmap, F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+           const_cast<void *>(plane ? a.x16_lo : a.x16), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return cudaErrorInvalidValue;
   }
+  if (!COMP) xlo_map = xmap;
   {
     const size_t row_bytes = (size_t)(a.k / 32) * BB;
     const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 8), (cuuint64_t)a.n};
@@ -338,7 +442,6 @@ cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
       return cudaErrorInvalidValue;
   }
   Params P{};
-  P.w = a.w;
   P.n = a.n;
   P.k = a.k;
   P.m = a.m;
@@ -350,8 +453,10 @@ cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
   P.ldc = a.ldc;
   P.split_stride = a.split_stride;
   P.status = cfg.status;
-  constexpr size_t smem = 1024 + NS * (A_BYTES + TN * KSTEP * 2) + RAW_NS * TM * RAW_ROW + (3 * NS + 2 * RAW_NS + 1) * 8 + 16;
-  auto kernel = qgemm_tc_kernel<QT, TN>;
+  constexpr size_t smem =
+      1024 + NS * NPL * (A_BYTES + TN * KSTEP * 2) + RAW_NS * TM * RAW_ROW + (3 * NS + 2 * RAW_NS + 1) * 8 + 16;
+  static_assert(smem <= 227 * 1024, "tile configuration exceeds the shared memory of one SM");
+  auto kernel = qgemm_tc_kernel<QT, TN, MODE>;
   static bool attr_done = false;  // per instantiation
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -368,28 +473,48 @@ cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
   at[0].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = at;
   lc.numAttrs = cfg.pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&lc, kernel, xmap, wmap, P);
+  return cudaLaunchKernelEx(&lc, kernel, xmap, xlo_map, wmap, P);
 }
 
-template <int QT>
+template <int QT, int MODE>
 cudaError_t launch_n(const QGemmArgs &a, const LaunchCfg &cfg) {
-  if (a.m > 128) return launch_t<QT, 256>(a, cfg);
-  if (a.m > 64) return launch_t<QT, 128>(a, cfg);
-  if (a.m > 32) return launch_t<QT, 64>(a, cfg);
-  if (a.m > 16) return launch_t<QT, 32>(a, cfg);
-  return launch_t<QT, 16>(a, cfg);
+  if constexpr (MODE != QGEMM_F16X3) {  // the compensated mode keeps two planes per operand: 128 tokens at most
+    if (a.m > 128) return launch_t<QT, 256, MODE>(a, cfg);
+  }
+  if (a.m > 64) return launch_t<QT, 128, MODE>(a, cfg);
+  if (a.m > 32) return launch_t<QT, 64, MODE>(a, cfg);
+  if (a.m > 16) return launch_t<QT, 32, MODE>(a, cfg);
+  return launch_t<QT, 16, MODE>(a, cfg);
+}
+template <int QT>
+cudaError_t launch_m(const QGemmArgs &a, const LaunchCfg &cfg) {
+  if (a.mode == QGEMM_BF16) return launch_n<QT, QGEMM_BF16>(a, cfg);
+  if (a.mode == QGEMM_F16) return launch_n<QT, QGEMM_F16>(a, cfg);
+  return launch_n<QT, QGEMM_F16X3>(a, cfg);
 }
 
-__global__ void to_bf16_kernel(const float *x, int ldx, int k, __nv_bfloat16 *y, int ldy) {
+// One value to its operand: hi (and, when lo is given, the f16 of what hi left over).
+template <bool F16>
+__device__ __forceinline__ void put16(float v, uint16_t *hi, uint16_t *lo, size_t at) {
+  const uint16_t h = to16<F16>(v);
+  hi[at] = h;
+  if constexpr (F16) {
+    if (lo) lo[at] = to16<true>(v - __half2float(__ushort_as_half(h)));
+  }
+}
+
+template <bool F16>
+__global__ void to16_kernel(const float *x, int ldx, int k, uint16_t *y, uint16_t *ylo, int ldy) {
   pdl_wait();
   pdl_launch_dependents();
   const int i = blockIdx.x * blockDim.x + threadIdx.x, row = blockIdx.y;
-  if (i < k) y[(size_t)row * ldy + i] = __float2bfloat16_rn(x[(size_t)row * ldx + i]);
+  if (i < k) put16<F16>(x[(size_t)row * ldx + i], y, ylo, (size_t)row * ldy + i);
 }
 
-// RMSNorm of one token row straight to the bf16 GEMM operand; f32 steps rounded like the
-// reference (src/models/transformer/layer.rs:423-443), then one rounding to bf16.
-__global__ void rmsnorm_bf16_kernel(const float *x, int ldx, const float *w, int d, float eps, __nv_bfloat16 *y, int ldy) {
+// RMSNorm of one token row straight to the 16-bit GEMM operand; f32 steps rounded like the
+// reference (src/models/transformer/layer.rs:423-443), then one rounding to the operand type.
+template <bool F16>
+__global__ void rmsnorm16_kernel(const float *x, int ldx, const float *w, int d, float eps, uint16_t *y, uint16_t *ylo, int ldy) {
   pdl_wait();
   pdl_launch_dependents();
   __shared__ float partial[32];
@@ -408,15 +533,16 @@ __global__ void rmsnorm_bf16_kernel(const float *x, int ldx, const float *w, int
   __syncthreads();
   const float inv = inv_s;
   for (int i = threadIdx.x; i < d; i += blockDim.x)
-    y[(size_t)blockIdx.x * ldy + i] = __float2bfloat16_rn(__fmul_rn(__fmul_rn(xr[i], inv), w[i]));
+    put16<F16>(__fmul_rn(__fmul_rn(xr[i], inv), w[i]), y, ylo, (size_t)blockIdx.x * ldy + i);
 }
 
-// h = silu(gate) * up (src/ir/elementwise.rs:6772-6830,7046-7050) to the bf16 operand of the down projection.
-__global__ void swiglu_bf16_kernel(const float *g, const float *u, int n, int ld, __nv_bfloat16 *y, int ldy) {
+// h = silu(gate) * up (src/ir/elementwise.rs:6772-6830,7046-7050) to the operand of the down projection.
+template <bool F16>
+__global__ void swiglu16_kernel(const float *g, const float *u, int n, int ld, uint16_t *y, uint16_t *ylo, int ldy) {
   pdl_wait();
   pdl_launch_dependents();
   const int i = blockIdx.x * blockDim.x + threadIdx.x, row = blockIdx.y;
-  if (i < n) y[(size_t)row * ldy + i] = __float2bfloat16_rn(swiglu(g[(size_t)row * ld + i], u[(size_t)row * ld + i]));
+  if (i < n) put16<F16>(swiglu(g[(size_t)row * ld + i], u[(size_t)row * ld + i]), y, ylo, (size_t)row * ldy + i);
 }
 
 template <typename K, typename... Args>
@@ -435,36 +561,34 @@ cudaError_t launch_simple(K kernel, dim3 grid, dim3 block, const LaunchCfg &cfg,
 
 }  // namespace
 
-cudaError_t launch_rmsnorm_bf16(const float *x, int ldx, const float *w, int d, float eps, int rows, void *y, int ldy,
-                                const LaunchCfg &cfg) {
-  return launch_simple(rmsnorm_bf16_kernel, dim3((unsigned)rows), dim3(512), cfg, x, ldx, w, d, eps, static_cast<__nv_bfloat16 *>(y),
-                       ldy);
+cudaError_t launch_rmsnorm16(const float *x, int ldx, const float *w, int d, float eps, int rows, const Operand16 &y,
+                             const LaunchCfg &cfg) {
+  uint16_t *hi = static_cast<uint16_t *>(y.hi), *lo = static_cast<uint16_t *>(y.lo);
+  if (y.f16) return launch_simple(rmsnorm16_kernel<true>, dim3((unsigned)rows), dim3(512), cfg, x, ldx, w, d, eps, hi, lo, y.ld);
+  return launch_simple(rmsnorm16_kernel<false>, dim3((unsigned)rows), dim3(512), cfg, x, ldx, w, d, eps, hi, lo, y.ld);
 }
-cudaError_t launch_swiglu_bf16(const float *g, const float *u, int n, int ld, int rows, void *y, int ldy, const LaunchCfg &cfg) {
-  return launch_simple(swiglu_bf16_kernel, dim3((unsigned)((n + 255) / 256), (unsigned)rows), dim3(256), cfg, g, u, n, ld,
-                       static_cast<__nv_bfloat16 *>(y), ldy);
+cudaError_t launch_swiglu16(const float *g, const float *u, int n, int ld, int rows, const Operand16 &y, const LaunchCfg &cfg) {
+  uint16_t *hi = static_cast<uint16_t *>(y.hi), *lo = static_cast<uint16_t *>(y.lo);
+  const dim3 grid((unsigned)((n + 255) / 256), (unsigned)rows);
+  if (y.f16) return launch_simple(swiglu16_kernel<true>, grid, dim3(256), cfg, g, u, n, ld, hi, lo, y.ld);
+  return launch_simple(swiglu16_kernel<false>, grid, dim3(256), cfg, g, u, n, ld, hi, lo, y.ld);
+}
+cudaError_t launch_to16(const float *x, int ldx, int k, int rows, const Operand16 &y, const LaunchCfg &cfg) {
+  uint16_t *hi = static_cast<uint16_t *>(y.hi), *lo = static_cast<uint16_t *>(y.lo);
+  const dim3 grid((unsigned)((k + 255) / 256), (unsigned)rows);
+  if (y.f16) return launch_simple(to16_kernel<true>, grid, dim3(256), cfg, x, ldx, k, hi, lo, y.ld);
+  return launch_simple(to16_kernel<false>, grid, dim3(256), cfg, x, ldx, k, hi, lo, y.ld);
 }
 
 cudaError_t launch_qgemm_tc(const QGemmArgs &a, const LaunchCfg &cfg) {
-  if (!a.w || !a.x_bf16 || !a.out || a.m < 1 || a.n < 1 || a.k < KSTEP || a.k % 256) return cudaErrorInvalidValue;
-  if ((reinterpret_cast<uintptr_t>(a.x_bf16) & 15) || (a.ldx * 2) % 16 || (reinterpret_cast<uintptr_t>(a.w) & 15))
+  if (!a.w || !a.x16 || !a.out || a.m < 1 || a.n < 1 || a.k < KSTEP || a.k % 256) return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(a.x16) & 15) || (a.ldx * 2) % 16 || (reinterpret_cast<uintptr_t>(a.w) & 15))
     return cudaErrorInvalidValue;
-  if (a.type == RG_TYPE_Q4_0) return launch_n<RG_TYPE_Q4_0>(a, cfg);
-  if (a.type == RG_TYPE_Q8_0) return launch_n<RG_TYPE_Q8_0>(a, cfg);
+  if (a.mode == QGEMM_F16X3 && (!a.x16_lo || (reinterpret_cast<uintptr_t>(a.x16_lo) & 15))) return cudaErrorInvalidValue;
+  if (a.mode < QGEMM_BF16 || a.mode > QGEMM_F16X3) return cudaErrorInvalidValue;
+  if (a.type == RG_TYPE_Q4_0) return launch_m<RG_TYPE_Q4_0>(a, cfg);
+  if (a.type == RG_TYPE_Q8_0) return launch_m<RG_TYPE_Q8_0>(a, cfg);
   return cudaErrorInvalidValue;
-}
-
-cudaError_t launch_to_bf16(const float *x, int ldx, int k, int rows, void *y, int ldy, const LaunchCfg &cfg) {
-  cudaLaunchConfig_t lc{};
-  lc.gridDim = dim3((unsigned)((k + 255) / 256), (unsigned)rows);
-  lc.blockDim = dim3(256);
-  lc.stream = cfg.stream;
-  cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  at[0].val.programmaticStreamSerializationAllowed = 1;
-  lc.attrs = at;
-  lc.numAttrs = cfg.pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&lc, to_bf16_kernel, x, ldx, k, static_cast<__nv_bfloat16 *>(y), ldy);
 }
 
 }  // namespace rg

@@ -251,7 +251,8 @@ struct rg_session {
   float *x = nullptr, *xn_f32 = nullptr, *qkv = nullptr, *q_rot = nullptr, *attn_scratch = nullptr, *attn_f32 = nullptr;
   float *partial = nullptr, *gate_f32 = nullptr, *up_f32 = nullptr, *h_f32 = nullptr, *logits = nullptr, *logits_l = nullptr;
   void *xn_pack = nullptr, *attn_pack = nullptr, *h_pack = nullptr, *head_pack = nullptr;
-  void *xb = nullptr;  // bf16 operand of the tensor-core path: [WMAX][max(d, qw, ffn_l)]
+  void *xb = nullptr;  // 16-bit operand planes (hi, lo) of the tensor-core path: [2][WMAX][max(d, qw, ffn_l)]
+  int gemm_mode = QGEMM_F16X3;
   int xb_ld = 0;
   float *cos_t = nullptr, *sin_t = nullptr;
   std::vector<void *> k_cache, v_cache;
@@ -541,13 +542,27 @@ static bool wide_path_ok(const rg_session *s) {
   return s->head->packed() && s->head->cols % 256 == 0;
 }
 
+// Operand planes of the tensor-core path.  The default mode is the compensated one: single bf16 or
+// f16 operands leave the logits of a prompt 1e-2 .. 1e-1 away from the f32 arithmetic.
+static Operand16 wide_operand(const rg_session *s) {
+  Operand16 o;
+  o.hi = s->xb;
+  o.lo = s->gemm_mode == QGEMM_F16X3 ? static_cast<uint8_t *>(s->xb) + (size_t)WMAX * s->xb_ld * 2 : nullptr;
+  o.ld = s->xb_ld;
+  o.f16 = s->gemm_mode != QGEMM_BF16;
+  return o;
+}
+
 static int32_t gemm_tc(rg_session *s, const DevTensor &w, int m, float *out, int ldc, const LaunchCfg &L) {
   QGemmArgs a;
   a.type = w.type;
   a.w = w.d;
   a.n = (int)w.rows;
   a.k = (int)w.cols;
-  a.x_bf16 = s->xb;
+  const Operand16 op = wide_operand(s);
+  a.x16 = op.hi;
+  a.x16_lo = op.lo;
+  a.mode = s->gemm_mode;
   a.ldx = s->xb_ld;
   a.m = m;
   a.out = out;
@@ -558,7 +573,7 @@ static int32_t gemm_tc(rg_session *s, const DevTensor &w, int m, float *out, int
 }
 
 // Forward for 9..256 columns (a prefill chunk, or decode of 9..32 rows): the projections run on
-// the tcgen05 tensor cores with bf16 operands; norms, RoPE, attention and residuals stay f32.
+// the tcgen05 tensor cores (compensated f16 operands by default); norms, RoPE, attention and residuals stay f32.
 static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool advance) {
   const rg_llama_config &c = s->cfg;
   const int d = c.d_model, hd = c.head_dim;
@@ -568,14 +583,15 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
   LaunchCfg plain = L;
   plain.pdl = false;
   const bool tp = s->tp_world > 1;
+  const Operand16 xop = wide_operand(s);
   int32_t rc;
   prof_mark(s, PROF_OTHER);
   RG_LAUNCH(s, launch_row_gather(s->token_embd.type, s->token_embd.d, d, ctl->tokens, ncols, s->x, d, plain));
   for (int l = 0; l < c.n_layers; ++l) {
     const LayerW &W = s->layers[(size_t)l];
     prof_mark(s, PROF_OTHER);
-    RG_LAUNCH(s, launch_rmsnorm_bf16(s->x, d, reinterpret_cast<const float *>(W.attn_norm.d), d, c.norm_eps, ncols, s->xb,
-                                     s->xb_ld, (tp && l > 0) ? plain : L));
+    RG_LAUNCH(s, launch_rmsnorm16(s->x, d, reinterpret_cast<const float *>(W.attn_norm.d), d, c.norm_eps, ncols, xop,
+                                  (tp && l > 0) ? plain : L));
     if ((rc = gemm_tc(s, W.q, ncols, s->qkv, qkv_w, L))) return rc;
     if ((rc = gemm_tc(s, W.k, ncols, s->qkv + qw, qkv_w, L))) return rc;
     if ((rc = gemm_tc(s, W.v, ncols, s->qkv + qw + kw, qkv_w, L))) return rc;
@@ -612,7 +628,7 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
     aa.out_f32 = s->attn_f32;
     RG_LAUNCH(s, launch_attention(aa, L));
     if (s->family_mask & (1u << PROF_ATTN)) s->launches_in_step++;  // split + combine
-    RG_LAUNCH(s, launch_to_bf16(s->attn_f32, qw, qw, ncols, s->xb, s->xb_ld, L));
+    RG_LAUNCH(s, launch_to16(s->attn_f32, qw, qw, ncols, xop, L));
     if ((rc = gemm_tc(s, W.o, ncols, s->partial, d, L))) return rc;
     if (tp) {
       if ((rc = tp_reduce_add(s, ncols))) return rc;
@@ -621,12 +637,12 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
       RG_LAUNCH(s, launch_add_rows(s->x, d, s->partial, d, d, ncols, L));
     }
     prof_mark(s, PROF_OTHER);
-    RG_LAUNCH(s, launch_rmsnorm_bf16(s->x, d, reinterpret_cast<const float *>(W.ffn_norm.d), d, c.norm_eps, ncols, s->xb,
-                                     s->xb_ld, tp ? plain : L));
+    RG_LAUNCH(s, launch_rmsnorm16(s->x, d, reinterpret_cast<const float *>(W.ffn_norm.d), d, c.norm_eps, ncols, xop,
+                                  tp ? plain : L));
     if ((rc = gemm_tc(s, W.gate, ncols, s->gate_f32, s->ffn_l, L))) return rc;
     if ((rc = gemm_tc(s, W.up, ncols, s->up_f32, s->ffn_l, L))) return rc;
     prof_mark(s, PROF_OTHER);
-    RG_LAUNCH(s, launch_swiglu_bf16(s->gate_f32, s->up_f32, s->ffn_l, s->ffn_l, ncols, s->xb, s->xb_ld, L));
+    RG_LAUNCH(s, launch_swiglu16(s->gate_f32, s->up_f32, s->ffn_l, s->ffn_l, ncols, xop, L));
     if ((rc = gemm_tc(s, W.down, ncols, s->partial, d, L))) return rc;
     if (tp) {
       if ((rc = tp_reduce_add(s, ncols))) return rc;
@@ -648,8 +664,8 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
     } else {
       // decode of many rows: logit column i is row i
       prof_mark(s, PROF_OTHER);
-      RG_LAUNCH(s, launch_rmsnorm_bf16(s->x, d, reinterpret_cast<const float *>(s->output_norm.d), d, c.norm_eps, n_logit_cols,
-                                       s->xb, s->xb_ld, tp ? plain : L));
+      RG_LAUNCH(s, launch_rmsnorm16(s->x, d, reinterpret_cast<const float *>(s->output_norm.d), d, c.norm_eps, n_logit_cols, xop,
+                                    tp ? plain : L));
       if ((rc = gemm_tc(s, *s->head, n_logit_cols, dst, ld, L))) return rc;
     }
     LaunchCfg am = L;
@@ -1207,7 +1223,8 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   RG_TRY(dalloc(s.get(), &s->logits_l, (size_t)BMAX * s->vocab_l));
   uint8_t *raw;
   s->xb_ld = std::max(d, std::max(qw, s->ffn_l));
-  RG_TRY(dalloc(s.get(), &raw, (size_t)WMAX * s->xb_ld * 2));
+  RG_TRY(dalloc(s.get(), &raw, (size_t)2 * WMAX * s->xb_ld * 2));
+  s->gemm_mode = (s->opt.reserved[1] >= 1 && s->opt.reserved[1] <= 3) ? s->opt.reserved[1] - 1 : QGEMM_F16X3;
   s->xb = raw;
   RG_TRY(dalloc(s.get(), &raw, xpack_bytes(d, MAXC)));
   s->xn_pack = raw;

@@ -332,13 +332,15 @@ def row_gather(ggml_type: int, weight, rows: int, cols: int, indices, device: in
     return out
 
 
-def qgemm(ggml_type: int, weight, n: int, k: int, activation, iters: int = 0, device: int = 0):
-    """Tensor-core GEMM (bf16 operands, f32 accumulate): returns (output [m,n], mean kernel ms or 0)."""
+def qgemm(ggml_type: int, weight, n: int, k: int, activation, iters: int = 0, device: int = 0, operand_mode: int = 0):
+    """Tensor-core GEMM, f32 accumulate; operand_mode 0 = bf16, 1 = f16, 2 = compensated f16 (hi + lo planes).
+    Returns (output [m,n], mean kernel ms or 0)."""
     w = np.ascontiguousarray(weight, dtype=np.uint8)
     a = np.ascontiguousarray(activation, dtype=np.float32).reshape(-1, k)
     out = np.empty((a.shape[0], n), dtype=np.float32)
     ms = C.c_float(0)
-    check(_lib.load().rg_b200_qgemm(device, ggml_type, _u8(w), n, k, _f32(a), a.shape[0], iters, _f32(out), C.byref(ms)))
+    check(_lib.load().rg_b200_qgemm(device, ggml_type, _u8(w), n, k, _f32(a), a.shape[0], int(operand_mode), iters,
+                                    _f32(out), C.byref(ms)))
     return out, ms.value
 
 

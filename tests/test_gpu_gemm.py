@@ -1,9 +1,12 @@
 """Prefill GEMM on the tcgen05 tensor cores against the CPU dequant + matmul (BASELINE config 3).
 
-Operands are bf16 (activations rounded to bf16, weights bf16(bf16(d) * (n - 8))), accumulation f32.
-Tolerance: the error of rounding both operands to bf16 is 2^-8 relative per product and averages
-out over K; the bound used is 2e-2 of |x|.|w| per output (norm-relative), and 1e-3 of it against a
-reference that applies the same operand rounding."""
+Operands are 16-bit, accumulation f32.  Mode 0 (bf16): activations rounded to bf16, weights
+bf16(bf16(d) * (n - 8)) for Q4_0 and bf16(d * q) for Q8_0.  Mode 1 (f16): activations rounded to IEEE
+half, weights f16(d * q).  Mode 2 (compensated f16, the session's): hi + lo planes of both operands.
+Tolerance: rounding both operands costs 2^-8 (bf16) or 2^-11 (f16) relative per product and
+averages out over K; the bound used is norm-relative (|x|.|w| per output), and 1e-5 of that norm
+against a reference that applies the same operand rounding.  The compensated mode must be within
+2e-6 of that norm of the exact product (f32 accumulation is all that is left)."""
 import numpy as np
 import pytest
 
@@ -19,29 +22,69 @@ def to_bf16(a):
     return (((b + r) >> 16) << 16).astype(np.uint32).view(np.float32)
 
 
-def bf16_weight(kind, data, n, k):
-    """The operand the kernel builds: bf16(bf16(d) * q) for Q4_0, bf16(d * q) for Q8_0."""
+def to_f16(a):
+    return np.asarray(a, dtype=np.float32).astype(np.float16).astype(np.float32)
+
+
+def operand_weight(kind, data, n, k, f16):
+    """The operand the kernel builds from the blocks."""
     dense = O.dequantize(kind, data, n * k).reshape(n, k // 32, 32)
+    if f16:
+        return to_f16(dense).reshape(n, k)
+    if kind == quant.Q8_0:
+        return to_bf16(dense).reshape(n, k)
     bb = quant.BLOCK_BYTES[kind]
     d = data.reshape(n, k // 32, bb)[:, :, :2].copy().view(np.float16).astype(np.float32)  # [n, blocks, 1]
     with np.errstate(divide="ignore", invalid="ignore"):
         q = np.where(d != 0, np.rint(dense / d), 0.0).astype(np.float32)
-    if kind == quant.Q8_0:
-        return to_bf16(dense).reshape(n, k)
     return to_bf16(to_bf16(d) * q).reshape(n, k)
 
 
+@pytest.mark.parametrize("mode", [0, 1, 2], ids=["bf16", "f16", "f16x3"])
 @pytest.mark.parametrize("kind", [quant.Q4_0, quant.Q8_0])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 256), (16, 128, 512), (200, 300, 1024), (33, 4096, 4096), (512, 1024, 4096)])
-def test_qgemm_matches_cpu_dequant_matmul(kind, m, n, k):
+def test_qgemm_matches_cpu_dequant_matmul(kind, m, n, k, mode):
     rng = np.random.default_rng(m + n + k)
     w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
     x = rng.standard_normal((m, k)).astype(np.float32)
     data = quant.encode(kind, w)
-    got, _ = session.qgemm(kind, data, n, k, x)
+    got, _ = session.qgemm(kind, data, n, k, x, operand_mode=mode)
     dense = O.dequantize(kind, data, n * k).reshape(n, k)
     scale = np.sqrt((x.astype(np.float64) ** 2).sum(1))[:, None] * np.sqrt((dense.astype(np.float64) ** 2).sum(1))[None, :]
     want = x.astype(np.float64) @ dense.astype(np.float64).T
-    assert (np.abs(got - want) / scale).max() < 2e-2 / np.sqrt(k) * 8
-    same_rounding = to_bf16(x).astype(np.float64) @ bf16_weight(kind, data, n, k).astype(np.float64).T
+    if mode == 2:
+        assert (np.abs(got - want) / scale).max() < 2e-6
+        return
+    f16 = mode == 1
+    assert (np.abs(got - want) / scale).max() < (2e-2 if not f16 else 2.5e-3) / np.sqrt(k) * 8
+    rx = to_f16(x) if f16 else to_bf16(x)
+    same_rounding = rx.astype(np.float64) @ operand_weight(kind, data, n, k, f16).astype(np.float64).T
     assert (np.abs(got - same_rounding) / scale).max() < 1e-5
+
+
+def test_f16_operands_saturate_large_finite_activations():
+    n, k = 128, 256
+    rng = np.random.default_rng(5)
+    data = quant.encode(quant.Q8_0, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+    x = np.zeros((16, k), dtype=np.float32)
+    x[0, 0] = 1.0e6  # beyond the f16 range: enters as 65504
+    x[1, 3] = -3.0
+    got, _ = session.qgemm(quant.Q8_0, data, n, k, x, operand_mode=1)
+    w = to_f16(O.dequantize(quant.Q8_0, data, n * k).reshape(n, k))
+    assert np.isfinite(got).all()
+    np.testing.assert_allclose(got[0], 65504.0 * w[:, 0], rtol=1e-6)
+    np.testing.assert_allclose(got[1], -3.0 * w[:, 3], rtol=1e-6)
+
+
+def test_compensated_mode_keeps_small_and_large_magnitudes():
+    """Weights and activations far from 1 (lo planes in the f16 subnormal range, hi near its top)."""
+    n, k, m = 256, 512, 40
+    rng = np.random.default_rng(11)
+    for wstd, xstd in ((1e-3, 1e-2), (0.5, 300.0), (0.02, 1.0)):
+        data = quant.encode(quant.Q4_0, (rng.standard_normal((n, k)) * wstd).astype(np.float32))
+        x = (rng.standard_normal((m, k)) * xstd).astype(np.float32)
+        got, _ = session.qgemm(quant.Q4_0, data, n, k, x, operand_mode=2)
+        dense = O.dequantize(quant.Q4_0, data, n * k).reshape(n, k).astype(np.float64)
+        want = x.astype(np.float64) @ dense.T
+        scale = np.sqrt((x.astype(np.float64) ** 2).sum(1))[:, None] * np.sqrt((dense ** 2).sum(1))[None, :]
+        assert (np.abs(got - want) / scale).max() < 1e-5, (wstd, xstd)
