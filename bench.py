@@ -3,6 +3,8 @@
     python bench.py --gpus 1 --steps 256 --warmup 8
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
     python bench.py --impl reference ...        # the CPU restatement of the reference path
+    python bench.py --workload gemv [--shapes 14336x4096 --types q4_0 --batches 1]   # isolated GEMV sweep
+    python bench.py --workload gemm [--shapes 14336x4096 --tokens 2048 --modes 0,2]  # prefill GEMM sweep
 
 A step is one greedy decode step (one new token per row) of a seeded synthetic model:
   * N = 1: Llama-3-8B shape, Q4_0 projections, Q8_0 embedding and head, f16 KV cache, batch 1,
@@ -151,8 +153,60 @@ def cpu_reference_arm(args, wl, threads):
     return 1.0 / t_token, t_token, sample
 
 
+GGML = {"q4_0": quant.Q4_0, "q8_0": quant.Q8_0}
+
+
+def random_blocks(rng, kind, n, k):
+    """Random block bytes with a sane f16 scale: as good as encoded weights for timing."""
+    w = rng.integers(0, 256, (n * k // 32, quant.BLOCK_BYTES[kind]), dtype=np.uint8)
+    w[:, 1] = 0x20
+    return w.reshape(-1)
+
+
+def op_sweep(args):
+    """Isolated kernels on one GPU, one JSON line per case (the second and third benchmark
+    configurations: quantized GEMV at B in {1,2,4,8}, prefill GEMM at M in {128,512,2048})."""
+    from rustgrad_b200 import session
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    tflops = float(peaks.get("bf16_tflops", 1590.0))
+    rng = np.random.default_rng(2)
+    shapes = [tuple(int(v) for v in sh.split("x")) for sh in args.shapes.split(",")]
+    for name in args.types.split(","):
+        kind = GGML[name]
+        for n, k in shapes:
+            w = random_blocks(rng, kind, n, k)
+            if args.workload == "gemv":
+                rotate = max(2, int(600e6 // w.size) + 1)  # distinct weight copies in turn: every launch reads HBM
+                for b in (int(v) for v in args.batches.split(",")):
+                    x = rng.standard_normal((b, k)).astype(np.float32)
+                    _, ms = session.qmatmul_bench(kind, w, n, k, x, rotate=rotate, iters=args.iters, warmup=args.op_warmup)
+                    nbytes = w.size + 4 * b * k + 4 * b * n
+                    print(json.dumps({"op": "qgemv", "type": name, "n": n, "k": k, "batch": b, "us": ms * 1e3,
+                                      "algorithmic_bytes": nbytes, "gbs": nbytes / ms / 1e6,
+                                      "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm}), flush=True)
+            else:
+                for m in (int(v) for v in args.tokens.split(",")):
+                    x = rng.standard_normal((m, k)).astype(np.float32)
+                    for mode in (int(v) for v in args.modes.split(",")):
+                        _, ms = session.qgemm(kind, w, n, k, x, iters=args.iters, operand_mode=mode)
+                        fl = 2.0 * m * n * k
+                        print(json.dumps({"op": "qgemm", "type": name, "n": n, "k": k, "tokens": m,
+                                          "operands": ["bf16", "f16", "f16 hi+lo (3 products)"][mode], "us": ms * 1e3,
+                                          "tflops": fl / ms / 1e9, "frac_of_measured_bf16_burst": fl / ms / 1e9 / tflops,
+                                          "tensor_work_frac": fl * (3 if mode == 2 else 1) / ms / 1e9 / tflops}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemm"])
+    ap.add_argument("--shapes", default="4096x4096,14336x4096,4096x14336,128256x4096")
+    ap.add_argument("--types", default="q4_0,q8_0")
+    ap.add_argument("--batches", default="1,2,4,8")
+    ap.add_argument("--tokens", default="128,512,2048")
+    ap.add_argument("--modes", default="0,1,2")
+    ap.add_argument("--iters", type=int, default=40)
+    ap.add_argument("--op-warmup", type=int, default=5)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
@@ -161,6 +215,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.workload != "decode":
+        return op_sweep(args)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
