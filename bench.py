@@ -34,9 +34,11 @@ import numpy as np  # noqa: E402
 from rustgrad_b200 import quant, synth  # noqa: E402
 
 PREFILL = 2048
-# dram__bytes_read.sum + dram__bytes_write.sum of one qgemv launch on the gate/up shape, from the
-# ncu capture summarised in profiles/ (None until captured)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one integer-GEMV launch, from
+# the ncu captures summarised in profiles/: 33.081 MB / 33.104 MB on Q4_0 [14336, 4096] and
+# 580.1 MB / 558.7 MB on Q8_0 [128256, 4096].  DRAM traffic grows in proportion to the bytes a launch
+# streams, so the traffic of the average launch of a step is its algorithmic bytes times this ratio.
+NCU_TRAFFIC_OVER_ALGORITHMIC = {"q4_0": 0.999, "q8_0": 1.038}
 
 
 def measured_peaks():
@@ -333,7 +335,9 @@ def main():
         "clocks": clocks.summary,
         "roofline": {"bound": "hbm", "kernel": "qgemv_kernel (all quantized GEMV launches of a step)", "achieved": achieved,
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak if achieved else None,
-                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "launches_per_step": gemv_launches,
+                     "traffic": gemv_bytes / gemv_launches * NCU_TRAFFIC_OVER_ALGORITHMIC["q4_0"],
+                     "traffic_note": "bytes per average GEMV launch: algorithmic bytes x the dram/algorithmic ratio of the ncu capture",
+                     "launches_per_step": gemv_launches,
                      "algorithmic_bytes_per_step": gemv_bytes, "kernel_ms_per_step": gemv_ms,
                      "step_bytes_over_step_time_gbs": (gemv_bytes / (ms_per_step * 1e-3) / 1e9)},
         "profile_ms_per_step": {k: v["ms_per_step"] for k, v in prof.items()},

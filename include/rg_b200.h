@@ -82,7 +82,9 @@ typedef struct {
   int32_t reserved[8];    /* reserved[0] == 1: never take the fused small-batch decode path nor the
                            * tensor-core path; reserved[1]: operand mode of the tensor-core path as
                            * in rg_b200_qgemm, offset by one (0 = default = compensated half,
-                           * 1 = bf16, 2 = half, 3 = compensated half) */
+                           * 1 = bf16, 2 = half, 3 = compensated half); reserved[2] == 1: batch-1
+                           * decode as one persistent cooperative kernel per step (optional; the
+                           * default is one launch per projection) */
 } rg_options;
 
 /* Per-run evidence in the vocabulary of MetalDeviceRunReport

@@ -1,0 +1,336 @@
+// Decode attention for one or two new tokens in ONE launch: RoPE of q and k, KV-cache append,
+// split-context GQA attention and the combine of the spans
+// (src/models/transformer/layer.rs:349-421 with src/ir/attention.rs:946-981,1157-1240; mask of
+// layer.rs:374-380 for a single new row; softmax pieces of attention.rs:495-558).
+//
+// One CTA per (context span, kv head, column).  The CTA rotates the query heads that share its kv
+// head into shared memory; the CTA whose span ends with the new token also rotates k, writes the k
+// and v rows into the cache and into its own staging buffer (that row is produced here, so it is
+// not part of the bulk copy).  K and V spans are staged by two bulk copies of the TMA engine.  Each
+// CTA leaves [max, sum, out[hd]] per head in a scratch; the last CTA of a (column, kv head) to
+// arrive (one atomic counter) combines the spans and writes the attention output, so no second
+// launch is needed.  The span length adapts to the position so that short contexts still spread
+// over the SMs.  Waits are bounded (status word).
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include "../../include/rg_b200.h"
+#include "kernels.h"
+#include "rg_device.cuh"
+
+namespace rg {
+namespace {
+
+constexpr int THREADS = 256;
+constexpr int WARPS = THREADS / 32;
+constexpr int MAX_G = 8;
+constexpr int STAGE_BYTES = 65536;  // K span + V span
+constexpr int SC_POS = 256;         // most positions a span can hold (head_dim 64, f16)
+
+template <typename KV>
+__device__ __forceinline__ KV to_kv(float v);
+template <>
+__device__ __forceinline__ float to_kv<float>(float v) {
+  return v;
+}
+template <>
+__device__ __forceinline__ __half to_kv<__half>(float v) {
+  return __float2half_rn(v);
+}
+template <int N>
+__device__ __forceinline__ void load_n(const float *p, float (&v)[N]) {
+#pragma unroll
+  for (int i = 0; i < N / 4; ++i) {
+    const float4 f = reinterpret_cast<const float4 *>(p)[i];
+    v[4 * i] = f.x, v[4 * i + 1] = f.y, v[4 * i + 2] = f.z, v[4 * i + 3] = f.w;
+  }
+}
+template <int N>
+__device__ __forceinline__ void load_n(const __half *p, float (&v)[N]) {
+  if constexpr (N == 8) {
+    const uint4 u = *reinterpret_cast<const uint4 *>(p);
+    const __half2 *h = reinterpret_cast<const __half2 *>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h[i]);
+      v[2 * i] = f.x, v[2 * i + 1] = f.y;
+    }
+  } else {
+    const uint2 u = *reinterpret_cast<const uint2 *>(p);
+    const __half2 *h = reinterpret_cast<const __half2 *>(&u);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float2 f = __half22float2(h[i]);
+      v[2 * i] = f.x, v[2 * i + 1] = f.y;
+    }
+  }
+}
+__device__ __forceinline__ float2 load2(const float *p) { return *reinterpret_cast<const float2 *>(p); }
+__device__ __forceinline__ float2 load2(const __half *p) { return __half22float2(*reinterpret_cast<const __half2 *>(p)); }
+
+__host__ __device__ constexpr int span_max(int hd, int kv_bytes) { return STAGE_BYTES / (2 * hd * kv_bytes); }
+
+// Span length for a context of `total` positions: spread over `per_head` CTAs, multiples of 16.
+__host__ __device__ inline int span_for(int total, int per_head, int smax) {
+  int span = (((total + per_head - 1) / per_head) + 15) & ~15;
+  if (span < 16) span = 16;
+  return span > smax ? smax : span;
+}
+
+template <typename KV, int HD>
+__global__ void __launch_bounds__(THREADS) attn_fused_kernel(const FusedAttnArgs A, int per_head, int *status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  constexpr int SMAX = span_max(HD, (int)sizeof(KV));
+  constexpr int DPL = HD / 16;  // dims per lane in the score phase
+  const int c = blockIdx.z, kvh = blockIdx.y, sp = blockIdx.x;
+  const int pos = A.col_pos[c], seq = A.col_seq[c];
+  const int total = pos + 1;
+  const int span = span_for(total, per_head, SMAX);
+  const int nspl = (total + span - 1) / span;
+  if (sp >= nspl) return;
+  const int G = A.heads / A.kv_heads;
+  const int p0 = sp * span;
+  const int np = min(span, total - p0);
+  const bool has_new = (p0 + np == total);
+  const int ncopy = has_new ? np - 1 : np;
+
+  extern __shared__ __align__(128) uint8_t smem[];
+  KV *ks = reinterpret_cast<KV *>(smem);
+  KV *vs = ks + (size_t)SMAX * HD;
+  float *qs = reinterpret_cast<float *>(smem + STAGE_BYTES);  // [G][HD]
+  float *sc = qs + MAX_G * HD;                                // [SMAX][MAX_G]
+  float *ml = sc + SC_POS * MAX_G;                            // [G][2]
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int dead_flag, last_flag;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    dead_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  KV *kc = static_cast<KV *>(A.k_cache), *vc = static_cast<KV *>(A.v_cache);
+  const size_t row0 = ((size_t)seq * A.kv_heads + kvh) * A.ctx + p0;
+  if (tid == 0 && ncopy > 0) {
+    const uint32_t bytes = (uint32_t)((size_t)ncopy * HD * sizeof(KV));
+    mbar_expect_tx(&bar, 2 * bytes);
+    bulk_g2s(ks, kc + row0 * HD, bytes, &bar);
+    bulk_g2s(vs, vc + row0 * HD, bytes, &bar);
+  }
+  const int qw = A.heads * HD, kw = A.kv_heads * HD;
+  const float *row = A.qkv + (size_t)c * (qw + 2 * kw);
+  const float *ct = A.cos_t + (size_t)pos * (HD / 2), *st = A.sin_t + (size_t)pos * (HD / 2);
+  // pairs (2i, 2i+1) of the projection rotate into (i, HD/2 + i) (layer.rs:349-371)
+  for (int it = tid; it < G * (HD / 2); it += THREADS) {
+    const int gq = it / (HD / 2), i = it - gq * (HD / 2);
+    const float2 xv = reinterpret_cast<const float2 *>(row + (size_t)(kvh * G + gq) * HD)[i];
+    const float cs = ct[i], sn = st[i];
+    qs[gq * HD + i] = __fsub_rn(__fmul_rn(xv.x, cs), __fmul_rn(xv.y, sn));
+    qs[gq * HD + HD / 2 + i] = __fadd_rn(__fmul_rn(xv.y, cs), __fmul_rn(xv.x, sn));
+  }
+  if (has_new) {
+    for (int i = tid; i < HD / 2; i += THREADS) {
+      const float2 xv = reinterpret_cast<const float2 *>(row + qw + (size_t)kvh * HD)[i];
+      const float cs = ct[i], sn = st[i];
+      const KV y1 = to_kv<KV>(__fsub_rn(__fmul_rn(xv.x, cs), __fmul_rn(xv.y, sn)));
+      const KV y2 = to_kv<KV>(__fadd_rn(__fmul_rn(xv.y, cs), __fmul_rn(xv.x, sn)));
+      KV *g = kc + (row0 + (np - 1)) * HD, *s = ks + (size_t)(np - 1) * HD;
+      g[i] = y1, g[HD / 2 + i] = y2;
+      s[i] = y1, s[HD / 2 + i] = y2;
+    }
+    for (int j = tid; j < HD; j += THREADS) {
+      const KV v = to_kv<KV>(row[qw + kw + (size_t)kvh * HD + j]);
+      vc[(row0 + (np - 1)) * HD + j] = v;
+      vs[(size_t)(np - 1) * HD + j] = v;
+    }
+  }
+  __syncthreads();
+  if (ncopy > 0) mbar_wait_bounded(&bar, 0, &dead_flag, status);
+  // ---- scores: 16 lanes per position; scale = 1 / f32(sqrt(hd)) applied as a division (attention.rs:1183-1188)
+  const float inv_scale = (float)(1.0 / (1.0 / sqrt((double)HD)));
+  {
+    const int sub = lane & 15, hi = lane >> 4;
+    for (int gq = 0; gq < G; ++gq) {
+      float qr[DPL];
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) qr[i] = qs[gq * HD + sub * DPL + i];
+      // four positions per half-warp in flight: their loads, products and shuffles interleave
+      for (int base = 0; base < np; base += 8 * WARPS) {
+        float dot[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int p = base + u * 2 * WARPS + warp * 2 + hi;
+          dot[u] = 0.0f;
+          if (p < np) {
+            float kr[DPL];
+            load_n<DPL>(ks + (size_t)p * HD + sub * DPL, kr);
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) dot[u] = fmaf(qr[i], kr[i], dot[u]);
+          }
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1)
+#pragma unroll
+          for (int u = 0; u < 4; ++u) dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], o);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int p = base + u * 2 * WARPS + warp * 2 + hi;
+          if (sub == 0 && p < np) sc[p * MAX_G + gq] = __fdiv_rn(dot[u], inv_scale);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (warp < G) {
+    const int gq = warp;
+    float m = -INFINITY;
+    for (int p = lane; p < np; p += 32) m = fmaxf(m, sc[p * MAX_G + gq]);
+    m = warp_max(m);
+    float l = 0.0f;
+    for (int p = lane; p < np; p += 32) {
+      const float e = exp2f(__fmul_rn(__fsub_rn(sc[p * MAX_G + gq], m), 1.44269504088896340736f));
+      sc[p * MAX_G + gq] = e;
+      l += e;
+    }
+    l = warp_sum(l);
+    if (lane == 0) {
+      ml[gq * 2] = m;
+      ml[gq * 2 + 1] = l;
+    }
+  }
+  __syncthreads();
+  // ---- P.V: one thread per (head, pair of dims)
+  for (int o = tid; o < G * (HD / 2); o += THREADS) {
+    const int gq = o / (HD / 2), dp = o - gq * (HD / 2);
+    float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll 8
+    for (int p = 0; p < np; ++p) {
+      const float pr = sc[p * MAX_G + gq];
+      const float2 vv = load2(vs + (size_t)p * HD + 2 * dp);
+      a0 = fmaf(pr, vv.x, a0);
+      a1 = fmaf(pr, vv.y, a1);
+    }
+    float *dst = A.scratch + (((size_t)c * A.heads + (size_t)(kvh * G + gq)) * A.max_splits + sp) * (HD + 2);
+    dst[2 + 2 * dp] = a0;
+    dst[2 + 2 * dp + 1] = a1;
+    if (dp == 0) {
+      dst[0] = ml[gq * 2];
+      dst[1] = ml[gq * 2 + 1];
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    unsigned *counter = A.counters + (size_t)c * A.kv_heads + kvh;
+    int last = 1;
+    if (nspl > 1) {
+      __threadfence();  // this CTA's partial results before its arrival
+      const unsigned old = atomicAdd(counter, 1u);
+      last = (old == (unsigned)(nspl - 1));
+      if (last) {
+        *counter = 0u;    // every arrival of this step has happened
+        __threadfence();  // the other spans' results before the combine reads them
+      }
+    }
+    last_flag = last;
+  }
+  __syncthreads();
+  if (!last_flag) return;
+  // ---- combine.  Span headers (max, sum) go to shared memory in one round of independent loads;
+  // the weights follow from them, and every output thread then fetches its column in batches of
+  // eight loads in flight (a dependent load-use loop would pay the L2 latency once per span).
+  float *hdr = sc;  // [G][nspl][2] then weights [G][nspl]; the scores are no longer needed
+  float *wts = sc + 2 * G * nspl;  // 3 * G * nspl floats in all: the launcher caps the number of spans
+  for (int i = tid; i < G * nspl * 2; i += THREADS) {
+    const int gq = i / (nspl * 2), r = i - gq * nspl * 2;
+    hdr[i] = __ldcg(A.scratch + (((size_t)c * A.heads + (size_t)(kvh * G + gq)) * A.max_splits + (r >> 1)) * (HD + 2) + (r & 1));
+  }
+  __syncthreads();
+  if (warp < G) {
+    const int gq = warp;
+    float M = -INFINITY;
+    for (int s = lane; s < nspl; s += 32) M = fmaxf(M, hdr[(gq * nspl + s) * 2]);
+    M = warp_max(M);
+    float L = 0.0f;
+    for (int s = lane; s < nspl; s += 32) {
+      const float wgt = exp2f(__fmul_rn(__fsub_rn(hdr[(gq * nspl + s) * 2], M), 1.44269504088896340736f));
+      wts[gq * nspl + s] = wgt;
+      L = fmaf(hdr[(gq * nspl + s) * 2 + 1], wgt, L);
+    }
+    L = warp_sum(L);
+    if (lane == 0) ml[gq * 2 + 1] = __frcp_rn(L);
+  }
+  __syncthreads();
+  for (int o = tid; o < G * HD; o += THREADS) {
+    const int gq = o / HD, d = o - gq * HD;
+    const float *base = A.scratch + ((size_t)c * A.heads + (size_t)(kvh * G + gq)) * A.max_splits * (HD + 2) + 2 + d;
+    float acc = 0.0f;
+    for (int s0 = 0; s0 < nspl; s0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (s0 + j < nspl) ? __ldcg(base + (size_t)(s0 + j) * (HD + 2)) : 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (s0 + j < nspl) acc = fmaf(v[j], wts[gq * nspl + s0 + j], acc);
+    }
+    A.out[(size_t)c * A.heads * HD + (size_t)(kvh * G + gq) * HD + d] = __fmul_rn(acc, ml[gq * 2 + 1]);
+  }
+}
+
+template <typename KV, int HD>
+cudaError_t launch_t(const FusedAttnArgs &a, const LaunchCfg &cfg) {
+  auto kernel = attn_fused_kernel<KV, HD>;
+  constexpr size_t smem = STAGE_BYTES + (MAX_G * HD + SC_POS * MAX_G + 2 * MAX_G) * sizeof(float);
+  static_assert(span_max(HD, (int)sizeof(KV)) <= SC_POS, "score buffer");
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr_done = true;
+  }
+  const int sms = cfg.sm_count > 0 ? cfg.sm_count : 148;
+  const int per_head = fused_attn_per_head(sms, a.kv_heads, a.cols);
+  cudaLaunchConfig_t lc{};
+  lc.gridDim = dim3((unsigned)a.max_splits, (unsigned)a.kv_heads, (unsigned)a.cols);
+  lc.blockDim = dim3(THREADS);
+  lc.dynamicSmemBytes = smem;
+  lc.stream = cfg.stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = cfg.pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&lc, kernel, a, per_head, cfg.status);
+}
+
+}  // namespace
+
+int fused_attn_per_head(int sm_count, int kv_heads, int cols) {
+  const int n = sm_count / (kv_heads * (cols > 0 ? cols : 1));
+  return n > 1 ? n : 1;
+}
+
+int fused_attn_max_splits(int ctx, int hd, bool kv_f32, int sm_count, int kv_heads) {
+  const int smax = span_max(hd, kv_f32 ? 4 : 2);
+  const int per_head = fused_attn_per_head(sm_count, kv_heads, 1);
+  const int by_ctx = (ctx + smax - 1) / smax;
+  return (per_head > by_ctx ? per_head : by_ctx) + 1;
+}
+
+int fused_attn_split_cap() { return SC_POS / 3; }  // span headers + weights of all heads fit the score buffer
+
+bool fused_attention_supported(int heads, int kv_heads, int hd) {
+  if (kv_heads < 1 || heads % kv_heads) return false;
+  const int g = heads / kv_heads;
+  return (hd == 64 || hd == 128) && g >= 1 && g <= MAX_G;
+}
+
+cudaError_t launch_attention_fused(const FusedAttnArgs &a, const LaunchCfg &cfg) {
+  if (!fused_attention_supported(a.heads, a.kv_heads, a.hd) || a.cols < 1 || !a.counters || !a.scratch || !a.out ||
+      a.max_splits > fused_attn_split_cap())
+    return cudaErrorInvalidValue;
+  if (a.hd == 128) return a.kv_f32 ? launch_t<float, 128>(a, cfg) : launch_t<__half, 128>(a, cfg);
+  return a.kv_f32 ? launch_t<float, 64>(a, cfg) : launch_t<__half, 64>(a, cfg);
+}
+
+}  // namespace rg

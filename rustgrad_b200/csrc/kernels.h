@@ -91,6 +91,57 @@ cudaError_t launch_rmsnorm16(const float *x, int ldx, const float *w, int d, flo
                              const LaunchCfg &cfg);
 cudaError_t launch_swiglu16(const float *g, const float *u, int n, int ld, int rows, const Operand16 &y, const LaunchCfg &cfg);
 
+// ---- Whole-step persistent decode kernel (batch 1, one GPU): decode_mega.cu -------------------
+enum MegaKind { MEGA_EMBED = 0, MEGA_GEMV = 1, MEGA_ATTN = 2, MEGA_FINISH = 3 };
+enum { MEGA_OP_LOGITS = 1 };  // MegaOp::flags: the rows are logits (track arg-max candidates)
+// One phase of the step.  Phases run in order with a grid barrier between them.
+struct MegaOp {
+  int32_t kind = MEGA_GEMV;
+  int32_t type = 0;  // GEMV: RG_TYPE_Q4_0 or RG_TYPE_Q8_0
+  int32_t epi = EPI_STORE;
+  int32_t nseg = 1;
+  int32_t seg_rows[3] = {0, 0, 0};
+  int32_t n_rows = 0;  // virtual rows (EPI_SWIGLU: rows of the gate matrix)
+  int32_t kb = 0;      // K / 32
+  int32_t map0 = 0;    // index of the first of three tensor maps
+  int32_t layer = 0;   // MEGA_ATTN: which KV cache
+  int32_t flags = 0;
+  const float *x = nullptr;       // GEMV input vector (f32, written by an earlier phase)
+  const float *norm_w = nullptr;  // RMSNorm weight applied while packing x; nullptr = none
+  float *y = nullptr;             // GEMV output vector
+};
+struct MegaParams {
+  const MegaOp *ops = nullptr;  // device array
+  int n_ops = 0;
+  const void *maps = nullptr;  // device array of tensor maps, 128 bytes each
+  int32_t *tokens = nullptr, *pos = nullptr;
+  const int32_t *seq = nullptr;
+  int32_t *step = nullptr, *history = nullptr, *d_ids = nullptr;
+  unsigned *bar_counter = nullptr, *bar_base = nullptr;
+  int *gdead = nullptr;  // set by the first CTA whose wait gave up
+  int *status = nullptr;
+  int d_model = 0, heads = 0, kv_heads = 0, ctx = 0;
+  float eps = 0.0f;
+  const float *cos_t = nullptr, *sin_t = nullptr;
+  void *const *k_cache = nullptr;  // device arrays of per-layer cache pointers
+  void *const *v_cache = nullptr;
+  float *qkv = nullptr, *attn_out = nullptr, *attn_scratch = nullptr;
+  unsigned *attn_counters = nullptr;  // [kv_heads], zero between phases
+  int max_splits = 0;
+  float *cand_val = nullptr;  // [grid] arg-max candidates
+  int *cand_idx = nullptr, *cand_bad = nullptr;
+  const uint8_t *embed = nullptr;
+  int embed_type = 0;
+  float *x = nullptr;
+  int u_bytes = 0, slots = 0, advance = 0;
+  unsigned long long *prof = nullptr;  // nullable: [gemv, attention, other, barrier] ns of CTA 0
+};
+size_t mega_tensor_map_bytes();
+cudaError_t mega_make_map(void *map_out, int type, const uint8_t *w, int rows, int k);
+bool mega_plan_smem(int max_k, int *u_bytes, int *slots, size_t *smem);
+int mega_max_splits(int ctx, int grid, int kv_heads, bool kv_f32);
+cudaError_t launch_decode_mega(const MegaParams &P, bool kv_f32, size_t smem, int grid, cudaStream_t stream);
+
 // Dense (F32/F16) weight GEMV for tensors the block formats cannot hold (K % 32 != 0) or that a
 // file stores dense.  x is plain f32 [batch, ldx]; same epilogues (EPI_SWIGLU unsupported).
 struct DenseGemvArgs {
@@ -154,6 +205,28 @@ constexpr int ATTN_SPAN = 128;  // context positions per CTA of the split kernel
 bool attention_supported(int heads, int kv_heads, int hd);  // hd in {64,128}, heads/kv_heads in {1,2,4,8}
 size_t attn_scratch_floats(int cols, int heads, int hd, int ctx);
 cudaError_t launch_attention(const AttnArgs &a, const LaunchCfg &cfg);
+
+// RoPE + KV append + split-context attention + combine in one launch (attn_fused.cu).  qkv rows are
+// the raw projections [cols, qw + 2*kw]; out is [cols, heads*hd] f32.  scratch holds
+// cols * heads * max_splits * (hd + 2) floats; counters (cols * kv_heads words) must be zero before
+// the first launch and are left zero by every launch.
+struct FusedAttnArgs {
+  const float *qkv = nullptr;
+  int cols = 0, heads = 0, kv_heads = 0, hd = 0, ctx = 0;
+  const int32_t *col_seq = nullptr, *col_pos = nullptr;
+  const float *cos_t = nullptr, *sin_t = nullptr;
+  void *k_cache = nullptr, *v_cache = nullptr;
+  bool kv_f32 = false;
+  float *scratch = nullptr;
+  int max_splits = 0;
+  unsigned *counters = nullptr;
+  float *out = nullptr;
+};
+bool fused_attention_supported(int heads, int kv_heads, int hd);
+int fused_attn_per_head(int sm_count, int kv_heads, int cols);
+int fused_attn_max_splits(int ctx, int hd, bool kv_f32, int sm_count, int kv_heads);
+int fused_attn_split_cap();
+cudaError_t launch_attention_fused(const FusedAttnArgs &a, const LaunchCfg &cfg);
 
 // Greedy selection per column with the reference's rules (generation.rs:260-287): lowest id wins
 // ties, any non-finite logit yields -1.  Also advances: next_tokens[c] = id, pos[c] += 1 when

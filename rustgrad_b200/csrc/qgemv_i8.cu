@@ -104,6 +104,11 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
       : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
 }
+__device__ __forceinline__ void mma_s8_acc(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 // Q4_0 word -> s8 bytes 16*(n-8): low nibbles (elements 4t..) and high nibbles (elements 16+4t..)
 __device__ __forceinline__ void q4_to_s8(uint32_t q, uint32_t &lo, uint32_t &hi) {
   lo = ((q << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
@@ -132,6 +137,26 @@ __device__ __forceinline__ void load_slot(uint32_t a, uint32_t s, uint32_t (&w)[
   sc[1] = lds16<R0 + G::BB>(s);
 }
 
+// Batch-1 variant: `s` already points at the scale of the block this lane scales; one scale per row.
+template <int QT, int RSLOT>
+__device__ __forceinline__ void load_slot_b1(uint32_t a, uint32_t s, uint32_t (&w)[6], uint32_t (&sc)[2]) {
+  using G = Geo<QT>;
+  constexpr int R0 = ((RSLOT >> 1) * 16 + (RSLOT & 1) * 8) * G::RS;
+  if constexpr (G::Q4) {
+    w[0] = lds32<R0>(a);
+    w[1] = lds32<R0 + 4>(a);
+    w[2] = lds32<R0 + 20>(a);
+  } else {
+    w[0] = lds32<R0>(a);
+    w[1] = lds32<R0 + 4>(a);
+    w[2] = lds32<R0 + 16>(a);
+    w[3] = lds32<R0 + 20>(a);
+    w[4] = lds32<R0 + 36>(a);
+    w[5] = lds32<R0 + 52>(a);
+  }
+  sc[0] = lds16<R0>(s);
+}
+
 // A operands of the even and the odd block of a pair for one row slot: {k 0..15, k 16..31}
 template <int QT>
 __device__ __forceinline__ void expand(const uint32_t (&w)[6], uint32_t (&ae)[2], uint32_t (&ao)[2]) {
@@ -155,7 +180,13 @@ __device__ __forceinline__ uint32_t digit_offset(int S, int kb, int c, int e) {
   return (uint32_t)((((kb * S + c) * 4 + t) * 8) + r * 4 + i);
 }
 
-template <int QT, int EPI>
+// B1 (batch 1): the four digit columns leave half of the MMA's eight columns idle, so the even and
+// the odd block of a pair share one accumulator tile: columns 0-3 take the even block's digits
+// (B rows k < 16 only), columns 4-7 the odd block's (B rows k >= 16 only), and the A operand carries
+// the even block in k < 16 and the odd block in k >= 16.  Two MMAs (low / high halves of both blocks)
+// accumulate in place; afterwards lanes t < 2 scale the even block and lanes t >= 2 the odd one, so
+// the per-lane scale / convert / accumulate work is half of the general layout's.
+template <int QT, int EPI, bool B1>
 __global__ void __launch_bounds__(THREADS, 1)
     qgemv_i8_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                     const __grid_constant__ CUtensorMap map2, const Params P) {
@@ -311,9 +342,10 @@ __global__ void __launch_bounds__(THREADS, 1)
   asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
 
   const int g = lane >> 2, t = lane & 3;
-  const bool col_live = g < S;              // this lane's B column carries a digit
-  const int my_batch = t >> 1;              // batch of this lane's accumulator columns
-  const bool acc_live = my_batch < P.batch;
+  const bool col_live = B1 ? true : g < S;  // this lane's B column carries a digit
+  const int my_batch = B1 ? 0 : t >> 1;     // batch of this lane's accumulator columns
+  const bool acc_live = B1 ? true : my_batch < P.batch;
+  const int blk_sel = t >> 1;               // B1: block of the pair this lane scales (0 even, 1 odd)
   float acc[2][2];  // [m-tile][row g / row g+8]
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt) acc[mt][0] = acc[mt][1] = 0.0f;
@@ -321,10 +353,12 @@ __global__ void __launch_bounds__(THREADS, 1)
   int stage = 0, c = 0, grp = 0;
   uint32_t phase = 0;
   const uint32_t smem_stage0 = smem_u32(stage0);
-  const uint32_t xs_lane = smem_u32(xs) + (uint32_t)((g * 4 + t) * 8);
-  const uint32_t sb_lane = smem_u32(sb) + (uint32_t)(my_batch * 4);
+  // B1: lanes g >= 4 feed the odd block's digits (column g - 4 of the next block)
+  const uint32_t xs_lane = B1 ? smem_u32(xs) + (uint32_t)(((g & 3) * 4 + t) * 8 + (g >> 2) * 128)
+                              : smem_u32(xs) + (uint32_t)((g * 4 + t) * 8);
+  const uint32_t sb_lane = B1 ? smem_u32(sb) + (uint32_t)(blk_sel * 4) : smem_u32(sb) + (uint32_t)(my_batch * 4);
   const uint32_t lane_w_off = (uint32_t)(g * G::RS + t * 4);
-  const uint32_t lane_s_off = (uint32_t)(g * G::RS);
+  const uint32_t lane_s_off = B1 ? (uint32_t)(g * G::RS + blk_sel * G::BB) : (uint32_t)(g * G::RS);
   for (int u = 0; u < units; ++u) {
     const int nb = min(G::KC, P.kb - c * G::KC);
     mbar_wait_bounded(&full[stage], phase, dead, P.status);
@@ -334,6 +368,30 @@ __global__ void __launch_bounds__(THREADS, 1)
     int gb = c * G::KC + 2 * warp;  // global block index of the pair's even block
     for (int p = warp; 2 * p < nb; p += CW, aw += CW * 2 * G::BB, as += CW * 2 * G::BB, gb += 2 * CW) {
       uint32_t wq[4][6], sc[4][2];
+      if constexpr (B1) {
+        load_slot_b1<QT, 0>(aw, as, wq[0], sc[0]);
+        load_slot_b1<QT, 1>(aw, as, wq[1], sc[1]);
+        load_slot_b1<QT, 2>(aw, as, wq[2], sc[2]);
+        load_slot_b1<QT, 3>(aw, as, wq[3], sc[3]);
+        const uint2 xv = lds64(xs_lane + (uint32_t)(gb * 128));
+        const float sv = ldsf(sb_lane + (uint32_t)(gb * 4));
+        const bool ev = g < 4;
+        const uint32_t b_lo0 = ev ? xv.x : 0u, b_lo1 = ev ? 0u : xv.x;  // MMA 1: low halves of both blocks
+        const uint32_t b_hi0 = ev ? xv.y : 0u, b_hi1 = ev ? 0u : xv.y;  // MMA 2: high halves
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          uint32_t ae[2][2], ao[2][2];
+          expand<QT>(wq[mt * 2], ae[0], ao[0]);
+          expand<QT>(wq[mt * 2 + 1], ae[1], ao[1]);
+          int c[4];
+          mma_s8(c, ae[0][0], ae[1][0], ao[0][0], ao[1][0], b_lo0, b_lo1);
+          mma_s8_acc(c, ae[0][1], ae[1][1], ao[0][1], ao[1][1], b_hi0, b_hi1);
+          const float f0 = (float)(c[0] + (c[1] << 8)), f1 = (float)(c[2] + (c[3] << 8));
+          acc[mt][0] = fmaf(half_bits_to_float(sc[mt * 2][0]) * sv, f0, acc[mt][0]);
+          acc[mt][1] = fmaf(half_bits_to_float(sc[mt * 2 + 1][0]) * sv, f1, acc[mt][1]);
+        }
+        continue;
+      }
       load_slot<QT, 0>(aw, as, wq[0], sc[0]);
       load_slot<QT, 1>(aw, as, wq[1], sc[1]);
       load_slot<QT, 2>(aw, as, wq[2], sc[2]);
@@ -388,8 +446,13 @@ __global__ void __launch_bounds__(THREADS, 1)
           float lo = 0.0f, hi = 0.0f;
 #pragma unroll
           for (int w = 0; w < CW; ++w) {
-            lo += red[(w * R + rr) * 4 + 2 * b];
-            hi += red[(w * R + rr) * 4 + 2 * b + 1];
+            if constexpr (B1) {  // slots: even block low / high digits, odd block low / high digits
+              lo += red[(w * R + rr) * 4] + red[(w * R + rr) * 4 + 2];
+              hi += red[(w * R + rr) * 4 + 1] + red[(w * R + rr) * 4 + 3];
+            } else {
+              lo += red[(w * R + rr) * 4 + 2 * b];
+              hi += red[(w * R + rr) * 4 + 2 * b + 1];
+            }
           }
           return fmaf(hi, 65536.0f, lo) * A_SCALE;
         };
@@ -443,7 +506,7 @@ cudaError_t make_map(CUtensorMap *map, const uint8_t *w, int rows, size_t row_by
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <int QT, int EPI>
+template <int QT, int EPI, bool B1>
 cudaError_t launch_t(const GemvI8Args &a, const LaunchCfg &cfg) {
   using G = Geo<QT>;
   Params P{};
@@ -486,7 +549,7 @@ cudaError_t launch_t(const GemvI8Args &a, const LaunchCfg &cfg) {
     cudaError_t e = make_map(&maps[i], a.w[src], a.seg_rows[src], row_bytes, G::RS);
     if (e != cudaSuccess) return e;
   }
-  auto kernel = qgemv_i8_kernel<QT, EPI>;
+  auto kernel = qgemv_i8_kernel<QT, EPI, B1>;
   static bool attr_done = false;  // per instantiation
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_FULL);
@@ -511,9 +574,9 @@ cudaError_t launch_t(const GemvI8Args &a, const LaunchCfg &cfg) {
 template <int QT>
 cudaError_t launch_e(const GemvI8Args &a, const LaunchCfg &cfg) {
   switch (a.epi) {
-    case EPI_STORE: return launch_t<QT, EPI_STORE>(a, cfg);
-    case EPI_RESIDUAL: return launch_t<QT, EPI_RESIDUAL>(a, cfg);
-    case EPI_SWIGLU: return launch_t<QT, EPI_SWIGLU>(a, cfg);
+    case EPI_STORE: return a.batch == 1 ? launch_t<QT, EPI_STORE, true>(a, cfg) : launch_t<QT, EPI_STORE, false>(a, cfg);
+    case EPI_RESIDUAL: return a.batch == 1 ? launch_t<QT, EPI_RESIDUAL, true>(a, cfg) : launch_t<QT, EPI_RESIDUAL, false>(a, cfg);
+    case EPI_SWIGLU: return a.batch == 1 ? launch_t<QT, EPI_SWIGLU, true>(a, cfg) : launch_t<QT, EPI_SWIGLU, false>(a, cfg);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -83,6 +83,8 @@ class CudaSessionTarget:
     disable_graph: bool = False
     disable_pdl: bool = False
     general_path_only: bool = False  # never take the fused small-batch decode path (tests)
+    gemm_operands: str = ""  # tensor-core path operands: "" (compensated f16), "bf16", "f16", "f16x3"
+    persistent_decode: bool = False  # batch-1 decode as one cooperative kernel per step (off by default)
     _opts: Options = field(default=None, repr=False)
 
     def options(self) -> Options:
@@ -91,6 +93,8 @@ class CudaSessionTarget:
         o.kv_f32, o.tp_rank, o.tp_world = int(self.kv_f32), self.tp_rank, self.tp_world
         o.disable_graph, o.disable_pdl = int(self.disable_graph), int(self.disable_pdl)
         o.reserved[0] = int(self.general_path_only)
+        o.reserved[1] = {"": 0, "bf16": 1, "f16": 2, "f16x3": 3}[self.gemm_operands]
+        o.reserved[2] = int(self.persistent_decode)
         if self.tp_world > 1:
             if len(self.nccl_id) != 128:
                 raise InvalidArgument(1, "tensor parallelism needs the 128-byte NCCL id of rank 0")  # noqa: F821

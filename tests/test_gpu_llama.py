@@ -181,6 +181,51 @@ def test_tensor_core_path_for_long_prompts_and_wide_decode_batches():
         toks = nxt
 
 
+@pytest.mark.parametrize("kv_f32", [True, False], ids=["kv_f32", "kv_f16"])
+def test_persistent_decode_kernel_matches_multi_launch_path_and_checker(kv_f32):
+    """Batch-1 decode of a head_dim-128 model can run as one persistent kernel per step (an option);
+    the same steps as separate launches and the CPU checker must agree, across several context spans."""
+    cfg = synth.scaled(synth.TINY, d_model=512, n_heads=8, n_kv_heads=2, head_dim=128, ffn_dim=1024, vocab=1000, n_layers=3,
+                       rope_theta=500000.0, max_context=1024)
+    tensors = synth.build_tensors(cfg, seed=12, body_type=quant.Q4_0, embed_type=quant.Q8_0, head_type=quant.Q8_0,
+                                  tied_head=False)
+    prompt = synth.prompt_ids(cfg, 700, seed=4)  # 700 positions: several spans per kv head
+    oracle = O.OracleModel(cfg, tensors, kv_f16=not kv_f32, threads=8)
+    want = oracle.forward(prompt, O.MODE_FAST)
+    mk = lambda **kw: session.LlamaCudaPlan.from_tensors(  # noqa: E731
+        cfg, tensors, session.CudaSessionTarget(kv_f32=kv_f32, max_context=1024, **kw)).prepare()
+    one, many = mk(persistent_decode=True), mk()
+    assert_logits_close(one.prefill_ids(prompt), want)
+    many.prefill_ids(prompt)
+    tok = O.select_greedy(want)
+    for _ in range(6):
+        w = oracle.forward([tok], O.MODE_FAST)
+        a, b = one.run_token(tok), many.run_token(tok)
+        assert_logits_close(a, w)
+        assert_logits_close(b, w)
+        assert np.abs(a - b).max() <= 1e-4
+        tok = O.select_greedy(w)
+    r1, r2 = one.report(), many.report()
+    assert r1["kernel_launches"] < r2["kernel_launches"]
+    # device-resident loop on both paths from the same state
+    ids1, _ = one.decode_loop([tok], 12)
+    ids2, _ = many.decode_loop([tok], 12)
+    want_ids = []
+    t = tok
+    for _ in range(12):
+        w = oracle.forward([t], O.MODE_FAST)
+        t = O.select_greedy(w)
+        want_ids.append(t)
+    assert ids1[:, 0].tolist() == want_ids and ids2[:, 0].tolist() == want_ids
+    assert one.position() == 700 + 6 + 12
+    # a one-token prompt on a fresh row is a persistent-kernel step too
+    fresh = mk(persistent_decode=True)
+    o2 = O.OracleModel(cfg, tensors, kv_f16=not kv_f32, threads=8)
+    assert_logits_close(fresh.prefill_ids([7]), o2.forward([7], O.MODE_FAST))
+    prof = one.decode_profile([t], 4)
+    assert prof["total"]["launches_per_step"] == 1 and prof["total"]["ms_per_step"] > 0
+
+
 def test_stop_on_eos_and_last_token_not_fed_back(tiny):
     cfg, tensors, data, prompt = tiny
     s = make_session(data, kv_f32=True)
