@@ -261,19 +261,26 @@ __global__ void __launch_bounds__(THREADS) attn_fused_kernel(const FusedAttnArgs
     if (lane == 0) ml[gq * 2 + 1] = __frcp_rn(L);
   }
   __syncthreads();
-  for (int o = tid; o < G * HD; o += THREADS) {
-    const int gq = o / HD, d = o - gq * HD;
+  for (int o = tid; o < G * (HD / 2); o += THREADS) {
+    const int gq = o / (HD / 2), d = 2 * (o - gq * (HD / 2));
     const float *base = A.scratch + ((size_t)c * A.heads + (size_t)(kvh * G + gq)) * A.max_splits * (HD + 2) + 2 + d;
-    float acc = 0.0f;
-    for (int s0 = 0; s0 < nspl; s0 += 8) {
-      float v[8];
+    float a0 = 0.0f, a1 = 0.0f;
+    for (int s0 = 0; s0 < nspl; s0 += 20) {
+      float2 v[20];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = (s0 + j < nspl) ? __ldcg(base + (size_t)(s0 + j) * (HD + 2)) : 0.0f;
+      for (int j = 0; j < 20; ++j)
+        v[j] = (s0 + j < nspl) ? __ldcg(reinterpret_cast<const float2 *>(base + (size_t)(s0 + j) * (HD + 2))) : make_float2(0.0f, 0.0f);
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (s0 + j < nspl) acc = fmaf(v[j], wts[gq * nspl + s0 + j], acc);
+      for (int j = 0; j < 20; ++j)
+        if (s0 + j < nspl) {
+          const float wgt = wts[gq * nspl + s0 + j];
+          a0 = fmaf(v[j].x, wgt, a0);
+          a1 = fmaf(v[j].y, wgt, a1);
+        }
     }
-    A.out[(size_t)c * A.heads * HD + (size_t)(kvh * G + gq) * HD + d] = __fmul_rn(acc, ml[gq * 2 + 1]);
+    float *dst = A.out + (size_t)c * A.heads * HD + (size_t)(kvh * G + gq) * HD + d;
+    dst[0] = __fmul_rn(a0, ml[gq * 2 + 1]);
+    dst[1] = __fmul_rn(a1, ml[gq * 2 + 1]);
   }
 }
 
@@ -285,6 +292,9 @@ cudaError_t launch_t(const FusedAttnArgs &a, const LaunchCfg &cfg) {
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    // same shared-memory / L1 split as the GEMV kernels on either side: no reconfiguration between launches
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
