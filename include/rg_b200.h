@@ -99,6 +99,7 @@ typedef struct {
   uint64_t fallback_count;    /* always 0: there is no CPU or library fallback */
   float last_prefill_ms;      /* CUDA-event time of the last prefill call */
   float last_decode_ms;       /* CUDA-event time of the last decode step */
+  uint64_t peer_reduce_launches; /* tensor-parallel partial sums done by the peer-memory kernel (0: NCCL path) */
 } rg_report;
 
 typedef struct rg_gguf rg_gguf;

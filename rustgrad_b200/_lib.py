@@ -32,7 +32,7 @@ class Report(C.Structure):
         ("kernel_launches", C.c_uint64), ("graph_replays", C.c_uint64), ("h2d_calls", C.c_uint64),
         ("h2d_bytes", C.c_uint64), ("d2h_calls", C.c_uint64), ("d2h_bytes", C.c_uint64), ("weight_bytes", C.c_uint64),
         ("kv_bytes", C.c_uint64), ("fallback_count", C.c_uint64), ("last_prefill_ms", C.c_float),
-        ("last_decode_ms", C.c_float),
+        ("last_decode_ms", C.c_float), ("peer_reduce_launches", C.c_uint64),
     ]
 
 

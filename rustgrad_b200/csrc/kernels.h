@@ -142,6 +142,22 @@ bool mega_plan_smem(int max_k, int *u_bytes, int *slots, size_t *smem);
 int mega_max_splits(int ctx, int grid, int kv_heads, bool kv_f32);
 cudaError_t launch_decode_mega(const MegaParams &P, bool kv_f32, size_t smem, int grid, cudaStream_t stream);
 
+// ---- Tensor-parallel partial sum + residual add over peer memory (tp_fused.cu) -----------------
+constexpr int TP_FUSED_CTAS = 16;
+constexpr int TP_FUSED_MAX_WORLD = 8;
+// Words of flag storage every rank provides: [2 buffers][TP_FUSED_CTAS][TP_FUSED_MAX_WORLD].
+constexpr int TP_FUSED_FLAG_WORDS = 2 * TP_FUSED_CTAS * TP_FUSED_MAX_WORLD;
+struct TpFusedArgs {
+  float *x = nullptr;  // residual rows [cols][ldx], local
+  int ldx = 0, n = 0, cols = 0;
+  const float *const *peer_partial = nullptr;  // device array [world]: this buffer on every rank (own rank included)
+  int ldp = 0;
+  unsigned *const *peer_flags = nullptr;  // device array [world]: flag storage of every rank
+  unsigned *epochs = nullptr;             // local, [2][TP_FUSED_CTAS], zero at start
+  int rank = 0, world = 1, buffer = 0;
+};
+cudaError_t launch_tp_allreduce_add(const TpFusedArgs &a, const LaunchCfg &cfg);
+
 // Dense (F32/F16) weight GEMV for tensors the block formats cannot hold (K % 32 != 0) or that a
 // file stores dense.  x is plain f32 [batch, ldx]; same epilogues (EPI_SWIGLU unsupported).
 struct DenseGemvArgs {

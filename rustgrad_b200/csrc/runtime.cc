@@ -273,6 +273,14 @@ struct rg_session {
   // profiling pass: only the kernel families in family_mask are launched
   unsigned family_mask = 0xffffffffu;
   int cur_kind = 0;
+  // tensor-parallel partial sums: [0] output projection, [1] down projection.  Fused form: the buffers live
+  // in one block that the other ranks map through CUDA IPC (tp_fused.cu); otherwise both point at `partial`
+  float *tp_part[2] = {nullptr, nullptr};
+  bool tp_fused = false;
+  const float **tp_peer_part[2] = {nullptr, nullptr};  // device arrays [world]
+  unsigned **tp_peer_flags = nullptr;                  // device array [world]
+  unsigned *tp_epochs = nullptr;
+  std::vector<void *> tp_ipc_opened;
   // one-launch decode attention (attn_fused.cu): arrival counters per (column, kv head); null = not used
   unsigned *attn_counters = nullptr;
   int attn_max_splits = 0;
@@ -284,6 +292,7 @@ struct rg_session {
 
   ~rg_session() {
     for (auto &g : graphs) cudaGraphExecDestroy(g.second);
+    for (void *p : tp_ipc_opened) cudaIpcCloseMemHandle(p);
     for (void *p : owned) cudaFree(p);
     if (h_ctrl) cudaFreeHost(h_ctrl);
     if (h_ids) cudaFreeHost(h_ids);
@@ -391,16 +400,35 @@ static int32_t linear(rg_session *s, const DevTensor *const *w, int n, const voi
   return RG_OK;
 }
 
-static int32_t tp_reduce_add(rg_session *s, int ncols) {
+// x += sum over ranks of the partial projection in buffer `which` (0: output projection, 1: down
+// projection).  Fused form: one kernel over NVLink peer memory; otherwise NCCL all-reduce + add.
+static int32_t tp_reduce_add(rg_session *s, int ncols, int which) {
   const int d = s->cfg.d_model;
   std::string err;
   prof_mark(s, PROF_OTHER);
   if (!(s->family_mask & (1u << PROF_OTHER))) return RG_OK;
-  int32_t rc = comm_allreduce_sum_f32(&s->comm, s->partial, (size_t)ncols * d, s->stream, &err);
+  if (s->tp_fused) {
+    TpFusedArgs a;
+    a.x = s->x;
+    a.ldx = d;
+    a.n = d;
+    a.cols = ncols;
+    a.peer_partial = s->tp_peer_part[which];
+    a.ldp = d;
+    a.peer_flags = s->tp_peer_flags;
+    a.epochs = s->tp_epochs;
+    a.rank = s->tp_rank;
+    a.world = s->tp_world;
+    a.buffer = which;
+    RG_LAUNCH(s, launch_tp_allreduce_add(a, lcfg(s)));
+    s->report.peer_reduce_launches++;
+    return RG_OK;
+  }
+  int32_t rc = comm_allreduce_sum_f32(&s->comm, s->tp_part[which], (size_t)ncols * d, s->stream, &err);
   if (rc) return fail(rc, err);
   LaunchCfg c = lcfg(s);
   c.pdl = false;  // follows a library kernel
-  RG_LAUNCH(s, launch_add_rows(s->x, d, s->partial, d, d, ncols, c));
+  RG_LAUNCH(s, launch_add_rows(s->x, d, s->tp_part[which], d, d, ncols, c));
   return RG_OK;
 }
 
@@ -453,6 +481,7 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
   LaunchCfg plain = L;
   plain.pdl = false;
   const bool tp = s->tp_world > 1;
+  const bool tp_lib = tp && !s->tp_fused;  // a library collective precedes some kernels: no dependent launch there
   int32_t rc;
   prof_mark(s, PROF_OTHER);
   RG_LAUNCH(s, launch_row_gather(s->token_embd.type, s->token_embd.d, d, ctl->tokens, ncols, s->x, d, plain));
@@ -461,7 +490,7 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
     const DevTensor *qkvw[3] = {&W.q, &W.k, &W.v};
     // the first GEMV of a layer follows a collective (library kernel) under tensor parallelism
     if ((rc = gemv_i8(s, qkvw, 3, s->x, d, nullptr, reinterpret_cast<const float *>(W.attn_norm.d), ncols, EPI_STORE, s->qkv,
-                      qkv_w, (tp && l > 0) ? plain : L)))
+                      qkv_w, (tp_lib && l > 0) ? plain : L)))
       return rc;
     prof_mark(s, PROF_ATTN);
     if (s->attn_counters) {
@@ -521,19 +550,19 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
     }
     const DevTensor *ow[1] = {&W.o};
     if (tp) {
-      if ((rc = gemv_i8(s, ow, 1, s->attn_f32, qw, nullptr, nullptr, ncols, EPI_STORE, s->partial, d, L))) return rc;
-      if ((rc = tp_reduce_add(s, ncols))) return rc;
+      if ((rc = gemv_i8(s, ow, 1, s->attn_f32, qw, nullptr, nullptr, ncols, EPI_STORE, s->tp_part[0], d, L))) return rc;
+      if ((rc = tp_reduce_add(s, ncols, 0))) return rc;
     } else if ((rc = gemv_i8(s, ow, 1, s->attn_f32, qw, nullptr, nullptr, ncols, EPI_RESIDUAL, s->x, d, L))) {
       return rc;
     }
     const DevTensor *guw[2] = {&W.gate, &W.up};
     if ((rc = gemv_i8(s, guw, 2, s->x, d, nullptr, reinterpret_cast<const float *>(W.ffn_norm.d), ncols, EPI_SWIGLU, s->h_f32,
-                      s->ffn_l, tp ? plain : L)))
+                      s->ffn_l, tp_lib ? plain : L)))
       return rc;
     const DevTensor *dw[1] = {&W.down};
     if (tp) {
-      if ((rc = gemv_i8(s, dw, 1, s->h_f32, s->ffn_l, nullptr, nullptr, ncols, EPI_STORE, s->partial, d, L))) return rc;
-      if ((rc = tp_reduce_add(s, ncols))) return rc;
+      if ((rc = gemv_i8(s, dw, 1, s->h_f32, s->ffn_l, nullptr, nullptr, ncols, EPI_STORE, s->tp_part[1], d, L))) return rc;
+      if ((rc = tp_reduce_add(s, ncols, 1))) return rc;
     } else if ((rc = gemv_i8(s, dw, 1, s->h_f32, s->ffn_l, nullptr, nullptr, ncols, EPI_RESIDUAL, s->x, d, L))) {
       return rc;
     }
@@ -544,7 +573,7 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
     float *dst = split_head ? s->logits_l : s->logits;
     const int ld = split_head ? s->vocab_l : c.vocab;
     if ((rc = gemv_i8(s, hw, 1, s->x, d, ctl->logit_cols, reinterpret_cast<const float *>(s->output_norm.d), n_logit_cols,
-                      EPI_STORE, dst, ld, tp ? plain : L)))
+                      EPI_STORE, dst, ld, tp_lib ? plain : L)))
       return rc;
     LaunchCfg am = L;
     prof_mark(s, PROF_OTHER);
@@ -614,6 +643,7 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
   LaunchCfg plain = L;
   plain.pdl = false;
   const bool tp = s->tp_world > 1;
+  const bool tp_lib = tp && !s->tp_fused;  // a library collective precedes some kernels: no dependent launch there
   const Operand16 xop = wide_operand(s);
   int32_t rc;
   prof_mark(s, PROF_OTHER);
@@ -622,7 +652,7 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
     const LayerW &W = s->layers[(size_t)l];
     prof_mark(s, PROF_OTHER);
     RG_LAUNCH(s, launch_rmsnorm16(s->x, d, reinterpret_cast<const float *>(W.attn_norm.d), d, c.norm_eps, ncols, xop,
-                                  (tp && l > 0) ? plain : L));
+                                  (tp_lib && l > 0) ? plain : L));
     if ((rc = gemm_tc(s, W.q, ncols, s->qkv, qkv_w, L))) return rc;
     if ((rc = gemm_tc(s, W.k, ncols, s->qkv + qw, qkv_w, L))) return rc;
     if ((rc = gemm_tc(s, W.v, ncols, s->qkv + qw + kw, qkv_w, L))) return rc;
@@ -660,26 +690,26 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
     RG_LAUNCH(s, launch_attention(aa, L));
     if (s->family_mask & (1u << PROF_ATTN)) s->launches_in_step++;  // split + combine
     RG_LAUNCH(s, launch_to16(s->attn_f32, qw, qw, ncols, xop, L));
-    if ((rc = gemm_tc(s, W.o, ncols, s->partial, d, L))) return rc;
+    if ((rc = gemm_tc(s, W.o, ncols, s->tp_part[0], d, L))) return rc;
     if (tp) {
-      if ((rc = tp_reduce_add(s, ncols))) return rc;
+      if ((rc = tp_reduce_add(s, ncols, 0))) return rc;
     } else {
       prof_mark(s, PROF_OTHER);
-      RG_LAUNCH(s, launch_add_rows(s->x, d, s->partial, d, d, ncols, L));
+      RG_LAUNCH(s, launch_add_rows(s->x, d, s->tp_part[0], d, d, ncols, L));
     }
     prof_mark(s, PROF_OTHER);
     RG_LAUNCH(s, launch_rmsnorm16(s->x, d, reinterpret_cast<const float *>(W.ffn_norm.d), d, c.norm_eps, ncols, xop,
-                                  tp ? plain : L));
+                                  tp_lib ? plain : L));
     if ((rc = gemm_tc(s, W.gate, ncols, s->gate_f32, s->ffn_l, L))) return rc;
     if ((rc = gemm_tc(s, W.up, ncols, s->up_f32, s->ffn_l, L))) return rc;
     prof_mark(s, PROF_OTHER);
     RG_LAUNCH(s, launch_swiglu16(s->gate_f32, s->up_f32, s->ffn_l, s->ffn_l, ncols, xop, L));
-    if ((rc = gemm_tc(s, W.down, ncols, s->partial, d, L))) return rc;
+    if ((rc = gemm_tc(s, W.down, ncols, s->tp_part[1], d, L))) return rc;
     if (tp) {
-      if ((rc = tp_reduce_add(s, ncols))) return rc;
+      if ((rc = tp_reduce_add(s, ncols, 1))) return rc;
     } else {
       prof_mark(s, PROF_OTHER);
-      RG_LAUNCH(s, launch_add_rows(s->x, d, s->partial, d, d, ncols, L));
+      RG_LAUNCH(s, launch_add_rows(s->x, d, s->tp_part[0], d, d, ncols, L));
     }
   }
   if (n_logit_cols > 0) {
@@ -690,13 +720,13 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
       // a prompt's last token: the integer GEMV with the final norm in its prologue
       const DevTensor *hw[1] = {s->head};
       if ((rc = gemv_i8(s, hw, 1, s->x, d, ctl->logit_cols, reinterpret_cast<const float *>(s->output_norm.d), n_logit_cols,
-                        EPI_STORE, dst, ld, tp ? plain : L)))
+                        EPI_STORE, dst, ld, tp_lib ? plain : L)))
         return rc;
     } else {
       // decode of many rows: logit column i is row i
       prof_mark(s, PROF_OTHER);
       RG_LAUNCH(s, launch_rmsnorm16(s->x, d, reinterpret_cast<const float *>(s->output_norm.d), d, c.norm_eps, n_logit_cols, xop,
-                                    tp ? plain : L));
+                                    tp_lib ? plain : L));
       if ((rc = gemm_tc(s, *s->head, n_logit_cols, dst, ld, L))) return rc;
     }
     LaunchCfg am = L;
@@ -714,6 +744,86 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
     RG_LAUNCH(s, launch_argmax(s->logits, c.vocab, c.vocab, n_logit_cols, s->d_ids, am));
     if (advance) RG_LAUNCH(s, launch_advance(s->d_ids, ctl->tokens, ctl->pos, s->d_history, &ctl->step, ncols, L));
   }
+  return RG_OK;
+}
+
+// Peer-memory exchange for the tensor-parallel partial sums: allocates this rank's block (two
+// partial buffers + flag words), trades CUDA IPC handles through the NCCL communicator and maps the
+// other ranks' blocks.  Every rank learns whether ALL ranks succeeded (one more all-reduce) and only
+// then switches to the fused kernel; otherwise the NCCL all-reduce path stays in place.
+static int32_t tp_fused_setup(rg_session *s) {
+  const int W = s->tp_world, d = s->cfg.d_model;
+  if (W > TP_FUSED_MAX_WORLD || d % 4) return RG_OK;
+  const size_t part_floats = (size_t)WMAX * d;
+  const size_t block_bytes = 2 * part_floats * sizeof(float) + TP_FUSED_FLAG_WORDS * sizeof(unsigned);
+  uint8_t *block = nullptr;
+  float *xchg = nullptr;  // [16 floats of handle + 1 ok flag] * (1 + W)
+  int32_t rc;
+  if ((rc = dalloc(s, &block, block_bytes))) return rc;
+  if ((rc = dalloc(s, &xchg, (size_t)17 * (1 + W)))) return rc;
+  RG_CUDA(cudaMemset(block, 0, block_bytes));
+  cudaIpcMemHandle_t mine;
+  float host[17 * (1 + TP_FUSED_MAX_WORLD)] = {0};
+  float ok = cudaIpcGetMemHandle(&mine, block) == cudaSuccess ? 1.0f : 0.0f;
+  cudaGetLastError();
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  memcpy(host, &mine, sizeof(mine));
+  host[16] = ok;
+  RG_CUDA(cudaMemcpy(xchg, host, 17 * sizeof(float), cudaMemcpyHostToDevice));
+  std::string err;
+  if ((rc = comm_allgather_f32(&s->comm, xchg, xchg + 17, 17, s->stream, &err))) return fail(rc, err);
+  RG_CUDA(cudaStreamSynchronize(s->stream));
+  RG_CUDA(cudaMemcpy(host + 17, xchg + 17, (size_t)17 * W * sizeof(float), cudaMemcpyDeviceToHost));
+  std::vector<uint8_t *> base((size_t)W, nullptr);
+  for (int r = 0; r < W; ++r) ok = std::min(ok, host[17 + 17 * r + 16]);
+  if (ok > 0.5f) {
+    for (int r = 0; r < W; ++r) {
+      if (r == s->tp_rank) {
+        base[(size_t)r] = block;
+        continue;
+      }
+      cudaIpcMemHandle_t h;
+      memcpy(&h, host + 17 + 17 * r, sizeof(h));
+      void *ptr = nullptr;
+      if (cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        cudaGetLastError();
+        ok = 0.0f;
+        break;
+      }
+      s->tp_ipc_opened.push_back(ptr);
+      base[(size_t)r] = static_cast<uint8_t *>(ptr);
+    }
+  }
+  // agreement: the fused path is used only if every rank mapped every block
+  host[0] = ok;
+  RG_CUDA(cudaMemcpy(xchg, host, sizeof(float), cudaMemcpyHostToDevice));
+  if ((rc = comm_allreduce_sum_f32(&s->comm, xchg, 1, s->stream, &err))) return fail(rc, err);
+  RG_CUDA(cudaStreamSynchronize(s->stream));
+  RG_CUDA(cudaMemcpy(host, xchg, sizeof(float), cudaMemcpyDeviceToHost));
+  if (host[0] < (float)W - 0.5f) return RG_OK;  // some rank could not: everyone keeps the NCCL path
+  std::vector<const float *> pa((size_t)W), pb((size_t)W);
+  std::vector<unsigned *> pf((size_t)W);
+  for (int r = 0; r < W; ++r) {
+    pa[(size_t)r] = reinterpret_cast<const float *>(base[(size_t)r]);
+    pb[(size_t)r] = reinterpret_cast<const float *>(base[(size_t)r]) + part_floats;
+    pf[(size_t)r] = reinterpret_cast<unsigned *>(base[(size_t)r] + 2 * part_floats * sizeof(float));
+  }
+  const float **d_pa, **d_pb;
+  unsigned **d_pf;
+  if ((rc = dalloc(s, &d_pa, (size_t)W))) return rc;
+  if ((rc = dalloc(s, &d_pb, (size_t)W))) return rc;
+  if ((rc = dalloc(s, &d_pf, (size_t)W))) return rc;
+  if ((rc = dalloc(s, &s->tp_epochs, (size_t)2 * TP_FUSED_CTAS))) return rc;
+  RG_CUDA(cudaMemcpy(d_pa, pa.data(), sizeof(void *) * (size_t)W, cudaMemcpyHostToDevice));
+  RG_CUDA(cudaMemcpy(d_pb, pb.data(), sizeof(void *) * (size_t)W, cudaMemcpyHostToDevice));
+  RG_CUDA(cudaMemcpy(d_pf, pf.data(), sizeof(void *) * (size_t)W, cudaMemcpyHostToDevice));
+  RG_CUDA(cudaMemset(s->tp_epochs, 0, sizeof(unsigned) * 2 * TP_FUSED_CTAS));
+  s->tp_peer_part[0] = d_pa;
+  s->tp_peer_part[1] = d_pb;
+  s->tp_peer_flags = d_pf;
+  s->tp_part[0] = reinterpret_cast<float *>(block);
+  s->tp_part[1] = reinterpret_cast<float *>(block) + part_floats;
+  s->tp_fused = true;
   return RG_OK;
 }
 
@@ -922,13 +1032,13 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
     if (s->family_mask & (1u << PROF_ATTN)) s->launches_in_step++;  // split + combine
     const DevTensor *ow[1] = {&W.o};
     if (s->tp_world > 1) {
-      if ((rc = linear(s, ow, 1, s->attn_pack, s->attn_f32, qw, ncols, EPI_STORE, s->partial, d))) return rc;
-      if ((rc = tp_reduce_add(s, ncols))) return rc;
+      if ((rc = linear(s, ow, 1, s->attn_pack, s->attn_f32, qw, ncols, EPI_STORE, s->tp_part[0], d))) return rc;
+      if ((rc = tp_reduce_add(s, ncols, 0))) return rc;
     } else if ((rc = linear(s, ow, 1, s->attn_pack, s->attn_f32, qw, ncols, EPI_RESIDUAL, s->x, d))) {
       return rc;
     }
     LaunchCfg after = L;
-    if (s->tp_world > 1) after.pdl = false;
+    if (s->tp_world > 1 && !s->tp_fused) after.pdl = false;
     const bool gu_dense = !W.gate.packed() || !W.up.packed() || W.gate.type != W.up.type;
     prof_mark(s, PROF_OTHER);
     RG_LAUNCH(s, launch_rmsnorm_pack(s->x, d, reinterpret_cast<const float *>(W.ffn_norm.d), d, c.norm_eps, ncols, nullptr,
@@ -956,15 +1066,15 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
     }
     const DevTensor *dw[1] = {&W.down};
     if (s->tp_world > 1) {
-      if ((rc = linear(s, dw, 1, s->h_pack, s->h_f32, s->ffn_l, ncols, EPI_STORE, s->partial, d))) return rc;
-      if ((rc = tp_reduce_add(s, ncols))) return rc;
+      if ((rc = linear(s, dw, 1, s->h_pack, s->h_f32, s->ffn_l, ncols, EPI_STORE, s->tp_part[1], d))) return rc;
+      if ((rc = tp_reduce_add(s, ncols, 1))) return rc;
     } else if ((rc = linear(s, dw, 1, s->h_pack, s->h_f32, s->ffn_l, ncols, EPI_RESIDUAL, s->x, d))) {
       return rc;
     }
   }
   if (n_logit_cols > 0) {
     LaunchCfg after = L;
-    if (s->tp_world > 1) after.pdl = false;
+    if (s->tp_world > 1 && !s->tp_fused) after.pdl = false;
     prof_mark(s, PROF_OTHER);
     RG_LAUNCH(s, launch_rmsnorm_pack(s->x, d, reinterpret_cast<const float *>(s->output_norm.d), d, c.norm_eps, n_logit_cols,
                                      ctl->logit_cols, s->head_pack, s->head->packed() ? nullptr : s->xn_f32, d, after));
@@ -1399,6 +1509,7 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
     }
   }
   RG_TRY(dalloc(s.get(), &s->partial, (size_t)WMAX * d));
+  s->tp_part[0] = s->tp_part[1] = s->partial;
   RG_TRY(dalloc(s.get(), &s->gate_f32, (size_t)WMAX * s->ffn_l));
   RG_TRY(dalloc(s.get(), &s->up_f32, (size_t)WMAX * s->ffn_l));
   RG_TRY(dalloc(s.get(), &s->h_f32, (size_t)MAXC * s->ffn_l));
@@ -1417,6 +1528,7 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   s->h_pack = raw;
   RG_TRY(dalloc(s.get(), &raw, xpack_bytes(d, MAXC)));
   s->head_pack = raw;
+  if (s->tp_world > 1 && !p->opt.disable_fused_allreduce && !env_flag("RG_B200_DISABLE_FUSED_ALLREDUCE")) RG_TRY(tp_fused_setup(s.get()));
   // RoPE tables in f64 on the host, cast to f32 (src/models/transformer/layer.rs:541-556)
   {
     const int half = hd / 2;

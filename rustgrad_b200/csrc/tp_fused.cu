@@ -1,0 +1,112 @@
+// Tensor-parallel sum of the f32 partial results of a row-split projection, fused with the residual
+// add, over NVLink peer memory: x[col][:] += sum over ranks of partial_r[col][:].
+// Stands where rustgrad's sharded plan inserts an all-reduce on the contracting axis
+// (src/sharding.rs:642-667, src/collective.rs:441) followed by the residual add of
+// src/models/transformer/layer.rs:455-470.
+//
+// One-shot exchange: every rank's projection kernel has written its partial into a buffer that the
+// other ranks map through CUDA IPC.  A CTA of this kernel then
+//   1. bumps its own epoch word and stores the epoch into its flag slot on EVERY rank
+//      (st.release.sys; the partial itself is complete: the producing kernel has finished);
+//   2. waits, bounded, until the slots written by all ranks have reached the epoch;
+//   3. reads its slice of every rank's partial with plain peer loads (volatile: the buffers are
+//      rewritten every call) and adds the sum, taken in rank order so that every rank computes
+//      the identical value, to the residual stream.
+// Two buffers alternate (output projection / down projection): a rank that has passed the second
+// exchange of a layer knows that every rank has finished reading the first buffer, so it may be
+// overwritten by the next layer.  No NCCL call, no separate add kernel; the kernel is an ordinary
+// launch and is captured in the decode graph like the others.
+#include "kernels.h"
+#include "rg_device.cuh"
+
+namespace rg {
+namespace {
+
+constexpr int THREADS = 256;
+
+__device__ __forceinline__ float4 ld_peer(const float4 *p) {
+  float4 v;
+  asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(THREADS) tp_allreduce_add_kernel(const TpFusedArgs A, int *status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  __shared__ unsigned s_epoch;
+  __shared__ int s_dead;
+  const int tid = threadIdx.x, b = blockIdx.x;
+  const int slot = (A.buffer * TP_FUSED_CTAS + b) * TP_FUSED_MAX_WORLD;
+  if (tid == 0) {
+    s_epoch = ++A.epochs[A.buffer * TP_FUSED_CTAS + b];
+    s_dead = 0;
+  }
+  __syncthreads();
+  const unsigned e = s_epoch;
+  if (tid < A.world) {
+    st_release_sys(A.peer_flags[tid] + slot + A.rank, e);  // tell rank `tid` that this rank's partial is ready
+    const unsigned *mine = A.peer_flags[A.rank] + slot + tid;  // written by rank `tid`
+    bool ok = false;
+    for (unsigned i = 0; i < (1u << 22); ++i) {
+      if ((int)(ld_acquire_sys(mine) - e) >= 0) {
+        ok = true;
+        break;
+      }
+      if (i > 128) __nanosleep(64);
+    }
+    if (!ok) {
+      s_dead = 1;
+      atomicExch(status, DEV_TIMEOUT);
+    }
+  }
+  __syncthreads();
+  if (s_dead) return;  // a rank never arrived: leave x untouched, the host sees the status
+  const int row4 = A.n / 4;
+  const int total = A.cols * row4;
+  for (int i = b * THREADS + tid; i < total; i += TP_FUSED_CTAS * THREADS) {
+    const int col = i / row4, j = i - col * row4;
+    float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int r = 0; r < A.world; ++r) {
+      const float4 p = ld_peer(reinterpret_cast<const float4 *>(A.peer_partial[r] + (size_t)col * A.ldp) + j);
+      sum.x = __fadd_rn(sum.x, p.x);
+      sum.y = __fadd_rn(sum.y, p.y);
+      sum.z = __fadd_rn(sum.z, p.z);
+      sum.w = __fadd_rn(sum.w, p.w);
+    }
+    float4 *dst = reinterpret_cast<float4 *>(A.x + (size_t)col * A.ldx) + j;
+    float4 v = *dst;
+    v.x = __fadd_rn(v.x, sum.x);
+    v.y = __fadd_rn(v.y, sum.y);
+    v.z = __fadd_rn(v.z, sum.z);
+    v.w = __fadd_rn(v.w, sum.w);
+    *dst = v;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_tp_allreduce_add(const TpFusedArgs &a, const LaunchCfg &cfg) {
+  if (!a.x || !a.peer_partial || !a.peer_flags || !a.epochs || a.world < 2 || a.world > TP_FUSED_MAX_WORLD || a.n % 4 ||
+      a.ldx % 4 || a.ldp % 4 || a.buffer < 0 || a.buffer > 1)
+    return cudaErrorInvalidValue;
+  cudaLaunchConfig_t lc{};
+  lc.gridDim = dim3(TP_FUSED_CTAS);
+  lc.blockDim = dim3(THREADS);
+  lc.stream = cfg.stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = cfg.pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&lc, tp_allreduce_add_kernel, a, cfg.status);
+}
+
+}  // namespace rg

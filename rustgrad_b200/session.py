@@ -85,6 +85,7 @@ class CudaSessionTarget:
     general_path_only: bool = False  # never take the fused small-batch decode path (tests)
     gemm_operands: str = ""  # tensor-core path operands: "" (compensated f16), "bf16", "f16", "f16x3"
     persistent_decode: bool = False  # batch-1 decode as one cooperative kernel per step (off by default)
+    disable_fused_allreduce: bool = False  # tensor-parallel partial sums through NCCL instead of peer memory
     _opts: Options = field(default=None, repr=False)
 
     def options(self) -> Options:
@@ -92,6 +93,7 @@ class CudaSessionTarget:
         o.device, o.max_batch, o.max_context = self.device, self.max_batch, self.max_context
         o.kv_f32, o.tp_rank, o.tp_world = int(self.kv_f32), self.tp_rank, self.tp_world
         o.disable_graph, o.disable_pdl = int(self.disable_graph), int(self.disable_pdl)
+        o.disable_fused_allreduce = int(self.disable_fused_allreduce)
         o.reserved[0] = int(self.general_path_only)
         o.reserved[1] = {"": 0, "bf16": 1, "f16": 2, "f16x3": 3}[self.gemm_operands]
         o.reserved[2] = int(self.persistent_decode)
