@@ -215,6 +215,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--prefill", type=int, default=PREFILL)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=1, help="rows decoded together (the headline workload is 1)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.workload != "decode":
@@ -265,45 +266,47 @@ def main():
         torch.cuda.synchronize()
 
     prefill = min(args.prefill, cfg["max_context"] - 2 * (args.steps + args.warmup) - 80)
-    target = session.CudaSessionTarget(device=local_rank, max_batch=1, tp_rank=rank if n > 1 else 0, tp_world=n, nccl_id=nccl_id)
+    B = args.batch
+    target = session.CudaSessionTarget(device=local_rank, max_batch=B, tp_rank=rank if n > 1 else 0, tp_world=n, nccl_id=nccl_id)
     plan = session.LlamaCudaPlan.synthetic(cfg, target, seed=wl["seed"], body_type=wl["body"], embed_type=wl["embed"],
                                            head_type=wl["head"])
     sess = target.prepare(plan)
-    prompt = synth.prompt_ids(cfg, prefill, seed=1)
-    logits = sess.prefill_ids(prompt)
-    first = int(np.argmax(logits))
+    first = []
+    for r in range(B):  # every row gets its own prompt of the same length
+        logits = sess.prefill_ids(synth.prompt_ids(cfg, prefill, seed=1 + r), row=r)
+        first.append(int(np.argmax(logits)))
     prefill_ms = sess.report()["last_prefill_ms"]
 
     # ---- device-resident loop: W warm-up steps, then exactly K timed steps
-    ids, _ = sess.decode_loop([first], args.warmup)
-    tok = int(ids[-1, 0])
+    ids, _ = sess.decode_loop(first, args.warmup)
+    tok = [int(v) for v in ids[-1]]
     r0 = sess.report()
     barrier()
     with ClockSampler(local_rank) as clocks:
-        ids, gpu_ms = sess.decode_loop([tok], args.steps)
+        ids, gpu_ms = sess.decode_loop(tok, args.steps)
         torch.cuda.synchronize()
     barrier()
     r1 = sess.report()
-    tok = int(ids[-1, 0])
+    tok = [int(v) for v in ids[-1]]
     launches = r1["kernel_launches"] - r0["kernel_launches"]
 
     # ---- end to end through the decode verb: host token in, host id out, every step
     for _ in range(3):
-        _, g = sess.decode([tok])
-        tok = int(g[0])
+        _, g = sess.decode(tok)
+        tok = [int(v) for v in g]
     r2 = sess.report()
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        _, g = sess.decode([tok])
-        tok = int(g[0])
+        _, g = sess.decode(tok)
+        tok = [int(v) for v in g]
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     barrier()
     r3 = sess.report()
 
     # ---- profiling pass: CUDA events between kernel families (serialized, no overlap)
-    prof = sess.decode_profile([tok], 16)
+    prof = sess.decode_profile(tok, 16)
     position = sess.position()
 
     t = torch.tensor([gpu_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
@@ -316,24 +319,25 @@ def main():
         return
 
     peak, peak_kind = measured_peaks()
-    gemv_bytes, gemv_launches = gemv_bytes_per_step(cfg, wl, n, 1)
+    gemv_bytes, gemv_launches = gemv_bytes_per_step(cfg, wl, n, B)
+    proj_kernel = ("qgemv_i8_kernel" if B <= 2 else "qgemv_kernel" if B <= 8 else "qgemm_tc_kernel") + " (all projection launches of a step)"
     gemv_ms = prof["gemv"]["ms_per_step"]
     achieved = gemv_bytes / (gemv_ms * 1e-3) / 1e9 if gemv_ms > 0 else None
     ms_per_step = gpu_ms / args.steps
     line = {
-        "metric": "decode_tokens_per_s", "value": args.steps / (gpu_ms * 1e-3), "unit": "tokens/s", "n_gpus": n,
+        "metric": "decode_tokens_per_s", "value": B * args.steps / (gpu_ms * 1e-3), "unit": "tokens/s", "n_gpus": n,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak" if n == 1 else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": wl["name"], "batch": 1, "prefill_tokens": prefill, "context_at_end": position,
+        "config": {"workload": wl["name"].replace("_b1", f"_b{B}"), "batch": B, "prefill_tokens": prefill, "context_at_end": position,
                    "kv_cache": "f16", "weights": "Q4_0 body, Q8_0 embedding+head" if n == 1 else "Q4_0",
                    "parallelism": "single GPU" if n == 1 else f"tp{n}", "l2": "inputs larger than L2 (weights >> 126 MB)",
                    "prefill_ms": prefill_ms},
-        "e2e": {"value": args.steps / (e2e_ms * 1e-3), "unit": "tokens/s",
+        "e2e": {"value": B * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": (r3["h2d_bytes"] - r2["h2d_bytes"]) / args.steps,
                 "d2h_bytes_per_step": (r3["d2h_bytes"] - r2["d2h_bytes"]) / args.steps},
         "gpu_launches": launches,
         "clocks": clocks.summary,
-        "roofline": {"bound": "hbm", "kernel": "qgemv_kernel (all quantized GEMV launches of a step)", "achieved": achieved,
+        "roofline": {"bound": "hbm", "kernel": proj_kernel, "achieved": achieved,
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak if achieved else None,
                      "traffic": gemv_bytes / gemv_launches * NCU_TRAFFIC_OVER_ALGORITHMIC["q4_0"],
                      "traffic_note": "bytes per average GEMV launch: algorithmic bytes x the dram/algorithmic ratio of the ncu capture",

@@ -206,7 +206,9 @@ __device__ __forceinline__ void q8_block_split(uint32_t dbits16, const uint32_t 
   }
 }
 
-__host__ __device__ constexpr int ring_depth(int tn, bool comp) { return comp ? (tn >= 128 ? 2 : 3) : (tn > 128 ? 3 : 4); }
+__host__ __device__ constexpr int ring_depth(int tn, bool comp) {
+  return comp ? (tn >= 128 ? 2 : 3) : (tn > 256 ? 2 : tn > 128 ? 3 : 4);
+}
 
 template <int QT, int TN, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -279,13 +281,17 @@ __global__ void __launch_bounds__(THREADS, 1)
         if (i >= NS) mbar_wait_bounded(&slot_free[slot], (uint32_t)((i / NS - 1) & 1), dead, P.status);
         mbar_expect_tx(&b_full[slot], (uint32_t)B_STAGE);
         tma_tile_2d(b_ring + slot * B_STAGE, &xmap, (step0 + i) * KSTEP, tok0, &b_full[slot]);
+        if constexpr (TN > 256)  // a TMA box holds at most 256 rows: the second half of the token tile
+          tma_tile_2d(b_ring + slot * B_STAGE + 256 * 128, &xmap, (step0 + i) * KSTEP, tok0 + 256, &b_full[slot]);
         if constexpr (COMP) tma_tile_2d(b_ring + slot * B_STAGE + B_BYTES, &xlo_map, (step0 + i) * KSTEP, tok0, &b_full[slot]);
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(TM, TN, F16);
+      // a 512-token tile is two 256-column accumulators fed by the same dequantised A tile
+      constexpr int MMA_N = TN > 256 ? 256 : TN;
+      constexpr uint32_t idesc = umma_idesc(TM, MMA_N, F16);
       for (int i = 0; i < nsteps; ++i) {
         const int slot = i % NS;
         const uint32_t ph = (uint32_t)((i / NS) & 1);
@@ -302,6 +308,8 @@ __global__ void __launch_bounds__(THREADS, 1)
             umma_16bit(tmem_base, a_hi, b_hi, idesc, 1u);
           } else {
             umma_16bit(tmem_base, a_hi, b_hi, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+            if constexpr (TN > 256)
+              umma_16bit(tmem_base + 256, a_hi, umma_desc(b_addr + 256 * 128 + kk * 32), idesc, (i > 0 || kk > 0) ? 1u : 0u);
           }
         }
         umma_commit(&slot_free[slot]);  // the slot may be rewritten once these MMAs have read it
@@ -424,7 +432,7 @@ cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
   for (int plane = 0; plane < NPL; ++plane) {
     const cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
     const cuuint64_t strides[1] = {(cuuint64_t)a.ldx * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)KSTEP, (cuuint32_t)TN};
+    const cuuint32_t box[2] = {(cuuint32_t)KSTEP, (cuuint32_t)(TN > 256 ? 256 : TN)};
     if (fn(plane ? &xlo_map : &xmap, F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
            const_cast<void *>(plane ? a.x16_lo : a.x16), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -479,6 +487,10 @@ cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
 template <int QT, int MODE>
 cudaError_t launch_n(const QGemmArgs &a, const LaunchCfg &cfg) {
   if constexpr (MODE != QGEMM_F16X3) {  // the compensated mode keeps two planes per operand: 128 tokens at most
+    // 512 tokens per weight tile halve the dequantisation work per flop; the Q8_0 raw ring does not leave room for it
+    if constexpr (QT == RG_TYPE_Q4_0) {
+      if (a.m > 256) return launch_t<QT, 512, MODE>(a, cfg);
+    }
     if (a.m > 128) return launch_t<QT, 256, MODE>(a, cfg);
   }
   if (a.m > 64) return launch_t<QT, 128, MODE>(a, cfg);
