@@ -79,6 +79,10 @@ struct QGemmArgs {
   size_t split_stride = 0;
 };
 cudaError_t launch_qgemm_tc(const QGemmArgs &a, const LaunchCfg &cfg);
+int qgemm_effective_splits(int k, int splits);
+// out[r][i] = sum over s < splits of part[s * stride + r * n + i]
+cudaError_t launch_reduce_splits(const float *part, int splits, size_t stride, int n, int rows, float *out, int ldo,
+                                 const LaunchCfg &cfg);
 // Destination of the f32 -> operand conversions: lo is written only for f16 operands and may be null.
 struct Operand16 {
   void *hi = nullptr, *lo = nullptr;
@@ -243,6 +247,19 @@ int fused_attn_per_head(int sm_count, int kv_heads, int cols);
 int fused_attn_max_splits(int ctx, int hd, bool kv_f32, int sm_count, int kv_heads);
 int fused_attn_split_cap();
 cudaError_t launch_attention_fused(const FusedAttnArgs &a, const LaunchCfg &cfg);
+
+// Causal attention for a chunk of consecutive prompt tokens of one sequence (attn_prefill.cu): q is
+// the rotated queries [cols][heads][hd] f32, the caches already hold the chunk's K / V rows, out is
+// [cols][heads*hd] f32.  Token i of the chunk sits at position pos0 + i.
+struct PrefillAttnArgs {
+  const float *q = nullptr;
+  const void *k_cache = nullptr, *v_cache = nullptr;
+  bool kv_f32 = false;
+  int cols = 0, heads = 0, kv_heads = 0, ctx = 0, seq = 0, pos0 = 0;
+  float *out = nullptr;
+};
+bool prefill_attention_supported(int heads, int kv_heads, int hd);
+cudaError_t launch_attention_prefill(const PrefillAttnArgs &a, const LaunchCfg &cfg);
 
 // Greedy selection per column with the reference's rules (generation.rs:260-287): lowest id wins
 // ties, any non-finite logit yields -1.  Also advances: next_tokens[c] = id, pos[c] += 1 when

@@ -557,6 +557,24 @@ __global__ void swiglu16_kernel(const float *g, const float *u, int n, int ld, u
   if (i < n) put16<F16>(swiglu(g[(size_t)row * ld + i], u[(size_t)row * ld + i]), y, ylo, (size_t)row * ldy + i);
 }
 
+// out[r][i] = sum over splits of part[s][r][i]: the K-split partial tiles of a small-M GEMM
+__global__ void reduce_splits_kernel(const float *part, int splits, size_t stride, int n, float *out, int ldo) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x, row = blockIdx.y;
+  if (i >= n) return;
+  const float *p = part + (size_t)row * n + i;
+  float acc = 0.0f;
+  for (int s0 = 0; s0 < splits; s0 += 8) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = (s0 + j < splits) ? p[(size_t)(s0 + j) * stride] : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += v[j];
+  }
+  out[(size_t)row * ldo + i] = acc;
+}
+
 template <typename K, typename... Args>
 cudaError_t launch_simple(K kernel, dim3 grid, dim3 block, const LaunchCfg &cfg, Args... args) {
   cudaLaunchConfig_t lc{};
@@ -590,6 +608,20 @@ cudaError_t launch_to16(const float *x, int ldx, int k, int rows, const Operand1
   const dim3 grid((unsigned)((k + 255) / 256), (unsigned)rows);
   if (y.f16) return launch_simple(to16_kernel<true>, grid, dim3(256), cfg, x, ldx, k, hi, lo, y.ld);
   return launch_simple(to16_kernel<false>, grid, dim3(256), cfg, x, ldx, k, hi, lo, y.ld);
+}
+
+cudaError_t launch_reduce_splits(const float *part, int splits, size_t stride, int n, int rows, float *out, int ldo,
+                                 const LaunchCfg &cfg) {
+  return launch_simple(reduce_splits_kernel, dim3((unsigned)((n + 255) / 256), (unsigned)rows), dim3(256), cfg, part, splits,
+                       stride, n, out, ldo);
+}
+
+// Number of K splits a launch with these arguments will actually use (whole 256-column raw tiles each).
+int qgemm_effective_splits(int k, int splits) {
+  const int total_steps = k / KSTEP;
+  if (splits < 1) splits = 1;
+  const int k_steps = ((total_steps / RAW_STEPS + splits - 1) / splits) * RAW_STEPS;
+  return (total_steps + k_steps - 1) / k_steps;
 }
 
 cudaError_t launch_qgemm_tc(const QGemmArgs &a, const LaunchCfg &cfg) {

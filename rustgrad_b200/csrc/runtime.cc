@@ -218,7 +218,8 @@ static int32_t check_tensor(rg_plan *p, const std::string &name, int32_t type, u
 // Session
 // ------------------------------------------------------------------------------------------
 static constexpr int MAXC = 8;    // columns of the GEMV paths: decode batch <= 8, short prefill tails
-static constexpr int WMAX = 256;  // columns of the tensor-core path: prefill chunk, decode batch 9..32
+static constexpr int WMAX = 1024;  // columns of the tensor-core path: prefill chunk, decode batch 9..32
+static constexpr int SCOLS = 256;  // columns the per-column attention kernels are given scratch for
 static constexpr int BMAX = 32;   // independent sequences per session
 
 struct Ctrl {  // device control block, uploaded in one copy per host-driven step
@@ -251,6 +252,8 @@ struct rg_session {
   float *x = nullptr, *xn_f32 = nullptr, *qkv = nullptr, *q_rot = nullptr, *attn_scratch = nullptr, *attn_f32 = nullptr;
   float *partial = nullptr, *gate_f32 = nullptr, *up_f32 = nullptr, *h_f32 = nullptr, *logits = nullptr, *logits_l = nullptr;
   void *xn_pack = nullptr, *attn_pack = nullptr, *h_pack = nullptr, *head_pack = nullptr;
+  bool chunk_is_prompt = false;  // the columns of the current step are consecutive positions of one sequence
+  float *split_scratch = nullptr;  // K-split partial tiles of the tensor-core GEMM at small token counts
   void *xb = nullptr;  // 16-bit operand planes (hi, lo) of the tensor-core path: [2][WMAX][max(d, qw, ffn_l)]
   int gemm_mode = QGEMM_F16X3;
   int xb_ld = 0;
@@ -628,11 +631,25 @@ static int32_t gemm_tc(rg_session *s, const DevTensor &w, int m, float *out, int
   a.out = out;
   a.ldc = ldc;
   prof_mark(s, PROF_GEMV);
+  // Few tokens (decode batches of 9..32): one CTA per 128 weight rows would leave most SMs without
+  // weights to stream, so K is split until about two CTAs per SM exist and the partial tiles are summed.
+  const int tiles = ((int)w.rows + 127) / 128;
+  int splits = (m <= BMAX && s->split_scratch) ? (2 * s->sm_count) / tiles : 1;
+  splits = qgemm_effective_splits(a.k, splits);
+  if (splits > 1) {
+    a.out = s->split_scratch;
+    a.ldc = a.n;
+    a.splits = splits;
+    a.split_stride = (size_t)m * a.n;
+    RG_LAUNCH(s, launch_qgemm_tc(a, L));
+    RG_LAUNCH(s, launch_reduce_splits(s->split_scratch, splits, a.split_stride, a.n, m, out, ldc, L));
+    return RG_OK;
+  }
   RG_LAUNCH(s, launch_qgemm_tc(a, L));
   return RG_OK;
 }
 
-// Forward for 9..256 columns (a prefill chunk, or decode of 9..32 rows): the projections run on
+// Forward for 9..1024 columns (a prefill chunk, or decode of 9..32 rows): the projections run on
 // the tcgen05 tensor cores (compensated f16 operands by default); norms, RoPE, attention and residuals stay f32.
 static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool advance) {
   const rg_llama_config &c = s->cfg;
@@ -673,22 +690,39 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
     ra.v_cache = s->v_cache[(size_t)l];
     ra.kv_f32 = s->kv_f32;
     RG_LAUNCH(s, launch_rope_append(ra, L));
-    AttnArgs aa;
-    aa.q = s->q_rot;
-    aa.k_cache = ra.k_cache;
-    aa.v_cache = ra.v_cache;
-    aa.kv_f32 = s->kv_f32;
-    aa.cols = ncols;
-    aa.heads = s->heads_l;
-    aa.kv_heads = s->kv_l;
-    aa.hd = hd;
-    aa.ctx = s->ctx;
-    aa.col_seq = ctl->seq;
-    aa.col_pos = ctl->pos;
-    aa.scratch = s->attn_scratch;
-    aa.out_f32 = s->attn_f32;
-    RG_LAUNCH(s, launch_attention(aa, L));
-    if (s->family_mask & (1u << PROF_ATTN)) s->launches_in_step++;  // split + combine
+    if (s->chunk_is_prompt && prefill_attention_supported(s->heads_l, s->kv_l, hd)) {
+      // consecutive positions of one sequence: the tiled causal kernel reads each K / V row once per CTA
+      PrefillAttnArgs pa;
+      pa.q = s->q_rot;
+      pa.k_cache = ra.k_cache;
+      pa.v_cache = ra.v_cache;
+      pa.kv_f32 = s->kv_f32;
+      pa.cols = ncols;
+      pa.heads = s->heads_l;
+      pa.kv_heads = s->kv_l;
+      pa.ctx = s->ctx;
+      pa.seq = s->h_ctrl->seq[0];
+      pa.pos0 = s->h_ctrl->pos[0];
+      pa.out = s->attn_f32;
+      RG_LAUNCH(s, launch_attention_prefill(pa, L));
+    } else {
+      AttnArgs aa;
+      aa.q = s->q_rot;
+      aa.k_cache = ra.k_cache;
+      aa.v_cache = ra.v_cache;
+      aa.kv_f32 = s->kv_f32;
+      aa.cols = ncols;
+      aa.heads = s->heads_l;
+      aa.kv_heads = s->kv_l;
+      aa.hd = hd;
+      aa.ctx = s->ctx;
+      aa.col_seq = ctl->seq;
+      aa.col_pos = ctl->pos;
+      aa.scratch = s->attn_scratch;
+      aa.out_f32 = s->attn_f32;
+      RG_LAUNCH(s, launch_attention(aa, L));
+      if (s->family_mask & (1u << PROF_ATTN)) s->launches_in_step++;  // split + combine
+    }
     RG_LAUNCH(s, launch_to16(s->attn_f32, qw, qw, ncols, xop, L));
     if ((rc = gemm_tc(s, W.o, ncols, s->tp_part[0], d, L))) return rc;
     if (tp) {
@@ -945,7 +979,7 @@ static int32_t mega_setup(rg_session *s) {
   P.attn_out = s->attn_f32;
   P.attn_scratch = s->attn_scratch;
   P.max_splits = mega_max_splits(s->ctx, grid, c.n_kv_heads, s->kv_f32);
-  if ((size_t)c.n_heads * P.max_splits * (hd + 2) > attn_scratch_floats(WMAX, s->heads_l, hd, s->ctx)) return RG_OK;
+  if ((size_t)c.n_heads * P.max_splits * (hd + 2) > attn_scratch_floats(SCOLS, s->heads_l, hd, s->ctx)) return RG_OK;
   P.embed = s->token_embd.d;
   P.embed_type = s->token_embd.type;
   P.x = s->x;
@@ -1493,17 +1527,17 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   s->history_cap = 8192;
   RG_TRY(dalloc(s.get(), &s->d_history, (size_t)s->history_cap * BMAX));
   RG_TRY(dalloc(s.get(), &s->d_status, 1));
-  // per-column buffers are sized for the widest forward (a 256-token prefill chunk)
+  // per-column buffers are sized for the widest forward (a 1024-token prefill chunk)
   RG_TRY(dalloc(s.get(), &s->x, (size_t)WMAX * d));
   RG_TRY(dalloc(s.get(), &s->xn_f32, (size_t)MAXC * d));
   RG_TRY(dalloc(s.get(), &s->qkv, (size_t)WMAX * (qw + 2 * kw)));
   RG_TRY(dalloc(s.get(), &s->q_rot, (size_t)WMAX * qw));
-  RG_TRY(dalloc(s.get(), &s->attn_scratch, attn_scratch_floats(WMAX, s->heads_l, hd, s->ctx)));
+  RG_TRY(dalloc(s.get(), &s->attn_scratch, attn_scratch_floats(SCOLS, s->heads_l, hd, s->ctx)));
   RG_TRY(dalloc(s.get(), &s->attn_f32, (size_t)WMAX * qw));
   if (fused_attention_supported(s->heads_l, s->kv_l, hd) && !env_flag("RG_B200_SPLIT_ATTENTION")) {
     s->attn_max_splits = fused_attn_max_splits(s->ctx, hd, s->kv_f32, s->sm_count, s->kv_l);
     if (s->attn_max_splits <= fused_attn_split_cap() &&
-        (size_t)2 * s->heads_l * s->attn_max_splits * (hd + 2) <= attn_scratch_floats(WMAX, s->heads_l, hd, s->ctx)) {
+        (size_t)2 * s->heads_l * s->attn_max_splits * (hd + 2) <= attn_scratch_floats(SCOLS, s->heads_l, hd, s->ctx)) {
       RG_TRY(dalloc(s.get(), &s->attn_counters, (size_t)2 * s->kv_l));
       RG_CUDA(cudaMemsetAsync(s->attn_counters, 0, sizeof(unsigned) * 2 * (size_t)s->kv_l, s->stream));
     }
@@ -1518,6 +1552,7 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   uint8_t *raw;
   s->xb_ld = std::max(d, std::max(qw, s->ffn_l));
   RG_TRY(dalloc(s.get(), &raw, (size_t)2 * WMAX * s->xb_ld * 2));
+  RG_TRY(dalloc(s.get(), &s->split_scratch, (size_t)BMAX * 2 * s->sm_count * 128));  // splits * rows <= 2 * SMs * 128
   s->gemm_mode = (s->opt.reserved[1] >= 1 && s->opt.reserved[1] <= 3) ? s->opt.reserved[1] - 1 : QGEMM_F16X3;
   s->xb = raw;
   RG_TRY(dalloc(s.get(), &raw, xpack_bytes(d, MAXC)));
@@ -1631,9 +1666,10 @@ int32_t rg_b200_prefill(rg_session *s, int32_t row, const int32_t *ids, size_t n
     if (ids[i] < 0 || ids[i] >= s->cfg.vocab) return fail(RG_TOKEN_OUT_OF_RANGE, "token " + std::to_string(ids[i]) + " at index " + std::to_string(i));
   RG_CUDA(cudaSetDevice(s->opt.device));
   RG_CUDA(cudaEventRecord(s->ev0, s->stream));
-  const bool wide_ok = wide_path_ok(s);  // prompt chunks of 256 tokens on the tensor cores
+  const bool wide_ok = wide_path_ok(s);  // prompt chunks of up to 1024 tokens on the tensor cores
   for (size_t done = 0; done < n;) {
-    const int chunk = (int)std::min<size_t>(wide_ok ? WMAX : MAXC, n - done);
+    const int wide_chunk = prefill_attention_supported(s->heads_l, s->kv_l, s->cfg.head_dim) && !env_flag("RG_B200_SPLIT_ATTENTION") ? WMAX : SCOLS;
+    const int chunk = (int)std::min<size_t>(wide_ok ? wide_chunk : MAXC, n - done);
     const bool last = done + (size_t)chunk == n;
     Ctrl *h = s->h_ctrl;
     for (int i = 0; i < chunk; ++i) {
@@ -1644,7 +1680,10 @@ int32_t rg_b200_prefill(rg_session *s, int32_t row, const int32_t *ids, size_t n
     h->logit_cols[0] = chunk - 1;
     h->step = 0;
     if ((rc = upload_ctrl(s))) return rc;
-    if ((rc = run_step(s, chunk, last ? 1 : 0, false, false))) return rc;
+    s->chunk_is_prompt = !env_flag("RG_B200_SPLIT_ATTENTION");
+    rc = run_step(s, chunk, last ? 1 : 0, false, false);
+    s->chunk_is_prompt = false;
+    if (rc) return rc;
     // the pinned control block is reused by the next chunk: wait for the upload to be consumed
     if (!last) RG_CUDA(x_sync(s->stream));
     done += (size_t)chunk;
