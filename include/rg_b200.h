@@ -173,6 +173,19 @@ int32_t rg_b200_decode(rg_session *s, const int32_t *tokens, int32_t batch, floa
  * not fed back.  out has room for max_new ids. */
 int32_t rg_b200_generate_greedy(rg_session *s, const int32_t *prompt, size_t n_prompt, size_t max_new,
                                 int32_t *out, size_t *n_out, int32_t *stopped);
+/* LlamaSampling::GumbelMax (src/models/transformer/generation.rs:10-19,227-287): the selected id of
+ * every row maximises logit / max(temperature, 1e-12) - ln(-ln(max(u, 1e-12))) in f32 with strict
+ * '>' (lowest id among equal scores); any non-finite LOGIT is RG_NON_FINITE_LOGITS.  Randomness is an
+ * explicit tape of uniforms supplied by the caller: `uniforms` holds one row of vocab_size floats per
+ * decoded row for rg_b200_decode_sampled, and max_new rows (row-major [step, vocabulary]; row 0 picks
+ * the first token from the prompt's logits) for rg_b200_generate_sampled.  Otherwise these behave as
+ * rg_b200_decode / rg_b200_generate_greedy. */
+int32_t rg_b200_decode_sampled(rg_session *s, const int32_t *tokens, int32_t batch, float temperature,
+                               const float *uniforms, float *logits, int32_t *ids);
+int32_t rg_b200_generate_sampled(rg_session *s, const int32_t *prompt, size_t n_prompt, size_t max_new,
+                                 float temperature, const float *uniforms, int32_t *out, size_t *n_out,
+                                 int32_t *stopped);
+
 /* Device-resident greedy loop for rows 0..batch-1: `steps` replays of the decode graph with the
  * selected token fed back on the device (the device-greedy session of
  * metal_greedy_generation.rs:52-72).  first_tokens[batch] seeds it; out [steps, batch] (nullable)

@@ -77,6 +77,7 @@ def lib():
         L.rgo_cache_len.argtypes = [C.c_void_p]
         L.rgo_forward.argtypes = [C.c_void_p, C.c_void_p, i32p, C.c_int, C.c_int, C.c_int, C.c_int, f32p]
         L.rgo_select_greedy.argtypes = [f32p, C.c_int, i32p]
+        L.rgo_select_gumbel.argtypes = [f32p, C.c_int, C.c_float, f32p, i32p]
         L.rgo_generate_greedy.argtypes = [C.c_void_p, C.c_void_p, i32p, C.c_int, C.c_int, C.c_int, C.c_int, i32p,
                                           C.POINTER(C.c_int), C.POINTER(C.c_int)]
         L.rgo_attention_decode.argtypes = [f32p, f32p, f32p, C.c_int, C.c_int, C.c_int, C.c_int, f32p]
@@ -169,6 +170,18 @@ def select_greedy(row: np.ndarray) -> int:
     rc = lib().rgo_select_greedy(_f32(row), row.size, C.byref(tok))
     if rc:
         raise OracleError(rc, "select_greedy")
+    return tok.value
+
+
+def select_gumbel(row: np.ndarray, temperature: float, uniforms: np.ndarray) -> int:
+    """Gumbel-max with an explicit uniform row (generation.rs:260-287)."""
+    row = np.ascontiguousarray(row, dtype=np.float32)
+    u = np.ascontiguousarray(uniforms, dtype=np.float32)
+    assert u.size == row.size
+    tok = C.c_int32(-1)
+    rc = lib().rgo_select_gumbel(_f32(row), row.size, float(temperature), _f32(u), C.byref(tok))
+    if rc:
+        raise OracleError(rc, "select_gumbel")
     return tok.value
 
 

@@ -615,6 +615,27 @@ int rgo_select_greedy(const float *row, int vocab, int32_t *token) {
   return RGO_OK;
 }
 
+/* Gumbel-max selection with an explicit uniform tape (src/models/transformer/generation.rs:10-19,
+ * 260-287): score = logit / max(T, 1e-12) - ln(-ln(max(u, 1e-12))), every step in f32; strict '>'
+ * keeps the lowest id among equal scores; only the logits are checked for finiteness. */
+int rgo_select_gumbel(const float *row, int vocab, float temperature, const float *uniforms, int32_t *token) {
+  if (vocab <= 0 || !uniforms) return RGO_ERR_NON_FINITE_LOGITS;
+  int best = -1;
+  float best_score = 0.0f;
+  const float t = fmaxf(temperature, 1e-12f);
+  for (int i = 0; i < vocab; ++i) {
+    if (!isfinite(row[i])) return RGO_ERR_NON_FINITE_LOGITS;
+    const float u = fmaxf(uniforms[i], 1e-12f);
+    const float score = row[i] / t - logf(-logf(u));
+    if (best < 0 || score > best_score) {
+      best = i;
+      best_score = score;
+    }
+  }
+  *token = best;
+  return RGO_OK;
+}
+
 /* src/models/transformer/generation.rs:106-160: prefill the whole prompt, then one-token steps;
  * the last generated token is not fed back; stop on EOS/EOT. */
 int rgo_generate_greedy(const rgo_model *m, rgo_cache *cache, const int32_t *prompt, int n_prompt, int max_new,

@@ -116,6 +116,7 @@ int rgo_forward(const rgo_model *model, rgo_cache *cache, const int32_t *tokens,
 /* src/models/transformer/generation.rs:260-287: strict '>' so the lowest id wins ties; any
  * non-finite logit is an error. */
 int rgo_select_greedy(const float *row, int vocab, int32_t *token);
+int rgo_select_gumbel(const float *row, int vocab, float temperature, const float *uniforms, int32_t *token);
 
 /* src/models/transformer/generation.rs:106-160. */
 int rgo_generate_greedy(const rgo_model *model, rgo_cache *cache, const int32_t *prompt,

@@ -376,17 +376,23 @@ __global__ void attn_combine_kernel(const float *scratch, int heads, int hd, con
 // ------------------------------------------------------------------------------ greedy selection
 // src/models/transformer/generation.rs:260-287: strict '>' so the lowest id wins ties; any
 // non-finite logit is an error, reported as id -1 (the sentinel of metal_step.rs:964-987).
-__global__ void argmax_kernel(const float *logits, int ld, int vocab, int32_t *out_ids) {
+// With a uniform tape the score is the Gumbel-max transform of generation.rs:10-19,273-278:
+// logit / max(T, 1e-12) - ln(-ln(max(u, 1e-12))), one row of `vocab` uniforms per column.
+__global__ void argmax_kernel(const float *logits, int ld, int vocab, const float *uniforms, float temperature,
+                              int32_t *out_ids) {
   pdl_wait();
   pdl_launch_dependents();
   const int c = blockIdx.x;
   const float *row = logits + (size_t)c * ld;
+  const float *urow = uniforms ? uniforms + (size_t)c * vocab : nullptr;
+  const float t = fmaxf(temperature, 1e-12f);
   float best = -INFINITY;
   int idx = 0x7fffffff;
   int bad = 0;
   for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = row[i];
+    float v = row[i];
     if (!finite_f32(v)) bad = 1;
+    if (urow) v = __fsub_rn(__fdiv_rn(v, t), logf(-logf(fmaxf(urow[i], 1e-12f))));
     if (v > best || idx == 0x7fffffff) {
       best = v;
       idx = i;
@@ -671,8 +677,12 @@ cudaError_t launch_attention(const AttnArgs &a, const LaunchCfg &cfg) {
   return launch(attn_combine_kernel, dim3(a.heads, a.cols), dim3(MAX_HD), 0, cfg, (const float *)a.scratch, a.heads, a.hd,
                 a.col_pos, splits, a.cols, static_cast<__half *>(a.out_pack), a.out_f32);
 }
+cudaError_t launch_select(const float *logits, int ld, int vocab, int cols, const float *uniforms, float temperature,
+                          int32_t *out_ids, const LaunchCfg &cfg) {
+  return launch(argmax_kernel, dim3((unsigned)cols), dim3(1024), 0, cfg, logits, ld, vocab, uniforms, temperature, out_ids);
+}
 cudaError_t launch_argmax(const float *logits, int ld, int vocab, int cols, int32_t *out_ids, const LaunchCfg &cfg) {
-  return launch(argmax_kernel, dim3(cols), dim3(1024), 0, cfg, logits, ld, vocab, out_ids);
+  return launch_select(logits, ld, vocab, cols, nullptr, 1.0f, out_ids, cfg);
 }
 cudaError_t launch_advance(const int32_t *ids, int32_t *tokens, int32_t *pos, int32_t *history, int32_t *step_counter, int cols,
                            const LaunchCfg &cfg) {

@@ -12,11 +12,13 @@
 //     the raw block bytes of the 128 weight rows, 256 columns (8 blocks) at a time, come through
 //     a second tiled 2-D map into a small ring, so no thread waits on global memory.
 //   * warp 1: allocates TMEM, issues tcgen05.mma from one thread, commits to mbarriers.
-//   * warps 2-9: two threads per weight row; each expands one block per stage (nibbles to exact
+//   * warps 2-17 (two groups of eight taking alternate stages): two threads per weight row; each expands one block per stage (nibbles to exact
 //     16-bit integers by bit pattern, one packed subtract and one packed multiply by the block
-//     scale per two weights) and writes its half of the 128-byte row into the K-major,
-//     128-byte-swizzled A tile; afterwards the same warps read the accumulator with tcgen05.ld
-//     and store it.
+//     scale per two weights) and writes its 32 values with tcgen05.st straight into TENSOR MEMORY:
+//     the A operand of the MMA is read from TMEM (lane = weight row, one 32-bit column per two K
+//     values), so the dequantised weights never pass through shared memory, whose bandwidth is
+//     then left to the activation tiles.  Afterwards the same warps read the accumulator with
+//     tcgen05.ld and store it.
 //   * Operand rings of 3-4 stages with bounded mbarrier waits; a time-out records a status and
 //     the kernel still frees its TMEM and exits.
 // Operand modes: bf16 (weights enter as bf16(bf16(d) * (n - 8)) for Q4_0), f16 (weights enter as
@@ -40,8 +42,9 @@ constexpr int TM = 128;       // weight rows per tile (MMA M)
 constexpr int KSTEP = 64;     // elements per stage (128 bytes: one swizzle row)
 constexpr int RAW_STEPS = 4;  // 64-element stages per raw weight tile (256 columns = 8 blocks)
 constexpr int RAW_NS = 2;     // raw ring depth
-constexpr int THREADS = 320;  // TMA warp, MMA warp, eight dequantisation / epilogue warps
-constexpr int A_BYTES = TM * KSTEP * 2;
+constexpr int DQ_GROUPS = 2;   // groups of eight dequantisation warps; group g expands the stages i = g (mod 2)
+constexpr int THREADS = 64 + DQ_GROUPS * 256;  // TMA warp, MMA warp, dequantisation / epilogue warps
+constexpr int A_COLS = KSTEP / 2;  // TMEM columns of one dequantised A stage (two 16-bit values per column)
 
 struct Params {
   int n, k;     // weight rows, columns
@@ -82,6 +85,21 @@ __device__ __forceinline__ void umma_16bit(uint32_t tmem_d, uint64_t adesc, uint
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Same with the A operand in tensor memory.
+__device__ __forceinline__ void umma_16bit_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_store16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+      "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
@@ -206,9 +224,9 @@ __device__ __forceinline__ void q8_block_split(uint32_t dbits16, const uint32_t 
   }
 }
 
-__host__ __device__ constexpr int ring_depth(int tn, bool comp) {
-  return comp ? (tn >= 128 ? 2 : 3) : (tn > 256 ? 2 : tn > 128 ? 3 : 4);
-}
+// Ring depth of the activation tiles (shared memory) and of the dequantised A stages (tensor memory).
+__host__ __device__ constexpr int ring_depth(int tn, bool comp) { return (comp && tn > 128) ? 2 : 4; }
+__host__ __device__ constexpr int pow2_cols(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
 
 template <int QT, int TN, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -220,14 +238,16 @@ __global__ void __launch_bounds__(THREADS, 1)
   constexpr int BB = Q4 ? 18 : 34;
   constexpr int NS = ring_depth(TN, COMP);  // operand ring depth
   constexpr int B_BYTES = TN * KSTEP * 2;
-  constexpr int A_STAGE = NPL * A_BYTES, B_STAGE = NPL * B_BYTES;
+  constexpr int B_STAGE = NPL * B_BYTES;
+  constexpr int A_STAGE_COLS = NPL * A_COLS;  // TMEM columns of one A stage (hi, lo)
   constexpr int RAW_ROW = 8 * BB;  // bytes of one weight row in a raw tile (144 / 272)
   constexpr int RAW_BYTES = TM * RAW_ROW;
-  constexpr int TMEM_COLS = TN < 32 ? 32 : TN;
+  constexpr int ACC_COLS = TN < 32 ? 32 : TN;            // accumulator columns, then the A ring
+  constexpr int TMEM_COLS = pow2_cols(ACC_COLS + NS * A_STAGE_COLS);
+  static_assert(ACC_COLS + NS * A_STAGE_COLS <= 512, "tensor memory budget");
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t *a_ring = smem;
-  uint8_t *b_ring = smem + NS * A_STAGE;
+  uint8_t *b_ring = smem;
   uint8_t *raw_ring = b_ring + NS * B_STAGE;
   uint64_t *bars = reinterpret_cast<uint64_t *>(raw_ring + RAW_NS * RAW_BYTES);
   uint64_t *b_full = bars, *a_full = bars + NS, *slot_free = bars + 2 * NS;
@@ -248,7 +268,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
     for (int s = 0; s < RAW_NS; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_free[s], 256);
+      mbar_init(&raw_free[s], DQ_GROUPS * 256);
     }
     mbar_init(acc_done, 1);
     *dead = 0;
@@ -281,35 +301,31 @@ __global__ void __launch_bounds__(THREADS, 1)
         if (i >= NS) mbar_wait_bounded(&slot_free[slot], (uint32_t)((i / NS - 1) & 1), dead, P.status);
         mbar_expect_tx(&b_full[slot], (uint32_t)B_STAGE);
         tma_tile_2d(b_ring + slot * B_STAGE, &xmap, (step0 + i) * KSTEP, tok0, &b_full[slot]);
-        if constexpr (TN > 256)  // a TMA box holds at most 256 rows: the second half of the token tile
-          tma_tile_2d(b_ring + slot * B_STAGE + 256 * 128, &xmap, (step0 + i) * KSTEP, tok0 + 256, &b_full[slot]);
         if constexpr (COMP) tma_tile_2d(b_ring + slot * B_STAGE + B_BYTES, &xlo_map, (step0 + i) * KSTEP, tok0, &b_full[slot]);
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
-      // a 512-token tile is two 256-column accumulators fed by the same dequantised A tile
-      constexpr int MMA_N = TN > 256 ? 256 : TN;
-      constexpr uint32_t idesc = umma_idesc(TM, MMA_N, F16);
+      constexpr uint32_t idesc = umma_idesc(TM, TN, F16);
       for (int i = 0; i < nsteps; ++i) {
         const int slot = i % NS;
         const uint32_t ph = (uint32_t)((i / NS) & 1);
         mbar_wait_bounded(&a_full[slot], ph, dead, P.status);
         mbar_wait_bounded(&b_full[slot], ph, dead, P.status);
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(a_ring + slot * A_STAGE), b_addr = smem_u32(b_ring + slot * B_STAGE);
+        const uint32_t b_addr = smem_u32(b_ring + slot * B_STAGE);
+        const uint32_t a_tm = tmem_base + (uint32_t)(ACC_COLS + slot * A_STAGE_COLS);  // lane 0, first column of the stage
 #pragma unroll
         for (int kk = 0; kk < KSTEP / 16; ++kk) {
-          const uint64_t a_hi = umma_desc(a_addr + kk * 32), b_hi = umma_desc(b_addr + kk * 32);
+          const uint32_t a_hi = a_tm + kk * 8;  // 16 K values = 8 columns
+          const uint64_t b_hi = umma_desc(b_addr + kk * 32);
           if constexpr (COMP) {  // the small terms first, then hi.hi
-            umma_16bit(tmem_base, a_hi, umma_desc(b_addr + B_BYTES + kk * 32), idesc, (i > 0 || kk > 0) ? 1u : 0u);
-            umma_16bit(tmem_base, umma_desc(a_addr + A_BYTES + kk * 32), b_hi, idesc, 1u);
-            umma_16bit(tmem_base, a_hi, b_hi, idesc, 1u);
+            umma_16bit_ta(tmem_base, a_hi, umma_desc(b_addr + B_BYTES + kk * 32), idesc, (i > 0 || kk > 0) ? 1u : 0u);
+            umma_16bit_ta(tmem_base, a_hi + A_COLS, b_hi, idesc, 1u);
+            umma_16bit_ta(tmem_base, a_hi, b_hi, idesc, 1u);
           } else {
-            umma_16bit(tmem_base, a_hi, b_hi, idesc, (i > 0 || kk > 0) ? 1u : 0u);
-            if constexpr (TN > 256)
-              umma_16bit(tmem_base + 256, a_hi, umma_desc(b_addr + 256 * 128 + kk * 32), idesc, (i > 0 || kk > 0) ? 1u : 0u);
+            umma_16bit_ta(tmem_base, a_hi, b_hi, idesc, (i > 0 || kk > 0) ? 1u : 0u);
           }
         }
         umma_commit(&slot_free[slot]);  // the slot may be rewritten once these MMAs have read it
@@ -319,13 +335,16 @@ __global__ void __launch_bounds__(THREADS, 1)
   } else {
     // ---------------------------------------------------------------- dequantisation: one block (half of a
     // stage's 64 columns) of one weight row per thread, two threads per row
-    const int tdq = threadIdx.x - 64;          // 0..255
-    const int r = tdq & 127, half = tdq >> 7;  // row of the tile, even / odd block of the stage
+    // a warp may touch only the TMEM lanes 32 * (warp % 4) .. +31, so its lanes own exactly those weight rows
+    const int r = (warp & 3) * 32 + lane;  // row of the tile
+    const int half = ((warp - 2) >> 2) & 1;  // even / odd block of the stage
+    const int grp = (warp - 2) >> 3;         // which stages this warp expands: two groups overlap the latency of
+                                             // load -> expand -> tcgen05.st of consecutive stages
     constexpr int QW = Q4 ? 4 : 8;             // quant words per block
-    for (int i = 0; i < nsteps; ++i) {
+    for (int i = grp; i < nsteps; i += DQ_GROUPS) {
       const int slot = i % NS;
       const int j = i / RAW_STEPS, rs = j % RAW_NS, sub = i % RAW_STEPS;
-      if (sub == 0) mbar_wait_bounded(&raw_full[rs], (uint32_t)((j / RAW_NS) & 1), dead, P.status);
+      if (sub < DQ_GROUPS) mbar_wait_bounded(&raw_full[rs], (uint32_t)((j / RAW_NS) & 1), dead, P.status);
       // pair layout: [d0 | q0] [d1 | q1] with a 2-byte scale in front of each block: the even block's
       // quants straddle word boundaries (funnel shift), the odd block's are word aligned
       const uint32_t *src = reinterpret_cast<const uint32_t *>(raw_ring + rs * RAW_BYTES + r * RAW_ROW + sub * 2 * BB);
@@ -342,7 +361,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
         for (int w = 0; w < QW; ++w) q[w] = src[QW + 1 + w];
       }
-      uint32_t lows[COMP ? 16 : 1];
+      uint32_t lows[16];
       if constexpr (COMP) {
         if constexpr (Q4) {
           q4_block_split(dbits, q, vals, lows);
@@ -354,19 +373,15 @@ __global__ void __launch_bounds__(THREADS, 1)
       } else {
         q8_block_to_16<F16>(dbits, q, vals);
       }
-      if (sub == RAW_STEPS - 1 || i + 1 == nsteps) mbar_arrive(&raw_free[rs]);  // raw bytes are in registers now
+      if (sub >= RAW_STEPS - DQ_GROUPS) mbar_arrive(&raw_free[rs]);  // this group's last stage of the raw tile is in registers
       if (i >= NS) mbar_wait_bounded(&slot_free[slot], (uint32_t)((i / NS - 1) & 1), dead, P.status);
-      uint8_t *row_dst = a_ring + slot * A_STAGE + r * 128;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint4 chunk = make_uint4(vals[4 * c], vals[4 * c + 1], vals[4 * c + 2], vals[4 * c + 3]);
-        *reinterpret_cast<uint4 *>(row_dst + (((4 * half + c) ^ (r & 7)) << 4)) = chunk;
-        if constexpr (COMP) {
-          chunk = make_uint4(lows[4 * c], lows[4 * c + 1], lows[4 * c + 2], lows[4 * c + 3]);
-          *reinterpret_cast<uint4 *>(row_dst + A_BYTES + (((4 * half + c) ^ (r & 7)) << 4)) = chunk;
-        }
-      }
-      proxy_fence_async();  // generic-proxy stores must be visible to the tensor core's async reads
+      tc_fence_after();
+      // this thread's block = 16 columns of its row's lane: [stage][plane][even block | odd block]
+      const uint32_t a_tm = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(ACC_COLS + slot * A_STAGE_COLS + half * 16);
+      tmem_store16(a_tm, vals);
+      if constexpr (COMP) tmem_store16(a_tm + A_COLS, lows);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      tc_fence_before();
       mbar_arrive(&a_full[slot]);
     }
     // ---------------------------------------------------------------- epilogue: TMEM -> global
@@ -377,7 +392,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     float *out = P.out + (size_t)blockIdx.z * P.split_stride;
     if (nsteps > 0) {
 #pragma unroll 1
-      for (int c0 = (warp >= 6 ? 16 : 0); c0 < TN; c0 += 32) {  // two warps share a lane quarter
+      for (int c0 = ((warp - 2) >> 2) * 16; c0 < TN; c0 += 16 * 2 * DQ_GROUPS) {  // four warps share a lane quarter
         if (tok0 + c0 >= P.m) break;
         uint32_t v[16];
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
@@ -432,7 +447,7 @@ cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
   for (int plane = 0; plane < NPL; ++plane) {
     const cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
     const cuuint64_t strides[1] = {(cuuint64_t)a.ldx * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)KSTEP, (cuuint32_t)(TN > 256 ? 256 : TN)};
+    const cuuint32_t box[2] = {(cuuint32_t)KSTEP, (cuuint32_t)TN};
     if (fn(plane ? &xlo_map : &xmap, F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
            const_cast<void *>(plane ? a.x16_lo : a.x16), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -461,8 +476,7 @@ cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
   P.ldc = a.ldc;
   P.split_stride = a.split_stride;
   P.status = cfg.status;
-  constexpr size_t smem =
-      1024 + NS * NPL * (A_BYTES + TN * KSTEP * 2) + RAW_NS * TM * RAW_ROW + (3 * NS + 2 * RAW_NS + 1) * 8 + 16;
+  constexpr size_t smem = 1024 + NS * NPL * (TN * KSTEP * 2) + RAW_NS * TM * RAW_ROW + (3 * NS + 2 * RAW_NS + 1) * 8 + 16;
   static_assert(smem <= 227 * 1024, "tile configuration exceeds the shared memory of one SM");
   auto kernel = qgemm_tc_kernel<QT, TN, MODE>;
   static bool attr_done = false;  // per instantiation
@@ -487,10 +501,6 @@ cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
 template <int QT, int MODE>
 cudaError_t launch_n(const QGemmArgs &a, const LaunchCfg &cfg) {
   if constexpr (MODE != QGEMM_F16X3) {  // the compensated mode keeps two planes per operand: 128 tokens at most
-    // 512 tokens per weight tile halve the dequantisation work per flop; the Q8_0 raw ring does not leave room for it
-    if constexpr (QT == RG_TYPE_Q4_0) {
-      if (a.m > 256) return launch_t<QT, 512, MODE>(a, cfg);
-    }
     if (a.m > 128) return launch_t<QT, 256, MODE>(a, cfg);
   }
   if (a.m > 64) return launch_t<QT, 128, MODE>(a, cfg);

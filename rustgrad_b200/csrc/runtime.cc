@@ -252,6 +252,10 @@ struct rg_session {
   float *x = nullptr, *xn_f32 = nullptr, *qkv = nullptr, *q_rot = nullptr, *attn_scratch = nullptr, *attn_f32 = nullptr;
   float *partial = nullptr, *gate_f32 = nullptr, *up_f32 = nullptr, *h_f32 = nullptr, *logits = nullptr, *logits_l = nullptr;
   void *xn_pack = nullptr, *attn_pack = nullptr, *h_pack = nullptr, *head_pack = nullptr;
+  // Gumbel-max selection for the current step: device rows of uniforms [logit cols][vocab]; null = greedy
+  const float *sample_uniforms = nullptr;
+  float sample_temperature = 1.0f;
+  float *d_uniforms = nullptr;  // [BMAX][vocab], allocated on first use
   bool chunk_is_prompt = false;  // the columns of the current step are consecutive positions of one sequence
   float *split_scratch = nullptr;  // K-split partial tiles of the tensor-core GEMM at small token counts
   void *xb = nullptr;  // 16-bit operand planes (hi, lo) of the tensor-core path: [2][WMAX][max(d, qw, ffn_l)]
@@ -590,7 +594,7 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
       if ((rc = comm_group_end(&err))) return fail(rc, err);
       am.pdl = false;
     }
-    RG_LAUNCH(s, launch_argmax(s->logits, c.vocab, c.vocab, n_logit_cols, s->d_ids, am));
+    RG_LAUNCH(s, launch_select(s->logits, c.vocab, c.vocab, n_logit_cols, s->sample_uniforms, s->sample_temperature, s->d_ids, am));
     if (advance) RG_LAUNCH(s, launch_advance(s->d_ids, ctl->tokens, ctl->pos, s->d_history, &ctl->step, ncols, L));
   }
   return RG_OK;
@@ -775,7 +779,7 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
       if ((rc = comm_group_end(&err))) return fail(rc, err);
       am.pdl = false;
     }
-    RG_LAUNCH(s, launch_argmax(s->logits, c.vocab, c.vocab, n_logit_cols, s->d_ids, am));
+    RG_LAUNCH(s, launch_select(s->logits, c.vocab, c.vocab, n_logit_cols, s->sample_uniforms, s->sample_temperature, s->d_ids, am));
     if (advance) RG_LAUNCH(s, launch_advance(s->d_ids, ctl->tokens, ctl->pos, s->d_history, &ctl->step, ncols, L));
   }
   return RG_OK;
@@ -1005,7 +1009,8 @@ static int32_t forward_mega(rg_session *s, bool advance, bool profile) {
 // One forward over `ncols` columns described by the device control block.  n_logit_cols columns
 // (indices in ctrl.logit_cols) get logits + greedy ids; 0 skips the head (non-final prefill chunk).
 static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance) {
-  if (s->mega_ok && ncols == 1 && n_logit_cols == 1 && s->family_mask == 0xffffffffu) return forward_mega(s, advance, false);
+  if (s->mega_ok && ncols == 1 && n_logit_cols == 1 && !s->sample_uniforms && s->family_mask == 0xffffffffu)
+    return forward_mega(s, advance, false);
   if (small_batch_path(s, ncols)) return forward_small(s, ncols, n_logit_cols, advance);
   if (ncols > MAXC) {
     if (!wide_path_ok(s))
@@ -1130,7 +1135,7 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
       if ((rc = comm_group_end(&err))) return fail(rc, err);
       am.pdl = false;
     }
-    RG_LAUNCH(s, launch_argmax(s->logits, c.vocab, c.vocab, n_logit_cols, s->d_ids, am));
+    RG_LAUNCH(s, launch_select(s->logits, c.vocab, c.vocab, n_logit_cols, s->sample_uniforms, s->sample_temperature, s->d_ids, am));
     if (advance) RG_LAUNCH(s, launch_advance(s->d_ids, ctl->tokens, ctl->pos, s->d_history, &ctl->step, ncols, L));
   }
   return RG_OK;
@@ -1170,7 +1175,9 @@ static int32_t decode_graph(rg_session *s, int batch, cudaGraphExec_t *out) {
   return RG_OK;
 }
 
-static bool mega_step(const rg_session *s, int ncols, int n_logit_cols) { return s->mega_ok && ncols == 1 && n_logit_cols == 1; }
+static bool mega_step(const rg_session *s, int ncols, int n_logit_cols) {
+  return s->mega_ok && ncols == 1 && n_logit_cols == 1 && !s->sample_uniforms;  // the persistent kernel selects greedily
+}
 
 static int32_t run_step(rg_session *s, int ncols, int n_logit_cols, bool advance, bool allow_graph) {
   if (allow_graph && s->use_graph && !mega_step(s, ncols, n_logit_cols)) {  // the persistent kernel is one launch already
@@ -1654,7 +1661,25 @@ int32_t rg_b200_reset_sequence(rg_session *s) {
   return RG_OK;
 }
 
-int32_t rg_b200_prefill(rg_session *s, int32_t row, const int32_t *ids, size_t n, float *last_logits) {
+// Uploads `rows` rows of uniforms and arms Gumbel-max selection for the next step(s); null disarms.
+static int32_t arm_sampling(rg_session *s, float temperature, const float *uniforms, int rows) {
+  s->sample_uniforms = nullptr;
+  if (!uniforms) return RG_OK;
+  if (!s->d_uniforms) {
+    int32_t rc = dalloc(s, &s->d_uniforms, (size_t)BMAX * (size_t)s->cfg.vocab);
+    if (rc) return rc;
+  }
+  const size_t bytes = sizeof(float) * (size_t)rows * (size_t)s->cfg.vocab;
+  RG_CUDA(x_memcpy_async(s->d_uniforms, uniforms, bytes, cudaMemcpyHostToDevice, s->stream));
+  s->report.h2d_calls++;
+  s->report.h2d_bytes += bytes;
+  s->sample_uniforms = s->d_uniforms;
+  s->sample_temperature = temperature;
+  return RG_OK;
+}
+
+static int32_t prefill_impl(rg_session *s, int32_t row, const int32_t *ids, size_t n, float *last_logits, float temperature,
+                            const float *uniforms) {
   int32_t rc = check_live(s);
   if (rc) return rc;
   if (!ids) return fail(RG_INVALID_ARGUMENT, "null ids");
@@ -1665,6 +1690,11 @@ int32_t rg_b200_prefill(rg_session *s, int32_t row, const int32_t *ids, size_t n
   for (size_t i = 0; i < n; ++i)
     if (ids[i] < 0 || ids[i] >= s->cfg.vocab) return fail(RG_TOKEN_OUT_OF_RANGE, "token " + std::to_string(ids[i]) + " at index " + std::to_string(i));
   RG_CUDA(cudaSetDevice(s->opt.device));
+  if ((rc = arm_sampling(s, temperature, uniforms, 1))) return rc;
+  struct Disarm {
+    rg_session *s;
+    ~Disarm() { s->sample_uniforms = nullptr; }
+  } disarm{s};
   RG_CUDA(cudaEventRecord(s->ev0, s->stream));
   const bool wide_ok = wide_path_ok(s);  // prompt chunks of up to 1024 tokens on the tensor cores
   for (size_t done = 0; done < n;) {
@@ -1695,7 +1725,12 @@ int32_t rg_b200_prefill(rg_session *s, int32_t row, const int32_t *ids, size_t n
   return RG_OK;
 }
 
-int32_t rg_b200_decode(rg_session *s, const int32_t *tokens, int32_t batch, float *logits, int32_t *greedy) {
+int32_t rg_b200_prefill(rg_session *s, int32_t row, const int32_t *ids, size_t n, float *last_logits) {
+  return prefill_impl(s, row, ids, n, last_logits, 1.0f, nullptr);
+}
+
+static int32_t decode_impl(rg_session *s, const int32_t *tokens, int32_t batch, float *logits, int32_t *greedy, float temperature,
+                           const float *uniforms) {
   int32_t rc = check_live(s);
   if (rc) return rc;
   if (!tokens) return fail(RG_INVALID_ARGUMENT, "null tokens");
@@ -1713,9 +1748,14 @@ int32_t rg_b200_decode(rg_session *s, const int32_t *tokens, int32_t batch, floa
     h->logit_cols[i] = i;
   }
   h->step = 0;
+  if ((rc = arm_sampling(s, temperature, uniforms, batch))) return rc;
+  struct Disarm {
+    rg_session *s;
+    ~Disarm() { s->sample_uniforms = nullptr; }
+  } disarm{s};
   RG_CUDA(cudaEventRecord(s->ev0, s->stream));
   if ((rc = upload_ctrl(s))) return rc;
-  if ((rc = run_step(s, batch, batch, true, true))) return rc;
+  if ((rc = run_step(s, batch, batch, true, uniforms == nullptr))) return rc;  // the captured graph selects greedily
   RG_CUDA(cudaEventRecord(s->ev1, s->stream));
   rc = finish_step(s, batch, logits, logits ? batch : 0);
   if (rc && rc != RG_NON_FINITE_LOGITS) return rc;
@@ -1726,8 +1766,18 @@ int32_t rg_b200_decode(rg_session *s, const int32_t *tokens, int32_t batch, floa
   return RG_OK;
 }
 
-int32_t rg_b200_generate_greedy(rg_session *s, const int32_t *prompt, size_t n_prompt, size_t max_new, int32_t *out, size_t *n_out,
-                                int32_t *stopped) {
+int32_t rg_b200_decode(rg_session *s, const int32_t *tokens, int32_t batch, float *logits, int32_t *greedy) {
+  return decode_impl(s, tokens, batch, logits, greedy, 1.0f, nullptr);
+}
+
+int32_t rg_b200_decode_sampled(rg_session *s, const int32_t *tokens, int32_t batch, float temperature, const float *uniforms,
+                               float *logits, int32_t *ids) {
+  if (!uniforms) return fail(RG_INVALID_ARGUMENT, "null uniforms");
+  return decode_impl(s, tokens, batch, logits, ids, temperature, uniforms);
+}
+
+static int32_t generate_impl(rg_session *s, const int32_t *prompt, size_t n_prompt, size_t max_new, int32_t *out, size_t *n_out,
+                             int32_t *stopped, bool sampled, float temperature, const float *uniforms) {
   int32_t rc = check_live(s);
   if (rc) return rc;
   if (!n_out || !stopped || (!out && max_new)) return fail(RG_INVALID_ARGUMENT, "null output");
@@ -1739,7 +1789,9 @@ int32_t rg_b200_generate_greedy(rg_session *s, const int32_t *prompt, size_t n_p
   for (size_t i = 0; i < n_prompt; ++i)
     if (prompt[i] < 0 || prompt[i] >= s->cfg.vocab) return fail(RG_TOKEN_OUT_OF_RANGE, "token " + std::to_string(prompt[i]) + " at index " + std::to_string(i));
   if (max_new == 0) return RG_OK;
-  if ((rc = rg_b200_prefill(s, 0, prompt, n_prompt, nullptr))) return rc;
+  if (sampled && !uniforms) return fail(RG_INVALID_ARGUMENT, "null uniforms");
+  const size_t V = (size_t)s->cfg.vocab;  // the tape is row-major [step, vocabulary] (generation.rs:7-9)
+  if ((rc = prefill_impl(s, 0, prompt, n_prompt, nullptr, temperature, sampled ? uniforms : nullptr))) return rc;
   int32_t token = s->h_ids[0];
   for (size_t step = 0; step < max_new; ++step) {
     out[(*n_out)++] = token;
@@ -1749,11 +1801,21 @@ int32_t rg_b200_generate_greedy(rg_session *s, const int32_t *prompt, size_t n_p
     }
     if (step + 1 < max_new) {
       int32_t next;
-      if ((rc = rg_b200_decode(s, &token, 1, nullptr, &next))) return rc;
+      if ((rc = decode_impl(s, &token, 1, nullptr, &next, temperature, sampled ? uniforms + (step + 1) * V : nullptr))) return rc;
       token = next;
     }
   }
   return RG_OK;
+}
+
+int32_t rg_b200_generate_greedy(rg_session *s, const int32_t *prompt, size_t n_prompt, size_t max_new, int32_t *out, size_t *n_out,
+                                int32_t *stopped) {
+  return generate_impl(s, prompt, n_prompt, max_new, out, n_out, stopped, false, 1.0f, nullptr);
+}
+
+int32_t rg_b200_generate_sampled(rg_session *s, const int32_t *prompt, size_t n_prompt, size_t max_new, float temperature,
+                                 const float *uniforms, int32_t *out, size_t *n_out, int32_t *stopped) {
+  return generate_impl(s, prompt, n_prompt, max_new, out, n_out, stopped, true, temperature, uniforms);
 }
 
 int32_t rg_b200_decode_loop(rg_session *s, const int32_t *first, int32_t batch, int32_t steps, int32_t *out, float *gpu_ms) {

@@ -270,20 +270,35 @@ class LlamaCudaSession:
         logits, _ = self.decode([token], want_logits=True)
         return logits[0]
 
-    def decode(self, tokens, want_logits: bool = False):
+    def decode(self, tokens, want_logits: bool = False, temperature: float | None = None, uniforms=None):
+        """One step for ``len(tokens)`` rows.  With ``temperature`` and ``uniforms`` ([rows, vocab]) the ids are
+        Gumbel-max samples (LlamaSampling::GumbelMax, generation.rs:10-19), otherwise greedy."""
         tokens = np.ascontiguousarray(tokens, dtype=np.int32)
         b = tokens.size
         logits = np.empty((b, self.vocab_size()), dtype=np.float32) if want_logits else None
-        greedy = np.empty(b, dtype=np.int32)
-        check(self._L.rg_b200_decode(self._h, _i32(tokens), b, _f32(logits) if want_logits else None, _i32(greedy)))
-        return logits, greedy
+        ids = np.empty(b, dtype=np.int32)
+        lp = _f32(logits) if want_logits else None
+        if uniforms is None:
+            check(self._L.rg_b200_decode(self._h, _i32(tokens), b, lp, _i32(ids)))
+        else:
+            u = np.ascontiguousarray(uniforms, dtype=np.float32).reshape(b, self.vocab_size())
+            check(self._L.rg_b200_decode_sampled(self._h, _i32(tokens), b, float(temperature), _f32(u), lp, _i32(ids)))
+        return logits, ids
 
-    def generate_ids(self, prompt_ids, max_new_tokens: int) -> LlamaCudaGeneration:
+    def generate_ids(self, prompt_ids, max_new_tokens: int, temperature: float | None = None,
+                     uniforms=None) -> LlamaCudaGeneration:
+        """LlamaMetalSession::generate_ids; ``uniforms`` ([max_new_tokens, vocab], row-major [step, vocabulary])
+        selects Gumbel-max sampling with ``temperature``, otherwise greedy."""
         p = np.ascontiguousarray(prompt_ids, dtype=np.int32)
         out = np.zeros(max(1, max_new_tokens), dtype=np.int32)
         n, stopped = C.c_size_t(0), C.c_int32(0)
-        check(self._L.rg_b200_generate_greedy(self._h, _i32(p), p.size, max_new_tokens, _i32(out), C.byref(n),
-                                              C.byref(stopped)))
+        if uniforms is None:
+            check(self._L.rg_b200_generate_greedy(self._h, _i32(p), p.size, max_new_tokens, _i32(out), C.byref(n),
+                                                  C.byref(stopped)))
+        else:
+            u = np.ascontiguousarray(uniforms, dtype=np.float32).reshape(max_new_tokens, self.vocab_size())
+            check(self._L.rg_b200_generate_sampled(self._h, _i32(p), p.size, max_new_tokens, float(temperature), _f32(u),
+                                                   _i32(out), C.byref(n), C.byref(stopped)))
         return LlamaCudaGeneration(p.tolist(), out[: n.value].tolist(), bool(stopped.value))
 
     def decode_loop(self, first_tokens, steps: int):
