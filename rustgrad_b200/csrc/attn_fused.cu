@@ -13,6 +13,7 @@
 // over the SMs.  Waits are bounded (status word).
 #include <cuda_fp16.h>
 #include <math.h>
+#include <stdlib.h>
 
 #include "../../include/rg_b200.h"
 #include "kernels.h"
@@ -316,7 +317,12 @@ cudaError_t launch_t(const FusedAttnArgs &a, const LaunchCfg &cfg) {
 }  // namespace
 
 int fused_attn_per_head(int sm_count, int kv_heads, int cols) {
-  const int n = sm_count / (kv_heads * (cols > 0 ? cols : 1));
+  static const int waves = [] {
+    const char *v = getenv("RG_B200_ATTN_WAVES");
+    const int w = v ? atoi(v) : 2;  // two spans per SM in flight: shorter spans, shorter dependent chains
+    return w >= 1 && w <= 3 ? w : 1;
+  }();
+  const int n = waves * sm_count / (kv_heads * (cols > 0 ? cols : 1));
   return n > 1 ? n : 1;
 }
 

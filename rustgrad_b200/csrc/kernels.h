@@ -80,6 +80,7 @@ struct QGemmArgs {
 };
 cudaError_t launch_qgemm_tc(const QGemmArgs &a, const LaunchCfg &cfg);
 int qgemm_effective_splits(int k, int splits);
+int qgemm_rows_per_cta(int mode);
 // out[r][i] = sum over s < splits of part[s * stride + r * n + i]
 cudaError_t launch_reduce_splits(const float *part, int splits, size_t stride, int n, int rows, float *out, int ldo,
                                  const LaunchCfg &cfg);

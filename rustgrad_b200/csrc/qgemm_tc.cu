@@ -4,7 +4,7 @@
 // (src/models/transformer/layer.rs:445-448, src/backend/cpu.rs:3484-3532 on the dequantised
 // weight of src/models/transformer/model.rs:982-995), with 16-bit operands and f32 accumulation.
 //
-// One CTA computes a [128 weight rows] x [TN tokens] tile over a K range:
+// One CTA computes RT tiles of [128 weight rows] x [TN tokens] (RT * 128 consecutive weight rows) over a K range:
 //   * MMA M = 128 weight rows (the dequantised tile is the A operand), MMA N = TN tokens (the
 //     activation tile is the B operand), K = 16 per tcgen05.mma, four per 64-element stage;
 //     the accumulator lives in TMEM (128 lanes x TN f32 columns).
@@ -42,8 +42,10 @@ constexpr int TM = 128;       // weight rows per tile (MMA M)
 constexpr int KSTEP = 64;     // elements per stage (128 bytes: one swizzle row)
 constexpr int RAW_STEPS = 4;  // 64-element stages per raw weight tile (256 columns = 8 blocks)
 constexpr int RAW_NS = 2;     // raw ring depth
-constexpr int DQ_GROUPS = 2;   // groups of eight dequantisation warps; group g expands the stages i = g (mod 2)
-constexpr int THREADS = 64 + DQ_GROUPS * 256;  // TMA warp, MMA warp, dequantisation / epilogue warps
+// RT = row tiles of 128 weight rows per CTA.  The compensated mode moves two activation planes per stage and is
+// bound by that traffic from L2, so there one activation tile feeds two row tiles (RT = 2, at most 128 tokens);
+// the single-operand modes are bound by the dequantisation and prefer one row tile against 256 tokens.
+constexpr int MAX_THREADS = 64 + 2 * 256;  // TMA warp, MMA warp, eight dequantisation / epilogue warps per row tile
 constexpr int A_COLS = KSTEP / 2;  // TMEM columns of one dequantised A stage (two 16-bit values per column)
 
 struct Params {
@@ -225,11 +227,12 @@ __device__ __forceinline__ void q8_block_split(uint32_t dbits16, const uint32_t 
 }
 
 // Ring depth of the activation tiles (shared memory) and of the dequantised A stages (tensor memory).
-__host__ __device__ constexpr int ring_depth(int tn, bool comp) { return (comp && tn > 128) ? 2 : 4; }
+__host__ __device__ constexpr int ring_depth(int tn, bool comp) { return comp ? (tn >= 64 ? 2 : 3) : 4; }  // tensor-memory budget
+__host__ __device__ constexpr int row_tiles(int mode) { return mode == QGEMM_F16X3 ? 2 : 1; }
 __host__ __device__ constexpr int pow2_cols(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
 
-template <int QT, int TN, int MODE>
-__global__ void __launch_bounds__(THREADS, 1)
+template <int QT, int TN, int MODE, int RT>
+__global__ void __launch_bounds__(MAX_THREADS, 1)
     qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap xlo_map,
                     const __grid_constant__ CUtensorMap wmap, const Params P) {
   constexpr bool Q4 = (QT == RG_TYPE_Q4_0);
@@ -239,36 +242,38 @@ __global__ void __launch_bounds__(THREADS, 1)
   constexpr int NS = ring_depth(TN, COMP);  // operand ring depth
   constexpr int B_BYTES = TN * KSTEP * 2;
   constexpr int B_STAGE = NPL * B_BYTES;
-  constexpr int A_STAGE_COLS = NPL * A_COLS;  // TMEM columns of one A stage (hi, lo)
+  constexpr int A_TILE_COLS = NPL * A_COLS;       // TMEM columns of one row tile's A stage (hi, lo)
+  constexpr int A_STAGE_COLS = RT * A_TILE_COLS;  // both row tiles
   constexpr int RAW_ROW = 8 * BB;  // bytes of one weight row in a raw tile (144 / 272)
   constexpr int RAW_BYTES = TM * RAW_ROW;
-  constexpr int ACC_COLS = TN < 32 ? 32 : TN;            // accumulator columns, then the A ring
+  constexpr int ACC_T = TN < 32 ? 32 : TN;  // accumulator columns of one row tile
+  constexpr int ACC_COLS = RT * ACC_T;      // accumulators first, then the A ring
   constexpr int TMEM_COLS = pow2_cols(ACC_COLS + NS * A_STAGE_COLS);
   static_assert(ACC_COLS + NS * A_STAGE_COLS <= 512, "tensor memory budget");
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t *b_ring = smem;
   uint8_t *raw_ring = b_ring + NS * B_STAGE;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(raw_ring + RAW_NS * RAW_BYTES);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(raw_ring + RAW_NS * RT * RAW_BYTES);
   uint64_t *b_full = bars, *a_full = bars + NS, *slot_free = bars + 2 * NS;
   uint64_t *raw_full = bars + 3 * NS, *raw_free = raw_full + RAW_NS, *acc_done = raw_free + RAW_NS;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_done + 1);
   volatile int *dead = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * TM, tok0 = blockIdx.y * TN;
+  const int n0 = blockIdx.x * (TM * RT), tok0 = blockIdx.y * TN;
   const int step0 = blockIdx.z * P.k_steps;
   const int nsteps = min(P.k_steps, P.k / KSTEP - step0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(&b_full[s], 1);
-      mbar_init(&a_full[s], 256);
+      mbar_init(&a_full[s], RT * 256);
       mbar_init(&slot_free[s], 1);
     }
     for (int s = 0; s < RAW_NS; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_free[s], DQ_GROUPS * 256);
+      mbar_init(&raw_free[s], RT * 256);
     }
     mbar_init(acc_done, 1);
     *dead = 0;
@@ -293,9 +298,12 @@ __global__ void __launch_bounds__(THREADS, 1)
         if (i % RAW_STEPS == 0) {
           const int j = i / RAW_STEPS, rs = j % RAW_NS;
           if (j >= RAW_NS) mbar_wait_bounded(&raw_free[rs], (uint32_t)((j / RAW_NS - 1) & 1), dead, P.status);
-          mbar_expect_tx(&raw_full[rs], (uint32_t)RAW_BYTES);
+          mbar_expect_tx(&raw_full[rs], (uint32_t)(RT * RAW_BYTES));
           // x in 8-byte elements; rows beyond the tensor arrive as zeros (zero scale, zero weights)
-          tma_tile_2d(raw_ring + rs * RAW_BYTES, &wmap, ((step0 + i) / RAW_STEPS) * (RAW_ROW / 8), n0, &raw_full[rs]);
+#pragma unroll
+          for (int t = 0; t < RT; ++t)
+            tma_tile_2d(raw_ring + (rs * RT + t) * RAW_BYTES, &wmap, ((step0 + i) / RAW_STEPS) * (RAW_ROW / 8), n0 + t * TM,
+                        &raw_full[rs]);
         }
         const int slot = i % NS;
         if (i >= NS) mbar_wait_bounded(&slot_free[slot], (uint32_t)((i / NS - 1) & 1), dead, P.status);
@@ -308,24 +316,32 @@ __global__ void __launch_bounds__(THREADS, 1)
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc(TM, TN, F16);
+      // one thread issues every MMA, so the loop is kept lean: a shared-memory descriptor is linear in the
+      // address (16-byte units), hence one base descriptor plus small constants per stage, K step and plane
+      const uint64_t b_desc0 = umma_desc(smem_u32(b_ring));
       for (int i = 0; i < nsteps; ++i) {
         const int slot = i % NS;
         const uint32_t ph = (uint32_t)((i / NS) & 1);
         mbar_wait_bounded(&a_full[slot], ph, dead, P.status);
         mbar_wait_bounded(&b_full[slot], ph, dead, P.status);
         tc_fence_after();
-        const uint32_t b_addr = smem_u32(b_ring + slot * B_STAGE);
+        const uint64_t b_desc = b_desc0 + (uint64_t)((slot * B_STAGE) >> 4);
         const uint32_t a_tm = tmem_base + (uint32_t)(ACC_COLS + slot * A_STAGE_COLS);  // lane 0, first column of the stage
+        const uint32_t first = i > 0 ? 1u : 0u;  // the very first MMA of a tile overwrites the accumulator
 #pragma unroll
         for (int kk = 0; kk < KSTEP / 16; ++kk) {
-          const uint32_t a_hi = a_tm + kk * 8;  // 16 K values = 8 columns
-          const uint64_t b_hi = umma_desc(b_addr + kk * 32);
-          if constexpr (COMP) {  // the small terms first, then hi.hi
-            umma_16bit_ta(tmem_base, a_hi, umma_desc(b_addr + B_BYTES + kk * 32), idesc, (i > 0 || kk > 0) ? 1u : 0u);
-            umma_16bit_ta(tmem_base, a_hi + A_COLS, b_hi, idesc, 1u);
-            umma_16bit_ta(tmem_base, a_hi, b_hi, idesc, 1u);
-          } else {
-            umma_16bit_ta(tmem_base, a_hi, b_hi, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          const uint64_t b_hi = b_desc + (uint64_t)(kk * 2);  // 32 bytes per K step
+#pragma unroll
+          for (int t = 0; t < RT; ++t) {
+            const uint32_t acc = tmem_base + t * ACC_T;
+            const uint32_t a_hi = a_tm + t * A_TILE_COLS + kk * 8;  // 16 K values = 8 columns
+            if constexpr (COMP) {  // the small terms first, then hi.hi
+              umma_16bit_ta(acc, a_hi, b_hi + (uint64_t)(B_BYTES >> 4), idesc, kk > 0 ? 1u : first);
+              umma_16bit_ta(acc, a_hi + A_COLS, b_hi, idesc, 1u);
+              umma_16bit_ta(acc, a_hi, b_hi, idesc, 1u);
+            } else {
+              umma_16bit_ta(acc, a_hi, b_hi, idesc, kk > 0 ? 1u : first);
+            }
           }
         }
         umma_commit(&slot_free[slot]);  // the slot may be rewritten once these MMAs have read it
@@ -338,16 +354,16 @@ __global__ void __launch_bounds__(THREADS, 1)
     // a warp may touch only the TMEM lanes 32 * (warp % 4) .. +31, so its lanes own exactly those weight rows
     const int r = (warp & 3) * 32 + lane;  // row of the tile
     const int half = ((warp - 2) >> 2) & 1;  // even / odd block of the stage
-    const int grp = (warp - 2) >> 3;         // which stages this warp expands: two groups overlap the latency of
-                                             // load -> expand -> tcgen05.st of consecutive stages
+    const int grp = (warp - 2) >> 3;         // row tile of this warp
     constexpr int QW = Q4 ? 4 : 8;             // quant words per block
-    for (int i = grp; i < nsteps; i += DQ_GROUPS) {
+    for (int i = 0; i < nsteps; ++i) {
       const int slot = i % NS;
       const int j = i / RAW_STEPS, rs = j % RAW_NS, sub = i % RAW_STEPS;
-      if (sub < DQ_GROUPS) mbar_wait_bounded(&raw_full[rs], (uint32_t)((j / RAW_NS) & 1), dead, P.status);
+      if (sub == 0) mbar_wait_bounded(&raw_full[rs], (uint32_t)((j / RAW_NS) & 1), dead, P.status);
       // pair layout: [d0 | q0] [d1 | q1] with a 2-byte scale in front of each block: the even block's
       // quants straddle word boundaries (funnel shift), the odd block's are word aligned
-      const uint32_t *src = reinterpret_cast<const uint32_t *>(raw_ring + rs * RAW_BYTES + r * RAW_ROW + sub * 2 * BB);
+      const uint32_t *src =
+          reinterpret_cast<const uint32_t *>(raw_ring + (rs * RT + grp) * RAW_BYTES + r * RAW_ROW + sub * 2 * BB);
       uint32_t q[QW], dbits, vals[16];  // 32 values of this block, in k order
       if (half == 0) {
         uint32_t raw[QW + 1];
@@ -373,11 +389,12 @@ __global__ void __launch_bounds__(THREADS, 1)
       } else {
         q8_block_to_16<F16>(dbits, q, vals);
       }
-      if (sub >= RAW_STEPS - DQ_GROUPS) mbar_arrive(&raw_free[rs]);  // this group's last stage of the raw tile is in registers
+      if (sub == RAW_STEPS - 1) mbar_arrive(&raw_free[rs]);  // the raw tile's last stage is in registers
       if (i >= NS) mbar_wait_bounded(&slot_free[slot], (uint32_t)((i / NS - 1) & 1), dead, P.status);
       tc_fence_after();
       // this thread's block = 16 columns of its row's lane: [stage][plane][even block | odd block]
-      const uint32_t a_tm = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(ACC_COLS + slot * A_STAGE_COLS + half * 16);
+      const uint32_t a_tm = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) +
+                            (uint32_t)(ACC_COLS + slot * A_STAGE_COLS + grp * A_TILE_COLS + half * 16);
       tmem_store16(a_tm, vals);
       if constexpr (COMP) tmem_store16(a_tm + A_COLS, lows);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -388,14 +405,14 @@ __global__ void __launch_bounds__(THREADS, 1)
     mbar_wait_bounded(acc_done, 0, dead, P.status);
     tc_fence_after();
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 belong to this warp
-    const int orow = n0 + quarter * 32 + lane;
+    const int orow = n0 + grp * TM + quarter * 32 + lane;  // this warp's row tile
     float *out = P.out + (size_t)blockIdx.z * P.split_stride;
     if (nsteps > 0) {
 #pragma unroll 1
-      for (int c0 = ((warp - 2) >> 2) * 16; c0 < TN; c0 += 16 * 2 * DQ_GROUPS) {  // four warps share a lane quarter
+      for (int c0 = half * 16; c0 < TN; c0 += 32) {  // two warps share a lane quarter of a row tile
         if (tok0 + c0 >= P.m) break;
         uint32_t v[16];
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(grp * ACC_T + c0);
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
@@ -433,7 +450,7 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-template <int QT, int TN, int MODE>
+template <int QT, int TN, int MODE, int RT>
 cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
   EncodeFn fn = encode_fn();
   if (!fn) return cudaErrorNotSupported;
@@ -476,9 +493,9 @@ cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
   P.ldc = a.ldc;
   P.split_stride = a.split_stride;
   P.status = cfg.status;
-  constexpr size_t smem = 1024 + NS * NPL * (TN * KSTEP * 2) + RAW_NS * TM * RAW_ROW + (3 * NS + 2 * RAW_NS + 1) * 8 + 16;
+  constexpr size_t smem = 1024 + NS * NPL * (TN * KSTEP * 2) + RAW_NS * RT * TM * RAW_ROW + (3 * NS + 2 * RAW_NS + 1) * 8 + 16;
   static_assert(smem <= 227 * 1024, "tile configuration exceeds the shared memory of one SM");
-  auto kernel = qgemm_tc_kernel<QT, TN, MODE>;
+  auto kernel = qgemm_tc_kernel<QT, TN, MODE, RT>;
   static bool attr_done = false;  // per instantiation
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -486,8 +503,8 @@ cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
     attr_done = true;
   }
   cudaLaunchConfig_t lc{};
-  lc.gridDim = dim3((unsigned)((a.n + TM - 1) / TM), (unsigned)((a.m + TN - 1) / TN), (unsigned)splits);
-  lc.blockDim = dim3(THREADS);
+  lc.gridDim = dim3((unsigned)((a.n + TM * RT - 1) / (TM * RT)), (unsigned)((a.m + TN - 1) / TN), (unsigned)splits);
+  lc.blockDim = dim3(64 + RT * 256);
   lc.dynamicSmemBytes = smem;
   lc.stream = cfg.stream;
   cudaLaunchAttribute at[1];
@@ -500,13 +517,15 @@ cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
 
 template <int QT, int MODE>
 cudaError_t launch_n(const QGemmArgs &a, const LaunchCfg &cfg) {
-  if constexpr (MODE != QGEMM_F16X3) {  // the compensated mode keeps two planes per operand: 128 tokens at most
-    if (a.m > 128) return launch_t<QT, 256, MODE>(a, cfg);
+  constexpr int RT = row_tiles(MODE);
+  // accumulators (RT tiles of TN columns) and the A ring share the 512 columns of tensor memory
+  if constexpr (RT == 1) {
+    if (a.m > 128) return launch_t<QT, 256, MODE, RT>(a, cfg);
   }
-  if (a.m > 64) return launch_t<QT, 128, MODE>(a, cfg);
-  if (a.m > 32) return launch_t<QT, 64, MODE>(a, cfg);
-  if (a.m > 16) return launch_t<QT, 32, MODE>(a, cfg);
-  return launch_t<QT, 16, MODE>(a, cfg);
+  if (a.m > 64) return launch_t<QT, 128, MODE, RT>(a, cfg);
+  if (a.m > 32) return launch_t<QT, 64, MODE, RT>(a, cfg);
+  if (a.m > 16) return launch_t<QT, 32, MODE, RT>(a, cfg);
+  return launch_t<QT, 16, MODE, RT>(a, cfg);
 }
 template <int QT>
 cudaError_t launch_m(const QGemmArgs &a, const LaunchCfg &cfg) {
@@ -625,6 +644,9 @@ cudaError_t launch_reduce_splits(const float *part, int splits, size_t stride, i
   return launch_simple(reduce_splits_kernel, dim3((unsigned)((n + 255) / 256), (unsigned)rows), dim3(256), cfg, part, splits,
                        stride, n, out, ldo);
 }
+
+// Weight rows one CTA covers in this operand mode.
+int qgemm_rows_per_cta(int mode) { return TM * row_tiles(mode); }
 
 // Number of K splits a launch with these arguments will actually use (whole 256-column raw tiles each).
 int qgemm_effective_splits(int k, int splits) {

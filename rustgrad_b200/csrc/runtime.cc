@@ -637,7 +637,8 @@ static int32_t gemm_tc(rg_session *s, const DevTensor &w, int m, float *out, int
   prof_mark(s, PROF_GEMV);
   // Few tokens (decode batches of 9..32): one CTA per 128 weight rows would leave most SMs without
   // weights to stream, so K is split until about two CTAs per SM exist and the partial tiles are summed.
-  const int tiles = ((int)w.rows + 127) / 128;
+  const int rows_per_cta = qgemm_rows_per_cta(s->gemm_mode);
+  const int tiles = ((int)w.rows + rows_per_cta - 1) / rows_per_cta;  // CTAs along the weight rows
   int splits = (m <= BMAX && s->split_scratch) ? (2 * s->sm_count) / tiles : 1;
   splits = qgemm_effective_splits(a.k, splits);
   if (splits > 1) {
