@@ -346,6 +346,15 @@ def main():
                      "step_bytes_over_step_time_gbs": (gemv_bytes / (ms_per_step * 1e-3) / 1e9)},
         "profile_ms_per_step": {k: v["ms_per_step"] for k, v in prof.items()},
     }
+    if n > 1:
+        # tensor parallel: what the exchange of partial sums costs (the "other" family is the 160 exchanges plus
+        # embedding, selection and the logits all-gather) and what each GPU streams
+        line["tensor_parallel"] = {
+            "exchange": "peer-memory kernel" if r1.get("peer_reduce_launches", 0) > 0 else "nccl all-reduce + add",
+            "exchange_and_other_ms_per_step": prof["other"]["ms_per_step"],
+            "exchange_and_other_share": prof["other"]["ms_per_step"] / prof["total"]["ms_per_step"],
+            "per_gpu_projection_gbs": achieved,
+        }
     if n == 1 and not args.no_cpu_baseline:
         tok_s, t_token, sample = cpu_reference_arm(args, wl, threads)
         line["cpu_baseline"] = {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}

@@ -389,14 +389,29 @@ __global__ void argmax_kernel(const float *logits, int ld, int vocab, const floa
   float best = -INFINITY;
   int idx = 0x7fffffff;
   int bad = 0;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    float v = row[i];
+  auto consider = [&](float v, float u, int i) {
     if (!finite_f32(v)) bad = 1;
-    if (urow) v = __fsub_rn(__fdiv_rn(v, t), logf(-logf(fmaxf(urow[i], 1e-12f))));
+    if (urow) v = __fsub_rn(__fdiv_rn(v, t), logf(-logf(fmaxf(u, 1e-12f))));
     if (v > best || idx == 0x7fffffff) {
       best = v;
       idx = i;
     }
+  };
+  const bool vec = ((vocab | ld) & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0 &&
+                   (!uniforms || (reinterpret_cast<uintptr_t>(uniforms) & 15) == 0);
+  if (vec) {  // four logits per load, several loads in flight per thread; ids still ascend within a thread
+    const float4 *row4 = reinterpret_cast<const float4 *>(row);
+    const float4 *u4 = reinterpret_cast<const float4 *>(urow);
+    for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) {
+      const float4 v = row4[i];
+      const float4 u = urow ? u4[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      consider(v.x, u.x, 4 * i);
+      consider(v.y, u.y, 4 * i + 1);
+      consider(v.z, u.z, 4 * i + 2);
+      consider(v.w, u.w, 4 * i + 3);
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) consider(row[i], urow ? urow[i] : 0.0f, i);
   }
   __shared__ float sv[32];
   __shared__ int si[32], sb[32];
