@@ -48,7 +48,10 @@ typedef enum {
 } rg_status;
 
 /* GGML tensor types on this path (src/gguf/tensor.rs:33-59). */
-enum { RG_TYPE_F32 = 0, RG_TYPE_F16 = 1, RG_TYPE_Q4_0 = 2, RG_TYPE_Q8_0 = 8 };
+enum { RG_TYPE_F32 = 0, RG_TYPE_F16 = 1, RG_TYPE_Q4_0 = 2, RG_TYPE_Q8_0 = 8,
+       /* 256-element super-blocks (blocks.rs:1164-1187,1219-1240): decoded bit-exactly; projections in these
+        * types run a plain decode-and-multiply GEMV (correct, not yet tuned), one GPU only */
+       RG_TYPE_Q4_K = 12, RG_TYPE_Q6_K = 14 };
 
 /* Mirror of LlamaModelConfig (src/models/transformer/model.rs:109-121). */
 typedef struct {

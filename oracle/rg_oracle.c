@@ -85,6 +85,7 @@ int rgo_block_elements(int t) {
   switch (t) {
     case RGO_F32: case RGO_F16: return 1;
     case RGO_Q4_0: case RGO_Q8_0: return 32;
+    case RGO_Q4_K: case RGO_Q6_K: return 256;
     default: return 0;
   }
 }
@@ -94,6 +95,8 @@ int rgo_block_bytes(int t) {
     case RGO_F16: return 2;
     case RGO_Q4_0: return 18;
     case RGO_Q8_0: return 34;
+    case RGO_Q4_K: return 144;
+    case RGO_Q6_K: return 210;
     default: return 0;
   }
 }
@@ -127,6 +130,59 @@ int rgo_decode_q8_0_block(const uint8_t *block, float out[32]) {
   return all_finite32(out) ? RGO_OK : RGO_ERR_NON_FINITE;
 }
 
+/* src/gguf/quantization/blocks.rs:1511-1522: eight 6-bit (scale, min) pairs packed in 12 bytes. */
+static void unpack_k_scales_mins(const uint8_t *packed, uint8_t scales[8], uint8_t mins[8]) {
+  for (int lane = 0; lane < 4; ++lane) {
+    scales[lane] = packed[lane] & 0x3f;
+    mins[lane] = packed[4 + lane] & 0x3f;
+    scales[4 + lane] = (uint8_t)((packed[8 + lane] & 0x0f) | ((packed[lane] >> 6) << 4));
+    mins[4 + lane] = (uint8_t)((packed[8 + lane] >> 4) | ((packed[4 + lane] >> 6) << 4));
+  }
+}
+
+/* src/gguf/quantization/blocks.rs:1164-1187: d, dmin (f16), 12 bytes of scales / mins, eight groups
+ * of 32 four-bit values; value = d * f32(scale) * f32(q) - dmin * f32(min), each step rounded to f32. */
+int rgo_decode_q4_k_block(const uint8_t *block, float out[256]) {
+  float d = half_le(block), dmin = half_le(block + 2);
+  if (!isfinite(d) || !isfinite(dmin)) return RGO_ERR_NON_FINITE;
+  uint8_t scales[8], mins[8];
+  unpack_k_scales_mins(block + 4, scales, mins);
+  const uint8_t *quants = block + 16;
+  for (int group = 0; group < 8; ++group) {
+    int source_group = group / 2, shift = (group % 2) * 4;
+    for (int lane = 0; lane < 32; ++lane) {
+      uint8_t q = (uint8_t)((quants[source_group * 32 + lane] >> shift) & 0x0f);
+      float a = d * (float)scales[group];
+      a = a * (float)q;
+      float b = dmin * (float)mins[group];
+      out[group * 32 + lane] = a - b;
+    }
+  }
+  for (int i = 0; i < 256; ++i)
+    if (!isfinite(out[i])) return RGO_ERR_NON_FINITE;
+  return RGO_OK;
+}
+
+/* src/gguf/quantization/blocks.rs:1219-1240: 128 bytes of low nibbles, 64 bytes of 2-bit highs, 16
+ * signed scales, trailing f16 d; value = d * f32((q - 32) * scale). */
+int rgo_decode_q6_k_block(const uint8_t *block, float out[256]) {
+  float d = half_le(block + 208);
+  if (!isfinite(d)) return RGO_ERR_NON_FINITE;
+  for (int index = 0; index < 256; ++index) {
+    int half_index = index / 128, within_half = index % 128;
+    int low_shift = (within_half / 64) * 4;
+    int low = (block[half_index * 64 + within_half % 64] >> low_shift) & 0x0f;
+    int high_shift = (within_half / 32) * 2;
+    int high = ((block[128 + half_index * 32 + within_half % 32] >> high_shift) & 0x03) << 4;
+    int quant = (low | high) - 32;
+    int scale = (int)(int8_t)block[192 + index / 16];
+    out[index] = d * (float)(quant * scale);
+  }
+  for (int i = 0; i < 256; ++i)
+    if (!isfinite(out[i])) return RGO_ERR_NON_FINITE;
+  return RGO_OK;
+}
+
 /* Decodes `count` consecutive elements starting at element `first` (both multiples of the block
  * size for packed types).  src/gguf/quantization/data.rs:415-428. */
 static int decode_span(int t, const uint8_t *bytes, size_t first, size_t count, float *out) {
@@ -145,6 +201,18 @@ static int decode_span(int t, const uint8_t *bytes, size_t first, size_t count, 
       for (size_t b = 0; b < count / 32; ++b) {
         int rc = (t == RGO_Q4_0) ? rgo_decode_q4_0_block(p + b * bb, out + b * 32)
                                  : rgo_decode_q8_0_block(p + b * bb, out + b * 32);
+        if (rc) return rc;
+      }
+      return RGO_OK;
+    }
+    case RGO_Q4_K:
+    case RGO_Q6_K: {
+      if (first % 256 || count % 256) return RGO_ERR_ARG;
+      size_t bb = (size_t)rgo_block_bytes(t);
+      const uint8_t *p = bytes + (first / 256) * bb;
+      for (size_t b = 0; b < count / 256; ++b) {
+        int rc = (t == RGO_Q4_K) ? rgo_decode_q4_k_block(p + b * bb, out + b * 256)
+                                 : rgo_decode_q6_k_block(p + b * bb, out + b * 256);
         if (rc) return rc;
       }
       return RGO_OK;
@@ -378,7 +446,7 @@ static float dot_fast(const float *x, const float *w, size_t k) {
  * the reference uses for a packed logits head only (model.rs:1036-1064, matmul/quantized.rs:157-177). */
 static int linear(const rgo_tensor *w, const float *x, int S, float *y, int mode, int threads, int head_f64) {
   size_t N = w->rows, K = w->cols;
-  int packed = (w->type == RGO_Q4_0 || w->type == RGO_Q8_0);
+  int packed = (w->type == RGO_Q4_0 || w->type == RGO_Q8_0 || w->type == RGO_Q4_K || w->type == RGO_Q6_K);
   int failed = 0;
 #pragma omp parallel num_threads(threads) if (mode == RGO_MODE_FAST && threads > 1)
   {

@@ -24,7 +24,7 @@ extern "C" {
 #endif
 
 /* GGML tensor type ids accepted on this path (src/gguf/tensor.rs:33-59). */
-enum { RGO_F32 = 0, RGO_F16 = 1, RGO_Q4_0 = 2, RGO_Q8_0 = 8 };
+enum { RGO_F32 = 0, RGO_F16 = 1, RGO_Q4_0 = 2, RGO_Q8_0 = 8, RGO_Q4_K = 12, RGO_Q6_K = 14 };
 
 /* Status codes. */
 enum {
@@ -115,6 +115,8 @@ int rgo_forward(const rgo_model *model, rgo_cache *cache, const int32_t *tokens,
 
 /* src/models/transformer/generation.rs:260-287: strict '>' so the lowest id wins ties; any
  * non-finite logit is an error. */
+int rgo_decode_q4_k_block(const uint8_t *block, float out[256]);
+int rgo_decode_q6_k_block(const uint8_t *block, float out[256]);
 int rgo_select_greedy(const float *row, int vocab, int32_t *token);
 int rgo_select_gumbel(const float *row, int vocab, float temperature, const float *uniforms, int32_t *token);
 

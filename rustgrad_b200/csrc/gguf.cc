@@ -14,6 +14,8 @@ int block_elements(int32_t t) {
     case RG_TYPE_F16: return 1;
     case RG_TYPE_Q4_0:
     case RG_TYPE_Q8_0: return 32;
+    case RG_TYPE_Q4_K:
+    case RG_TYPE_Q6_K: return 256;
     default: return 0;
   }
 }
@@ -23,6 +25,8 @@ int block_bytes(int32_t t) {
     case RG_TYPE_F16: return 2;
     case RG_TYPE_Q4_0: return 18;
     case RG_TYPE_Q8_0: return 34;
+    case RG_TYPE_Q4_K: return 144;
+    case RG_TYPE_Q6_K: return 210;
     default: return 0;
   }
 }

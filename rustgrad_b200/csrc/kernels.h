@@ -166,7 +166,7 @@ cudaError_t launch_tp_allreduce_add(const TpFusedArgs &a, const LaunchCfg &cfg);
 // Dense (F32/F16) weight GEMV for tensors the block formats cannot hold (K % 32 != 0) or that a
 // file stores dense.  x is plain f32 [batch, ldx]; same epilogues (EPI_SWIGLU unsupported).
 struct DenseGemvArgs {
-  int type = 0;  // RG_TYPE_F32 or RG_TYPE_F16
+  int type = 0;  // RG_TYPE_F32, RG_TYPE_F16, or a block type without a tuned kernel (RG_TYPE_Q4_K, RG_TYPE_Q6_K)
   const uint8_t *w = nullptr;
   int rows = 0, k = 0;
   const float *x = nullptr;

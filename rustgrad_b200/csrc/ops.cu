@@ -45,6 +45,38 @@ __device__ __forceinline__ float decode_element(int type, const uint8_t *bytes, 
     if (bad && !finite_f32(d)) *bad = true;
     return __fmul_rn(__fsub_rn((float)nib, 8.0f), d);
   }
+  if (type == RG_TYPE_Q4_K) {
+    // blocks.rs:1164-1187: value = d * f32(scale) * f32(q) - dmin * f32(min), each step rounded to f32;
+    // the 6-bit scales and mins of the eight 32-element groups are packed as in blocks.rs:1511-1522
+    const uint8_t *b = bytes + (e >> 8) * 144;
+    const int idx = (int)(e & 255), group = idx >> 5, gl = idx & 31;
+    const float d = half_bits_to_float((uint32_t)b[0] | ((uint32_t)b[1] << 8));
+    const float dmin = half_bits_to_float((uint32_t)b[2] | ((uint32_t)b[3] << 8));
+    if (bad && (!finite_f32(d) || !finite_f32(dmin))) *bad = true;
+    const uint8_t *p = b + 4;
+    int sc, mn;
+    if (group < 4) {
+      sc = p[group] & 0x3f;
+      mn = p[4 + group] & 0x3f;
+    } else {
+      sc = (p[4 + group] & 0x0f) | ((p[group - 4] >> 6) << 4);
+      mn = (p[4 + group] >> 4) | ((p[group] >> 6) << 4);
+    }
+    const int q = (b[16 + (group >> 1) * 32 + gl] >> ((group & 1) * 4)) & 0x0f;
+    return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dmin, (float)mn));
+  }
+  if (type == RG_TYPE_Q6_K) {
+    // blocks.rs:1219-1240: value = d * f32((q - 32) * scale)
+    const uint8_t *b = bytes + (e >> 8) * 210;
+    const int idx = (int)(e & 255), half_index = idx >> 7, within = idx & 127;
+    const float d = half_bits_to_float((uint32_t)b[208] | ((uint32_t)b[209] << 8));
+    if (bad && !finite_f32(d)) *bad = true;
+    const int low = (b[half_index * 64 + (within & 63)] >> ((within >> 6) * 4)) & 0x0f;
+    const int high = ((b[128 + half_index * 32 + (within & 31)] >> ((within >> 5) * 2)) & 0x03) << 4;
+    const int quant = (low | high) - 32;
+    const int scale = (int)(int8_t)b[192 + (idx >> 4)];
+    return __fmul_rn(d, (float)(quant * scale));
+  }
   const uint8_t *b = bytes + blk * 34;
   const float d = half_bits_to_float((uint32_t)b[0] | ((uint32_t)b[1] << 8));
   if (bad && !finite_f32(d)) *bad = true;
@@ -503,6 +535,36 @@ __global__ void dense_gemv_kernel(const W *w, int rows, int k, const float *x, i
   }
 }
 
+// Decode-and-multiply GEMV for block types without a tuned kernel (the K-quants): one warp per weight
+// row, every lane decodes its elements with decode_element.  Correct and simple; not a roofline kernel.
+__global__ void block_gemv_kernel(int type, const uint8_t *w, int rows, int k, const float *x, int ldx, int batch, int epi,
+                                  float *y, int ldy) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= rows) return;
+  const size_t base = (size_t)row * (size_t)k;
+  float acc[8];
+#pragma unroll
+  for (int b = 0; b < 8; ++b) acc[b] = 0.0f;
+  for (int i = lane; i < k; i += 32) {
+    const float wv = decode_element(type, w, base + (size_t)i, nullptr);
+#pragma unroll
+    for (int b = 0; b < 8; ++b)
+      if (b < batch) acc[b] = fmaf(x[(size_t)b * ldx + i], wv, acc[b]);
+  }
+#pragma unroll
+  for (int b = 0; b < 8; ++b) {
+    if (b >= batch) break;
+    const float v = warp_sum(acc[b]);
+    if (lane == 0) {
+      float *dst = y + (size_t)b * ldy + row;
+      *dst = (epi == EPI_RESIDUAL) ? __fadd_rn(*dst, v) : v;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------ synthetic tensors
 __device__ __forceinline__ uint64_t splitmix64(uint64_t z) {
   z += 0x9E3779B97F4A7C15ull;
@@ -712,6 +774,8 @@ cudaError_t launch_dense_gemv(const DenseGemvArgs &a, const LaunchCfg &cfg) {
   if (a.type == RG_TYPE_F16)
     return launch(dense_gemv_kernel<__half>, grid, block, 0, cfg, reinterpret_cast<const __half *>(a.w), a.rows, a.k, a.x, a.ldx,
                   a.batch, a.epi, a.y, a.ldy);
+  if (a.type == RG_TYPE_Q4_K || a.type == RG_TYPE_Q6_K)
+    return launch(block_gemv_kernel, grid, block, 0, cfg, a.type, a.w, a.rows, a.k, a.x, a.ldx, a.batch, a.epi, a.y, a.ldy);
   return cudaErrorInvalidValue;
 }
 cudaError_t launch_synth(int type, uint8_t *out, uint64_t seed, float std, uint64_t full_cols, uint64_t row0, uint64_t rows,

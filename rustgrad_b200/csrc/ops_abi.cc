@@ -76,6 +76,16 @@ int32_t check_weight(int32_t type, uint64_t n, uint64_t k, size_t *nbytes) {
 }
 
 int32_t scan_scales(int32_t type, const uint8_t *bytes, size_t nbytes) {
+  if (type == RG_TYPE_Q4_K || type == RG_TYPE_Q6_K) {  // d (and dmin) of every super-block must be finite
+    const size_t kb = (size_t)block_bytes(type);
+    for (size_t b = 0; b < nbytes / kb; ++b) {
+      const uint8_t *blk = bytes + b * kb;
+      const bool bad = type == RG_TYPE_Q4_K ? (((blk[1] >> 2) & 0x1f) == 0x1f || ((blk[3] >> 2) & 0x1f) == 0x1f)
+                                            : (((blk[209] >> 2) & 0x1f) == 0x1f);
+      if (bad) return fail(RG_NON_FINITE_SCALE, "block " + std::to_string(b));
+    }
+    return RG_OK;
+  }
   if (type != RG_TYPE_Q4_0 && type != RG_TYPE_Q8_0) return RG_OK;
   const size_t bb = (size_t)block_bytes(type);
   for (size_t b = 0; b < nbytes / bb; ++b)

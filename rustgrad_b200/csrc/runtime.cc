@@ -192,6 +192,8 @@ static int32_t check_tensor(rg_plan *p, const std::string &name, int32_t type, u
     return fail(RG_SHAPE_MISMATCH, name + ": expected [" + std::to_string(slot->rows) + "," + std::to_string(slot->cols) +
                                        "], got [" + std::to_string(rows) + "," + std::to_string(cols) + "]");
   if (cols % (uint64_t)block_elements(type)) return fail(RG_SHAPE_MISMATCH, name + ": columns are not a multiple of the block size");
+  if ((type == RG_TYPE_Q4_K || type == RG_TYPE_Q6_K) && p->tp_world > 1)
+    return fail(RG_UNSUPPORTED_GEOMETRY, name + ": K-quant tensors are not sharded (single GPU only)");
   if (slot->t && slot->t->type >= 0) return fail(RG_INVALID_ARGUMENT, name + ": tensor bound twice");
   const uint64_t W = (uint64_t)p->tp_world, R = (uint64_t)p->tp_rank;
   *r0 = 0, *lr = rows, *c0 = 0, *lc = cols;
@@ -1349,6 +1351,15 @@ int32_t rg_b200_plan_add_tensor(rg_plan *p, const char *name, int32_t type, uint
     for (uint64_t b = 0; b < blocks; ++b) {
       const uint8_t *blk = bytes + b * bb;
       if (((blk[1] >> 2) & 0x1f) == 0x1f) return fail(RG_NON_FINITE_SCALE, std::string(name) + ": block " + std::to_string(b));
+    }
+  }
+  if (type == RG_TYPE_Q4_K || type == RG_TYPE_Q6_K) {
+    const uint64_t blocks = rows * cols / 256;
+    for (uint64_t b = 0; b < blocks; ++b) {
+      const uint8_t *blk = bytes + b * bb;
+      const bool bad = type == RG_TYPE_Q4_K ? (((blk[1] >> 2) & 0x1f) == 0x1f || ((blk[3] >> 2) & 0x1f) == 0x1f)
+                                            : (((blk[209] >> 2) & 0x1f) == 0x1f);
+      if (bad) return fail(RG_NON_FINITE_SCALE, std::string(name) + ": block " + std::to_string(b));
     }
   }
   if (slot.ignored) return RG_OK;

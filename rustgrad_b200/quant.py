@@ -15,9 +15,27 @@ from __future__ import annotations
 
 import numpy as np
 
-F32, F16, Q4_0, Q8_0 = 0, 1, 2, 8
-BLOCK_BYTES = {F32: 4, F16: 2, Q4_0: 18, Q8_0: 34}
-BLOCK_ELEMS = {F32: 1, F16: 1, Q4_0: 32, Q8_0: 32}
+F32, F16, Q4_0, Q8_0, Q4_K, Q6_K = 0, 1, 2, 8, 12, 14
+BLOCK_BYTES = {F32: 4, F16: 2, Q4_0: 18, Q8_0: 34, Q4_K: 144, Q6_K: 210}
+BLOCK_ELEMS = {F32: 1, F16: 1, Q4_0: 32, Q8_0: 32, Q4_K: 256, Q6_K: 256}
+
+
+def random_k_blocks(ggml_type: int, n_blocks: int, rng, scale: float = 0.02) -> np.ndarray:
+    """Valid Q4_K / Q6_K super-blocks with random contents and small finite f16 scales.  There is no
+    K-quant encoder here (the reference has none either): tests decode these bytes on both sides."""
+    bb = BLOCK_BYTES[ggml_type]
+    blocks = rng.integers(0, 256, (n_blocks, bb), dtype=np.uint8)
+    if ggml_type == Q4_K:
+        d = (rng.random(n_blocks) * scale / 63.0 / 8.0 + 1e-5).astype(np.float16)
+        dmin = (rng.random(n_blocks) * scale / 63.0 / 2.0).astype(np.float16)
+        blocks[:, 0:2] = d.view(np.uint8).reshape(n_blocks, 2)
+        blocks[:, 2:4] = dmin.view(np.uint8).reshape(n_blocks, 2)
+    elif ggml_type == Q6_K:
+        d = (rng.random(n_blocks) * scale / 32.0 / 64.0 + 1e-6).astype(np.float16)
+        blocks[:, 208:210] = d.view(np.uint8).reshape(n_blocks, 2)
+    else:
+        raise ValueError("not a K-quant type")
+    return blocks.reshape(-1)
 
 
 def tensor_nbytes(ggml_type: int, elements: int) -> int:

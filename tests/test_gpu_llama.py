@@ -283,7 +283,7 @@ def test_binding_rejections_precede_device_work(tiny):
     with pytest.raises(E.UnsupportedType):
         plan_with(lambda t: t.update({"output_norm.weight": (quant.Q8_0, 1, 256, np.zeros(272, np.uint8))}))
     with pytest.raises(E.UnsupportedType):
-        plan_with(lambda t: t.update({"blk.1.ffn_up.weight": (12, 688, 256, np.zeros(688 * 144, np.uint8))}))
+        plan_with(lambda t: t.update({"blk.1.ffn_up.weight": (13, 688, 256, np.zeros(688 * 176, np.uint8))}))  # Q5_K
 
     def poison(t):
         kind, rows, cols, data = t["blk.1.ffn_gate.weight"]

@@ -128,7 +128,7 @@ def test_qmatmul_rejects_unsupported_geometry_and_types():
         session.qmatmul(quant.Q4_0, w, 1, 96, np.ones((1, 96), np.float32))
     assert e.value.status == 20
     with pytest.raises(session.RgError) as e:
-        session.qmatmul(12, w, 1, 256, np.ones((1, 256), np.float32))  # Q4_K is outside this path
+        session.qmatmul(13, w, 1, 256, np.ones((1, 256), np.float32))  # Q5_K is outside this path
     assert e.value.status == 2
     with pytest.raises(session.RgError) as e:
         session.qmatmul(quant.Q4_0, w, 1, 40, np.ones((1, 40), np.float32))

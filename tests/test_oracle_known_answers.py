@@ -52,13 +52,15 @@ def test_rank_two_packed_weight_decodes_rowwise():
 
 
 def test_geometry_table():
-    # src/gguf/tests.rs:872-876: (raw id, block elements, block bytes)
+    # src/gguf/tests.rs:872-879: (raw id, block elements, block bytes)
     L = O.lib()
     assert (L.rgo_block_elements(2), L.rgo_block_bytes(2)) == (32, 18)
     assert (L.rgo_block_elements(8), L.rgo_block_bytes(8)) == (32, 34)
     assert (L.rgo_block_elements(0), L.rgo_block_bytes(0)) == (1, 4)
     assert (L.rgo_block_elements(1), L.rgo_block_bytes(1)) == (1, 2)
-    assert L.rgo_block_elements(12) == 0  # K-quants are outside this path
+    assert (L.rgo_block_elements(12), L.rgo_block_bytes(12)) == (256, 144)
+    assert (L.rgo_block_elements(14), L.rgo_block_bytes(14)) == (256, 210)
+    assert L.rgo_block_elements(13) == 0  # Q5_K is outside this path
 
 
 @pytest.mark.parametrize("kind,block", [(O.Q4_0, q4_0_block(0x3C00, 3, 14)), (O.Q8_0, q8_0_block(0x3800))])
