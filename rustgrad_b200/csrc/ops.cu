@@ -535,8 +535,92 @@ __global__ void dense_gemv_kernel(const W *w, int rows, int k, const float *x, i
   }
 }
 
-// Decode-and-multiply GEMV for block types without a tuned kernel (the K-quants): one warp per weight
-// row, every lane decodes its elements with decode_element.  Correct and simple; not a roofline kernel.
+// K-quant GEMV: one warp per weight row, one 256-element super-block per warp iteration, eight
+// consecutive elements per lane (so a lane decodes its group's 6-bit scale / min or its int8 scale once and
+// reads its quants as whole bytes).  The decoded values are those of decode_element (same f32 steps).
+template <int TYPE>
+__global__ void kquant_gemv_kernel(const uint8_t *w, int rows, int k, const float *x, int ldx, int batch, int epi, float *y,
+                                   int ldy) {
+  pdl_wait();
+  pdl_launch_dependents();
+  constexpr int BB = TYPE == RG_TYPE_Q4_K ? 144 : 210;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= rows) return;
+  const int nsb = k >> 8;
+  const uint8_t *wr = w + (size_t)row * (size_t)nsb * BB;
+  float acc[8];
+#pragma unroll
+  for (int b = 0; b < 8; ++b) acc[b] = 0.0f;
+  for (int sb = 0; sb < nsb; ++sb) {  // (unrolling by four was measured slower: register pressure)
+    const uint8_t *blk = wr + (size_t)sb * BB;
+    float wv[8];
+    if constexpr (TYPE == RG_TYPE_Q4_K) {
+      const int group = lane >> 2;
+      const float d = half_bits_to_float((uint32_t)blk[0] | ((uint32_t)blk[1] << 8));
+      const float dmin = half_bits_to_float((uint32_t)blk[2] | ((uint32_t)blk[3] << 8));
+      const uint8_t *p = blk + 4;
+      int sc, mn;
+      if (group < 4) {
+        sc = p[group] & 0x3f;
+        mn = p[4 + group] & 0x3f;
+      } else {
+        sc = (p[4 + group] & 0x0f) | ((p[group - 4] >> 6) << 4);
+        mn = (p[4 + group] >> 4) | ((p[group] >> 6) << 4);
+      }
+      const float ds = __fmul_rn(d, (float)sc), off = __fmul_rn(dmin, (float)mn);
+      const uint2 q8 = *reinterpret_cast<const uint2 *>(blk + 16 + (group >> 1) * 32 + (lane & 3) * 8);  // 8-byte aligned
+      const int shift = (group & 1) * 4;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t word = j < 4 ? q8.x : q8.y;
+        const int q = (int)((word >> ((j & 3) * 8 + shift)) & 0x0f);
+        wv[j] = __fsub_rn(__fmul_rn(ds, (float)q), off);
+      }
+    } else {
+      const int half_index = lane >> 4, l16 = lane & 15;
+      const float d = half_bits_to_float((uint32_t)blk[208] | ((uint32_t)blk[209] << 8));
+      const uint8_t *lo = blk + half_index * 64 + (l16 & 7) * 8;
+      const uint8_t *hi = blk + 128 + half_index * 32 + (l16 & 3) * 8;
+      const int low_shift = (l16 >> 3) * 4, high_shift = (l16 >> 2) * 2;
+      const int scale = (int)(int8_t)blk[192 + (lane >> 1)];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int quant = (((lo[j] >> low_shift) & 0x0f) | (((hi[j] >> high_shift) & 0x03) << 4)) - 32;
+        wv[j] = __fmul_rn(d, (float)(quant * scale));
+      }
+    }
+    const int e0 = sb * 256 + lane * 8;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      if (b >= batch) break;
+      const float4 x0 = *reinterpret_cast<const float4 *>(x + (size_t)b * ldx + e0);
+      const float4 x1 = *reinterpret_cast<const float4 *>(x + (size_t)b * ldx + e0 + 4);
+      float a = acc[b];
+      a = fmaf(x0.x, wv[0], a);
+      a = fmaf(x0.y, wv[1], a);
+      a = fmaf(x0.z, wv[2], a);
+      a = fmaf(x0.w, wv[3], a);
+      a = fmaf(x1.x, wv[4], a);
+      a = fmaf(x1.y, wv[5], a);
+      a = fmaf(x1.z, wv[6], a);
+      a = fmaf(x1.w, wv[7], a);
+      acc[b] = a;
+    }
+  }
+#pragma unroll
+  for (int b = 0; b < 8; ++b) {
+    if (b >= batch) break;
+    const float v = warp_sum(acc[b]);
+    if (lane == 0) {
+      float *dst = y + (size_t)b * ldy + row;
+      *dst = (epi == EPI_RESIDUAL) ? __fadd_rn(*dst, v) : v;
+    }
+  }
+}
+
+// Decode-and-multiply GEMV for any block type, element by element (used when the activation rows are not
+// 16-byte aligned): one warp per weight row, every lane decodes its elements with decode_element.
 __global__ void block_gemv_kernel(int type, const uint8_t *w, int rows, int k, const float *x, int ldx, int batch, int epi,
                                   float *y, int ldy) {
   pdl_wait();
@@ -774,8 +858,16 @@ cudaError_t launch_dense_gemv(const DenseGemvArgs &a, const LaunchCfg &cfg) {
   if (a.type == RG_TYPE_F16)
     return launch(dense_gemv_kernel<__half>, grid, block, 0, cfg, reinterpret_cast<const __half *>(a.w), a.rows, a.k, a.x, a.ldx,
                   a.batch, a.epi, a.y, a.ldy);
-  if (a.type == RG_TYPE_Q4_K || a.type == RG_TYPE_Q6_K)
-    return launch(block_gemv_kernel, grid, block, 0, cfg, a.type, a.w, a.rows, a.k, a.x, a.ldx, a.batch, a.epi, a.y, a.ldy);
+  if (a.type == RG_TYPE_Q4_K || a.type == RG_TYPE_Q6_K) {
+    const bool aligned = (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (a.ldx & 3) == 0 && (a.k & 255) == 0 &&
+                         (a.type == RG_TYPE_Q6_K || (reinterpret_cast<uintptr_t>(a.w) & 7) == 0);
+    if (!aligned)
+      return launch(block_gemv_kernel, grid, block, 0, cfg, a.type, a.w, a.rows, a.k, a.x, a.ldx, a.batch, a.epi, a.y, a.ldy);
+    if (a.type == RG_TYPE_Q4_K)
+      return launch(kquant_gemv_kernel<RG_TYPE_Q4_K>, grid, block, 0, cfg, a.w, a.rows, a.k, a.x, a.ldx, a.batch, a.epi, a.y,
+                    a.ldy);
+    return launch(kquant_gemv_kernel<RG_TYPE_Q6_K>, grid, block, 0, cfg, a.w, a.rows, a.k, a.x, a.ldx, a.batch, a.epi, a.y, a.ldy);
+  }
   return cudaErrorInvalidValue;
 }
 cudaError_t launch_synth(int type, uint8_t *out, uint64_t seed, float std, uint64_t full_cols, uint64_t row0, uint64_t rows,
