@@ -681,6 +681,28 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
     if ((rc = gemm_tc(s, W.k, ncols, s->qkv + qw, qkv_w, L))) return rc;
     if ((rc = gemm_tc(s, W.v, ncols, s->qkv + qw + kw, qkv_w, L))) return rc;
     prof_mark(s, PROF_ATTN);
+    if (!s->chunk_is_prompt && ncols <= BMAX && s->attn_counters) {
+      // a decode batch: RoPE, cache append, split attention and the combine in one launch
+      FusedAttnArgs fa;
+      fa.qkv = s->qkv;
+      fa.cols = ncols;
+      fa.heads = s->heads_l;
+      fa.kv_heads = s->kv_l;
+      fa.hd = hd;
+      fa.ctx = s->ctx;
+      fa.col_seq = ctl->seq;
+      fa.col_pos = ctl->pos;
+      fa.cos_t = s->cos_t;
+      fa.sin_t = s->sin_t;
+      fa.k_cache = s->k_cache[(size_t)l];
+      fa.v_cache = s->v_cache[(size_t)l];
+      fa.kv_f32 = s->kv_f32;
+      fa.scratch = s->attn_scratch;
+      fa.max_splits = s->attn_max_splits;
+      fa.counters = s->attn_counters;
+      fa.out = s->attn_f32;
+      RG_LAUNCH(s, launch_attention_fused(fa, L));
+    } else {
     RopeArgs ra;
     ra.qkv = s->qkv;
     ra.cols = ncols;
@@ -729,6 +751,7 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
       aa.out_f32 = s->attn_f32;
       RG_LAUNCH(s, launch_attention(aa, L));
       if (s->family_mask & (1u << PROF_ATTN)) s->launches_in_step++;  // split + combine
+    }
     }
     RG_LAUNCH(s, launch_to16(s->attn_f32, qw, qw, ncols, xop, L));
     if ((rc = gemm_tc(s, W.o, ncols, s->tp_part[0], d, L))) return rc;
@@ -1556,9 +1579,9 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   if (fused_attention_supported(s->heads_l, s->kv_l, hd) && !env_flag("RG_B200_SPLIT_ATTENTION")) {
     s->attn_max_splits = fused_attn_max_splits(s->ctx, hd, s->kv_f32, s->sm_count, s->kv_l);
     if (s->attn_max_splits <= fused_attn_split_cap() &&
-        (size_t)2 * s->heads_l * s->attn_max_splits * (hd + 2) <= attn_scratch_floats(SCOLS, s->heads_l, hd, s->ctx)) {
-      RG_TRY(dalloc(s.get(), &s->attn_counters, (size_t)2 * s->kv_l));
-      RG_CUDA(cudaMemsetAsync(s->attn_counters, 0, sizeof(unsigned) * 2 * (size_t)s->kv_l, s->stream));
+        (size_t)BMAX * s->heads_l * s->attn_max_splits * (hd + 2) <= attn_scratch_floats(SCOLS, s->heads_l, hd, s->ctx)) {
+      RG_TRY(dalloc(s.get(), &s->attn_counters, (size_t)BMAX * s->kv_l));
+      RG_CUDA(cudaMemsetAsync(s->attn_counters, 0, sizeof(unsigned) * BMAX * (size_t)s->kv_l, s->stream));
     }
   }
   RG_TRY(dalloc(s.get(), &s->partial, (size_t)WMAX * d));
