@@ -75,6 +75,7 @@ __host__ __device__ constexpr int span_max(int hd, int kv_bytes) { return STAGE_
 __host__ __device__ inline int span_for(int total, int per_head, int smax) {
   int span = (((total + per_head - 1) / per_head) + 15) & ~15;
   if (span < 16) span = 16;
+  if (span < 64 && total > 64) span = 64;  // shorter spans only add partial results for the combine to gather
   return span > smax ? smax : span;
 }
 
