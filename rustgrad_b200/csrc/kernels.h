@@ -79,6 +79,9 @@ struct QGemmArgs {
   size_t split_stride = 0;
 };
 cudaError_t launch_qgemm_tc(const QGemmArgs &a, const LaunchCfg &cfg);
+// 128 x 512 tiles with the A operand in shared memory (qgemm_tc_wide.cu): single-operand modes, Q4_0, m > 256
+bool qgemm_tc_wide_applies(const QGemmArgs &a);
+cudaError_t launch_qgemm_tc_wide(const QGemmArgs &a, const LaunchCfg &cfg);
 int qgemm_effective_splits(int k, int splits);
 int qgemm_rows_per_cta(int mode);
 // out[r][i] = sum over s < splits of part[s * stride + r * n + i]

@@ -662,6 +662,7 @@ cudaError_t launch_qgemm_tc(const QGemmArgs &a, const LaunchCfg &cfg) {
     return cudaErrorInvalidValue;
   if (a.mode == QGEMM_F16X3 && (!a.x16_lo || (reinterpret_cast<uintptr_t>(a.x16_lo) & 15))) return cudaErrorInvalidValue;
   if (a.mode < QGEMM_BF16 || a.mode > QGEMM_F16X3) return cudaErrorInvalidValue;
+  if (qgemm_tc_wide_applies(a)) return launch_qgemm_tc_wide(a, cfg);  // more than 256 tokens, one operand plane
   if (a.type == RG_TYPE_Q4_0) return launch_m<RG_TYPE_Q4_0>(a, cfg);
   if (a.type == RG_TYPE_Q8_0) return launch_m<RG_TYPE_Q8_0>(a, cfg);
   return cudaErrorInvalidValue;
