@@ -5,16 +5,21 @@
 //
 // Why a second GEMV kernel: the f16-MMA kernel (qgemv.cu) is bound by the instructions that expand
 // nibbles to f16, not by HBM.  Here the weights never leave the integer domain:
-//  * Q8_0 quants are already the s8 A operand of mma.sync.m16n8k32; Q4_0 nibbles become
-//    s8 values 16*(n-8) with one shift and two logic ops per 8 weights (xor 8 turns offset binary
-//    into two's complement, kept in the high nibble of each byte).  The natural byte order of a
-//    Q4_0 word (low nibbles = elements 4t..4t+3, high nibbles = 16+4t..) is exactly the A fragment.
+//  * Q8_0 quants are already the s8 A operand of mma.sync.m16n8k32.  A Q4_0 word is used as it
+//    lies in memory: byte i of word t is n[4t+i] + 16 n[16+4t+i] (low nibble = element 4t+i, high
+//    nibble = element 16+4t+i), an unsigned A operand (u8 x s8 MMA).  For k < 16 the A bytes are the
+//    raw word and the activation operand holds 16 X[k]; for k >= 16 they are the word with the low
+//    nibbles masked off (16 n[k], one logic op per 8 weights) against X[k] - 16 X[k-16].  The cross
+//    terms cancel exactly: the integer sum is 16 * sum(n X).  The offset of the format,
+//    -8 * sum(X) per block, does not depend on the row: the prologue stores 128 * sum(X) split in
+//    two words and the main loop subtracts it from the folded digit sums.
 //  * The activation block (32 values) is converted once per CTA to 32-bit block fixed point,
-//    x = s_b * X with s_b a power of two and |X| < 2^30, and X is split into four signed base-256
+//    x = s_b * X with s_b a power of two and |X| < 2^30 (Q8_0) or 2^26 (Q4_0, which leaves room
+//    for the factor 16 and the difference above), and X is split into four signed base-256
 //    digits that sit in four B columns.  One MMA per (16 rows x 32 k) block gives four exact int32
 //    digit sums; (c0 + 256 c1) and (c2 + 256 c3) are converted to f32 and accumulated with the
-//    factor d * s_b.  Everything up to that conversion is exact, so the result carries the full
-//    f32 activation (relative 2^-30 of the block maximum) and f32 accumulation over blocks.
+//    factor d * s_b.  Everything up to that conversion is exact, so the result carries the f32
+//    activation to 2^-30 (Q4_0: 2^-26) of the block maximum and f32 accumulation over blocks.
 //  * The packed activations stay resident in shared memory for the whole kernel, produced by the
 //    CTA itself in the prologue from the previous kernel's f32 output, optionally through RMSNorm:
 //    no separate normalisation / packing kernel, no activation traffic per stage.
@@ -85,11 +90,6 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
   asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
   return v;
 }
-__device__ __forceinline__ float ldsf(uint32_t addr) {
-  float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
-  return v;
-}
 __device__ __forceinline__ void tma_box_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
@@ -98,21 +98,29 @@ __device__ __forceinline__ void tma_box_2d(void *smem_dst, const CUtensorMap *ma
       : "memory");
 }
 // D(16x8,s32) = A(16x32,s8,row) * B(32x8,s8,col)
-__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+// UA: the A bytes are unsigned (Q4_0 words), else signed (Q8_0 quants); B is always signed digits
+template <bool UA>
+__device__ __forceinline__ void mma_i8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   const int z = 0;
-  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
+  if constexpr (UA)
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
+  else
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
 }
-__device__ __forceinline__ void mma_s8_acc(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-// Q4_0 word -> s8 bytes 16*(n-8): low nibbles (elements 4t..) and high nibbles (elements 16+4t..)
-__device__ __forceinline__ void q4_to_s8(uint32_t q, uint32_t &lo, uint32_t &hi) {
-  lo = ((q << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
-  hi = (q & 0xF0F0F0F0u) ^ 0x80808080u;
+template <bool UA>
+__device__ __forceinline__ void mma_i8_acc(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  if constexpr (UA)
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  else
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // Row slot rs of a stage is shared row (rs >> 1) * 16 + (rs & 1) * 8 + g; `a` points at
@@ -161,8 +169,10 @@ __device__ __forceinline__ void load_slot_b1(uint32_t a, uint32_t s, uint32_t (&
 template <int QT>
 __device__ __forceinline__ void expand(const uint32_t (&w)[6], uint32_t (&ae)[2], uint32_t (&ao)[2]) {
   if constexpr (Geo<QT>::Q4) {
-    q4_to_s8(__funnelshift_r(w[0], w[1], 16), ae[0], ae[1]);
-    q4_to_s8(w[2], ao[0], ao[1]);
+    ae[0] = __funnelshift_r(w[0], w[1], 16);  // n[k] + 16 n[k+16], against 16 X[k]
+    ae[1] = ae[0] & 0xF0F0F0F0u;              // 16 n[k+16], against X[k+16] - 16 X[k]
+    ao[0] = w[2];
+    ao[1] = w[2] & 0xF0F0F0F0u;
   } else {
     ae[0] = __funnelshift_r(w[0], w[1], 16);
     ae[1] = __funnelshift_r(w[2], w[3], 16);
@@ -174,7 +184,8 @@ __device__ __forceinline__ void expand(const uint32_t (&w)[6], uint32_t (&ae)[2]
 // Shared layout of the resident activations: digits then block scales.
 //   digit byte of element e of block kb, column c (= 4*batch + digit):
 //     ((kb * S + c) * 4 + t) * 8 + r * 4 + i,  e < 16: t = e/4, r = 0;  e >= 16: t = (e-16)/4, r = 1;  i = e%4
-//   scale of (block kb, batch b): float at kb * B + b
+//   side words of (block kb, batch b), four 32-bit words at (kb * B + b) * 4:
+//     {scale, T_lo, scale, T_hi}; T = 128 * sum(X) = T_lo + 65536 T_hi is the Q4_0 offset term (0 for Q8_0)
 __device__ __forceinline__ uint32_t digit_offset(int S, int kb, int c, int e) {
   const int t = (e & 15) >> 2, r = e >> 4, i = e & 3;
   return (uint32_t)((((kb * S + c) * 4 + t) * 8) + r * 4 + i);
@@ -202,7 +213,7 @@ __global__ void __launch_bounds__(THREADS, 1)
   static_assert(RED_BYTES % 128 == 0, "alignment");
   const int S = 4 * P.batch;
   const int xs_bytes = (P.kb * S * 32 + 127) & ~127;
-  const int sb_bytes = (P.kb * P.batch * 4 + 127) & ~127;
+  const int sb_bytes = (P.kb * P.batch * 16 + 127) & ~127;
   uint8_t *xs = smem + 128 + RED_BYTES;
   float *sb = reinterpret_cast<float *>(xs + xs_bytes);
   uint8_t *stage0 = xs + xs_bytes + sb_bytes;
@@ -315,18 +326,35 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
       for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
       const uint32_t E = __float_as_uint(m) >> 23;  // biased exponent of the block maximum (m >= 0)
+      constexpr uint32_t XBITS = G::Q4 ? 25u : 29u;  // |X| < 2^(XBITS + 1)
       float s = 0.0f;
-      uint32_t Y[4] = {0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u};
+      int X[4] = {0, 0, 0, 0};
       if (E >= 40u && E < 255u) {
-        s = __uint_as_float((E - 29u) << 23);  // 2^(floor(log2 m) - 29), so |X| < 2^30
-        const float up = __uint_as_float((283u - E) << 23);
-        // X + 0x80808080 turns the four signed base-256 digits of X into unsigned bytes (digit + 128)
+        s = __uint_as_float((E - XBITS) << 23);  // 2^(floor(log2 m) - XBITS)
+        const float up = __uint_as_float((254u + XBITS - E) << 23);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) Y[i] = (uint32_t)__float2int_rn(v[i] * up) + 0x80808080u;
+        for (int i = 0; i < 4; ++i) X[i] = __float2int_rn(v[i] * up);
       } else if (E == 255u) {  // inf / NaN input must stay visible in the result
         s = __uint_as_float(0x7fc00000u);
-        Y[0] = 0x80808081u;
+        X[0] = 1;
       }
+      int t_lo = 0, t_hi = 0;
+      if constexpr (G::Q4) {
+        int sum = (X[0] + X[1]) + (X[2] + X[3]);  // |sum over the block| < 2^31
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        t_lo = (sum & 0x1FF) << 7;  // 128 * sum = t_lo + 65536 * t_hi
+        t_hi = sum >> 9;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int xp = __shfl_xor_sync(0xffffffffu, X[i], 4);  // element e - 16 for the upper half
+          X[i] = (quad < 4) ? (X[i] << 4) : (X[i] - (xp << 4));
+        }
+      }
+      // X + 0x80808080 turns the four signed base-256 digits of X into unsigned bytes (digit + 128)
+      uint32_t Y[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) Y[i] = (uint32_t)X[i] + 0x80808080u;
       // 4x4 byte transpose: word d = digit d of the lane's four elements, then back to signed
       const uint32_t t0 = prmt(Y[0], Y[1], 0x5140u), t1 = prmt(Y[2], Y[3], 0x5140u);
       const uint32_t t2 = prmt(Y[0], Y[1], 0x7362u), t3 = prmt(Y[2], Y[3], 0x7362u);
@@ -336,7 +364,9 @@ __global__ void __launch_bounds__(THREADS, 1)
       dst[1 * plane] = prmt(t0, t1, 0x7632u) ^ 0x80808080u;
       dst[2 * plane] = prmt(t2, t3, 0x5410u) ^ 0x80808080u;
       dst[3 * plane] = prmt(t2, t3, 0x7632u) ^ 0x80808080u;
-      if (quad == 0) sb[kb * P.batch + b] = s;
+      if (quad == 0)
+        *reinterpret_cast<float4 *>(sb + (kb * P.batch + b) * 4) =
+            make_float4(s, __int_as_float(t_lo), s, __int_as_float(t_hi));
     }
   }
   asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
@@ -356,7 +386,8 @@ __global__ void __launch_bounds__(THREADS, 1)
   // B1: lanes g >= 4 feed the odd block's digits (column g - 4 of the next block)
   const uint32_t xs_lane = B1 ? smem_u32(xs) + (uint32_t)(((g & 3) * 4 + t) * 8 + (g >> 2) * 128)
                               : smem_u32(xs) + (uint32_t)((g * 4 + t) * 8);
-  const uint32_t sb_lane = B1 ? smem_u32(sb) + (uint32_t)(blk_sel * 4) : smem_u32(sb) + (uint32_t)(my_batch * 4);
+  // this lane's accumulator columns are digits 0,1 (t even) or 2,3 (t odd): {scale, T_lo} or {scale, T_hi}
+  const uint32_t sb_lane = smem_u32(sb) + (uint32_t)((B1 ? blk_sel : my_batch) * 16 + (t & 1) * 8);
   const uint32_t lane_w_off = (uint32_t)(g * G::RS + t * 4);
   const uint32_t lane_s_off = B1 ? (uint32_t)(g * G::RS + blk_sel * G::BB) : (uint32_t)(g * G::RS);
   for (int u = 0; u < units; ++u) {
@@ -374,7 +405,9 @@ __global__ void __launch_bounds__(THREADS, 1)
         load_slot_b1<QT, 2>(aw, as, wq[2], sc[2]);
         load_slot_b1<QT, 3>(aw, as, wq[3], sc[3]);
         const uint2 xv = lds64(xs_lane + (uint32_t)(gb * 128));
-        const float sv = ldsf(sb_lane + (uint32_t)(gb * 4));
+        const uint2 side = lds64(sb_lane + (uint32_t)(gb * 16));
+        const float sv = __uint_as_float(side.x);
+        const int off = G::Q4 ? (int)side.y : 0;
         const bool ev = g < 4;
         const uint32_t b_lo0 = ev ? xv.x : 0u, b_lo1 = ev ? 0u : xv.x;  // MMA 1: low halves of both blocks
         const uint32_t b_hi0 = ev ? xv.y : 0u, b_hi1 = ev ? 0u : xv.y;  // MMA 2: high halves
@@ -384,9 +417,9 @@ __global__ void __launch_bounds__(THREADS, 1)
           expand<QT>(wq[mt * 2], ae[0], ao[0]);
           expand<QT>(wq[mt * 2 + 1], ae[1], ao[1]);
           int c[4];
-          mma_s8(c, ae[0][0], ae[1][0], ao[0][0], ao[1][0], b_lo0, b_lo1);
-          mma_s8_acc(c, ae[0][1], ae[1][1], ao[0][1], ao[1][1], b_hi0, b_hi1);
-          const float f0 = (float)(c[0] + (c[1] << 8)), f1 = (float)(c[2] + (c[3] << 8));
+          mma_i8<G::Q4>(c, ae[0][0], ae[1][0], ao[0][0], ao[1][0], b_lo0, b_lo1);
+          mma_i8_acc<G::Q4>(c, ae[0][1], ae[1][1], ao[0][1], ao[1][1], b_hi0, b_hi1);
+          const float f0 = (float)(c[0] + (c[1] << 8) - off), f1 = (float)(c[2] + (c[3] << 8) - off);
           acc[mt][0] = fmaf(half_bits_to_float(sc[mt * 2][0]) * sv, f0, acc[mt][0]);
           acc[mt][1] = fmaf(half_bits_to_float(sc[mt * 2 + 1][0]) * sv, f1, acc[mt][1]);
         }
@@ -402,9 +435,16 @@ __global__ void __launch_bounds__(THREADS, 1)
         xo = lds64(xs_lane + (uint32_t)((gb + 1) * S * 32));
       }
       float se = 0.0f, so = 0.0f;
+      int offe = 0, offo = 0;
       if (acc_live) {
-        se = ldsf(sb_lane + (uint32_t)(gb * P.batch * 4));
-        so = ldsf(sb_lane + (uint32_t)((gb + 1) * P.batch * 4));
+        const uint2 sde = lds64(sb_lane + (uint32_t)(gb * P.batch * 16));
+        const uint2 sdo = lds64(sb_lane + (uint32_t)((gb + 1) * P.batch * 16));
+        se = __uint_as_float(sde.x);
+        so = __uint_as_float(sdo.x);
+        if constexpr (G::Q4) {
+          offe = (int)sde.y;
+          offo = (int)sdo.y;
+        }
       }
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
@@ -412,11 +452,11 @@ __global__ void __launch_bounds__(THREADS, 1)
         expand<QT>(wq[mt * 2], ae[0], ao[0]);
         expand<QT>(wq[mt * 2 + 1], ae[1], ao[1]);
         int ce[4], co[4];
-        mma_s8(ce, ae[0][0], ae[1][0], ae[0][1], ae[1][1], xe.x, xe.y);
-        mma_s8(co, ao[0][0], ao[1][0], ao[0][1], ao[1][1], xo.x, xo.y);
+        mma_i8<G::Q4>(ce, ae[0][0], ae[1][0], ae[0][1], ae[1][1], xe.x, xe.y);
+        mma_i8<G::Q4>(co, ao[0][0], ao[1][0], ao[0][1], ao[1][1], xo.x, xo.y);
         // this lane's two columns are digit 2j and 2j+1 of one batch: fold them exactly
-        const float fe0 = (float)(ce[0] + (ce[1] << 8)), fe1 = (float)(ce[2] + (ce[3] << 8));
-        const float fo0 = (float)(co[0] + (co[1] << 8)), fo1 = (float)(co[2] + (co[3] << 8));
+        const float fe0 = (float)(ce[0] + (ce[1] << 8) - offe), fe1 = (float)(ce[2] + (ce[3] << 8) - offe);
+        const float fo0 = (float)(co[0] + (co[1] << 8) - offo), fo1 = (float)(co[2] + (co[3] << 8) - offo);
         acc[mt][0] = fmaf(half_bits_to_float(sc[mt * 2][0]) * se, fe0, acc[mt][0]);
         acc[mt][1] = fmaf(half_bits_to_float(sc[mt * 2 + 1][0]) * se, fe1, acc[mt][1]);
         acc[mt][0] = fmaf(half_bits_to_float(sc[mt * 2][1]) * so, fo0, acc[mt][0]);
@@ -437,7 +477,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         }
       asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
       const int vr0 = r_begin + grp * GROUP_ROWS;
-      constexpr float A_SCALE = G::Q4 ? 0.0625f : 1.0f;  // Q4_0 operands were 16 * (n - 8)
+      constexpr float A_SCALE = G::Q4 ? 0.0625f : 1.0f;  // the Q4_0 digit sums carry a factor 16
       for (int idx = ctid; idx < GROUP_ROWS * 2; idx += CW * 32) {
         const int row = idx >> 1, b = idx & 1;
         const int vrow = vr0 + row;
@@ -533,7 +573,7 @@ cudaError_t launch_t(const GemvI8Args &a, const LaunchCfg &cfg) {
   P.rows_per_cta = ((boxes + sms - 1) / sms) * BOXR;
   const int grid = (P.n_rows + P.rows_per_cta - 1) / P.rows_per_cta;
   const int S = 4 * a.batch;
-  const int fixed = 128 + CW * R * 4 * 4 + ((P.kb * S * 32 + 127) & ~127) + ((P.kb * a.batch * 4 + 127) & ~127);
+  const int fixed = 128 + CW * R * 4 * 4 + ((P.kb * S * 32 + 127) & ~127) + ((P.kb * a.batch * 16 + 127) & ~127);
   const int stage_bytes = R * G::RS;
   int stages = (SMEM_LIMIT - fixed) / stage_bytes;
   if (stages < 3) stages = (SMEM_FULL - fixed) / stage_bytes;  // too large to share an SM: take it whole
