@@ -281,92 +281,149 @@ __global__ void __launch_bounds__(THREADS, 1)
   }
 
   // -------------------------------------------------------------------- consumers
-  pdl_wait();
   const int ctid = threadIdx.x;  // 0 .. CW*32-1
+  const int quad = lane & 7;
+  // Eight lanes per block, four consecutive elements per lane (= one 32-bit word of each digit
+  // plane in the fragment layout); a warp converts four blocks per iteration.  The lane's float4
+  // index of block kb is kb * 8 + quad = ctid + iteration * CW * 32.
+  auto pack_block = [&](const float (&v)[4], int kb, int b) {
+    float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    if (!(fabsf(v[0] + v[1] + v[2] + v[3]) <= 3.0e38f)) m = __uint_as_float(0x7f800000u);  // fmaxf drops NaN: keep it visible
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const uint32_t E = __float_as_uint(m) >> 23;  // biased exponent of the block maximum (m >= 0)
+    constexpr uint32_t XBITS = G::Q4 ? 25u : 29u;  // |X| < 2^(XBITS + 1)
+    float s = 0.0f;
+    int X[4] = {0, 0, 0, 0};
+    if (E >= 40u && E < 255u) {
+      s = __uint_as_float((E - XBITS) << 23);  // 2^(floor(log2 m) - XBITS)
+      const float up = __uint_as_float((254u + XBITS - E) << 23);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) X[i] = __float2int_rn(v[i] * up);
+    } else if (E == 255u) {  // inf / NaN input must stay visible in the result
+      s = __uint_as_float(0x7fc00000u);
+      X[0] = 1;
+    }
+    int t_lo = 0, t_hi = 0;
+    if constexpr (G::Q4) {
+      int sum = (X[0] + X[1]) + (X[2] + X[3]);  // |sum over the block| < 2^31
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      t_lo = (sum & 0x1FF) << 7;  // 128 * sum = t_lo + 65536 * t_hi
+      t_hi = sum >> 9;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int xp = __shfl_xor_sync(0xffffffffu, X[i], 4);  // element e - 16 for the upper half
+        X[i] = (quad < 4) ? (X[i] << 4) : (X[i] - (xp << 4));
+      }
+    }
+    // X + 0x80808080 turns the four signed base-256 digits of X into unsigned bytes (digit + 128)
+    uint32_t Y[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) Y[i] = (uint32_t)X[i] + 0x80808080u;
+    // 4x4 byte transpose: word d = digit d of the lane's four elements, then back to signed
+    const uint32_t t0 = prmt(Y[0], Y[1], 0x5140u), t1 = prmt(Y[2], Y[3], 0x5140u);
+    const uint32_t t2 = prmt(Y[0], Y[1], 0x7362u), t3 = prmt(Y[2], Y[3], 0x7362u);
+    uint32_t *dst = reinterpret_cast<uint32_t *>(xs + digit_offset(S, kb, 4 * b, quad * 4));
+    const int plane = 32 / 4;  // words between consecutive columns of a block
+    dst[0 * plane] = prmt(t0, t1, 0x5410u) ^ 0x80808080u;
+    dst[1 * plane] = prmt(t0, t1, 0x7632u) ^ 0x80808080u;
+    dst[2 * plane] = prmt(t2, t3, 0x5410u) ^ 0x80808080u;
+    dst[3 * plane] = prmt(t2, t3, 0x7632u) ^ 0x80808080u;
+    if (quad == 0)
+      *reinterpret_cast<float4 *>(sb + (kb * P.batch + b) * 4) =
+          make_float4(s, __int_as_float(t_lo), s, __int_as_float(t_hi));
+  };
+  // y = (x * (1 / sqrt(mean(x^2) + eps))) * w, every step rounded to f32 (layer.rs:423-443)
+  auto inv_rms = [&](float ss) {
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < CW; ++w) tot += red[w];
+    const float mean = __fdiv_rn(tot, (float)(P.kb * 32));
+    const float inv = __frcp_rn(__fsqrt_rn(__fadd_rn(mean, P.eps)));
+    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+    return inv;
+  };
+
   // ---- prologue: (RMSNorm and) block fixed-point packing of the activations into shared memory
-  for (int b = 0; b < P.batch; ++b) {
-    const float *xr = P.x + (size_t)(P.col_map ? P.col_map[b] : b) * P.ldx;
+  constexpr int PRE = 5;  // register-resident form: up to PRE blocks per lane (K <= PRE * CW * 128)
+  const int kb0 = warp * 4 + (lane >> 3);
+  float resid0 = 0.0f;
+  if (B1 && P.kb <= PRE * CW * 4) {
+    // The norm weights are constant data: fetch them before the grid dependency resolves, then the
+    // activation once; both passes (sum of squares, packing) run from registers.
+    float4 wv[PRE], xv[PRE];
+    if (P.norm_w) {
+#pragma unroll
+      for (int it = 0; it < PRE; ++it)
+        if (kb0 + it * CW * 4 < P.kb) wv[it] = __ldg(reinterpret_cast<const float4 *>(P.norm_w) + ctid + it * CW * 32);
+    }
+    pdl_wait();
+    const float *xr = P.x + (size_t)(P.col_map ? P.col_map[0] : 0) * P.ldx;
+#pragma unroll
+    for (int it = 0; it < PRE; ++it)
+      if (kb0 + it * CW * 4 < P.kb) xv[it] = __ldg(reinterpret_cast<const float4 *>(xr) + ctid + it * CW * 32);
+    if (EPI == EPI_RESIDUAL && ctid < GROUP_ROWS * 2 && (ctid & 1) == 0 && r_begin + (ctid >> 1) < r_end)
+      resid0 = P.y[r_begin + (ctid >> 1)];  // the first row group's residual, off the epilogue's path
     float inv = 1.0f;
     if (P.norm_w) {
-      // y = (x * (1 / sqrt(mean(x^2) + eps))) * w, every step rounded to f32 (layer.rs:423-443)
       float ss = 0.0f;
-      for (int i = ctid; i < P.kb * 8; i += CW * 32) {
-        const float4 f = __ldg(reinterpret_cast<const float4 *>(xr) + i);
-        ss = fmaf(f.x, f.x, ss);
-        ss = fmaf(f.y, f.y, ss);
-        ss = fmaf(f.z, f.z, ss);
-        ss = fmaf(f.w, f.w, ss);
-      }
-      ss = warp_sum(ss);
-      if (lane == 0) red[warp] = ss;
-      asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
-      float tot = 0.0f;
 #pragma unroll
-      for (int w = 0; w < CW; ++w) tot += red[w];
-      const float mean = __fdiv_rn(tot, (float)(P.kb * 32));
-      inv = __frcp_rn(__fsqrt_rn(__fadd_rn(mean, P.eps)));
-      asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
-    }
-    // Eight lanes per block, four consecutive elements per lane (= one 32-bit word of each digit
-    // plane in the fragment layout); a warp converts four blocks per iteration.
-    const int quad = lane & 7;
-#pragma unroll 4
-    for (int kb = warp * 4 + (lane >> 3); kb < P.kb; kb += CW * 4) {
-      const float4 f = __ldg(reinterpret_cast<const float4 *>(xr + kb * 32) + quad);
-      float v[4] = {f.x, f.y, f.z, f.w};
-      if (P.norm_w) {
-        const float4 w = __ldg(reinterpret_cast<const float4 *>(P.norm_w + kb * 32) + quad);
-        v[0] = __fmul_rn(__fmul_rn(v[0], inv), w.x);
-        v[1] = __fmul_rn(__fmul_rn(v[1], inv), w.y);
-        v[2] = __fmul_rn(__fmul_rn(v[2], inv), w.z);
-        v[3] = __fmul_rn(__fmul_rn(v[3], inv), w.w);
-      }
-      float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-      if (!(fabsf(v[0] + v[1] + v[2] + v[3]) <= 3.0e38f)) m = __uint_as_float(0x7f800000u);  // fmaxf drops NaN: keep it visible
-#pragma unroll
-      for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-      const uint32_t E = __float_as_uint(m) >> 23;  // biased exponent of the block maximum (m >= 0)
-      constexpr uint32_t XBITS = G::Q4 ? 25u : 29u;  // |X| < 2^(XBITS + 1)
-      float s = 0.0f;
-      int X[4] = {0, 0, 0, 0};
-      if (E >= 40u && E < 255u) {
-        s = __uint_as_float((E - XBITS) << 23);  // 2^(floor(log2 m) - XBITS)
-        const float up = __uint_as_float((254u + XBITS - E) << 23);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) X[i] = __float2int_rn(v[i] * up);
-      } else if (E == 255u) {  // inf / NaN input must stay visible in the result
-        s = __uint_as_float(0x7fc00000u);
-        X[0] = 1;
-      }
-      int t_lo = 0, t_hi = 0;
-      if constexpr (G::Q4) {
-        int sum = (X[0] + X[1]) + (X[2] + X[3]);  // |sum over the block| < 2^31
-#pragma unroll
-        for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        t_lo = (sum & 0x1FF) << 7;  // 128 * sum = t_lo + 65536 * t_hi
-        t_hi = sum >> 9;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int xp = __shfl_xor_sync(0xffffffffu, X[i], 4);  // element e - 16 for the upper half
-          X[i] = (quad < 4) ? (X[i] << 4) : (X[i] - (xp << 4));
+      for (int it = 0; it < PRE; ++it)
+        if (kb0 + it * CW * 4 < P.kb) {
+          ss = fmaf(xv[it].x, xv[it].x, ss);
+          ss = fmaf(xv[it].y, xv[it].y, ss);
+          ss = fmaf(xv[it].z, xv[it].z, ss);
+          ss = fmaf(xv[it].w, xv[it].w, ss);
         }
-      }
-      // X + 0x80808080 turns the four signed base-256 digits of X into unsigned bytes (digit + 128)
-      uint32_t Y[4];
+      inv = inv_rms(ss);
+    }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) Y[i] = (uint32_t)X[i] + 0x80808080u;
-      // 4x4 byte transpose: word d = digit d of the lane's four elements, then back to signed
-      const uint32_t t0 = prmt(Y[0], Y[1], 0x5140u), t1 = prmt(Y[2], Y[3], 0x5140u);
-      const uint32_t t2 = prmt(Y[0], Y[1], 0x7362u), t3 = prmt(Y[2], Y[3], 0x7362u);
-      uint32_t *dst = reinterpret_cast<uint32_t *>(xs + digit_offset(S, kb, 4 * b, quad * 4));
-      const int plane = 32 / 4;  // words between consecutive columns of a block
-      dst[0 * plane] = prmt(t0, t1, 0x5410u) ^ 0x80808080u;
-      dst[1 * plane] = prmt(t0, t1, 0x7632u) ^ 0x80808080u;
-      dst[2 * plane] = prmt(t2, t3, 0x5410u) ^ 0x80808080u;
-      dst[3 * plane] = prmt(t2, t3, 0x7632u) ^ 0x80808080u;
-      if (quad == 0)
-        *reinterpret_cast<float4 *>(sb + (kb * P.batch + b) * 4) =
-            make_float4(s, __int_as_float(t_lo), s, __int_as_float(t_hi));
+    for (int it = 0; it < PRE; ++it)
+      if (kb0 + it * CW * 4 < P.kb) {
+        float v[4] = {xv[it].x, xv[it].y, xv[it].z, xv[it].w};
+        if (P.norm_w) {
+          v[0] = __fmul_rn(__fmul_rn(v[0], inv), wv[it].x);
+          v[1] = __fmul_rn(__fmul_rn(v[1], inv), wv[it].y);
+          v[2] = __fmul_rn(__fmul_rn(v[2], inv), wv[it].z);
+          v[3] = __fmul_rn(__fmul_rn(v[3], inv), wv[it].w);
+        }
+        pack_block(v, kb0 + it * CW * 4, 0);
+      }
+  } else {
+    pdl_wait();
+    if (EPI == EPI_RESIDUAL && ctid < GROUP_ROWS * 2 && (ctid & 1) < P.batch && r_begin + (ctid >> 1) < r_end)
+      resid0 = P.y[(size_t)(ctid & 1) * P.ldy + r_begin + (ctid >> 1)];
+    for (int b = 0; b < P.batch; ++b) {
+      const float *xr = P.x + (size_t)(P.col_map ? P.col_map[b] : b) * P.ldx;
+      float inv = 1.0f;
+      if (P.norm_w) {
+        float ss = 0.0f;
+        for (int i = ctid; i < P.kb * 8; i += CW * 32) {
+          const float4 f = __ldg(reinterpret_cast<const float4 *>(xr) + i);
+          ss = fmaf(f.x, f.x, ss);
+          ss = fmaf(f.y, f.y, ss);
+          ss = fmaf(f.z, f.z, ss);
+          ss = fmaf(f.w, f.w, ss);
+        }
+        inv = inv_rms(ss);
+      }
+#pragma unroll 4
+      for (int kb = kb0; kb < P.kb; kb += CW * 4) {
+        const float4 f = __ldg(reinterpret_cast<const float4 *>(xr + kb * 32) + quad);
+        float v[4] = {f.x, f.y, f.z, f.w};
+        if (P.norm_w) {
+          const float4 w = __ldg(reinterpret_cast<const float4 *>(P.norm_w + kb * 32) + quad);
+          v[0] = __fmul_rn(__fmul_rn(v[0], inv), w.x);
+          v[1] = __fmul_rn(__fmul_rn(v[1], inv), w.y);
+          v[2] = __fmul_rn(__fmul_rn(v[2], inv), w.z);
+          v[3] = __fmul_rn(__fmul_rn(v[3], inv), w.w);
+        }
+        pack_block(v, kb, b);
+      }
     }
   }
   asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
@@ -501,7 +558,7 @@ __global__ void __launch_bounds__(THREADS, 1)
           P.y[(size_t)b * P.ldy + vrow] = v;
         } else if (EPI == EPI_RESIDUAL) {
           float *dst = P.y + (size_t)b * P.ldy + vrow;
-          *dst = __fadd_rn(*dst, v);
+          *dst = __fadd_rn(grp == 0 ? resid0 : *dst, v);
         } else {
           P.y[(size_t)b * P.ldy + vrow] = swiglu(v, total(row + 16));
         }
