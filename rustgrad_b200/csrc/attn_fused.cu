@@ -80,9 +80,12 @@ __host__ __device__ inline int span_for(int total, int per_head, int smax) {
 }
 
 template <typename KV, int HD>
-__global__ void __launch_bounds__(THREADS) attn_fused_kernel(const FusedAttnArgs A, int per_head, int *status) {
-  pdl_wait();
-  pdl_launch_dependents();
+__global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnArgs A, int per_head, int *status) {
+  // A.early: the positions and the cached rows of earlier positions were written at least one
+  // attention launch ago, and every attention launch lets its dependents start only after its own
+  // dependency wait, so they are complete whenever this CTA runs: the position, the rotation
+  // factors and the bulk copies of the cached spans need not wait for the projection kernel.
+  if (!A.early) pdl_wait();
   constexpr int SMAX = span_max(HD, (int)sizeof(KV));
   constexpr int DPL = HD / 16;  // dims per lane in the score phase
   const int c = blockIdx.z, kvh = blockIdx.y, sp = blockIdx.x;
@@ -90,7 +93,10 @@ __global__ void __launch_bounds__(THREADS) attn_fused_kernel(const FusedAttnArgs
   const int total = pos + 1;
   const int span = span_for(total, per_head, SMAX);
   const int nspl = (total + span - 1) / span;
-  if (sp >= nspl) return;
+  if (sp >= nspl) {
+    pdl_launch_dependents();
+    return;
+  }
   const int G = A.heads / A.kv_heads;
   const int p0 = sp * span;
   const int np = min(span, total - p0);
@@ -123,18 +129,25 @@ __global__ void __launch_bounds__(THREADS) attn_fused_kernel(const FusedAttnArgs
   const int qw = A.heads * HD, kw = A.kv_heads * HD;
   const float *row = A.qkv + (size_t)c * (qw + 2 * kw);
   const float *ct = A.cos_t + (size_t)pos * (HD / 2), *st = A.sin_t + (size_t)pos * (HD / 2);
+  float cs0 = 0.0f, sn0 = 0.0f;  // rotation factors of this thread's first pair (constant tables)
+  if (tid < G * (HD / 2)) {
+    cs0 = ct[tid % (HD / 2)];
+    sn0 = st[tid % (HD / 2)];
+  }
+  if (A.early) pdl_wait();
+  pdl_launch_dependents();
   // pairs (2i, 2i+1) of the projection rotate into (i, HD/2 + i) (layer.rs:349-371)
   for (int it = tid; it < G * (HD / 2); it += THREADS) {
     const int gq = it / (HD / 2), i = it - gq * (HD / 2);
     const float2 xv = reinterpret_cast<const float2 *>(row + (size_t)(kvh * G + gq) * HD)[i];
-    const float cs = ct[i], sn = st[i];
+    const float cs = it == tid ? cs0 : ct[i], sn = it == tid ? sn0 : st[i];
     qs[gq * HD + i] = __fsub_rn(__fmul_rn(xv.x, cs), __fmul_rn(xv.y, sn));
     qs[gq * HD + HD / 2 + i] = __fadd_rn(__fmul_rn(xv.y, cs), __fmul_rn(xv.x, sn));
   }
   if (has_new) {
     for (int i = tid; i < HD / 2; i += THREADS) {
       const float2 xv = reinterpret_cast<const float2 *>(row + qw + (size_t)kvh * HD)[i];
-      const float cs = ct[i], sn = st[i];
+      const float cs = i == tid ? cs0 : ct[i], sn = i == tid ? sn0 : st[i];
       const KV y1 = to_kv<KV>(__fsub_rn(__fmul_rn(xv.x, cs), __fmul_rn(xv.y, sn)));
       const KV y2 = to_kv<KV>(__fadd_rn(__fmul_rn(xv.y, cs), __fmul_rn(xv.x, sn)));
       KV *g = kc + (row0 + (np - 1)) * HD, *s = ks + (size_t)(np - 1) * HD;
@@ -238,15 +251,39 @@ __global__ void __launch_bounds__(THREADS) attn_fused_kernel(const FusedAttnArgs
   }
   __syncthreads();
   if (!last_flag) return;
-  // ---- combine.  Span headers (max, sum) go to shared memory in one round of independent loads;
-  // the weights follow from them, and every output thread then fetches its column in batches of
-  // eight loads in flight (a dependent load-use loop would pay the L2 latency once per span).
+  // ---- combine.  The span headers (max, sum) and the first CB spans of this thread's output
+  // column are requested together, before the weights exist: one round trip to L2 instead of one
+  // for the headers and one per batch of spans (a dependent load-use loop would pay it per span).
+  constexpr int CB = 40;
+  constexpr int HPT = 6;  // headers per thread: 2 * MAX_G * split cap <= HPT * THREADS
   float *hdr = sc;  // [G][nspl][2] then weights [G][nspl]; the scores are no longer needed
   float *wts = sc + 2 * G * nspl;  // 3 * G * nspl floats in all: the launcher caps the number of spans
-  for (int i = tid; i < G * nspl * 2; i += THREADS) {
-    const int gq = i / (nspl * 2), r = i - gq * nspl * 2;
-    hdr[i] = __ldcg(A.scratch + (((size_t)c * A.heads + (size_t)(kvh * G + gq)) * A.max_splits + (r >> 1)) * (HD + 2) + (r & 1));
+  const int nh = G * nspl * 2, nout = G * (HD / 2);
+  const float *head0 = A.scratch + ((size_t)c * A.heads + (size_t)kvh * G) * A.max_splits * (HD + 2);
+  float hreg[HPT];
+#pragma unroll
+  for (int j = 0; j < HPT; ++j) {
+    const int i = tid + j * THREADS;
+    hreg[j] = 0.0f;
+    if (i < nh) {
+      const int gq = i / (nspl * 2), r = i - gq * nspl * 2;
+      hreg[j] = __ldcg(head0 + ((size_t)gq * A.max_splits + (r >> 1)) * (HD + 2) + (r & 1));
+    }
   }
+  auto column = [&](int o) {
+    const int gq = o / (HD / 2), d = 2 * (o - gq * (HD / 2));
+    return head0 + (size_t)gq * A.max_splits * (HD + 2) + 2 + d;
+  };
+  float2 v0[CB];
+  {
+    const float *base = column(tid < nout ? tid : 0);
+#pragma unroll
+    for (int j = 0; j < CB; ++j)
+      v0[j] = (tid < nout && j < nspl) ? __ldcg(reinterpret_cast<const float2 *>(base + (size_t)j * (HD + 2))) : make_float2(0.0f, 0.0f);
+  }
+#pragma unroll
+  for (int j = 0; j < HPT; ++j)
+    if (tid + j * THREADS < nh) hdr[tid + j * THREADS] = hreg[j];
   __syncthreads();
   if (warp < G) {
     const int gq = warp;
@@ -263,11 +300,22 @@ __global__ void __launch_bounds__(THREADS) attn_fused_kernel(const FusedAttnArgs
     if (lane == 0) ml[gq * 2 + 1] = __frcp_rn(L);
   }
   __syncthreads();
-  for (int o = tid; o < G * (HD / 2); o += THREADS) {
+  for (int o = tid; o < nout; o += THREADS) {
     const int gq = o / (HD / 2), d = 2 * (o - gq * (HD / 2));
-    const float *base = A.scratch + ((size_t)c * A.heads + (size_t)(kvh * G + gq)) * A.max_splits * (HD + 2) + 2 + d;
+    const float *base = column(o);
     float a0 = 0.0f, a1 = 0.0f;
-    for (int s0 = 0; s0 < nspl; s0 += 20) {
+    int s0 = 0;
+    if (o == tid) {  // spans 0 .. CB-1 are already here, in span order like the rounds below
+#pragma unroll
+      for (int j = 0; j < CB; ++j)
+        if (j < nspl) {
+          const float wgt = wts[gq * nspl + j];
+          a0 = fmaf(v0[j].x, wgt, a0);
+          a1 = fmaf(v0[j].y, wgt, a1);
+        }
+      s0 = CB;
+    }
+    for (; s0 < nspl; s0 += 20) {
       float2 v[20];
 #pragma unroll
       for (int j = 0; j < 20; ++j)

@@ -245,6 +245,9 @@ struct FusedAttnArgs {
   int max_splits = 0;
   unsigned *counters = nullptr;
   float *out = nullptr;
+  // the launch may read positions, rotation tables and cached rows before its grid dependency
+  // resolves: only when an earlier attention launch of the same step separates it from their writers
+  bool early = false;
 };
 bool fused_attention_supported(int heads, int kv_heads, int hd);
 int fused_attn_per_head(int sm_count, int kv_heads, int cols);

@@ -349,16 +349,17 @@ __global__ void __launch_bounds__(THREADS, 1)
   };
 
   // ---- prologue: (RMSNorm and) block fixed-point packing of the activations into shared memory
-  constexpr int PRE = 5;  // register-resident form: up to PRE blocks per lane (K <= PRE * CW * 128)
+  // register-resident form: up to PRE blocks per lane (K <= PRE * CW * 128), PRE_W with a norm
+  constexpr int PRE = 8, PRE_W = 5;
   const int kb0 = warp * 4 + (lane >> 3);
   float resid0 = 0.0f;
-  if (B1 && P.kb <= PRE * CW * 4) {
+  if (B1 && P.kb <= (P.norm_w ? PRE_W : PRE) * CW * 4) {
     // The norm weights are constant data: fetch them before the grid dependency resolves, then the
     // activation once; both passes (sum of squares, packing) run from registers.
-    float4 wv[PRE], xv[PRE];
+    float4 wv[PRE_W], xv[PRE];
     if (P.norm_w) {
 #pragma unroll
-      for (int it = 0; it < PRE; ++it)
+      for (int it = 0; it < PRE_W; ++it)
         if (kb0 + it * CW * 4 < P.kb) wv[it] = __ldg(reinterpret_cast<const float4 *>(P.norm_w) + ctid + it * CW * 32);
     }
     pdl_wait();
@@ -372,7 +373,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     if (P.norm_w) {
       float ss = 0.0f;
 #pragma unroll
-      for (int it = 0; it < PRE; ++it)
+      for (int it = 0; it < PRE_W; ++it)
         if (kb0 + it * CW * 4 < P.kb) {
           ss = fmaf(xv[it].x, xv[it].x, ss);
           ss = fmaf(xv[it].y, xv[it].y, ss);
@@ -385,7 +386,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     for (int it = 0; it < PRE; ++it)
       if (kb0 + it * CW * 4 < P.kb) {
         float v[4] = {xv[it].x, xv[it].y, xv[it].z, xv[it].w};
-        if (P.norm_w) {
+        if (it < PRE_W && P.norm_w) {
           v[0] = __fmul_rn(__fmul_rn(v[0], inv), wv[it].x);
           v[1] = __fmul_rn(__fmul_rn(v[1], inv), wv[it].y);
           v[2] = __fmul_rn(__fmul_rn(v[2], inv), wv[it].z);

@@ -522,6 +522,7 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
       fa.max_splits = s->attn_max_splits;
       fa.counters = s->attn_counters;
       fa.out = s->attn_f32;
+      fa.early = l > 0;  // layer 0 follows the kernels that set the positions
       RG_LAUNCH(s, launch_attention_fused(fa, L));
     } else {
       RopeArgs ra;
