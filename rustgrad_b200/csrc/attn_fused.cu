@@ -79,7 +79,33 @@ __host__ __device__ inline int span_for(int total, int per_head, int smax) {
   return span > smax ? smax : span;
 }
 
-template <typename KV, int HD>
+// Sum over the 16 lanes of a half-warp of NV values per lane (NV = 16, 8 or 4): while more than
+// one value is left, each level halves them (a lane keeps the half its lane bit selects and adds
+// the partner's copy of it), then plain butterfly adds.  Returns the total of value index
+// sub >> log2(16 / NV); 15 shuffles for 16 values instead of 64.
+template <int NV>
+__device__ __forceinline__ float reduce_scatter16(float (&val)[NV], int sub) {
+  int n = NV;
+#pragma unroll
+  for (int off = 8; off >= 1; off >>= 1) {
+    if (n > 1) {
+      n >>= 1;
+      const bool up = (sub & off) != 0;
+#pragma unroll
+      for (int j = 0; j < NV / 2; ++j)
+        if (j < n) {
+          const float a = val[j], b = val[j + n];
+          const float send = up ? a : b, keep = up ? b : a;
+          val[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+    } else {
+      val[0] += __shfl_xor_sync(0xffffffffu, val[0], off);
+    }
+  }
+  return val[0];
+}
+
+template <typename KV, int HD, int G>
 __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnArgs A, int per_head, int *status) {
   // A.early: the positions and the cached rows of earlier positions were written at least one
   // attention launch ago, and every attention launch lets its dependents start only after its own
@@ -97,7 +123,6 @@ __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnA
     pdl_launch_dependents();
     return;
   }
-  const int G = A.heads / A.kv_heads;
   const int p0 = sp * span;
   const int np = min(span, total - p0);
   const bool has_new = (p0 + np == total);
@@ -165,34 +190,36 @@ __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnA
   // ---- scores: 16 lanes per position; scale = 1 / f32(sqrt(hd)) applied as a division (attention.rs:1183-1188)
   const float inv_scale = (float)(1.0 / (1.0 / sqrt((double)HD)));
   {
+    // 16 lanes per position, DPL dims per lane; a K row is converted once and used by GH heads;
+    // eight positions per warp in flight (four per half-warp)
+    constexpr int GH = G < 4 ? G : 4, NV = 4 * GH;
     const int sub = lane & 15, hi = lane >> 4;
-    for (int gq = 0; gq < G; ++gq) {
-      float qr[DPL];
+    for (int g0 = 0; g0 < G; g0 += GH) {
+      float qr[GH][DPL];
 #pragma unroll
-      for (int i = 0; i < DPL; ++i) qr[i] = qs[gq * HD + sub * DPL + i];
-      // four positions per half-warp in flight: their loads, products and shuffles interleave
+      for (int h = 0; h < GH; ++h)
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) qr[h][i] = qs[(g0 + h) * HD + sub * DPL + i];
       for (int base = 0; base < np; base += 8 * WARPS) {
-        float dot[4];
+        float dot[NV];  // index u * GH + h
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const int p = base + u * 2 * WARPS + warp * 2 + hi;
-          dot[u] = 0.0f;
+#pragma unroll
+          for (int h = 0; h < GH; ++h) dot[u * GH + h] = 0.0f;
           if (p < np) {
             float kr[DPL];
             load_n<DPL>(ks + (size_t)p * HD + sub * DPL, kr);
 #pragma unroll
-            for (int i = 0; i < DPL; ++i) dot[u] = fmaf(qr[i], kr[i], dot[u]);
+            for (int h = 0; h < GH; ++h)
+#pragma unroll
+              for (int i = 0; i < DPL; ++i) dot[u * GH + h] = fmaf(qr[h][i], kr[i], dot[u * GH + h]);
           }
         }
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1)
-#pragma unroll
-          for (int u = 0; u < 4; ++u) dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], o);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int p = base + u * 2 * WARPS + warp * 2 + hi;
-          if (sub == 0 && p < np) sc[p * MAX_G + gq] = __fdiv_rn(dot[u], inv_scale);
-        }
+        const float tot = reduce_scatter16<NV>(dot, sub);
+        const int v = sub / (16 / NV), u = v / GH, h = v - u * GH;
+        const int p = base + u * 2 * WARPS + warp * 2 + hi;
+        if ((sub & (16 / NV - 1)) == 0 && p < np) sc[p * MAX_G + g0 + h] = __fdiv_rn(tot, inv_scale);
       }
     }
   }
@@ -215,16 +242,49 @@ __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnA
     }
   }
   __syncthreads();
-  // ---- P.V: one thread per (head, pair of dims)
+  // ---- P.V: one thread per (pair of dims, position class p mod PG) for all heads, so a V pair is
+  // converted once; the PG partial sums meet in the K staging buffer (free after the scores)
+  constexpr int PG = THREADS / (HD / 2);
+  static_assert(PG * MAX_G * HD * 4 <= STAGE_BYTES / 2, "partial sums fit the K staging buffer");
+  float *pvs = reinterpret_cast<float *>(smem);  // [PG][G][HD]
+  {
+    const int pg = tid / (HD / 2), dp = tid - pg * (HD / 2);
+    float acc[G][2];
+#pragma unroll
+    for (int h = 0; h < G; ++h) acc[h][0] = acc[h][1] = 0.0f;
+#pragma unroll 4
+    for (int p = pg; p < np; p += PG) {
+      const float2 vv = load2(vs + (size_t)p * HD + 2 * dp);
+      float pr[G];
+      if constexpr (G % 4 == 0) {
+#pragma unroll
+        for (int h4 = 0; h4 < G / 4; ++h4) {
+          const float4 f = *reinterpret_cast<const float4 *>(sc + p * MAX_G + 4 * h4);
+          pr[4 * h4] = f.x, pr[4 * h4 + 1] = f.y, pr[4 * h4 + 2] = f.z, pr[4 * h4 + 3] = f.w;
+        }
+      } else {
+#pragma unroll
+        for (int h = 0; h < G; ++h) pr[h] = sc[p * MAX_G + h];
+      }
+#pragma unroll
+      for (int h = 0; h < G; ++h) {
+        acc[h][0] = fmaf(pr[h], vv.x, acc[h][0]);
+        acc[h][1] = fmaf(pr[h], vv.y, acc[h][1]);
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < G; ++h)
+      *reinterpret_cast<float2 *>(pvs + ((size_t)pg * G + h) * HD + 2 * dp) = make_float2(acc[h][0], acc[h][1]);
+  }
+  __syncthreads();
   for (int o = tid; o < G * (HD / 2); o += THREADS) {
     const int gq = o / (HD / 2), dp = o - gq * (HD / 2);
     float a0 = 0.0f, a1 = 0.0f;
-#pragma unroll 8
-    for (int p = 0; p < np; ++p) {
-      const float pr = sc[p * MAX_G + gq];
-      const float2 vv = load2(vs + (size_t)p * HD + 2 * dp);
-      a0 = fmaf(pr, vv.x, a0);
-      a1 = fmaf(pr, vv.y, a1);
+#pragma unroll
+    for (int pg = 0; pg < PG; ++pg) {
+      const float2 f = *reinterpret_cast<const float2 *>(pvs + ((size_t)pg * G + gq) * HD + 2 * dp);
+      a0 += f.x;
+      a1 += f.y;
     }
     float *dst = A.scratch + (((size_t)c * A.heads + (size_t)(kvh * G + gq)) * A.max_splits + sp) * (HD + 2);
     dst[2 + 2 * dp] = a0;
@@ -334,9 +394,9 @@ __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnA
   }
 }
 
-template <typename KV, int HD>
+template <typename KV, int HD, int G>
 cudaError_t launch_t(const FusedAttnArgs &a, const LaunchCfg &cfg) {
-  auto kernel = attn_fused_kernel<KV, HD>;
+  auto kernel = attn_fused_kernel<KV, HD, G>;
   constexpr size_t smem = STAGE_BYTES + (MAX_G * HD + SC_POS * MAX_G + 2 * MAX_G) * sizeof(float);
   static_assert(span_max(HD, (int)sizeof(KV)) <= SC_POS, "score buffer");
   static bool attr_done = false;
@@ -363,6 +423,12 @@ cudaError_t launch_t(const FusedAttnArgs &a, const LaunchCfg &cfg) {
   return cudaLaunchKernelEx(&lc, kernel, a, per_head, cfg.status);
 }
 
+template <int G>
+cudaError_t launch_g(const FusedAttnArgs &a, const LaunchCfg &cfg) {
+  if (a.hd == 128) return a.kv_f32 ? launch_t<float, 128, G>(a, cfg) : launch_t<__half, 128, G>(a, cfg);
+  return a.kv_f32 ? launch_t<float, 64, G>(a, cfg) : launch_t<__half, 64, G>(a, cfg);
+}
+
 }  // namespace
 
 int fused_attn_per_head(int sm_count, int kv_heads, int cols) {
@@ -387,15 +453,20 @@ int fused_attn_split_cap() { return SC_POS / 3; }  // span headers + weights of 
 bool fused_attention_supported(int heads, int kv_heads, int hd) {
   if (kv_heads < 1 || heads % kv_heads) return false;
   const int g = heads / kv_heads;
-  return (hd == 64 || hd == 128) && g >= 1 && g <= MAX_G;
+  return (hd == 64 || hd == 128) && (g == 1 || g == 2 || g == 4 || g == 8);
 }
 
 cudaError_t launch_attention_fused(const FusedAttnArgs &a, const LaunchCfg &cfg) {
   if (!fused_attention_supported(a.heads, a.kv_heads, a.hd) || a.cols < 1 || !a.counters || !a.scratch || !a.out ||
       a.max_splits > fused_attn_split_cap())
     return cudaErrorInvalidValue;
-  if (a.hd == 128) return a.kv_f32 ? launch_t<float, 128>(a, cfg) : launch_t<__half, 128>(a, cfg);
-  return a.kv_f32 ? launch_t<float, 64>(a, cfg) : launch_t<__half, 64>(a, cfg);
+  switch (a.heads / a.kv_heads) {
+    case 1: return launch_g<1>(a, cfg);
+    case 2: return launch_g<2>(a, cfg);
+    case 4: return launch_g<4>(a, cfg);
+    case 8: return launch_g<8>(a, cfg);
+    default: return cudaErrorInvalidValue;
+  }
 }
 
 }  // namespace rg
