@@ -28,6 +28,8 @@
 //    prefetch issued before the grid dependency wait.
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "../../include/rg_b200.h"
 #include "kernels.h"
 #include "rg_device.cuh"
@@ -282,57 +284,74 @@ __global__ void __launch_bounds__(THREADS, 1)
 
   // -------------------------------------------------------------------- consumers
   const int ctid = threadIdx.x;  // 0 .. CW*32-1
-  const int quad = lane & 7;
-  // Eight lanes per block, four consecutive elements per lane (= one 32-bit word of each digit
-  // plane in the fragment layout); a warp converts four blocks per iteration.  The lane's float4
-  // index of block kb is kb * 8 + quad = ctid + iteration * CW * 32.
-  auto pack_block = [&](const float (&v)[4], int kb, int b) {
-    float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-    if (!(fabsf(v[0] + v[1] + v[2] + v[3]) <= 3.0e38f)) m = __uint_as_float(0x7f800000u);  // fmaxf drops NaN: keep it visible
+  // ---- prologue: (RMSNorm and) block fixed-point packing of the activations into shared memory.
+  // Four lanes per block: lane q of a block holds elements 4q..4q+3 and 16+4q..16+4q+3 (the two
+  // 32-bit words of each digit plane that one consumer lane fetches together); a warp converts
+  // eight blocks per pass, the CTA PASS_BLOCKS.  All lanes run every shuffle; `live` only guards
+  // the stores, so independent passes can be interleaved by the compiler.
+  constexpr int PASS_BLOCKS = CW * 8;
+  const int q4 = lane & 3;
+  const int kbw = warp * 8 + (lane >> 2);
+  auto pack_block = [&](float (&v)[8], int kb, int b, bool live) {
+    float m = 0.0f, tot = 0.0f;
 #pragma unroll
-    for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    for (int i = 0; i < 8; ++i) {
+      m = fmaxf(m, fabsf(v[i]));
+      tot += v[i];
+    }
+    if (!(fabsf(tot) <= 3.0e38f)) m = __uint_as_float(0x7f800000u);  // fmaxf drops NaN: keep it visible
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
     const uint32_t E = __float_as_uint(m) >> 23;  // biased exponent of the block maximum (m >= 0)
     constexpr uint32_t XBITS = G::Q4 ? 25u : 29u;  // |X| < 2^(XBITS + 1)
     float s = 0.0f;
-    int X[4] = {0, 0, 0, 0};
+    int X[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (E >= 40u && E < 255u) {
       s = __uint_as_float((E - XBITS) << 23);  // 2^(floor(log2 m) - XBITS)
       const float up = __uint_as_float((254u + XBITS - E) << 23);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) X[i] = __float2int_rn(v[i] * up);
+      for (int i = 0; i < 8; ++i) X[i] = __float2int_rn(v[i] * up);
     } else if (E == 255u) {  // inf / NaN input must stay visible in the result
       s = __uint_as_float(0x7fc00000u);
       X[0] = 1;
     }
     int t_lo = 0, t_hi = 0;
     if constexpr (G::Q4) {
-      int sum = (X[0] + X[1]) + (X[2] + X[3]);  // |sum over the block| < 2^31
-#pragma unroll
-      for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      int sum = ((X[0] + X[1]) + (X[2] + X[3])) + ((X[4] + X[5]) + (X[6] + X[7]));  // |sum over the block| < 2^31
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
       t_lo = (sum & 0x1FF) << 7;  // 128 * sum = t_lo + 65536 * t_hi
       t_hi = sum >> 9;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int xp = __shfl_xor_sync(0xffffffffu, X[i], 4);  // element e - 16 for the upper half
-        X[i] = (quad < 4) ? (X[i] << 4) : (X[i] - (xp << 4));
+        X[4 + i] -= X[i] << 4;  // X[k] - 16 X[k-16]
+        X[i] <<= 4;             // 16 X[k]
       }
     }
-    // X + 0x80808080 turns the four signed base-256 digits of X into unsigned bytes (digit + 128)
-    uint32_t Y[4];
+    // X + 0x80808080 turns the four signed base-256 digits of X into unsigned bytes (digit + 128);
+    // 4x4 byte transposes: word d = digit d of four elements, then back to signed
+    uint32_t Y[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) Y[i] = (uint32_t)X[i] + 0x80808080u;
-    // 4x4 byte transpose: word d = digit d of the lane's four elements, then back to signed
-    const uint32_t t0 = prmt(Y[0], Y[1], 0x5140u), t1 = prmt(Y[2], Y[3], 0x5140u);
-    const uint32_t t2 = prmt(Y[0], Y[1], 0x7362u), t3 = prmt(Y[2], Y[3], 0x7362u);
-    uint32_t *dst = reinterpret_cast<uint32_t *>(xs + digit_offset(S, kb, 4 * b, quad * 4));
-    const int plane = 32 / 4;  // words between consecutive columns of a block
-    dst[0 * plane] = prmt(t0, t1, 0x5410u) ^ 0x80808080u;
-    dst[1 * plane] = prmt(t0, t1, 0x7632u) ^ 0x80808080u;
-    dst[2 * plane] = prmt(t2, t3, 0x5410u) ^ 0x80808080u;
-    dst[3 * plane] = prmt(t2, t3, 0x7632u) ^ 0x80808080u;
-    if (quad == 0)
-      *reinterpret_cast<float4 *>(sb + (kb * P.batch + b) * 4) =
-          make_float4(s, __int_as_float(t_lo), s, __int_as_float(t_hi));
+    for (int i = 0; i < 8; ++i) Y[i] = (uint32_t)X[i] + 0x80808080u;
+    uint32_t D[2][4];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const uint32_t t0 = prmt(Y[4 * r], Y[4 * r + 1], 0x5140u), t1 = prmt(Y[4 * r + 2], Y[4 * r + 3], 0x5140u);
+      const uint32_t t2 = prmt(Y[4 * r], Y[4 * r + 1], 0x7362u), t3 = prmt(Y[4 * r + 2], Y[4 * r + 3], 0x7362u);
+      D[r][0] = prmt(t0, t1, 0x5410u) ^ 0x80808080u;
+      D[r][1] = prmt(t0, t1, 0x7632u) ^ 0x80808080u;
+      D[r][2] = prmt(t2, t3, 0x5410u) ^ 0x80808080u;
+      D[r][3] = prmt(t2, t3, 0x7632u) ^ 0x80808080u;
+    }
+    if (live) {
+      uint2 *dst = reinterpret_cast<uint2 *>(xs + digit_offset(S, kb, 4 * b, q4 * 4));
+      const int plane = 32 / 8;  // 64-bit words between consecutive columns of a block
+#pragma unroll
+      for (int d = 0; d < 4; ++d) dst[d * plane] = make_uint2(D[0][d], D[1][d]);
+      if (q4 == 0)
+        *reinterpret_cast<float4 *>(sb + (kb * P.batch + b) * 4) =
+            make_float4(s, __int_as_float(t_lo), s, __int_as_float(t_hi));
+    }
   };
   // y = (x * (1 / sqrt(mean(x^2) + eps))) * w, every step rounded to f32 (layer.rs:423-443)
   auto inv_rms = [&](float ss) {
@@ -347,53 +366,75 @@ __global__ void __launch_bounds__(THREADS, 1)
     asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
     return inv;
   };
-
-  // ---- prologue: (RMSNorm and) block fixed-point packing of the activations into shared memory
-  // register-resident form: up to PRE blocks per lane (K <= PRE * CW * 128), PRE_W with a norm
-  constexpr int PRE = 8, PRE_W = 5;
-  const int kb0 = warp * 4 + (lane >> 3);
-  float resid0 = 0.0f;
-  if (B1 && P.kb <= (P.norm_w ? PRE_W : PRE) * CW * 4) {
-    // The norm weights are constant data: fetch them before the grid dependency resolves, then the
-    // activation once; both passes (sum of squares, packing) run from registers.
-    float4 wv[PRE_W], xv[PRE];
-    if (P.norm_w) {
+  auto load8 = [&](const float *base, int kb, float4 &lo, float4 &hi) {
+    lo = __ldg(reinterpret_cast<const float4 *>(base + (size_t)kb * 32) + q4);
+    hi = __ldg(reinterpret_cast<const float4 *>(base + (size_t)kb * 32) + 4 + q4);
+  };
+  auto sumsq = [](float ss, const float4 &f) {
+    ss = fmaf(f.x, f.x, ss);
+    ss = fmaf(f.y, f.y, ss);
+    ss = fmaf(f.z, f.z, ss);
+    return fmaf(f.w, f.w, ss);
+  };
+  auto normed = [](float (&v)[8], float inv, const float4 &wl, const float4 &wh) {
+    const float w[8] = {wl.x, wl.y, wl.z, wl.w, wh.x, wh.y, wh.z, wh.w};
 #pragma unroll
-      for (int it = 0; it < PRE_W; ++it)
-        if (kb0 + it * CW * 4 < P.kb) wv[it] = __ldg(reinterpret_cast<const float4 *>(P.norm_w) + ctid + it * CW * 32);
+    for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(v[i], inv), w[i]);
+  };
+
+  float resid0 = 0.0f;
+  // Register-resident form (batch 1, up to four passes, three with a norm): the norm weights are
+  // constant data and are fetched before the grid dependency resolves, the activation is read
+  // once, and both uses (sum of squares, packing) run from registers as straight-line code.
+  auto fast = [&](auto np_c, auto norm_c) {
+    constexpr int NP = decltype(np_c)::value;
+    constexpr bool NORM = decltype(norm_c)::value;
+    const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 wl[NORM ? NP : 1], wh[NORM ? NP : 1], xl[NP], xh[NP];
+    if constexpr (NORM) {
+#pragma unroll
+      for (int it = 0; it < NP; ++it) {
+        wl[it] = wh[it] = zero;
+        if (it * PASS_BLOCKS + kbw < P.kb) load8(P.norm_w, it * PASS_BLOCKS + kbw, wl[it], wh[it]);
+      }
     }
     pdl_wait();
     const float *xr = P.x + (size_t)(P.col_map ? P.col_map[0] : 0) * P.ldx;
 #pragma unroll
-    for (int it = 0; it < PRE; ++it)
-      if (kb0 + it * CW * 4 < P.kb) xv[it] = __ldg(reinterpret_cast<const float4 *>(xr) + ctid + it * CW * 32);
+    for (int it = 0; it < NP; ++it) {
+      xl[it] = xh[it] = zero;
+      if (it * PASS_BLOCKS + kbw < P.kb) load8(xr, it * PASS_BLOCKS + kbw, xl[it], xh[it]);
+    }
     if (EPI == EPI_RESIDUAL && ctid < GROUP_ROWS * 2 && (ctid & 1) == 0 && r_begin + (ctid >> 1) < r_end)
       resid0 = P.y[r_begin + (ctid >> 1)];  // the first row group's residual, off the epilogue's path
     float inv = 1.0f;
-    if (P.norm_w) {
+    if constexpr (NORM) {
       float ss = 0.0f;
 #pragma unroll
-      for (int it = 0; it < PRE_W; ++it)
-        if (kb0 + it * CW * 4 < P.kb) {
-          ss = fmaf(xv[it].x, xv[it].x, ss);
-          ss = fmaf(xv[it].y, xv[it].y, ss);
-          ss = fmaf(xv[it].z, xv[it].z, ss);
-          ss = fmaf(xv[it].w, xv[it].w, ss);
-        }
+      for (int it = 0; it < NP; ++it) ss = sumsq(sumsq(ss, xl[it]), xh[it]);
       inv = inv_rms(ss);
     }
 #pragma unroll
-    for (int it = 0; it < PRE; ++it)
-      if (kb0 + it * CW * 4 < P.kb) {
-        float v[4] = {xv[it].x, xv[it].y, xv[it].z, xv[it].w};
-        if (it < PRE_W && P.norm_w) {
-          v[0] = __fmul_rn(__fmul_rn(v[0], inv), wv[it].x);
-          v[1] = __fmul_rn(__fmul_rn(v[1], inv), wv[it].y);
-          v[2] = __fmul_rn(__fmul_rn(v[2], inv), wv[it].z);
-          v[3] = __fmul_rn(__fmul_rn(v[3], inv), wv[it].w);
-        }
-        pack_block(v, kb0 + it * CW * 4, 0);
-      }
+    for (int it = 0; it < NP; ++it) {
+      float v[8] = {xl[it].x, xl[it].y, xl[it].z, xl[it].w, xh[it].x, xh[it].y, xh[it].z, xh[it].w};
+      if constexpr (NORM) normed(v, inv, wl[it], wh[it]);
+      const int kb = it * PASS_BLOCKS + kbw;
+      pack_block(v, kb, 0, kb < P.kb);
+    }
+  };
+  const int npass = (P.kb + PASS_BLOCKS - 1) / PASS_BLOCKS;
+  using std::integral_constant;
+  if (B1 && npass <= (P.norm_w ? 3 : 4)) {
+    if (P.norm_w) {
+      if (npass == 1) fast(integral_constant<int, 1>{}, integral_constant<bool, true>{});
+      else if (npass == 2) fast(integral_constant<int, 2>{}, integral_constant<bool, true>{});
+      else fast(integral_constant<int, 3>{}, integral_constant<bool, true>{});
+    } else {
+      if (npass == 1) fast(integral_constant<int, 1>{}, integral_constant<bool, false>{});
+      else if (npass == 2) fast(integral_constant<int, 2>{}, integral_constant<bool, false>{});
+      else if (npass == 3) fast(integral_constant<int, 3>{}, integral_constant<bool, false>{});
+      else fast(integral_constant<int, 4>{}, integral_constant<bool, false>{});
+    }
   } else {
     pdl_wait();
     if (EPI == EPI_RESIDUAL && ctid < GROUP_ROWS * 2 && (ctid & 1) < P.batch && r_begin + (ctid >> 1) < r_end)
@@ -403,27 +444,21 @@ __global__ void __launch_bounds__(THREADS, 1)
       float inv = 1.0f;
       if (P.norm_w) {
         float ss = 0.0f;
-        for (int i = ctid; i < P.kb * 8; i += CW * 32) {
-          const float4 f = __ldg(reinterpret_cast<const float4 *>(xr) + i);
-          ss = fmaf(f.x, f.x, ss);
-          ss = fmaf(f.y, f.y, ss);
-          ss = fmaf(f.z, f.z, ss);
-          ss = fmaf(f.w, f.w, ss);
-        }
+        for (int i = ctid; i < P.kb * 8; i += CW * 32) ss = sumsq(ss, __ldg(reinterpret_cast<const float4 *>(xr) + i));
         inv = inv_rms(ss);
       }
-#pragma unroll 4
-      for (int kb = kb0; kb < P.kb; kb += CW * 4) {
-        const float4 f = __ldg(reinterpret_cast<const float4 *>(xr + kb * 32) + quad);
-        float v[4] = {f.x, f.y, f.z, f.w};
-        if (P.norm_w) {
-          const float4 w = __ldg(reinterpret_cast<const float4 *>(P.norm_w + kb * 32) + quad);
-          v[0] = __fmul_rn(__fmul_rn(v[0], inv), w.x);
-          v[1] = __fmul_rn(__fmul_rn(v[1], inv), w.y);
-          v[2] = __fmul_rn(__fmul_rn(v[2], inv), w.z);
-          v[3] = __fmul_rn(__fmul_rn(v[3], inv), w.w);
+      for (int kbb = warp * 8; kbb < P.kb; kbb += PASS_BLOCKS) {  // warp-uniform trip count
+        const int kb = kbb + (lane >> 2);
+        const bool live = kb < P.kb;
+        float4 xl = make_float4(0.0f, 0.0f, 0.0f, 0.0f), xh = xl;
+        if (live) load8(xr, kb, xl, xh);
+        float v[8] = {xl.x, xl.y, xl.z, xl.w, xh.x, xh.y, xh.z, xh.w};
+        if (P.norm_w && live) {
+          float4 wl, wh;
+          load8(P.norm_w, kb, wl, wh);
+          normed(v, inv, wl, wh);
         }
-        pack_block(v, kb, b);
+        pack_block(v, kb, b, live);
       }
     }
   }
