@@ -249,9 +249,12 @@ __global__ void __launch_bounds__(THREADS, 1)
       if (round > 0) mbar_wait_bounded(&empty[stage], (uint32_t)((round - 1) & 1), dead, P.status);
       const int vr0 = r_begin + grp * GROUP_ROWS;
       uint8_t *sw = stage0 + (size_t)stage * STAGE_BYTES;
-      if (lane == 0) mbar_expect_tx(&full[stage], (uint32_t)STAGE_BYTES);
+      // a partial last group fetches only the boxes that hold rows of this CTA
+      const int nbx = (min(GROUP_ROWS, r_end - vr0) + BOXR - 1) / BOXR;
+      const bool box_live = PAIR ? (lane & 1) < nbx : lane < nbx;
+      if (lane == 0) mbar_expect_tx(&full[stage], (uint32_t)((PAIR ? 2 * nbx : nbx) * BOXR * G::RS));
       __syncwarp();
-      if (lane < R / BOXR) {
+      if (lane < R / BOXR && box_live) {
         const CUtensorMap *map = &map0;
         int row;
         if (PAIR) {
@@ -490,13 +493,17 @@ __global__ void __launch_bounds__(THREADS, 1)
     uint32_t aw = sw + lane_w_off + (uint32_t)warp * (2 * G::BB);
     uint32_t as = sw + lane_s_off + (uint32_t)warp * (2 * G::BB);
     int gb = c * G::KC + 2 * warp;  // global block index of the pair's even block
+    // rows 16..31 of a partial last group are not this CTA's: their boxes were not fetched
+    const bool two_tiles = PAIR || r_end - (r_begin + grp * GROUP_ROWS) > 16;
     for (int p = warp; 2 * p < nb; p += CW, aw += CW * 2 * G::BB, as += CW * 2 * G::BB, gb += 2 * CW) {
       uint32_t wq[4][6], sc[4][2];
       if constexpr (B1) {
         load_slot_b1<QT, 0>(aw, as, wq[0], sc[0]);
         load_slot_b1<QT, 1>(aw, as, wq[1], sc[1]);
-        load_slot_b1<QT, 2>(aw, as, wq[2], sc[2]);
-        load_slot_b1<QT, 3>(aw, as, wq[3], sc[3]);
+        if (two_tiles) {
+          load_slot_b1<QT, 2>(aw, as, wq[2], sc[2]);
+          load_slot_b1<QT, 3>(aw, as, wq[3], sc[3]);
+        }
         const uint2 xv = lds64(xs_lane + (uint32_t)(gb * 128));
         const uint2 side = lds64(sb_lane + (uint32_t)(gb * 16));
         const float sv = __uint_as_float(side.x);
@@ -506,6 +513,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         const uint32_t b_hi0 = ev ? xv.y : 0u, b_hi1 = ev ? 0u : xv.y;  // MMA 2: high halves
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt) {
+          if (mt == 1 && !two_tiles) break;
           uint32_t ae[2][2], ao[2][2];
           expand<QT>(wq[mt * 2], ae[0], ao[0]);
           expand<QT>(wq[mt * 2 + 1], ae[1], ao[1]);
@@ -541,6 +549,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       }
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
+        if (mt == 1 && !two_tiles) break;
         uint32_t ae[2][2], ao[2][2];
         expand<QT>(wq[mt * 2], ae[0], ao[0]);
         expand<QT>(wq[mt * 2 + 1], ae[1], ao[1]);
