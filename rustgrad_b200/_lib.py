@@ -45,6 +45,11 @@ EXPORTS = [
     "rg_b200_reset_sequence", "rg_b200_prefill", "rg_b200_decode", "rg_b200_generate_greedy", "rg_b200_decode_sampled", "rg_b200_generate_sampled", "rg_b200_decode_loop", "rg_b200_decode_profile",
     "rg_b200_report", "rg_b200_session_stream", "rg_b200_nccl_unique_id", "rg_b200_dequantize", "rg_b200_qmatmul",
     "rg_b200_row_gather", "rg_b200_qmatmul_bench", "rg_b200_qgemm", "rg_b200_attention_decode", "rg_b200_attention_decode_noalloc",
+    # include/rg_b200_tokenizer.h (bound in tokenizer.py)
+    "rg_b200_tokenizer_new", "rg_b200_tokenizer_from_gguf", "rg_b200_tokenizer_free", "rg_b200_tokenizer_config",
+    "rg_b200_tokenizer_is_end", "rg_b200_tokenizer_parse_preset", "rg_b200_tokenizer_encode", "rg_b200_tokenizer_decode",
+    "rg_b200_tok_stream_new", "rg_b200_tok_stream_push", "rg_b200_tok_stream_finish", "rg_b200_tok_stream_free",
+    "rg_b200_chat_template_from_gguf", "rg_b200_chat_template_text", "rg_b200_chat_render",
 ]
 
 _lib = None

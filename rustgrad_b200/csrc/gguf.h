@@ -52,3 +52,8 @@ int block_elements(int32_t ggml_type);
 int block_bytes(int32_t ggml_type);
 
 }  // namespace rg
+
+// The handle of rg_b200_gguf_open.
+struct rg_gguf {
+  rg::Gguf g;
+};

@@ -112,9 +112,6 @@ struct Slot {
 
 using namespace rg;
 
-struct rg_gguf {
-  Gguf g;
-};
 
 struct rg_plan {
   rg_llama_config cfg{};
