@@ -261,6 +261,38 @@ int32_t rg_b200_attention_decode_noalloc(const float *q_dev, const void *keys_de
                                          int32_t kv_heads, int32_t head_dim, int32_t ctx, int32_t n_pos, int32_t kv_f32,
                                          float *out_dev, void *stream, int32_t wait);
 
+/* ---- Verbs of a continuous-batching step.  rustgrad's serving scheduler
+ * (src/models/transformer/serving/mod.rs:557-690) rebuilds a batch from per-request K/V
+ * snapshots at every step; here a request keeps one cache row of the session while it runs, and a
+ * step is one decode launch over an arbitrary set of rows plus one prefill per newly admitted
+ * prompt.  rustgrad_b200/serving.py holds the scheduler that drives them. ---- */
+typedef struct rg_kv_snapshot rg_kv_snapshot;
+/* Forgets the cached positions of one row (a finished request's slot is handed to the next). */
+int32_t rg_b200_reset_row(rg_session *s, int32_t row);
+/* rg_b200_prefill that also returns the token selected from the last row's logits: greedy when
+ * temperature <= 0 or uniforms is NULL, else Gumbel-max with one row of `vocab` uniforms
+ * (serving/mod.rs:649-665). */
+int32_t rg_b200_prefill_select(rg_session *s, int32_t row, const int32_t *ids, size_t n, float temperature,
+                               const float *uniforms, float *last_logits, int32_t *selected);
+/* One decode step over n distinct rows, each at its own position: column i feeds tokens[i] to
+ * row rows[i].  temperatures (nullable) holds one value per column, <= 0 meaning greedy; uniforms
+ * is [n, vocab] and is only read for sampled columns.  logits (nullable) receives [n, vocab].
+ * Positions advance only when the whole step succeeded. */
+int32_t rg_b200_decode_rows(rg_session *s, const int32_t *rows, const int32_t *tokens, int32_t n,
+                            const float *temperatures, const float *uniforms, float *logits, int32_t *ids);
+/* Selection alone on host logits [n, vocab] (a prompt fully covered by a cached prefix needs no
+ * forward pass, serving/mod.rs:591-603), same rules as above, on the device. */
+int32_t rg_b200_select(rg_session *s, const float *logits, int32_t n, const float *temperatures, const float *uniforms,
+                       int32_t *ids);
+/* Immutable device copy of the first `length` cached positions of a row, all layers
+ * (LlamaNativePrefixSnapshot, serving/mod.rs:182-190); restore writes it into any row of a
+ * session of the same shape and sets that row's position to its length. */
+int32_t rg_b200_kv_snapshot_create(rg_session *s, int32_t row, int32_t length, rg_kv_snapshot **out);
+int32_t rg_b200_kv_snapshot_length(const rg_kv_snapshot *k);
+size_t rg_b200_kv_snapshot_bytes(const rg_kv_snapshot *k);
+int32_t rg_b200_kv_snapshot_restore(rg_session *s, const rg_kv_snapshot *k, int32_t row);
+void rg_b200_kv_snapshot_free(rg_kv_snapshot *k);
+
 /* Device-resident operator benchmark: weight uploaded once, `iters` launches timed with CUDA
  * events on the library's stream; `rotate` distinct weight copies are cycled so that each launch
  * reads HBM rather than L2.  kernel_ms receives the mean time of one launch. */

@@ -45,6 +45,8 @@ EXPORTS = [
     "rg_b200_reset_sequence", "rg_b200_prefill", "rg_b200_decode", "rg_b200_generate_greedy", "rg_b200_decode_sampled", "rg_b200_generate_sampled", "rg_b200_decode_loop", "rg_b200_decode_profile",
     "rg_b200_report", "rg_b200_session_stream", "rg_b200_nccl_unique_id", "rg_b200_dequantize", "rg_b200_qmatmul",
     "rg_b200_row_gather", "rg_b200_qmatmul_bench", "rg_b200_qgemm", "rg_b200_attention_decode", "rg_b200_attention_decode_noalloc",
+    "rg_b200_reset_row", "rg_b200_prefill_select", "rg_b200_decode_rows", "rg_b200_select", "rg_b200_kv_snapshot_create",
+    "rg_b200_kv_snapshot_length", "rg_b200_kv_snapshot_bytes", "rg_b200_kv_snapshot_restore", "rg_b200_kv_snapshot_free",
     # include/rg_b200_tokenizer.h (bound in tokenizer.py)
     "rg_b200_tokenizer_new", "rg_b200_tokenizer_from_gguf", "rg_b200_tokenizer_free", "rg_b200_tokenizer_config",
     "rg_b200_tokenizer_is_end", "rg_b200_tokenizer_parse_preset", "rg_b200_tokenizer_encode", "rg_b200_tokenizer_decode",
@@ -111,6 +113,17 @@ def load() -> C.CDLL:
                                      C.c_size_t, f32p]
     L.rg_b200_qgemm.argtypes = [C.c_int32, C.c_int32, u8p, C.c_uint64, C.c_uint64, f32p, C.c_uint64, C.c_int32, C.c_int32,
                                 f32p, f32p]
+    L.rg_b200_reset_row.argtypes = [vp, C.c_int32]
+    L.rg_b200_prefill_select.argtypes = [vp, C.c_int32, i32p, C.c_size_t, C.c_float, f32p, f32p, i32p]
+    L.rg_b200_decode_rows.argtypes = [vp, i32p, i32p, C.c_int32, f32p, f32p, f32p, i32p]
+    L.rg_b200_select.argtypes = [vp, f32p, C.c_int32, f32p, f32p, i32p]
+    L.rg_b200_kv_snapshot_create.argtypes = [vp, C.c_int32, C.c_int32, C.POINTER(vp)]
+    L.rg_b200_kv_snapshot_length.argtypes = [vp]
+    L.rg_b200_kv_snapshot_bytes.restype = C.c_size_t
+    L.rg_b200_kv_snapshot_bytes.argtypes = [vp]
+    L.rg_b200_kv_snapshot_restore.argtypes = [vp, vp, C.c_int32]
+    L.rg_b200_kv_snapshot_free.restype = None
+    L.rg_b200_kv_snapshot_free.argtypes = [vp]
     L.rg_b200_attention_decode_noalloc.argtypes = [vp, vp, vp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                                    C.c_int32, vp, vp, C.c_int32]
     L.rg_b200_attention_decode.argtypes = [C.c_int32, f32p, vp, vp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,

@@ -273,8 +273,9 @@ cudaError_t launch_attention_prefill(const PrefillAttnArgs &a, const LaunchCfg &
 // advance is set.
 cudaError_t launch_argmax(const float *logits, int ld, int vocab, int cols, int32_t *out_ids, const LaunchCfg &cfg);
 // Same with the Gumbel-max score transform when `uniforms` ([cols][vocab], device) is given (generation.rs:10-19,273-278).
+// `temps` (device, nullable): one temperature per column; columns with a non-positive one are greedy.
 cudaError_t launch_select(const float *logits, int ld, int vocab, int cols, const float *uniforms, float temperature,
-                          int32_t *out_ids, const LaunchCfg &cfg);
+                          int32_t *out_ids, const LaunchCfg &cfg, const float *temps = nullptr);
 cudaError_t launch_advance(const int32_t *ids, int32_t *tokens, int32_t *pos, int32_t *history, int32_t *step_counter,
                            int cols, const LaunchCfg &cfg);
 

@@ -410,14 +410,17 @@ __global__ void attn_combine_kernel(const float *scratch, int heads, int hd, con
 // non-finite logit is an error, reported as id -1 (the sentinel of metal_step.rs:964-987).
 // With a uniform tape the score is the Gumbel-max transform of generation.rs:10-19,273-278:
 // logit / max(T, 1e-12) - ln(-ln(max(u, 1e-12))), one row of `vocab` uniforms per column.
+// `temps` (nullable) holds one temperature per column; a column whose temperature is not
+// positive is selected greedily whatever the tape holds (mixed batches of a serving step).
 __global__ void argmax_kernel(const float *logits, int ld, int vocab, const float *uniforms, float temperature,
-                              int32_t *out_ids) {
+                              const float *temps, int32_t *out_ids) {
   pdl_wait();
   pdl_launch_dependents();
   const int c = blockIdx.x;
   const float *row = logits + (size_t)c * ld;
-  const float *urow = uniforms ? uniforms + (size_t)c * vocab : nullptr;
-  const float t = fmaxf(temperature, 1e-12f);
+  const float tc = temps ? temps[c] : temperature;
+  const float *urow = uniforms && (!temps || tc > 0.0f) ? uniforms + (size_t)c * vocab : nullptr;
+  const float t = fmaxf(tc, 1e-12f);
   float best = -INFINITY;
   int idx = 0x7fffffff;
   int bad = 0;
@@ -430,7 +433,7 @@ __global__ void argmax_kernel(const float *logits, int ld, int vocab, const floa
     }
   };
   const bool vec = ((vocab | ld) & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0 &&
-                   (!uniforms || (reinterpret_cast<uintptr_t>(uniforms) & 15) == 0);
+                   (!urow || (reinterpret_cast<uintptr_t>(urow) & 15) == 0);
   if (vec) {  // four logits per load, several loads in flight per thread; ids still ascend within a thread
     const float4 *row4 = reinterpret_cast<const float4 *>(row);
     const float4 *u4 = reinterpret_cast<const float4 *>(urow);
@@ -839,8 +842,8 @@ cudaError_t launch_attention(const AttnArgs &a, const LaunchCfg &cfg) {
                 a.col_pos, splits, a.cols, static_cast<__half *>(a.out_pack), a.out_f32);
 }
 cudaError_t launch_select(const float *logits, int ld, int vocab, int cols, const float *uniforms, float temperature,
-                          int32_t *out_ids, const LaunchCfg &cfg) {
-  return launch(argmax_kernel, dim3((unsigned)cols), dim3(1024), 0, cfg, logits, ld, vocab, uniforms, temperature, out_ids);
+                          int32_t *out_ids, const LaunchCfg &cfg, const float *temps) {
+  return launch(argmax_kernel, dim3((unsigned)cols), dim3(1024), 0, cfg, logits, ld, vocab, uniforms, temperature, temps, out_ids);
 }
 cudaError_t launch_argmax(const float *logits, int ld, int vocab, int cols, int32_t *out_ids, const LaunchCfg &cfg) {
   return launch_select(logits, ld, vocab, cols, nullptr, 1.0f, out_ids, cfg);

@@ -7,6 +7,8 @@
 // src/sharded_cuda_execute.rs (static Megatron split instead of a general sharded plan).
 #include <cuda_runtime.h>
 #include <math.h>
+
+#include <cmath>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -255,6 +257,8 @@ struct rg_session {
   const float *sample_uniforms = nullptr;
   float sample_temperature = 1.0f;
   float *d_uniforms = nullptr;  // [BMAX][vocab], allocated on first use
+  const float *sample_temps = nullptr;  // per-column temperatures of a mixed step (device), else null
+  float *d_temps = nullptr;             // [BMAX]
   bool chunk_is_prompt = false;  // the columns of the current step are consecutive positions of one sequence
   float *split_scratch = nullptr;  // K-split partial tiles of the tensor-core GEMM at small token counts
   void *xb = nullptr;  // 16-bit operand planes (hi, lo) of the tensor-core path: [2][WMAX][max(d, qw, ffn_l)]
@@ -594,7 +598,7 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
       if ((rc = comm_group_end(&err))) return fail(rc, err);
       am.pdl = false;
     }
-    RG_LAUNCH(s, launch_select(s->logits, c.vocab, c.vocab, n_logit_cols, s->sample_uniforms, s->sample_temperature, s->d_ids, am));
+    RG_LAUNCH(s, launch_select(s->logits, c.vocab, c.vocab, n_logit_cols, s->sample_uniforms, s->sample_temperature, s->d_ids, am, s->sample_temps));
     if (advance) RG_LAUNCH(s, launch_advance(s->d_ids, ctl->tokens, ctl->pos, s->d_history, &ctl->step, ncols, L));
   }
   return RG_OK;
@@ -803,7 +807,7 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
       if ((rc = comm_group_end(&err))) return fail(rc, err);
       am.pdl = false;
     }
-    RG_LAUNCH(s, launch_select(s->logits, c.vocab, c.vocab, n_logit_cols, s->sample_uniforms, s->sample_temperature, s->d_ids, am));
+    RG_LAUNCH(s, launch_select(s->logits, c.vocab, c.vocab, n_logit_cols, s->sample_uniforms, s->sample_temperature, s->d_ids, am, s->sample_temps));
     if (advance) RG_LAUNCH(s, launch_advance(s->d_ids, ctl->tokens, ctl->pos, s->d_history, &ctl->step, ncols, L));
   }
   return RG_OK;
@@ -1159,7 +1163,7 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
       if ((rc = comm_group_end(&err))) return fail(rc, err);
       am.pdl = false;
     }
-    RG_LAUNCH(s, launch_select(s->logits, c.vocab, c.vocab, n_logit_cols, s->sample_uniforms, s->sample_temperature, s->d_ids, am));
+    RG_LAUNCH(s, launch_select(s->logits, c.vocab, c.vocab, n_logit_cols, s->sample_uniforms, s->sample_temperature, s->d_ids, am, s->sample_temps));
     if (advance) RG_LAUNCH(s, launch_advance(s->d_ids, ctl->tokens, ctl->pos, s->d_history, &ctl->step, ncols, L));
   }
   return RG_OK;
@@ -1807,6 +1811,197 @@ int32_t rg_b200_decode_sampled(rg_session *s, const int32_t *tokens, int32_t bat
                                float *logits, int32_t *ids) {
   if (!uniforms) return fail(RG_INVALID_ARGUMENT, "null uniforms");
   return decode_impl(s, tokens, batch, logits, ids, temperature, uniforms);
+}
+
+// ---- verbs of a continuous-batching step (serving/mod.rs:557-690 runs over these) --------------
+// Uploads per-column temperatures and the uniform tape of a mixed step.  A column with a
+// non-positive temperature is greedy; with no positive temperature at all nothing is armed.
+static int32_t arm_mixed(rg_session *s, const float *temps, const float *uniforms, int n) {
+  s->sample_uniforms = nullptr;
+  s->sample_temps = nullptr;
+  if (!temps) return RG_OK;
+  bool any = false;
+  for (int i = 0; i < n; ++i) {
+    if (temps[i] > 0.0f && !std::isfinite(temps[i])) return fail(RG_INVALID_ARGUMENT, "temperature must be finite");
+    any = any || temps[i] > 0.0f;
+  }
+  if (!any) return RG_OK;
+  if (!uniforms) return fail(RG_INVALID_ARGUMENT, "a sampled column needs the uniform tape");
+  int32_t rc = arm_sampling(s, 1.0f, uniforms, n);
+  if (rc) return rc;
+  if (!s->d_temps && (rc = dalloc(s, &s->d_temps, (size_t)BMAX))) return rc;
+  RG_CUDA(x_memcpy_async(s->d_temps, temps, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, s->stream));
+  s->report.h2d_calls++;
+  s->report.h2d_bytes += sizeof(float) * (size_t)n;
+  s->sample_temps = s->d_temps;
+  return RG_OK;
+}
+
+int32_t rg_b200_reset_row(rg_session *s, int32_t row) {
+  int32_t rc = check_live(s);
+  if (rc) return rc;
+  if (row < 0 || row >= s->max_batch) return fail(RG_INVALID_ARGUMENT, "row out of range");
+  s->position[(size_t)row] = 0;
+  return RG_OK;
+}
+
+int32_t rg_b200_prefill_select(rg_session *s, int32_t row, const int32_t *ids, size_t n, float temperature, const float *uniforms,
+                               float *last_logits, int32_t *selected) {
+  const bool sampled = temperature > 0.0f && uniforms;
+  const int32_t rc = prefill_impl(s, row, ids, n, last_logits, sampled ? temperature : 1.0f, sampled ? uniforms : nullptr);
+  if (rc == RG_OK && selected) *selected = s->h_ids[0];
+  return rc;
+}
+
+int32_t rg_b200_decode_rows(rg_session *s, const int32_t *rows, const int32_t *tokens, int32_t n, const float *temperatures,
+                            const float *uniforms, float *logits, int32_t *ids) {
+  int32_t rc = check_live(s);
+  if (rc) return rc;
+  if (!rows || !tokens) return fail(RG_INVALID_ARGUMENT, "null rows or tokens");
+  if (n < 1 || n > s->max_batch) return fail(RG_INVALID_ARGUMENT, "batch out of range");
+  for (int i = 0; i < n; ++i) {
+    if (rows[i] < 0 || rows[i] >= s->max_batch) return fail(RG_INVALID_ARGUMENT, "row out of range");
+    for (int j = 0; j < i; ++j)
+      if (rows[j] == rows[i]) return fail(RG_INVALID_ARGUMENT, "row " + std::to_string(rows[i]) + " appears twice in one step");
+    if (tokens[i] < 0 || tokens[i] >= s->cfg.vocab) return fail(RG_TOKEN_OUT_OF_RANGE, "token " + std::to_string(tokens[i]) + " in column " + std::to_string(i));
+    if (s->position[(size_t)rows[i]] >= s->ctx) return fail(RG_CONTEXT_EXHAUSTED, "row " + std::to_string(rows[i]) + " is full");
+  }
+  RG_CUDA(cudaSetDevice(s->opt.device));
+  Ctrl *h = s->h_ctrl;
+  for (int i = 0; i < n; ++i) {
+    h->tokens[i] = tokens[i];
+    h->pos[i] = s->position[(size_t)rows[i]];
+    h->seq[i] = rows[i];
+    h->logit_cols[i] = i;
+  }
+  h->step = 0;
+  if ((rc = arm_mixed(s, temperatures, uniforms, n))) return rc;
+  struct Disarm {
+    rg_session *s;
+    ~Disarm() { s->sample_uniforms = nullptr, s->sample_temps = nullptr; }
+  } disarm{s};
+  RG_CUDA(cudaEventRecord(s->ev0, s->stream));
+  if ((rc = upload_ctrl(s))) return rc;
+  if ((rc = run_step(s, n, n, true, s->sample_uniforms == nullptr))) return rc;
+  RG_CUDA(cudaEventRecord(s->ev1, s->stream));
+  rc = finish_step(s, n, logits, logits ? n : 0);
+  if (rc && rc != RG_NON_FINITE_LOGITS) return rc;
+  cudaEventElapsedTime(&s->report.last_decode_ms, s->ev0, s->ev1);
+  if (rc) return rc;
+  if (ids) memcpy(ids, s->h_ids, sizeof(int32_t) * (size_t)n);
+  for (int i = 0; i < n; ++i) s->position[(size_t)rows[i]] += 1;
+  return RG_OK;
+}
+
+int32_t rg_b200_select(rg_session *s, const float *logits, int32_t n, const float *temperatures, const float *uniforms, int32_t *ids) {
+  int32_t rc = check_live(s);
+  if (rc) return rc;
+  if (!logits || !ids || n < 1 || n > s->max_batch) return fail(RG_INVALID_ARGUMENT, "bad selection arguments");
+  RG_CUDA(cudaSetDevice(s->opt.device));
+  const size_t bytes = sizeof(float) * (size_t)n * (size_t)s->cfg.vocab;
+  RG_CUDA(x_memcpy_async(s->logits, logits, bytes, cudaMemcpyHostToDevice, s->stream));
+  s->report.h2d_calls++;
+  s->report.h2d_bytes += bytes;
+  if ((rc = arm_mixed(s, temperatures, uniforms, n))) return rc;
+  struct Disarm {
+    rg_session *s;
+    ~Disarm() { s->sample_uniforms = nullptr, s->sample_temps = nullptr; }
+  } disarm{s};
+  LaunchCfg am = lcfg(s);
+  am.pdl = false;
+  RG_LAUNCH(s, launch_select(s->logits, s->cfg.vocab, s->cfg.vocab, n, s->sample_uniforms, s->sample_temperature, s->d_ids, am,
+                             s->sample_temps));
+  if ((rc = finish_step(s, n, nullptr, 0))) return rc;
+  memcpy(ids, s->h_ids, sizeof(int32_t) * (size_t)n);
+  return RG_OK;
+}
+
+// An immutable copy of the first `length` cached positions of one row, all layers
+// (LlamaNativePrefixSnapshot of serving/mod.rs:182-190): [layer][K, V][kv head][length][head_dim].
+struct rg_kv_snapshot {
+  int device = 0;
+  int length = 0;
+  size_t bytes = 0;
+  size_t row_bytes = 0;  // length * head_dim * element size
+  int n_layers = 0, kv_heads = 0;
+  uint8_t *data = nullptr;
+};
+
+static size_t kv_esize(const rg_session *s) { return s->kv_f32 ? 4 : 2; }
+
+int32_t rg_b200_kv_snapshot_create(rg_session *s, int32_t row, int32_t length, rg_kv_snapshot **out) {
+  int32_t rc = check_live(s);
+  if (rc) return rc;
+  if (!out || row < 0 || row >= s->max_batch || length < 1 || length > s->position[(size_t)row])
+    return fail(RG_INVALID_ARGUMENT, "snapshot of positions the row does not hold");
+  RG_CUDA(cudaSetDevice(s->opt.device));
+  auto snap = std::make_unique<rg_kv_snapshot>();
+  const size_t hd = (size_t)s->cfg.head_dim, es = kv_esize(s);
+  snap->device = s->opt.device;
+  snap->length = length;
+  snap->n_layers = s->cfg.n_layers;
+  snap->kv_heads = s->kv_l;
+  snap->row_bytes = (size_t)length * hd * es;
+  snap->bytes = 2 * (size_t)snap->n_layers * (size_t)snap->kv_heads * snap->row_bytes;
+  void *p = nullptr;
+  if (x_malloc(&p, snap->bytes) != cudaSuccess) return fail(RG_OUT_OF_MEMORY, "KV snapshot of " + std::to_string(snap->bytes) + " bytes");
+  snap->data = static_cast<uint8_t *>(p);
+  const size_t src_pitch = (size_t)s->ctx * hd * es, head_block = (size_t)snap->kv_heads * snap->row_bytes;
+  for (int l = 0; l < snap->n_layers; ++l)
+    for (int kv = 0; kv < 2; ++kv) {
+      const uint8_t *src = static_cast<const uint8_t *>(kv ? s->v_cache[(size_t)l] : s->k_cache[(size_t)l]) +
+                           (size_t)row * (size_t)snap->kv_heads * src_pitch;
+      uint8_t *dst = snap->data + ((size_t)l * 2 + (size_t)kv) * head_block;
+      cudaError_t e = cudaMemcpy2DAsync(dst, snap->row_bytes, src, src_pitch, snap->row_bytes, (size_t)snap->kv_heads,
+                                        cudaMemcpyDeviceToDevice, s->stream);
+      if (e != cudaSuccess) {
+        cudaFree(snap->data);
+        return fail(RG_CUDA_ERROR, std::string("snapshot copy: ") + cudaGetErrorString(e));
+      }
+    }
+  cudaError_t e = x_sync(s->stream);
+  if (e != cudaSuccess) {
+    cudaFree(snap->data);
+    s->poisoned = true;
+    return fail(RG_POISONED, std::string("stream synchronize: ") + cudaGetErrorString(e));
+  }
+  *out = snap.release();
+  return RG_OK;
+}
+
+int32_t rg_b200_kv_snapshot_length(const rg_kv_snapshot *k) { return k ? k->length : -1; }
+size_t rg_b200_kv_snapshot_bytes(const rg_kv_snapshot *k) { return k ? k->bytes : 0; }
+
+int32_t rg_b200_kv_snapshot_restore(rg_session *s, const rg_kv_snapshot *k, int32_t row) {
+  int32_t rc = check_live(s);
+  if (rc) return rc;
+  if (!k || row < 0 || row >= s->max_batch) return fail(RG_INVALID_ARGUMENT, "bad restore arguments");
+  const size_t hd = (size_t)s->cfg.head_dim, es = kv_esize(s);
+  if (k->device != s->opt.device || k->n_layers != s->cfg.n_layers || k->kv_heads != s->kv_l || k->length > s->ctx ||
+      k->row_bytes != (size_t)k->length * hd * es)
+    return fail(RG_SHAPE_MISMATCH, "snapshot was taken from a session of another shape");
+  RG_CUDA(cudaSetDevice(s->opt.device));
+  const size_t dst_pitch = (size_t)s->ctx * hd * es, head_block = (size_t)k->kv_heads * k->row_bytes;
+  for (int l = 0; l < k->n_layers; ++l)
+    for (int kv = 0; kv < 2; ++kv) {
+      uint8_t *dst = static_cast<uint8_t *>(kv ? s->v_cache[(size_t)l] : s->k_cache[(size_t)l]) + (size_t)row * (size_t)k->kv_heads * dst_pitch;
+      const uint8_t *src = k->data + ((size_t)l * 2 + (size_t)kv) * head_block;
+      RG_CUDA(cudaMemcpy2DAsync(dst, dst_pitch, src, k->row_bytes, k->row_bytes, (size_t)k->kv_heads, cudaMemcpyDeviceToDevice, s->stream));
+    }
+  cudaError_t e = x_sync(s->stream);
+  if (e != cudaSuccess) {
+    s->poisoned = true;
+    return fail(RG_POISONED, std::string("stream synchronize: ") + cudaGetErrorString(e));
+  }
+  s->position[(size_t)row] = k->length;  // the row now holds exactly the snapshot's positions
+  return RG_OK;
+}
+
+void rg_b200_kv_snapshot_free(rg_kv_snapshot *k) {
+  if (!k) return;
+  cudaSetDevice(k->device);
+  cudaFree(k->data);
+  delete k;
 }
 
 static int32_t generate_impl(rg_session *s, const int32_t *prompt, size_t n_prompt, size_t max_new, int32_t *out, size_t *n_out,
