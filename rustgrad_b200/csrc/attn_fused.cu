@@ -364,28 +364,18 @@ __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnA
     const int gq = o / (HD / 2), d = 2 * (o - gq * (HD / 2));
     const float *base = column(o);
     float a0 = 0.0f, a1 = 0.0f;
-    int s0 = 0;
-    if (o == tid) {  // spans 0 .. CB-1 are already here, in span order like the rounds below
+    for (int s0 = 0; s0 < nspl; s0 += CB) {  // spans in order; CB independent loads per round
+      if (o != tid || s0 != 0) {             // the first round of the first column is already here
+#pragma unroll
+        for (int j = 0; j < CB; ++j)
+          v0[j] = (s0 + j < nspl) ? __ldcg(reinterpret_cast<const float2 *>(base + (size_t)(s0 + j) * (HD + 2))) : make_float2(0.0f, 0.0f);
+      }
 #pragma unroll
       for (int j = 0; j < CB; ++j)
-        if (j < nspl) {
-          const float wgt = wts[gq * nspl + j];
-          a0 = fmaf(v0[j].x, wgt, a0);
-          a1 = fmaf(v0[j].y, wgt, a1);
-        }
-      s0 = CB;
-    }
-    for (; s0 < nspl; s0 += 20) {
-      float2 v[20];
-#pragma unroll
-      for (int j = 0; j < 20; ++j)
-        v[j] = (s0 + j < nspl) ? __ldcg(reinterpret_cast<const float2 *>(base + (size_t)(s0 + j) * (HD + 2))) : make_float2(0.0f, 0.0f);
-#pragma unroll
-      for (int j = 0; j < 20; ++j)
         if (s0 + j < nspl) {
           const float wgt = wts[gq * nspl + s0 + j];
-          a0 = fmaf(v[j].x, wgt, a0);
-          a1 = fmaf(v[j].y, wgt, a1);
+          a0 = fmaf(v0[j].x, wgt, a0);
+          a1 = fmaf(v0[j].y, wgt, a1);
         }
     }
     float *dst = A.out + (size_t)c * A.heads * HD + (size_t)(kvh * G + gq) * HD + d;
@@ -445,7 +435,12 @@ int fused_attn_max_splits(int ctx, int hd, bool kv_f32, int sm_count, int kv_hea
   const int smax = span_max(hd, kv_f32 ? 4 : 2);
   const int per_head = fused_attn_per_head(sm_count, kv_heads, 1);
   const int by_ctx = (ctx + smax - 1) / smax;
-  return (per_head > by_ctx ? per_head : by_ctx) + 1;
+  // span_for never goes below 64 positions once the context exceeds 64 (and a context of up to 64
+  // has at most four spans of 16), so few kv heads do not mean hundreds of spans
+  int by_floor = (ctx + 63) / 64;
+  if (by_floor < 4) by_floor = 4;
+  const int spread = per_head < by_floor ? per_head : by_floor;
+  return (spread > by_ctx ? spread : by_ctx) + 1;
 }
 
 int fused_attn_split_cap() { return SC_POS / 3; }  // span headers + weights of all heads fit the score buffer

@@ -73,16 +73,24 @@ __global__ void __launch_bounds__(THREADS) tp_allreduce_add_kernel(const TpFused
   const int total = A.cols * row4;
   for (int i = b * THREADS + tid; i < total; i += TP_FUSED_CTAS * THREADS) {
     const int col = i / row4, j = i - col * row4;
+    // all ranks' slices and the residual are requested before the first sum: one NVLink round trip
+    // for the whole exchange instead of one per rank
+    float4 p[TP_FUSED_MAX_WORLD];
+#pragma unroll
+    for (int r = 0; r < TP_FUSED_MAX_WORLD; ++r)
+      if (r < A.world) p[r] = ld_peer(reinterpret_cast<const float4 *>(A.peer_partial[r] + (size_t)col * A.ldp) + j);
+    const float4 resid = *(reinterpret_cast<const float4 *>(A.x + (size_t)col * A.ldx) + j);
     float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    for (int r = 0; r < A.world; ++r) {
-      const float4 p = ld_peer(reinterpret_cast<const float4 *>(A.peer_partial[r] + (size_t)col * A.ldp) + j);
-      sum.x = __fadd_rn(sum.x, p.x);
-      sum.y = __fadd_rn(sum.y, p.y);
-      sum.z = __fadd_rn(sum.z, p.z);
-      sum.w = __fadd_rn(sum.w, p.w);
-    }
+#pragma unroll
+    for (int r = 0; r < TP_FUSED_MAX_WORLD; ++r)
+      if (r < A.world) {  // rank order: every rank computes the identical value
+        sum.x = __fadd_rn(sum.x, p[r].x);
+        sum.y = __fadd_rn(sum.y, p[r].y);
+        sum.z = __fadd_rn(sum.z, p[r].z);
+        sum.w = __fadd_rn(sum.w, p[r].w);
+      }
     float4 *dst = reinterpret_cast<float4 *>(A.x + (size_t)col * A.ldx) + j;
-    float4 v = *dst;
+    float4 v = resid;
     v.x = __fadd_rn(v.x, sum.x);
     v.y = __fadd_rn(v.y, sum.y);
     v.z = __fadd_rn(v.z, sum.z);
