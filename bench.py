@@ -5,6 +5,7 @@
     python bench.py --impl reference ...        # the CPU restatement of the reference path
     python bench.py --workload gemv [--shapes 14336x4096 --types q4_0 --batches 1]   # isolated GEMV sweep
     python bench.py --workload gemm [--shapes 14336x4096 --tokens 2048 --modes 0,2]  # prefill GEMM sweep
+    python bench.py --workload serving [--requests 16 --batch 8 --prompt-tokens 128 --new-tokens 64]  # continuous batching
 
 A step is one greedy decode step (one new token per row) of a seeded synthetic model:
   * N = 1: Llama-3-8B shape, Q4_0 projections, Q8_0 embedding and head, f16 KV cache, batch 1,
@@ -199,9 +200,48 @@ def op_sweep(args):
                                           "tensor_work_frac": fl * (3 if mode == 2 else 1) / ms / 1e9 / tflops}), flush=True)
 
 
+def serving_run(args):
+    """Continuous batching on the 8B shape, one GPU: `requests` prompts that share a prefix arrive
+    at once, `batch` of them run per step; wall-clock tokens/s of the whole job through the
+    scheduler (host tokens in, host tokens out), with and without the prefix cache."""
+    from rustgrad_b200 import serving, session
+    cfg = dict(synth.LLAMA_8B)
+    B = max(1, min(args.batch if args.batch > 1 else 8, 32))
+    target = session.CudaSessionTarget(max_batch=B, max_context=args.prompt_tokens + args.new_tokens + 8)
+    s = session.LlamaCudaPlan.synthetic(cfg, target, seed=6).prepare()
+    shared = synth.prompt_ids(cfg, args.shared_prefix, seed=11).tolist()
+    prompts = [shared + synth.prompt_ids(cfg, args.prompt_tokens - args.shared_prefix, seed=100 + r).tolist()
+               for r in range(args.requests)]
+    for label, entries in (("no prefix cache", 0), ("prefix cache", 64)):
+        sched = serving.LlamaServingScheduler(s, batch_size=B, prefix_max_entries=entries, prefix_max_bytes=8 << 30)
+        if entries:  # the shared prefix is resident before the requests arrive
+            warm = sched.submit_ids(shared, serving.GenerationConfig(1))
+            while sched.pending():
+                sched.step()
+            sched.remove(warm)
+        t0 = time.perf_counter()
+        ids = [sched.submit_ids(p, serving.GenerationConfig(args.new_tokens)) for p in prompts]
+        steps = 0
+        while sched.pending():
+            sched.step()
+            steps += 1
+        dt = time.perf_counter() - t0
+        generated = sum(len(sched.result(i).generated_ids) for i in ids)
+        print(json.dumps({"op": "serving", "config": label, "requests": args.requests, "batch": B,
+                          "prompt_tokens": args.prompt_tokens, "shared_prefix": args.shared_prefix,
+                          "new_tokens": args.new_tokens, "steps": steps, "seconds": dt,
+                          "generated_tokens_per_s": generated / dt,
+                          "prompt_and_generated_tokens_per_s": (generated + args.requests * args.prompt_tokens) / dt,
+                          "prefix": sched.prefix_stats()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemm"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemm", "serving"])
+    ap.add_argument("--requests", type=int, default=16)
+    ap.add_argument("--prompt-tokens", type=int, default=128)
+    ap.add_argument("--new-tokens", type=int, default=64)
+    ap.add_argument("--shared-prefix", type=int, default=96, help="leading prompt tokens every request shares")
     ap.add_argument("--shapes", default="4096x4096,14336x4096,4096x14336,128256x4096")
     ap.add_argument("--types", default="q4_0,q8_0")
     ap.add_argument("--batches", default="1,2,4,8")
@@ -218,6 +258,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1, help="rows decoded together (the headline workload is 1)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.workload == "serving":
+        return serving_run(args)
     if args.workload != "decode":
         return op_sweep(args)
     rank = int(os.environ.get("RANK", "0"))

@@ -645,6 +645,7 @@ static int32_t gemm_tc(rg_session *s, const DevTensor &w, int m, float *out, int
   const int tiles = ((int)w.rows + rows_per_cta - 1) / rows_per_cta;  // CTAs along the weight rows
   int splits = (m <= BMAX && s->split_scratch) ? (2 * s->sm_count) / tiles : 1;
   splits = qgemm_effective_splits(a.k, splits);
+  while (splits > 1 && (size_t)splits * (size_t)m * (size_t)a.n > (size_t)BMAX * 2 * (size_t)s->sm_count * 256) --splits;  // never past the scratch
   if (splits > 1) {
     a.out = s->split_scratch;
     a.ldc = a.n;
@@ -1596,7 +1597,8 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   uint8_t *raw;
   s->xb_ld = std::max(d, std::max(qw, s->ffn_l));
   RG_TRY(dalloc(s.get(), &raw, (size_t)2 * WMAX * s->xb_ld * 2));
-  RG_TRY(dalloc(s.get(), &s->split_scratch, (size_t)BMAX * 2 * s->sm_count * 128));  // splits * rows <= 2 * SMs * 128
+  // splits <= 2 * SMs / tiles and rows <= tiles * rows_per_cta (256 with two row tiles per CTA)
+  RG_TRY(dalloc(s.get(), &s->split_scratch, (size_t)BMAX * 2 * s->sm_count * 256));
   s->gemm_mode = (s->opt.reserved[1] >= 1 && s->opt.reserved[1] <= 3) ? s->opt.reserved[1] - 1 : QGEMM_F16X3;
   s->xb = raw;
   RG_TRY(dalloc(s.get(), &raw, xpack_bytes(d, MAXC)));

@@ -428,3 +428,33 @@ def test_full_size_8b_shape_properties():
     ids_p, _ = d.decode_loop([first], 12)
     assert ids_p[:, 0].tolist() == ids1[:, 0].tolist()
     assert d.report()["kernel_launches"] < b.report()["kernel_launches"]
+
+
+def test_thirty_two_rows_at_full_width_match_one_row():
+    """A decode batch of 32 at the 8B width (2 layers): the K-split tensor-core path has its
+    largest partial-sum footprint here (every projection, 32 tokens); all rows carry the same
+    sequence, so every row must reproduce the one-row session."""
+    cfg = synth.scaled(synth.LLAMA_8B, n_layers=2, max_context=64)
+    prompt = synth.prompt_ids(cfg, 5, seed=3)
+
+    def make(batch):
+        target = session.CudaSessionTarget(max_context=64, max_batch=batch)
+        return session.LlamaCudaPlan.synthetic(cfg, target, seed=6).prepare()
+
+    one = make(1)
+    tok = int(np.argmax(one.prefill_ids(prompt)))
+    want, _ = one.decode([tok], want_logits=True)
+    many = make(32)
+    for r in range(32):
+        many.prefill_ids(prompt, row=r, want_logits=False)
+    got, greedy = many.decode([tok] * 32, want_logits=True)
+    for r in range(32):
+        assert_logits_close(got[r], want[0])
+    assert len(set(greedy.tolist())) == 1
+    # a 32-token prompt remainder after a restored prefix takes the same path (prefill, m = 32)
+    again = make(1)
+    long_prompt = synth.prompt_ids(cfg, 40, seed=4)
+    full = again.prefill_ids(long_prompt)
+    split = make(1)
+    split.prefill_ids(long_prompt[:8], want_logits=False)
+    assert_logits_close(split.prefill_ids(long_prompt[8:]), full)
