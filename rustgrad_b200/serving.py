@@ -185,7 +185,6 @@ class _Request:
     row: Optional[int] = None
     cached: int = 0  # positions of prompt + generated already in the row
     prefix_reference: Optional[tuple] = None
-    logits: Optional[np.ndarray] = None  # logits waiting for a selection (prefix hit on the whole prompt)
     pending_token: Optional[int] = None
     result: Optional[ServingResult] = None
 
