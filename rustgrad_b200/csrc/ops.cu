@@ -585,24 +585,31 @@ __global__ void kquant_gemv_kernel(const uint8_t *w, int rows, int k, const floa
     float wv[8];
     if constexpr (TYPE == RG_TYPE_Q4_K) {
       const int group = lane >> 2;
-      const float d = half_bits_to_float((uint32_t)blk[0] | ((uint32_t)blk[1] << 8));
-      const float dmin = half_bits_to_float((uint32_t)blk[2] | ((uint32_t)blk[3] << 8));
-      const uint8_t *p = blk + 4;
+      // d, dmin and the twelve packed scale bytes as one 16-byte load (blocks are 16-byte aligned)
+      const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+      const float d = half_bits_to_float(hdr.x & 0xffffu);
+      const float dmin = half_bits_to_float(hdr.x >> 16);
+      auto pbyte = [&](int i) -> int {
+        const uint32_t word = i < 4 ? hdr.y : (i < 8 ? hdr.z : hdr.w);
+        return (int)((word >> ((i & 3) * 8)) & 0xffu);
+      };
       int sc, mn;
       if (group < 4) {
-        sc = p[group] & 0x3f;
-        mn = p[4 + group] & 0x3f;
+        sc = pbyte(group) & 0x3f;
+        mn = pbyte(4 + group) & 0x3f;
       } else {
-        sc = (p[4 + group] & 0x0f) | ((p[group - 4] >> 6) << 4);
-        mn = (p[4 + group] >> 4) | ((p[group] >> 6) << 4);
+        sc = (pbyte(4 + group) & 0x0f) | ((pbyte(group - 4) >> 6) << 4);
+        mn = (pbyte(4 + group) >> 4) | ((pbyte(group) >> 6) << 4);
       }
       const float ds = __fmul_rn(d, (float)sc), off = __fmul_rn(dmin, (float)mn);
       const uint2 q8 = *reinterpret_cast<const uint2 *>(blk + 16 + (group >> 1) * 32 + (lane & 3) * 8);  // 8-byte aligned
       const int shift = (group & 1) * 4;
+      // one shift + mask per word leaves each nibble alone in its byte: the conversions then read bytes
+      const uint32_t m0 = (q8.x >> shift) & 0x0F0F0F0Fu, m1 = (q8.y >> shift) & 0x0F0F0F0Fu;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const uint32_t word = j < 4 ? q8.x : q8.y;
-        const int q = (int)((word >> ((j & 3) * 8 + shift)) & 0x0f);
+        const uint32_t word = j < 4 ? m0 : m1;
+        const uint32_t q = (word >> ((j & 3) * 8)) & 0xffu;
         wv[j] = __fsub_rn(__fmul_rn(ds, (float)q), off);
       }
     } else {
@@ -888,7 +895,7 @@ cudaError_t launch_dense_gemv(const DenseGemvArgs &a, const LaunchCfg &cfg) {
                   a.batch, a.epi, a.y, a.ldy);
   if (a.type == RG_TYPE_Q4_K || a.type == RG_TYPE_Q6_K) {
     const bool aligned = (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (a.ldx & 3) == 0 && (a.k & 255) == 0 &&
-                         (a.type == RG_TYPE_Q6_K || (reinterpret_cast<uintptr_t>(a.w) & 7) == 0);
+                         (a.type == RG_TYPE_Q6_K || (reinterpret_cast<uintptr_t>(a.w) & 15) == 0);
     if (!aligned)
       return launch(block_gemv_kernel, grid, block, 0, cfg, a.type, a.w, a.rows, a.k, a.x, a.ldx, a.batch, a.epi, a.y, a.ldy);
     const size_t row_bytes = (size_t)(a.k >> 8) * (a.type == RG_TYPE_Q4_K ? 144 : 210);
