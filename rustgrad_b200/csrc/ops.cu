@@ -540,7 +540,8 @@ __global__ void dense_gemv_kernel(const W *w, int rows, int k, const float *x, i
 
 // K-quant GEMV: one warp per weight row, one 256-element super-block per warp iteration, eight
 // consecutive elements per lane (so a lane decodes its group's 6-bit scale / min or its int8 scale once and
-// reads its quants as whole bytes).  The decoded values are those of decode_element (same f32 steps).
+// reads its quants as whole bytes).  The scale (and, for Q4_K, the minimum) of a lane's group is applied
+// once per super-block to the sum of quant * x (and of x), not per element.
 // STAGED: the CTA's eight rows (contiguous bytes) arrive in shared memory by one TMA bulk copy issued
 // before the grid dependency wait; with one super-block load in flight per warp the direct form
 // keeps under 5 KB per SM in flight and stays near 0.7 TB/s whatever its inner loop does.
@@ -582,7 +583,8 @@ __global__ void kquant_gemv_kernel(const uint8_t *w, int rows, int k, const floa
   for (int b = 0; b < 8; ++b) acc[b] = 0.0f;
   for (int sb = 0; sb < nsb; ++sb) {  // (unrolling by four was measured slower: register pressure)
     const uint8_t *blk = wr + (size_t)sb * BB;
-    float wv[8];
+    float wv[8];          // the lane's eight quants as floats
+    float mul, sub = 0.0f;  // weight = mul * quant - sub, applied to the lane's sums once per super-block
     if constexpr (TYPE == RG_TYPE_Q4_K) {
       const int group = lane >> 2;
       // d, dmin and the twelve packed scale bytes as one 16-byte load (blocks are 16-byte aligned)
@@ -601,7 +603,8 @@ __global__ void kquant_gemv_kernel(const uint8_t *w, int rows, int k, const floa
         sc = (pbyte(4 + group) & 0x0f) | ((pbyte(group - 4) >> 6) << 4);
         mn = (pbyte(4 + group) >> 4) | ((pbyte(group) >> 6) << 4);
       }
-      const float ds = __fmul_rn(d, (float)sc), off = __fmul_rn(dmin, (float)mn);
+      mul = __fmul_rn(d, (float)sc);
+      sub = __fmul_rn(dmin, (float)mn);
       const uint2 q8 = *reinterpret_cast<const uint2 *>(blk + 16 + (group >> 1) * 32 + (lane & 3) * 8);  // 8-byte aligned
       const int shift = (group & 1) * 4;
       // one shift + mask per word leaves each nibble alone in its byte: the conversions then read bytes
@@ -610,7 +613,7 @@ __global__ void kquant_gemv_kernel(const uint8_t *w, int rows, int k, const floa
       for (int j = 0; j < 8; ++j) {
         const uint32_t word = j < 4 ? m0 : m1;
         const uint32_t q = (word >> ((j & 3) * 8)) & 0xffu;
-        wv[j] = __fsub_rn(__fmul_rn(ds, (float)q), off);
+        wv[j] = (float)q;
       }
     } else {
       const int half_index = lane >> 4, l16 = lane & 15;
@@ -618,11 +621,11 @@ __global__ void kquant_gemv_kernel(const uint8_t *w, int rows, int k, const floa
       const uint8_t *lo = blk + half_index * 64 + (l16 & 7) * 8;
       const uint8_t *hi = blk + 128 + half_index * 32 + (l16 & 3) * 8;
       const int low_shift = (l16 >> 3) * 4, high_shift = (l16 >> 2) * 2;
-      const int scale = (int)(int8_t)blk[192 + (lane >> 1)];
+      mul = __fmul_rn(d, (float)(int)(int8_t)blk[192 + (lane >> 1)]);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int quant = (((lo[j] >> low_shift) & 0x0f) | (((hi[j] >> high_shift) & 0x03) << 4)) - 32;
-        wv[j] = __fmul_rn(d, (float)(quant * scale));
+        wv[j] = (float)quant;
       }
     }
     const int e0 = sb * 256 + lane * 8;
@@ -631,8 +634,7 @@ __global__ void kquant_gemv_kernel(const uint8_t *w, int rows, int k, const floa
       if (b >= batch) break;
       const float4 x0 = *reinterpret_cast<const float4 *>(x + (size_t)b * ldx + e0);
       const float4 x1 = *reinterpret_cast<const float4 *>(x + (size_t)b * ldx + e0 + 4);
-      float a = acc[b];
-      a = fmaf(x0.x, wv[0], a);
+      float a = x0.x * wv[0];
       a = fmaf(x0.y, wv[1], a);
       a = fmaf(x0.z, wv[2], a);
       a = fmaf(x0.w, wv[3], a);
@@ -640,7 +642,9 @@ __global__ void kquant_gemv_kernel(const uint8_t *w, int rows, int k, const floa
       a = fmaf(x1.y, wv[5], a);
       a = fmaf(x1.z, wv[6], a);
       a = fmaf(x1.w, wv[7], a);
-      acc[b] = a;
+      float r = fmaf(mul, a, acc[b]);
+      if constexpr (TYPE == RG_TYPE_Q4_K) r = fmaf(-sub, ((x0.x + x0.y) + (x0.z + x0.w)) + ((x1.x + x1.y) + (x1.z + x1.w)), r);
+      acc[b] = r;
     }
   }
 #pragma unroll
