@@ -166,3 +166,32 @@ def test_snapshot_restore_round_trip_and_shape_checks(model):
         snap.restore(other, 0)
     with pytest.raises(session.RgError):
         serving._Snapshot(s, 0, 50)
+
+
+def test_decode_rows_rejections_leave_positions_unchanged(model):
+    import ctypes as C
+    from rustgrad_b200 import _lib
+    cfg, data = model
+    s = make_session(data, max_batch=3, kv_f32=True)
+    L = _lib.load()
+    for r in range(3):
+        s.prefill_ids(synth.prompt_ids(cfg, 4 + r, seed=r), row=r, want_logits=False)
+    before = [s.position(r) for r in range(3)]
+
+    def call(rows, toks):
+        rows, toks = np.array(rows, np.int32), np.array(toks, np.int32)
+        ids = np.empty(len(rows), np.int32)
+        i32 = C.POINTER(C.c_int32)
+        return L.rg_b200_decode_rows(s._h, rows.ctypes.data_as(i32), toks.ctypes.data_as(i32), len(rows), None, None, None,
+                                     ids.ctypes.data_as(i32)), ids
+
+    assert call([0, 0], [1, 1])[0] == 1          # the same row twice: RG_INVALID_ARGUMENT
+    assert call([0, 3], [1, 1])[0] == 1          # row out of range
+    assert call([0, 1], [1, cfg["vocab"]])[0] == 5  # RG_TOKEN_OUT_OF_RANGE
+    assert [s.position(r) for r in range(3)] == before
+    rc, ids = call([2, 0], [1, 2])               # any order, any subset
+    assert rc == 0 and [s.position(r) for r in range(3)] == [before[0] + 1, before[1], before[2] + 1]
+    solo = make_session(data, max_batch=1, kv_f32=True)
+    solo.prefill_ids(synth.prompt_ids(cfg, 6, seed=2), want_logits=False)
+    _, want = solo.decode([1])
+    assert int(ids[0]) == int(want[0])           # column 0 fed row 2, whose prompt had seed 2
