@@ -14,6 +14,10 @@ A step is one greedy decode step (one new token per row) of a seeded synthetic m
 `value` times K replays of the decode graph with the selected token fed back on the device
 (inputs resident in HBM); `e2e` times K calls of the session's decode verb with host tokens in
 and host ids out.  The weights (4.5 GB / 39 GB) are far larger than L2, so every step reads HBM.
+At N > 1 a two-layer model of the 70B width first runs through the tensor-parallel session and is
+compared with the CPU checker and the single-GPU session (`tp_parity`; a mismatch exits non-zero).
+At N = 1 the line also carries the 70B shape on one GPU (`scale_anchor`), the point the N > 1
+lines scale from.
 """
 from __future__ import annotations
 
@@ -120,28 +124,42 @@ class ClockSampler:
                             "samples": len(sm)}
 
 
-def cpu_reference_arm(args, wl, threads):
+def random_blocks(rng, kind, n, k):
+    """Random block bytes with a sane f16 scale: as good as encoded weights for timing."""
+    w = rng.integers(0, 256, (n * k // 32, quant.BLOCK_BYTES[kind]), dtype=np.uint8)
+    w[:, 1] = 0x20
+    return w.reshape(-1)
+
+
+def cpu_reference_arm(args, wl, threads, context):
     """Times the CPU restatement of the reference path on a bounded sample of the workload.
 
     One decode token costs t_head + L * t_layer.  The sample runs the full-width model with 1 and
     with 3 layers and an eighth of the vocabulary rows in embedding and head, takes
     t_layer = (T3 - T1) / 2 and t_head = 8 * (T1 - t_layer), and scales to the model's layer count.
-    Weights come from the host generator (same distribution as the device generator); the context
-    is a 16-token prompt.
+    The decode steps run at the GPU arm's context: the checker's KV cache is filled to `context`
+    positions with seeded values first, so attention reads as many rows as on the GPU.  Weights are
+    random block bytes with a sane scale (the time of the CPU path does not depend on the values).
     """
     from oracle import oracle as O
     cfg = wl["cfg"]
     steps = max(1, min(args.steps, 3))
     vocab_div = 8
-    sub3 = synth.scaled(cfg, n_layers=3, max_context=64, vocab=cfg["vocab"] // vocab_div)
-    tensors3 = synth.build_tensors(sub3, seed=wl["seed"], body_type=wl["body"], embed_type=wl["embed"], head_type=wl["head"],
-                                   tied_head=False)
+    rng = np.random.default_rng(wl["seed"])
+    sub3 = synth.scaled(cfg, n_layers=3, max_context=context + steps + 8, vocab=cfg["vocab"] // vocab_div)
+    tensors3 = {}
+    for name, rows, cols, is_norm in synth.tensor_inventory(sub3, tied_head=False):
+        if is_norm:
+            tensors3[name] = (quant.F32, 1, cols, np.ones(cols, dtype=np.float32).view(np.uint8))
+        else:
+            kind = wl["embed"] if name == "token_embd.weight" else wl["head"] if name == "output.weight" else wl["body"]
+            tensors3[name] = (kind, rows, cols, random_blocks(rng, kind, rows, cols))
     times = {}
     for layers in (1, 3):
         sub = synth.scaled(sub3, n_layers=layers)
         keep = {k: v for k, v in tensors3.items() if not k.startswith("blk.") or int(k.split(".")[1]) < layers}
         m = O.OracleModel(sub, keep, kv_f16=True, threads=threads)
-        m.forward(synth.prompt_ids(sub, 16, seed=1), O.MODE_FAST)
+        m.fill_cache_seeded(context, seed=1)
         m.forward([1], O.MODE_FAST)  # warm-up step
         t0 = time.perf_counter()
         for i in range(steps):
@@ -151,19 +169,12 @@ def cpu_reference_arm(args, wl, threads):
     t_layer = max((times[3] - times[1]) / 2.0, 1e-9)
     t_head = max(times[1] - t_layer, 0.0) * vocab_div
     t_token = t_head + cfg["n_layers"] * t_layer
-    sample = (f"{steps} decode steps each of a 1-layer and a 3-layer full-width model with vocab/{vocab_div} rows, "
-              f"scaled to {cfg['n_layers']} layers and the full vocabulary")
+    sample = (f"{steps} decode steps at context {context} each of a 1-layer and a 3-layer full-width model with "
+              f"vocab/{vocab_div} rows, scaled to {cfg['n_layers']} layers and the full vocabulary")
     return 1.0 / t_token, t_token, sample
 
 
 GGML = {"q4_0": quant.Q4_0, "q8_0": quant.Q8_0}
-
-
-def random_blocks(rng, kind, n, k):
-    """Random block bytes with a sane f16 scale: as good as encoded weights for timing."""
-    w = rng.integers(0, 256, (n * k // 32, quant.BLOCK_BYTES[kind]), dtype=np.uint8)
-    w[:, 1] = 0x20
-    return w.reshape(-1)
 
 
 def op_sweep(args):
@@ -235,6 +246,86 @@ def serving_run(args):
                           "prefix": sched.prefix_stats()}), flush=True)
 
 
+def tp_parity_check(n, rank, local_rank, dist, threads):
+    """Two layers of the 70B width (d 8192, 64 / 8 heads, ffn 28672, Q4_0, a quarter of the
+    vocabulary) through the tensor-parallel session: a 16-token prompt and 4 decode steps.  Rank 0
+    compares its logits with the CPU checker and with the single-GPU session on the same bytes;
+    every rank's greedy ids must equal rank 0's.  Returns the `tp_parity` object (on every rank)."""
+    import torch
+    from rustgrad_b200 import session
+    cfg = synth.scaled(synth.LLAMA_70B, n_layers=2, max_context=64, vocab=32064)
+    box = [session.nccl_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    target = session.CudaSessionTarget(device=local_rank, tp_rank=rank, tp_world=n, nccl_id=box[0], max_context=64)
+    sess = session.LlamaCudaPlan.synthetic(cfg, target, seed=7, body_type=quant.Q4_0, embed_type=quant.Q4_0,
+                                           head_type=quant.Q4_0).prepare()
+    prompt = synth.prompt_ids(cfg, 16, seed=1)
+    logits = [sess.prefill_ids(prompt)]
+    ids = [int(np.argmax(logits[0]))]
+    for _ in range(4):
+        lg, greedy = sess.decode([ids[-1]], want_logits=True)
+        logits.append(lg[0])
+        ids.append(int(greedy[0]))
+    fused = sess.report().get("peer_reduce_launches", 0) > 0
+    sess.close()
+    mine = torch.tensor(ids, dtype=torch.int64, device="cuda")
+    everyone = [torch.empty_like(mine) for _ in range(n)]
+    dist.all_gather(everyone, mine)
+    ids_equal = all(bool((t == everyone[0]).all()) for t in everyone)
+    out = {"world": n, "layers": 2, "width": "llama3_70b", "prompt_tokens": 16, "decode_steps": 4, "ids_equal": ids_equal,
+           "exchange": "peer-memory kernel" if fused else "nccl all-reduce + add"}
+    verdict = torch.zeros(3, dtype=torch.float64, device="cuda")
+    if rank == 0:
+        from oracle import oracle as O
+        single_target = session.CudaSessionTarget(device=local_rank, max_context=64)
+        plan = session.LlamaCudaPlan.synthetic(cfg, single_target, seed=7, body_type=quant.Q4_0, embed_type=quant.Q4_0,
+                                               head_type=quant.Q4_0)
+        tensors = {}
+        for name, rows, cols, is_norm in synth.tensor_inventory(cfg, tied_head=False):
+            tensors[name] = (quant.F32 if is_norm else quant.Q4_0, rows, cols, plan.read_tensor(name))
+        single = plan.prepare()
+        oracle = O.OracleModel(cfg, tensors, kv_f16=True, threads=threads)
+        want = [oracle.forward(prompt, O.MODE_FAST)]
+        one = [single.prefill_ids(prompt)]
+        want_ids = [O.select_greedy(want[0])]
+        for _ in range(4):
+            want.append(oracle.forward([want_ids[-1]], O.MODE_FAST))
+            one.append(single.decode([want_ids[-1]], want_logits=True)[0][0])
+            want_ids.append(O.select_greedy(want[-1]))
+        oracle.close()
+        single.close()
+        got, want, one = np.stack(logits), np.stack(want), np.stack(one)
+        max_abs = float(np.abs(got - want).max())
+        ok = ids == want_ids and max_abs <= 1e-2 and max_abs <= 1e-3 * float(np.abs(want).max()) + 1e-6
+        verdict = torch.tensor([max_abs, float(np.abs(got - one).max()), float(ok)], dtype=torch.float64, device="cuda")
+    dist.broadcast(verdict, src=0)
+    out.update({"max_abs": float(verdict[0]), "max_abs_vs_single_gpu": float(verdict[1]), "bar": "1e-2 abs, 1e-3 of max |logit|",
+                "ids_equal_checker": bool(verdict[2] > 0.5) and ids_equal, "ok": bool(verdict[2] > 0.5) and ids_equal})
+    return out
+
+
+def scale_anchor(args, local_rank):
+    """The 70B shape (all Q4_0, 39 GB) on ONE GPU: decode tokens/s after a 2048-token prefill, the
+    point the tensor-parallel lines at N = 2, 4, 8 scale from."""
+    from rustgrad_b200 import session
+    wl = workload(2)
+    cfg = wl["cfg"]
+    steps = max(8, min(args.steps, 32))
+    target = session.CudaSessionTarget(device=local_rank, max_batch=1)
+    sess = session.LlamaCudaPlan.synthetic(cfg, target, seed=wl["seed"], body_type=wl["body"], embed_type=wl["embed"],
+                                           head_type=wl["head"]).prepare()
+    logits = sess.prefill_ids(synth.prompt_ids(cfg, min(args.prefill, 2048), seed=1))
+    prefill_ms = sess.report()["last_prefill_ms"]
+    ids, _ = sess.decode_loop([int(np.argmax(logits))], 3)
+    ids, gpu_ms = sess.decode_loop([int(ids[-1][0])], steps)
+    sess.close()
+    gemv_bytes, _ = gemv_bytes_per_step(cfg, wl, 1, 1)
+    ms = gpu_ms / steps
+    return {"workload": "llama3_70b_shape_q4_0_decode_b1_tp1", "value": steps / (gpu_ms * 1e-3), "unit": "tokens/s",
+            "ms_per_step": ms, "steps": steps, "prefill_ms": prefill_ms,
+            "step_bytes_over_step_time_gbs": gemv_bytes / (ms * 1e-3) / 1e9}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemm", "serving"])
@@ -255,6 +346,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--prefill", type=int, default=PREFILL)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-tp-parity", action="store_true", help="skip the tensor-parallel parity check at N > 1")
+    ap.add_argument("--no-scale-anchor", action="store_true", help="skip the 70B single-GPU figure at N = 1")
     ap.add_argument("--batch", type=int, default=1, help="rows decoded together (the headline workload is 1)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -270,14 +363,18 @@ def main():
     cfg = wl["cfg"]
     threads = os.cpu_count() or 1
 
+    prefill = min(args.prefill, cfg["max_context"] - 2 * (args.steps + args.warmup) - 80)
+
     if args.impl == "reference":
         if rank != 0:
             return
-        tok_s, t_token, sample = cpu_reference_arm(args, wl, threads)
+        tok_s, t_token, sample = cpu_reference_arm(args, wl, threads, prefill + args.warmup)
         line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": n,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_token * 1e3, "higher_is_better": True,
                 "scaling": "weak" if n == 1 else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": wl["name"], "batch": 1, "context": 16},
+                "config": {"workload": wl["name"], "batch": 1, "prefill_tokens": prefill, "context": prefill + args.warmup,
+                           "kv_cache": "f16", "weights": "Q4_0 body, Q8_0 embedding+head" if n == 1 else "Q4_0",
+                           "parallelism": "host cores"},
                 "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
                 "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
@@ -307,8 +404,15 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    prefill = min(args.prefill, cfg["max_context"] - 2 * (args.steps + args.warmup) - 80)
     B = args.batch
+    parity = None
+    if n > 1 and not args.no_tp_parity:
+        parity = tp_parity_check(n, rank, local_rank, dist, threads)
+        if not parity["ok"]:
+            if rank == 0:
+                print(json.dumps({"tp_parity": parity}))
+            dist.destroy_process_group()
+            raise SystemExit("tensor-parallel parity check failed")
     target = session.CudaSessionTarget(device=local_rank, max_batch=B, tp_rank=rank if n > 1 else 0, tp_world=n, nccl_id=nccl_id)
     plan = session.LlamaCudaPlan.synthetic(cfg, target, seed=wl["seed"], body_type=wl["body"], embed_type=wl["embed"],
                                            head_type=wl["head"])
@@ -348,7 +452,8 @@ def main():
     r3 = sess.report()
 
     # ---- profiling pass: CUDA events between kernel families (serialized, no overlap)
-    prof = sess.decode_profile(tok, 16)
+    prof = sess.decode_profile(tok, 16, in_step=True)   # launch attributes as in the timed step
+    prof_serial = sess.decode_profile(tok, 16)          # every kernel alone, no overlap
     position = sess.position()
 
     t = torch.tensor([gpu_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
@@ -382,11 +487,16 @@ def main():
         "roofline": {"bound": "hbm", "kernel": proj_kernel, "achieved": achieved,
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak if achieved else None,
                      "traffic": gemv_bytes / gemv_launches * NCU_TRAFFIC_OVER_ALGORITHMIC["q4_0"],
-                     "traffic_note": "bytes per average GEMV launch: algorithmic bytes x the dram/algorithmic ratio of the ncu capture",
+                     "traffic_note": ("not measured in this run: algorithmic bytes of the average GEMV launch x the "
+                                      "dram/algorithmic ratio (1.000) of the ncu capture summarised under profiles/"),
                      "launches_per_step": gemv_launches,
                      "algorithmic_bytes_per_step": gemv_bytes, "kernel_ms_per_step": gemv_ms,
+                     "kernel_ms_per_step_serialized": prof_serial["gemv"]["ms_per_step"],
+                     "timing": ("CUDA events around 16 replays of the step's GEMV launches alone, with the dependent-launch "
+                                "edges they have inside the step; `..._serialized` is the same without any overlap"),
                      "step_bytes_over_step_time_gbs": (gemv_bytes / (ms_per_step * 1e-3) / 1e9)},
         "profile_ms_per_step": {k: v["ms_per_step"] for k, v in prof.items()},
+        "profile_ms_per_step_serialized": {k: v["ms_per_step"] for k, v in prof_serial.items()},
     }
     if n > 1:
         # tensor parallel: what the exchange of partial sums costs (the "other" family is the 160 exchanges plus
@@ -397,9 +507,14 @@ def main():
             "exchange_and_other_share": prof["other"]["ms_per_step"] / prof["total"]["ms_per_step"],
             "per_gpu_projection_gbs": achieved,
         }
-    if n == 1 and not args.no_cpu_baseline:
-        tok_s, t_token, sample = cpu_reference_arm(args, wl, threads)
+    if parity is not None:
+        line["tp_parity"] = parity
+    if not args.no_cpu_baseline:
+        tok_s, t_token, sample = cpu_reference_arm(args, wl, threads, prefill + args.warmup)
         line["cpu_baseline"] = {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
+    if n == 1 and B == 1 and not args.no_scale_anchor:
+        sess.close()
+        line["scale_anchor"] = scale_anchor(args, local_rank)
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

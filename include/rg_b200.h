@@ -82,12 +82,11 @@ typedef struct {
   int32_t disable_graph; /* 1: launch decode kernels directly instead of replaying a CUDA graph */
   int32_t disable_pdl;   /* 1: no programmatic dependent launch between kernels */
   int32_t disable_fused_allreduce; /* 1: TP all-reduce through NCCL only */
-  int32_t reserved[8];    /* reserved[0] == 1: never take the fused small-batch decode path nor the
-                           * tensor-core path; reserved[1]: operand mode of the tensor-core path as
-                           * in rg_b200_qgemm, offset by one (0 = default = compensated half,
-                           * 1 = bf16, 2 = half, 3 = compensated half); reserved[2] == 1: batch-1
-                           * decode as one persistent cooperative kernel per step (optional; the
-                           * default is one launch per projection) */
+  int32_t general_path_only; /* 1: never take the fused small-batch decode path nor the tensor-core
+                              * path (every step runs the 3..8-column kernels; used by tests) */
+  int32_t gemm_operand_mode; /* operands of the tensor-core path, as in rg_b200_qgemm offset by one:
+                              * 0 = default = compensated half, 1 = bf16, 2 = half, 3 = compensated half */
+  int32_t reserved[6];       /* must be zero */
 } rg_options;
 
 /* Per-run evidence in the vocabulary of MetalDeviceRunReport
@@ -118,6 +117,17 @@ const char *rg_b200_last_error(void);
  * "memcpy", "launch", "sync") fails; n < 0 disarms.  Stands where rustgrad's mock driver has its
  * fail-after-N knobs (src/cuda.rs:5895-5960).  Never makes the GPU itself fault. */
 int32_t rg_b200_test_fail_after(const char *what, int32_t n);
+/* How many launches of a kernel family this process has made: "qgemv_i8", "qgemv", "qgemm_tc",
+ * "qgemm_tc_wide", "attn_fused", "attn_prefill", "attn_split", "tp_exchange", "kquant_gemv",
+ * "dense_gemv"; UINT64_MAX for an unknown name.  Evidence for tests and reports of which kernel
+ * served a call (the role of MetalDeviceRunReport's dispatch counts, src/runtime/metal/session.rs:145-185). */
+uint64_t rg_b200_launch_count(const char *kernel);
+/* Test hook for the device-side time-out path (bounded waits that end in a status word, the
+ * stand-in for rustgrad's unprovable-completion rule, src/runtime/cuda_graph.rs:542-546): enqueues
+ * on the session's stream one launch of the partial-sum exchange kernel whose peer flag is never
+ * written and whose poll limit is a few thousand polls.  The wait runs out, nothing faults or
+ * hangs, and the session's next step returns RG_TIMEOUT and leaves the session poisoned. */
+int32_t rg_b200_test_expire_device_wait(rg_session *s);
 
 /* ---- GGUF container: replaces read_gguf / GgufFile (src/gguf/mod.rs:166-173,256-384,
  * src/gguf/reader.rs:8-301).  The bytes are borrowed and must outlive the handle. ---- */
@@ -203,6 +213,11 @@ int32_t rg_b200_decode_loop(rg_session *s, const int32_t *first_tokens, int32_t 
  * kernels per step.  Positions are not advanced and nothing is committed. */
 int32_t rg_b200_decode_profile(rg_session *s, const int32_t *first_tokens, int32_t batch, int32_t steps,
                                float out_ms[4], uint64_t out_launches[4]);
+/* The same pass with the launch attributes of the real step: consecutive launches of a family
+ * keep their programmatic dependent-launch edges, so a kernel's weight prefetch overlaps the end
+ * of the kernel before it as it does inside a decode step (src/cuda_profile.rs:15-60). */
+int32_t rg_b200_decode_profile_in_step(rg_session *s, const int32_t *first_tokens, int32_t batch, int32_t steps,
+                                       float out_ms[4], uint64_t out_launches[4]);
 int32_t rg_b200_report(const rg_session *s, rg_report *out);
 /* cudaStream_t the session launches on (for CUDA-event timing by the caller). */
 void *rg_b200_session_stream(const rg_session *s);
@@ -248,7 +263,9 @@ int32_t rg_b200_attention_decode(int32_t device, const float *q, const void *key
  * has no counterpart in rustgrad (whose CUDA layer always draws scratch from its pooled
  * allocator).  All pointers are DEVICE pointers owned by the caller: q [heads, head_dim] f32,
  * caches [kv_heads, ctx, head_dim] (ctx = rows allocated per kv head, of which the first n_pos are
- * used; the new token sits at n_pos - 1), out [heads, head_dim] f32.  The split-context partials
+ * used; the new token sits at n_pos - 1), out [heads, head_dim] f32.  keys_dev and values_dev must
+ * be 16-byte aligned (they are fetched by bulk copies), q_dev and out_dev 4-byte aligned; a pointer
+ * that is not is refused with RG_INVALID_ARGUMENT before anything is launched.  The split-context partials
  * live in a 4 MiB array inside the library image, held by every GPU that loads the library until
  * the process ends; heads * ceil(ctx / 128) * (head_dim + 2) may not exceed 1 048 576 floats, and
  * anything larger is refused with RG_UNSUPPORTED_GEOMETRY.  The call makes no cudaMalloc, cudaFree

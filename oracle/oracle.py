@@ -75,6 +75,7 @@ def lib():
         L.rgo_cache_clear.restype = None
         L.rgo_cache_clear.argtypes = [C.c_void_p]
         L.rgo_cache_len.argtypes = [C.c_void_p]
+        L.rgo_cache_fill_seeded.argtypes = [C.c_void_p, C.c_int, C.c_uint64]
         L.rgo_forward.argtypes = [C.c_void_p, C.c_void_p, i32p, C.c_int, C.c_int, C.c_int, C.c_int, f32p]
         L.rgo_select_greedy.argtypes = [f32p, C.c_int, i32p]
         L.rgo_select_gumbel.argtypes = [f32p, C.c_int, C.c_float, f32p, i32p]
@@ -226,6 +227,12 @@ class OracleModel:
 
     def reset(self):
         lib().rgo_cache_clear(self.cache)
+
+    def fill_cache_seeded(self, n_pos: int, seed: int = 1) -> None:
+        """Timing aid: the cache holds ``n_pos`` positions of seeded pseudo-random K / V rows afterwards."""
+        rc = lib().rgo_cache_fill_seeded(self.cache, n_pos, seed)
+        if rc:
+            raise OracleError(rc, "cache_fill_seeded")
 
     @property
     def position(self) -> int:

@@ -405,6 +405,30 @@ void rgo_cache_destroy(rgo_cache *c) {
   free(c);
 }
 void rgo_cache_clear(rgo_cache *c) { c->len = 0; }
+/* Timing aid (no counterpart in the reference): makes the cache hold `n_pos` positions of seeded
+ * pseudo-random K / V rows, uniform in [-1, 1), so that a decode step can be timed at a long context
+ * without running the prompt through the CPU path first. */
+int rgo_cache_fill_seeded(rgo_cache *c, int n_pos, uint64_t seed) {
+  const rgo_config *cfg = &c->model->cfg;
+  if (n_pos < 0 || n_pos > cfg->max_context) return RGO_ERR_CONTEXT;
+  uint64_t z = seed * 0x9E3779B97F4A7C15ull + 0xD1342543DE82EF95ull;
+  for (int l = 0; l < cfg->n_layers; ++l)
+    for (int h = 0; h < cfg->n_kv_heads; ++h)
+      for (int p = 0; p < n_pos; ++p) {
+        size_t base = ((size_t)h * cfg->max_context + (size_t)p) * cfg->head_dim;
+        for (int i = 0; i < cfg->head_dim; ++i) {
+          z ^= z << 13, z ^= z >> 7, z ^= z << 17; /* xorshift64 */
+          float k = (float)((double)(z >> 40) / 8388608.0 - 1.0);
+          z ^= z << 13, z ^= z >> 7, z ^= z << 17;
+          float v = (float)((double)(z >> 40) / 8388608.0 - 1.0);
+          if (c->kv_f16) k = rgo_f16_to_f32(rgo_f32_to_f16(k)), v = rgo_f16_to_f32(rgo_f32_to_f16(v));
+          c->keys[l][base + i] = k;
+          c->values[l][base + i] = v;
+        }
+      }
+  c->len = n_pos;
+  return RGO_OK;
+}
 int rgo_cache_len(const rgo_cache *c) { return c->len; }
 
 /* ---- primitives of the forward ---- */

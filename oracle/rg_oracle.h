@@ -107,6 +107,8 @@ rgo_cache *rgo_cache_create(const rgo_model *model, int kv_f16);
 void rgo_cache_destroy(rgo_cache *cache);
 void rgo_cache_clear(rgo_cache *cache);
 int rgo_cache_len(const rgo_cache *cache);
+/* Timing aid: `n_pos` positions of seeded pseudo-random K / V rows; the cache length becomes n_pos. */
+int rgo_cache_fill_seeded(rgo_cache *cache, int n_pos, uint64_t seed);
 
 /* src/models/transformer/model.rs:909-921 -> plan_with_past :740-836 -> execute_all :959-1064.
  * logits: [n_tokens, vocab] (all rows) when all_logits != 0, else [vocab] (last row). */

@@ -165,3 +165,24 @@ class SimpleTokenizer:
                 raise TokenizerError("UnknownTokenId", token_id)
             raw += self.tok2bytes[token_id]
         return bytes(raw).decode("utf-8", errors="replace")
+
+
+def stop_ids_from_gguf_metadata(tokens, token_types, eos_key=None, eot_key=None):
+    """The stop ids a model configuration takes from its tokenizer (mod.rs:284-296, read by
+    LlamaModelConfig::from_gguf, model.rs:288-292): eos is the `tokenizer.ggml.eos_token_id` value
+    or 0; eot is the `tokenizer.ggml.eot_token_id` value, else the id of the LAST special token
+    (type other than 1) spelled <|im_end|>, else none; every configured id must index the
+    vocabulary.  Returns (eos, eot or None); raises TokenizerError("ConfiguredTokenIdOutOfRange")."""
+    count = len(tokens)
+    eos = 0 if eos_key is None else eos_key
+    eot = eot_key
+    if eot is None:
+        for token_id in range(count - 1, -1, -1):
+            if token_types[token_id] != 1 and tokens[token_id] == "<|im_end|>":
+                eot = token_id
+                break
+    if eos >= count:
+        raise TokenizerError("ConfiguredTokenIdOutOfRange", "eos", eos, count)
+    if eot is not None and eot >= count:
+        raise TokenizerError("ConfiguredTokenIdOutOfRange", "eot", eot, count)
+    return eos, eot

@@ -23,7 +23,8 @@ class Options(C.Structure):
     _fields_ = [
         ("device", C.c_int32), ("max_batch", C.c_int32), ("max_context", C.c_int32), ("kv_f32", C.c_int32),
         ("tp_rank", C.c_int32), ("tp_world", C.c_int32), ("nccl_id", C.c_uint8 * 128), ("disable_graph", C.c_int32),
-        ("disable_pdl", C.c_int32), ("disable_fused_allreduce", C.c_int32), ("reserved", C.c_int32 * 8),
+        ("disable_pdl", C.c_int32), ("disable_fused_allreduce", C.c_int32), ("general_path_only", C.c_int32),
+        ("gemm_operand_mode", C.c_int32), ("reserved", C.c_int32 * 6),
     ]
 
 
@@ -37,12 +38,12 @@ class Report(C.Structure):
 
 
 EXPORTS = [
-    "rg_b200_version", "rg_b200_status_string", "rg_b200_last_error", "rg_b200_test_fail_after", "rg_b200_gguf_open",
+    "rg_b200_version", "rg_b200_status_string", "rg_b200_last_error", "rg_b200_test_fail_after", "rg_b200_test_expire_device_wait", "rg_b200_launch_count", "rg_b200_gguf_open",
     "rg_b200_gguf_close", "rg_b200_gguf_tensor_count", "rg_b200_gguf_tensor_info", "rg_b200_gguf_llama_config",
     "rg_b200_plan_create", "rg_b200_plan_add_tensor", "rg_b200_plan_from_gguf", "rg_b200_plan_synth_tensor",
     "rg_b200_plan_tensor_nbytes", "rg_b200_plan_read_tensor", "rg_b200_plan_destroy", "rg_b200_session_prepare",
     "rg_b200_session_destroy", "rg_b200_position", "rg_b200_max_context", "rg_b200_vocab_size", "rg_b200_is_full",
-    "rg_b200_reset_sequence", "rg_b200_prefill", "rg_b200_decode", "rg_b200_generate_greedy", "rg_b200_decode_sampled", "rg_b200_generate_sampled", "rg_b200_decode_loop", "rg_b200_decode_profile",
+    "rg_b200_reset_sequence", "rg_b200_prefill", "rg_b200_decode", "rg_b200_generate_greedy", "rg_b200_decode_sampled", "rg_b200_generate_sampled", "rg_b200_decode_loop", "rg_b200_decode_profile", "rg_b200_decode_profile_in_step",
     "rg_b200_report", "rg_b200_session_stream", "rg_b200_nccl_unique_id", "rg_b200_dequantize", "rg_b200_qmatmul",
     "rg_b200_row_gather", "rg_b200_qmatmul_bench", "rg_b200_qgemm", "rg_b200_attention_decode", "rg_b200_attention_decode_noalloc",
     "rg_b200_reset_row", "rg_b200_prefill_select", "rg_b200_decode_rows", "rg_b200_select", "rg_b200_kv_snapshot_create",
@@ -72,6 +73,9 @@ def load() -> C.CDLL:
     L.rg_b200_status_string.argtypes = [C.c_int32]
     L.rg_b200_last_error.restype = C.c_char_p
     L.rg_b200_test_fail_after.argtypes = [C.c_char_p, C.c_int32]
+    L.rg_b200_test_expire_device_wait.argtypes = [vp]
+    L.rg_b200_launch_count.restype = C.c_uint64
+    L.rg_b200_launch_count.argtypes = [C.c_char_p]
     L.rg_b200_gguf_open.argtypes = [u8p, C.c_size_t, C.POINTER(vp)]
     L.rg_b200_gguf_close.restype = None
     L.rg_b200_gguf_close.argtypes = [vp]
@@ -103,6 +107,7 @@ def load() -> C.CDLL:
     L.rg_b200_generate_sampled.argtypes = [vp, i32p, C.c_size_t, C.c_size_t, C.c_float, f32p, i32p, C.POINTER(C.c_size_t), i32p]
     L.rg_b200_decode_loop.argtypes = [vp, i32p, C.c_int32, C.c_int32, i32p, f32p]
     L.rg_b200_decode_profile.argtypes = [vp, i32p, C.c_int32, C.c_int32, f32p, C.POINTER(C.c_uint64)]
+    L.rg_b200_decode_profile_in_step.argtypes = [vp, i32p, C.c_int32, C.c_int32, f32p, C.POINTER(C.c_uint64)]
     L.rg_b200_report.argtypes = [vp, C.POINTER(Report)]
     L.rg_b200_session_stream.restype = vp
     L.rg_b200_session_stream.argtypes = [vp]

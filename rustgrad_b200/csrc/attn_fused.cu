@@ -389,14 +389,15 @@ cudaError_t launch_t(const FusedAttnArgs &a, const LaunchCfg &cfg) {
   auto kernel = attn_fused_kernel<KV, HD, G>;
   constexpr size_t smem = STAGE_BYTES + (MAX_G * HD + SC_POS * MAX_G + 2 * MAX_G) * sizeof(float);
   static_assert(span_max(HD, (int)sizeof(KV)) <= SC_POS, "score buffer");
-  static bool attr_done = false;
-  if (!attr_done) {
+  static DeviceOnce attr_once;  // per instantiation and device
+  bool *attr_flag = attr_once.slot();
+  if (!attr_flag || !*attr_flag) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     // same shared-memory / L1 split as the GEMV kernels on either side: no reconfiguration between launches
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
-    attr_done = true;
+    if (attr_flag) *attr_flag = true;
   }
   const int sms = cfg.sm_count > 0 ? cfg.sm_count : 148;
   const int per_head = fused_attn_per_head(sms, a.kv_heads, a.cols);
@@ -452,6 +453,7 @@ bool fused_attention_supported(int heads, int kv_heads, int hd) {
 }
 
 cudaError_t launch_attention_fused(const FusedAttnArgs &a, const LaunchCfg &cfg) {
+  count_launch(LC_ATTN_FUSED);
   if (!fused_attention_supported(a.heads, a.kv_heads, a.hd) || a.cols < 1 || !a.counters || !a.scratch || !a.out ||
       a.max_splits > fused_attn_split_cap())
     return cudaErrorInvalidValue;

@@ -207,11 +207,12 @@ template <typename KV, int G>
 cudaError_t launch_t(const PrefillAttnArgs &a, const LaunchCfg &cfg) {
   auto kernel = attn_prefill_kernel<KV, G>;
   constexpr size_t smem = (size_t)(ROWS * QS_LD + HD * TK + ROWS * PS_LD) * sizeof(float) + (size_t)TK * HD * sizeof(KV);
-  static bool attr_done = false;
-  if (!attr_done) {
+  static DeviceOnce attr_once;  // per instantiation and device
+  bool *attr_flag = attr_once.slot();
+  if (!attr_flag || !*attr_flag) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    attr_done = true;
+    if (attr_flag) *attr_flag = true;
   }
   constexpr int TQ = ROWS / G;
   cudaLaunchConfig_t lc{};
@@ -247,6 +248,7 @@ bool prefill_attention_supported(int heads, int kv_heads, int hd) {
 }
 
 cudaError_t launch_attention_prefill(const PrefillAttnArgs &a, const LaunchCfg &cfg) {
+  count_launch(LC_ATTN_PREFILL);
   if (!prefill_attention_supported(a.heads, a.kv_heads, HD) || !a.q || !a.k_cache || !a.v_cache || !a.out || a.cols < 1 ||
       a.pos0 < 0 || a.pos0 + a.cols > a.ctx)
     return cudaErrorInvalidValue;

@@ -311,13 +311,16 @@ int32_t gguf_llama_config(const Gguf &g, rg_llama_config *out, std::string *err)
     *err = "unsupported architecture " + arch->s;
     return RG_UNSUPPORTED_VARIANT;
   }
+  // the tokenizer is built first and supplies the stop ids (model.rs:133; mod.rs:284-296)
+  int32_t stop_eos = 0, stop_eot = -1;
+  int32_t rc;
+  if ((rc = gguf_tokenizer_stop_ids(g, &stop_eos, &stop_eot, err))) return rc;
   const GgufValue *tokens = find(g, "tokenizer.ggml.tokens");
   if (!tokens || tokens->type != 9 || tokens->elem_type != 8) {
     *err = "missing metadata tokenizer.ggml.tokens";
     return RG_MISSING_METADATA;
   }
   int64_t layers, d, ffn, heads, kv, ctx;
-  int32_t rc;
   const std::string p = "llama.";
   if ((rc = req_usize(g, p + "block_count", &layers, err))) return rc;
   if ((rc = req_usize(g, p + "embedding_length", &d, err))) return rc;
@@ -380,12 +383,8 @@ int32_t gguf_llama_config(const Gguf &g, rg_llama_config *out, std::string *err)
   out->max_context = (int32_t)ctx;
   out->norm_eps = (float)eps;
   out->rope_theta = theta;
-  out->eos_id = -1;
-  out->eot_id = -1;
-  if (const GgufValue *v = find(g, "tokenizer.ggml.eos_token_id"))
-    if (is_int(*v)) out->eos_id = (int32_t)v->u;
-  if (const GgufValue *v = find(g, "tokenizer.ggml.eot_token_id"))
-    if (is_int(*v)) out->eot_id = (int32_t)v->u;
+  out->eos_id = stop_eos;
+  out->eot_id = stop_eot;
   return RG_OK;
 }
 

@@ -47,6 +47,9 @@ int32_t gguf_parse(const uint8_t *bytes, size_t len, Gguf *out, std::string *err
 // LlamaModelConfig::from_gguf (src/models/transformer/model.rs:126-298).
 int32_t gguf_llama_config(const Gguf &g, rg_llama_config *out, std::string *err);
 
+// Stop ids as the reference's tokenizer derives them from the same file (tokenizer.cc).
+int32_t gguf_tokenizer_stop_ids(const Gguf &g, int32_t *eos, int32_t *eot, std::string *why);
+
 // (block elements, block bytes) of a ggml type on this path; 0 when unsupported.
 int block_elements(int32_t ggml_type);
 int block_bytes(int32_t ggml_type);

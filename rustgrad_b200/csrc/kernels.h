@@ -14,6 +14,24 @@ struct LaunchCfg {
   int *status = nullptr;  // device status word (see rg_device.cuh)
 };
 
+// cudaFuncSetAttribute applies to the current device only: a launcher keeps one flag per device
+// ordinal so that a process driving sessions on several GPUs prepares its kernels on each of them.
+struct DeviceOnce {
+  bool done[64] = {};
+  bool *slot() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;  // unknown device: set every time
+    return &done[dev];
+  }
+};
+
+// Launch counters per kernel family (process-wide), so a test can prove which kernel served a call.
+enum LaunchCounter {
+  LC_QGEMV_I8 = 0, LC_QGEMV, LC_QGEMM_TC, LC_QGEMM_TC_WIDE, LC_ATTN_FUSED, LC_ATTN_PREFILL, LC_ATTN_SPLIT, LC_TP_EXCHANGE,
+  LC_KQUANT_GEMV, LC_DENSE_GEMV, LC_COUNT
+};
+void count_launch(int which);
+
 enum GemvEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2 };
 
 // y = x . W^T for packed W given as up to three row segments that share K (virtual rows are the
@@ -99,57 +117,6 @@ cudaError_t launch_rmsnorm16(const float *x, int ldx, const float *w, int d, flo
                              const LaunchCfg &cfg);
 cudaError_t launch_swiglu16(const float *g, const float *u, int n, int ld, int rows, const Operand16 &y, const LaunchCfg &cfg);
 
-// ---- Whole-step persistent decode kernel (batch 1, one GPU): decode_mega.cu -------------------
-enum MegaKind { MEGA_EMBED = 0, MEGA_GEMV = 1, MEGA_ATTN = 2, MEGA_FINISH = 3 };
-enum { MEGA_OP_LOGITS = 1 };  // MegaOp::flags: the rows are logits (track arg-max candidates)
-// One phase of the step.  Phases run in order with a grid barrier between them.
-struct MegaOp {
-  int32_t kind = MEGA_GEMV;
-  int32_t type = 0;  // GEMV: RG_TYPE_Q4_0 or RG_TYPE_Q8_0
-  int32_t epi = EPI_STORE;
-  int32_t nseg = 1;
-  int32_t seg_rows[3] = {0, 0, 0};
-  int32_t n_rows = 0;  // virtual rows (EPI_SWIGLU: rows of the gate matrix)
-  int32_t kb = 0;      // K / 32
-  int32_t map0 = 0;    // index of the first of three tensor maps
-  int32_t layer = 0;   // MEGA_ATTN: which KV cache
-  int32_t flags = 0;
-  const float *x = nullptr;       // GEMV input vector (f32, written by an earlier phase)
-  const float *norm_w = nullptr;  // RMSNorm weight applied while packing x; nullptr = none
-  float *y = nullptr;             // GEMV output vector
-};
-struct MegaParams {
-  const MegaOp *ops = nullptr;  // device array
-  int n_ops = 0;
-  const void *maps = nullptr;  // device array of tensor maps, 128 bytes each
-  int32_t *tokens = nullptr, *pos = nullptr;
-  const int32_t *seq = nullptr;
-  int32_t *step = nullptr, *history = nullptr, *d_ids = nullptr;
-  unsigned *bar_counter = nullptr, *bar_base = nullptr;
-  int *gdead = nullptr;  // set by the first CTA whose wait gave up
-  int *status = nullptr;
-  int d_model = 0, heads = 0, kv_heads = 0, ctx = 0;
-  float eps = 0.0f;
-  const float *cos_t = nullptr, *sin_t = nullptr;
-  void *const *k_cache = nullptr;  // device arrays of per-layer cache pointers
-  void *const *v_cache = nullptr;
-  float *qkv = nullptr, *attn_out = nullptr, *attn_scratch = nullptr;
-  unsigned *attn_counters = nullptr;  // [kv_heads], zero between phases
-  int max_splits = 0;
-  float *cand_val = nullptr;  // [grid] arg-max candidates
-  int *cand_idx = nullptr, *cand_bad = nullptr;
-  const uint8_t *embed = nullptr;
-  int embed_type = 0;
-  float *x = nullptr;
-  int u_bytes = 0, slots = 0, advance = 0;
-  unsigned long long *prof = nullptr;  // nullable: [gemv, attention, other, barrier] ns of CTA 0
-};
-size_t mega_tensor_map_bytes();
-cudaError_t mega_make_map(void *map_out, int type, const uint8_t *w, int rows, int k);
-bool mega_plan_smem(int max_k, int *u_bytes, int *slots, size_t *smem);
-int mega_max_splits(int ctx, int grid, int kv_heads, bool kv_f32);
-cudaError_t launch_decode_mega(const MegaParams &P, bool kv_f32, size_t smem, int grid, cudaStream_t stream);
-
 // ---- Tensor-parallel partial sum + residual add over peer memory (tp_fused.cu) -----------------
 constexpr int TP_FUSED_CTAS = 16;
 constexpr int TP_FUSED_MAX_WORLD = 8;
@@ -163,6 +130,7 @@ struct TpFusedArgs {
   unsigned *const *peer_flags = nullptr;  // device array [world]: flag storage of every rank
   unsigned *epochs = nullptr;             // local, [2][TP_FUSED_CTAS], zero at start
   int rank = 0, world = 1, buffer = 0;
+  unsigned poll_limit = 1u << 22;  // polls of a flag word before the wait gives up with DEV_TIMEOUT
 };
 cudaError_t launch_tp_allreduce_add(const TpFusedArgs &a, const LaunchCfg &cfg);
 

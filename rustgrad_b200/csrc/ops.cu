@@ -840,11 +840,12 @@ template <typename KV, int G, int HD>
 static cudaError_t launch_attn_t(const AttnArgs &a, const LaunchCfg &cfg, int splits) {
   constexpr size_t smem = 2 * (size_t)ATTN_SPAN * HD * sizeof(KV);
   auto kernel = attn_split_kernel<KV, G, HD>;
-  static bool attr_done = false;  // per instantiation
-  if (!attr_done) {
+  static DeviceOnce attr_once;  // per instantiation and device
+  bool *attr_flag = attr_once.slot();
+  if (!attr_flag || !*attr_flag) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    attr_done = true;
+    if (attr_flag) *attr_flag = true;
   }
   return launch(kernel, dim3(splits, a.kv_heads, a.cols), dim3(ATT_THREADS), smem, cfg, a.q, static_cast<const KV *>(a.k_cache),
                 static_cast<const KV *>(a.v_cache), a.heads, a.kv_heads, a.ctx, a.col_seq, a.col_pos, a.scratch, splits,
@@ -866,6 +867,7 @@ bool attention_supported(int heads, int kv_heads, int hd) {
   return (hd == 64 || hd == 128) && (g == 1 || g == 2 || g == 4 || g == 8);
 }
 cudaError_t launch_attention(const AttnArgs &a, const LaunchCfg &cfg) {
+  count_launch(LC_ATTN_SPLIT);
   if (!attention_supported(a.heads, a.kv_heads, a.hd)) return cudaErrorInvalidValue;
   const int splits = (a.ctx + ATTN_SPAN - 1) / ATTN_SPAN;
   cudaError_t e;
@@ -891,6 +893,7 @@ cudaError_t launch_advance(const int32_t *ids, int32_t *tokens, int32_t *pos, in
 cudaError_t launch_dense_gemv(const DenseGemvArgs &a, const LaunchCfg &cfg) {
   if (a.batch < 1 || a.batch > 8 || a.epi == EPI_SWIGLU) return cudaErrorInvalidValue;
   const dim3 grid((a.rows + 7) / 8), block(256);
+  if (a.type == RG_TYPE_F32 || a.type == RG_TYPE_F16) count_launch(LC_DENSE_GEMV);
   if (a.type == RG_TYPE_F32)
     return launch(dense_gemv_kernel<float>, grid, block, 0, cfg, reinterpret_cast<const float *>(a.w), a.rows, a.k, a.x, a.ldx,
                   a.batch, a.epi, a.y, a.ldy);
@@ -898,6 +901,7 @@ cudaError_t launch_dense_gemv(const DenseGemvArgs &a, const LaunchCfg &cfg) {
     return launch(dense_gemv_kernel<__half>, grid, block, 0, cfg, reinterpret_cast<const __half *>(a.w), a.rows, a.k, a.x, a.ldx,
                   a.batch, a.epi, a.y, a.ldy);
   if (a.type == RG_TYPE_Q4_K || a.type == RG_TYPE_Q6_K) {
+    count_launch(LC_KQUANT_GEMV);
     const bool aligned = (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (a.ldx & 3) == 0 && (a.k & 255) == 0 &&
                          (a.type == RG_TYPE_Q6_K || (reinterpret_cast<uintptr_t>(a.w) & 15) == 0);
     if (!aligned)
@@ -907,12 +911,13 @@ cudaError_t launch_dense_gemv(const DenseGemvArgs &a, const LaunchCfg &cfg) {
     if (row_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15) == 0 && stage <= 72 * 1024) {
       auto k4 = kquant_gemv_kernel<RG_TYPE_Q4_K, true>;
       auto k6 = kquant_gemv_kernel<RG_TYPE_Q6_K, true>;
-      static bool attr_done = false;
-      if (!attr_done) {
+      static DeviceOnce attr_once;  // per instantiation and device
+      bool *attr_flag = attr_once.slot();
+      if (!attr_flag || !*attr_flag) {
         cudaError_t e = cudaFuncSetAttribute(k4, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(k6, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
         if (e != cudaSuccess) return e;
-        attr_done = true;
+        if (attr_flag) *attr_flag = true;
       }
       if (a.type == RG_TYPE_Q4_K)
         return launch(k4, grid, block, stage, cfg, a.w, a.rows, a.k, a.x, a.ldx, a.batch, a.epi, a.y, a.ldy, cfg.status);
@@ -1021,6 +1026,13 @@ extern "C" int32_t rg_b200_attention_decode_noalloc(const float *q_dev, const vo
     return status;
   };
   if (!q_dev || !keys_dev || !values_dev || !out_dev) return fail(RG_INVALID_ARGUMENT, "null device pointer");
+  // the K / V spans travel by bulk copies, which need 16-byte aligned global addresses (every row is a
+  // multiple of 16 bytes); q and out are read and written as f32 words.  A pointer cut from the middle
+  // of an arena is refused here rather than left to fault on the device.
+  if ((reinterpret_cast<uintptr_t>(keys_dev) & 15) || (reinterpret_cast<uintptr_t>(values_dev) & 15))
+    return fail(RG_INVALID_ARGUMENT, "keys_dev and values_dev must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(q_dev) & 3) || (reinterpret_cast<uintptr_t>(out_dev) & 3))
+    return fail(RG_INVALID_ARGUMENT, "q_dev and out_dev must be 4-byte aligned");
   if (n_pos < 1 || ctx < n_pos) return fail(RG_INVALID_ARGUMENT, "need 1 <= n_pos <= ctx");
   if (heads < 1 || kv_heads < 1 || !attention_supported(heads, kv_heads, head_dim))
     return fail(RG_UNSUPPORTED_GEOMETRY, "head_dim must be 64 or 128 and query heads per kv head 1, 2, 4 or 8");

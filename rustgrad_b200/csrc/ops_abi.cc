@@ -12,10 +12,26 @@
 #include "gguf.h"
 #include "kernels.h"
 
+#include <atomic>
+
 namespace rg {
 extern thread_local std::string g_last_error;
+
+static std::atomic<uint64_t> g_launch_counts[LC_COUNT];
+void count_launch(int which) {
+  if (which >= 0 && which < LC_COUNT) g_launch_counts[which].fetch_add(1, std::memory_order_relaxed);
 }
+}  // namespace rg
 using namespace rg;
+
+extern "C" uint64_t rg_b200_launch_count(const char *kernel) {
+  static const char *names[LC_COUNT] = {"qgemv_i8", "qgemv", "qgemm_tc", "qgemm_tc_wide", "attn_fused", "attn_prefill",
+                                        "attn_split", "tp_exchange", "kquant_gemv", "dense_gemv"};
+  if (!kernel) return 0;
+  for (int i = 0; i < LC_COUNT; ++i)
+    if (!strcmp(kernel, names[i])) return g_launch_counts[i].load(std::memory_order_relaxed);
+  return ~0ull;
+}
 
 namespace {
 

@@ -496,11 +496,12 @@ cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
   constexpr size_t smem = 1024 + NS * NPL * (TN * KSTEP * 2) + RAW_NS * RT * TM * RAW_ROW + (3 * NS + 2 * RAW_NS + 1) * 8 + 16;
   static_assert(smem <= 227 * 1024, "tile configuration exceeds the shared memory of one SM");
   auto kernel = qgemm_tc_kernel<QT, TN, MODE, RT>;
-  static bool attr_done = false;  // per instantiation
-  if (!attr_done) {
+  static DeviceOnce attr_once;  // per instantiation and device
+  bool *attr_flag = attr_once.slot();
+  if (!attr_flag || !*attr_flag) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    attr_done = true;
+    if (attr_flag) *attr_flag = true;
   }
   cudaLaunchConfig_t lc{};
   lc.gridDim = dim3((unsigned)((a.n + TM * RT - 1) / (TM * RT)), (unsigned)((a.m + TN - 1) / TN), (unsigned)splits);
@@ -663,6 +664,7 @@ cudaError_t launch_qgemm_tc(const QGemmArgs &a, const LaunchCfg &cfg) {
   if (a.mode == QGEMM_F16X3 && (!a.x16_lo || (reinterpret_cast<uintptr_t>(a.x16_lo) & 15))) return cudaErrorInvalidValue;
   if (a.mode < QGEMM_BF16 || a.mode > QGEMM_F16X3) return cudaErrorInvalidValue;
   if (qgemm_tc_wide_applies(a)) return launch_qgemm_tc_wide(a, cfg);  // more than 256 tokens, one operand plane
+  count_launch(LC_QGEMM_TC);
   if (a.type == RG_TYPE_Q4_0) return launch_m<RG_TYPE_Q4_0>(a, cfg);
   if (a.type == RG_TYPE_Q8_0) return launch_m<RG_TYPE_Q8_0>(a, cfg);
   return cudaErrorInvalidValue;

@@ -399,11 +399,12 @@ cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
       1024 + NS * NPL * (A_BYTES + TN * KSTEP * 2) + RAW_NS * TM * RAW_ROW + (3 * NS + 2 * RAW_NS + 1) * 8 + 16;
   static_assert(smem <= 227 * 1024, "tile configuration exceeds the shared memory of one SM");
   auto kernel = qgemm_tc_kernel<QT, TN, MODE>;
-  static bool attr_done = false;  // per instantiation
-  if (!attr_done) {
+  static DeviceOnce attr_once;  // per instantiation and device
+  bool *attr_flag = attr_once.slot();
+  if (!attr_flag || !*attr_flag) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    attr_done = true;
+    if (attr_flag) *attr_flag = true;
   }
   cudaLaunchConfig_t lc{};
   lc.gridDim = dim3((unsigned)((a.n + TM - 1) / TM), (unsigned)((a.m + TN - 1) / TN), (unsigned)splits);
@@ -429,6 +430,7 @@ bool qgemm_tc_wide_applies(const QGemmArgs &a) {
 
 cudaError_t launch_qgemm_tc_wide(const QGemmArgs &a, const LaunchCfg &cfg) {
   if (!qgemm_tc_wide_applies(a)) return cudaErrorInvalidValue;
+  count_launch(LC_QGEMM_TC_WIDE);
   return a.mode == QGEMM_BF16 ? launch_t<RG_TYPE_Q4_0, 512, QGEMM_BF16>(a, cfg) : launch_t<RG_TYPE_Q4_0, 512, QGEMM_F16>(a, cfg);
 }
 

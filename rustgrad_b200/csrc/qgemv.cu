@@ -464,11 +464,12 @@ cudaError_t launch_t(const GemvArgs &a, const LaunchCfg &cfg) {
   }
 
   auto kernel = qgemv_kernel<QT, NT, EPI>;
-  static bool attr_done = false;  // per instantiation
-  if (!attr_done) {
+  static DeviceOnce attr_once;  // per instantiation and device
+  bool *attr_flag = attr_once.slot();
+  if (!attr_flag || !*attr_flag) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
     if (e != cudaSuccess) return e;
-    attr_done = true;
+    if (attr_flag) *attr_flag = true;
   }
   cudaLaunchConfig_t lc{};
   lc.gridDim = dim3((unsigned)grid);
@@ -498,6 +499,7 @@ cudaError_t launch_e(const GemvArgs &a, const LaunchCfg &cfg) {
 size_t xpack_bytes(int k, int batch) { return (size_t)((k + 31) / 32 * 32) * (size_t)batch * 4; }
 
 cudaError_t launch_qgemv(const GemvArgs &a, const LaunchCfg &cfg) {
+  count_launch(LC_QGEMV);
   if (a.k <= 0 || a.k % 256 || a.batch < 1 || a.batch > 8 || a.nseg < 1 || a.nseg > 3) return cudaErrorInvalidValue;
   if (a.epi == EPI_SWIGLU && (a.nseg != 2 || a.seg_rows[0] != a.seg_rows[1])) return cudaErrorInvalidValue;
   for (int i = 0; i + 1 < a.nseg; ++i)

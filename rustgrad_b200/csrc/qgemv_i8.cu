@@ -692,13 +692,14 @@ cudaError_t launch_t(const GemvI8Args &a, const LaunchCfg &cfg) {
     if (e != cudaSuccess) return e;
   }
   auto kernel = qgemv_i8_kernel<QT, EPI, B1>;
-  static bool attr_done = false;  // per instantiation
-  if (!attr_done) {
+  static DeviceOnce attr_once;  // per instantiation and device
+  bool *attr_flag = attr_once.slot();
+  if (!attr_flag || !*attr_flag) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_FULL);
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
-    attr_done = true;
+    if (attr_flag) *attr_flag = true;
   }
   cudaLaunchConfig_t lc{};
   lc.gridDim = dim3((unsigned)grid);
@@ -733,6 +734,7 @@ bool qgemv_i8_supported(int k, int batch) {
 
 cudaError_t launch_qgemv_i8(const GemvI8Args &a, const LaunchCfg &cfg) {
   if (!qgemv_i8_supported(a.k, a.batch) || a.nseg < 1 || a.nseg > 3 || !a.x || !a.y) return cudaErrorInvalidValue;
+  count_launch(LC_QGEMV_I8);
   if (a.epi == EPI_SWIGLU && (a.nseg != 2 || a.seg_rows[0] != a.seg_rows[1])) return cudaErrorInvalidValue;
   for (int i = 0; i + 1 < a.nseg; ++i)
     if (a.epi != EPI_SWIGLU && a.seg_rows[i] % BOXR) return cudaErrorInvalidValue;

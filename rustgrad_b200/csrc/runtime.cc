@@ -294,11 +294,6 @@ struct rg_session {
   // one-launch decode attention (attn_fused.cu): arrival counters per (column, kv head); null = not used
   unsigned *attn_counters = nullptr;
   int attn_max_splits = 0;
-  // whole-step persistent kernel for batch-1 decode on one GPU (decode_mega.cu)
-  bool mega_ok = false;
-  MegaParams mega;
-  size_t mega_smem = 0;
-  int mega_phases = 0;
 
   ~rg_session() {
     for (auto &g : graphs) cudaGraphExecDestroy(g.second);
@@ -417,7 +412,10 @@ static int32_t tp_reduce_add(rg_session *s, int ncols, int which) {
   std::string err;
   prof_mark(s, PROF_OTHER);
   if (!(s->family_mask & (1u << PROF_OTHER))) return RG_OK;
-  if (s->tp_fused) {
+  // The one-shot peer-memory kernel is tuned for the latency of a decode step (16 CTAs, every rank
+  // pulls every rank's whole partial).  A prompt chunk moves megabytes per exchange, which is
+  // bandwidth work: it goes through the ring / tree of ncclAllReduce, then one add kernel.
+  if (s->tp_fused && ncols <= BMAX) {
     TpFusedArgs a;
     a.x = s->x;
     a.ldx = d;
@@ -444,7 +442,7 @@ static int32_t tp_reduce_add(rg_session *s, int ncols, int which) {
 
 // True when every projection of the model can run the integer tensor-core GEMV at this width.
 static bool small_batch_path(const rg_session *s, int ncols) {
-  if (ncols > 2 || s->opt.reserved[0] == 1) return false;  // reserved[0] == 1: force the general path (tests)
+  if (ncols > 2 || s->opt.general_path_only) return false;
   const int d = s->cfg.d_model, qw = s->heads_l * s->cfg.head_dim;
   if (!qgemv_i8_supported(d, ncols) || !qgemv_i8_supported(qw, ncols) || !qgemv_i8_supported(s->ffn_l, ncols)) return false;
   for (const LayerW &W : s->layers) {
@@ -503,7 +501,10 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
                       qkv_w, (tp_lib && l > 0) ? plain : L)))
       return rc;
     prof_mark(s, PROF_ATTN);
-    if (s->attn_counters) {
+    // Two columns of ONE sequence (a two-token prompt chunk) must not share the one-launch kernel:
+    // column 1 reads the cache row that column 0 appends in the same launch.  Such a chunk takes
+    // the append-then-attend launches below; columns of distinct sequences never read each other's rows.
+    if (s->attn_counters && (!s->chunk_is_prompt || ncols == 1)) {
       // RoPE, cache append, split attention and the combine in one launch
       FusedAttnArgs fa;
       fa.qkv = s->qkv;
@@ -606,7 +607,7 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
 
 // True when every projection can run the tensor-core GEMM (packed, K a multiple of 256).
 static bool wide_path_ok(const rg_session *s) {
-  if (s->opt.reserved[0] == 1) return false;
+  if (s->opt.general_path_only) return false;
   for (const LayerW &W : s->layers)
     for (const DevTensor *t : {&W.q, &W.k, &W.v, &W.o, &W.gate, &W.up, &W.down})
       if (!t->packed() || t->cols % 256) return false;
@@ -646,6 +647,7 @@ static int32_t gemm_tc(rg_session *s, const DevTensor &w, int m, float *out, int
   int splits = (m <= BMAX && s->split_scratch) ? (2 * s->sm_count) / tiles : 1;
   splits = qgemm_effective_splits(a.k, splits);
   while (splits > 1 && (size_t)splits * (size_t)m * (size_t)a.n > (size_t)BMAX * 2 * (size_t)s->sm_count * 256) --splits;  // never past the scratch
+  splits = qgemm_effective_splits(a.k, splits);  // the launcher's own count: the reduction sums exactly the tiles it writes
   if (splits > 1) {
     a.out = s->split_scratch;
     a.ldc = a.n;
@@ -894,152 +896,9 @@ static int32_t tp_fused_setup(rg_session *s) {
   return RG_OK;
 }
 
-// Builds the phase list, tensor maps and device state of the persistent decode kernel.  It is an
-// option (reserved[2] == 1 or RG_B200_PERSISTENT_DECODE=1): measured on the Llama-3-8B shape it
-// runs a step in 2.44 ms against 2.33 ms for the launch-per-projection path, because the integer
-// GEMV loop is bound by instruction issue, not by launch gaps.  Leaves s->mega_ok false when the
-// model does not qualify: tensor parallel, head_dim other than 128, dense or mixed-type projections,
-// or an input vector too wide for the shared-memory plan.
-static int32_t mega_setup(rg_session *s) {
-  const rg_llama_config &c = s->cfg;
-  if (s->tp_world > 1 || s->opt.reserved[0] == 1 || !(s->opt.reserved[2] == 1 || env_flag("RG_B200_PERSISTENT_DECODE"))) return RG_OK;
-  const int d = c.d_model, hd = c.head_dim, qw = c.n_heads * hd, ffn = c.ffn_dim;
-  const int G = c.n_heads / c.n_kv_heads;
-  if (hd != 128 || G > 8 || d % 256 || ffn % 256 || !s->head->packed()) return RG_OK;
-  for (const LayerW &W : s->layers) {
-    if (!W.q.packed() || W.k.type != W.q.type || W.v.type != W.q.type || !W.o.packed() || !W.gate.packed() ||
-        W.up.type != W.gate.type || !W.down.packed())
-      return RG_OK;
-  }
-  int u_bytes, slots;
-  if (!mega_plan_smem(std::max(d, std::max(qw, ffn)), &u_bytes, &slots, &s->mega_smem)) return RG_OK;
-  const int grid = s->sm_count;
-  std::vector<MegaOp> ops;
-  std::vector<uint8_t> maps;
-  const size_t mb = mega_tensor_map_bytes();
-  auto add_gemv = [&](std::initializer_list<const DevTensor *> w, int epi, const float *x, const float *norm_w, float *y,
-                      int flags) -> int32_t {
-    MegaOp op;
-    op.kind = MEGA_GEMV;
-    op.type = (*w.begin())->type;
-    op.epi = epi;
-    op.nseg = (int)w.size();
-    op.map0 = (int)(maps.size() / mb);
-    op.kb = (int)((*w.begin())->cols / 32);
-    int i = 0, total = 0;
-    for (const DevTensor *t : w) {
-      op.seg_rows[i++] = (int)t->rows;
-      total += (int)t->rows;
-    }
-    op.n_rows = epi == EPI_SWIGLU ? (int)(*w.begin())->rows : total;
-    op.flags = flags;
-    op.x = x;
-    op.norm_w = norm_w;
-    op.y = y;
-    for (int m = 0; m < 3; ++m) {
-      const DevTensor *t = *(w.begin() + (m < (int)w.size() ? m : 0));
-      maps.resize(maps.size() + mb);
-      RG_CUDA(mega_make_map(maps.data() + maps.size() - mb, t->type, t->d, (int)t->rows, (int)t->cols));
-    }
-    ops.push_back(op);
-    return RG_OK;
-  };
-  int32_t rc;
-  MegaOp embed;
-  embed.kind = MEGA_EMBED;
-  ops.push_back(embed);
-  for (int l = 0; l < c.n_layers; ++l) {
-    const LayerW &W = s->layers[(size_t)l];
-    if ((rc = add_gemv({&W.q, &W.k, &W.v}, EPI_STORE, s->x, reinterpret_cast<const float *>(W.attn_norm.d), s->qkv, 0))) return rc;
-    MegaOp attn;
-    attn.kind = MEGA_ATTN;
-    attn.layer = l;
-    ops.push_back(attn);
-    if ((rc = add_gemv({&W.o}, EPI_RESIDUAL, s->attn_f32, nullptr, s->x, 0))) return rc;
-    if ((rc = add_gemv({&W.gate, &W.up}, EPI_SWIGLU, s->x, reinterpret_cast<const float *>(W.ffn_norm.d), s->h_f32, 0))) return rc;
-    if ((rc = add_gemv({&W.down}, EPI_RESIDUAL, s->h_f32, nullptr, s->x, 0))) return rc;
-  }
-  if ((rc = add_gemv({s->head}, EPI_STORE, s->x, reinterpret_cast<const float *>(s->output_norm.d), s->logits, MEGA_OP_LOGITS)))
-    return rc;
-  MegaOp fin;
-  fin.kind = MEGA_FINISH;
-  ops.push_back(fin);
-
-  MegaParams &P = s->mega;
-  MegaOp *d_ops;
-  uint8_t *d_maps;
-  void **d_k, **d_v;
-  unsigned *d_words;
-  if ((rc = dalloc(s, &d_ops, ops.size()))) return rc;
-  if ((rc = dalloc(s, &d_maps, maps.size()))) return rc;
-  if ((rc = dalloc(s, &d_k, (size_t)c.n_layers))) return rc;
-  if ((rc = dalloc(s, &d_v, (size_t)c.n_layers))) return rc;
-  const size_t n_words = 40 + (size_t)c.n_kv_heads + 3 * (size_t)grid + 8;  // counters, timers, candidates
-  if ((rc = dalloc(s, &d_words, n_words))) return rc;
-  RG_CUDA(cudaMemcpy(d_ops, ops.data(), ops.size() * sizeof(MegaOp), cudaMemcpyHostToDevice));
-  RG_CUDA(cudaMemcpy(d_maps, maps.data(), maps.size(), cudaMemcpyHostToDevice));
-  RG_CUDA(cudaMemcpy(d_k, s->k_cache.data(), sizeof(void *) * (size_t)c.n_layers, cudaMemcpyHostToDevice));
-  RG_CUDA(cudaMemcpy(d_v, s->v_cache.data(), sizeof(void *) * (size_t)c.n_layers, cudaMemcpyHostToDevice));
-  RG_CUDA(cudaMemset(d_words, 0, n_words * sizeof(unsigned)));
-  P.ops = d_ops;
-  P.n_ops = (int)ops.size();
-  P.maps = d_maps;
-  P.tokens = s->d_ctrl->tokens;
-  P.pos = s->d_ctrl->pos;
-  P.seq = s->d_ctrl->seq;
-  P.step = &s->d_ctrl->step;
-  P.history = s->d_history;
-  P.d_ids = s->d_ids;
-  P.bar_counter = d_words;
-  P.bar_base = d_words + 1;
-  P.gdead = reinterpret_cast<int *>(d_words + 2);
-  P.prof = reinterpret_cast<unsigned long long *>(d_words + 4);  // 16 x u64, 8-byte aligned
-  P.attn_counters = d_words + 40;
-  P.cand_val = reinterpret_cast<float *>(d_words + 40 + c.n_kv_heads);
-  P.cand_idx = reinterpret_cast<int *>(d_words + 40 + c.n_kv_heads + grid);
-  P.cand_bad = reinterpret_cast<int *>(d_words + 40 + c.n_kv_heads + 2 * grid);
-  P.status = s->d_status;
-  P.d_model = d;
-  P.heads = c.n_heads;
-  P.kv_heads = c.n_kv_heads;
-  P.ctx = s->ctx;
-  P.eps = c.norm_eps;
-  P.cos_t = s->cos_t;
-  P.sin_t = s->sin_t;
-  P.k_cache = d_k;
-  P.v_cache = d_v;
-  P.qkv = s->qkv;
-  P.attn_out = s->attn_f32;
-  P.attn_scratch = s->attn_scratch;
-  P.max_splits = mega_max_splits(s->ctx, grid, c.n_kv_heads, s->kv_f32);
-  if ((size_t)c.n_heads * P.max_splits * (hd + 2) > attn_scratch_floats(SCOLS, s->heads_l, hd, s->ctx)) return RG_OK;
-  P.embed = s->token_embd.d;
-  P.embed_type = s->token_embd.type;
-  P.x = s->x;
-  P.u_bytes = u_bytes;
-  P.slots = slots;
-  s->mega_phases = (int)ops.size();
-  s->mega_ok = true;
-  return RG_OK;
-}
-
-// Batch-1 decode step (or a one-token prefill chunk) as a single cooperative launch.
-static int32_t forward_mega(rg_session *s, bool advance, bool profile) {
-  MegaParams P = s->mega;
-  P.advance = advance ? 1 : 0;
-  if (!profile) P.prof = nullptr;
-  if (inject(g_faults.launch_after)) return fail(RG_CUDA_ERROR, "injected launch failure");
-  cudaError_t e = launch_decode_mega(P, s->kv_f32, s->mega_smem, s->sm_count, s->stream);
-  s->launches_in_step = 1;
-  if (e != cudaSuccess) return fail(RG_CUDA_ERROR, std::string("launch_decode_mega: ") + cudaGetErrorString(e));
-  return RG_OK;
-}
-
 // One forward over `ncols` columns described by the device control block.  n_logit_cols columns
 // (indices in ctrl.logit_cols) get logits + greedy ids; 0 skips the head (non-final prefill chunk).
 static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance) {
-  if (s->mega_ok && ncols == 1 && n_logit_cols == 1 && !s->sample_uniforms && s->family_mask == 0xffffffffu)
-    return forward_mega(s, advance, false);
   if (small_batch_path(s, ncols)) return forward_small(s, ncols, n_logit_cols, advance);
   if (ncols > MAXC) {
     if (!wide_path_ok(s))
@@ -1204,12 +1063,8 @@ static int32_t decode_graph(rg_session *s, int batch, cudaGraphExec_t *out) {
   return RG_OK;
 }
 
-static bool mega_step(const rg_session *s, int ncols, int n_logit_cols) {
-  return s->mega_ok && ncols == 1 && n_logit_cols == 1 && !s->sample_uniforms;  // the persistent kernel selects greedily
-}
-
 static int32_t run_step(rg_session *s, int ncols, int n_logit_cols, bool advance, bool allow_graph) {
-  if (allow_graph && s->use_graph && !mega_step(s, ncols, n_logit_cols)) {  // the persistent kernel is one launch already
+  if (allow_graph && s->use_graph) {
     cudaGraphExec_t exec;
     int32_t rc = decode_graph(s, ncols, &exec);
     if (rc) return rc;
@@ -1296,6 +1151,52 @@ int32_t rg_b200_test_fail_after(const char *what, int32_t n) {
   else if (!strcmp(what, "launch")) g_faults.launch_after = n;
   else if (!strcmp(what, "sync")) g_faults.sync_after = n;
   else return RG_INVALID_ARGUMENT;
+  return RG_OK;
+}
+
+// Test hook: makes a bounded device-side wait of this session run out, without faulting or hanging
+// anything.  The partial-sum exchange kernel is launched on the session's stream as rank 0 of a
+// pretended world of two whose flag words all live in local memory; nothing ever writes the slot of
+// rank 1, the poll limit is cut to a few thousand polls, so the kernel records DEV_TIMEOUT in the
+// session's status word and returns.  The session's next step reports RG_TIMEOUT and is poisoned.
+int32_t rg_b200_test_expire_device_wait(rg_session *s) {
+  int32_t rc = check_live(s);
+  if (rc) return rc;
+  RG_CUDA(cudaSetDevice(s->opt.device));
+  const int d = s->cfg.d_model;
+  if (d % 4) return fail(RG_UNSUPPORTED_GEOMETRY, "d_model must be a multiple of 4");
+  float *part = nullptr, *x = nullptr;
+  unsigned *flags = nullptr, *epochs = nullptr;
+  const float **d_parts = nullptr;
+  unsigned **d_flags = nullptr;
+  if ((rc = dalloc(s, &part, (size_t)d)) || (rc = dalloc(s, &x, (size_t)d)) || (rc = dalloc(s, &flags, (size_t)TP_FUSED_FLAG_WORDS)) ||
+      (rc = dalloc(s, &epochs, (size_t)2 * TP_FUSED_CTAS)) || (rc = dalloc(s, &d_parts, (size_t)2)) || (rc = dalloc(s, &d_flags, (size_t)2)))
+    return rc;
+  RG_CUDA(cudaMemsetAsync(part, 0, sizeof(float) * (size_t)d, s->stream));
+  RG_CUDA(cudaMemsetAsync(x, 0, sizeof(float) * (size_t)d, s->stream));
+  RG_CUDA(cudaMemsetAsync(flags, 0, sizeof(unsigned) * TP_FUSED_FLAG_WORDS, s->stream));
+  RG_CUDA(cudaMemsetAsync(epochs, 0, sizeof(unsigned) * 2 * TP_FUSED_CTAS, s->stream));
+  const float *hp[2] = {part, part};
+  unsigned *hf[2] = {flags, flags};
+  RG_CUDA(cudaMemcpyAsync(d_parts, hp, sizeof(hp), cudaMemcpyHostToDevice, s->stream));
+  RG_CUDA(cudaMemcpyAsync(d_flags, hf, sizeof(hf), cudaMemcpyHostToDevice, s->stream));
+  RG_CUDA(cudaStreamSynchronize(s->stream));
+  TpFusedArgs a;
+  a.x = x;
+  a.ldx = d;
+  a.n = d;
+  a.cols = 1;
+  a.peer_partial = d_parts;
+  a.ldp = d;
+  a.peer_flags = d_flags;
+  a.epochs = epochs;
+  a.rank = 0;
+  a.world = 2;
+  a.buffer = 0;
+  a.poll_limit = 4096;
+  LaunchCfg c = lcfg(s);
+  c.pdl = false;
+  RG_CUDA(launch_tp_allreduce_add(a, c));
   return RG_OK;
 }
 
@@ -1599,7 +1500,7 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   RG_TRY(dalloc(s.get(), &raw, (size_t)2 * WMAX * s->xb_ld * 2));
   // splits <= 2 * SMs / tiles and rows <= tiles * rows_per_cta (256 with two row tiles per CTA)
   RG_TRY(dalloc(s.get(), &s->split_scratch, (size_t)BMAX * 2 * s->sm_count * 256));
-  s->gemm_mode = (s->opt.reserved[1] >= 1 && s->opt.reserved[1] <= 3) ? s->opt.reserved[1] - 1 : QGEMM_F16X3;
+  s->gemm_mode = (s->opt.gemm_operand_mode >= 1 && s->opt.gemm_operand_mode <= 3) ? s->opt.gemm_operand_mode - 1 : QGEMM_F16X3;
   s->xb = raw;
   RG_TRY(dalloc(s.get(), &raw, xpack_bytes(d, MAXC)));
   s->xn_pack = raw;
@@ -1664,7 +1565,6 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   for (auto &L : s->layers)
     for (DevTensor *t : {&L.attn_norm, &L.q, &L.k, &L.v, &L.o, &L.ffn_norm, &L.gate, &L.up, &L.down}) own(*t);
   p->consumed = true;
-  if ((rc = mega_setup(s.get()))) return rc;
   s->position.assign((size_t)s->max_batch, 0);
   s->report.weight_bytes = s->weight_bytes;
   s->report.kv_bytes = s->kv_bytes;
@@ -2067,7 +1967,7 @@ int32_t rg_b200_decode_loop(rg_session *s, const int32_t *first, int32_t batch, 
   }
   h->step = 0;
   if ((rc = upload_ctrl(s))) return rc;
-  if (s->use_graph && !mega_step(s, batch, batch)) {
+  if (s->use_graph) {
     cudaGraphExec_t exec;
     if ((rc = decode_graph(s, batch, &exec))) return rc;  // capture outside the timed region
   }
@@ -2098,8 +1998,8 @@ int32_t rg_b200_decode_loop(rg_session *s, const int32_t *first, int32_t batch, 
   return RG_OK;
 }
 
-int32_t rg_b200_decode_profile(rg_session *s, const int32_t *first, int32_t batch, int32_t steps, float out_ms[4],
-                               uint64_t out_launches[4]) {
+static int32_t decode_profile_impl(rg_session *s, const int32_t *first, int32_t batch, int32_t steps, float out_ms[4],
+                                   uint64_t out_launches[4], bool serialized) {
   int32_t rc = check_live(s);
   if (rc) return rc;
   if (!first || !out_ms || batch < 1 || batch > s->max_batch || steps < 1) return fail(RG_INVALID_ARGUMENT, "bad arguments");
@@ -2117,36 +2017,8 @@ int32_t rg_b200_decode_profile(rg_session *s, const int32_t *first, int32_t batc
   }
   h->step = 0;
   if ((rc = upload_ctrl(s))) return rc;
-  if (mega_step(s, batch, batch)) {
-    // one persistent kernel per step: its first CTA clocks the phases it runs (projections, attention,
-    // embedding + selection, grid barriers); the event time is the whole step
-    const MegaParams &P = s->mega;
-    if ((rc = forward_mega(s, false, true))) return rc;  // warm
-    RG_CUDA(cudaMemsetAsync(P.prof, 0, 8 * sizeof(unsigned long long), s->stream));
-    RG_CUDA(cudaEventRecord(s->ev0, s->stream));
-    for (int it = 0; it < steps; ++it)
-      if ((rc = forward_mega(s, false, true))) return rc;
-    RG_CUDA(cudaEventRecord(s->ev1, s->stream));
-    unsigned long long ns[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    RG_CUDA(x_memcpy_async(ns, P.prof, sizeof(ns), cudaMemcpyDeviceToHost, s->stream));
-    if ((rc = finish_step(s, 0, nullptr, 0))) return rc;
-    float ms = 0.0f;
-    cudaEventElapsedTime(&ms, s->ev0, s->ev1);
-    out_ms[0] = (float)((double)ns[0] * 1e-6 / steps);
-    out_ms[1] = (float)((double)ns[1] * 1e-6 / steps);
-    out_ms[2] = (float)((double)(ns[2] + ns[3]) * 1e-6 / steps);  // embedding, selection and barrier waits
-    out_ms[3] = ms / (float)steps;
-    if (env_flag("RG_B200_MEGA_TRACE"))
-      fprintf(stderr,
-              "persistent decode, first CTA, us per step: projections %.1f (pack %.1f, main loop %.1f, reduce+epilogue %.1f), "
-              "attention %.1f (staging wait %.1f), embed+select %.1f, grid barriers %.1f; step %.1f\n",
-              ns[0] * 1e-3 / steps, ns[4] * 1e-3 / steps, ns[5] * 1e-3 / steps, ns[6] * 1e-3 / steps, ns[1] * 1e-3 / steps,
-              ns[7] * 1e-3 / steps, ns[2] * 1e-3 / steps, ns[3] * 1e-3 / steps, ms * 1e3 / steps);
-    if (out_launches) out_launches[0] = 1, out_launches[1] = 0, out_launches[2] = 0, out_launches[3] = 1;
-    return RG_OK;
-  }
   const bool saved_pdl = s->use_pdl;
-  s->use_pdl = false;  // serialized launches: every kernel runs alone
+  if (serialized) s->use_pdl = false;  // serialized launches: every kernel runs alone
   s->launches_in_step = 0;
   rc = forward(s, batch, batch, false);  // loads every kernel before capture; nothing is committed
   double total = 0.0;
@@ -2191,6 +2063,16 @@ int32_t rg_b200_decode_profile(rg_session *s, const int32_t *first, int32_t batc
   out_ms[3] = (float)total;
   if (out_launches) out_launches[3] = out_launches[0] + out_launches[1] + out_launches[2];
   return finish_step(s, 0, nullptr, 0);
+}
+
+int32_t rg_b200_decode_profile(rg_session *s, const int32_t *first, int32_t batch, int32_t steps, float out_ms[4],
+                               uint64_t out_launches[4]) {
+  return decode_profile_impl(s, first, batch, steps, out_ms, out_launches, true);
+}
+
+int32_t rg_b200_decode_profile_in_step(rg_session *s, const int32_t *first, int32_t batch, int32_t steps, float out_ms[4],
+                                       uint64_t out_launches[4]) {
+  return decode_profile_impl(s, first, batch, steps, out_ms, out_launches, false);
 }
 
 int32_t rg_b200_report(const rg_session *s, rg_report *out) {

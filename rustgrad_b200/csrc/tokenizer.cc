@@ -461,12 +461,7 @@ int32_t rg_b200_tokenizer_new(const char *const *normal, const size_t *normal_le
   return build(nv, sv, c, out, err);
 }
 
-int32_t rg_b200_tokenizer_from_gguf(const rg_gguf *gguf, rg_tokenizer **out, rg_tok_error *err) {
-  if (!gguf || !out) {
-    set_error(err, RG_TOK_INVALID_ARGUMENT);
-    return RG_TOK_INVALID_ARGUMENT;
-  }
-  const rg::Gguf &g = gguf->g;
+static int32_t tokenizer_from_gguf_impl(const rg::Gguf &g, rg_tokenizer **out, rg_tok_error *err) {
   static const char *TOKENS = "tokenizer.ggml.tokens", *TYPES = "tokenizer.ggml.token_type", *PRE = "tokenizer.ggml.pre";
   static const char *BOS = "tokenizer.ggml.bos_token_id", *EOS = "tokenizer.ggml.eos_token_id";
   static const char *EOT = "tokenizer.ggml.eot_token_id", *ADD_BOS = "tokenizer.ggml.add_bos_token";
@@ -544,6 +539,14 @@ int32_t rg_b200_tokenizer_from_gguf(const rg_gguf *gguf, rg_tokenizer **out, rg_
   if (cfg.has_bos && cfg.bos_id >= count) return fail(RG_TOK_CONFIGURED_ID_OUT_OF_RANGE, cfg.bos_id, count, BOS);
   if (cfg.has_eot && cfg.eot_id >= count) return fail(RG_TOK_CONFIGURED_ID_OUT_OF_RANGE, cfg.eot_id, count, EOT);
   return build(normal, special, cfg, out, err);
+}
+
+int32_t rg_b200_tokenizer_from_gguf(const rg_gguf *gguf, rg_tokenizer **out, rg_tok_error *err) {
+  if (!gguf || !out) {
+    set_error(err, RG_TOK_INVALID_ARGUMENT);
+    return RG_TOK_INVALID_ARGUMENT;
+  }
+  return tokenizer_from_gguf_impl(gguf->g, out, err);
 }
 
 void rg_b200_tokenizer_free(rg_tokenizer *t) { delete t; }
@@ -783,3 +786,29 @@ int32_t rg_b200_chat_render(const rg_tokenizer *t, const int32_t *roles, const c
 }
 
 }  // extern "C"
+
+namespace rg {
+
+// The model configuration takes its stop ids from the tokenizer built from the same file
+// (src/models/transformer/model.rs:133,288-292 with src/tokenizer/mod.rs:284-296): eos is the
+// metadata value or 0, eot the metadata value or the last special token named <|im_end|>, and a
+// file whose tokenizer does not build has no model configuration either.
+int32_t gguf_tokenizer_stop_ids(const Gguf &g, int32_t *eos, int32_t *eot, std::string *why) {
+  rg_tokenizer *t = nullptr;
+  rg_tok_error e{};
+  const int32_t rc = tokenizer_from_gguf_impl(g, &t, &e);
+  if (rc != RG_TOK_OK) {
+    if (why)
+      *why = "tokenizer: status " + std::to_string(rc) + " (" + std::string(e.text, e.text_len < sizeof(e.text) ? e.text_len : sizeof(e.text)) +
+             ", " + std::to_string(e.value) + ", " + std::to_string(e.value2) + ")";
+    if (rc == RG_TOK_MISSING_METADATA) return RG_MISSING_METADATA;
+    if (rc == RG_TOK_UNSUPPORTED_PRESET) return RG_UNSUPPORTED_VARIANT;
+    return RG_INVALID_ARGUMENT;
+  }
+  *eos = (int32_t)t->cfg.eos_id;
+  *eot = t->cfg.has_eot ? (int32_t)t->cfg.eot_id : -1;
+  delete t;
+  return RG_OK;
+}
+
+}  // namespace rg

@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(THREADS) tp_allreduce_add_kernel(const TpFused
     st_release_sys(A.peer_flags[tid] + slot + A.rank, e);  // tell rank `tid` that this rank's partial is ready
     const unsigned *mine = A.peer_flags[A.rank] + slot + tid;  // written by rank `tid`
     bool ok = false;
-    for (unsigned i = 0; i < (1u << 22); ++i) {
+    for (unsigned i = 0; i < A.poll_limit; ++i) {
       if ((int)(ld_acquire_sys(mine) - e) >= 0) {
         ok = true;
         break;
@@ -102,6 +102,7 @@ __global__ void __launch_bounds__(THREADS) tp_allreduce_add_kernel(const TpFused
 }  // namespace
 
 cudaError_t launch_tp_allreduce_add(const TpFusedArgs &a, const LaunchCfg &cfg) {
+  count_launch(LC_TP_EXCHANGE);
   if (!a.x || !a.peer_partial || !a.peer_flags || !a.epochs || a.world < 2 || a.world > TP_FUSED_MAX_WORLD || a.n % 4 ||
       a.ldx % 4 || a.ldp % 4 || a.buffer < 0 || a.buffer > 1)
     return cudaErrorInvalidValue;

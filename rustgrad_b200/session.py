@@ -84,7 +84,6 @@ class CudaSessionTarget:
     disable_pdl: bool = False
     general_path_only: bool = False  # never take the fused small-batch decode path (tests)
     gemm_operands: str = ""  # tensor-core path operands: "" (compensated f16), "bf16", "f16", "f16x3"
-    persistent_decode: bool = False  # batch-1 decode as one cooperative kernel per step (off by default)
     disable_fused_allreduce: bool = False  # tensor-parallel partial sums through NCCL instead of peer memory
     _opts: Options = field(default=None, repr=False)
 
@@ -94,9 +93,8 @@ class CudaSessionTarget:
         o.kv_f32, o.tp_rank, o.tp_world = int(self.kv_f32), self.tp_rank, self.tp_world
         o.disable_graph, o.disable_pdl = int(self.disable_graph), int(self.disable_pdl)
         o.disable_fused_allreduce = int(self.disable_fused_allreduce)
-        o.reserved[0] = int(self.general_path_only)
-        o.reserved[1] = {"": 0, "bf16": 1, "f16": 2, "f16x3": 3}[self.gemm_operands]
-        o.reserved[2] = int(self.persistent_decode)
+        o.general_path_only = int(self.general_path_only)
+        o.gemm_operand_mode = {"": 0, "bf16": 1, "f16": 2, "f16x3": 3}[self.gemm_operands]
         if self.tp_world > 1:
             if len(self.nccl_id) != 128:
                 raise InvalidArgument(1, "tensor parallelism needs the 128-byte NCCL id of rank 0")  # noqa: F821
@@ -309,12 +307,14 @@ class LlamaCudaSession:
         check(self._L.rg_b200_decode_loop(self._h, _i32(t), t.size, steps, _i32(out), C.byref(ms)))
         return out, ms.value
 
-    def decode_profile(self, first_tokens, steps: int) -> dict:
-        """CUDA-event time per step of each kernel family replayed alone (serialized launches)."""
+    def decode_profile(self, first_tokens, steps: int, in_step: bool = False) -> dict:
+        """CUDA-event time per step of each kernel family replayed alone: serialized launches, or
+        (``in_step``) with the dependent-launch edges the real step has between consecutive kernels."""
         t = np.ascontiguousarray(first_tokens, dtype=np.int32)
         ms = (C.c_float * 4)()
         marks = (C.c_uint64 * 4)()
-        check(self._L.rg_b200_decode_profile(self._h, _i32(t), t.size, steps, ms, marks))
+        fn = self._L.rg_b200_decode_profile_in_step if in_step else self._L.rg_b200_decode_profile
+        check(fn(self._h, _i32(t), t.size, steps, ms, marks))
         keys = ("gemv", "attention", "other", "total")
         return {k: {"ms_per_step": ms[i], "launches_per_step": marks[i]} for i, k in enumerate(keys)}
 
@@ -325,6 +325,18 @@ class LlamaCudaSession:
 
     def stream(self) -> int:
         return int(self._L.rg_b200_session_stream(self._h) or 0)
+
+    def expire_device_wait(self) -> None:
+        """Test hook: the next step finds that a bounded device-side wait ran out (nothing faults or hangs)."""
+        check(self._L.rg_b200_test_expire_device_wait(self._h))
+
+
+def launch_count(kernel: str) -> int:
+    """Launches of a kernel family made by this process so far (see rg_b200_launch_count)."""
+    n = _lib.load().rg_b200_launch_count(kernel.encode())
+    if n == 0xFFFFFFFFFFFFFFFF:
+        raise KeyError(kernel)
+    return int(n)
 
 
 # ---- operator-level calls (host arrays in, host arrays out) --------------------------------

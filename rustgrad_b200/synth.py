@@ -77,3 +77,19 @@ def gguf_bytes(cfg: dict, tensors: dict) -> bytes:
 
 def prompt_ids(cfg: dict, n: int, seed: int) -> np.ndarray:
     return np.random.default_rng(seed).integers(0, cfg["vocab"], size=n, dtype=np.int32)
+
+
+def device_weight(ggml_type: int, n: int, k: int, seed: int, std: float = 0.02, device: int = 0) -> np.ndarray:
+    """The block bytes of one [n, k] tensor drawn N(0, std) and quantized on the GPU (the generator
+    that fills synthetic models, read back): seconds faster than the host encoder for tensors of
+    tens of millions of elements.  k must be a multiple of 64."""
+    from . import session
+    hd = 128 if k % 128 == 0 else 64
+    cfg = dict(n_layers=1, d_model=k, n_heads=k // hd, n_kv_heads=k // hd, head_dim=hd, ffn_dim=n, vocab=32,
+               max_context=16, norm_eps=1e-5, rope_theta=10000.0)
+    plan = session.LlamaCudaPlan.empty(cfg, session.CudaSessionTarget(device=device))
+    try:
+        plan.synth_tensor("blk.0.ffn_gate.weight", ggml_type, n, k, seed, std)
+        return plan.read_tensor("blk.0.ffn_gate.weight")
+    finally:
+        plan.close()

@@ -41,7 +41,8 @@ def test_gguf_roundtrip_config_and_tensor_inventory():
     got = g.llama_config()
     for key in ("n_layers", "d_model", "n_heads", "n_kv_heads", "head_dim", "ffn_dim", "vocab", "max_context"):
         assert got[key] == cfg[key], key
-    assert abs(got["norm_eps"] - 1e-5) < 1e-12 and got["rope_theta"] == 10000.0 and got["eos_id"] == -1
+    assert abs(got["norm_eps"] - 1e-5) < 1e-12 and got["rope_theta"] == 10000.0
+    assert got["eos_id"] == 0 and got["eot_id"] == -1  # no stop keys in the file: eos defaults to 0, no eot
     infos = {name: (t, dims, off, n) for name, t, dims, off, n in g.tensors()}
     assert set(infos) == set(tensors)
     raw = np.frombuffer(data, np.uint8)
@@ -123,3 +124,54 @@ def test_llama_config_rejections_are_typed():
     with_bias = dict(tensors)
     with_bias["blk.0.attn_q.bias"] = (quant.F32, 1, 256, np.zeros(1024, np.uint8))
     assert cfg_status(base, with_bias) == 17
+
+
+def test_stop_ids_follow_the_tokenizer_rule():
+    """eos = metadata value or 0; eot = metadata value, else the last special token spelled
+    <|im_end|>; ids must index the vocabulary (src/tokenizer/mod.rs:284-296 via model.rs:288-292).
+    The library's answer is compared with the checker's restatement of the rule."""
+    from oracle import tokenizer_oracle as T
+    cfg, tensors, _ = tiny_file()
+    base = gguf_writer.llama_metadata(cfg)
+    tokens, types = gguf_writer.synthetic_token_table(cfg["vocab"])
+
+    def config_of(tokens, types, eos=None, eot=None):
+        md = [kv for kv in base if b"tokenizer.ggml.tokens" not in kv[:60] and b"tokenizer.ggml.token_type" not in kv[:60]]
+        md += [gguf_writer.kv_str_array("tokenizer.ggml.tokens", tokens), gguf_writer.kv_i32_array("tokenizer.ggml.token_type", types)]
+        if eos is not None:
+            md.append(gguf_writer.kv_u32("tokenizer.ggml.eos_token_id", eos))
+        if eot is not None:
+            md.append(gguf_writer.kv_u32("tokenizer.ggml.eot_token_id", eot))
+        g = session.GgufFile(build(md, tensors))
+        try:
+            return g.llama_config()
+        finally:
+            g.close()
+
+    def agree(tokens, types, eos=None, eot=None):
+        got = config_of(tokens, types, eos, eot)
+        want = T.stop_ids_from_gguf_metadata(tokens, types, eos, eot)
+        assert (got["eos_id"], got["eot_id"]) == (want[0], -1 if want[1] is None else want[1])
+        return got["eos_id"], got["eot_id"]
+
+    assert agree(tokens, types) == (0, -1)
+    assert agree(tokens, types, eos=7) == (7, -1)
+    chatml_tokens, chatml_types = list(tokens), list(types)
+    for i in (9, 40):                      # two specials with the ChatML end marker: the last one counts
+        chatml_tokens[i], chatml_types[i] = "<|im_end|>", 3
+    assert agree(chatml_tokens, chatml_types) == (0, 40)
+    assert agree(chatml_tokens, chatml_types, eos=5, eot=11) == (5, 11)   # an explicit key wins
+    normal_named = list(tokens)
+    normal_named[12] = "<|im_end|>"        # a NORMAL token of that spelling is not a stop token
+    assert agree(normal_named, types) == (0, -1)
+    for bad in (dict(eos=cfg["vocab"]), dict(eot=cfg["vocab"] + 3)):
+        with pytest.raises(session.RgError) as e:
+            config_of(tokens, types, **bad)
+        assert e.value.status == 1
+        with pytest.raises(T.TokenizerError):
+            T.stop_ids_from_gguf_metadata(tokens, types, bad.get("eos"), bad.get("eot"))
+    # without the token types there is no tokenizer, hence no model configuration
+    md = [kv for kv in base if b"tokenizer.ggml.token_type" not in kv[:60]]
+    g = session.GgufFile(build(md, tensors))
+    with pytest.raises(session.MissingMetadata):
+        g.llama_config()

@@ -21,7 +21,7 @@ def assert_logits_close(got, want):
 
 @pytest.fixture(scope="module")
 def tiny():
-    """BASELINE config 1: 2 layers, d 256, 4 heads, ffn 688, vocab 512, Q8_0, tied head, as a GGUF file."""
+    """The tiny end-to-end model: 2 layers, d 256, 4 heads, ffn 688, vocab 512, Q8_0, tied head, as a GGUF file."""
     cfg = dict(synth.TINY)
     tensors = synth.build_tensors(cfg, seed=0, body_type=quant.Q8_0)
     data = synth.gguf_bytes(cfg, tensors)
@@ -169,61 +169,21 @@ def test_tensor_core_path_for_long_prompts_and_wide_decode_batches():
         p = synth.prompt_ids(cfg, 3 + r % 5, seed=40 + r)
         s.prefill_ids(p, row=r)
         toks.append(O.select_greedy(oracles[r].forward(p, O.MODE_FAST)))
+    near_ties = []
     for _ in range(3):
         logits, greedy = s.decode(toks, want_logits=True)
         nxt = []
         for r in range(rows):
             w = oracles[r].forward([toks[r]], O.MODE_FAST)
             assert_logits_close(logits[r], w)
-            top2 = np.sort(w)[-2:]
             nxt.append(O.select_greedy(w))
-            assert int(greedy[r]) == nxt[r] or (top2[1] - top2[0]) < 2e-3
+            if int(greedy[r]) != nxt[r]:
+                top2 = np.sort(w)[-2:]
+                near_ties.append((r, float(top2[1] - top2[0])))
         toks = nxt
-
-
-@pytest.mark.parametrize("kv_f32", [True, False], ids=["kv_f32", "kv_f16"])
-def test_persistent_decode_kernel_matches_multi_launch_path_and_checker(kv_f32):
-    """Batch-1 decode of a head_dim-128 model can run as one persistent kernel per step (an option);
-    the same steps as separate launches and the CPU checker must agree, across several context spans."""
-    cfg = synth.scaled(synth.TINY, d_model=512, n_heads=8, n_kv_heads=2, head_dim=128, ffn_dim=1024, vocab=1000, n_layers=3,
-                       rope_theta=500000.0, max_context=1024)
-    tensors = synth.build_tensors(cfg, seed=12, body_type=quant.Q4_0, embed_type=quant.Q8_0, head_type=quant.Q8_0,
-                                  tied_head=False)
-    prompt = synth.prompt_ids(cfg, 700, seed=4)  # 700 positions: several spans per kv head
-    oracle = O.OracleModel(cfg, tensors, kv_f16=not kv_f32, threads=8)
-    want = oracle.forward(prompt, O.MODE_FAST)
-    mk = lambda **kw: session.LlamaCudaPlan.from_tensors(  # noqa: E731
-        cfg, tensors, session.CudaSessionTarget(kv_f32=kv_f32, max_context=1024, **kw)).prepare()
-    one, many = mk(persistent_decode=True), mk()
-    assert_logits_close(one.prefill_ids(prompt), want)
-    many.prefill_ids(prompt)
-    tok = O.select_greedy(want)
-    for _ in range(6):
-        w = oracle.forward([tok], O.MODE_FAST)
-        a, b = one.run_token(tok), many.run_token(tok)
-        assert_logits_close(a, w)
-        assert_logits_close(b, w)
-        assert np.abs(a - b).max() <= 1e-4
-        tok = O.select_greedy(w)
-    r1, r2 = one.report(), many.report()
-    assert r1["kernel_launches"] < r2["kernel_launches"]
-    # device-resident loop on both paths from the same state
-    ids1, _ = one.decode_loop([tok], 12)
-    ids2, _ = many.decode_loop([tok], 12)
-    want_ids = []
-    t = tok
-    for _ in range(12):
-        w = oracle.forward([t], O.MODE_FAST)
-        t = O.select_greedy(w)
-        want_ids.append(t)
-    assert ids1[:, 0].tolist() == want_ids and ids2[:, 0].tolist() == want_ids
-    assert one.position() == 700 + 6 + 12
-    # a one-token prompt on a fresh row is a persistent-kernel step too
-    fresh = mk(persistent_decode=True)
-    o2 = O.OracleModel(cfg, tensors, kv_f16=not kv_f32, threads=8)
-    assert_logits_close(fresh.prefill_ids([7]), o2.forward([7], O.MODE_FAST))
-    prof = one.decode_profile([t], 4)
-    assert prof["total"]["launches_per_step"] == 1 and prof["total"]["ms_per_step"] > 0
+    # a differing greedy id is a finding, never silently accepted: none is expected on this model
+    print(f"greedy ids differing from the checker on the tensor-core decode path: {len(near_ties)} {near_ties}")
+    assert not near_ties
 
 
 def test_stop_on_eos_and_last_token_not_fed_back(tiny):
@@ -357,7 +317,7 @@ def test_device_synthesized_weights_match_host_recipe():
 
 
 def test_llama3_8b_width_model_matches_cpu_path_on_device_synthesized_weights():
-    """BASELINE config 4 at full width (d 4096, 32/8 heads of 128, ffn 14336, vocab 128256, Q4_0 body,
+    """The Llama-3-8B shape at full width (d 4096, 32/8 heads of 128, ffn 14336, vocab 128256, Q4_0 body,
     Q8_0 embedding + head, f16 KV) with 3 of the 32 layers, so the CPU checker finishes in seconds.
     The weights are generated on the device and read back, so both sides see the same bytes."""
     cfg = synth.scaled(synth.LLAMA_8B, n_layers=3, max_context=256)
@@ -380,15 +340,14 @@ def test_llama3_8b_width_model_matches_cpu_path_on_device_synthesized_weights():
         logits, greedy = s.decode([tok], want_logits=True)
         assert_logits_close(logits[0], want)
         nxt = O.select_greedy(want)
-        top2 = np.sort(want)[-2:]
-        assert int(greedy[0]) == nxt or (top2[1] - top2[0]) < 1e-5, "greedy token differs beyond a numerical tie"
+        assert int(greedy[0]) == nxt, ("greedy id differs from the checker", np.sort(want)[-2:])
         tok = nxt
 
 
 def test_full_size_8b_shape_properties():
-    """BASELINE config 4 at its full size (32 layers, 4.5 GB of Q4_0 / Q8_0 weights synthesised on the
-    device).  The CPU checker cannot run this size in a test, so the size-independent properties of
-    the path are checked instead: the same sequence through different kernels and call patterns."""
+    """The Llama-3-8B shape at its full size (32 layers, 4.5 GB of Q4_0 / Q8_0 weights synthesised on the
+    device): size-independent properties of the path, the same sequence through different kernels
+    and call patterns (the comparison with the CPU checker at this size is the test below)."""
     cfg = synth.scaled(synth.LLAMA_8B, max_context=1024)
     prompt = synth.prompt_ids(cfg, 300, seed=1)
 
@@ -422,12 +381,6 @@ def test_full_size_8b_shape_properties():
         tok = int(greedy[0])
         host_ids.append(tok)
     assert host_ids == ids1[:, 0].tolist()
-    # the optional persistent whole-step kernel produces the same tokens
-    d = make(persistent_decode=True)
-    d.prefill_ids(prompt)
-    ids_p, _ = d.decode_loop([first], 12)
-    assert ids_p[:, 0].tolist() == ids1[:, 0].tolist()
-    assert d.report()["kernel_launches"] < b.report()["kernel_launches"]
 
 
 def test_thirty_two_rows_at_full_width_match_one_row():
@@ -458,3 +411,157 @@ def test_thirty_two_rows_at_full_width_match_one_row():
     split = make(1)
     split.prefill_ids(long_prompt[:8], want_logits=False)
     assert_logits_close(split.prefill_ids(long_prompt[8:]), full)
+
+
+def device_model(cfg, seed, embed=quant.Q8_0, head=quant.Q8_0, **target_kw):
+    """A model synthesised on the device and read back, so the session and the checker hold the same bytes."""
+    target = session.CudaSessionTarget(**target_kw)
+    plan = session.LlamaCudaPlan.synthetic(cfg, target, seed=seed, embed_type=embed, head_type=head)
+    tensors = {}
+    for name, rows, cols, is_norm in synth.tensor_inventory(cfg, tied_head=False):
+        kind = quant.F32 if is_norm else embed if name == "token_embd.weight" else head if name == "output.weight" else quant.Q4_0
+        tensors[name] = (kind, rows, cols, plan.read_tensor(name))
+    return plan.prepare(), tensors
+
+
+def check_prefill_and_decode(s, oracle, prompt, steps):
+    """Prefill logits, then `steps` decode steps: every logit inside the bar, every greedy id equal."""
+    want = oracle.forward(prompt, O.MODE_FAST)
+    got = s.prefill_ids(prompt)
+    assert_logits_close(got, want)
+    tok = O.select_greedy(want)
+    assert int(np.argmax(got)) == tok
+    worst = float(np.abs(got - want).max())
+    for _ in range(steps):
+        want = oracle.forward([tok], O.MODE_FAST)
+        logits, greedy = s.decode([tok], want_logits=True)
+        assert_logits_close(logits[0], want)
+        worst = max(worst, float(np.abs(logits[0] - want).max()))
+        tok = O.select_greedy(want)
+        assert int(greedy[0]) == tok, ("greedy id differs from the checker", np.sort(want)[-2:])
+    return worst
+
+
+def test_llama3_8b_shape_at_full_depth_matches_cpu_path():
+    """All 32 layers of the Llama-3-8B shape (Q4_0 body, Q8_0 embedding + head, f16 KV cache): a
+    16-token prompt (tensor-core path, compensated operands) and 4 decode steps (integer GEMV, fused
+    attention) against the CPU checker on the same bytes: logit bar, identical greedy ids."""
+    cfg = synth.scaled(synth.LLAMA_8B, max_context=64)
+    s, tensors = device_model(cfg, seed=6, max_context=64)
+    oracle = O.OracleModel(cfg, tensors, kv_f16=True)
+    worst = check_prefill_and_decode(s, oracle, synth.prompt_ids(cfg, 16, seed=1), 4)
+    print(f"32 layers: max |logit - checker| = {worst:.3e}")
+    assert session.launch_count("qgemv_i8") > 0 and session.launch_count("attn_fused") > 0
+
+
+def test_long_prompt_at_depth_on_the_tensor_core_path():
+    """A 300-token prompt through 8 full-width layers: two tensor-core chunks with the tiled causal
+    attention, then decode steps over a cache of 300 positions."""
+    cfg = synth.scaled(synth.LLAMA_8B, n_layers=8, max_context=320)
+    s, tensors = device_model(cfg, seed=6, max_context=320)
+    oracle = O.OracleModel(cfg, tensors, kv_f16=True)
+    before = session.launch_count("attn_prefill"), session.launch_count("qgemm_tc")
+    worst = check_prefill_and_decode(s, oracle, synth.prompt_ids(cfg, 300, seed=2), 2)
+    print(f"8 layers, 300-token prompt: max |logit - checker| = {worst:.3e}")
+    assert session.launch_count("attn_prefill") > before[0] and session.launch_count("qgemm_tc") > before[1]
+
+
+def test_llama3_70b_width_on_one_gpu_matches_cpu_path():
+    """The Llama-3-70B width (d 8192, 64 / 8 heads of 128, ffn 28672, full vocabulary, everything
+    Q4_0) with 2 of the 80 layers on one GPU against the CPU checker."""
+    cfg = synth.scaled(synth.LLAMA_70B, n_layers=2, max_context=64)
+    s, tensors = device_model(cfg, seed=7, embed=quant.Q4_0, head=quant.Q4_0, max_context=64)
+    oracle = O.OracleModel(cfg, tensors, kv_f16=True)
+    worst = check_prefill_and_decode(s, oracle, synth.prompt_ids(cfg, 16, seed=1), 4)
+    print(f"70B width, 2 layers: max |logit - checker| = {worst:.3e}")
+
+
+@pytest.fixture(scope="module")
+def small_hd128():
+    """A model every projection of which qualifies for the integer GEMV and the one-launch attention."""
+    cfg = synth.scaled(synth.TINY, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn_dim=1024, vocab=640, n_layers=3,
+                       rope_theta=500000.0, max_context=1100)
+    tensors = synth.build_tensors(cfg, seed=21, body_type=quant.Q4_0, embed_type=quant.Q8_0, head_type=quant.Q8_0,
+                                  tied_head=False)
+    return cfg, tensors
+
+
+def test_two_token_prompt_chunks_see_their_own_first_token(small_hd128):
+    """A chunk of exactly two prompt tokens runs the two-column GEMV path; its second column reads the
+    K / V row its first column appends, so the two must not share the one-launch attention kernel.
+    Cases: a 2-token prompt, a prompt of 1024 + 2 tokens, and 2 tokens after a cached prefix."""
+    cfg, tensors = small_hd128
+    mk = lambda: session.LlamaCudaPlan.from_tensors(  # noqa: E731
+        cfg, tensors, session.CudaSessionTarget(kv_f32=True, max_context=1100)).prepare()
+    oracle = O.OracleModel(cfg, tensors, threads=4)
+    pair = [17, 301]
+    s = mk()
+    got = s.prefill_ids(pair)
+    assert_logits_close(got, oracle.forward(pair, O.MODE_FAST))
+    steps = mk()
+    steps.run_token(pair[0])
+    assert np.abs(steps.run_token(pair[1]) - got).max() <= 1e-4
+    # 1026 tokens: a 1024-token tensor-core chunk, then a 2-token chunk
+    long_prompt = synth.prompt_ids(cfg, 1026, seed=5)
+    oracle.reset()
+    want = oracle.forward(long_prompt, O.MODE_FAST)
+    s = mk()
+    assert_logits_close(s.prefill_ids(long_prompt), want)
+    # 2 tokens after 5 cached ones (what a prefix-cache hit leaves to prefill)
+    oracle.reset()
+    want = oracle.forward(long_prompt[:7], O.MODE_FAST)
+    s = mk()
+    s.prefill_ids(long_prompt[:5], want_logits=False)
+    assert_logits_close(s.prefill_ids(long_prompt[5:7]), want)
+
+
+def test_gguf_without_stop_keys_stops_on_token_zero():
+    """rustgrad takes the stop ids from the tokenizer: without `tokenizer.ggml.eos_token_id` the eos
+    id is 0 (src/tokenizer/mod.rs:284-296, model.rs:288-292).  The embedding rows of token 0 and of
+    the token this model emits first are swapped (the head is tied; the prompt is renamed alike), so the
+    greedy run emits 0."""
+    cfg = dict(synth.TINY)
+    tensors = synth.build_tensors(cfg, seed=0, body_type=quant.Q8_0)
+    prompt = synth.prompt_ids(cfg, 16, seed=1)
+    base = O.OracleModel(cfg, tensors, threads=1)
+    first = base.generate_greedy(prompt, 1, O.MODE_STRICT)[0][0]
+    assert first != 0
+    kind, rows, cols, data = tensors["token_embd.weight"]
+    emb = data.reshape(rows, -1).copy()
+    emb[[0, first]] = emb[[first, 0]]
+    swapped = dict(tensors)
+    swapped["token_embd.weight"] = (kind, rows, cols, emb.reshape(-1))
+    # the same renaming in the prompt: the model now behaves as before with ids 0 and `first` exchanged
+    prompt = np.where(prompt == first, 0, np.where(prompt == 0, first, prompt)).astype(np.int32)
+    data = synth.gguf_bytes(cfg, swapped)  # the writer emits no eos / eot key
+    g = session.GgufFile(data)
+    got_cfg = g.llama_config()
+    g.close()
+    assert got_cfg["eos_id"] == 0 and got_cfg["eot_id"] == -1
+    s = make_session(data, kv_f32=True)
+    gen = s.generate_ids(prompt, 8)
+    assert gen.generated_ids == [0] and gen.stopped and s.position() == 16
+    # the checker with the reference's default agrees; with no stop id the run goes on
+    oracle = O.OracleModel(dict(cfg, eos_id=0), swapped, threads=1)
+    assert oracle.generate_greedy(prompt, 8, O.MODE_STRICT) == ([0], True)
+
+
+def test_bounded_device_wait_that_runs_out_is_a_timeout_then_poisoned(tiny):
+    """A device-side wait never spins for ever: it gives up, records a status and the kernel
+    returns.  The hook launches the exchange kernel against a flag nobody writes with a short poll
+    limit; the step that follows reports the time-out and the session refuses further work."""
+    cfg, tensors, data, prompt = tiny
+    s = make_session(data, kv_f32=True)
+    s.prefill_ids(prompt[:4])
+    before = session.launch_count("tp_exchange")
+    s.expire_device_wait()
+    assert session.launch_count("tp_exchange") == before + 1
+    with pytest.raises(session.Timeout):
+        s.run_token(3)
+    assert s.position() == 4
+    with pytest.raises(session.Poisoned):
+        s.run_token(3)
+    with pytest.raises(session.Poisoned):
+        s.reset_sequence()
+    # other sessions of the process are untouched
+    assert np.isfinite(make_session(data, kv_f32=True).prefill_ids(prompt)).all()

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from oracle import oracle as O
-from rustgrad_b200 import quant, session
+from rustgrad_b200 import quant, session, synth
 
 pytestmark = pytest.mark.gpu
 
@@ -86,6 +86,33 @@ def test_qmatmul_matches_f64_blockwise_plan(kind, n, k):
         err = rel_err(got, want, x, dense)
         assert err.max() < 2e-6, (m, err.max())
         assert np.abs(got - want).max() <= 1e-3 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("kind", [quant.Q4_0, quant.Q8_0], ids=["q4_0", "q8_0"])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)])
+def test_qmatmul_at_the_decode_sweep_shapes(kind, n, k):
+    """The isolated GEMV sweep at its own sizes: weights N(0, 0.02) quantized to Q4_0 / Q8_0,
+    activations N(0, 1), 1, 2, 4 and 8 rows (1-2: integer tensor-core kernel, 4-8: f16-MMA kernel),
+    against the f64 blockwise plan.  Same bars as the small shapes above."""
+    rng = np.random.default_rng(3)
+    data = synth.device_weight(kind, n, k, seed=2)
+    x8 = rng.standard_normal((8, k), dtype=np.float32)
+    want8 = O.quantized_matmul(kind, data, n, k, x8)
+    bb = quant.BLOCK_BYTES[kind]
+    rows = data.reshape(n, k // 32 * bb)
+    wnorm = np.empty(n)
+    for r0 in range(0, n, 8192):  # row norms of the decoded weight, a slab at a time
+        slab = O.dequantize(kind, rows[r0:r0 + 8192].reshape(-1), rows[r0:r0 + 8192].shape[0] * k)
+        wnorm[r0:r0 + 8192] = np.sqrt((slab.reshape(-1, k).astype(np.float64) ** 2).sum(axis=1))
+    i8, f16 = session.launch_count("qgemv_i8"), session.launch_count("qgemv")
+    for m in (1, 2, 4, 8):
+        got = session.qmatmul(kind, data, n, k, x8[:m])
+        want = want8[:m]
+        scale = np.sqrt((x8[:m].astype(np.float64) ** 2).sum(axis=1))[:, None] * wnorm[None, :]
+        err = np.abs(got.astype(np.float64) - want.astype(np.float64)) / scale
+        assert err.max() < 2e-6, (m, err.max())
+        assert np.abs(got - want).max() <= 1e-3 * np.abs(want).max()
+    assert session.launch_count("qgemv_i8") == i8 + 2 and session.launch_count("qgemv") == f16 + 2
 
 
 def test_qmatmul_more_than_eight_rows_and_dense_weights():

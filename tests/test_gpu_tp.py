@@ -1,5 +1,7 @@
-"""Tensor-parallel session on 2 GPUs (one process per GPU, NCCL) against the CPU checker and the
-single-GPU session.  Skipped when fewer than two devices are visible."""
+"""Tensor-parallel session on 2, 4 and 8 GPUs (one process per GPU, NCCL) against the CPU checker and
+the single-GPU session.  A case is skipped when fewer devices are visible than it needs.  The
+model has 16 query heads over 8 kv heads, so a rank owns 4, 2 or 1 kv heads as the 70B shape does
+at the same world sizes."""
 import os
 import socket
 
@@ -10,8 +12,8 @@ from rustgrad_b200 import quant, synth
 
 pytestmark = pytest.mark.gpu
 
-CFG = synth.scaled(synth.TINY, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn_dim=1024, vocab=640, n_layers=2,
-                   rope_theta=500000.0)
+CFG = synth.scaled(synth.TINY, d_model=1024, n_heads=16, n_kv_heads=8, head_dim=128, ffn_dim=2048, vocab=640, n_layers=2,
+                   rope_theta=500000.0, max_context=128)
 
 
 def free_port():
@@ -47,22 +49,26 @@ def worker(rank, world, port, out_dir, fused=True):
     ids_loop, _ = s.decode_loop([tok], 5)  # graph replays with the exchange kernel inside
     np.save(os.path.join(out_dir, f"loop{rank}.npy"), ids_loop[:, 0])
     np.save(os.path.join(out_dir, f"peer{rank}.npy"), np.array([s.report()["peer_reduce_launches"]]))
+    # a 40-token prompt: exchanges of more than 32 columns go through ncclAllReduce even with the peer kernel on
+    s.reset_sequence()
+    np.save(os.path.join(out_dir, f"long{rank}.npy"), s.prefill_ids(synth.prompt_ids(CFG, 40, seed=3)))
     dist.barrier()
     s.close()
     dist.destroy_process_group()
 
 
-def test_two_gpu_tensor_parallel_matches_single_gpu_and_cpu_path(tmp_path):
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tensor_parallel_matches_single_gpu_and_cpu_path(tmp_path, world):
     import torch
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     from oracle import oracle as O
     from rustgrad_b200 import session
-    mp.spawn(worker, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
-    l0, l1 = np.load(tmp_path / "logits0.npy"), np.load(tmp_path / "logits1.npy")
-    i0, i1 = np.load(tmp_path / "ids0.npy"), np.load(tmp_path / "ids1.npy")
-    assert np.array_equal(l0, l1) and np.array_equal(i0, i1)  # every rank holds identical logits
+    mp.spawn(worker, args=(world, free_port(), str(tmp_path)), nprocs=world, join=True)
+    l0, i0 = np.load(tmp_path / "logits0.npy"), np.load(tmp_path / "ids0.npy")
+    for r in range(1, world):  # every rank holds identical logits
+        assert np.array_equal(l0, np.load(tmp_path / f"logits{r}.npy")) and np.array_equal(i0, np.load(tmp_path / f"ids{r}.npy"))
     tensors = synth.build_tensors(CFG, seed=6, body_type=quant.Q4_0, embed_type=quant.Q8_0, head_type=quant.Q8_0, tied_head=False)
     oracle = O.OracleModel(CFG, tensors, threads=4)
     prompt = synth.prompt_ids(CFG, 11, seed=2)
@@ -77,16 +83,21 @@ def test_two_gpu_tensor_parallel_matches_single_gpu_and_cpu_path(tmp_path):
     single = session.LlamaCudaPlan.from_tensors(CFG, tensors, session.CudaSessionTarget(kv_f32=True)).prepare()
     assert np.abs(single.prefill_ids(prompt) - l0[0]).max() <= 1e-4
     # the partial sums went through the peer-memory kernel, and the graph-replayed loop agrees with the checker
-    assert np.load(tmp_path / "peer0.npy")[0] > 0 and np.load(tmp_path / "peer1.npy")[0] > 0
+    assert all(np.load(tmp_path / f"peer{r}.npy")[0] > 0 for r in range(world))
     loop_want = []
     t = ids[-1]
     for _ in range(5):
         t = O.select_greedy(oracle.forward([t]))
         loop_want.append(t)
-    assert np.load(tmp_path / "loop0.npy").tolist() == loop_want == np.load(tmp_path / "loop1.npy").tolist()
+    assert all(np.load(tmp_path / f"loop{r}.npy").tolist() == loop_want for r in range(world))
+    oracle.reset()
+    long_want = oracle.forward(synth.prompt_ids(CFG, 40, seed=3))
+    for r in range(world):
+        diff = np.abs(np.load(tmp_path / f"long{r}.npy") - long_want).max()
+        assert diff <= 1e-2 and diff <= 1e-3 * np.abs(long_want).max() + 1e-6
     # the same run through NCCL all-reduce + add gives the same logits up to summation order
     nccl_dir = tmp_path / "nccl"
     nccl_dir.mkdir()
-    mp.spawn(worker, args=(2, free_port(), str(nccl_dir), False), nprocs=2, join=True)
+    mp.spawn(worker, args=(world, free_port(), str(nccl_dir), False), nprocs=world, join=True)
     assert np.load(nccl_dir / "peer0.npy")[0] == 0
     assert np.abs(np.load(nccl_dir / "logits0.npy") - l0).max() <= 1e-4

@@ -15,6 +15,7 @@ import ctypes as C
 import numpy as np
 import pytest
 
+from oracle import oracle as O
 from rustgrad_b200 import _lib, session
 
 pytestmark = pytest.mark.gpu
@@ -60,6 +61,9 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point():
         got = run_noalloc(q, k, v, ctx)
         assert np.isfinite(got).all()
         assert np.abs(got - want).max() <= 1e-6, (heads, n_pos)
+        # and against the CPU checker's softmax composition (summation order differs: 2e-5)
+        ref = O.attention_decode(q, k.astype(np.float32), v.astype(np.float32))
+        assert np.abs(got - ref).max() <= 2e-5, (heads, n_pos)
 
 
 def test_sizes_beyond_the_fixed_array_are_refused():
@@ -74,3 +78,9 @@ def test_sizes_beyond_the_fixed_array_are_refused():
     assert L.rg_b200_attention_decode_noalloc(p, p, p, 64, 8, 128, 64, 65, 0, p, None, 1) == 1   # n_pos > ctx
     assert L.rg_b200_attention_decode_noalloc(p, p, p, 6, 2, 96, 64, 1, 0, p, None, 1) == 20     # head geometry
     assert L.rg_b200_attention_decode_noalloc(None, p, p, 8, 2, 128, 64, 1, 0, p, None, 1) == 1  # null pointer
+    # a cache pointer cut from the middle of an arena at an odd offset would fault the bulk copies
+    odd = C.c_void_p(buf.data_ptr() + 4)
+    assert L.rg_b200_attention_decode_noalloc(p, odd, p, 8, 2, 128, 64, 1, 0, p, None, 1) == 1
+    assert L.rg_b200_attention_decode_noalloc(p, p, odd, 8, 2, 128, 64, 1, 0, p, None, 1) == 1
+    assert b"16-byte" in L.rg_b200_last_error()
+    assert L.rg_b200_attention_decode_noalloc(C.c_void_p(buf.data_ptr() + 2), p, p, 8, 2, 128, 64, 1, 0, p, None, 1) == 1
