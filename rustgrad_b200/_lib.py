@@ -7,8 +7,11 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
+import os
+
 HERE = Path(__file__).resolve().parent
-LIB_PATH = HERE / "librg_b200.so"
+# RG_B200_LIB names another build of the library (a development variant); the default is the in-tree build
+LIB_PATH = Path(os.environ["RG_B200_LIB"]) if os.environ.get("RG_B200_LIB") else HERE / "librg_b200.so"
 
 
 class LlamaConfig(C.Structure):

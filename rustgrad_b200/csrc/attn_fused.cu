@@ -379,8 +379,59 @@ __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnA
         }
     }
     float *dst = A.out + (size_t)c * A.heads * HD + (size_t)(kvh * G + gq) * HD + d;
-    dst[0] = __fmul_rn(a0, ml[gq * 2 + 1]);
-    dst[1] = __fmul_rn(a1, ml[gq * 2 + 1]);
+    const float o0 = __fmul_rn(a0, ml[gq * 2 + 1]), o1 = __fmul_rn(a1, ml[gq * 2 + 1]);
+    dst[0] = o0;
+    dst[1] = o1;
+    if (A.pack_out) {
+      // The sixteen lanes of a half-warp hold one 32-element block of the output projection's input
+      // (lane j: elements 2j, 2j + 1): pack it as block fixed point for the integer GEMV (rg_device.cuh).
+      const int e_glob = (kvh * G + gq) * HD + d, kbo = e_glob >> 5, j = lane & 15;
+      const int kb_all = A.heads * HD / 32;
+      const bool q4 = A.pack_type == RG_TYPE_Q4_0;
+      float m = fmaxf(fabsf(o0), fabsf(o1));
+#pragma unroll
+      for (int off = 1; off < 16; off <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+      const unsigned bad = __ballot_sync(0xffffffffu, !(fabsf(o0) <= 3.0e38f) || !(fabsf(o1) <= 3.0e38f));
+      if ((bad >> (lane & 16)) & 0xFFFFu) m = __uint_as_float(0x7f800000u);  // keep NaN / inf visible
+      const uint32_t E = __float_as_uint(m) >> 23, XBITS = q4 ? 25u : 29u;
+      float sc_b = 0.0f;
+      int X0 = 0, X1 = 0;
+      if (E >= 40u && E < 255u) {
+        sc_b = __uint_as_float((E - XBITS) << 23);
+        const float up = __uint_as_float((254u + XBITS - E) << 23);
+        X0 = __float2int_rn(o0 * up);
+        X1 = __float2int_rn(o1 * up);
+      } else if (E == 255u) {
+        sc_b = __uint_as_float(0x7fc00000u);
+        X0 = j == 0 ? 1 : 0;
+      }
+      int t_lo = 0, t_hi = 0;
+      if (q4) {
+        int sum = X0 + X1;
+#pragma unroll
+        for (int off = 1; off < 16; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        t_lo = (sum & 0x1FF) << 7;
+        t_hi = sum >> 9;
+        const int p0 = __shfl_xor_sync(0xffffffffu, X0, 8), p1 = __shfl_xor_sync(0xffffffffu, X1, 8);
+        if (j < 8) {
+          X0 <<= 4;
+          X1 <<= 4;
+        } else {
+          X0 -= p0 << 4;
+          X1 -= p1 << 4;
+        }
+      }
+      const uint32_t Y0 = (uint32_t)X0 + 0x80808080u, Y1 = (uint32_t)X1 + 0x80808080u;
+      uint8_t *dq = A.pack_out + (size_t)kbo * 128 + ((j & 7) >> 1) * 8 + (j >> 3) * 4 + (j & 1) * 2;
+#pragma unroll
+      for (int dg = 0; dg < 4; ++dg) {
+        const uint32_t b0 = ((Y0 >> (8 * dg)) & 0xFFu) ^ 0x80u, b1 = ((Y1 >> (8 * dg)) & 0xFFu) ^ 0x80u;
+        *reinterpret_cast<uint16_t *>(dq + dg * 32) = (uint16_t)(b0 | (b1 << 8));
+      }
+      if (j == 0)
+        *reinterpret_cast<float4 *>(A.pack_out + xq_side_offset(kb_all) + (size_t)kbo * 16) =
+            make_float4(sc_b, __int_as_float(t_lo), sc_b, __int_as_float(t_hi));
+    }
   }
 }
 
@@ -457,6 +508,7 @@ cudaError_t launch_attention_fused(const FusedAttnArgs &a, const LaunchCfg &cfg)
   if (!fused_attention_supported(a.heads, a.kv_heads, a.hd) || a.cols < 1 || !a.counters || !a.scratch || !a.out ||
       a.max_splits > fused_attn_split_cap())
     return cudaErrorInvalidValue;
+  if (a.pack_out && (a.cols != 1 || (reinterpret_cast<uintptr_t>(a.pack_out) & 127))) return cudaErrorInvalidValue;
   switch (a.heads / a.kv_heads) {
     case 1: return launch_g<1>(a, cfg);
     case 2: return launch_g<2>(a, cfg);

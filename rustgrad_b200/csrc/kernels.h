@@ -71,8 +71,20 @@ struct GemvI8Args {
   int epi = EPI_STORE;
   float *y = nullptr;
   int ldy = 0;
+  // Batch 1 only.  xq: the input vector already packed by the kernel that produced it
+  // (qgemv_i8_xq_bytes(k) bytes, 128-byte aligned); x, col_map and norm_w are then unused, and with
+  // xq_norm the results are scaled by 1 / sqrt(mean(x^2) + eps) taken from the vector's block sums
+  // (the producer folded the norm weight into the packed values).
+  const uint8_t *xq = nullptr;
+  bool xq_norm = false;
+  // EPI_RESIDUAL, batch 1, rows a multiple of 32: besides y, write the new rows packed as the input
+  // of the next GEMV, whose block type is pack_type, with pack_w (nullable) folded in.
+  uint8_t *pack_out = nullptr;
+  const float *pack_w = nullptr;
+  int pack_type = 0;
 };
 bool qgemv_i8_supported(int k, int batch);
+size_t qgemv_i8_xq_bytes(int k);
 cudaError_t launch_qgemv_i8(const GemvI8Args &a, const LaunchCfg &cfg);
 
 // tcgen05 GEMM for many tokens: out[m][n] = x[m][k] (16-bit) . W[n][k]^T with W in Q4_0 / Q8_0 blocks
@@ -216,6 +228,10 @@ struct FusedAttnArgs {
   // the launch may read positions, rotation tables and cached rows before its grid dependency
   // resolves: only when an earlier attention launch of the same step separates it from their writers
   bool early = false;
+  // cols == 1: also leave the output packed as the input of the integer GEMV of the output
+  // projection (qgemv_i8_xq_bytes(heads * hd) bytes; pack_type = that projection's block type)
+  uint8_t *pack_out = nullptr;
+  int pack_type = 0;
 };
 bool fused_attention_supported(int heads, int kv_heads, int hd);
 int fused_attn_per_head(int sm_count, int kv_heads, int cols);

@@ -26,7 +26,19 @@
 //  * Weight streaming is the same as in qgemv.cu: persistent CTA per SM, tiled 2-D TMA boxes of
 //    8 rows into a 3-6 stage mbarrier pipeline with bounded waits, bank-conflict-free pitch, weight
 //    prefetch issued before the grid dependency wait.
+//  * Warp roles: 16 consumer warps (MMA), four per scheduler, one producer warp (TMA), one epilogue warp.  At the end
+//    of a row group the consumers fold their accumulators into one value per row, drop them into one
+//    of two shared buffers and arrive on an mbarrier; the epilogue warp sums the 16 partials in warp
+//    order and applies the epilogue while the consumers are already in the next row group.
+//  * Batch 1 can take its activations already packed (`xq`): the kernel that produced the vector
+//    wrote the digit planes, the per-block side words and a per-block sum of squares, and this
+//    kernel's prologue is one bulk copy into shared memory.  RMSNorm then runs in deferred form:
+//    the producer folds the norm weight into the packed values, and 1 / sqrt(mean(x^2) + eps), a
+//    scalar, multiplies the finished dot products (x.w is packed instead of (x.inv).w: one rounding
+//    moves, far inside the 1e-3 bar).  The residual epilogue is such a producer (`pack_out`).
 #include <cuda.h>
+
+#include <stdlib.h>
 
 #include <type_traits>
 
@@ -39,9 +51,11 @@ namespace {
 
 constexpr int R = 32;     // weight rows per stage: two m16 tiles
 constexpr int BOXR = 8;   // rows per TMA box
-constexpr int CW = 14;    // consumer warps
+constexpr int CW = 16;    // consumer warps: four per scheduler
 constexpr int MAX_STAGES = 6;
-constexpr int THREADS = (CW + 1) * 32;
+constexpr int THREADS = (CW + 2) * 32;  // consumers, producer warp, epilogue warp
+constexpr int HDR_BYTES = 256;          // mbarriers and flags at the start of shared memory
+constexpr int RED_BYTES = 2 * CW * R * 2 * 4;  // [2 buffers][CW][R][batch <= 2] partial sums
 // One CTA per SM.  (Letting two CTAs share an SM so that the next kernel could move in early under
 // programmatic dependent launch was measured slower: freed slots fill unevenly and some SMs end up
 // with two CTAs of the same kernel.)
@@ -52,9 +66,16 @@ template <int QT>
 struct Geo {
   static constexpr bool Q4 = (QT == RG_TYPE_Q4_0);
   static constexpr int BB = Q4 ? 18 : 34;
-  static constexpr int KC = Q4 ? 56 : 40;  // blocks per stage; pitch 1008 / 1360 bytes (28 / 20 banks mod 32)
-  static constexpr int RS = KC * BB;
-  static_assert(RS % 16 == 0 && (BOXR * RS) % 128 == 0 && RS / 8 <= 256, "TMA box geometry");
+  // Blocks per stage: 32 pairs (Q4_0) or 16 pairs (Q8_0), a whole number of rounds of the 16 consumer
+  // warps, and a divisor of every K that is a multiple of 2048 / 1024 elements.  A row of a stage
+  // is the chunk's bytes plus 16 bytes of padding (the TMA box simply reaches 16 bytes into the
+  // next chunk): pitch 1168 / 1104 bytes = 4 / 20 words mod 32, so the eight rows of a fragment
+  // load fall into distinct banks.
+  static constexpr int KC = Q4 ? 64 : 32;
+  static constexpr int CHUNK_BYTES = KC * BB;
+  static constexpr int RS = CHUNK_BYTES + 16;
+  static_assert(CHUNK_BYTES % 16 == 0 && RS % 16 == 0 && (BOXR * RS) % 128 == 0 && RS / 8 <= 256, "TMA box geometry");
+  static_assert((RS / 4) % 8 == 4, "bank-conflict-free pitch");
 };
 
 struct Params {
@@ -73,7 +94,14 @@ struct Params {
   int rows_per_cta;
   int stages;
   int *status;
+  const uint8_t *xq;    // batch 1: activations already packed (see xq_* below); x / norm_w unused
+  int xq_norm;          // the packed values carry the norm weight: scale the results by inv_rms from the block sums
+  uint8_t *pack_out;    // EPI_RESIDUAL, batch 1: also write the new rows packed for the next GEMV
+  const float *pack_w;  // norm weight folded into the packed output (nullable)
+  int pack_q4;          // block type of the GEMV that will read pack_out: 1 Q4_0, 0 Q8_0
 };
+
+// (layout of a packed activation vector in global memory: xq_side_offset / xq_ssq_offset in rg_device.cuh)
 
 template <int OFF>
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
@@ -206,17 +234,21 @@ __global__ void __launch_bounds__(THREADS, 1)
   using G = Geo<QT>;
   constexpr bool PAIR = (EPI == EPI_SWIGLU);
   constexpr int GROUP_ROWS = PAIR ? 16 : 32;
+  constexpr int NB = B1 ? 1 : 2;  // batch columns a partial-sum slot holds
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
   uint64_t *empty = full + MAX_STAGES;
-  volatile int *dead = reinterpret_cast<volatile int *>(empty + MAX_STAGES);
-  float *red = reinterpret_cast<float *>(smem + 128);  // [CW][R][4]; also scratch of the prologue
-  constexpr int RED_BYTES = CW * R * 4 * 4;
-  static_assert(RED_BYTES % 128 == 0, "alignment");
+  uint64_t *red_full = empty + MAX_STAGES;  // [2]: the consumers' partial sums of a row group are in place
+  uint64_t *red_free = red_full + 2;        // [2]: the epilogue warp has read them
+  uint64_t *xbar = red_free + 2;            // bulk copy of pre-packed activations
+  volatile int *dead = reinterpret_cast<volatile int *>(xbar + 1);
+  static_assert((2 * MAX_STAGES + 5) * 8 + 4 <= HDR_BYTES, "header");
+  float *red = reinterpret_cast<float *>(smem + HDR_BYTES);  // [2][CW][R][NB]; also scratch of the prologue
+  static_assert(RED_BYTES % 128 == 0 && HDR_BYTES % 128 == 0, "alignment");
   const int S = 4 * P.batch;
   const int xs_bytes = (P.kb * S * 32 + 127) & ~127;
   const int sb_bytes = (P.kb * P.batch * 16 + 127) & ~127;
-  uint8_t *xs = smem + 128 + RED_BYTES;
+  uint8_t *xs = smem + HDR_BYTES + RED_BYTES;
   float *sb = reinterpret_cast<float *>(xs + xs_bytes);
   uint8_t *stage0 = xs + xs_bytes + sb_bytes;
   constexpr int STAGE_BYTES = R * G::RS;
@@ -235,11 +267,116 @@ __global__ void __launch_bounds__(THREADS, 1)
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], CW);
     }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&red_full[b], CW);
+      mbar_init(&red_free[b], 1);
+    }
+    mbar_init(xbar, 1);
     *dead = 0;
     mbar_fence_init();
   }
   __syncthreads();
   pdl_launch_dependents();
+
+  // 1 / sqrt(mean(x^2) + eps) from the per-block sums of squares of a pre-packed vector; every warp
+  // that needs it computes it alone, in the same order
+  auto inv_from_blocks = [&]() {
+    const float *ssq = reinterpret_cast<const float *>(P.xq + xq_ssq_offset(P.kb));
+    float ss = 0.0f;
+    for (int i = lane; i < P.kb; i += 32) ss += __ldcg(ssq + i);
+    ss = warp_sum(ss);
+    const float mean = __fdiv_rn(ss, (float)(P.kb * 32));
+    return __frcp_rn(__fsqrt_rn(__fadd_rn(mean, P.eps)));
+  };
+
+  // One row group's epilogue, run by a whole warp (lane = row of the group): sum the consumer warps'
+  // partials in warp order, scale, apply the epilogue, optionally pack the new rows.
+  constexpr float A_SCALE = G::Q4 ? 0.0625f : 1.0f;  // the Q4_0 digit sums carry a factor 16
+  auto group_epilogue = [&](int grp, float out_scale, auto wait_for_partials) {
+      const int buf = grp & 1;
+      const int vr0 = r_begin + grp * GROUP_ROWS;
+      const int vrow = vr0 + lane;
+      float resid[NB];
+#pragma unroll
+      for (int b = 0; b < NB; ++b) resid[b] = 0.0f;
+      if (EPI == EPI_RESIDUAL && vrow < r_end) {  // requested before the wait: off the critical path
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+          if (b < P.batch) resid[b] = P.y[(size_t)b * P.ldy + vrow];
+      }
+      float pw = 1.0f;
+      if (EPI == EPI_RESIDUAL && B1 && P.pack_out && P.pack_w && vrow < r_end) pw = __ldg(P.pack_w + vrow);
+      wait_for_partials();
+      float tot[NB];
+#pragma unroll
+      for (int b = 0; b < NB; ++b) tot[b] = 0.0f;
+      const float *rb = red + (size_t)buf * CW * R * NB + lane * NB;
+#pragma unroll
+      for (int w = 0; w < CW; ++w)
+#pragma unroll
+        for (int b = 0; b < NB; ++b) tot[b] += rb[w * R * NB + b];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&red_free[buf]);
+#pragma unroll
+      for (int b = 0; b < NB; ++b) tot[b] *= out_scale;
+      float xn[NB];
+      if constexpr (EPI == EPI_SWIGLU) {
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          const float up = __shfl_down_sync(0xffffffffu, tot[b], 16);
+          xn[b] = 0.0f;
+          if (lane < 16 && vrow < r_end && b < P.batch) P.y[(size_t)b * P.ldy + vrow] = swiglu(tot[b], up);
+        }
+      } else {
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          xn[b] = EPI == EPI_RESIDUAL ? __fadd_rn(resid[b], tot[b]) : tot[b];
+          if (vrow < r_end && b < P.batch) P.y[(size_t)b * P.ldy + vrow] = xn[b];
+        }
+      }
+      if constexpr (EPI == EPI_RESIDUAL && B1) {
+        if (P.pack_out) {
+          // the 32 new rows are block vr0 / 32 of the next GEMV's input: pack them here (the launcher
+          // gives every CTA whole blocks), with that GEMV's norm weight folded in
+          const int kbo = vr0 >> 5;
+          const int kb_all = P.n_rows >> 5;
+          const float ssq = warp_sum(__fmul_rn(xn[0], xn[0]));
+          const float val = __fmul_rn(xn[0], pw);
+          float m = warp_max(fabsf(val));
+          if (__any_sync(0xffffffffu, !(fabsf(val) <= 3.0e38f))) m = __uint_as_float(0x7f800000u);  // keep NaN / inf visible
+          const uint32_t E = __float_as_uint(m) >> 23;
+          const uint32_t XBITS = P.pack_q4 ? 25u : 29u;
+          float s = 0.0f;
+          int X = 0;
+          if (E >= 40u && E < 255u) {
+            s = __uint_as_float((E - XBITS) << 23);
+            X = __float2int_rn(val * __uint_as_float((254u + XBITS - E) << 23));
+          } else if (E == 255u) {
+            s = __uint_as_float(0x7fc00000u);
+            X = lane == 0 ? 1 : 0;
+          }
+          int t_lo = 0, t_hi = 0;
+          if (P.pack_q4) {
+            int sum = X;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            t_lo = (sum & 0x1FF) << 7;
+            t_hi = sum >> 9;
+            const int partner = __shfl_xor_sync(0xffffffffu, X, 16);
+            X = lane < 16 ? X << 4 : X - (partner << 4);
+          }
+          const uint32_t Y = (uint32_t)X + 0x80808080u;
+          uint8_t *dst = P.pack_out + (size_t)kbo * 128 + ((lane & 15) >> 2) * 8 + (lane >> 4) * 4 + (lane & 3);
+#pragma unroll
+          for (int d = 0; d < 4; ++d) dst[d * 32] = (uint8_t)(((Y >> (8 * d)) & 0xFFu) ^ 0x80u);
+          if (lane == 0) {
+            *reinterpret_cast<float4 *>(P.pack_out + xq_side_offset(kb_all) + (size_t)kbo * 16) =
+                make_float4(s, __int_as_float(t_lo), s, __int_as_float(t_hi));
+            reinterpret_cast<float *>(P.pack_out + xq_ssq_offset(kb_all))[kbo] = ssq;
+          }
+        }
+      }
+  };
 
   if (warp == CW) {
     // ------------------------------------------------------------------ producer (weights only:
@@ -271,7 +408,7 @@ __global__ void __launch_bounds__(THREADS, 1)
             }
           }
         }
-        tma_box_2d(sw + lane * BOXR * G::RS, map, c * (G::RS / 8), row, &full[stage]);
+        tma_box_2d(sw + lane * BOXR * G::RS, map, c * (G::CHUNK_BYTES / 8), row, &full[stage]);
       }
       if (++c == n_chunks) {
         c = 0;
@@ -281,6 +418,35 @@ __global__ void __launch_bounds__(THREADS, 1)
         stage = 0;
         ++round;
       }
+    }
+    return;
+  }
+
+  if (warp == CW + 1) {
+    // ------------------------------------------------------------------ epilogue warp
+    if (n_groups == 0) return;
+    pdl_wait();  // the residual rows, the block sums and every store below touch the step's buffers
+    float out_scale = A_SCALE;
+    if (P.xq && P.xq_norm) out_scale *= inv_from_blocks();
+    for (int grp = 0; grp < n_groups; ++grp) {
+      const int buf = grp & 1;
+      group_epilogue(grp, out_scale, [&]() {
+        // a row group takes microseconds: poll with a pause so this warp leaves the issue slots to the consumers
+        {
+          bool ok = *dead != 0;
+          for (uint32_t i = 0; !ok && i < (1u << 22); ++i) {
+            ok = mbar_try_wait(&red_full[buf], (uint32_t)((grp >> 1) & 1));
+            if (!ok) {
+              __nanosleep(100);
+              if ((i & 1023u) == 1023u && *dead) break;
+            }
+          }
+          if (!ok && !*dead) {
+            *dead = 1;
+            if (P.status) atomicExch(P.status, DEV_TIMEOUT);
+          }
+        }
+      });
     }
     return;
   }
@@ -385,7 +551,6 @@ __global__ void __launch_bounds__(THREADS, 1)
     for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(v[i], inv), w[i]);
   };
 
-  float resid0 = 0.0f;
   // Register-resident form (batch 1, up to four passes, three with a norm): the norm weights are
   // constant data and are fetched before the grid dependency resolves, the activation is read
   // once, and both uses (sum of squares, packing) run from registers as straight-line code.
@@ -408,8 +573,6 @@ __global__ void __launch_bounds__(THREADS, 1)
       xl[it] = xh[it] = zero;
       if (it * PASS_BLOCKS + kbw < P.kb) load8(xr, it * PASS_BLOCKS + kbw, xl[it], xh[it]);
     }
-    if (EPI == EPI_RESIDUAL && ctid < GROUP_ROWS * 2 && (ctid & 1) == 0 && r_begin + (ctid >> 1) < r_end)
-      resid0 = P.y[r_begin + (ctid >> 1)];  // the first row group's residual, off the epilogue's path
     float inv = 1.0f;
     if constexpr (NORM) {
       float ss = 0.0f;
@@ -427,7 +590,17 @@ __global__ void __launch_bounds__(THREADS, 1)
   };
   const int npass = (P.kb + PASS_BLOCKS - 1) / PASS_BLOCKS;
   using std::integral_constant;
-  if (B1 && npass <= (P.norm_w ? 3 : 4)) {
+  if (B1 && P.xq) {
+    // the producer of the vector packed it: one bulk copy of digits and side words
+    pdl_wait();
+    if (ctid == 0) {
+      const uint32_t db = (uint32_t)P.kb * 128u, sbb = (uint32_t)P.kb * 16u;
+      mbar_expect_tx(xbar, db + sbb);
+      bulk_g2s(xs, P.xq, db, xbar);
+      bulk_g2s(sb, P.xq + xq_side_offset(P.kb), sbb, xbar);
+    }
+    mbar_wait_bounded(xbar, 0, dead, P.status);
+  } else if (B1 && npass <= (P.norm_w ? 3 : 4)) {
     if (P.norm_w) {
       if (npass == 1) fast(integral_constant<int, 1>{}, integral_constant<bool, true>{});
       else if (npass == 2) fast(integral_constant<int, 2>{}, integral_constant<bool, true>{});
@@ -440,8 +613,6 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
   } else {
     pdl_wait();
-    if (EPI == EPI_RESIDUAL && ctid < GROUP_ROWS * 2 && (ctid & 1) < P.batch && r_begin + (ctid >> 1) < r_end)
-      resid0 = P.y[(size_t)(ctid & 1) * P.ldy + r_begin + (ctid >> 1)];
     for (int b = 0; b < P.batch; ++b) {
       const float *xr = P.x + (size_t)(P.col_map ? P.col_map[b] : b) * P.ldx;
       float inv = 1.0f;
@@ -486,26 +657,30 @@ __global__ void __launch_bounds__(THREADS, 1)
   const uint32_t sb_lane = smem_u32(sb) + (uint32_t)((B1 ? blk_sel : my_batch) * 16 + (t & 1) * 8);
   const uint32_t lane_w_off = (uint32_t)(g * G::RS + t * 4);
   const uint32_t lane_s_off = B1 ? (uint32_t)(g * G::RS + blk_sel * G::BB) : (uint32_t)(g * G::RS);
+  const float fold = (t & 1) ? 65536.0f : 1.0f;  // this lane's accumulators hold the low or the high digit pair
+  constexpr uint32_t PAIRB = 2 * G::BB;
   for (int u = 0; u < units; ++u) {
     const int nb = min(G::KC, P.kb - c * G::KC);
     mbar_wait_bounded(&full[stage], phase, dead, P.status);
     const uint32_t sw = smem_stage0 + (uint32_t)stage * (uint32_t)STAGE_BYTES;
-    uint32_t aw = sw + lane_w_off + (uint32_t)warp * (2 * G::BB);
-    uint32_t as = sw + lane_s_off + (uint32_t)warp * (2 * G::BB);
+    uint32_t aw = sw + lane_w_off + (uint32_t)warp * PAIRB;
+    uint32_t as = sw + lane_s_off + (uint32_t)warp * PAIRB;
     int gb = c * G::KC + 2 * warp;  // global block index of the pair's even block
     // rows 16..31 of a partial last group are not this CTA's: their boxes were not fetched
     const bool two_tiles = PAIR || r_end - (r_begin + grp * GROUP_ROWS) > 16;
-    for (int p = warp; 2 * p < nb; p += CW, aw += CW * 2 * G::BB, as += CW * 2 * G::BB, gb += 2 * CW) {
-      uint32_t wq[4][6], sc[4][2];
-      if constexpr (B1) {
-        load_slot_b1<QT, 0>(aw, as, wq[0], sc[0]);
-        load_slot_b1<QT, 1>(aw, as, wq[1], sc[1]);
+    if constexpr (B1) {
+      // one block pair of all 32 rows: loads, then two accumulating MMAs per m-tile, then scales
+      auto fetch = [&](uint32_t a, uint32_t s, int gbp, uint32_t (&wq)[4][6], uint32_t (&sc)[4][2], uint2 &xv, uint2 &side) {
+        load_slot_b1<QT, 0>(a, s, wq[0], sc[0]);
+        load_slot_b1<QT, 1>(a, s, wq[1], sc[1]);
         if (two_tiles) {
-          load_slot_b1<QT, 2>(aw, as, wq[2], sc[2]);
-          load_slot_b1<QT, 3>(aw, as, wq[3], sc[3]);
+          load_slot_b1<QT, 2>(a, s, wq[2], sc[2]);
+          load_slot_b1<QT, 3>(a, s, wq[3], sc[3]);
         }
-        const uint2 xv = lds64(xs_lane + (uint32_t)(gb * 128));
-        const uint2 side = lds64(sb_lane + (uint32_t)(gb * 16));
+        xv = lds64(xs_lane + (uint32_t)(gbp * 128));
+        side = lds64(sb_lane + (uint32_t)(gbp * 16));
+      };
+      auto math = [&](const uint32_t (&wq)[4][6], const uint32_t (&sc)[4][2], const uint2 &xv, const uint2 &side) {
         const float sv = __uint_as_float(side.x);
         const int off = G::Q4 ? (int)side.y : 0;
         const bool ev = g < 4;
@@ -517,98 +692,88 @@ __global__ void __launch_bounds__(THREADS, 1)
           uint32_t ae[2][2], ao[2][2];
           expand<QT>(wq[mt * 2], ae[0], ao[0]);
           expand<QT>(wq[mt * 2 + 1], ae[1], ao[1]);
-          int c[4];
-          mma_i8<G::Q4>(c, ae[0][0], ae[1][0], ao[0][0], ao[1][0], b_lo0, b_lo1);
-          mma_i8_acc<G::Q4>(c, ae[0][1], ae[1][1], ao[0][1], ao[1][1], b_hi0, b_hi1);
-          const float f0 = (float)(c[0] + (c[1] << 8) - off), f1 = (float)(c[2] + (c[3] << 8) - off);
+          int cc[4];
+          mma_i8<G::Q4>(cc, ae[0][0], ae[1][0], ao[0][0], ao[1][0], b_lo0, b_lo1);
+          mma_i8_acc<G::Q4>(cc, ae[0][1], ae[1][1], ao[0][1], ao[1][1], b_hi0, b_hi1);
+          const float f0 = (float)(cc[0] + (cc[1] << 8) - off), f1 = (float)(cc[2] + (cc[3] << 8) - off);
           acc[mt][0] = fmaf(half_bits_to_float(sc[mt * 2][0]) * sv, f0, acc[mt][0]);
           acc[mt][1] = fmaf(half_bits_to_float(sc[mt * 2 + 1][0]) * sv, f1, acc[mt][1]);
         }
-        continue;
+      };
+      for (int p = warp; 2 * p < nb; p += CW, aw += CW * PAIRB, as += CW * PAIRB, gb += 2 * CW) {
+        uint32_t wa[4][6], sa[4][2];
+        uint2 xa, sda;
+        fetch(aw, as, gb, wa, sa, xa, sda);
+        math(wa, sa, xa, sda);
       }
-      load_slot<QT, 0>(aw, as, wq[0], sc[0]);
-      load_slot<QT, 1>(aw, as, wq[1], sc[1]);
-      load_slot<QT, 2>(aw, as, wq[2], sc[2]);
-      load_slot<QT, 3>(aw, as, wq[3], sc[3]);
-      uint2 xe = make_uint2(0, 0), xo = make_uint2(0, 0);
-      if (col_live) {
-        xe = lds64(xs_lane + (uint32_t)(gb * S * 32));
-        xo = lds64(xs_lane + (uint32_t)((gb + 1) * S * 32));
-      }
-      float se = 0.0f, so = 0.0f;
-      int offe = 0, offo = 0;
-      if (acc_live) {
-        const uint2 sde = lds64(sb_lane + (uint32_t)(gb * P.batch * 16));
-        const uint2 sdo = lds64(sb_lane + (uint32_t)((gb + 1) * P.batch * 16));
-        se = __uint_as_float(sde.x);
-        so = __uint_as_float(sdo.x);
-        if constexpr (G::Q4) {
-          offe = (int)sde.y;
-          offo = (int)sdo.y;
+    } else {
+      for (int p = warp; 2 * p < nb; p += CW, aw += CW * PAIRB, as += CW * PAIRB, gb += 2 * CW) {
+        uint32_t wq[4][6], sc[4][2];
+        load_slot<QT, 0>(aw, as, wq[0], sc[0]);
+        load_slot<QT, 1>(aw, as, wq[1], sc[1]);
+        load_slot<QT, 2>(aw, as, wq[2], sc[2]);
+        load_slot<QT, 3>(aw, as, wq[3], sc[3]);
+        uint2 xe = make_uint2(0, 0), xo = make_uint2(0, 0);
+        if (col_live) {
+          xe = lds64(xs_lane + (uint32_t)(gb * S * 32));
+          xo = lds64(xs_lane + (uint32_t)((gb + 1) * S * 32));
         }
-      }
+        float se = 0.0f, so = 0.0f;
+        int offe = 0, offo = 0;
+        if (acc_live) {
+          const uint2 sde = lds64(sb_lane + (uint32_t)(gb * P.batch * 16));
+          const uint2 sdo = lds64(sb_lane + (uint32_t)((gb + 1) * P.batch * 16));
+          se = __uint_as_float(sde.x);
+          so = __uint_as_float(sdo.x);
+          if constexpr (G::Q4) {
+            offe = (int)sde.y;
+            offo = (int)sdo.y;
+          }
+        }
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
-        if (mt == 1 && !two_tiles) break;
-        uint32_t ae[2][2], ao[2][2];
-        expand<QT>(wq[mt * 2], ae[0], ao[0]);
-        expand<QT>(wq[mt * 2 + 1], ae[1], ao[1]);
-        int ce[4], co[4];
-        mma_i8<G::Q4>(ce, ae[0][0], ae[1][0], ae[0][1], ae[1][1], xe.x, xe.y);
-        mma_i8<G::Q4>(co, ao[0][0], ao[1][0], ao[0][1], ao[1][1], xo.x, xo.y);
-        // this lane's two columns are digit 2j and 2j+1 of one batch: fold them exactly
-        const float fe0 = (float)(ce[0] + (ce[1] << 8) - offe), fe1 = (float)(ce[2] + (ce[3] << 8) - offe);
-        const float fo0 = (float)(co[0] + (co[1] << 8) - offo), fo1 = (float)(co[2] + (co[3] << 8) - offo);
-        acc[mt][0] = fmaf(half_bits_to_float(sc[mt * 2][0]) * se, fe0, acc[mt][0]);
-        acc[mt][1] = fmaf(half_bits_to_float(sc[mt * 2 + 1][0]) * se, fe1, acc[mt][1]);
-        acc[mt][0] = fmaf(half_bits_to_float(sc[mt * 2][1]) * so, fo0, acc[mt][0]);
-        acc[mt][1] = fmaf(half_bits_to_float(sc[mt * 2 + 1][1]) * so, fo1, acc[mt][1]);
+        for (int mt = 0; mt < 2; ++mt) {
+          if (mt == 1 && !two_tiles) break;
+          uint32_t ae[2][2], ao[2][2];
+          expand<QT>(wq[mt * 2], ae[0], ao[0]);
+          expand<QT>(wq[mt * 2 + 1], ae[1], ao[1]);
+          int ce[4], co[4];
+          mma_i8<G::Q4>(ce, ae[0][0], ae[1][0], ae[0][1], ae[1][1], xe.x, xe.y);
+          mma_i8<G::Q4>(co, ao[0][0], ao[1][0], ao[0][1], ao[1][1], xo.x, xo.y);
+          // this lane's two columns are digit 2j and 2j+1 of one batch: fold them exactly
+          const float fe0 = (float)(ce[0] + (ce[1] << 8) - offe), fe1 = (float)(ce[2] + (ce[3] << 8) - offe);
+          const float fo0 = (float)(co[0] + (co[1] << 8) - offo), fo1 = (float)(co[2] + (co[3] << 8) - offo);
+          acc[mt][0] = fmaf(half_bits_to_float(sc[mt * 2][0]) * se, fe0, acc[mt][0]);
+          acc[mt][1] = fmaf(half_bits_to_float(sc[mt * 2 + 1][0]) * se, fe1, acc[mt][1]);
+          acc[mt][0] = fmaf(half_bits_to_float(sc[mt * 2][1]) * so, fo0, acc[mt][0]);
+          acc[mt][1] = fmaf(half_bits_to_float(sc[mt * 2 + 1][1]) * so, fo1, acc[mt][1]);
+        }
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[stage]);
 
     if (c == n_chunks - 1) {
-      // ---- cross-warp K reduction (fixed order) and epilogue for this row group
+      // ---- end of a row group: one value per row (and batch column) from this warp into the
+      // group's buffer, then on to the next group; the epilogue warp does the rest
+      const int buf = grp & 1;
+      if (grp >= 2) mbar_wait_bounded(&red_free[buf], (uint32_t)(((grp >> 1) - 1) & 1), dead, P.status);
+      float *rb = red + ((size_t)buf * CW + warp) * R * NB;
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
         for (int hs = 0; hs < 2; ++hs) {
-          red[(warp * R + mt * 16 + hs * 8 + g) * 4 + t] = acc[mt][hs];
+          float v = acc[mt][hs] * fold;  // low digits + 65536 * high digits
           acc[mt][hs] = 0.0f;
-        }
-      asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
-      const int vr0 = r_begin + grp * GROUP_ROWS;
-      constexpr float A_SCALE = G::Q4 ? 0.0625f : 1.0f;  // the Q4_0 digit sums carry a factor 16
-      for (int idx = ctid; idx < GROUP_ROWS * 2; idx += CW * 32) {
-        const int row = idx >> 1, b = idx & 1;
-        const int vrow = vr0 + row;
-        if (vrow >= r_end || b >= P.batch) continue;
-        auto total = [&](int rr) {
-          float lo = 0.0f, hi = 0.0f;
-#pragma unroll
-          for (int w = 0; w < CW; ++w) {
-            if constexpr (B1) {  // slots: even block low / high digits, odd block low / high digits
-              lo += red[(w * R + rr) * 4] + red[(w * R + rr) * 4 + 2];
-              hi += red[(w * R + rr) * 4 + 1] + red[(w * R + rr) * 4 + 3];
-            } else {
-              lo += red[(w * R + rr) * 4 + 2 * b];
-              hi += red[(w * R + rr) * 4 + 2 * b + 1];
-            }
+          v += __shfl_xor_sync(0xffffffffu, v, 1);
+          if constexpr (B1) {
+            v += __shfl_xor_sync(0xffffffffu, v, 2);  // even block + odd block
+            if (t == 0) rb[mt * 16 + hs * 8 + g] = v;
+          } else {
+            if ((t & 1) == 0) rb[(mt * 16 + hs * 8 + g) * NB + (t >> 1)] = v;
           }
-          return fmaf(hi, 65536.0f, lo) * A_SCALE;
-        };
-        const float v = total(row);
-        if (EPI == EPI_STORE) {
-          P.y[(size_t)b * P.ldy + vrow] = v;
-        } else if (EPI == EPI_RESIDUAL) {
-          float *dst = P.y + (size_t)b * P.ldy + vrow;
-          *dst = __fadd_rn(grp == 0 ? resid0 : *dst, v);
-        } else {
-          P.y[(size_t)b * P.ldy + vrow] = swiglu(v, total(row + 16));
         }
-      }
-      asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&red_full[buf]);
     }
     if (++c == n_chunks) {
       c = 0;
@@ -670,12 +835,18 @@ cudaError_t launch_t(const GemvI8Args &a, const LaunchCfg &cfg) {
   P.y = a.y;
   P.ldy = a.ldy;
   P.status = cfg.status;
+  P.xq = a.xq;
+  P.xq_norm = a.xq_norm ? 1 : 0;
+  P.pack_out = a.pack_out;
+  P.pack_w = a.pack_w;
+  P.pack_q4 = a.pack_type == RG_TYPE_Q4_0 ? 1 : 0;
   const int sms = cfg.sm_count > 0 ? cfg.sm_count : 148;
   const int boxes = (P.n_rows + BOXR - 1) / BOXR;
   P.rows_per_cta = ((boxes + sms - 1) / sms) * BOXR;
+  if (a.pack_out) P.rows_per_cta = (P.rows_per_cta + 31) & ~31;  // whole 32-element blocks of the next GEMV's input per CTA
   const int grid = (P.n_rows + P.rows_per_cta - 1) / P.rows_per_cta;
   const int S = 4 * a.batch;
-  const int fixed = 128 + CW * R * 4 * 4 + ((P.kb * S * 32 + 127) & ~127) + ((P.kb * a.batch * 16 + 127) & ~127);
+  const int fixed = HDR_BYTES + RED_BYTES + ((P.kb * S * 32 + 127) & ~127) + ((P.kb * a.batch * 16 + 127) & ~127);
   const int stage_bytes = R * G::RS;
   int stages = (SMEM_LIMIT - fixed) / stage_bytes;
   if (stages < 3) stages = (SMEM_FULL - fixed) / stage_bytes;  // too large to share an SM: take it whole
@@ -732,8 +903,21 @@ bool qgemv_i8_supported(int k, int batch) {
   return k > 0 && k % 256 == 0 && batch >= 1 && batch <= 2 && (size_t)k * 4 * batch <= 120 * 1024;
 }
 
+size_t qgemv_i8_xq_bytes(int k) {
+  const int kb = k / 32;
+  return xq_ssq_offset(kb) + (((size_t)kb * 4 + 127) & ~(size_t)127);
+}
+
 cudaError_t launch_qgemv_i8(const GemvI8Args &a, const LaunchCfg &cfg) {
-  if (!qgemv_i8_supported(a.k, a.batch) || a.nseg < 1 || a.nseg > 3 || !a.x || !a.y) return cudaErrorInvalidValue;
+  if (!qgemv_i8_supported(a.k, a.batch) || a.nseg < 1 || a.nseg > 3 || (!a.x && !a.xq) || !a.y) return cudaErrorInvalidValue;
+  if (a.xq && (a.batch != 1 || (reinterpret_cast<uintptr_t>(a.xq) & 127))) return cudaErrorInvalidValue;
+  if (a.pack_out) {  // only the residual epilogue of a batch-1 step packs, and only whole blocks
+    int rows = 0;
+    for (int i = 0; i < a.nseg; ++i) rows += a.seg_rows[i];
+    if (a.epi != EPI_RESIDUAL || a.batch != 1 || rows % 32 || (reinterpret_cast<uintptr_t>(a.pack_out) & 127) ||
+        (a.pack_type != RG_TYPE_Q4_0 && a.pack_type != RG_TYPE_Q8_0))
+      return cudaErrorInvalidValue;
+  }
   count_launch(LC_QGEMV_I8);
   if (a.epi == EPI_SWIGLU && (a.nseg != 2 || a.seg_rows[0] != a.seg_rows[1])) return cudaErrorInvalidValue;
   for (int i = 0; i + 1 < a.nseg; ++i)

@@ -145,6 +145,18 @@ __device__ __forceinline__ void xpack_store(__half *xpack, int S, int b, int k, 
   xpack[xpack_half_index(S, k, 2 * b + 1)] = lo;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Packed activation vector of the integer GEMV (qgemv_i8.cu) in global memory, batch 1,
+// K = 32 * kb elements: written by the kernel that produces the vector, bulk-copied by the GEMV.
+//   [kb][128] digit bytes: block fixed point x = s * X, X split into four signed base-256 digits;
+//             digit d of element e of a block sits at byte d * 32 + ((e & 15) >> 2) * 8 + (e >> 4) * 4 + (e & 3).
+//             For a Q4_0 consumer the stored integers are 16 X[e] (e < 16) and X[e] - 16 X[e - 16] (e >= 16).
+//   [kb][4]   side words {s, T_lo, s, T_hi} with 128 * sum(X) = T_lo + 65536 T_hi (Q4_0; zero for Q8_0)
+//   [kb]      f32 sum of squares of the block's elements before any norm weight (deferred RMSNorm)
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ inline size_t xq_side_offset(int kb) { return (size_t)kb * 128; }
+__host__ __device__ inline size_t xq_ssq_offset(int kb) { return (size_t)kb * 128 + (((size_t)kb * 16 + 127) & ~(size_t)127); }
+
 // SwiGLU with the reference's operation order (src/ir/elementwise.rs:6772-6830,7046-7050):
 // silu(g) = g * (1 / (1 + exp2(g * (-1/ln 2)))), every step rounded to f32.
 __device__ __forceinline__ float swiglu(float g, float u) {

@@ -253,6 +253,9 @@ struct rg_session {
   float *x = nullptr, *xn_f32 = nullptr, *qkv = nullptr, *q_rot = nullptr, *attn_scratch = nullptr, *attn_f32 = nullptr;
   float *partial = nullptr, *gate_f32 = nullptr, *up_f32 = nullptr, *h_f32 = nullptr, *logits = nullptr, *logits_l = nullptr;
   void *xn_pack = nullptr, *attn_pack = nullptr, *h_pack = nullptr, *head_pack = nullptr;
+  // batch-1 decode: activation vectors packed by their producers for the integer GEMV that reads them
+  // (qgemv_i8.cu): the residual stream after a projection, and the attention output
+  uint8_t *xq_x = nullptr, *xq_attn = nullptr;
   // Gumbel-max selection for the current step: device rows of uniforms [logit cols][vocab]; null = greedy
   const float *sample_uniforms = nullptr;
   float sample_temperature = 1.0f;
@@ -453,9 +456,24 @@ static bool small_batch_path(const rg_session *s, int ncols) {
   return s->head->packed();
 }
 
+// Packed input / output of one integer GEMV launch of a batch-1 step (see GemvI8Args).
+struct PackedIo {
+  const uint8_t *xq = nullptr;
+  bool xq_norm = false;
+  uint8_t *pack_out = nullptr;
+  const float *pack_w = nullptr;
+  int pack_type = 0;
+};
+
 static int32_t gemv_i8(rg_session *s, const DevTensor *const *w, int n, const float *x, int ldx, const int32_t *col_map,
-                       const float *norm_w, int batch, int epi, float *y, int ldy, const LaunchCfg &L) {
+                       const float *norm_w, int batch, int epi, float *y, int ldy, const LaunchCfg &L,
+                       const PackedIo &io = PackedIo()) {
   GemvI8Args a;
+  a.xq = io.xq;
+  a.xq_norm = io.xq_norm;
+  a.pack_out = io.pack_out;
+  a.pack_w = io.pack_w;
+  a.pack_type = io.pack_type;
   a.type = w[0]->type;
   a.nseg = n;
   for (int i = 0; i < n; ++i) {
@@ -491,14 +509,26 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
   const bool tp = s->tp_world > 1;
   const bool tp_lib = tp && !s->tp_fused;  // a library collective precedes some kernels: no dependent launch there
   int32_t rc;
+  // One column on one GPU: the residual epilogues (output and down projection) leave the new residual
+  // stream packed, with the next norm weight folded in, for the projection that reads it, whose
+  // prologue is then a single bulk copy; the norm's scalar factor is applied to that projection's results.
+  const bool pre = ncols == 1 && !tp && s->xq_x && !env_flag("RG_B200_NO_PREPACK");
+  // likewise the one-launch attention packs its output for the output projection (any world size:
+  // the heads are rank-local)
+  const bool pre_attn = ncols == 1 && s->xq_attn && s->attn_counters && !env_flag("RG_B200_NO_PREPACK");
   prof_mark(s, PROF_OTHER);
   RG_LAUNCH(s, launch_row_gather(s->token_embd.type, s->token_embd.d, d, ctl->tokens, ncols, s->x, d, plain));
   for (int l = 0; l < c.n_layers; ++l) {
     const LayerW &W = s->layers[(size_t)l];
     const DevTensor *qkvw[3] = {&W.q, &W.k, &W.v};
+    PackedIo qkv_io;
+    if (pre && l > 0) {  // layer 0 reads the embedding row, which nothing packed
+      qkv_io.xq = s->xq_x;
+      qkv_io.xq_norm = true;
+    }
     // the first GEMV of a layer follows a collective (library kernel) under tensor parallelism
     if ((rc = gemv_i8(s, qkvw, 3, s->x, d, nullptr, reinterpret_cast<const float *>(W.attn_norm.d), ncols, EPI_STORE, s->qkv,
-                      qkv_w, (tp_lib && l > 0) ? plain : L)))
+                      qkv_w, (tp_lib && l > 0) ? plain : L, qkv_io)))
       return rc;
     prof_mark(s, PROF_ATTN);
     // Two columns of ONE sequence (a two-token prompt chunk) must not share the one-launch kernel:
@@ -525,6 +555,10 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
       fa.counters = s->attn_counters;
       fa.out = s->attn_f32;
       fa.early = l > 0;  // layer 0 follows the kernels that set the positions
+      if (pre_attn) {
+        fa.pack_out = s->xq_attn;
+        fa.pack_type = W.o.type;
+      }
       RG_LAUNCH(s, launch_attention_fused(fa, L));
     } else {
       RopeArgs ra;
@@ -561,22 +595,42 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
       if (s->family_mask & (1u << PROF_ATTN)) s->launches_in_step++;  // split + combine
     }
     const DevTensor *ow[1] = {&W.o};
+    PackedIo o_in;
+    if (pre_attn) o_in.xq = s->xq_attn;
     if (tp) {
-      if ((rc = gemv_i8(s, ow, 1, s->attn_f32, qw, nullptr, nullptr, ncols, EPI_STORE, s->tp_part[0], d, L))) return rc;
+      if ((rc = gemv_i8(s, ow, 1, s->attn_f32, qw, nullptr, nullptr, ncols, EPI_STORE, s->tp_part[0], d, L, o_in))) return rc;
       if ((rc = tp_reduce_add(s, ncols, 0))) return rc;
-    } else if ((rc = gemv_i8(s, ow, 1, s->attn_f32, qw, nullptr, nullptr, ncols, EPI_RESIDUAL, s->x, d, L))) {
-      return rc;
+    } else {
+      PackedIo io = o_in;
+      if (pre) {
+        io.pack_out = s->xq_x;
+        io.pack_w = reinterpret_cast<const float *>(W.ffn_norm.d);
+        io.pack_type = W.gate.type;
+      }
+      if ((rc = gemv_i8(s, ow, 1, s->attn_f32, qw, nullptr, nullptr, ncols, EPI_RESIDUAL, s->x, d, L, io))) return rc;
     }
     const DevTensor *guw[2] = {&W.gate, &W.up};
+    PackedIo gu_io;
+    if (pre) {
+      gu_io.xq = s->xq_x;
+      gu_io.xq_norm = true;
+    }
     if ((rc = gemv_i8(s, guw, 2, s->x, d, nullptr, reinterpret_cast<const float *>(W.ffn_norm.d), ncols, EPI_SWIGLU, s->h_f32,
-                      s->ffn_l, tp_lib ? plain : L)))
+                      s->ffn_l, tp_lib ? plain : L, gu_io)))
       return rc;
     const DevTensor *dw[1] = {&W.down};
     if (tp) {
       if ((rc = gemv_i8(s, dw, 1, s->h_f32, s->ffn_l, nullptr, nullptr, ncols, EPI_STORE, s->tp_part[1], d, L))) return rc;
       if ((rc = tp_reduce_add(s, ncols, 1))) return rc;
-    } else if ((rc = gemv_i8(s, dw, 1, s->h_f32, s->ffn_l, nullptr, nullptr, ncols, EPI_RESIDUAL, s->x, d, L))) {
-      return rc;
+    } else {
+      PackedIo io;
+      if (pre) {  // read next by the following layer's q/k/v projection, or by the head after the last layer
+        const bool last = l + 1 == c.n_layers;
+        io.pack_out = s->xq_x;
+        io.pack_w = reinterpret_cast<const float *>(last ? s->output_norm.d : s->layers[(size_t)l + 1].attn_norm.d);
+        io.pack_type = last ? s->head->type : s->layers[(size_t)l + 1].q.type;
+      }
+      if ((rc = gemv_i8(s, dw, 1, s->h_f32, s->ffn_l, nullptr, nullptr, ncols, EPI_RESIDUAL, s->x, d, L, io))) return rc;
     }
   }
   if (n_logit_cols > 0) {
@@ -584,8 +638,13 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
     const bool split_head = tp && s->head == &s->output;
     float *dst = split_head ? s->logits_l : s->logits;
     const int ld = split_head ? s->vocab_l : c.vocab;
+    PackedIo head_io;
+    if (pre) {  // one column: the logit column is column 0
+      head_io.xq = s->xq_x;
+      head_io.xq_norm = true;
+    }
     if ((rc = gemv_i8(s, hw, 1, s->x, d, ctl->logit_cols, reinterpret_cast<const float *>(s->output_norm.d), n_logit_cols,
-                      EPI_STORE, dst, ld, tp_lib ? plain : L)))
+                      EPI_STORE, dst, ld, tp_lib ? plain : L, head_io)))
       return rc;
     LaunchCfg am = L;
     prof_mark(s, PROF_OTHER);
@@ -1510,6 +1569,8 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   s->h_pack = raw;
   RG_TRY(dalloc(s.get(), &raw, xpack_bytes(d, MAXC)));
   s->head_pack = raw;
+  RG_TRY(dalloc(s.get(), &s->xq_x, qgemv_i8_xq_bytes(d)));
+  RG_TRY(dalloc(s.get(), &s->xq_attn, qgemv_i8_xq_bytes(qw)));
   if (s->tp_world > 1 && !p->opt.disable_fused_allreduce && !env_flag("RG_B200_DISABLE_FUSED_ALLREDUCE")) RG_TRY(tp_fused_setup(s.get()));
   // RoPE tables in f64 on the host, cast to f32 (src/models/transformer/layer.rs:541-556)
   {
