@@ -454,6 +454,7 @@ def main():
     # ---- profiling pass: CUDA events between kernel families (serialized, no overlap)
     prof = sess.decode_profile(tok, 16, in_step=True)   # launch attributes as in the timed step
     prof_serial = sess.decode_profile(tok, 16)          # every kernel alone, no overlap
+    prof_sites = sess.decode_profile_projections(tok, 16) if B <= 2 else None
     position = sess.position()
 
     t = torch.tensor([gpu_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
@@ -497,6 +498,7 @@ def main():
                      "step_bytes_over_step_time_gbs": (gemv_bytes / (ms_per_step * 1e-3) / 1e9)},
         "profile_ms_per_step": {k: v["ms_per_step"] for k, v in prof.items()},
         "profile_ms_per_step_serialized": {k: v["ms_per_step"] for k, v in prof_serial.items()},
+        "gemv_ms_per_step_by_projection": prof_sites,
     }
     if n > 1:
         # tensor parallel: what the exchange of partial sums costs (the "other" family is the 160 exchanges plus

@@ -218,6 +218,11 @@ int32_t rg_b200_decode_profile(rg_session *s, const int32_t *first_tokens, int32
  * of the kernel before it as it does inside a decode step (src/cuda_profile.rs:15-60). */
 int32_t rg_b200_decode_profile_in_step(rg_session *s, const int32_t *first_tokens, int32_t batch, int32_t steps,
                                        float out_ms[4], uint64_t out_launches[4]);
+/* The GEMV family split by projection (batch 1 or 2, the integer tensor-core path): milliseconds per
+ * step of the launches of [0] q+k+v, [1] attention output, [2] gate+up, [3] down, [4] logits head,
+ * each set replayed alone with the step's launch attributes (src/cuda_profile.rs:15-60). */
+int32_t rg_b200_decode_profile_projections(rg_session *s, const int32_t *first_tokens, int32_t batch, int32_t steps,
+                                           float out_ms[5]);
 int32_t rg_b200_report(const rg_session *s, rg_report *out);
 /* cudaStream_t the session launches on (for CUDA-event timing by the caller). */
 void *rg_b200_session_stream(const rg_session *s);

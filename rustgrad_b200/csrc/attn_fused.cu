@@ -106,7 +106,8 @@ __device__ __forceinline__ float reduce_scatter16(float (&val)[NV], int sub) {
 }
 
 template <typename KV, int HD, int G>
-__global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnArgs A, int per_head, int *status) {
+__global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnArgs A, int per_head, int *status,
+                                                                 unsigned long long *trace) {
   // A.early: the positions and the cached rows of earlier positions were written at least one
   // attention launch ago, and every attention launch lets its dependents start only after its own
   // dependency wait, so they are complete whenever this CTA runs: the position, the rotation
@@ -159,8 +160,11 @@ __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnA
     cs0 = ct[tid % (HD / 2)];
     sn0 = st[tid % (HD / 2)];
   }
+  const bool tr_first = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  if (tid == 0) trace_stamp(trace, 0, tr_first, false);  // CTA started, K / V copies issued
   if (A.early) pdl_wait();
   pdl_launch_dependents();
+  if (tid == 0) trace_stamp(trace, 1, tr_first, false);  // grid dependency resolved
   // pairs (2i, 2i+1) of the projection rotate into (i, HD/2 + i) (layer.rs:349-371)
   for (int it = tid; it < G * (HD / 2); it += THREADS) {
     const int gq = it / (HD / 2), i = it - gq * (HD / 2);
@@ -187,6 +191,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnA
   }
   __syncthreads();
   if (ncopy > 0) mbar_wait_bounded(&bar, 0, &dead_flag, status);
+  if (tid == 0) trace_stamp(trace, 2, tr_first, false);  // q rotated, K / V spans in shared memory
   // ---- scores: 16 lanes per position; scale = 1 / f32(sqrt(hd)) applied as a division (attention.rs:1183-1188)
   const float inv_scale = (float)(1.0 / (1.0 / sqrt((double)HD)));
   {
@@ -295,6 +300,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnA
     }
   }
   __syncthreads();
+  if (tid == 0) trace_stamp(trace, 3, tr_first, false);  // this span's partial result written
   if (tid == 0) {
     unsigned *counter = A.counters + (size_t)c * A.kv_heads + kvh;
     int last = 1;
@@ -311,6 +317,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnA
   }
   __syncthreads();
   if (!last_flag) return;
+  if (tid == 0 && kvh == 0 && c == 0) trace_stamp(trace, 8, true, false);  // last span of kv head 0 arrived (slot 8)
   // ---- combine.  The span headers (max, sum) and the first CB spans of this thread's output
   // column are requested together, before the weights exist: one round trip to L2 instead of one
   // for the headers and one per batch of spans (a dependent load-use loop would pay it per span).
@@ -433,6 +440,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnA
             make_float4(sc_b, __int_as_float(t_lo), sc_b, __int_as_float(t_hi));
     }
   }
+  if (tid == 0 && kvh == 0 && c == 0) trace_stamp(trace, 9, true, false);  // combined output of kv head 0 stored (slot 9)
 }
 
 template <typename KV, int HD, int G>
@@ -462,7 +470,7 @@ cudaError_t launch_t(const FusedAttnArgs &a, const LaunchCfg &cfg) {
   at[0].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = at;
   lc.numAttrs = cfg.pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&lc, kernel, a, per_head, cfg.status);
+  return cudaLaunchKernelEx(&lc, kernel, a, per_head, cfg.status, cfg.trace);
 }
 
 template <int G>

@@ -12,6 +12,9 @@ struct LaunchCfg {
   bool pdl = false;    // launch with programmatic stream serialization
   int sm_count = 148;
   int *status = nullptr;  // device status word (see rg_device.cuh)
+  // Development trace (nullable): 16 u64 slots of this launch; the first and the last CTA of the
+  // integer GEMV and of the one-launch attention stamp %globaltimer at their phase boundaries.
+  unsigned long long *trace = nullptr;
 };
 
 // cudaFuncSetAttribute applies to the current device only: a launcher keeps one flag per device
@@ -77,14 +80,21 @@ struct GemvI8Args {
   // (the producer folded the norm weight into the packed values).
   const uint8_t *xq = nullptr;
   bool xq_norm = false;
-  // EPI_RESIDUAL, batch 1, rows a multiple of 32: besides y, write the new rows packed as the input
-  // of the next GEMV, whose block type is pack_type, with pack_w (nullable) folded in.
+  // blocks of xq that its producer left unpacked (device array of block indices): the prologue packs
+  // them from x.  A SwiGLU producer leaves the blocks that straddle two of its CTAs.
+  const int32_t *xq_fix = nullptr;
+  int xq_nfix = 0;
+  // EPI_RESIDUAL or EPI_SWIGLU, batch 1, rows a multiple of 32: besides y, write the new rows packed
+  // as the input of the next GEMV, whose block type is pack_type, with pack_w (nullable; residual
+  // only) folded in.  The residual form packs every block; the SwiGLU form those inside one CTA.
   uint8_t *pack_out = nullptr;
   const float *pack_w = nullptr;
   int pack_type = 0;
 };
 bool qgemv_i8_supported(int k, int batch);
 size_t qgemv_i8_xq_bytes(int k);
+// Output rows per CTA of a launch over n_rows rows (EPI_SWIGLU: rows of the gate matrix).
+int qgemv_i8_rows_per_cta(int n_rows, int sm_count, bool whole_blocks);
 cudaError_t launch_qgemv_i8(const GemvI8Args &a, const LaunchCfg &cfg);
 
 // tcgen05 GEMM for many tokens: out[m][n] = x[m][k] (16-bit) . W[n][k]^T with W in Q4_0 / Q8_0 blocks

@@ -89,6 +89,7 @@ struct Params {
   const float *norm_w;     // nullable: RMSNorm weight (prologue normalises when set)
   float eps;
   int batch;  // 1..2
+  int epi;    // GemvEpilogue
   float *y;
   int ldy;
   int rows_per_cta;
@@ -96,7 +97,10 @@ struct Params {
   int *status;
   const uint8_t *xq;    // batch 1: activations already packed (see xq_* below); x / norm_w unused
   int xq_norm;          // the packed values carry the norm weight: scale the results by inv_rms from the block sums
-  uint8_t *pack_out;    // EPI_RESIDUAL, batch 1: also write the new rows packed for the next GEMV
+  unsigned long long *trace;
+  const int32_t *xq_fix;  // blocks of xq its producer could not pack (they straddle two of its CTAs): packed here from x
+  int xq_nfix;
+  uint8_t *pack_out;    // EPI_RESIDUAL / EPI_SWIGLU, batch 1: also write the new rows packed for the next GEMV
   const float *pack_w;  // norm weight folded into the packed output (nullable)
   int pack_q4;          // block type of the GEMV that will read pack_out: 1 Q4_0, 0 Q8_0
 };
@@ -221,19 +225,64 @@ __device__ __forceinline__ uint32_t digit_offset(int S, int kb, int c, int e) {
   return (uint32_t)((((kb * S + c) * 4 + t) * 8) + r * 4 + i);
 }
 
+// One 32-element block of a packed activation vector (rg_device.cuh), lane = element: block fixed point
+// of `val`, digits, side words, and (ssq_out) the sum of squares `ssq` the caller reduced.  All 32 lanes call.
+__device__ __forceinline__ void pack_block_warp(float val, bool q4, uint8_t *xq, int kbo, int kb_all, int lane, bool ssq_out,
+                                                float ssq) {
+  float m = warp_max(fabsf(val));
+  if (__any_sync(0xffffffffu, !(fabsf(val) <= 3.0e38f))) m = __uint_as_float(0x7f800000u);  // keep NaN / inf visible
+  const uint32_t E = __float_as_uint(m) >> 23;
+  const uint32_t XBITS = q4 ? 25u : 29u;
+  float s = 0.0f;
+  int X = 0;
+  if (E >= 40u && E < 255u) {
+    s = __uint_as_float((E - XBITS) << 23);
+    X = __float2int_rn(val * __uint_as_float((254u + XBITS - E) << 23));
+  } else if (E == 255u) {
+    s = __uint_as_float(0x7fc00000u);
+    X = lane == 0 ? 1 : 0;
+  }
+  int t_lo = 0, t_hi = 0;
+  if (q4) {
+    int sum = X;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    t_lo = (sum & 0x1FF) << 7;
+    t_hi = sum >> 9;
+    const int partner = __shfl_xor_sync(0xffffffffu, X, 16);
+    X = lane < 16 ? X << 4 : X - (partner << 4);
+  }
+  const uint32_t Y = (uint32_t)X + 0x80808080u;
+  uint8_t *dst = xq + (size_t)kbo * 128 + ((lane & 15) >> 2) * 8 + (lane >> 4) * 4 + (lane & 3);
+#pragma unroll
+  for (int d = 0; d < 4; ++d) dst[d * 32] = (uint8_t)(((Y >> (8 * d)) & 0xFFu) ^ 0x80u);
+  if (lane == 0) {
+    *reinterpret_cast<float4 *>(xq + xq_side_offset(kb_all) + (size_t)kbo * 16) =
+        make_float4(s, __int_as_float(t_lo), s, __int_as_float(t_hi));
+    if (ssq_out) reinterpret_cast<float *>(xq + xq_ssq_offset(kb_all))[kbo] = ssq;
+  }
+}
+
 // B1 (batch 1): the four digit columns leave half of the MMA's eight columns idle, so the even and
 // the odd block of a pair share one accumulator tile: columns 0-3 take the even block's digits
 // (B rows k < 16 only), columns 4-7 the odd block's (B rows k >= 16 only), and the A operand carries
 // the even block in k < 16 and the odd block in k >= 16.  Two MMAs (low / high halves of both blocks)
 // accumulate in place; afterwards lanes t < 2 scale the even block and lanes t >= 2 the odd one, so
 // the per-lane scale / convert / accumulate work is half of the general layout's.
-template <int QT, int EPI, bool B1>
+// XQ: the activations arrive packed (batch 1).  Those instantiations carry no self-packing code at
+// all: the kernels of a decode step alternate, and a step runs faster the less code they hold (the
+// unrolled register-resident prologues alone are 50 KB per instantiation; with them in, every launch
+// of a step started on cold instruction caches and the step took 9 % longer).
+template <int QT, bool B1, bool XQ>
 __global__ void __launch_bounds__(THREADS, 1)
     qgemv_i8_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                     const __grid_constant__ CUtensorMap map2, const Params P) {
   using G = Geo<QT>;
-  constexpr bool PAIR = (EPI == EPI_SWIGLU);
-  constexpr int GROUP_ROWS = PAIR ? 16 : 32;
+  // The epilogue is a run-time switch: every projection of a decode step then runs the same kernel
+  // (per block type), which stays in the instruction caches from launch to launch.
+  const int EPI = P.epi;
+  const bool PAIR = (EPI == EPI_SWIGLU);
+  const int GROUP_ROWS = PAIR ? 16 : 32;
   constexpr int NB = B1 ? 1 : 2;  // batch columns a partial-sum slot holds
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
@@ -257,7 +306,14 @@ __global__ void __launch_bounds__(THREADS, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r_begin = blockIdx.x * P.rows_per_cta;
   const int r_end = min(P.n_rows, r_begin + P.rows_per_cta);
-  const int n_groups = (r_end > r_begin) ? (r_end - r_begin + GROUP_ROWS - 1) / GROUP_ROWS : 0;
+  // Row groups of GROUP_ROWS rows.  A SwiGLU launch hands out rows in units of 8, so a CTA may start
+  // in the middle of a 16-row unit of its output: its first group is then 8 rows, and every later
+  // group is one aligned half of a 32-element block of the next GEMV's input (see the packing below).
+  const int first_rows = (PAIR && (r_begin & 8)) ? 8 : GROUP_ROWS;
+  const int cta_rows = r_end - r_begin;
+  const int n_groups = cta_rows <= 0 ? 0 : cta_rows <= first_rows ? 1 : 1 + (cta_rows - first_rows + GROUP_ROWS - 1) / GROUP_ROWS;
+  auto group_start = [&](int grp) { return grp == 0 ? r_begin : r_begin + first_rows + (grp - 1) * GROUP_ROWS; };
+  auto group_rows = [&](int grp, int vr0) { return min(grp == 0 ? first_rows : GROUP_ROWS, r_end - vr0); };
   const int n_chunks = (P.kb + G::KC - 1) / G::KC;
   const int units = n_groups * n_chunks;
   const int stages = P.stages;
@@ -277,6 +333,8 @@ __global__ void __launch_bounds__(THREADS, 1)
   }
   __syncthreads();
   pdl_launch_dependents();
+  const bool tr_first = blockIdx.x == 0, tr_last = blockIdx.x == gridDim.x - 1;
+  if (threadIdx.x == 0) trace_stamp(P.trace, 0, tr_first, tr_last);  // CTA started
 
   // 1 / sqrt(mean(x^2) + eps) from the per-block sums of squares of a pre-packed vector; every warp
   // that needs it computes it alone, in the same order
@@ -292,20 +350,23 @@ __global__ void __launch_bounds__(THREADS, 1)
   // One row group's epilogue, run by a whole warp (lane = row of the group): sum the consumer warps'
   // partials in warp order, scale, apply the epilogue, optionally pack the new rows.
   constexpr float A_SCALE = G::Q4 ? 0.0625f : 1.0f;  // the Q4_0 digit sums carry a factor 16
+  [[maybe_unused]] float half0 = 0.0f;   // SwiGLU packing: first 16 rows of the block in progress
+  [[maybe_unused]] int half0_blk = -1;
   auto group_epilogue = [&](int grp, float out_scale, auto wait_for_partials) {
       const int buf = grp & 1;
-      const int vr0 = r_begin + grp * GROUP_ROWS;
+      const int vr0 = group_start(grp);
       const int vrow = vr0 + lane;
+      const int vend = vr0 + group_rows(grp, vr0);  // rows of this group are [vr0, vend)
       float resid[NB];
 #pragma unroll
       for (int b = 0; b < NB; ++b) resid[b] = 0.0f;
-      if (EPI == EPI_RESIDUAL && vrow < r_end) {  // requested before the wait: off the critical path
+      if (EPI == EPI_RESIDUAL && vrow < vend) {  // requested before the wait: off the critical path
 #pragma unroll
         for (int b = 0; b < NB; ++b)
           if (b < P.batch) resid[b] = P.y[(size_t)b * P.ldy + vrow];
       }
       float pw = 1.0f;
-      if (EPI == EPI_RESIDUAL && B1 && P.pack_out && P.pack_w && vrow < r_end) pw = __ldg(P.pack_w + vrow);
+      if (EPI == EPI_RESIDUAL && B1 && P.pack_out && P.pack_w && vrow < vend) pw = __ldg(P.pack_w + vrow);
       wait_for_partials();
       float tot[NB];
 #pragma unroll
@@ -320,60 +381,41 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
       for (int b = 0; b < NB; ++b) tot[b] *= out_scale;
       float xn[NB];
-      if constexpr (EPI == EPI_SWIGLU) {
+      if (EPI == EPI_SWIGLU) {
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
           const float up = __shfl_down_sync(0xffffffffu, tot[b], 16);
-          xn[b] = 0.0f;
-          if (lane < 16 && vrow < r_end && b < P.batch) P.y[(size_t)b * P.ldy + vrow] = swiglu(tot[b], up);
+          xn[b] = swiglu(tot[b], up);
+          if (lane < 16 && vrow < vend && b < P.batch) P.y[(size_t)b * P.ldy + vrow] = xn[b];
+        }
+        if constexpr (B1) {
+          // The 16 new rows are half a block of the next GEMV's input.  When both halves of a block
+          // belong to this CTA the block is packed here (first half kept from the previous group);
+          // blocks that straddle two CTAs are left to the consumer (its xq_fix list).
+          if (P.pack_out) {
+            if ((vr0 & 31) == 0) {
+              half0 = xn[0];
+              half0_blk = vr0 + 32 <= r_end ? (vr0 >> 5) : -1;
+            } else if ((vr0 & 31) == 16 && vend - vr0 == 16 && half0_blk == (vr0 >> 5)) {
+              const float second = __shfl_sync(0xffffffffu, xn[0], lane & 15);
+              pack_block_warp(lane < 16 ? half0 : second, P.pack_q4 != 0, P.pack_out, vr0 >> 5, P.n_rows >> 5, lane, false, 0.0f);
+              half0_blk = -1;
+            }
+          }
         }
       } else {
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
           xn[b] = EPI == EPI_RESIDUAL ? __fadd_rn(resid[b], tot[b]) : tot[b];
-          if (vrow < r_end && b < P.batch) P.y[(size_t)b * P.ldy + vrow] = xn[b];
+          if (vrow < vend && b < P.batch) P.y[(size_t)b * P.ldy + vrow] = xn[b];
         }
       }
-      if constexpr (EPI == EPI_RESIDUAL && B1) {
-        if (P.pack_out) {
+      if constexpr (B1) {
+        if (EPI == EPI_RESIDUAL && P.pack_out) {
           // the 32 new rows are block vr0 / 32 of the next GEMV's input: pack them here (the launcher
           // gives every CTA whole blocks), with that GEMV's norm weight folded in
-          const int kbo = vr0 >> 5;
-          const int kb_all = P.n_rows >> 5;
           const float ssq = warp_sum(__fmul_rn(xn[0], xn[0]));
-          const float val = __fmul_rn(xn[0], pw);
-          float m = warp_max(fabsf(val));
-          if (__any_sync(0xffffffffu, !(fabsf(val) <= 3.0e38f))) m = __uint_as_float(0x7f800000u);  // keep NaN / inf visible
-          const uint32_t E = __float_as_uint(m) >> 23;
-          const uint32_t XBITS = P.pack_q4 ? 25u : 29u;
-          float s = 0.0f;
-          int X = 0;
-          if (E >= 40u && E < 255u) {
-            s = __uint_as_float((E - XBITS) << 23);
-            X = __float2int_rn(val * __uint_as_float((254u + XBITS - E) << 23));
-          } else if (E == 255u) {
-            s = __uint_as_float(0x7fc00000u);
-            X = lane == 0 ? 1 : 0;
-          }
-          int t_lo = 0, t_hi = 0;
-          if (P.pack_q4) {
-            int sum = X;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            t_lo = (sum & 0x1FF) << 7;
-            t_hi = sum >> 9;
-            const int partner = __shfl_xor_sync(0xffffffffu, X, 16);
-            X = lane < 16 ? X << 4 : X - (partner << 4);
-          }
-          const uint32_t Y = (uint32_t)X + 0x80808080u;
-          uint8_t *dst = P.pack_out + (size_t)kbo * 128 + ((lane & 15) >> 2) * 8 + (lane >> 4) * 4 + (lane & 3);
-#pragma unroll
-          for (int d = 0; d < 4; ++d) dst[d * 32] = (uint8_t)(((Y >> (8 * d)) & 0xFFu) ^ 0x80u);
-          if (lane == 0) {
-            *reinterpret_cast<float4 *>(P.pack_out + xq_side_offset(kb_all) + (size_t)kbo * 16) =
-                make_float4(s, __int_as_float(t_lo), s, __int_as_float(t_hi));
-            reinterpret_cast<float *>(P.pack_out + xq_ssq_offset(kb_all))[kbo] = ssq;
-          }
+          pack_block_warp(__fmul_rn(xn[0], pw), P.pack_q4 != 0, P.pack_out, vr0 >> 5, P.n_rows >> 5, lane, true, ssq);
         }
       }
   };
@@ -384,10 +426,10 @@ __global__ void __launch_bounds__(THREADS, 1)
     int grp = 0, c = 0, stage = 0, round = 0;
     for (int u = 0; u < units; ++u) {
       if (round > 0) mbar_wait_bounded(&empty[stage], (uint32_t)((round - 1) & 1), dead, P.status);
-      const int vr0 = r_begin + grp * GROUP_ROWS;
+      const int vr0 = group_start(grp);
       uint8_t *sw = stage0 + (size_t)stage * STAGE_BYTES;
-      // a partial last group fetches only the boxes that hold rows of this CTA
-      const int nbx = (min(GROUP_ROWS, r_end - vr0) + BOXR - 1) / BOXR;
+      // a partial group fetches only the boxes that hold its rows
+      const int nbx = (group_rows(grp, vr0) + BOXR - 1) / BOXR;
       const bool box_live = PAIR ? (lane & 1) < nbx : lane < nbx;
       if (lane == 0) mbar_expect_tx(&full[stage], (uint32_t)((PAIR ? 2 * nbx : nbx) * BOXR * G::RS));
       __syncwarp();
@@ -426,8 +468,9 @@ __global__ void __launch_bounds__(THREADS, 1)
     // ------------------------------------------------------------------ epilogue warp
     if (n_groups == 0) return;
     pdl_wait();  // the residual rows, the block sums and every store below touch the step's buffers
+    if (lane == 0) trace_stamp(P.trace, 1, tr_first, tr_last);  // grid dependency resolved
     float out_scale = A_SCALE;
-    if (P.xq && P.xq_norm) out_scale *= inv_from_blocks();
+    if (XQ && P.xq_norm) out_scale *= inv_from_blocks();
     for (int grp = 0; grp < n_groups; ++grp) {
       const int buf = grp & 1;
       group_epilogue(grp, out_scale, [&]() {
@@ -447,7 +490,9 @@ __global__ void __launch_bounds__(THREADS, 1)
           }
         }
       });
+      if (lane == 0 && grp == 0) trace_stamp(P.trace, 4, tr_first, tr_last);  // first row group stored
     }
+    if (lane == 0) trace_stamp(P.trace, 5, tr_first, tr_last);  // last row group stored
     return;
   }
 
@@ -588,10 +633,13 @@ __global__ void __launch_bounds__(THREADS, 1)
       pack_block(v, kb, 0, kb < P.kb);
     }
   };
-  const int npass = (P.kb + PASS_BLOCKS - 1) / PASS_BLOCKS;
   using std::integral_constant;
-  if (B1 && P.xq) {
+  if constexpr (XQ) {
     // the producer of the vector packed it: one bulk copy of digits and side words
+    // blocks the producer could not pack come from the plain f32 copy of the vector; the list is
+    // constant data, so the first pass's block index is fetched before the grid dependency resolves
+    const bool fix0 = kbw < P.xq_nfix;
+    const int kb0 = fix0 ? __ldg(P.xq_fix + kbw) : 0;
     pdl_wait();
     if (ctid == 0) {
       const uint32_t db = (uint32_t)P.kb * 128u, sbb = (uint32_t)P.kb * 16u;
@@ -599,8 +647,26 @@ __global__ void __launch_bounds__(THREADS, 1)
       bulk_g2s(xs, P.xq, db, xbar);
       bulk_g2s(sb, P.xq + xq_side_offset(P.kb), sbb, xbar);
     }
+    const float *xr = P.xq_nfix > 0 ? P.x + (size_t)(P.col_map ? P.col_map[0] : 0) * P.ldx : nullptr;
+    float4 xl0 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), xh0 = xl0;
+    if (fix0) load8(xr, kb0, xl0, xh0);  // in flight together with the bulk copy
     mbar_wait_bounded(xbar, 0, dead, P.status);
-  } else if (B1 && npass <= (P.norm_w ? 3 : 4)) {
+    if (P.xq_nfix > 0) {
+      float v0[8] = {xl0.x, xl0.y, xl0.z, xl0.w, xh0.x, xh0.y, xh0.z, xh0.w};
+      pack_block(v0, kb0, 0, fix0);
+      for (int s0 = PASS_BLOCKS; s0 < P.xq_nfix; s0 += PASS_BLOCKS) {  // uniform trip count
+        const int slot = s0 + kbw;
+        const bool live = slot < P.xq_nfix;
+        const int kb = live ? __ldg(P.xq_fix + slot) : 0;
+        float4 xl = make_float4(0.0f, 0.0f, 0.0f, 0.0f), xh = xl;
+        if (live) load8(xr, kb, xl, xh);
+        float v[8] = {xl.x, xl.y, xl.z, xl.w, xh.x, xh.y, xh.z, xh.w};
+        pack_block(v, kb, 0, live);
+      }
+    }
+  } else {
+  const int npass = (P.kb + PASS_BLOCKS - 1) / PASS_BLOCKS;
+  if (B1 && npass <= (P.norm_w ? 3 : 4)) {
     if (P.norm_w) {
       if (npass == 1) fast(integral_constant<int, 1>{}, integral_constant<bool, true>{});
       else if (npass == 2) fast(integral_constant<int, 2>{}, integral_constant<bool, true>{});
@@ -636,7 +702,9 @@ __global__ void __launch_bounds__(THREADS, 1)
       }
     }
   }
+  }
   asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+  if (ctid == 0) trace_stamp(P.trace, 2, tr_first, tr_last);  // activations in shared memory
 
   const int g = lane >> 2, t = lane & 3;
   const bool col_live = B1 ? true : g < S;  // this lane's B column carries a digit
@@ -667,28 +735,30 @@ __global__ void __launch_bounds__(THREADS, 1)
     uint32_t as = sw + lane_s_off + (uint32_t)warp * PAIRB;
     int gb = c * G::KC + 2 * warp;  // global block index of the pair's even block
     // rows 16..31 of a partial last group are not this CTA's: their boxes were not fetched
-    const bool two_tiles = PAIR || r_end - (r_begin + grp * GROUP_ROWS) > 16;
+    const bool two_tiles = PAIR || r_end - group_start(grp) > 16;
     if constexpr (B1) {
-      // one block pair of all 32 rows: loads, then two accumulating MMAs per m-tile, then scales
-      auto fetch = [&](uint32_t a, uint32_t s, int gbp, uint32_t (&wq)[4][6], uint32_t (&sc)[4][2], uint2 &xv, uint2 &side) {
+      // one block pair of all 32 rows: loads, then two accumulating MMAs per m-tile, then scales;
+      // no branch inside, so the two m-tiles are scheduled as interleaved chains
+      auto fetch = [&](auto tt, uint32_t a, uint32_t s, int gbp, uint32_t (&wq)[4][6], uint32_t (&sc)[4][2], uint2 &xv, uint2 &side) {
+        constexpr bool TT = decltype(tt)::value;
         load_slot_b1<QT, 0>(a, s, wq[0], sc[0]);
         load_slot_b1<QT, 1>(a, s, wq[1], sc[1]);
-        if (two_tiles) {
+        if constexpr (TT) {
           load_slot_b1<QT, 2>(a, s, wq[2], sc[2]);
           load_slot_b1<QT, 3>(a, s, wq[3], sc[3]);
         }
         xv = lds64(xs_lane + (uint32_t)(gbp * 128));
         side = lds64(sb_lane + (uint32_t)(gbp * 16));
       };
-      auto math = [&](const uint32_t (&wq)[4][6], const uint32_t (&sc)[4][2], const uint2 &xv, const uint2 &side) {
+      auto math = [&](auto tt, const uint32_t (&wq)[4][6], const uint32_t (&sc)[4][2], const uint2 &xv, const uint2 &side) {
+        constexpr bool TT = decltype(tt)::value;
         const float sv = __uint_as_float(side.x);
         const int off = G::Q4 ? (int)side.y : 0;
         const bool ev = g < 4;
         const uint32_t b_lo0 = ev ? xv.x : 0u, b_lo1 = ev ? 0u : xv.x;  // MMA 1: low halves of both blocks
         const uint32_t b_hi0 = ev ? xv.y : 0u, b_hi1 = ev ? 0u : xv.y;  // MMA 2: high halves
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
-          if (mt == 1 && !two_tiles) break;
+        for (int mt = 0; mt < (TT ? 2 : 1); ++mt) {
           uint32_t ae[2][2], ao[2][2];
           expand<QT>(wq[mt * 2], ae[0], ao[0]);
           expand<QT>(wq[mt * 2 + 1], ae[1], ao[1]);
@@ -700,11 +770,13 @@ __global__ void __launch_bounds__(THREADS, 1)
           acc[mt][1] = fmaf(half_bits_to_float(sc[mt * 2 + 1][0]) * sv, f1, acc[mt][1]);
         }
       };
+      // both m-tiles always: rows of a tile that is not this CTA's are computed on whatever the stage
+      // holds and never stored
       for (int p = warp; 2 * p < nb; p += CW, aw += CW * PAIRB, as += CW * PAIRB, gb += 2 * CW) {
         uint32_t wa[4][6], sa[4][2];
         uint2 xa, sda;
-        fetch(aw, as, gb, wa, sa, xa, sda);
-        math(wa, sa, xa, sda);
+        fetch(std::true_type{}, aw, as, gb, wa, sa, xa, sda);
+        math(std::true_type{}, wa, sa, xa, sda);
       }
     } else {
       for (int p = warp; 2 * p < nb; p += CW, aw += CW * PAIRB, as += CW * PAIRB, gb += 2 * CW) {
@@ -784,6 +856,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       phase ^= 1u;
     }
   }
+  if (ctid == 0) trace_stamp(P.trace, 3, tr_first, tr_last);  // last weight stage consumed
 }
 
 using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -813,12 +886,14 @@ cudaError_t make_map(CUtensorMap *map, const uint8_t *w, int rows, size_t row_by
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <int QT, int EPI, bool B1>
+template <int QT, bool B1, bool XQ>
 cudaError_t launch_t(const GemvI8Args &a, const LaunchCfg &cfg) {
   using G = Geo<QT>;
   Params P{};
   for (int i = 0; i < 3; ++i) P.seg_rows[i] = a.seg_rows[i];
   P.nseg = a.nseg;
+  const int EPI = a.epi;
+  P.epi = a.epi;
   if (EPI == EPI_SWIGLU) {
     P.n_rows = a.seg_rows[0];
   } else {
@@ -835,15 +910,15 @@ cudaError_t launch_t(const GemvI8Args &a, const LaunchCfg &cfg) {
   P.y = a.y;
   P.ldy = a.ldy;
   P.status = cfg.status;
+  P.trace = cfg.trace;
   P.xq = a.xq;
   P.xq_norm = a.xq_norm ? 1 : 0;
   P.pack_out = a.pack_out;
   P.pack_w = a.pack_w;
   P.pack_q4 = a.pack_type == RG_TYPE_Q4_0 ? 1 : 0;
-  const int sms = cfg.sm_count > 0 ? cfg.sm_count : 148;
-  const int boxes = (P.n_rows + BOXR - 1) / BOXR;
-  P.rows_per_cta = ((boxes + sms - 1) / sms) * BOXR;
-  if (a.pack_out) P.rows_per_cta = (P.rows_per_cta + 31) & ~31;  // whole 32-element blocks of the next GEMV's input per CTA
+  P.xq_fix = a.xq_fix;
+  P.xq_nfix = a.xq_fix ? a.xq_nfix : 0;
+  P.rows_per_cta = qgemv_i8_rows_per_cta(P.n_rows, cfg.sm_count, EPI == EPI_RESIDUAL && a.pack_out != nullptr);
   const int grid = (P.n_rows + P.rows_per_cta - 1) / P.rows_per_cta;
   const int S = 4 * a.batch;
   const int fixed = HDR_BYTES + RED_BYTES + ((P.kb * S * 32 + 127) & ~127) + ((P.kb * a.batch * 16 + 127) & ~127);
@@ -862,7 +937,7 @@ cudaError_t launch_t(const GemvI8Args &a, const LaunchCfg &cfg) {
     cudaError_t e = make_map(&maps[i], a.w[src], a.seg_rows[src], row_bytes, G::RS);
     if (e != cudaSuccess) return e;
   }
-  auto kernel = qgemv_i8_kernel<QT, EPI, B1>;
+  auto kernel = qgemv_i8_kernel<QT, B1, XQ>;
   static DeviceOnce attr_once;  // per instantiation and device
   bool *attr_flag = attr_once.slot();
   if (!attr_flag || !*attr_flag) {
@@ -887,12 +962,9 @@ cudaError_t launch_t(const GemvI8Args &a, const LaunchCfg &cfg) {
 
 template <int QT>
 cudaError_t launch_e(const GemvI8Args &a, const LaunchCfg &cfg) {
-  switch (a.epi) {
-    case EPI_STORE: return a.batch == 1 ? launch_t<QT, EPI_STORE, true>(a, cfg) : launch_t<QT, EPI_STORE, false>(a, cfg);
-    case EPI_RESIDUAL: return a.batch == 1 ? launch_t<QT, EPI_RESIDUAL, true>(a, cfg) : launch_t<QT, EPI_RESIDUAL, false>(a, cfg);
-    case EPI_SWIGLU: return a.batch == 1 ? launch_t<QT, EPI_SWIGLU, true>(a, cfg) : launch_t<QT, EPI_SWIGLU, false>(a, cfg);
-    default: return cudaErrorInvalidValue;
-  }
+  if (a.epi != EPI_STORE && a.epi != EPI_RESIDUAL && a.epi != EPI_SWIGLU) return cudaErrorInvalidValue;
+  if (a.batch != 1) return launch_t<QT, false, false>(a, cfg);
+  return a.xq ? launch_t<QT, true, true>(a, cfg) : launch_t<QT, true, false>(a, cfg);
 }
 
 }  // namespace
@@ -903,6 +975,14 @@ bool qgemv_i8_supported(int k, int batch) {
   return k > 0 && k % 256 == 0 && batch >= 1 && batch <= 2 && (size_t)k * 4 * batch <= 120 * 1024;
 }
 
+int qgemv_i8_rows_per_cta(int n_rows, int sm_count, bool whole_blocks) {
+  const int sms = sm_count > 0 ? sm_count : 148;
+  const int boxes = (n_rows + BOXR - 1) / BOXR;
+  int rows = ((boxes + sms - 1) / sms) * BOXR;
+  if (whole_blocks) rows = (rows + 31) & ~31;  // a residual epilogue that packs owns whole 32-element blocks
+  return rows;
+}
+
 size_t qgemv_i8_xq_bytes(int k) {
   const int kb = k / 32;
   return xq_ssq_offset(kb) + (((size_t)kb * 4 + 127) & ~(size_t)127);
@@ -910,11 +990,13 @@ size_t qgemv_i8_xq_bytes(int k) {
 
 cudaError_t launch_qgemv_i8(const GemvI8Args &a, const LaunchCfg &cfg) {
   if (!qgemv_i8_supported(a.k, a.batch) || a.nseg < 1 || a.nseg > 3 || (!a.x && !a.xq) || !a.y) return cudaErrorInvalidValue;
-  if (a.xq && (a.batch != 1 || (reinterpret_cast<uintptr_t>(a.xq) & 127))) return cudaErrorInvalidValue;
+  if (a.xq && (a.batch != 1 || (reinterpret_cast<uintptr_t>(a.xq) & 127) || (a.xq_fix && a.xq_nfix > 0 && !a.x)))
+    return cudaErrorInvalidValue;
   if (a.pack_out) {  // only the residual epilogue of a batch-1 step packs, and only whole blocks
     int rows = 0;
     for (int i = 0; i < a.nseg; ++i) rows += a.seg_rows[i];
-    if (a.epi != EPI_RESIDUAL || a.batch != 1 || rows % 32 || (reinterpret_cast<uintptr_t>(a.pack_out) & 127) ||
+    if (a.epi == EPI_SWIGLU) rows = a.seg_rows[0];
+    if ((a.epi != EPI_RESIDUAL && a.epi != EPI_SWIGLU) || a.batch != 1 || rows % 32 || (reinterpret_cast<uintptr_t>(a.pack_out) & 127) ||
         (a.pack_type != RG_TYPE_Q4_0 && a.pack_type != RG_TYPE_Q8_0))
       return cudaErrorInvalidValue;
   }

@@ -157,6 +157,16 @@ __device__ __forceinline__ void xpack_store(__half *xpack, int S, int b, int k, 
 __host__ __device__ inline size_t xq_side_offset(int kb) { return (size_t)kb * 128; }
 __host__ __device__ inline size_t xq_ssq_offset(int kb) { return (size_t)kb * 128 + (((size_t)kb * 16 + 127) & ~(size_t)127); }
 
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Phase stamp of the development trace: slot 0..7 for the first CTA of a launch, 8..15 for the last.
+__device__ __forceinline__ void trace_stamp(unsigned long long *trace, int slot, bool first_cta, bool last_cta) {
+  if (trace && (first_cta || last_cta)) trace[(first_cta ? 0 : 8) + slot] = global_ns();
+}
+
 // SwiGLU with the reference's operation order (src/ir/elementwise.rs:6772-6830,7046-7050):
 // silu(g) = g * (1 / (1 + exp2(g * (-1/ln 2)))), every step rounded to f32.
 __device__ __forceinline__ float swiglu(float g, float u) {

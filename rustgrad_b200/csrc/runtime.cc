@@ -255,7 +255,9 @@ struct rg_session {
   void *xn_pack = nullptr, *attn_pack = nullptr, *h_pack = nullptr, *head_pack = nullptr;
   // batch-1 decode: activation vectors packed by their producers for the integer GEMV that reads them
   // (qgemv_i8.cu): the residual stream after a projection, and the attention output
-  uint8_t *xq_x = nullptr, *xq_attn = nullptr;
+  uint8_t *xq_x = nullptr, *xq_attn = nullptr, *xq_h = nullptr;
+  int32_t *xq_h_fix = nullptr;  // blocks of the SwiGLU output that straddle two CTAs of the gate/up launch
+  int xq_h_nfix = 0;
   // Gumbel-max selection for the current step: device rows of uniforms [logit cols][vocab]; null = greedy
   const float *sample_uniforms = nullptr;
   float sample_temperature = 1.0f;
@@ -286,6 +288,12 @@ struct rg_session {
   // profiling pass: only the kernel families in family_mask are launched
   unsigned family_mask = 0xffffffffu;
   int cur_kind = 0;
+  // finer selection inside the GEMV family for the per-projection profile (bit = GemvSite); all by default
+  unsigned gemv_site_mask = 0xffffffffu;
+  int cur_site = 0;
+  // development trace (RG_B200_TRACE=1): 16 u64 per launch of a small-batch step, in launch order
+  unsigned long long *d_trace = nullptr;
+  int trace_cap = 0, trace_next = 0;
   // tensor-parallel partial sums: [0] output projection, [1] down projection.  Fused form: the buffers live
   // in one block that the other ranks map through CUDA IPC (tp_fused.cu); otherwise both point at `partial`
   float *tp_part[2] = {nullptr, nullptr};
@@ -332,10 +340,16 @@ static LaunchCfg lcfg(rg_session *s) {
   c.status = s->d_status;
   return c;
 }
+// The next launch's slots of the development trace (null when tracing is off or the buffer is full).
+static unsigned long long *next_trace(rg_session *s) {
+  if (!s->d_trace || s->trace_next >= s->trace_cap) return nullptr;
+  return s->d_trace + (size_t)16 * (size_t)s->trace_next++;
+}
 
 #define RG_LAUNCH(s, expr)                                                                       \
   do {                                                                                           \
-    if ((s)->family_mask & (1u << (s)->cur_kind)) {                                              \
+    if (((s)->family_mask & (1u << (s)->cur_kind)) &&                                            \
+        ((s)->cur_kind != 0 || ((s)->gemv_site_mask & (1u << (s)->cur_site)))) {                 \
       cudaError_t e__ = x_launch(expr);                                                          \
       (s)->launches_in_step++;                                                                   \
       if (e__ != cudaSuccess)                                                                    \
@@ -345,6 +359,8 @@ static LaunchCfg lcfg(rg_session *s) {
   } while (0)
 
 enum ProfKind { PROF_GEMV = 0, PROF_ATTN = 1, PROF_OTHER = 2, PROF_END = 3 };
+// Which projection a GEMV launch serves (forward_small); SITE_ANY for the other paths.
+enum GemvSite { SITE_ANY = 0, SITE_QKV = 1, SITE_O = 2, SITE_GATE_UP = 3, SITE_DOWN = 4, SITE_HEAD = 5, SITE_END = 6 };
 
 // Names the kernel family of the launches that follow; the profiling pass launches one family
 // at a time.
@@ -458,8 +474,11 @@ static bool small_batch_path(const rg_session *s, int ncols) {
 
 // Packed input / output of one integer GEMV launch of a batch-1 step (see GemvI8Args).
 struct PackedIo {
+  int site = SITE_ANY;
   const uint8_t *xq = nullptr;
   bool xq_norm = false;
+  const int32_t *xq_fix = nullptr;
+  int xq_nfix = 0;
   uint8_t *pack_out = nullptr;
   const float *pack_w = nullptr;
   int pack_type = 0;
@@ -471,6 +490,8 @@ static int32_t gemv_i8(rg_session *s, const DevTensor *const *w, int n, const fl
   GemvI8Args a;
   a.xq = io.xq;
   a.xq_norm = io.xq_norm;
+  a.xq_fix = io.xq_fix;
+  a.xq_nfix = io.xq_nfix;
   a.pack_out = io.pack_out;
   a.pack_w = io.pack_w;
   a.pack_type = io.pack_type;
@@ -491,7 +512,11 @@ static int32_t gemv_i8(rg_session *s, const DevTensor *const *w, int n, const fl
   a.y = y;
   a.ldy = ldy;
   prof_mark(s, PROF_GEMV);
-  RG_LAUNCH(s, launch_qgemv_i8(a, L));
+  s->cur_site = io.site;
+  LaunchCfg Lt = L;
+  Lt.trace = next_trace(s);
+  RG_LAUNCH(s, launch_qgemv_i8(a, Lt));
+  s->cur_site = SITE_ANY;
   return RG_OK;
 }
 
@@ -512,6 +537,7 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
   // One column on one GPU: the residual epilogues (output and down projection) leave the new residual
   // stream packed, with the next norm weight folded in, for the projection that reads it, whose
   // prologue is then a single bulk copy; the norm's scalar factor is applied to that projection's results.
+  s->trace_next = 0;
   const bool pre = ncols == 1 && !tp && s->xq_x && !env_flag("RG_B200_NO_PREPACK");
   // likewise the one-launch attention packs its output for the output projection (any world size:
   // the heads are rank-local)
@@ -522,6 +548,7 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
     const LayerW &W = s->layers[(size_t)l];
     const DevTensor *qkvw[3] = {&W.q, &W.k, &W.v};
     PackedIo qkv_io;
+    qkv_io.site = SITE_QKV;
     if (pre && l > 0) {  // layer 0 reads the embedding row, which nothing packed
       qkv_io.xq = s->xq_x;
       qkv_io.xq_norm = true;
@@ -559,7 +586,9 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
         fa.pack_out = s->xq_attn;
         fa.pack_type = W.o.type;
       }
-      RG_LAUNCH(s, launch_attention_fused(fa, L));
+      LaunchCfg Lt = L;
+      Lt.trace = next_trace(s);
+      RG_LAUNCH(s, launch_attention_fused(fa, Lt));
     } else {
       RopeArgs ra;
       ra.qkv = s->qkv;
@@ -596,6 +625,7 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
     }
     const DevTensor *ow[1] = {&W.o};
     PackedIo o_in;
+    o_in.site = SITE_O;
     if (pre_attn) o_in.xq = s->xq_attn;
     if (tp) {
       if ((rc = gemv_i8(s, ow, 1, s->attn_f32, qw, nullptr, nullptr, ncols, EPI_STORE, s->tp_part[0], d, L, o_in))) return rc;
@@ -611,19 +641,29 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
     }
     const DevTensor *guw[2] = {&W.gate, &W.up};
     PackedIo gu_io;
+    gu_io.site = SITE_GATE_UP;
     if (pre) {
       gu_io.xq = s->xq_x;
       gu_io.xq_norm = true;
+    }
+    PackedIo down_in;  // the SwiGLU epilogue packs the blocks that lie inside one of its CTAs, the down projection the rest
+    down_in.site = SITE_DOWN;
+    if (pre_attn && s->xq_h) {
+      gu_io.pack_out = s->xq_h;
+      gu_io.pack_type = W.down.type;
+      down_in.xq = s->xq_h;
+      down_in.xq_fix = s->xq_h_fix;
+      down_in.xq_nfix = s->xq_h_nfix;
     }
     if ((rc = gemv_i8(s, guw, 2, s->x, d, nullptr, reinterpret_cast<const float *>(W.ffn_norm.d), ncols, EPI_SWIGLU, s->h_f32,
                       s->ffn_l, tp_lib ? plain : L, gu_io)))
       return rc;
     const DevTensor *dw[1] = {&W.down};
     if (tp) {
-      if ((rc = gemv_i8(s, dw, 1, s->h_f32, s->ffn_l, nullptr, nullptr, ncols, EPI_STORE, s->tp_part[1], d, L))) return rc;
+      if ((rc = gemv_i8(s, dw, 1, s->h_f32, s->ffn_l, nullptr, nullptr, ncols, EPI_STORE, s->tp_part[1], d, L, down_in))) return rc;
       if ((rc = tp_reduce_add(s, ncols, 1))) return rc;
     } else {
-      PackedIo io;
+      PackedIo io = down_in;
       if (pre) {  // read next by the following layer's q/k/v projection, or by the head after the last layer
         const bool last = l + 1 == c.n_layers;
         io.pack_out = s->xq_x;
@@ -639,6 +679,7 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
     float *dst = split_head ? s->logits_l : s->logits;
     const int ld = split_head ? s->vocab_l : c.vocab;
     PackedIo head_io;
+    head_io.site = SITE_HEAD;
     if (pre) {  // one column: the logit column is column 0
       head_io.xq = s->xq_x;
       head_io.xq_norm = true;
@@ -1571,6 +1612,23 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   s->head_pack = raw;
   RG_TRY(dalloc(s.get(), &s->xq_x, qgemv_i8_xq_bytes(d)));
   RG_TRY(dalloc(s.get(), &s->xq_attn, qgemv_i8_xq_bytes(qw)));
+  if (env_flag("RG_B200_TRACE")) {
+    s->trace_cap = 5 * c.n_layers + 2;
+    RG_TRY(dalloc(s.get(), &s->d_trace, (size_t)16 * (size_t)s->trace_cap));
+    RG_CUDA(cudaMemsetAsync(s->d_trace, 0, sizeof(unsigned long long) * 16 * (size_t)s->trace_cap, s->stream));
+  }
+  if (s->ffn_l % 32 == 0) {
+    RG_TRY(dalloc(s.get(), &s->xq_h, qgemv_i8_xq_bytes(s->ffn_l)));
+    // the gate/up launch gives each CTA rows_per_cta rows of the SwiGLU output: a 32-row block that
+    // holds a CTA boundary is packed by the down projection instead
+    const int rpc = qgemv_i8_rows_per_cta(s->ffn_l, s->sm_count, false);
+    std::vector<int32_t> fix;
+    for (int b = rpc; b < s->ffn_l; b += rpc)
+      if (b % 32) fix.push_back(b / 32);
+    s->xq_h_nfix = (int)fix.size();
+    RG_TRY(dalloc(s.get(), &s->xq_h_fix, fix.size() + 1));
+    if (!fix.empty()) RG_CUDA(cudaMemcpy(s->xq_h_fix, fix.data(), fix.size() * sizeof(int32_t), cudaMemcpyHostToDevice));
+  }
   if (s->tp_world > 1 && !p->opt.disable_fused_allreduce && !env_flag("RG_B200_DISABLE_FUSED_ALLREDUCE")) RG_TRY(tp_fused_setup(s.get()));
   // RoPE tables in f64 on the host, cast to f32 (src/models/transformer/layer.rs:541-556)
   {
@@ -2060,10 +2118,10 @@ int32_t rg_b200_decode_loop(rg_session *s, const int32_t *first, int32_t batch, 
 }
 
 static int32_t decode_profile_impl(rg_session *s, const int32_t *first, int32_t batch, int32_t steps, float out_ms[4],
-                                   uint64_t out_launches[4], bool serialized) {
+                                   uint64_t out_launches[4], bool serialized, float *site_ms = nullptr) {
   int32_t rc = check_live(s);
   if (rc) return rc;
-  if (!first || !out_ms || batch < 1 || batch > s->max_batch || steps < 1) return fail(RG_INVALID_ARGUMENT, "bad arguments");
+  if (!first || (!out_ms && !site_ms) || batch < 1 || batch > s->max_batch || steps < 1) return fail(RG_INVALID_ARGUMENT, "bad arguments");
   for (int i = 0; i < batch; ++i) {
     if (first[i] < 0 || first[i] >= s->cfg.vocab) return fail(RG_TOKEN_OUT_OF_RANGE, "token in row " + std::to_string(i));
     if (s->position[(size_t)i] >= s->ctx) return fail(RG_CONTEXT_EXHAUSTED, "row " + std::to_string(i));
@@ -2082,26 +2140,29 @@ static int32_t decode_profile_impl(rg_session *s, const int32_t *first, int32_t 
   if (serialized) s->use_pdl = false;  // serialized launches: every kernel runs alone
   s->launches_in_step = 0;
   rc = forward(s, batch, batch, false);  // loads every kernel before capture; nothing is committed
-  double total = 0.0;
-  for (int fam = 0; fam < 3 && !rc; ++fam) {
+  // one selection of the step's launches, captured as a graph and replayed `steps` times between two events
+  auto time_selection = [&](unsigned family_mask, unsigned site_mask, float *ms_out, uint64_t *launches_out) -> int32_t {
     cudaGraphExec_t exec = nullptr;
-    s->family_mask = 1u << fam;
+    s->family_mask = family_mask;
+    s->gemv_site_mask = site_mask;
     s->launches_in_step = 0;
+    int32_t r = RG_OK;
     cudaError_t e = cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal);
     if (e == cudaSuccess) {
-      rc = forward(s, batch, batch, false);
+      r = forward(s, batch, batch, false);
       cudaGraph_t graph = nullptr;
       e = cudaStreamEndCapture(s->stream, &graph);
-      if (e == cudaSuccess && !rc) e = cudaGraphInstantiate(&exec, graph, 0);
+      if (e == cudaSuccess && !r) e = cudaGraphInstantiate(&exec, graph, 0);
       if (graph) cudaGraphDestroy(graph);
     }
     s->family_mask = 0xffffffffu;
-    if (!rc && e != cudaSuccess) rc = fail(RG_CUDA_ERROR, std::string("profile graph: ") + cudaGetErrorString(e));
-    if (rc) {
+    s->gemv_site_mask = 0xffffffffu;
+    if (!r && e != cudaSuccess) r = fail(RG_CUDA_ERROR, std::string("profile graph: ") + cudaGetErrorString(e));
+    if (r) {
       if (exec) cudaGraphExecDestroy(exec);
-      break;
+      return r;
     }
-    if (out_launches) out_launches[fam] = s->launches_in_step;
+    if (launches_out) *launches_out = s->launches_in_step;
     e = cudaGraphLaunch(exec, s->stream);  // warm replay
     if (e == cudaSuccess) e = cudaEventRecord(s->ev0, s->stream);
     for (int it = 0; it < steps && e == cudaSuccess; ++it) e = cudaGraphLaunch(exec, s->stream);
@@ -2112,17 +2173,27 @@ static int32_t decode_profile_impl(rg_session *s, const int32_t *first, int32_t 
     cudaGraphExecDestroy(exec);
     if (e != cudaSuccess) {
       s->poisoned = true;
-      rc = fail(RG_CUDA_ERROR, std::string("profile replay: ") + cudaGetErrorString(e));
-      break;
+      return fail(RG_CUDA_ERROR, std::string("profile replay: ") + cudaGetErrorString(e));
     }
-    out_ms[fam] = ms / (float)steps;
-    total += out_ms[fam];
+    *ms_out = ms / (float)steps;
+    return RG_OK;
+  };
+  double total = 0.0;
+  if (site_ms) {
+    // the projections of the GEMV family one at a time: q+k+v, output, gate+up, down, head
+    for (int site = SITE_QKV; site < SITE_END && !rc; ++site) rc = time_selection(1u << PROF_GEMV, 1u << site, &site_ms[site - 1], nullptr);
+  } else {
+    for (int fam = 0; fam < 3 && !rc; ++fam) {
+      rc = time_selection(1u << fam, 0xffffffffu, &out_ms[fam], out_launches ? &out_launches[fam] : nullptr);
+      if (!rc) total += out_ms[fam];
+    }
   }
-  s->family_mask = 0xffffffffu;
   s->use_pdl = saved_pdl;
   if (rc) return rc;
-  out_ms[3] = (float)total;
-  if (out_launches) out_launches[3] = out_launches[0] + out_launches[1] + out_launches[2];
+  if (!site_ms) {
+    out_ms[3] = (float)total;
+    if (out_launches) out_launches[3] = out_launches[0] + out_launches[1] + out_launches[2];
+  }
   return finish_step(s, 0, nullptr, 0);
 }
 
@@ -2134,6 +2205,21 @@ int32_t rg_b200_decode_profile(rg_session *s, const int32_t *first, int32_t batc
 int32_t rg_b200_decode_profile_in_step(rg_session *s, const int32_t *first, int32_t batch, int32_t steps, float out_ms[4],
                                        uint64_t out_launches[4]) {
   return decode_profile_impl(s, first, batch, steps, out_ms, out_launches, false);
+}
+
+int32_t rg_b200_decode_profile_projections(rg_session *s, const int32_t *first, int32_t batch, int32_t steps, float out_ms[5]) {
+  return decode_profile_impl(s, first, batch, steps, nullptr, nullptr, false, out_ms);
+}
+
+// Development aid, not part of the documented interface: copies the phase stamps of the last
+// small-batch step (RG_B200_TRACE=1 at prepare) to `out` (16 u64 per launch); returns the launch count.
+int32_t rg_b200_debug_read_trace(rg_session *s, unsigned long long *out, int32_t max_launches) {
+  if (!s || !out || !s->d_trace) return 0;
+  cudaSetDevice(s->opt.device);
+  const int n = std::min(max_launches, s->trace_cap);
+  cudaStreamSynchronize(s->stream);
+  cudaMemcpy(out, s->d_trace, sizeof(unsigned long long) * 16 * (size_t)n, cudaMemcpyDeviceToHost);
+  return n;
 }
 
 int32_t rg_b200_report(const rg_session *s, rg_report *out) {

@@ -318,6 +318,13 @@ class LlamaCudaSession:
         keys = ("gemv", "attention", "other", "total")
         return {k: {"ms_per_step": ms[i], "launches_per_step": marks[i]} for i, k in enumerate(keys)}
 
+    def decode_profile_projections(self, first_tokens, steps: int) -> dict:
+        """Milliseconds per step of the GEMV launches of each projection, each set replayed alone."""
+        t = np.ascontiguousarray(first_tokens, dtype=np.int32)
+        ms = (C.c_float * 5)()
+        check(self._L.rg_b200_decode_profile_projections(self._h, _i32(t), t.size, steps, ms))
+        return dict(zip(("qkv", "attn_output", "gate_up", "down", "head"), (float(v) for v in ms)))
+
     def report(self) -> dict:
         r = Report()
         check(self._L.rg_b200_report(self._h, C.byref(r)))
