@@ -218,7 +218,8 @@ static int32_t check_tensor(rg_plan *p, const std::string &name, int32_t type, u
 // ------------------------------------------------------------------------------------------
 // Session
 // ------------------------------------------------------------------------------------------
-static constexpr int MAXC = 8;    // columns of the GEMV paths: decode batch <= 8, short prefill tails
+static constexpr int MAXC = 16;   // columns of the GEMV paths: decode batches <= 16 (dense-weight GEMVs: <= DENSE_MAXC)
+static constexpr int DENSE_MAXC = 8;  // columns the dense-weight GEMV takes; prompt chunk of models with dense tensors
 static constexpr int WMAX = 1024;  // columns of the tensor-core path: prefill chunk, decode batch 9..32
 static constexpr int SCOLS = 256;  // columns the per-column attention kernels are given scratch for
 static constexpr int BMAX = 32;   // independent sequences per session
@@ -1000,7 +1001,10 @@ static int32_t tp_fused_setup(rg_session *s) {
 // (indices in ctrl.logit_cols) get logits + greedy ids; 0 skips the head (non-final prefill chunk).
 static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance) {
   if (small_batch_path(s, ncols)) return forward_small(s, ncols, n_logit_cols, advance);
-  if (ncols > MAXC) {
+  // Decode batches of 9..16 rows stream the weights once through the f16-MMA GEMV (four column
+  // tiles); prompt chunks of that size and everything wider run on the tcgen05 GEMM.
+  const bool gemv16 = ncols > DENSE_MAXC && ncols <= MAXC && !s->chunk_is_prompt && wide_path_ok(s) && !env_flag("RG_B200_NO_GEMV16");
+  if (ncols > DENSE_MAXC && !gemv16) {
     if (!wide_path_ok(s))
       return fail(RG_UNSUPPORTED_GEOMETRY, "more than 8 columns need packed projections with K a multiple of 256");
     return forward_wide(s, ncols, n_logit_cols, advance);
@@ -1024,6 +1028,30 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
     int32_t rc = linear(s, qkvw, 3, s->xn_pack, s->xn_f32, d, ncols, EPI_STORE, s->qkv, qkv_w);
     if (rc) return rc;
     prof_mark(s, PROF_ATTN);
+    if (gemv16 && s->attn_counters) {
+      // rows of distinct sequences: RoPE, cache append, split attention and the combine in one launch
+      FusedAttnArgs fa;
+      fa.qkv = s->qkv;
+      fa.cols = ncols;
+      fa.heads = s->heads_l;
+      fa.kv_heads = s->kv_l;
+      fa.hd = hd;
+      fa.ctx = s->ctx;
+      fa.col_seq = ctl->seq;
+      fa.col_pos = ctl->pos;
+      fa.cos_t = s->cos_t;
+      fa.sin_t = s->sin_t;
+      fa.k_cache = s->k_cache[(size_t)l];
+      fa.v_cache = s->v_cache[(size_t)l];
+      fa.kv_f32 = s->kv_f32;
+      fa.scratch = s->attn_scratch;
+      fa.max_splits = s->attn_max_splits;
+      fa.counters = s->attn_counters;
+      fa.out = s->attn_f32;
+      RG_LAUNCH(s, launch_attention_fused(fa, L));
+      prof_mark(s, PROF_OTHER);
+      RG_LAUNCH(s, launch_pack(s->attn_f32, qw, qw, ncols, s->attn_pack, L));
+    } else {
     RopeArgs ra;
     ra.qkv = s->qkv;
     ra.cols = ncols;
@@ -1057,6 +1085,7 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
     aa.out_f32 = W.o.packed() ? nullptr : s->attn_f32;
     RG_LAUNCH(s, launch_attention(aa, L));
     if (s->family_mask & (1u << PROF_ATTN)) s->launches_in_step++;  // split + combine
+    }
     const DevTensor *ow[1] = {&W.o};
     if (s->tp_world > 1) {
       if ((rc = linear(s, ow, 1, s->attn_pack, s->attn_f32, qw, ncols, EPI_STORE, s->tp_part[0], d))) return rc;
@@ -1757,7 +1786,7 @@ static int32_t prefill_impl(rg_session *s, int32_t row, const int32_t *ids, size
   const bool wide_ok = wide_path_ok(s);  // prompt chunks of up to 1024 tokens on the tensor cores
   for (size_t done = 0; done < n;) {
     const int wide_chunk = prefill_attention_supported(s->heads_l, s->kv_l, s->cfg.head_dim) && !env_flag("RG_B200_SPLIT_ATTENTION") ? WMAX : SCOLS;
-    const int chunk = (int)std::min<size_t>(wide_ok ? wide_chunk : MAXC, n - done);
+    const int chunk = (int)std::min<size_t>(wide_ok ? wide_chunk : DENSE_MAXC, n - done);
     const bool last = done + (size_t)chunk == n;
     Ctrl *h = s->h_ctrl;
     for (int i = 0; i < chunk; ++i) {

@@ -159,8 +159,9 @@ def test_tensor_core_path_for_long_prompts_and_wide_decode_batches():
         w = oracle.forward([tok], O.MODE_FAST)
         assert_logits_close(wide.run_token(tok), w)
         tok = O.select_greedy(w)
-    # 16 rows decoding together
+    # 16 rows decoding together: the f16-MMA GEMV with four column tiles streams the weights once
     rows = 16
+    before = session.launch_count("qgemv")
     s = session.LlamaCudaPlan.from_tensors(cfg, tensors, session.CudaSessionTarget(kv_f32=True, max_batch=rows,
                                                                                   max_context=64)).prepare()
     oracles = [O.OracleModel(cfg, tensors, threads=2) for _ in range(rows)]
@@ -182,8 +183,43 @@ def test_tensor_core_path_for_long_prompts_and_wide_decode_batches():
                 near_ties.append((r, float(top2[1] - top2[0])))
         toks = nxt
     # a differing greedy id is a finding, never silently accepted: none is expected on this model
-    print(f"greedy ids differing from the checker on the tensor-core decode path: {len(near_ties)} {near_ties}")
+    print(f"greedy ids differing from the checker on the 16-row decode path: {len(near_ties)} {near_ties}")
     assert not near_ties
+    assert session.launch_count("qgemv") > before
+
+
+def test_twenty_rows_decode_on_the_tensor_core_path(monkeypatch):
+    """Decode batches of 17..32 rows (and, with the GEMV route switched off, 9..16) run the projections on
+    the tcgen05 GEMM with compensated f16 operands: logit bar and greedy ids against the checker."""
+    cfg = synth.scaled(synth.TINY, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn_dim=1024, vocab=640, n_layers=3,
+                       rope_theta=500000.0, max_context=64)
+    tensors = synth.build_tensors(cfg, seed=9, body_type=quant.Q4_0, embed_type=quant.Q8_0, head_type=quant.Q8_0,
+                                  tied_head=False)
+    for rows, no_gemv16 in ((20, False), (12, True)):
+        if no_gemv16:
+            monkeypatch.setenv("RG_B200_NO_GEMV16", "1")
+        before = session.launch_count("qgemm_tc")
+        s = session.LlamaCudaPlan.from_tensors(cfg, tensors, session.CudaSessionTarget(kv_f32=True, max_batch=rows,
+                                                                                      max_context=64)).prepare()
+        oracles = [O.OracleModel(cfg, tensors, threads=2) for _ in range(rows)]
+        toks = []
+        for r in range(rows):
+            p = synth.prompt_ids(cfg, 3 + r % 5, seed=70 + r)
+            s.prefill_ids(p, row=r)
+            toks.append(O.select_greedy(oracles[r].forward(p, O.MODE_FAST)))
+        differing = 0
+        for _ in range(2):
+            logits, greedy = s.decode(toks, want_logits=True)
+            nxt = []
+            for r in range(rows):
+                w = oracles[r].forward([toks[r]], O.MODE_FAST)
+                assert_logits_close(logits[r], w)
+                nxt.append(O.select_greedy(w))
+                differing += int(greedy[r]) != nxt[r]
+            toks = nxt
+        print(f"{rows} rows on the tensor-core path: greedy ids differing from the checker: {differing}")
+        assert differing == 0
+        assert session.launch_count("qgemm_tc") > before
 
 
 def test_stop_on_eos_and_last_token_not_fed_back(tiny):
