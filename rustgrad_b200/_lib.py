@@ -56,6 +56,10 @@ EXPORTS = [
     "rg_b200_tokenizer_is_end", "rg_b200_tokenizer_parse_preset", "rg_b200_tokenizer_encode", "rg_b200_tokenizer_decode",
     "rg_b200_tok_stream_new", "rg_b200_tok_stream_push", "rg_b200_tok_stream_finish", "rg_b200_tok_stream_free",
     "rg_b200_chat_template_from_gguf", "rg_b200_chat_template_text", "rg_b200_chat_render",
+    # include/rg_b200_workflow.h (bound in workflow.py)
+    "rg_b200_workflow_open", "rg_b200_workflow_close", "rg_b200_workflow_session", "rg_b200_workflow_tokenizer",
+    "rg_b200_workflow_generate_text", "rg_b200_workflow_generate_chat", "rg_b200_workflow_prompt_ids",
+    "rg_b200_workflow_generated_ids", "rg_b200_workflow_decoded", "rg_b200_workflow_rendered_prompt",
 ]
 
 _lib = None

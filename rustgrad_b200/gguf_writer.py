@@ -68,8 +68,50 @@ def synthetic_token_table(vocab: int):
     return tokens, [1] * vocab
 
 
-def llama_metadata(cfg: dict) -> list[bytes]:
-    tokens, types = synthetic_token_table(cfg["vocab"])
+CHAT_SPECIALS = ("<|begin_of_text|>", "<|end_of_text|>", "<|start_header_id|>", "<|end_header_id|>", "<|eot_id|>")
+
+
+def chat_token_table(vocab: int):
+    """A token table text can be encoded with: the 256 characters of the GPT-2 byte alphabet
+    (src/tokenizer/mod.rs:505-528) as ids 0..255, a few ranked merges (the id of a merged token is
+    its rank), filler tokens, and the Llama-3 control tokens as the last five ids (type 3).
+    Returns (tokens, types, ids) with ids = {"bos", "eos", "eot"}."""
+    direct = list(range(33, 127)) + list(range(161, 173)) + list(range(174, 256))
+    table = {b: chr(b) for b in direct}
+    extra = 0
+    for b in range(256):
+        if b not in table:
+            table[b] = chr(256 + extra)
+            extra += 1
+    enc = lambda text: "".join(table[b] for b in text.encode("utf-8"))  # noqa: E731
+    tokens = [table[b] for b in range(256)]
+    for word in ("he", "ll", "lo", "hell", "hello", " w", "or", "ld", " wor", " world", "th", " th", " the", "in", "er", "\n\n"):
+        tokens.append(enc(word))
+    if vocab < len(tokens) + len(CHAT_SPECIALS):
+        raise ValueError("vocabulary too small for the chat token table")
+    alphabet = "abcdefghijklmnopqrstuvwxyzABCDEFGHIJKLMNOPQRSTUVWXYZ0123456789"
+    i = 0
+    while len(tokens) < vocab - len(CHAT_SPECIALS):
+        n, chars = i, []
+        while True:
+            chars.append(alphabet[n % len(alphabet)])
+            n //= len(alphabet)
+            if n == 0:
+                break
+        tokens.append("zz" + "".join(chars) + "q")
+        i += 1
+    types = [1] * len(tokens) + [3] * len(CHAT_SPECIALS)
+    tokens += list(CHAT_SPECIALS)
+    base = vocab - len(CHAT_SPECIALS)
+    return tokens, types, {"bos": base, "eos": base + 1, "eot": base + 4}
+
+
+def llama_metadata(cfg: dict, chat_tokens: bool = False) -> list[bytes]:
+    if chat_tokens:
+        tokens, types, ids = chat_token_table(cfg["vocab"])
+    else:
+        tokens, types = synthetic_token_table(cfg["vocab"])
+        ids = None
     kvs = [
         kv_str("general.architecture", "llama"),
         kv_u32("general.alignment", ALIGNMENT),
@@ -85,12 +127,15 @@ def llama_metadata(cfg: dict) -> list[bytes]:
         kv_str("tokenizer.ggml.pre", "llama-bpe"),
         kv_str_array("tokenizer.ggml.tokens", tokens),
         kv_i32_array("tokenizer.ggml.token_type", types),
-        kv_bool("tokenizer.ggml.add_bos_token", False),
+        kv_bool("tokenizer.ggml.add_bos_token", chat_tokens),
     ]
+    if ids is not None:
+        kvs += [kv_u32("tokenizer.ggml.bos_token_id", ids["bos"]), kv_u32("tokenizer.ggml.eos_token_id", ids["eos"]),
+                kv_u32("tokenizer.ggml.eot_token_id", ids["eot"])]
     if cfg["head_dim"] * cfg["n_heads"] != cfg["d_model"]:
         kvs.append(kv_u32("llama.attention.key_length", cfg["head_dim"]))
         kvs.append(kv_u32("llama.attention.value_length", cfg["head_dim"]))
-    if cfg.get("eos_id", -1) >= 0:
+    if ids is None and cfg.get("eos_id", -1) >= 0:
         kvs.append(kv_u32("tokenizer.ggml.eos_token_id", cfg["eos_id"]))
     return kvs
 

@@ -69,9 +69,11 @@ def build_tensors(cfg: dict, seed: int, body_type: int = Q8_0, embed_type: int |
     return tensors
 
 
-def gguf_bytes(cfg: dict, tensors: dict) -> bytes:
+def gguf_bytes(cfg: dict, tensors: dict, chat_tokens: bool = False) -> bytes:
+    """The model as a GGUF file; ``chat_tokens`` gives it a token table that text can be encoded with
+    (byte alphabet, merges, Llama-3 control tokens) instead of opaque token names."""
     buf = io.BytesIO()
-    gguf_writer.write_gguf(buf, gguf_writer.llama_metadata(cfg), tensors)
+    gguf_writer.write_gguf(buf, gguf_writer.llama_metadata(cfg, chat_tokens), tensors)
     return buf.getvalue()
 
 
