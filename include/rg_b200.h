@@ -41,7 +41,7 @@ typedef enum {
   RG_MALFORMED_GGUF = 14,
   RG_MISSING_TENSOR = 15,
   RG_UNEXPECTED_TENSOR = 16,
-  RG_UNSUPPORTED_VARIANT = 17,  /* rope scaling, experts, partial rotary, biases, q/k norms */
+  RG_UNSUPPORTED_VARIANT = 17,  /* rope scaling, experts, MLA, LoRA, partial q/k-norm or bias families */
   RG_MISSING_METADATA = 18,
   RG_EMPTY_PROMPT = 19,
   RG_UNSUPPORTED_GEOMETRY = 20  /* a shape the sm_100a kernels do not cover (K % 256 != 0 for packed) */
@@ -67,6 +67,14 @@ typedef struct {
   double rope_theta;
   int32_t eos_id; /* -1 = none */
   int32_t eot_id; /* -1 = none */
+  /* Variants of the layer the reference's binder accepts (model.rs:160-175,253-282,
+   * layer.rs:274-346,481-571); all zero for the plain Llama layer.  They run on one GPU. */
+  int32_t rope_dim; /* rotary lanes per head (llama.rope.dimension_count), even, <= head_dim; 0 = head_dim.
+                     * The query is de-interleaved over its last rope_dim lanes, the key over the whole
+                     * head, and lanes [0, rope_dim) of both rotate (layer.rs:481-571). */
+  int32_t qk_norm;  /* 0 none; 1 per head: blk.N.attn_{q,k}_norm.weight [head_dim];
+                     * 2 per projection: weights [heads * head_dim], query and key widths equal */
+  int32_t qkv_bias; /* 1: blk.N.attn_{q,k,v}.bias, added after the lane permutation */
 } rg_llama_config;
 
 /* Session options.  Zero-initialise, then set what differs.  (rustgrad has no config framework:
@@ -287,7 +295,7 @@ int32_t rg_b200_attention_decode_noalloc(const float *q_dev, const void *keys_de
  * (src/models/transformer/serving/mod.rs:557-690) rebuilds a batch from per-request K/V
  * snapshots at every step; here a request keeps one cache row of the session while it runs, and a
  * step is one decode launch over an arbitrary set of rows plus one prefill per newly admitted
- * prompt.  rustgrad_b200/serving.py holds the scheduler that drives them. ---- */
+ * prompt.  rg_b200_serving.h declares the scheduler that drives them. ---- */
 typedef struct rg_kv_snapshot rg_kv_snapshot;
 /* Forgets the cached positions of one row (a finished request's slot is handed to the next). */
 int32_t rg_b200_reset_row(rg_session *s, int32_t row);

@@ -37,6 +37,7 @@ class Config(C.Structure):
         ("n_layers", C.c_int32), ("d_model", C.c_int32), ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32),
         ("head_dim", C.c_int32), ("ffn_dim", C.c_int32), ("vocab", C.c_int32), ("max_context", C.c_int32),
         ("norm_eps", C.c_float), ("rope_theta", C.c_double), ("eos_id", C.c_int32), ("eot_id", C.c_int32),
+        ("rope_dim", C.c_int32), ("qk_norm", C.c_int32), ("qkv_bias", C.c_int32),
     ]
 
 
@@ -197,7 +198,8 @@ class OracleModel:
         self.cfg = Config(
             config["n_layers"], config["d_model"], config["n_heads"], config["n_kv_heads"], config["head_dim"],
             config["ffn_dim"], config["vocab"], config["max_context"], config["norm_eps"], config["rope_theta"],
-            config.get("eos_id", -1), config.get("eot_id", -1))
+            config.get("eos_id", -1), config.get("eot_id", -1), config.get("rope_dim", 0), config.get("qk_norm", 0),
+            config.get("qkv_bias", 0))
         self.vocab = config["vocab"]
         self.threads = threads or (os.cpu_count() or 1)
         self._keep = []

@@ -288,8 +288,10 @@ typedef struct {
   const uint8_t *bytes;
 } rgo_tensor;
 
+#define RGO_LAYER_TENSORS 14
 typedef struct {
   rgo_tensor attn_norm, attn_q, attn_k, attn_v, attn_output, ffn_norm, ffn_gate, ffn_up, ffn_down;
+  rgo_tensor q_norm, k_norm, q_bias, k_bias, v_bias; /* variants only */
 } rgo_layer;
 
 struct rgo_model {
@@ -311,13 +313,15 @@ rgo_model *rgo_model_create(const rgo_config *c) {
       c->head_dim <= 0 || c->ffn_dim <= 0 || c->vocab <= 0 || c->max_context <= 0 ||
       c->n_heads % c->n_kv_heads || (c->head_dim & 1))
     return NULL;
+  if (c->rope_dim < 0 || c->rope_dim > c->head_dim || (c->rope_dim & 1) || c->qk_norm < 0 || c->qk_norm > 2) return NULL;
+  if (c->qk_norm == 2 && c->n_heads != c->n_kv_heads) return NULL; /* model.rs:262-268: equal widths only */
   rgo_model *m = (rgo_model *)calloc(1, sizeof(*m));
   m->cfg = *c;
   m->layers = (rgo_layer *)calloc((size_t)c->n_layers, sizeof(rgo_layer));
   m->token_embd.type = m->output_norm.type = m->output.type = -1;
   for (int l = 0; l < c->n_layers; ++l) {
     rgo_tensor *t = (rgo_tensor *)&m->layers[l];
-    for (int i = 0; i < 9; ++i) t[i].type = -1;
+    for (int i = 0; i < RGO_LAYER_TENSORS; ++i) t[i].type = -1;
   }
   return m;
 }
@@ -349,6 +353,13 @@ static rgo_tensor *find_tensor(rgo_model *m, const char *name, size_t *rows, siz
   if (!strcmp(s, "ffn_gate.weight")) { *rows = f; *cols = d; return &L->ffn_gate; }
   if (!strcmp(s, "ffn_up.weight")) { *rows = f; *cols = d; return &L->ffn_up; }
   if (!strcmp(s, "ffn_down.weight")) { *rows = d; *cols = f; return &L->ffn_down; }
+  /* model.rs:427-449: present only for the variant the configuration names */
+  size_t hd = (size_t)c->head_dim;
+  if (c->qk_norm && !strcmp(s, "attn_q_norm.weight")) { *rows = 1; *cols = c->qk_norm == 1 ? hd : qw; *is_norm = 1; return &L->q_norm; }
+  if (c->qk_norm && !strcmp(s, "attn_k_norm.weight")) { *rows = 1; *cols = c->qk_norm == 1 ? hd : kw; *is_norm = 1; return &L->k_norm; }
+  if (c->qkv_bias && !strcmp(s, "attn_q.bias")) { *rows = 1; *cols = qw; *is_norm = 1; return &L->q_bias; }
+  if (c->qkv_bias && !strcmp(s, "attn_k.bias")) { *rows = 1; *cols = kw; *is_norm = 1; return &L->k_bias; }
+  if (c->qkv_bias && !strcmp(s, "attn_v.bias")) { *rows = 1; *cols = kw; *is_norm = 1; return &L->v_bias; }
   return NULL;
 }
 
@@ -376,6 +387,9 @@ int rgo_model_check(const rgo_model *m) {
     const rgo_tensor *t = (const rgo_tensor *)&m->layers[l];
     for (int i = 0; i < 9; ++i)
       if (t[i].type < 0) return RGO_ERR_ARG;
+    const rgo_layer *L = &m->layers[l];
+    if (m->cfg.qk_norm && (L->q_norm.type < 0 || L->k_norm.type < 0)) return RGO_ERR_ARG;
+    if (m->cfg.qkv_bias && (L->q_bias.type < 0 || L->k_bias.type < 0 || L->v_bias.type < 0)) return RGO_ERR_ARG;
   }
   return RGO_OK;
 }
@@ -510,25 +524,30 @@ static int linear(const rgo_tensor *w, const float *x, int S, float *y, int mode
   return failed ? RGO_ERR_NON_FINITE : RGO_OK;
 }
 
-/* src/models/transformer/layer.rs:481-525 with rope_dim == head_dim: out[j] = in[2j],
- * out[half + j] = in[2j + 1] inside every head. */
-static void deinterleave_heads(float *v, int heads, int hd, float *tmp) {
-  int half = hd / 2;
+/* permute_rope_projection (src/models/transformer/layer.rs:481-525): inside every head the last
+ * `permuted` lanes are de-interleaved, out[prefix + j] = in[prefix + 2j],
+ * out[prefix + permuted/2 + j] = in[prefix + 2j + 1], and the first prefix = hd - permuted lanes
+ * stay.  The query is permuted over its last rope_dim lanes (preserve_prefix), the key over the
+ * whole head (layer.rs:274-293). */
+static void deinterleave_heads(float *v, int heads, int hd, int permuted, float *tmp) {
+  int half = permuted / 2, prefix = hd - permuted;
   for (int h = 0; h < heads; ++h) {
-    float *p = v + (size_t)h * hd;
+    float *p = v + (size_t)h * hd + prefix;
     for (int j = 0; j < half; ++j) {
       tmp[j] = p[2 * j];
       tmp[half + j] = p[2 * j + 1];
     }
-    memcpy(p, tmp, (size_t)hd * sizeof(float));
+    memcpy(p, tmp, (size_t)permuted * sizeof(float));
   }
 }
 
-/* src/models/transformer/layer.rs:528-571 */
-static void rope_heads(float *v, int heads, int hd, int position, double theta) {
-  int half = hd / 2;
+/* apply_rope (src/models/transformer/layer.rs:528-571): lanes [0, rope_dim) of every head rotate as
+ * the halves [0, rope_dim/2) and [rope_dim/2, rope_dim) with frequency 1 / theta^(2i / rope_dim);
+ * lanes [rope_dim, hd) pass through. */
+static void rope_heads(float *v, int heads, int hd, int rope_dim, int position, double theta) {
+  int half = rope_dim / 2;
   for (int i = 0; i < half; ++i) {
-    double frequency = 1.0 / pow(theta, (double)(2 * i) / (double)hd);
+    double frequency = 1.0 / pow(theta, (double)(2 * i) / (double)rope_dim);
     double angle = (double)position * frequency;
     float c = (float)cos(angle), s = (float)sin(angle);
     for (int h = 0; h < heads; ++h) {
@@ -625,6 +644,8 @@ int rgo_forward(const rgo_model *m, rgo_cache *cache, const int32_t *tokens, int
   float *proj = (float *)malloc((size_t)S * d * 4);
   float *gate = (float *)malloc((size_t)S * F * 4), *up = (float *)malloc((size_t)S * F * 4);
   float *wn = (float *)malloc((size_t)d * 4), *tmp = (float *)malloc((size_t)hd * 4);
+  float *vec = (float *)malloc((size_t)qw * 4), *vec2 = (float *)malloc((size_t)qw * 4);
+  const int rope_dim = c->rope_dim ? c->rope_dim : hd;
 
   /* embedding: src/gguf/quantization/row_gather.rs:170-181 */
   for (int s = 0; s < S && !rc; ++s)
@@ -640,10 +661,37 @@ int rgo_forward(const rgo_model *m, rgo_cache *cache, const int32_t *tokens, int
     float *K_l = cache->keys[l], *V_l = cache->values[l];
     for (int s = 0; s < S; ++s) {
       float *qs = q + (size_t)s * qw, *ks = k + (size_t)s * kw, *vs = v + (size_t)s * kw;
-      deinterleave_heads(qs, H, hd, tmp);
-      deinterleave_heads(ks, KV, hd, tmp);
-      rope_heads(qs, H, hd, past + s, c->rope_theta);
-      rope_heads(ks, KV, hd, past + s, c->rope_theta);
+      deinterleave_heads(qs, H, hd, rope_dim, tmp); /* preserve_prefix: only the rotary lanes */
+      deinterleave_heads(ks, KV, hd, hd, tmp);
+      if (c->qkv_bias) { /* layer.rs:294-299: after the permutation, lane by lane */
+        norm_weight(&L->q_bias, vec);
+        for (int i = 0; i < qw; ++i) qs[i] = qs[i] + vec[i];
+        norm_weight(&L->k_bias, vec);
+        for (int i = 0; i < kw; ++i) ks[i] = ks[i] + vec[i];
+        norm_weight(&L->v_bias, vec);
+        for (int i = 0; i < kw; ++i) vs[i] = vs[i] + vec[i];
+      }
+      if (c->qk_norm == 2) { /* layer.rs:300-317: RMSNorm over the whole projection */
+        norm_weight(&L->q_norm, vec);
+        rms_norm_strict(qs, vec, qw, c->norm_eps, vec2);
+        memcpy(qs, vec2, (size_t)qw * 4);
+        norm_weight(&L->k_norm, vec);
+        rms_norm_strict(ks, vec, kw, c->norm_eps, vec2);
+        memcpy(ks, vec2, (size_t)kw * 4);
+      } else if (c->qk_norm == 1) { /* layer.rs:321-331: RMSNorm inside every head */
+        norm_weight(&L->q_norm, vec);
+        for (int h = 0; h < H; ++h) {
+          rms_norm_strict(qs + (size_t)h * hd, vec, hd, c->norm_eps, vec2);
+          memcpy(qs + (size_t)h * hd, vec2, (size_t)hd * 4);
+        }
+        norm_weight(&L->k_norm, vec);
+        for (int h = 0; h < KV; ++h) {
+          rms_norm_strict(ks + (size_t)h * hd, vec, hd, c->norm_eps, vec2);
+          memcpy(ks + (size_t)h * hd, vec2, (size_t)hd * 4);
+        }
+      }
+      rope_heads(qs, H, hd, rope_dim, past + s, c->rope_theta);
+      rope_heads(ks, KV, hd, rope_dim, past + s, c->rope_theta);
       /* cache append: src/models/transformer/layer.rs:348-373 */
       for (int h = 0; h < KV; ++h)
         for (int j = 0; j < hd; ++j) {
@@ -688,6 +736,7 @@ int rgo_forward(const rgo_model *m, rgo_cache *cache, const int32_t *tokens, int
   }
   if (!rc) cache->len = past + S; /* commit only on success: model.rs:917-920 */
   free(x); free(nx); free(q); free(k); free(v); free(att); free(proj); free(gate); free(up); free(wn); free(tmp);
+  free(vec); free(vec2);
   return rc;
 }
 
@@ -796,6 +845,8 @@ int rgo_forward_f64(const rgo_model *m, const int32_t *tokens, int S, double *lo
   if (rgo_model_check(m) || S <= 0 || S > c->max_context) return RGO_ERR_ARG;
   int d = c->d_model, hd = c->head_dim, H = c->n_heads, KV = c->n_kv_heads, F = c->ffn_dim;
   int qw = H * hd, kw = KV * hd, group = H / KV, half = hd / 2;
+  const int rope_dim = c->rope_dim ? c->rope_dim : hd;
+  const int variant = rope_dim != hd || c->qk_norm || c->qkv_bias;
   double *x = (double *)malloc((size_t)S * d * 8), *nx = (double *)malloc((size_t)S * d * 8);
   double *q = (double *)malloc((size_t)S * qw * 8), *k = (double *)malloc((size_t)S * kw * 8);
   double *v = (double *)malloc((size_t)S * kw * 8), *att = (double *)malloc((size_t)S * qw * 8);
@@ -815,6 +866,48 @@ int rgo_forward_f64(const rgo_model *m, const int32_t *tokens, int S, double *lo
     linear_f64(&L->attn_q, nx, S, q);
     linear_f64(&L->attn_k, nx, S, k);
     linear_f64(&L->attn_v, nx, S, v);
+    if (variant) {
+      /* the variants in double precision, written from the definitions: lane permutation of the
+       * rotary part, bias, RMS normalisation of q and k, rotation of the first rope_dim lanes */
+      double *pd = (double *)malloc((size_t)hd * 8);
+      for (int s = 0; s < S; ++s) {
+        for (int h = 0; h < H + KV; ++h) {
+          double *p = (h < H) ? q + (size_t)s * qw + (size_t)h * hd : k + (size_t)s * kw + (size_t)(h - H) * hd;
+          int permuted = (h < H) ? rope_dim : hd, prefix = hd - permuted;
+          for (int j = 0; j < permuted / 2; ++j) {
+            pd[j] = p[prefix + 2 * j];
+            pd[permuted / 2 + j] = p[prefix + 2 * j + 1];
+          }
+          for (int j = 0; j < permuted; ++j) p[prefix + j] = pd[j];
+        }
+        if (c->qkv_bias) {
+          decode_span(L->q_bias.type, L->q_bias.bytes, 0, (size_t)qw, tmp);
+          for (int i = 0; i < qw; ++i) q[(size_t)s * qw + i] += tmp[i];
+          decode_span(L->k_bias.type, L->k_bias.bytes, 0, (size_t)kw, tmp);
+          for (int i = 0; i < kw; ++i) k[(size_t)s * kw + i] += tmp[i];
+          decode_span(L->v_bias.type, L->v_bias.bytes, 0, (size_t)kw, tmp);
+          for (int i = 0; i < kw; ++i) v[(size_t)s * kw + i] += tmp[i];
+        }
+        if (c->qk_norm == 2) {
+          rms_f64(q + (size_t)s * qw, &L->q_norm, qw, c->norm_eps, q + (size_t)s * qw, tmp);
+          rms_f64(k + (size_t)s * kw, &L->k_norm, kw, c->norm_eps, k + (size_t)s * kw, tmp);
+        } else if (c->qk_norm == 1) {
+          for (int h = 0; h < H; ++h) rms_f64(q + (size_t)s * qw + (size_t)h * hd, &L->q_norm, hd, c->norm_eps, q + (size_t)s * qw + (size_t)h * hd, tmp);
+          for (int h = 0; h < KV; ++h) rms_f64(k + (size_t)s * kw + (size_t)h * hd, &L->k_norm, hd, c->norm_eps, k + (size_t)s * kw + (size_t)h * hd, tmp);
+        }
+        for (int i = 0; i < rope_dim / 2; ++i) {
+          double ang = (double)s / pow(c->rope_theta, (double)(2 * i) / rope_dim);
+          double cs = cos(ang), sn = sin(ang);
+          for (int h = 0; h < H + KV; ++h) {
+            double *p = (h < H) ? q + (size_t)s * qw + (size_t)h * hd : k + (size_t)s * kw + (size_t)(h - H) * hd;
+            double a = p[i], b = p[rope_dim / 2 + i];
+            p[i] = a * cs - b * sn;
+            p[rope_dim / 2 + i] = b * cs + a * sn;
+          }
+        }
+      }
+      free(pd);
+    } else
     /* rotate adjacent lane pairs (2i, 2i+1) in place: equivalent to de-interleave + split-half */
     for (int s = 0; s < S; ++s)
       for (int i = 0; i < half; ++i) {

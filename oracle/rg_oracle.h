@@ -80,6 +80,10 @@ typedef struct {
   double rope_theta;
   int32_t eos_id; /* -1 = none */
   int32_t eot_id; /* -1 = none */
+  /* model variants (src/models/transformer/model.rs:160-175,253-282); zero = the plain Llama layer */
+  int32_t rope_dim; /* rotary lanes per head, even, <= head_dim; 0 = head_dim */
+  int32_t qk_norm;  /* 0 none, 1 per head (weights [head_dim]), 2 per projection (weights [width]) */
+  int32_t qkv_bias; /* 1: blk.N.attn_{q,k,v}.bias are bound */
 } rgo_config;
 
 typedef struct rgo_model rgo_model;

@@ -40,6 +40,13 @@ impl LlamaCudaModelPlan {
             rope_theta: c.rope_theta(),
             eos_id: c.token_ids().eos() as i32,
             eot_id: c.token_ids().eot().map_or(-1, |t| t as i32),
+            rope_dim: s.rope_dim() as i32,
+            qk_norm: match c.qk_norm() {
+                crate::models::transformer::LlamaQkNorm::None => 0,
+                crate::models::transformer::LlamaQkNorm::PerHead => 1,
+                crate::models::transformer::LlamaQkNorm::PerProjection => 2,
+            },
+            qkv_bias: c.qkv_bias() as i32,
         }
     }
 

@@ -1,9 +1,9 @@
 //! Raw bindings to `librg_b200.so`, the sm_100a implementation of rustgrad's GGUF-quantized Llama
 //! inference path, plus (in [`safe`]) the typed facade a rustgrad fork wires to its `SessionTarget`.
 //!
-//! Every item mirrors a declaration of `include/rg_b200.h`, `include/rg_b200_tokenizer.h` or
-//! `include/rg_b200_workflow.h`; the headers carry the documentation and, for each entry point, the
-//! rustgrad interface it stands in for.  All 78 exports are declared here.
+//! Every item mirrors a declaration of `include/rg_b200.h`, `include/rg_b200_tokenizer.h`,
+//! `include/rg_b200_workflow.h` or `include/rg_b200_serving.h`; the headers carry the documentation and, for each entry point, the
+//! rustgrad interface it stands in for.  All 92 exports are declared here.
 #![allow(non_camel_case_types)]
 
 use core::ffi::{c_char, c_void};
@@ -67,6 +67,12 @@ pub struct rg_llama_config {
     pub eos_id: i32,
     /// -1 = none
     pub eot_id: i32,
+    /// rotary lanes per head; 0 = head_dim
+    pub rope_dim: i32,
+    /// 0 none, 1 per head, 2 per projection
+    pub qk_norm: i32,
+    /// 1: q / k / v projection biases are bound
+    pub qkv_bias: i32,
 }
 
 #[repr(C)]
@@ -166,6 +172,111 @@ pub struct rg_prompt_output {
 /// `rg_text_callback`: one call per generated token (`token_id = -1` for the final flush).
 pub type rg_text_callback = unsafe extern "C" fn(user: *mut c_void, token_id: i32, text: *const c_char, text_len: usize);
 
+/// Opaque scheduler handle of `include/rg_b200_serving.h`.
+#[repr(C)]
+pub struct rg_scheduler {
+    _private: [u8; 0],
+}
+
+/// `rg_serving_status`: `LlamaServingError` by kind.
+pub mod serving_status {
+    pub const OK: i32 = 0;
+    pub const EMPTY_BATCH: i32 = 1;
+    pub const EMPTY_PROMPT: i32 = 2;
+    pub const CONTEXT_LENGTH: i32 = 3;
+    pub const TOKEN_OUT_OF_RANGE: i32 = 4;
+    pub const INVALID_TEMPERATURE: i32 = 5;
+    pub const UNIFORM_TAPE_LENGTH: i32 = 6;
+    pub const INVALID_UNIFORM: i32 = 7;
+    pub const UNKNOWN_REQUEST: i32 = 8;
+    pub const SESSION: i32 = 9;
+    pub const TOKENIZER: i32 = 10;
+    pub const INVALID_ARGUMENT: i32 = 11;
+    pub const NOT_COMPLETE: i32 = 12;
+}
+
+#[repr(C)]
+#[derive(Clone, Copy, Debug, Default, PartialEq, Eq)]
+pub struct rg_serving_error {
+    pub kind: i32,
+    pub value: i64,
+    pub value2: i64,
+}
+
+#[repr(C)]
+#[derive(Clone, Copy, Debug)]
+pub struct rg_serving_options {
+    pub batch_size: i32,
+    pub max_rows: i32,
+    pub prefix_max_entries: usize,
+    pub prefix_max_bytes: usize,
+    pub stop_ids: *const i32,
+    pub n_stop_ids: usize,
+    pub has_bos: i32,
+    pub bos_id: i32,
+}
+
+#[repr(C)]
+#[derive(Clone, Copy, Debug)]
+pub struct rg_serving_sampling {
+    pub greedy: i32,
+    pub temperature: f32,
+    pub uniforms: *const f32,
+    pub n_uniforms: usize,
+}
+
+#[repr(C)]
+#[derive(Clone, Copy, Debug, Default, PartialEq, Eq)]
+pub struct rg_token_event {
+    pub request_id: u64,
+    pub arrival_order: u64,
+    pub generation_step: i32,
+    pub token_id: i32,
+    pub stopped: i32,
+    pub complete: i32,
+}
+
+#[repr(C)]
+#[derive(Clone, Copy, Debug)]
+pub struct rg_serving_result {
+    pub request_id: u64,
+    pub prompt_ids: *const i32,
+    pub n_prompt_ids: usize,
+    pub generated_ids: *const i32,
+    pub n_generated_ids: usize,
+    pub decoded: *const c_char,
+    pub decoded_bytes: usize,
+    pub stopped: i32,
+}
+
+#[repr(C)]
+#[derive(Clone, Copy, Debug, Default, PartialEq, Eq)]
+pub struct rg_prefix_stats {
+    pub entries: u64,
+    pub bytes: u64,
+    pub hits: u64,
+    pub misses: u64,
+    pub stale_rejections: u64,
+    pub evictions: u64,
+    pub generation: u64,
+}
+
+/// `rg_serving_backend`: the session verbs a step is made of, as a table of C functions.
+#[repr(C)]
+#[derive(Clone, Copy)]
+pub struct rg_serving_backend {
+    pub ctx: *mut c_void,
+    pub vocab: i32,
+    pub max_context: i32,
+    pub reset_row: Option<unsafe extern "C" fn(ctx: *mut c_void, row: i32) -> i32>,
+    pub prefill_select: Option<unsafe extern "C" fn(ctx: *mut c_void, row: i32, ids: *const i32, n: usize, temperature: f32, uniforms: *const f32, last_logits: *mut f32, selected: *mut i32) -> i32>,
+    pub decode_rows: Option<unsafe extern "C" fn(ctx: *mut c_void, rows: *const i32, tokens: *const i32, n: i32, temperatures: *const f32, uniforms: *const f32, ids: *mut i32) -> i32>,
+    pub select: Option<unsafe extern "C" fn(ctx: *mut c_void, logits: *const f32, temperature: f32, uniforms: *const f32, id: *mut i32) -> i32>,
+    pub snapshot_create: Option<unsafe extern "C" fn(ctx: *mut c_void, row: i32, length: i32, snapshot: *mut *mut c_void, bytes: *mut usize) -> i32>,
+    pub snapshot_restore: Option<unsafe extern "C" fn(ctx: *mut c_void, snapshot: *const c_void, row: i32) -> i32>,
+    pub snapshot_free: Option<unsafe extern "C" fn(ctx: *mut c_void, snapshot: *mut c_void)>,
+}
+
 unsafe extern "C" {
     // ---- include/rg_b200.h
     pub fn rg_b200_version() -> *const c_char;
@@ -250,4 +361,20 @@ unsafe extern "C" {
     pub fn rg_b200_workflow_generated_ids(w: *const rg_workflow) -> *const i32;
     pub fn rg_b200_workflow_decoded(w: *const rg_workflow) -> *const c_char;
     pub fn rg_b200_workflow_rendered_prompt(w: *const rg_workflow) -> *const c_char;
+
+    // ---- include/rg_b200_serving.h
+    pub fn rg_b200_scheduler_new(session: *mut rg_session, tokenizer: *const rg_tokenizer, options: *const rg_serving_options, out: *mut *mut rg_scheduler, err: *mut rg_serving_error) -> i32;
+    pub fn rg_b200_scheduler_new_with_backend(backend: *const rg_serving_backend, tokenizer: *const rg_tokenizer, options: *const rg_serving_options, out: *mut *mut rg_scheduler, err: *mut rg_serving_error) -> i32;
+    pub fn rg_b200_scheduler_free(s: *mut rg_scheduler);
+    pub fn rg_b200_scheduler_submit_ids(s: *mut rg_scheduler, prompt: *const i32, n: usize, max_new_tokens: usize, sampling: *const rg_serving_sampling, request_id: *mut u64, err: *mut rg_serving_error) -> i32;
+    pub fn rg_b200_scheduler_submit_text(s: *mut rg_scheduler, prompt: *const c_char, prompt_len: usize, max_new_tokens: usize, sampling: *const rg_serving_sampling, request_id: *mut u64, err: *mut rg_serving_error) -> i32;
+    pub fn rg_b200_scheduler_submit_chat(s: *mut rg_scheduler, roles: *const i32, contents: *const *const c_char, content_len: *const usize, n_messages: usize, max_new_tokens: usize, sampling: *const rg_serving_sampling, request_id: *mut u64, err: *mut rg_serving_error) -> i32;
+    pub fn rg_b200_scheduler_status(s: *const rg_scheduler, request_id: u64, status: *mut i32) -> i32;
+    pub fn rg_b200_scheduler_result(s: *const rg_scheduler, request_id: u64, out: *mut rg_serving_result) -> i32;
+    pub fn rg_b200_scheduler_remove(s: *mut rg_scheduler, request_id: u64) -> i32;
+    pub fn rg_b200_scheduler_pending(s: *const rg_scheduler) -> usize;
+    pub fn rg_b200_scheduler_completed(s: *const rg_scheduler, ids: *mut u64, cap: usize) -> usize;
+    pub fn rg_b200_scheduler_prefix_stats(s: *const rg_scheduler, out: *mut rg_prefix_stats);
+    pub fn rg_b200_scheduler_invalidate_prefix_cache(s: *mut rg_scheduler);
+    pub fn rg_b200_scheduler_step(s: *mut rg_scheduler, events: *mut rg_token_event, cap: usize, n_events: *mut usize, err: *mut rg_serving_error) -> i32;
 }

@@ -19,6 +19,7 @@ class LlamaConfig(C.Structure):
         ("n_layers", C.c_int32), ("d_model", C.c_int32), ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32),
         ("head_dim", C.c_int32), ("ffn_dim", C.c_int32), ("vocab", C.c_int32), ("max_context", C.c_int32),
         ("norm_eps", C.c_float), ("rope_theta", C.c_double), ("eos_id", C.c_int32), ("eot_id", C.c_int32),
+        ("rope_dim", C.c_int32), ("qk_norm", C.c_int32), ("qkv_bias", C.c_int32),
     ]
 
 
@@ -60,6 +61,11 @@ EXPORTS = [
     "rg_b200_workflow_open", "rg_b200_workflow_close", "rg_b200_workflow_session", "rg_b200_workflow_tokenizer",
     "rg_b200_workflow_generate_text", "rg_b200_workflow_generate_chat", "rg_b200_workflow_prompt_ids",
     "rg_b200_workflow_generated_ids", "rg_b200_workflow_decoded", "rg_b200_workflow_rendered_prompt",
+    # include/rg_b200_serving.h (bound in serving.py)
+    "rg_b200_scheduler_new", "rg_b200_scheduler_new_with_backend", "rg_b200_scheduler_free", "rg_b200_scheduler_submit_ids",
+    "rg_b200_scheduler_submit_text", "rg_b200_scheduler_submit_chat", "rg_b200_scheduler_status", "rg_b200_scheduler_result",
+    "rg_b200_scheduler_remove", "rg_b200_scheduler_pending", "rg_b200_scheduler_completed", "rg_b200_scheduler_prefix_stats",
+    "rg_b200_scheduler_invalidate_prefix_cache", "rg_b200_scheduler_step",
 ]
 
 _lib = None

@@ -346,8 +346,8 @@ int32_t gguf_llama_config(const Gguf &g, rg_llama_config *out, std::string *err)
     *err = "invalid partial rotary dimensions";
     return RG_UNSUPPORTED_VARIANT;
   }
-  if (rope != hd) {
-    *err = "partial rotary dimensions are not supported by the CUDA session";
+  if (rope != hd && hd % 2) {
+    *err = "partial rotary dimensions with odd key head width";
     return RG_UNSUPPORTED_VARIANT;
   }
   for (auto &kvp : g.metadata)
@@ -367,12 +367,31 @@ int32_t gguf_llama_config(const Gguf &g, rg_llama_config *out, std::string *err)
     *err = "invalid configuration value";
     return RG_INVALID_ARGUMENT;
   }
-  for (const char *t : {"blk.0.attn_q_norm.weight", "blk.0.attn_k_norm.weight", "blk.0.attn_q.bias", "blk.0.attn_k.bias",
-                        "blk.0.attn_v.bias"})
-    if (g.by_name.count(t)) {
-      *err = std::string("q/k normalisation and projection biases are not supported by the CUDA session: ") + t;
+  // q/k normalisation and projection biases: complete families only, shapes decide the kind (model.rs:253-282)
+  auto tensor_dims = [&](const char *name) -> const std::vector<uint64_t> * {
+    auto it = g.by_name.find(name);
+    return it == g.by_name.end() ? nullptr : &g.tensors[it->second].shape;
+  };
+  const uint64_t qw = (uint64_t)heads * (uint64_t)hd, kw = (uint64_t)kv * (uint64_t)hd;
+  const std::vector<uint64_t> *qn = tensor_dims("blk.0.attn_q_norm.weight"), *kn = tensor_dims("blk.0.attn_k_norm.weight");
+  int32_t qk_norm = 0;
+  if (qn || kn) {
+    auto is1 = [](const std::vector<uint64_t> *v, uint64_t n) { return v && v->size() == 1 && (*v)[0] == n; };
+    if (is1(qn, (uint64_t)hd) && is1(kn, (uint64_t)hd)) qk_norm = 1;
+    else if (qw == kw && is1(qn, qw) && is1(kn, kw)) qk_norm = 2;
+    else {
+      *err = "partial or incompatible q/k normalization";
       return RG_UNSUPPORTED_VARIANT;
     }
+  }
+  const bool qb = tensor_dims("blk.0.attn_q.bias"), kb = tensor_dims("blk.0.attn_k.bias"), vb = tensor_dims("blk.0.attn_v.bias");
+  if (qb != kb || qb != vb) {
+    *err = "partial q/k/v projection bias family";
+    return RG_UNSUPPORTED_VARIANT;
+  }
+  out->rope_dim = rope == hd ? 0 : (int32_t)rope;
+  out->qk_norm = qk_norm;
+  out->qkv_bias = qb ? 1 : 0;
   out->n_layers = (int32_t)layers;
   out->d_model = (int32_t)d;
   out->n_heads = (int32_t)heads;

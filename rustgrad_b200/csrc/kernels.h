@@ -200,6 +200,14 @@ struct RopeArgs {
   float *q_out = nullptr;
   void *k_cache = nullptr, *v_cache = nullptr;
   bool kv_f32 = false;
+  // Model variants (layer.rs:274-346,481-571); the defaults are the plain layer.  rope_dim rotary
+  // lanes per head (tables [ctx, rope_dim / 2]); the query is de-interleaved over its last rope_dim
+  // lanes, the key over the whole head; biases are added after the permutation; qk_norm 1 is an RMS
+  // norm inside every head (weights [hd]), 2 over the whole projection (weights [width]).
+  int rope_dim = 0;  // 0 = hd
+  int qk_norm = 0;
+  float eps = 0.0f;
+  const float *q_norm = nullptr, *k_norm = nullptr, *q_bias = nullptr, *k_bias = nullptr, *v_bias = nullptr;
 };
 cudaError_t launch_rope_append(const RopeArgs &a, const LaunchCfg &cfg);
 

@@ -200,6 +200,99 @@ __global__ void rope_append_kernel(const float *qkv, int heads, int kv_heads, in
   }
 }
 
+// The same step for the model variants (layer.rs:274-346,481-571): one CTA per column keeps the
+// column's q, k and v in shared memory and applies, in the reference's order, the lane permutation
+// (query: its last rope_dim lanes; key: the whole head), the biases, the RMS norm of q and k over the
+// projection or inside every head, and the rotation of lanes [0, rope_dim).  Every step rounds to
+// f32 like the reference; only the order of the sums of squares differs.
+template <typename KV>
+__global__ void qkv_variant_kernel(const RopeArgs A, KV *k_cache, KV *v_cache) {
+  pdl_wait();
+  pdl_launch_dependents();
+  extern __shared__ float vs[];
+  __shared__ float red[33];
+  const int c = blockIdx.x, tid = threadIdx.x, hd = A.hd;
+  const int qw = A.heads * hd, kw = A.kv_heads * hd, rope = A.rope_dim ? A.rope_dim : hd, half = rope / 2;
+  const int pos = A.col_pos[c], seq = A.col_seq[c];
+  const float *row = A.qkv + (size_t)c * (qw + 2 * kw);
+  float *q = vs, *k = vs + qw;  // permuted (+ bias); v needs no staging
+  for (int i = tid; i < qw + kw; i += blockDim.x) {
+    const bool is_q = i < qw;
+    const int e = is_q ? i : i - qw, h = e / hd, j = e - h * hd;
+    const int permuted = is_q ? rope : hd, prefix = hd - permuted;
+    int src = j;
+    if (j >= prefix) {
+      const int r = j - prefix;
+      src = prefix + (r < permuted / 2 ? 2 * r : 2 * (r - permuted / 2) + 1);
+    }
+    float v = row[(is_q ? 0 : qw) + h * hd + src];
+    const float *bias = is_q ? A.q_bias : A.k_bias;
+    if (bias) v = __fadd_rn(v, bias[e]);
+    vs[i] = v;
+  }
+  __syncthreads();
+  // y = (x * (1 / sqrt(mean(x^2) + eps))) * w over `n` elements starting at `base`
+  auto block_sumsq = [&](const float *base, int n) {
+    float ss = 0.0f;
+    for (int i = tid; i < n; i += blockDim.x) ss = fmaf(base[i], base[i], ss);
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    if (tid == 0) {
+      float tot = 0.0f;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
+      red[32] = tot;
+    }
+    __syncthreads();
+    const float tot = red[32];
+    __syncthreads();
+    return tot;
+  };
+  auto inv_of = [&](float ss, int n) { return __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)n), A.eps))); };
+  if (A.qk_norm == 2) {
+    for (int which = 0; which < 2; ++which) {
+      float *base = which ? k : q;
+      const int n = which ? kw : qw;
+      const float *w = which ? A.k_norm : A.q_norm;
+      const float inv = inv_of(block_sumsq(base, n), n);
+      for (int i = tid; i < n; i += blockDim.x) base[i] = __fmul_rn(__fmul_rn(base[i], inv), w[i]);
+      __syncthreads();
+    }
+  } else if (A.qk_norm == 1) {
+    const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
+    for (int h = warp; h < A.heads + A.kv_heads; h += nwarps) {  // one warp per head
+      float *base = vs + (size_t)h * hd;  // q heads then k heads are contiguous
+      const float *w = h < A.heads ? A.q_norm : A.k_norm;
+      float ss = 0.0f;
+      for (int j = lane; j < hd; j += 32) ss = fmaf(base[j], base[j], ss);
+      const float inv = inv_of(warp_sum(ss), hd);
+      for (int j = lane; j < hd; j += 32) base[j] = __fmul_rn(__fmul_rn(base[j], inv), w[j]);
+    }
+    __syncthreads();
+  }
+  const float *ct = A.cos_t + (size_t)pos * half, *st = A.sin_t + (size_t)pos * half;
+  for (int it = tid; it < (A.heads + A.kv_heads) * hd; it += blockDim.x) {
+    const int h = it / hd, j = it - h * hd;
+    const float *base = vs + (size_t)h * hd;
+    float y = base[j];
+    if (j < rope) {  // lanes [0, half) and [half, rope) rotate as pairs (i, half + i)
+      const int i = j < half ? j : j - half;
+      const float x1 = base[i], x2 = base[half + i], cs = ct[i], sn = st[i];
+      y = j < half ? __fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn)) : __fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn));
+    }
+    if (h < A.heads)
+      A.q_out[((size_t)c * A.heads + h) * hd + j] = y;
+    else
+      k_cache[(((size_t)seq * A.kv_heads + (h - A.heads)) * A.ctx + pos) * hd + j] = to_kv<KV>(y);
+  }
+  for (int it = tid; it < kw; it += blockDim.x) {
+    const int h = it / hd, j = it - h * hd;
+    float v = row[qw + kw + it];
+    if (A.v_bias) v = __fadd_rn(v, A.v_bias[it]);
+    v_cache[(((size_t)seq * A.kv_heads + h) * A.ctx + pos) * hd + j] = to_kv<KV>(v);
+  }
+}
+
 // ------------------------------------------------------------------------------ attention
 // Split-context decode attention.  One CTA per (context span, kv head, column) handles the G query
 // heads that share the kv head.  Scratch per (column, head, split): [m, l, out[hd]].
@@ -826,6 +919,27 @@ cudaError_t launch_rmsnorm_pack(const float *x, int ldx, const float *w, int d, 
                 y, ldy);
 }
 cudaError_t launch_rope_append(const RopeArgs &a, const LaunchCfg &cfg) {
+  const int rope = a.rope_dim ? a.rope_dim : a.hd;
+  if (rope != a.hd || a.qk_norm || a.q_bias || a.k_bias || a.v_bias) {
+    if (rope < 2 || rope > a.hd || (rope & 1) || (a.qk_norm && (!a.q_norm || !a.k_norm)) || a.qk_norm > 2) return cudaErrorInvalidValue;
+    const size_t smem = (size_t)(a.heads + a.kv_heads) * a.hd * sizeof(float);
+    auto set = [&](auto kernel) {
+      static DeviceOnce once;
+      bool *flag = once.slot();
+      if (flag && *flag) return cudaSuccess;
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      if (e == cudaSuccess && flag) *flag = true;
+      return e;
+    };
+    if (smem > 160 * 1024) return cudaErrorInvalidValue;
+    cudaError_t e = a.kv_f32 ? set(qkv_variant_kernel<float>) : set(qkv_variant_kernel<__half>);
+    if (e != cudaSuccess) return e;
+    if (a.kv_f32)
+      return launch(qkv_variant_kernel<float>, dim3(a.cols), dim3(256), smem, cfg, a, static_cast<float *>(a.k_cache),
+                    static_cast<float *>(a.v_cache));
+    return launch(qkv_variant_kernel<__half>, dim3(a.cols), dim3(256), smem, cfg, a, static_cast<__half *>(a.k_cache),
+                  static_cast<__half *>(a.v_cache));
+  }
   if (a.kv_f32)
     return launch(rope_append_kernel<float>, dim3(a.cols), dim3(256), 0, cfg, a.qkv, a.heads, a.kv_heads, a.hd, a.ctx, a.col_seq,
                   a.col_pos, a.cos_t, a.sin_t, a.q_out, static_cast<float *>(a.k_cache), static_cast<float *>(a.v_cache));
@@ -900,6 +1014,11 @@ cudaError_t launch_dense_gemv(const DenseGemvArgs &a, const LaunchCfg &cfg) {
   if (a.type == RG_TYPE_F16)
     return launch(dense_gemv_kernel<__half>, grid, block, 0, cfg, reinterpret_cast<const __half *>(a.w), a.rows, a.k, a.x, a.ldx,
                   a.batch, a.epi, a.y, a.ldy);
+  if (a.type == RG_TYPE_Q4_0 || a.type == RG_TYPE_Q8_0) {  // rows whose K is not a multiple of 256
+    if (a.k % 32) return cudaErrorInvalidValue;
+    count_launch(LC_DENSE_GEMV);
+    return launch(block_gemv_kernel, grid, block, 0, cfg, a.type, a.w, a.rows, a.k, a.x, a.ldx, a.batch, a.epi, a.y, a.ldy);
+  }
   if (a.type == RG_TYPE_Q4_K || a.type == RG_TYPE_Q6_K) {
     count_launch(LC_KQUANT_GEMV);
     const bool aligned = (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (a.ldx & 3) == 0 && (a.k & 255) == 0 &&

@@ -93,11 +93,15 @@ struct DevTensor {
   uint64_t rows = 0, cols = 0;  // rank-local shape
   uint8_t *d = nullptr;
   size_t nbytes = 0;
-  bool packed() const { return type == RG_TYPE_Q4_0 || type == RG_TYPE_Q8_0; }
+  // served by the tensor-core GEMV / GEMM kernels: Q4_0 / Q8_0 rows of whole 256-element groups.  Block
+  // tensors with any other K (a multiple of 32, as the reference requires) take the generic
+  // decode-and-multiply GEMV like the dense ones
+  bool packed() const { return (type == RG_TYPE_Q4_0 || type == RG_TYPE_Q8_0) && cols % 256 == 0; }
 };
 
 struct LayerW {
   DevTensor attn_norm, q, k, v, o, ffn_norm, gate, up, down;
+  DevTensor q_norm, k_norm, q_bias, k_bias, v_bias;  // model variants only (f32 vectors)
 };
 
 enum Split { SPLIT_NONE, SPLIT_ROWS, SPLIT_COLS };
@@ -137,7 +141,9 @@ struct rg_plan {
       drop(output_norm);
       drop(output);
       for (auto &l : layers)
-        for (DevTensor *t : {&l.attn_norm, &l.q, &l.k, &l.v, &l.o, &l.ffn_norm, &l.gate, &l.up, &l.down}) drop(*t);
+        for (DevTensor *t : {&l.attn_norm, &l.q, &l.k, &l.v, &l.o, &l.ffn_norm, &l.gate, &l.up, &l.down, &l.q_norm, &l.k_norm, &l.q_bias,
+                             &l.k_bias, &l.v_bias})
+          drop(*t);
     }
     if (d_status) cudaFree(d_status);
     if (stream) cudaStreamDestroy(stream);
@@ -162,7 +168,7 @@ static bool find_slot(rg_plan *p, const std::string &name, Slot *s) {
   if (name == "output_norm.weight") return set(&p->output_norm, 1, d, true, SPLIT_NONE);
   if (name == "rope_freqs.weight") {
     s->ignored = true;
-    return set(nullptr, 1, (uint64_t)c.head_dim / 2, true, SPLIT_NONE);
+    return set(nullptr, 1, (uint64_t)(c.rope_dim ? c.rope_dim : c.head_dim) / 2, true, SPLIT_NONE);
   }
   int layer = -1, used = 0;
   if (sscanf(name.c_str(), "blk.%d.%n", &layer, &used) != 1 || layer < 0 || layer >= c.n_layers) return false;
@@ -177,6 +183,13 @@ static bool find_slot(rg_plan *p, const std::string &name, Slot *s) {
   if (suffix == "ffn_gate.weight") return set(&L.gate, f, d, false, SPLIT_ROWS);
   if (suffix == "ffn_up.weight") return set(&L.up, f, d, false, SPLIT_ROWS);
   if (suffix == "ffn_down.weight") return set(&L.down, d, f, false, SPLIT_COLS);
+  // present only in the variant the configuration names (model.rs:427-449)
+  const uint64_t hd = (uint64_t)c.head_dim;
+  if (c.qk_norm && suffix == "attn_q_norm.weight") return set(&L.q_norm, 1, c.qk_norm == 1 ? hd : qw, true, SPLIT_NONE);
+  if (c.qk_norm && suffix == "attn_k_norm.weight") return set(&L.k_norm, 1, c.qk_norm == 1 ? hd : kw, true, SPLIT_NONE);
+  if (c.qkv_bias && suffix == "attn_q.bias") return set(&L.q_bias, 1, qw, true, SPLIT_NONE);
+  if (c.qkv_bias && suffix == "attn_k.bias") return set(&L.k_bias, 1, kw, true, SPLIT_NONE);
+  if (c.qkv_bias && suffix == "attn_v.bias") return set(&L.v_bias, 1, kw, true, SPLIT_NONE);
   return false;
 }
 
@@ -205,11 +218,6 @@ static int32_t check_tensor(rg_plan *p, const std::string &name, int32_t type, u
     *lc = cols / W;
     *c0 = R * *lc;
   }
-  const bool is_packed = (type == RG_TYPE_Q4_0 || type == RG_TYPE_Q8_0);
-  if (is_packed && !slot->norm && name != "token_embd.weight" && (*lc % 256))
-    return fail(RG_UNSUPPORTED_GEOMETRY, name + ": packed projections need a (rank-local) K that is a multiple of 256");
-  if (is_packed && name == "token_embd.weight" && p->output.type < 0 && (*lc % 256))
-    ;  // a tied head over such an embedding is rejected at prepare
   return RG_OK;
 }
 
@@ -266,6 +274,10 @@ struct rg_session {
   const float *sample_temps = nullptr;  // per-column temperatures of a mixed step (device), else null
   float *d_temps = nullptr;             // [BMAX]
   bool chunk_is_prompt = false;  // the columns of the current step are consecutive positions of one sequence
+  // partial rotary lanes, q / k RMS norms or projection biases: such models take the general
+  // q/k/v post-processing kernel and the three-launch attention on every path
+  bool variant = false;
+  int rope_dim = 0;  // rotary lanes per head (head_dim for the plain layer)
   float *split_scratch = nullptr;  // K-split partial tiles of the tensor-core GEMM at small token counts
   void *xb = nullptr;  // 16-bit operand planes (hi, lo) of the tensor-core path: [2][WMAX][max(d, qw, ffn_l)]
   int gemm_mode = QGEMM_F16X3;
@@ -460,9 +472,21 @@ static int32_t tp_reduce_add(rg_session *s, int ncols, int which) {
   return RG_OK;
 }
 
+// Variant fields of the q/k/v post-processing launch (no-ops for the plain layer).
+static void rope_variant(const rg_session *s, const LayerW &W, RopeArgs *ra) {
+  ra->rope_dim = s->rope_dim;
+  ra->qk_norm = s->cfg.qk_norm;
+  ra->eps = s->cfg.norm_eps;
+  ra->q_norm = reinterpret_cast<const float *>(W.q_norm.d);
+  ra->k_norm = reinterpret_cast<const float *>(W.k_norm.d);
+  ra->q_bias = reinterpret_cast<const float *>(W.q_bias.d);
+  ra->k_bias = reinterpret_cast<const float *>(W.k_bias.d);
+  ra->v_bias = reinterpret_cast<const float *>(W.v_bias.d);
+}
+
 // True when every projection of the model can run the integer tensor-core GEMV at this width.
 static bool small_batch_path(const rg_session *s, int ncols) {
-  if (ncols > 2 || s->opt.general_path_only) return false;
+  if (ncols > 2 || s->opt.general_path_only || s->variant) return false;
   const int d = s->cfg.d_model, qw = s->heads_l * s->cfg.head_dim;
   if (!qgemv_i8_supported(d, ncols) || !qgemv_i8_supported(qw, ncols) || !qgemv_i8_supported(s->ffn_l, ncols)) return false;
   for (const LayerW &W : s->layers) {
@@ -606,7 +630,8 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
       ra.k_cache = s->k_cache[(size_t)l];
       ra.v_cache = s->v_cache[(size_t)l];
       ra.kv_f32 = s->kv_f32;
-      RG_LAUNCH(s, launch_rope_append(ra, L));
+      rope_variant(s, W, &ra);
+    RG_LAUNCH(s, launch_rope_append(ra, L));
       AttnArgs aa;
       aa.q = s->q_rot;
       aa.k_cache = ra.k_cache;
@@ -787,7 +812,7 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
     if ((rc = gemm_tc(s, W.k, ncols, s->qkv + qw, qkv_w, L))) return rc;
     if ((rc = gemm_tc(s, W.v, ncols, s->qkv + qw + kw, qkv_w, L))) return rc;
     prof_mark(s, PROF_ATTN);
-    if (!s->chunk_is_prompt && ncols <= BMAX && s->attn_counters) {
+    if (!s->chunk_is_prompt && ncols <= BMAX && s->attn_counters && !s->variant) {
       // a decode batch: RoPE, cache append, split attention and the combine in one launch
       FusedAttnArgs fa;
       fa.qkv = s->qkv;
@@ -824,8 +849,9 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
     ra.k_cache = s->k_cache[(size_t)l];
     ra.v_cache = s->v_cache[(size_t)l];
     ra.kv_f32 = s->kv_f32;
+    rope_variant(s, W, &ra);
     RG_LAUNCH(s, launch_rope_append(ra, L));
-    if (s->chunk_is_prompt && prefill_attention_supported(s->heads_l, s->kv_l, hd)) {
+    if (s->chunk_is_prompt && prefill_attention_supported(s->heads_l, s->kv_l, hd)) {  // q and the caches are post-processed already
       // consecutive positions of one sequence: the tiled causal kernel reads each K / V row once per CTA
       PrefillAttnArgs pa;
       pa.q = s->q_rot;
@@ -1028,7 +1054,7 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
     int32_t rc = linear(s, qkvw, 3, s->xn_pack, s->xn_f32, d, ncols, EPI_STORE, s->qkv, qkv_w);
     if (rc) return rc;
     prof_mark(s, PROF_ATTN);
-    if (gemv16 && s->attn_counters) {
+    if (gemv16 && s->attn_counters && !s->variant) {
       // rows of distinct sequences: RoPE, cache append, split attention and the combine in one launch
       FusedAttnArgs fa;
       fa.qkv = s->qkv;
@@ -1067,6 +1093,7 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
     ra.k_cache = s->k_cache[(size_t)l];
     ra.v_cache = s->v_cache[(size_t)l];
     ra.kv_f32 = s->kv_f32;
+    rope_variant(s, W, &ra);
     RG_LAUNCH(s, launch_rope_append(ra, L));
     AttnArgs aa;
     aa.q = s->q_rot;
@@ -1367,6 +1394,9 @@ int32_t rg_b200_plan_create(const rg_llama_config *c, const rg_options *o, rg_pl
   if (c->n_layers <= 0 || c->d_model <= 0 || c->n_heads <= 0 || c->n_kv_heads <= 0 || c->head_dim <= 0 || c->ffn_dim <= 0 ||
       c->vocab <= 0 || c->max_context <= 0 || c->n_heads % c->n_kv_heads || !(c->norm_eps >= 0.0f) || !(c->rope_theta > 0.0))
     return fail(RG_INVALID_ARGUMENT, "invalid model configuration");
+  if (c->rope_dim < 0 || c->rope_dim > c->head_dim || (c->rope_dim & 1) || c->qk_norm < 0 || c->qk_norm > 2 ||
+      (c->qk_norm == 2 && c->n_heads != c->n_kv_heads))
+    return fail(RG_INVALID_ARGUMENT, "invalid rotary width or q/k normalisation kind");
   if (!attention_supported(c->n_heads, c->n_kv_heads, c->head_dim))
     return fail(RG_UNSUPPORTED_GEOMETRY, "head_dim must be 64 or 128 and query heads per kv head 1, 2, 4 or 8");
   auto p = std::make_unique<rg_plan>();
@@ -1378,6 +1408,8 @@ int32_t rg_b200_plan_create(const rg_llama_config *c, const rg_options *o, rg_pl
   if (p->tp_world > 1 && (c->n_heads % p->tp_world || c->n_kv_heads % p->tp_world || c->ffn_dim % p->tp_world))
     return fail(RG_UNSUPPORTED_GEOMETRY, "heads, kv heads and ffn width must divide by the tensor-parallel world size");
   if (p->opt.max_batch > BMAX) return fail(RG_UNSUPPORTED_GEOMETRY, "max_batch above 32 is not supported");
+  if (p->tp_world > 1 && ((c->rope_dim && c->rope_dim != c->head_dim) || c->qk_norm || c->qkv_bias))
+    return fail(RG_UNSUPPORTED_GEOMETRY, "partial rotary, q/k normalisation and projection biases run on one GPU only");
   RG_CUDA(cudaSetDevice(p->opt.device));
   int sms = 0;
   RG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->opt.device));
@@ -1564,9 +1596,16 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
     for (int i = 0; i < 9; ++i)
       if (ts[i]->type < 0) return fail(RG_MISSING_TENSOR, "blk." + std::to_string(l) + "." + names[i] + ".weight");
   }
+  for (int l = 0; l < c.n_layers; ++l) {
+    LayerW &L = p->layers[(size_t)l];
+    const std::string pre = "blk." + std::to_string(l) + ".";
+    if (c.qk_norm && L.q_norm.type < 0) return fail(RG_MISSING_TENSOR, pre + "attn_q_norm.weight");
+    if (c.qk_norm && L.k_norm.type < 0) return fail(RG_MISSING_TENSOR, pre + "attn_k_norm.weight");
+    if (c.qkv_bias && L.q_bias.type < 0) return fail(RG_MISSING_TENSOR, pre + "attn_q.bias");
+    if (c.qkv_bias && L.k_bias.type < 0) return fail(RG_MISSING_TENSOR, pre + "attn_k.bias");
+    if (c.qkv_bias && L.v_bias.type < 0) return fail(RG_MISSING_TENSOR, pre + "attn_v.bias");
+  }
   const bool tied = p->output.type < 0;
-  if (tied && p->token_embd.packed() && (c.d_model % 256))
-    return fail(RG_UNSUPPORTED_GEOMETRY, "a packed tied head needs d_model to be a multiple of 256");
   RG_CUDA(cudaSetDevice(p->opt.device));
   auto s = std::make_unique<rg_session>();
   s->cfg = c;
@@ -1581,6 +1620,8 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   s->ctx = p->opt.max_context > 0 ? p->opt.max_context : c.max_context;
   if (s->ctx > c.max_context) return fail(RG_INVALID_ARGUMENT, "max_context above the model's context length");
   s->kv_f32 = p->opt.kv_f32 != 0;
+  s->rope_dim = c.rope_dim ? c.rope_dim : c.head_dim;
+  s->variant = s->rope_dim != c.head_dim || c.qk_norm || c.qkv_bias;
   s->use_graph = !p->opt.disable_graph && !env_flag("RG_B200_DISABLE_GRAPH");
   s->use_pdl = !p->opt.disable_pdl && !env_flag("RG_B200_DISABLE_PDL");
   s->sm_count = p->sm_count;
@@ -1661,10 +1702,10 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   if (s->tp_world > 1 && !p->opt.disable_fused_allreduce && !env_flag("RG_B200_DISABLE_FUSED_ALLREDUCE")) RG_TRY(tp_fused_setup(s.get()));
   // RoPE tables in f64 on the host, cast to f32 (src/models/transformer/layer.rs:541-556)
   {
-    const int half = hd / 2;
+    const int half = s->rope_dim / 2;  // angle(p, i) = p / theta^(2i / rope_dim)
     std::vector<float> cs((size_t)s->ctx * half), sn((size_t)s->ctx * half);
     for (int i = 0; i < half; ++i) {
-      const double freq = 1.0 / pow(c.rope_theta, (double)(2 * i) / (double)hd);
+      const double freq = 1.0 / pow(c.rope_theta, (double)(2 * i) / (double)s->rope_dim);
       for (int pos = 0; pos < s->ctx; ++pos) {
         const double ang = (double)pos * freq;
         cs[(size_t)pos * half + i] = (float)cos(ang);
@@ -1711,7 +1752,9 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   own(s->output_norm);
   own(s->output);
   for (auto &L : s->layers)
-    for (DevTensor *t : {&L.attn_norm, &L.q, &L.k, &L.v, &L.o, &L.ffn_norm, &L.gate, &L.up, &L.down}) own(*t);
+    for (DevTensor *t : {&L.attn_norm, &L.q, &L.k, &L.v, &L.o, &L.ffn_norm, &L.gate, &L.up, &L.down, &L.q_norm, &L.k_norm, &L.q_bias,
+                         &L.k_bias, &L.v_bias})
+      own(*t);
   p->consumed = true;
   s->position.assign((size_t)s->max_batch, 0);
   s->report.weight_bytes = s->weight_bytes;

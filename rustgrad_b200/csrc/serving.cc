@@ -1,0 +1,490 @@
+// Continuous-batching scheduler behind include/rg_b200_serving.h: admission, arrival-order
+// selection, cache-row bookkeeping and the prefix cache of rustgrad's LlamaServingScheduler
+// (src/models/transformer/serving/mod.rs:192-352 PrefixCache, :371-690 scheduler, :726-790
+// validate_request).  Host policy only: a step is composed from the session verbs in the
+// rg_serving_backend table (prefill_select, decode_rows, select, kv snapshots).
+#include <math.h>
+#include <string.h>
+
+#include <algorithm>
+#include <map>
+#include <memory>
+#include <set>
+#include <string>
+#include <vector>
+
+#include "../../include/rg_b200_serving.h"
+
+namespace {
+
+int32_t fail(rg_serving_error *err, int32_t kind, int64_t value = 0, int64_t value2 = 0) {
+  if (err) *err = rg_serving_error{kind, value, value2};
+  return kind;
+}
+
+// A device K/V copy shared by the cache and by the requests that lean on it.
+struct Snapshot {
+  const rg_serving_backend *be;
+  void *handle;
+  int32_t length;
+  size_t bytes;
+  Snapshot(const rg_serving_backend *b, void *h, int32_t n, size_t sz) : be(b), handle(h), length(n), bytes(sz) {}
+  Snapshot(const Snapshot &) = delete;
+  Snapshot &operator=(const Snapshot &) = delete;
+  ~Snapshot() {
+    if (handle) be->snapshot_free(be->ctx, handle);
+  }
+};
+using SnapshotRef = std::shared_ptr<Snapshot>;
+using Key = std::vector<int32_t>;
+
+struct Entry {
+  uint64_t generation;
+  SnapshotRef snapshot;
+  std::vector<float> logits;
+  size_t bytes;
+  uint64_t last_used;
+  uint64_t references = 0;
+};
+
+// PrefixCache (serving/mod.rs:192-352): longest-prefix lookup, least-recently-used eviction of
+// unreferenced entries under an entry and a byte budget, generation counter for invalidation.
+struct PrefixCache {
+  size_t max_entries = 0, max_bytes = 0;
+  uint64_t generation = 0, clock = 0, bytes = 0, hits = 0, misses = 0, stale_rejections = 0, evictions = 0;
+  std::map<Key, Entry> entries;
+
+  void invalidate() {
+    ++generation;
+    bytes = 0;
+    entries.clear();
+  }
+  void release(const Key &key) {
+    auto it = entries.find(key);
+    if (it != entries.end() && it->second.references) --it->second.references;
+  }
+  // The longest entry that is a prefix of `tokens`; the caller holds a reference until release().
+  const Key *longest(const Key &tokens, Entry **found) {
+    for (auto it = entries.begin(); it != entries.end();) {
+      if (it->second.generation != generation) {
+        bytes -= it->second.bytes;
+        ++stale_rejections;
+        it = entries.erase(it);
+      } else {
+        ++it;
+      }
+    }
+    const Key *best = nullptr;
+    Entry *best_entry = nullptr;
+    for (auto &kv : entries) {
+      const Key &k = kv.first;
+      if (k.size() <= tokens.size() && std::equal(k.begin(), k.end(), tokens.begin()) && (!best || k.size() > best->size())) {
+        best = &k;
+        best_entry = &kv.second;
+      }
+    }
+    if (!best) {
+      ++misses;
+      return nullptr;
+    }
+    best_entry->last_used = ++clock;
+    ++best_entry->references;
+    ++hits;
+    *found = best_entry;
+    return best;
+  }
+  bool insert(const Key &tokens, SnapshotRef snapshot, const float *logits, size_t n_logits) {
+    if (max_entries == 0 || max_bytes == 0) return false;
+    const size_t size = snapshot->bytes + n_logits * 4 + tokens.size() * 4;
+    if (size > max_bytes) return false;
+    auto old = entries.find(tokens);
+    if (old != entries.end()) {
+      bytes -= old->second.bytes;
+      entries.erase(old);
+    }
+    while (entries.size() >= max_entries || bytes + size > max_bytes) {
+      auto victim = entries.end();
+      for (auto it = entries.begin(); it != entries.end(); ++it)
+        if (it->second.references == 0 && (victim == entries.end() || it->second.last_used < victim->second.last_used)) victim = it;
+      if (victim == entries.end()) return false;
+      bytes -= victim->second.bytes;
+      entries.erase(victim);
+      ++evictions;
+    }
+    Entry e;
+    e.generation = generation;
+    e.snapshot = std::move(snapshot);
+    e.logits.assign(logits, logits + n_logits);
+    e.bytes = size;
+    e.last_used = ++clock;
+    bytes += size;
+    entries.emplace(tokens, std::move(e));
+    return true;
+  }
+};
+
+struct Request {
+  uint64_t id = 0, arrival = 0;
+  Key prompt;
+  size_t max_new = 0;
+  bool greedy = true;
+  float temperature = 0.f;
+  std::vector<float> uniforms;  // [max_new, vocab]
+  int32_t status = RG_REQUEST_QUEUED;
+  std::vector<int32_t> generated;
+  bool stopped = false;
+  int32_t row = -1;
+  bool has_pending = false;
+  int32_t pending_token = 0;
+  bool has_result = false;
+  std::string decoded;
+};
+
+}  // namespace
+
+struct rg_scheduler {
+  rg_serving_backend be{};
+  const rg_tokenizer *tokenizer = nullptr;
+  int32_t batch_size = 0;
+  std::set<int32_t> stop_ids;
+  bool has_bos = false;
+  int32_t bos_id = 0;
+  std::set<int32_t> free_rows;
+  uint64_t next_id = 0, next_arrival = 0;
+  std::vector<uint64_t> order;
+  std::map<uint64_t, Request> requests;
+  PrefixCache prefixes;
+
+  const float *tape_row(const Request &r) const {
+    return r.greedy ? nullptr : r.uniforms.data() + r.generated.size() * (size_t)be.vocab;
+  }
+  int32_t release_row(Request &r) {
+    if (r.row < 0) return RG_OK;
+    const int32_t rc = be.reset_row(be.ctx, r.row);
+    free_rows.insert(r.row);
+    r.row = -1;
+    return rc;
+  }
+};
+
+namespace {
+
+// The table over one rg_session.
+int32_t be_reset_row(void *c, int32_t row) { return rg_b200_reset_row((rg_session *)c, row); }
+int32_t be_prefill_select(void *c, int32_t row, const int32_t *ids, size_t n, float t, const float *u, float *last, int32_t *sel) {
+  return rg_b200_prefill_select((rg_session *)c, row, ids, n, t, u, last, sel);
+}
+int32_t be_decode_rows(void *c, const int32_t *rows, const int32_t *toks, int32_t n, const float *t, const float *u, int32_t *ids) {
+  return rg_b200_decode_rows((rg_session *)c, rows, toks, n, t, u, nullptr, ids);
+}
+int32_t be_select(void *c, const float *logits, float t, const float *u, int32_t *id) {
+  return rg_b200_select((rg_session *)c, logits, 1, &t, u, id);
+}
+int32_t be_snapshot_create(void *c, int32_t row, int32_t length, void **snap, size_t *bytes) {
+  rg_kv_snapshot *k = nullptr;
+  const int32_t rc = rg_b200_kv_snapshot_create((rg_session *)c, row, length, &k);
+  if (rc) return rc;
+  *snap = k;
+  *bytes = rg_b200_kv_snapshot_bytes(k);
+  return RG_OK;
+}
+int32_t be_snapshot_restore(void *c, const void *snap, int32_t row) {
+  return rg_b200_kv_snapshot_restore((rg_session *)c, (const rg_kv_snapshot *)snap, row);
+}
+void be_snapshot_free(void *, void *snap) { rg_b200_kv_snapshot_free((rg_kv_snapshot *)snap); }
+
+int32_t encode_text(const rg_tokenizer *tok, const char *text, size_t len, Key *out, rg_serving_error *err) {
+  rg_tok_error terr{};
+  size_t n = 0;
+  int32_t trc = rg_b200_tokenizer_encode(tok, text, len, nullptr, 0, &n, &terr);
+  if (trc != RG_TOK_OK && !(trc == RG_TOK_INVALID_ARGUMENT && n > 0)) return fail(err, RG_SERVING_TOKENIZER, trc);
+  std::vector<uint32_t> ids(n ? n : 1);
+  if (n && (trc = rg_b200_tokenizer_encode(tok, text, len, ids.data(), ids.size(), &n, &terr)) != RG_TOK_OK)
+    return fail(err, RG_SERVING_TOKENIZER, trc);
+  for (size_t i = 0; i < n; ++i) out->push_back((int32_t)ids[i]);
+  return RG_SERVING_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t rg_b200_scheduler_new_with_backend(const rg_serving_backend *backend, const rg_tokenizer *tokenizer,
+                                           const rg_serving_options *o, rg_scheduler **out, rg_serving_error *err) {
+  if (!backend || !o || !out) return fail(err, RG_SERVING_INVALID_ARGUMENT);
+  if (o->batch_size <= 0) return fail(err, RG_SERVING_EMPTY_BATCH, o->batch_size);
+  const int32_t rows = o->max_rows > 0 ? o->max_rows : o->batch_size;
+  if (rows < o->batch_size) return fail(err, RG_SERVING_EMPTY_BATCH, rows, o->batch_size);
+  if (o->n_stop_ids && !o->stop_ids) return fail(err, RG_SERVING_INVALID_ARGUMENT);
+  auto s = new rg_scheduler();
+  s->be = *backend;
+  s->tokenizer = tokenizer;
+  s->batch_size = o->batch_size;
+  s->stop_ids.insert(o->stop_ids, o->stop_ids + o->n_stop_ids);
+  s->has_bos = o->has_bos != 0;
+  s->bos_id = o->bos_id;
+  for (int32_t r = 0; r < rows; ++r) s->free_rows.insert(r);
+  s->prefixes.max_entries = o->prefix_max_entries;
+  s->prefixes.max_bytes = o->prefix_max_bytes;
+  *out = s;
+  return RG_SERVING_OK;
+}
+
+int32_t rg_b200_scheduler_new(rg_session *session, const rg_tokenizer *tokenizer, const rg_serving_options *options,
+                              rg_scheduler **out, rg_serving_error *err) {
+  if (!session) return fail(err, RG_SERVING_INVALID_ARGUMENT);
+  rg_serving_backend be{};
+  be.ctx = session;
+  be.vocab = rg_b200_vocab_size(session);
+  be.max_context = rg_b200_max_context(session);
+  be.reset_row = be_reset_row;
+  be.prefill_select = be_prefill_select;
+  be.decode_rows = be_decode_rows;
+  be.select = be_select;
+  be.snapshot_create = be_snapshot_create;
+  be.snapshot_restore = be_snapshot_restore;
+  be.snapshot_free = be_snapshot_free;
+  return rg_b200_scheduler_new_with_backend(&be, tokenizer, options, out, err);
+}
+
+void rg_b200_scheduler_free(rg_scheduler *s) {
+  if (!s) return;
+  for (auto &kv : s->requests) s->release_row(kv.second);
+  delete s;  // the prefix entries free their snapshots
+}
+
+int32_t rg_b200_scheduler_submit_ids(rg_scheduler *s, const int32_t *prompt, size_t n, size_t max_new,
+                                     const rg_serving_sampling *sampling, uint64_t *request_id, rg_serving_error *err) {
+  if (!s || (n && !prompt)) return fail(err, RG_SERVING_INVALID_ARGUMENT);
+  const int64_t vocab = s->be.vocab, ctx = s->be.max_context;
+  if (n == 0) return fail(err, RG_SERVING_EMPTY_PROMPT);
+  if (n + max_new > (size_t)ctx) return fail(err, RG_SERVING_CONTEXT_LENGTH, (int64_t)(n + max_new), ctx);
+  for (size_t i = 0; i < n; ++i)
+    if (prompt[i] < 0 || prompt[i] >= vocab) return fail(err, RG_SERVING_TOKEN_OUT_OF_RANGE, prompt[i], vocab);
+  Request r;
+  r.greedy = !sampling || sampling->greedy;
+  if (!r.greedy) {
+    if (!isfinite(sampling->temperature) || sampling->temperature <= 0.0f) return fail(err, RG_SERVING_INVALID_TEMPERATURE);
+    const size_t required = max_new * (size_t)vocab;
+    const size_t actual = sampling->uniforms ? sampling->n_uniforms : 0;
+    if (actual < required) return fail(err, RG_SERVING_UNIFORM_TAPE_LENGTH, (int64_t)required, (int64_t)actual);
+    for (size_t i = 0; i < required; ++i) {
+      const float u = sampling->uniforms[i];
+      if (!isfinite(u) || u < 0.0f || u >= 1.0f) return fail(err, RG_SERVING_INVALID_UNIFORM, (int64_t)i);
+    }
+    r.temperature = sampling->temperature;
+    r.uniforms.assign(sampling->uniforms, sampling->uniforms + required);
+  }
+  r.id = s->next_id++;
+  r.arrival = s->next_arrival++;
+  r.prompt.assign(prompt, prompt + n);
+  r.max_new = max_new;
+  if (max_new == 0) {
+    r.status = RG_REQUEST_COMPLETE;
+    r.has_result = true;
+  }
+  if (request_id) *request_id = r.id;
+  s->order.push_back(r.id);
+  s->requests.emplace(r.id, std::move(r));
+  return RG_SERVING_OK;
+}
+
+int32_t rg_b200_scheduler_submit_text(rg_scheduler *s, const char *prompt, size_t prompt_len, size_t max_new,
+                                      const rg_serving_sampling *sampling, uint64_t *request_id, rg_serving_error *err) {
+  if (!s || !s->tokenizer || (prompt_len && !prompt)) return fail(err, RG_SERVING_INVALID_ARGUMENT);
+  Key ids;
+  if (s->has_bos) ids.push_back(s->bos_id);
+  if (int32_t rc = encode_text(s->tokenizer, prompt ? prompt : "", prompt_len, &ids, err)) return rc;
+  return rg_b200_scheduler_submit_ids(s, ids.data(), ids.size(), max_new, sampling, request_id, err);
+}
+
+int32_t rg_b200_scheduler_submit_chat(rg_scheduler *s, const int32_t *roles, const char *const *contents,
+                                      const size_t *content_len, size_t n_messages, size_t max_new,
+                                      const rg_serving_sampling *sampling, uint64_t *request_id, rg_serving_error *err) {
+  if (!s || !s->tokenizer || (n_messages && (!roles || !contents || !content_len))) return fail(err, RG_SERVING_INVALID_ARGUMENT);
+  rg_tok_error terr{};
+  size_t bytes = 0;
+  int32_t trc = rg_b200_chat_render(s->tokenizer, roles, contents, content_len, n_messages, 1, nullptr, 0, &bytes, &terr);
+  if (trc != RG_TOK_OK && !(trc == RG_TOK_INVALID_ARGUMENT && bytes > 0)) return fail(err, RG_SERVING_TOKENIZER, trc);
+  std::string rendered(bytes, '\0');
+  if (bytes && (trc = rg_b200_chat_render(s->tokenizer, roles, contents, content_len, n_messages, 1, &rendered[0], bytes, &bytes,
+                                          &terr)) != RG_TOK_OK)
+    return fail(err, RG_SERVING_TOKENIZER, trc);
+  Key ids;
+  if (int32_t rc = encode_text(s->tokenizer, rendered.data(), rendered.size(), &ids, err)) return rc;
+  return rg_b200_scheduler_submit_ids(s, ids.data(), ids.size(), max_new, sampling, request_id, err);
+}
+
+int32_t rg_b200_scheduler_status(const rg_scheduler *s, uint64_t id, int32_t *status) {
+  if (!s || !status) return RG_SERVING_INVALID_ARGUMENT;
+  auto it = s->requests.find(id);
+  if (it == s->requests.end()) return RG_SERVING_UNKNOWN_REQUEST;
+  *status = it->second.status;
+  return RG_SERVING_OK;
+}
+
+int32_t rg_b200_scheduler_result(const rg_scheduler *s, uint64_t id, rg_serving_result *out) {
+  if (!s || !out) return RG_SERVING_INVALID_ARGUMENT;
+  auto it = s->requests.find(id);
+  if (it == s->requests.end()) return RG_SERVING_UNKNOWN_REQUEST;
+  const Request &r = it->second;
+  if (!r.has_result) return RG_SERVING_NOT_COMPLETE;
+  *out = rg_serving_result{r.id, r.prompt.data(), r.prompt.size(), r.generated.data(), r.generated.size(),
+                           r.decoded.c_str(), r.decoded.size(), r.stopped ? 1 : 0};
+  return RG_SERVING_OK;
+}
+
+int32_t rg_b200_scheduler_remove(rg_scheduler *s, uint64_t id) {
+  if (!s) return RG_SERVING_INVALID_ARGUMENT;
+  auto it = s->requests.find(id);
+  if (it == s->requests.end()) return RG_SERVING_UNKNOWN_REQUEST;
+  s->release_row(it->second);
+  s->requests.erase(it);
+  s->order.erase(std::find(s->order.begin(), s->order.end(), id));
+  return RG_SERVING_OK;
+}
+
+size_t rg_b200_scheduler_pending(const rg_scheduler *s) {
+  size_t n = 0;
+  if (s)
+    for (auto &kv : s->requests) n += kv.second.status != RG_REQUEST_COMPLETE;
+  return n;
+}
+
+size_t rg_b200_scheduler_completed(const rg_scheduler *s, uint64_t *ids, size_t cap) {
+  size_t n = 0;
+  if (!s) return 0;
+  for (uint64_t id : s->order)
+    if (s->requests.at(id).has_result) {
+      if (ids && n < cap) ids[n] = id;
+      ++n;
+    }
+  return n;
+}
+
+void rg_b200_scheduler_prefix_stats(const rg_scheduler *s, rg_prefix_stats *out) {
+  if (!s || !out) return;
+  const PrefixCache &c = s->prefixes;
+  *out = rg_prefix_stats{(uint64_t)c.entries.size(), c.bytes, c.hits, c.misses, c.stale_rejections, c.evictions, c.generation};
+}
+
+void rg_b200_scheduler_invalidate_prefix_cache(rg_scheduler *s) {
+  if (s) s->prefixes.invalidate();
+}
+
+int32_t rg_b200_scheduler_step(rg_scheduler *s, rg_token_event *events, size_t cap, size_t *n_events, rg_serving_error *err) {
+  if (!s || !n_events || (!events && cap)) return fail(err, RG_SERVING_INVALID_ARGUMENT);
+  *n_events = 0;
+  std::vector<Request *> selected;
+  for (uint64_t id : s->order) {
+    Request &r = s->requests.at(id);
+    if (r.status != RG_REQUEST_COMPLETE) selected.push_back(&r);
+    if ((int32_t)selected.size() == s->batch_size) break;
+  }
+  if (selected.empty()) return RG_SERVING_OK;
+  if (cap < selected.size()) return fail(err, RG_SERVING_INVALID_ARGUMENT, (int64_t)selected.size(), (int64_t)cap);
+  const size_t vocab = (size_t)s->be.vocab;
+  std::map<uint64_t, int32_t> chosen;
+  std::vector<Request *> decode_cols, admitted;
+  // a failure un-admits what this step admitted, so that the step can be run again as a whole
+  auto roll_back = [&](int32_t rc) {
+    for (Request *r : admitted) {
+      s->release_row(*r);
+      r->status = RG_REQUEST_QUEUED;
+    }
+    return fail(err, RG_SERVING_SESSION, rc);
+  };
+  std::vector<float> last(vocab);
+  for (Request *r : selected) {
+    if (r->has_pending) {
+      decode_cols.push_back(r);
+      continue;
+    }
+    // a new request: lean on the longest cached prefix, prefill what is left
+    r->row = *s->free_rows.begin();
+    s->free_rows.erase(s->free_rows.begin());
+    r->status = RG_REQUEST_RUNNING;
+    admitted.push_back(r);
+    size_t cached = 0;
+    Entry *hit = nullptr;
+    const Key *key = s->prefixes.longest(r->prompt, &hit);
+    const float *tape = s->tape_row(*r);
+    int32_t token = -1, rc = RG_OK;
+    if (key) {
+      const Key held = *key;  // the reference taken by longest() is dropped once the row has its own copy
+      rc = s->be.snapshot_restore(s->be.ctx, hit->snapshot->handle, r->row);
+      cached = (size_t)hit->snapshot->length;
+      if (!rc && cached == r->prompt.size()) {
+        rc = s->be.select(s->be.ctx, hit->logits.data(), r->temperature, tape, &token);
+        s->prefixes.release(held);
+        if (rc) return roll_back(rc);
+        chosen[r->id] = token;
+        continue;
+      }
+      s->prefixes.release(held);
+      if (rc) return roll_back(rc);
+    }
+    rc = s->be.prefill_select(s->be.ctx, r->row, r->prompt.data() + cached, r->prompt.size() - cached, r->temperature, tape,
+                              last.data(), &token);
+    if (rc) return roll_back(rc);
+    if (s->prefixes.max_entries && s->prefixes.max_bytes) {
+      void *handle = nullptr;
+      size_t bytes = 0;
+      if ((rc = s->be.snapshot_create(s->be.ctx, r->row, (int32_t)r->prompt.size(), &handle, &bytes))) return roll_back(rc);
+      auto snap = std::make_shared<Snapshot>(&s->be, handle, (int32_t)r->prompt.size(), bytes);
+      s->prefixes.insert(r->prompt, std::move(snap), last.data(), vocab);
+    }
+    chosen[r->id] = token;
+  }
+  if (!decode_cols.empty()) {
+    const int32_t n = (int32_t)decode_cols.size();
+    std::vector<int32_t> rows(n), toks(n), ids(n);
+    std::vector<float> temps(n, 0.f), tapes;
+    for (int32_t i = 0; i < n; ++i) {
+      const Request &r = *decode_cols[i];
+      rows[i] = r.row;
+      toks[i] = r.pending_token;
+      if (!r.greedy) {
+        if (tapes.empty()) tapes.assign((size_t)n * vocab, 0.f);
+        temps[i] = r.temperature;
+        memcpy(&tapes[(size_t)i * vocab], s->tape_row(r), vocab * sizeof(float));
+      }
+    }
+    const int32_t rc = s->be.decode_rows(s->be.ctx, rows.data(), toks.data(), n, temps.data(), tapes.empty() ? nullptr : tapes.data(),
+                                         ids.data());
+    if (rc) return roll_back(rc);
+    for (int32_t i = 0; i < n; ++i) chosen[decode_cols[i]->id] = ids[i];
+  }
+  // commit
+  for (Request *r : selected) {
+    const int32_t token = chosen.at(r->id);
+    rg_token_event ev{r->id, r->arrival, (int32_t)r->generated.size(), token, 0, 0};
+    r->generated.push_back(token);
+    r->stopped = s->stop_ids.count(token) != 0;
+    const bool complete = r->stopped || r->generated.size() == r->max_new;
+    if (complete) {
+      r->status = RG_REQUEST_COMPLETE;
+      r->has_pending = false;
+      s->release_row(*r);
+      if (s->tokenizer) {
+        std::vector<uint32_t> gen(r->generated.begin(), r->generated.end());
+        rg_tok_error terr{};
+        size_t bytes = 0;
+        rg_b200_tokenizer_decode(s->tokenizer, gen.data(), gen.size(), nullptr, 0, &bytes, &terr);
+        r->decoded.resize(bytes);
+        if (bytes && rg_b200_tokenizer_decode(s->tokenizer, gen.data(), gen.size(), &r->decoded[0], bytes, &bytes, &terr) != RG_TOK_OK)
+          r->decoded.clear();
+      }
+      r->has_result = true;
+    } else {
+      r->has_pending = true;
+      r->pending_token = token;
+    }
+    ev.stopped = r->stopped;
+    ev.complete = complete;
+    events[(*n_events)++] = ev;
+  }
+  return RG_SERVING_OK;
+}
+
+}  // extern "C"

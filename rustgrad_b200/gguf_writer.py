@@ -132,6 +132,8 @@ def llama_metadata(cfg: dict, chat_tokens: bool = False) -> list[bytes]:
     if ids is not None:
         kvs += [kv_u32("tokenizer.ggml.bos_token_id", ids["bos"]), kv_u32("tokenizer.ggml.eos_token_id", ids["eos"]),
                 kv_u32("tokenizer.ggml.eot_token_id", ids["eot"])]
+    if cfg.get("rope_dim", 0) and cfg["rope_dim"] != cfg["head_dim"]:
+        kvs.append(kv_u32("llama.rope.dimension_count", cfg["rope_dim"]))
     if cfg["head_dim"] * cfg["n_heads"] != cfg["d_model"]:
         kvs.append(kv_u32("llama.attention.key_length", cfg["head_dim"]))
         kvs.append(kv_u32("llama.attention.value_length", cfg["head_dim"]))

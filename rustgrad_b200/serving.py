@@ -1,43 +1,114 @@
-"""Continuous batching with a prefix cache over one ``LlamaCudaSession``: the scheduler of
-rustgrad's ``LlamaServingScheduler`` (src/models/transformer/serving/mod.rs:371-690) with the same
-verbs (submit_ids / submit_text / submit_chat / status / result / remove / step / prefix_stats /
-invalidate_prefix_cache) and the same policy: requests are served in arrival order, at most
-``batch_size`` per step, one token per selected request per step.  (The reference stages a step
-and commits it as a whole; here a device call that fails raises, the session reports its typed
-status, and the requests that were not reached keep their state.)
+"""Continuous batching with a prefix cache over one ``LlamaCudaSession``: the verbs of rustgrad's
+``LlamaServingScheduler`` (src/models/transformer/serving/mod.rs:371-690) -- submit_ids /
+submit_text / submit_chat / status / result / remove / step / prefix_stats /
+invalidate_prefix_cache -- bound to the scheduler of ``include/rg_b200_serving.h``.
 
-What differs, because the caches live in HBM rather than in per-request host tensors:
-
-* a request keeps one cache row of the session from its first step to its last, instead of a
-  batch being rebuilt from snapshots at every step;
-* a prefix entry is taken when a prompt has been prefilled (and for a prompt extended from an
-  entry), as a device-to-device copy of the row's K/V; decode steps do not add entries (the
-  reference inserts one per computed step and lets its byte budget evict them);
-* decode columns of one step run as ONE launch sequence over all running rows; newly admitted
-  prompts are prefilled one after the other in the same step.
-
-All device work goes through the C ABI (``rg_b200_prefill_select``, ``rg_b200_decode_rows``,
-``rg_b200_select``, ``rg_b200_kv_snapshot_*``); this module only decides what runs.
+The policy (arrival order, batch size, cache rows, prefix cache, admission checks) is compiled code
+in the library; this module only converts arguments and results.  ``ServingBackend`` lets a test
+drive that policy through a table of Python callables instead of a device session.
 """
 from __future__ import annotations
 
 import ctypes as C
-import math
 from dataclasses import dataclass, field
 from typing import Optional
 
 import numpy as np
 
 from . import _lib
-from .session import LlamaCudaSession, check
+from .tokenizer import ROLES
+
+KINDS = ["Ok", "EmptyBatch", "EmptyPrompt", "ContextLength", "TokenOutOfRange", "InvalidTemperature", "UniformTapeLength",
+         "InvalidUniform", "UnknownRequest", "Session", "Tokenizer", "InvalidArgument", "NotComplete"]
+STATUS = ["queued", "running", "complete"]
+f32p, i32p, vp = C.POINTER(C.c_float), C.POINTER(C.c_int32), C.c_void_p
+
+
+class _Error(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("value", C.c_int64), ("value2", C.c_int64)]
+
+
+class _Options(C.Structure):
+    _fields_ = [("batch_size", C.c_int32), ("max_rows", C.c_int32), ("prefix_max_entries", C.c_size_t),
+                ("prefix_max_bytes", C.c_size_t), ("stop_ids", i32p), ("n_stop_ids", C.c_size_t), ("has_bos", C.c_int32),
+                ("bos_id", C.c_int32)]
+
+
+class _Sampling(C.Structure):
+    _fields_ = [("greedy", C.c_int32), ("temperature", C.c_float), ("uniforms", f32p), ("n_uniforms", C.c_size_t)]
+
+
+class _Event(C.Structure):
+    _fields_ = [("request_id", C.c_uint64), ("arrival_order", C.c_uint64), ("generation_step", C.c_int32),
+                ("token_id", C.c_int32), ("stopped", C.c_int32), ("complete", C.c_int32)]
+
+
+class _Result(C.Structure):
+    _fields_ = [("request_id", C.c_uint64), ("prompt_ids", i32p), ("n_prompt_ids", C.c_size_t), ("generated_ids", i32p),
+                ("n_generated_ids", C.c_size_t), ("decoded", C.c_char_p), ("decoded_bytes", C.c_size_t), ("stopped", C.c_int32)]
+
+
+class _Stats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("entries", "bytes", "hits", "misses", "stale_rejections", "evictions", "generation")]
+
+
+_RESET = C.CFUNCTYPE(C.c_int32, vp, C.c_int32)
+_PREFILL = C.CFUNCTYPE(C.c_int32, vp, C.c_int32, i32p, C.c_size_t, C.c_float, f32p, f32p, i32p)
+_DECODE = C.CFUNCTYPE(C.c_int32, vp, i32p, i32p, C.c_int32, f32p, f32p, i32p)
+_SELECT = C.CFUNCTYPE(C.c_int32, vp, f32p, C.c_float, f32p, i32p)
+_SNAP_CREATE = C.CFUNCTYPE(C.c_int32, vp, C.c_int32, C.c_int32, C.POINTER(vp), C.POINTER(C.c_size_t))
+_SNAP_RESTORE = C.CFUNCTYPE(C.c_int32, vp, vp, C.c_int32)
+_SNAP_FREE = C.CFUNCTYPE(None, vp, vp)
+
+
+class _Backend(C.Structure):
+    _fields_ = [("ctx", vp), ("vocab", C.c_int32), ("max_context", C.c_int32), ("reset_row", _RESET),
+                ("prefill_select", _PREFILL), ("decode_rows", _DECODE), ("select", _SELECT), ("snapshot_create", _SNAP_CREATE),
+                ("snapshot_restore", _SNAP_RESTORE), ("snapshot_free", _SNAP_FREE)]
+
+
+def _L():
+    L = _lib.load()
+    if getattr(L, "_serving_bound", False):
+        return L
+    ep, u64p = C.POINTER(_Error), C.POINTER(C.c_uint64)
+    L.rg_b200_scheduler_new.argtypes = [vp, vp, C.POINTER(_Options), C.POINTER(vp), ep]
+    L.rg_b200_scheduler_new_with_backend.argtypes = [C.POINTER(_Backend), vp, C.POINTER(_Options), C.POINTER(vp), ep]
+    L.rg_b200_scheduler_free.restype = None
+    L.rg_b200_scheduler_free.argtypes = [vp]
+    L.rg_b200_scheduler_submit_ids.argtypes = [vp, i32p, C.c_size_t, C.c_size_t, C.POINTER(_Sampling), u64p, ep]
+    L.rg_b200_scheduler_submit_text.argtypes = [vp, C.c_char_p, C.c_size_t, C.c_size_t, C.POINTER(_Sampling), u64p, ep]
+    L.rg_b200_scheduler_submit_chat.argtypes = [vp, i32p, C.POINTER(C.c_char_p), C.POINTER(C.c_size_t), C.c_size_t, C.c_size_t,
+                                                C.POINTER(_Sampling), u64p, ep]
+    L.rg_b200_scheduler_status.argtypes = [vp, C.c_uint64, i32p]
+    L.rg_b200_scheduler_result.argtypes = [vp, C.c_uint64, C.POINTER(_Result)]
+    L.rg_b200_scheduler_remove.argtypes = [vp, C.c_uint64]
+    L.rg_b200_scheduler_pending.restype = C.c_size_t
+    L.rg_b200_scheduler_pending.argtypes = [vp]
+    L.rg_b200_scheduler_completed.restype = C.c_size_t
+    L.rg_b200_scheduler_completed.argtypes = [vp, u64p, C.c_size_t]
+    L.rg_b200_scheduler_prefix_stats.restype = None
+    L.rg_b200_scheduler_prefix_stats.argtypes = [vp, C.POINTER(_Stats)]
+    L.rg_b200_scheduler_invalidate_prefix_cache.restype = None
+    L.rg_b200_scheduler_invalidate_prefix_cache.argtypes = [vp]
+    L.rg_b200_scheduler_step.argtypes = [vp, C.POINTER(_Event), C.c_size_t, C.POINTER(C.c_size_t), ep]
+    L._serving_bound = True
+    return L
 
 
 class ServingError(Exception):
-    """LlamaServingError (serving/mod.rs:792-860) by kind."""
+    """LlamaServingError (serving/mod.rs:792-860) by kind; ``value`` / ``value2`` carry its numbers
+    (requested and maximum length, token and vocabulary, required and actual tape length, the
+    status of the session verb that failed)."""
 
-    def __init__(self, kind: str, **detail):
-        self.kind, self.detail = kind, detail
-        super().__init__(f"{kind}: {detail}")
+    def __init__(self, kind: str, value: int = 0, value2: int = 0, text: str = ""):
+        self.kind, self.value, self.value2 = kind, value, value2
+        super().__init__(f"{kind}: {value}, {value2}" + (f" ({text})" if text else ""))
+
+
+def _raise(rc: int, err: _Error):
+    text = _lib.load().rg_b200_last_error().decode(errors="replace") if rc == 9 else ""
+    raise ServingError(KINDS[rc] if 0 <= rc < len(KINDS) else str(rc), err.value, err.value2, text)
 
 
 @dataclass
@@ -79,314 +150,182 @@ class ServingResult:
     stopped: bool
 
 
-class _Snapshot:
-    """A device K/V copy shared by the cache and by requests that lean on it."""
+class ServingBackend:
+    """The session verbs of a step as Python callables, for driving the compiled policy without a
+    device.  Subclass and override; every verb returns an ``rg_status`` (0 = ok)."""
+    vocab = 0
+    max_context = 0
 
-    def __init__(self, session: LlamaCudaSession, row: int, length: int):
-        self._L = _lib.load()
-        self._h = C.c_void_p()
-        check(self._L.rg_b200_kv_snapshot_create(session._h, row, length, C.byref(self._h)))
-        self.length = length
-        self.bytes = int(self._L.rg_b200_kv_snapshot_bytes(self._h))
+    def reset_row(self, row: int) -> int:
+        return 0
 
-    def restore(self, session: LlamaCudaSession, row: int) -> None:
-        check(self._L.rg_b200_kv_snapshot_restore(session._h, self._h, row))
+    def prefill_select(self, row: int, ids: list, temperature: float, uniforms, last_logits: np.ndarray):
+        """Returns (status, selected token); fills last_logits [vocab]."""
+        raise NotImplementedError
 
-    def __del__(self):
-        if getattr(self, "_h", None):
-            self._L.rg_b200_kv_snapshot_free(self._h)
-            self._h = None
+    def decode_rows(self, rows: list, tokens: list, temperatures: list, uniforms):
+        """Returns (status, ids)."""
+        raise NotImplementedError
 
+    def select(self, logits: np.ndarray, temperature: float, uniforms):
+        """Returns (status, id)."""
+        raise NotImplementedError
 
-@dataclass
-class _Entry:
-    generation: int
-    snapshot: _Snapshot
-    logits: np.ndarray
-    bytes: int
-    last_used: int
-    references: int = 0
+    def snapshot_create(self, row: int, length: int):
+        """Returns (status, handle > 0, bytes)."""
+        raise NotImplementedError
 
+    def snapshot_restore(self, handle: int, row: int) -> int:
+        raise NotImplementedError
 
-class _PrefixCache:
-    """PrefixCache (serving/mod.rs:192-352): longest-prefix lookup, LRU eviction of unreferenced
-    entries under an entry and a byte budget, generation counter for invalidation."""
+    def snapshot_free(self, handle: int) -> None:
+        pass
 
-    def __init__(self, max_entries: int, max_bytes: int):
-        self.max_entries, self.max_bytes = max_entries, max_bytes
-        self.generation = self.clock = self.bytes = 0
-        self.hits = self.misses = self.stale_rejections = self.evictions = 0
-        self.entries: dict[tuple, _Entry] = {}
+    def _table(self) -> _Backend:
+        v = self.vocab
 
-    def stats(self) -> dict:
-        return {"entries": len(self.entries), "bytes": self.bytes, "hits": self.hits, "misses": self.misses,
-                "stale_rejections": self.stale_rejections, "evictions": self.evictions, "generation": self.generation}
+        def tape(p, n):
+            return None if not p else np.ctypeslib.as_array(p, shape=(n,)).copy()
 
-    def invalidate(self) -> None:
-        self.generation += 1
-        self.bytes = 0
-        self.entries.clear()
+        def prefill(_, row, ids, n, temp, uni, last, sel):
+            rc, tok = self.prefill_select(row, [ids[i] for i in range(n)], temp, tape(uni, v), np.ctypeslib.as_array(last, shape=(v,)))
+            sel[0] = tok
+            return rc
 
-    def release(self, key) -> None:
-        e = self.entries.get(key)
-        if e is not None:
-            e.references = max(0, e.references - 1)
+        def decode(_, rows, toks, n, temps, uni, out):
+            rc, ids = self.decode_rows([rows[i] for i in range(n)], [toks[i] for i in range(n)], [temps[i] for i in range(n)],
+                                       None if not uni else tape(uni, n * v).reshape(n, v))
+            for i, t in enumerate(ids):
+                out[i] = t
+            return rc
 
-    def longest(self, tokens: list):
-        for key in [k for k, e in self.entries.items() if e.generation != self.generation]:
-            self.bytes -= self.entries.pop(key).bytes
-            self.stale_rejections += 1
-        best = None
-        for key in self.entries:
-            if len(key) <= len(tokens) and tuple(tokens[: len(key)]) == key and (best is None or len(key) > len(best)):
-                best = key
-        if best is None:
-            self.misses += 1
-            return None
-        self.clock += 1
-        e = self.entries[best]
-        e.last_used = self.clock
-        e.references += 1
-        self.hits += 1
-        return best, e.snapshot, e.logits
+        def select(_, logits, temp, uni, out):
+            rc, tok = self.select(np.ctypeslib.as_array(logits, shape=(v,)).copy(), temp, tape(uni, v))
+            out[0] = tok
+            return rc
 
-    def insert(self, tokens: list, snapshot: _Snapshot, logits: np.ndarray) -> bool:
-        if self.max_entries == 0 or self.max_bytes == 0:
-            return False
-        size = snapshot.bytes + logits.size * 4 + len(tokens) * 4
-        if size > self.max_bytes:
-            return False
-        key = tuple(tokens)
-        old = self.entries.pop(key, None)
-        if old is not None:
-            self.bytes -= old.bytes
-        while len(self.entries) >= self.max_entries or self.bytes + size > self.max_bytes:
-            free = [(e.last_used, k) for k, e in self.entries.items() if e.references == 0]
-            if not free:
-                return False
-            _, victim = min(free)
-            self.bytes -= self.entries.pop(victim).bytes
-            self.evictions += 1
-        self.clock += 1
-        self.bytes += size
-        self.entries[key] = _Entry(self.generation, snapshot, logits, size, self.clock)
-        return True
+        def snap_create(_, row, length, handle, nbytes):
+            rc, h, b = self.snapshot_create(row, length)
+            handle[0], nbytes[0] = h, b
+            return rc
 
-
-@dataclass
-class _Request:
-    id: int
-    arrival: int
-    prompt: list
-    config: GenerationConfig
-    status: str  # "queued" | "running" | "complete"
-    generated: list = field(default_factory=list)
-    stopped: bool = False
-    row: Optional[int] = None
-    cached: int = 0  # positions of prompt + generated already in the row
-    prefix_reference: Optional[tuple] = None
-    pending_token: Optional[int] = None
-    result: Optional[ServingResult] = None
+        self._keep = [_RESET(lambda _, row: self.reset_row(row)), _PREFILL(prefill), _DECODE(decode), _SELECT(select),
+                      _SNAP_CREATE(snap_create), _SNAP_RESTORE(lambda _, h, row: self.snapshot_restore(h, row)),
+                      _SNAP_FREE(lambda _, h: self.snapshot_free(h))]
+        return _Backend(None, self.vocab, self.max_context, *self._keep)
 
 
 class LlamaServingScheduler:
-    def __init__(self, session: LlamaCudaSession, tokenizer=None, batch_size: int = 1, prefix_max_entries: int = 0,
-                 prefix_max_bytes: int = 0, stop_ids=(), bos_id: Optional[int] = None, max_rows: Optional[int] = None):
-        if batch_size == 0:
-            raise ServingError("EmptyBatch")
-        self.session, self.tokenizer, self.batch_size = session, tokenizer, batch_size
-        self.stop_ids, self.bos_id = set(int(t) for t in stop_ids), bos_id
-        self._rows = list(range(max_rows if max_rows is not None else batch_size))
-        if len(self._rows) < batch_size:
-            raise ServingError("EmptyBatch", rows=len(self._rows), batch_size=batch_size)
-        self._free_rows = list(self._rows)
-        self._next_id = self._next_arrival = 0
-        self._order: list[int] = []
-        self._requests: dict[int, _Request] = {}
-        self._prefixes = _PrefixCache(prefix_max_entries, prefix_max_bytes)
-        self._L = _lib.load()
+    def __init__(self, session, tokenizer=None, batch_size: int = 1, prefix_max_entries: int = 0, prefix_max_bytes: int = 0,
+                 stop_ids=(), bos_id: Optional[int] = None, max_rows: Optional[int] = None):
+        self._lib = _L()
+        self.session, self.tokenizer = session, tokenizer
+        stops = np.array(sorted(int(t) for t in stop_ids), dtype=np.int32)
+        opts = _Options(batch_size, 0 if max_rows is None else max_rows, prefix_max_entries, prefix_max_bytes,
+                        stops.ctypes.data_as(i32p), stops.size, int(bos_id is not None), bos_id or 0)
+        if max_rows is not None and max_rows <= 0:
+            raise ServingError("EmptyBatch", max_rows, batch_size)
+        self._h, err = vp(), _Error()
+        tok = tokenizer._h if tokenizer is not None else None
+        if isinstance(session, ServingBackend):
+            self._table = session._table()
+            rc = self._lib.rg_b200_scheduler_new_with_backend(C.byref(self._table), tok, C.byref(opts), C.byref(self._h), C.byref(err))
+        else:
+            rc = self._lib.rg_b200_scheduler_new(session._h, tok, C.byref(opts), C.byref(self._h), C.byref(err))
+        if rc:
+            self._h = None
+            _raise(rc, err)
+        self.batch_size = batch_size
 
-    # ---- admission (serving/mod.rs:408-477, validate_request :726-790) ------------------------
-    def submit_ids(self, prompt, config: GenerationConfig) -> int:
-        prompt = [int(t) for t in prompt]
-        vocab, ctx = self.session.vocab_size(), self.session.max_context()
-        if not prompt:
-            raise ServingError("EmptyPrompt")
-        requested = len(prompt) + config.max_new_tokens
-        if requested > ctx:
-            raise ServingError("ContextLength", requested=requested, maximum=ctx)
-        for t in prompt:
-            if t < 0 or t >= vocab:
-                raise ServingError("TokenOutOfRange", token=t, vocab=vocab)
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.rg_b200_scheduler_free(self._h)
+            self._h = None
+
+    __del__ = close
+
+    @staticmethod
+    def _sampling(config: GenerationConfig):
         s = config.sampling
-        if not s.greedy:
-            if not math.isfinite(s.temperature) or s.temperature <= 0.0:
-                raise ServingError("InvalidTemperature")
-            required = config.max_new_tokens * vocab
-            flat = np.zeros(0, np.float32) if s.uniforms is None else np.ascontiguousarray(s.uniforms, dtype=np.float32).ravel()
-            if flat.size < required:
-                raise ServingError("UniformTapeLength", required=required, actual=int(flat.size))
-            u = flat[:required].reshape(config.max_new_tokens, vocab)
-            bad = np.flatnonzero(~np.isfinite(u.ravel()) | (u.ravel() < 0.0) | (u.ravel() >= 1.0))
-            if bad.size:
-                raise ServingError("InvalidUniform", index=int(bad[0]))
-            config = GenerationConfig(config.max_new_tokens, Sampling(float(s.temperature), u))
-        rid = self._next_id
-        self._next_id += 1
-        arrival = self._next_arrival
-        self._next_arrival += 1
-        done = config.max_new_tokens == 0
-        req = _Request(rid, arrival, prompt, config, "complete" if done else "queued")
-        if done:
-            req.result = ServingResult(rid, list(prompt), [], "", False)
-        self._requests[rid] = req
-        self._order.append(rid)
-        return rid
+        if s.greedy:
+            return _Sampling(1, 0.0, None, 0), None
+        flat = np.zeros(0, np.float32) if s.uniforms is None else np.ascontiguousarray(s.uniforms, dtype=np.float32).ravel()
+        return _Sampling(0, float(s.temperature), flat.ctypes.data_as(f32p), flat.size), flat
+
+    # ---- admission (serving/mod.rs:408-477) ----------------------------------------------------
+    def submit_ids(self, prompt, config: GenerationConfig) -> int:
+        ids = np.ascontiguousarray([int(t) for t in prompt], dtype=np.int32)
+        sampling, _keep = self._sampling(config)
+        rid, err = C.c_uint64(), _Error()
+        rc = self._lib.rg_b200_scheduler_submit_ids(self._h, ids.ctypes.data_as(i32p), ids.size, config.max_new_tokens,
+                                                    C.byref(sampling), C.byref(rid), C.byref(err))
+        if rc:
+            _raise(rc, err)
+        return rid.value
 
     def submit_text(self, prompt: str, config: GenerationConfig) -> int:
-        ids = self.tokenizer.encode(prompt)
-        if self.bos_id is not None:
-            ids.insert(0, self.bos_id)
-        return self.submit_ids(ids, config)
+        raw = prompt.encode("utf-8")
+        sampling, _keep = self._sampling(config)
+        rid, err = C.c_uint64(), _Error()
+        rc = self._lib.rg_b200_scheduler_submit_text(self._h, raw, len(raw), config.max_new_tokens, C.byref(sampling),
+                                                     C.byref(rid), C.byref(err))
+        if rc:
+            _raise(rc, err)
+        return rid.value
 
-    def submit_chat(self, template, messages, config: GenerationConfig) -> int:
-        return self.submit_ids(self.tokenizer.encode(template.render(self.tokenizer, messages, True)), config)
+    def submit_chat(self, messages, config: GenerationConfig) -> int:
+        """(role, content) messages through the one checked chat template, generation prompt added."""
+        messages = list(messages)
+        n = len(messages)
+        roles = (C.c_int32 * max(n, 1))(*[ROLES[r] for r, _ in messages])
+        raw = [c.encode("utf-8") for _, c in messages]
+        strs = (C.c_char_p * max(n, 1))(*raw)
+        lens = (C.c_size_t * max(n, 1))(*[len(r) for r in raw])
+        sampling, _keep = self._sampling(config)
+        rid, err = C.c_uint64(), _Error()
+        rc = self._lib.rg_b200_scheduler_submit_chat(self._h, roles, strs, lens, n, config.max_new_tokens, C.byref(sampling),
+                                                     C.byref(rid), C.byref(err))
+        if rc:
+            _raise(rc, err)
+        return rid.value
 
     def status(self, rid: int) -> Optional[str]:
-        r = self._requests.get(rid)
-        return None if r is None else r.status
+        st = C.c_int32()
+        return None if self._lib.rg_b200_scheduler_status(self._h, rid, C.byref(st)) else STATUS[st.value]
 
     def result(self, rid: int) -> Optional[ServingResult]:
-        r = self._requests.get(rid)
-        return None if r is None else r.result
+        r = _Result()
+        if self._lib.rg_b200_scheduler_result(self._h, rid, C.byref(r)):
+            return None
+        return ServingResult(r.request_id, [r.prompt_ids[i] for i in range(r.n_prompt_ids)],
+                             [r.generated_ids[i] for i in range(r.n_generated_ids)],
+                             C.string_at(r.decoded, r.decoded_bytes).decode("utf-8", "replace"), bool(r.stopped))
 
     def completed_results(self):
-        return [self._requests[i].result for i in self._order if self._requests[i].result is not None]
+        n = self._lib.rg_b200_scheduler_completed(self._h, None, 0)
+        ids = (C.c_uint64 * max(n, 1))()
+        self._lib.rg_b200_scheduler_completed(self._h, ids, n)
+        return [self.result(ids[i]) for i in range(n)]
 
     def pending(self) -> int:
-        return sum(1 for r in self._requests.values() if r.status != "complete")
+        return self._lib.rg_b200_scheduler_pending(self._h)
 
     def prefix_stats(self) -> dict:
-        return self._prefixes.stats()
+        st = _Stats()
+        self._lib.rg_b200_scheduler_prefix_stats(self._h, C.byref(st))
+        return {n: getattr(st, n) for n, _ in _Stats._fields_}
 
     def remove(self, rid: int) -> bool:
-        r = self._requests.pop(rid, None)
-        if r is None:
-            return False
-        if r.prefix_reference is not None:
-            self._prefixes.release(r.prefix_reference)
-        self._release_row(r)
-        self._order.remove(rid)
-        return True
+        return self._lib.rg_b200_scheduler_remove(self._h, rid) == 0
 
     def invalidate_prefix_cache(self) -> None:
-        self._prefixes.invalidate()
-        for r in self._requests.values():
-            r.prefix_reference = None
+        self._lib.rg_b200_scheduler_invalidate_prefix_cache(self._h)
 
-    def _release_row(self, r: _Request) -> None:
-        if r.row is not None:
-            check(self._L.rg_b200_reset_row(self.session._h, r.row))
-            self._free_rows.append(r.row)
-            self._free_rows.sort()
-            r.row = None
-
-    # ---- one step (serving/mod.rs:557-690) ----------------------------------------------------
+    # ---- one step (serving/mod.rs:557-690) -----------------------------------------------------
     def step(self) -> list[TokenEvent]:
-        selected = [self._requests[i] for i in self._order if self._requests[i].status != "complete"][: self.batch_size]
-        if not selected:
-            return []
-        vocab = self.session.vocab_size()
-        chosen: dict[int, int] = {}
-        decode_cols = []
-        for r in selected:
-            r.status = "running"
-            if r.row is None:
-                r.row = self._free_rows.pop(0)
-            if r.pending_token is not None:
-                decode_cols.append(r)
-                continue
-            # a new request: lean on the longest cached prefix, prefill what is left
-            hit = self._prefixes.longest(r.prompt)
-            logits = None
-            if hit is not None:
-                key, snapshot, cached_logits = hit
-                r.prefix_reference = key
-                snapshot.restore(self.session, r.row)
-                r.cached = snapshot.length
-                if snapshot.length == len(r.prompt):
-                    logits = cached_logits
-            temp, tape = self._tape_row(r)
-            if logits is not None:
-                ids = np.empty(1, dtype=np.int32)
-                t = np.array([temp], dtype=np.float32)
-                check(self._L.rg_b200_select(self.session._h, _f32(np.ascontiguousarray(logits)), 1, _f32(t),
-                                             _f32(tape) if tape is not None else None, _i32(ids)))
-                chosen[r.id] = int(ids[0])
-                self._prefixes.release(r.prefix_reference)  # the row holds its own copy of the prefix now
-                r.prefix_reference = None
-            else:
-                rest = np.ascontiguousarray(r.prompt[r.cached:], dtype=np.int32)
-                last = np.empty(vocab, dtype=np.float32)
-                sel = C.c_int32(0)
-                check(self._L.rg_b200_prefill_select(self.session._h, r.row, _i32(rest), rest.size, float(temp),
-                                                     _f32(tape) if tape is not None else None, _f32(last), C.byref(sel)))
-                if r.prefix_reference is not None:
-                    self._prefixes.release(r.prefix_reference)
-                    r.prefix_reference = None
-                r.cached = len(r.prompt)
-                if self._prefixes.max_entries and self._prefixes.max_bytes:
-                    self._prefixes.insert(list(r.prompt), _Snapshot(self.session, r.row, r.cached), last)
-                chosen[r.id] = int(sel.value)
-        if decode_cols:
-            n = len(decode_cols)
-            rows = np.array([r.row for r in decode_cols], dtype=np.int32)
-            toks = np.array([r.pending_token for r in decode_cols], dtype=np.int32)
-            temps = np.zeros(n, dtype=np.float32)
-            tapes = None
-            for i, r in enumerate(decode_cols):
-                temp, tape = self._tape_row(r)
-                if tape is not None:
-                    if tapes is None:
-                        tapes = np.zeros((n, vocab), dtype=np.float32)
-                    temps[i], tapes[i] = temp, tape
-            ids = np.empty(n, dtype=np.int32)
-            check(self._L.rg_b200_decode_rows(self.session._h, _i32(rows), _i32(toks), n, _f32(temps),
-                                              _f32(tapes) if tapes is not None else None, None, _i32(ids)))
-            for i, r in enumerate(decode_cols):
-                r.cached += 1
-                r.pending_token = None
-                chosen[r.id] = int(ids[i])
-        events = []
-        for r in selected:
-            token = chosen[r.id]
-            step = len(r.generated)
-            r.generated.append(token)
-            r.stopped = token in self.stop_ids
-            complete = r.stopped or len(r.generated) == r.config.max_new_tokens
-            if complete:
-                if r.prefix_reference is not None:
-                    self._prefixes.release(r.prefix_reference)
-                    r.prefix_reference = None
-                r.status = "complete"
-                self._release_row(r)
-                decoded = self.tokenizer.decode(r.generated) if self.tokenizer is not None else ""
-                r.result = ServingResult(r.id, list(r.prompt), list(r.generated), decoded, r.stopped)
-            else:
-                r.pending_token = token
-            events.append(TokenEvent(r.id, r.arrival, step, token, r.stopped, complete))
-        return events
-
-    def _tape_row(self, r: _Request):
-        s = r.config.sampling
-        if s.greedy:
-            return 0.0, None
-        return s.temperature, np.ascontiguousarray(s.uniforms[len(r.generated)])
-
-
-def _f32(a):
-    return a.ctypes.data_as(C.POINTER(C.c_float))
-
-
-def _i32(a):
-    return a.ctypes.data_as(C.POINTER(C.c_int32))
+        events, n, err = (_Event * self.batch_size)(), C.c_size_t(), _Error()
+        rc = self._lib.rg_b200_scheduler_step(self._h, events, self.batch_size, C.byref(n), C.byref(err))
+        if rc:
+            _raise(rc, err)
+        return [TokenEvent(e.request_id, e.arrival_order, e.generation_step, e.token_id, bool(e.stopped), bool(e.complete))
+                for e in events[: n.value]]

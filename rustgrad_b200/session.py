@@ -63,7 +63,8 @@ def _f32(a: np.ndarray):
 def config_struct(cfg: dict) -> LlamaConfig:
     return LlamaConfig(cfg["n_layers"], cfg["d_model"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"],
                        cfg["ffn_dim"], cfg["vocab"], cfg["max_context"], cfg["norm_eps"], cfg["rope_theta"],
-                       cfg.get("eos_id", -1), cfg.get("eot_id", -1))
+                       cfg.get("eos_id", -1), cfg.get("eot_id", -1), cfg.get("rope_dim", 0), cfg.get("qk_norm", 0),
+                       cfg.get("qkv_bias", 0))
 
 
 def config_dict(c: LlamaConfig) -> dict:
@@ -407,3 +408,23 @@ def qmatmul_bench(ggml_type: int, weight, n: int, k: int, activation, rotate: in
     check(_lib.load().rg_b200_qmatmul_bench(device, ggml_type, _u8(w), n, k, _f32(a), a.shape[0], rotate, iters, warmup,
                                             _f32(out), C.byref(ms)))
     return out, ms.value
+
+
+class KvSnapshot:
+    """Immutable device copy of the first ``length`` cached positions of a row, all layers
+    (LlamaNativePrefixSnapshot, src/models/transformer/serving/mod.rs:182-190)."""
+
+    def __init__(self, session: "LlamaCudaSession", row: int, length: int):
+        self._L = _lib.load()
+        self._h = C.c_void_p()
+        check(self._L.rg_b200_kv_snapshot_create(session._h, row, length, C.byref(self._h)))
+        self.length = length
+        self.bytes = int(self._L.rg_b200_kv_snapshot_bytes(self._h))
+
+    def restore(self, session: "LlamaCudaSession", row: int) -> None:
+        check(self._L.rg_b200_kv_snapshot_restore(session._h, self._h, row))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._L.rg_b200_kv_snapshot_free(self._h)
+            self._h = None

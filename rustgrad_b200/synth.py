@@ -41,6 +41,13 @@ def tensor_inventory(cfg: dict, tied_head: bool):
             (p + "ffn_gate.weight", f, d, False), (p + "ffn_up.weight", f, d, False),
             (p + "ffn_down.weight", d, f, False),
         ]
+        # model variants (src/models/transformer/model.rs:427-449): q / k RMS norm weights, projection biases
+        if cfg.get("qk_norm", 0):
+            per_head = cfg["qk_norm"] == 1
+            inv += [(p + "attn_q_norm.weight", 1, cfg["head_dim"] if per_head else qw, True),
+                    (p + "attn_k_norm.weight", 1, cfg["head_dim"] if per_head else kw, True)]
+        if cfg.get("qkv_bias", 0):
+            inv += [(p + "attn_q.bias", 1, qw, True), (p + "attn_k.bias", 1, kw, True), (p + "attn_v.bias", 1, kw, True)]
     if not tied_head:
         inv.append(("output.weight", cfg["vocab"], d, False))
     return inv
@@ -59,7 +66,13 @@ def build_tensors(cfg: dict, seed: int, body_type: int = Q8_0, embed_type: int |
     tensors = {}
     for name, rows, cols, is_norm in tensor_inventory(cfg, tied_head):
         if is_norm:
-            tensors[name] = (F32, 1, cols, np.ones(cols, dtype=np.float32).view(np.uint8))
+            if name.endswith(".bias"):  # biases and q / k norm weights are not trivial, or a test could not see them
+                vec = (rng.standard_normal(cols, dtype=np.float32) * np.float32(0.05)).astype(np.float32)
+            elif "_norm.weight" in name and ("attn_q_norm" in name or "attn_k_norm" in name):
+                vec = (np.float32(1.0) + rng.standard_normal(cols, dtype=np.float32) * np.float32(0.1)).astype(np.float32)
+            else:
+                vec = np.ones(cols, dtype=np.float32)
+            tensors[name] = (F32, 1, cols, vec.view(np.uint8))
             continue
         t = embed_type if name == "token_embd.weight" else head_type if name == "output.weight" else body_type
         if cols % 32:

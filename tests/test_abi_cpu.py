@@ -119,11 +119,18 @@ def test_llama_config_rejections_are_typed():
     assert cfg_status([kv for kv in base if b"llama.block_count" not in kv[:80]]) == 18
     assert cfg_status(base + [gguf_writer.kv_f32("llama.rope.scaling.factor", 8.0)]) == 17
     assert cfg_status(base + [gguf_writer.kv_u32("llama.expert_count", 8)]) == 17
-    assert cfg_status(base + [gguf_writer.kv_u32("llama.rope.dimension_count", 32)]) == 17   # partial rotary
+    assert cfg_status(base + [gguf_writer.kv_u32("llama.rope.dimension_count", 33)]) == 17   # odd rotary width
+    assert cfg_status(base + [gguf_writer.kv_u32("llama.rope.dimension_count", 128)]) == 17  # wider than the head
     assert cfg_status(base + [gguf_writer.kv_u32("llama.attention.value_length", 32)]) == 17
     with_bias = dict(tensors)
     with_bias["blk.0.attn_q.bias"] = (quant.F32, 1, 256, np.zeros(1024, np.uint8))
-    assert cfg_status(base, with_bias) == 17
+    assert cfg_status(base, with_bias) == 17          # one bias of the three: a partial family
+    only_q_norm = dict(tensors)
+    only_q_norm["blk.0.attn_q_norm.weight"] = (quant.F32, 1, 64, np.zeros(256, np.uint8))
+    assert cfg_status(base, only_q_norm) == 17        # a query norm without the key norm
+    # complete families and partial rotary lanes are model variants the session runs
+    g = session.GgufFile(build(base + [gguf_writer.kv_u32("llama.rope.dimension_count", 32)], tensors))
+    assert g.llama_config()["rope_dim"] == 32
 
 
 def test_stop_ids_follow_the_tokenizer_rule():

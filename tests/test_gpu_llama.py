@@ -293,9 +293,6 @@ def test_binding_rejections_precede_device_work(tiny):
     del missing["blk.1.ffn_norm.weight"]
     with pytest.raises(E.MissingTensor):
         E.LlamaCudaPlan.from_tensors(cfg, missing, target).prepare()
-    with pytest.raises(E.UnsupportedGeometry):  # packed K must be a multiple of 256
-        c2 = synth.scaled(cfg, d_model=128, n_heads=2, n_kv_heads=2)
-        E.LlamaCudaPlan.from_tensors(c2, synth.build_tensors(c2, 0), target)
 
 
 def test_host_injected_failures_are_typed_and_recoverable(tiny):
@@ -601,3 +598,87 @@ def test_bounded_device_wait_that_runs_out_is_a_timeout_then_poisoned(tiny):
         s.reset_sequence()
     # other sessions of the process are untouched
     assert np.isfinite(make_session(data, kv_f32=True).prefill_ids(prompt)).all()
+
+
+def test_packed_rows_of_any_whole_number_of_blocks():
+    """rustgrad accepts packed tensors whose K is a multiple of 32 (src/gguf/quantization/data.rs:268-270).
+    Rows that are not whole groups of 256 elements take the generic decode-and-multiply GEMV."""
+    # q width 256 and k width 128 over K = 160, ffn_down over K = 224: neither a multiple of 256
+    cfg = synth.scaled(synth.TINY, d_model=160, n_heads=4, n_kv_heads=2, head_dim=64, ffn_dim=224, vocab=96, n_layers=2)
+    tensors = synth.build_tensors(cfg, seed=3, body_type=quant.Q4_0, embed_type=quant.Q8_0, head_type=quant.Q8_0, tied_head=False)
+    oracle = O.OracleModel(cfg, tensors, threads=2)
+    s = session.LlamaCudaPlan.from_tensors(cfg, tensors, session.CudaSessionTarget(kv_f32=True)).prepare()
+    prompt = synth.prompt_ids(cfg, 11, seed=4)
+    want_ids, _ = oracle.generate_greedy(prompt, 10, O.MODE_STRICT)
+    assert s.generate_ids(prompt, 10).generated_ids == want_ids
+    oracle.reset()
+    s.reset_sequence()
+    assert_logits_close(s.prefill_ids(prompt), oracle.forward(prompt))
+
+
+VARIANTS = [dict(rope_dim=32, qk_norm=1, qkv_bias=1), dict(rope_dim=16), dict(qk_norm=2, n_kv_heads=4), dict(qkv_bias=1),
+            dict(rope_dim=2, qk_norm=1, qkv_bias=1, body=quant.Q4_0, head_dim=128, n_heads=2, n_kv_heads=1)]
+
+
+@pytest.mark.parametrize("variant", VARIANTS, ids=lambda v: "-".join(f"{k}{v[k]}" for k in sorted(v)))
+def test_model_variants_match_cpu_path(variant):
+    """Partial rotary lanes (the query permuted over its last rope_dim lanes, the key over the head),
+    RMS norms of q and k per head or per projection, and q / k / v biases
+    (src/models/transformer/layer.rs:274-346,481-571; model.rs:253-282): prefill in chunks, token
+    steps and batched decode against the CPU checker, through a GGUF file."""
+    variant = dict(variant)
+    body = variant.pop("body", quant.Q8_0)
+    base = dict(d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn_dim=512, vocab=320, n_layers=2, max_context=96)
+    base.update(variant)
+    cfg = synth.scaled(synth.TINY, **base)
+    tensors = synth.build_tensors(cfg, seed=8, body_type=body)
+    data = synth.gguf_bytes(cfg, tensors)
+    g = session.GgufFile(data)
+    got_cfg = g.llama_config()
+    g.close()
+    for key in ("rope_dim", "qk_norm", "qkv_bias"):
+        want = cfg.get(key, 0)
+        assert got_cfg[key] == (0 if key == "rope_dim" and want == cfg["head_dim"] else want), key
+    s = make_session(data, kv_f32=True, max_batch=3)
+    oracle = O.OracleModel(cfg, tensors, threads=2)
+    prompt = synth.prompt_ids(cfg, 21, seed=9)       # one tensor-core chunk when the model qualifies, else chunks of 8
+    assert_logits_close(s.prefill_ids(prompt), oracle.forward(prompt))
+    tok = 5
+    for _ in range(4):                                # token steps
+        want = oracle.forward([tok])
+        got = s.run_token(tok)
+        assert_logits_close(got, want)
+        tok = O.select_greedy(want)
+        assert int(np.argmax(got)) == tok
+    # three rows decoding together at different positions
+    oracles = [oracle] + [O.OracleModel(cfg, tensors, threads=2) for _ in range(2)]
+    toks = [tok]
+    for r in (1, 2):
+        p = synth.prompt_ids(cfg, 3 + 4 * r, seed=20 + r)
+        s.prefill_ids(p, row=r, want_logits=False)
+        toks.append(O.select_greedy(oracles[r].forward(p)))
+    logits, greedy = s.decode(toks, want_logits=True)
+    for r in range(3):
+        want = oracles[r].forward([toks[r]])
+        assert_logits_close(logits[r], want)
+        assert int(greedy[r]) == O.select_greedy(want)
+
+
+def test_incomplete_variant_families_are_refused():
+    cfg = synth.scaled(synth.TINY, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn_dim=512, vocab=320, n_layers=2,
+                       qk_norm=1, qkv_bias=1)
+    tensors = synth.build_tensors(cfg, seed=8)
+    target = session.CudaSessionTarget()
+    missing = {k: v for k, v in tensors.items() if k != "blk.1.attn_k.bias"}
+    with pytest.raises(session.MissingTensor):
+        session.LlamaCudaPlan.from_tensors(cfg, missing, target).prepare()
+    plain = synth.scaled(cfg, qk_norm=0, qkv_bias=0)
+    with pytest.raises(session.UnexpectedTensor):   # variant tensors a plain configuration does not name
+        session.LlamaCudaPlan.from_tensors(plain, tensors, target)
+    # a file with only the query norm, or only two of the three biases, has no configuration
+    for drop in ("blk.0.attn_k_norm.weight", "blk.0.attn_v.bias"):
+        partial = {k: v for k, v in tensors.items() if k != drop}
+        g = session.GgufFile(synth.gguf_bytes(cfg, partial))
+        with pytest.raises(session.UnsupportedVariant):
+            g.llama_config()
+        g.close()

@@ -1,4 +1,4 @@
-"""Continuous batching over one GPU session (rustgrad_b200/serving.py, the scheduler of
+"""Continuous batching over one GPU session (the scheduler of include/rg_b200_serving.h, after
 src/models/transformer/serving/mod.rs): every request must produce exactly the tokens it produces
 alone, whatever it shares a step with and whether or not its prompt came from the prefix cache."""
 import numpy as np
@@ -141,10 +141,10 @@ def test_stop_tokens_removal_and_admission_errors(model):
     assert e.value.kind == "InvalidTemperature"
     with pytest.raises(serving.ServingError) as e:
         sched.submit_ids(p, serving.GenerationConfig(2, serving.Sampling(1.0, np.zeros(3, np.float32))))
-    assert e.value.kind == "UniformTapeLength" and e.value.detail == {"required": 2 * cfg["vocab"], "actual": 3}
+    assert e.value.kind == "UniformTapeLength" and (e.value.value, e.value.value2) == (2 * cfg["vocab"], 3)
     with pytest.raises(serving.ServingError) as e:
         sched.submit_ids(p, serving.GenerationConfig(1, serving.Sampling(1.0, np.ones(cfg["vocab"], np.float32))))
-    assert e.value.kind == "InvalidUniform" and e.value.detail == {"index": 0}
+    assert e.value.kind == "InvalidUniform" and e.value.value == 0
     with pytest.raises(serving.ServingError):
         serving.LlamaServingScheduler(s, batch_size=0)
 
@@ -154,7 +154,7 @@ def test_snapshot_restore_round_trip_and_shape_checks(model):
     p = synth.prompt_ids(cfg, 10, seed=95)
     s = make_session(data, max_batch=2, kv_f32=False)
     logits = s.prefill_ids(p, row=0)
-    snap = serving._Snapshot(s, 0, 10)
+    snap = session.KvSnapshot(s, 0, 10)
     assert snap.bytes == 2 * cfg["n_layers"] * cfg["n_kv_heads"] * 10 * cfg["head_dim"] * 2
     snap.restore(s, 1)
     assert s.position(1) == 10
@@ -165,7 +165,7 @@ def test_snapshot_restore_round_trip_and_shape_checks(model):
     with pytest.raises(session.RgError):
         snap.restore(other, 0)
     with pytest.raises(session.RgError):
-        serving._Snapshot(s, 0, 50)
+        session.KvSnapshot(s, 0, 50)
 
 
 def test_decode_rows_rejections_leave_positions_unchanged(model):
@@ -195,3 +195,35 @@ def test_decode_rows_rejections_leave_positions_unchanged(model):
     solo.prefill_ids(synth.prompt_ids(cfg, 6, seed=2), want_logits=False)
     _, want = solo.decode([1])
     assert int(ids[0]) == int(want[0])           # column 0 fed row 2, whose prompt had seed 2
+
+
+def test_text_and_chat_requests_share_steps_and_decode_their_results():
+    """submit_text / submit_chat (serving/mod.rs:408-477): the scheduler encodes with the model's own
+    tokenizer (BOS in front of plain text, the checked template for chat) and decodes each result."""
+    from oracle import tokenizer_oracle as T
+    from rustgrad_b200 import gguf_writer, tokenizer
+    cfg = dict(synth.TINY)
+    tensors = synth.build_tensors(cfg, seed=0, body_type=quant.Q8_0)
+    data = synth.gguf_bytes(cfg, tensors, chat_tokens=True)
+    tokens, types, ids = gguf_writer.chat_token_table(cfg["vocab"])
+    normal = [(t, i) for i, (t, ty) in enumerate(zip(tokens, types)) if ty == 1]
+    special = [(t, i) for i, (t, ty) in enumerate(zip(tokens, types)) if ty != 1]
+    check_tok = T.SimpleTokenizer(normal, special, eos_id=ids["eos"], eot_id=ids["eot"], bos_id=ids["bos"])
+    g = session.GgufFile(data)
+    tok = tokenizer.SimpleTokenizer.from_gguf(g)
+    g.close()
+    s = make_session(data, max_batch=2, kv_f32=True)
+    stops = [ids["eos"], ids["eot"]]
+    sched = serving.LlamaServingScheduler(s, tokenizer=tok, batch_size=2, stop_ids=stops, bos_id=ids["bos"])
+    a = sched.submit_text("hello world", serving.GenerationConfig(6))
+    messages = [("system", "be brief"), ("user", "hello")]
+    b = sched.submit_chat(messages, serving.GenerationConfig(6))
+    run_all(sched)
+    want_a = [ids["bos"]] + check_tok.encode("hello world")
+    want_b = check_tok.encode(tokenizer.LlamaChatTemplate().render(tok, messages, True))
+    for rid, prompt in ((a, want_a), (b, want_b)):
+        r = sched.result(rid)
+        assert r.prompt_ids == prompt
+        gen = alone(data, prompt, 6)
+        cut = next((i + 1 for i, t in enumerate(gen) if t in stops), len(gen))
+        assert r.generated_ids == gen[:cut] and r.decoded == check_tok.decode(gen[:cut])

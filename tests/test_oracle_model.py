@@ -56,6 +56,67 @@ def test_strict_forward_matches_independent_f64_forward_on_dense_fixture():
     assert np.abs(want).max() > 1e-3  # the fixture is not degenerate
 
 
+def variant_fixture(qk_norm, rope_dim=2):
+    """The dense fixture with partial rotary lanes, q / k RMS norms and q / k / v biases, weights by the
+    formulas of src/models/transformer/model_tests.rs:258-297."""
+    c = dict(DENSE_CFG, rope_dim=rope_dim, qk_norm=qk_norm, qkv_bias=1)
+    if qk_norm == 2:  # per projection: equal query and key widths only (model.rs:262-268)
+        c["n_kv_heads"] = c["n_heads"]
+    hd, qw, kw = c["head_dim"], c["n_heads"] * c["head_dim"], c["n_kv_heads"] * c["head_dim"]
+    tensors = dense_fixture()
+    if qk_norm == 2:
+        for layer in range(2):
+            p, salt = f"blk.{layer}.", layer * 9
+            for name, s_, sc in (("attn_k.weight", 3, 0.014), ("attn_v.weight", 4, 0.013)):
+                tensors[p + name] = (O.F32, kw, c["d_model"], values(kw * c["d_model"], salt + s_, sc).view(np.uint8))
+    f32 = np.float32
+    for layer in range(2):
+        p = f"blk.{layer}."
+        nq, nk = (hd, hd) if qk_norm == 1 else (qw, kw)
+        tensors[p + "attn_q_norm.weight"] = (O.F32, 1, nq, np.array(
+            [f32(0.91) + f32(layer) * f32(0.02) + f32(i % hd) * f32(0.03) for i in range(nq)], dtype=np.float32).view(np.uint8))
+        tensors[p + "attn_k_norm.weight"] = (O.F32, 1, nk, np.array(
+            [f32(1.07) - f32(layer) * f32(0.01) - f32(i % hd) * f32(0.02) for i in range(nk)], dtype=np.float32).view(np.uint8))
+        for name, width, salt in (("attn_q.bias", qw, 3), ("attn_k.bias", kw, 5), ("attn_v.bias", kw, 7)):
+            tensors[p + name] = (O.F32, 1, width, np.array(
+                [(f32(i + layer * 3 + salt) - f32(8.0)) * f32(0.004) for i in range(width)], dtype=np.float32).view(np.uint8))
+    return c, tensors
+
+
+def test_partial_rotary_qk_norms_and_biases_match_independent_f64_forward():
+    # src/models/transformer/model_tests.rs:380-411 (per head, rope_dim 2: 5e-5) and :457 (per projection)
+    for qk_norm, rope_dim in ((1, 2), (2, 2), (0, 2), (1, 4)):
+        cfg, tensors = variant_fixture(qk_norm, rope_dim)
+        if qk_norm == 0:
+            cfg["qk_norm"] = 0
+            tensors = {k: v for k, v in tensors.items() if "_norm.weight" not in k or "attn_q_norm" not in k and "attn_k_norm" not in k}
+        m = O.OracleModel(cfg, tensors, threads=1)
+        tokens = [3, 4, 5]
+        full = m.forward(tokens, O.MODE_STRICT, all_logits=True)
+        assert np.abs(full - m.forward_f64(tokens)).max() <= 5e-5, (qk_norm, rope_dim)
+        m.reset()
+        step = np.stack([m.forward([t]) for t in tokens])
+        m.reset()
+        chunk = np.concatenate([m.forward(tokens[:2], all_logits=True), m.forward(tokens[2:], all_logits=True)])
+        assert np.abs(full - step).max() <= 5e-5 and np.abs(full - chunk).max() <= 5e-5
+    # the variants change the result: the same weights without them give other logits
+    plain = O.OracleModel(DENSE_CFG, dense_fixture(), threads=1).forward([3, 4, 5])
+    cfg, tensors = variant_fixture(1, 2)
+    assert np.abs(O.OracleModel(cfg, tensors, threads=1).forward([3, 4, 5]) - plain).max() > 1e-4
+    # a variant tensor the configuration does not name is refused, a missing one too
+    try:
+        O.OracleModel(DENSE_CFG, tensors, threads=1)
+        raise AssertionError("expected a refusal")
+    except O.OracleError:
+        pass
+    missing = {k: v for k, v in tensors.items() if k != "blk.1.attn_v.bias"}
+    try:
+        O.OracleModel(cfg, missing, threads=1)
+        raise AssertionError("expected a refusal")
+    except O.OracleError:
+        pass
+
+
 def test_full_equals_tokenwise_equals_chunked_cache():
     # src/models/transformer/model_tests.rs:643-669
     m = O.OracleModel(DENSE_CFG, dense_fixture(), threads=1)

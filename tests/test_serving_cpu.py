@@ -1,67 +1,302 @@
-"""Host-side bookkeeping of the serving scheduler (rustgrad_b200/serving.py) without a device:
-the prefix cache follows PrefixCache of src/models/transformer/serving/mod.rs:192-352."""
+"""The compiled serving scheduler (include/rg_b200_serving.h) driven without a device, through a
+table of Python callables in place of the session verbs: admission, arrival order, cache rows,
+stop ids, sampling tapes, the prefix cache (PrefixCache of
+src/models/transformer/serving/mod.rs:192-352) and what a failed step leaves behind."""
 import numpy as np
+import pytest
 
 from rustgrad_b200 import serving
 
-
-class FakeSnapshot:
-    def __init__(self, length, nbytes=1000):
-        self.length, self.bytes = length, nbytes
+VOCAB = 50
 
 
-def logits():
-    return np.zeros(10, dtype=np.float32)
+def next_token(history):
+    """The fake model: a pure function of everything its row holds."""
+    return (sum(history) * 7 + len(history) * 3 + 1) % VOCAB
+
+
+def fake_logits(history):
+    out = np.zeros(VOCAB, dtype=np.float32)
+    out[next_token(history)] = 1.0
+    return out
+
+
+def pick(logits, temperature, uniforms):
+    """Greedy, or Gumbel-max over the tape (serving/mod.rs:649-665)."""
+    if uniforms is None or temperature <= 0:
+        return int(np.argmax(logits))
+    u = np.maximum(uniforms.astype(np.float64), 1e-30)
+    return int(np.argmax(logits.astype(np.float64) / temperature - np.log(-np.log(u))))
+
+
+class FakeSession(serving.ServingBackend):
+    vocab, max_context = VOCAB, 64
+
+    def __init__(self, snapshot_bytes=1000):
+        self.rows, self.snapshots, self.next_handle = {}, {}, 1
+        self.snapshot_bytes = snapshot_bytes
+        self.calls = []
+        self.fail = {}            # verb -> status to return once
+
+    def _failing(self, verb):
+        return self.fail.pop(verb, 0)
+
+    def reset_row(self, row):
+        self.calls.append(("reset", row))
+        self.rows[row] = []
+        return 0
+
+    def prefill_select(self, row, ids, temperature, uniforms, last_logits):
+        self.calls.append(("prefill", row, len(ids)))
+        rc = self._failing("prefill")
+        if rc:
+            return rc, -1
+        self.rows.setdefault(row, []).extend(ids)
+        last_logits[:] = fake_logits(self.rows[row])
+        return 0, pick(last_logits, temperature, uniforms)
+
+    def decode_rows(self, rows, tokens, temperatures, uniforms):
+        self.calls.append(("decode", tuple(rows)))
+        rc = self._failing("decode")
+        if rc:
+            return rc, []
+        out = []
+        for i, (row, tok) in enumerate(zip(rows, tokens)):
+            self.rows[row].append(tok)
+            out.append(pick(fake_logits(self.rows[row]), temperatures[i], None if uniforms is None else uniforms[i]))
+        return 0, out
+
+    def select(self, logits, temperature, uniforms):
+        self.calls.append(("select",))
+        return 0, pick(logits, temperature, uniforms)
+
+    def snapshot_create(self, row, length):
+        h = self.next_handle
+        self.next_handle += 1
+        self.snapshots[h] = list(self.rows[row][:length])
+        return 0, h, self.snapshot_bytes
+
+    def snapshot_restore(self, handle, row):
+        self.calls.append(("restore", row, len(self.snapshots[handle])))
+        self.rows[row] = list(self.snapshots[handle])
+        return 0
+
+    def snapshot_free(self, handle):
+        del self.snapshots[handle]
+
+
+def alone(prompt, n, stop=()):
+    history, out = list(prompt), []
+    for _ in range(n):
+        out.append(next_token(history))
+        history.append(out[-1])
+        if out[-1] in stop:
+            break
+    return out
+
+
+def run_all(sched, limit=200):
+    steps = []
+    while sched.pending() and len(steps) < limit:
+        steps.append(sched.step())
+    assert sched.pending() == 0
+    return steps
 
 
 def entry_bytes(tokens, nbytes=1000):
-    return nbytes + 10 * 4 + len(tokens) * 4
+    return nbytes + VOCAB * 4 + len(tokens) * 4
 
 
-def test_longest_prefix_wins_and_counts_hits_and_misses():
-    c = serving._PrefixCache(8, 1 << 20)
-    assert c.longest([1, 2, 3]) is None and c.stats()["misses"] == 1
-    assert c.insert([1, 2], FakeSnapshot(2), logits()) and c.insert([1, 2, 3, 4], FakeSnapshot(4), logits())
-    assert c.insert([9], FakeSnapshot(1), logits())
-    key, snap, _ = c.longest([1, 2, 3, 4, 5])
-    assert key == (1, 2, 3, 4) and snap.length == 4
-    key, snap, _ = c.longest([1, 2, 7])
-    assert key == (1, 2)
-    assert c.longest([2, 1]) is None
-    st = c.stats()
+def test_arrival_order_batch_size_and_row_reuse():
+    fake = FakeSession()
+    sched = serving.LlamaServingScheduler(fake, batch_size=2, max_rows=3)
+    prompts = [[1, 2, 3], [4, 5], [6], [7, 8, 9, 10]]
+    lengths = [3, 5, 2, 4]
+    ids = [sched.submit_ids(p, serving.GenerationConfig(n)) for p, n in zip(prompts, lengths)]
+    assert [sched.status(i) for i in ids] == ["queued"] * 4
+    first = sched.step()
+    assert [(e.request_id, e.arrival_order, e.generation_step) for e in first] == [(ids[0], 0, 0), (ids[1], 1, 0)]
+    assert [sched.status(i) for i in ids] == ["running", "running", "queued", "queued"]
+    assert [c for c in fake.calls if c[0] == "prefill"] == [("prefill", 0, 3), ("prefill", 1, 2)]
+    second = sched.step()
+    assert ("decode", (0, 1)) in fake.calls and [e.generation_step for e in second] == [1, 1]
+    run_all(sched)
+    for i, p, n in zip(ids, prompts, lengths):
+        r = sched.result(i)
+        assert (r.generated_ids, r.prompt_ids, r.stopped, r.decoded) == (alone(p, n), p, False, "")
+    assert [r.request_id for r in sched.completed_results()] == ids
+    # the third request got the row the first one handed back; no request ever saw row 2
+    assert {c[1] for c in fake.calls if c[0] == "prefill"} == {0, 1}
+    assert sched.step() == []
+
+
+def test_one_decode_launch_sequence_per_step_and_late_arrivals_wait():
+    fake = FakeSession()
+    sched = serving.LlamaServingScheduler(fake, batch_size=3)
+    a = sched.submit_ids([1], serving.GenerationConfig(4))
+    sched.step()
+    b = sched.submit_ids([2], serving.GenerationConfig(4))
+    fake.calls.clear()
+    events = sched.step()      # one running row decodes, one new prompt is prefilled
+    assert [e.request_id for e in events] == [a, b]
+    assert [c[0] for c in fake.calls] == ["prefill", "decode"] and fake.calls[1] == ("decode", (0,))
+    fake.calls.clear()
+    sched.step()
+    assert fake.calls == [("decode", (0, 1))]
+
+
+def test_stop_ids_end_a_request_and_the_stop_token_is_reported():
+    p = [3, 1, 4]
+    want = alone(p, 8)
+    stop = want[3]
+    fake = FakeSession()
+    sched = serving.LlamaServingScheduler(fake, batch_size=1, stop_ids=[stop, 49])
+    rid = sched.submit_ids(p, serving.GenerationConfig(8))
+    events = [e for step in run_all(sched) for e in step]
+    r = sched.result(rid)
+    assert r.generated_ids == want[: want.index(stop) + 1] and r.stopped
+    assert (events[-1].stopped, events[-1].complete, events[-1].token_id) == (True, True, stop)
+    assert not any(e.complete for e in events[:-1])
+
+
+def test_admission_checks_come_before_an_id_is_given():
+    fake = FakeSession()
+    sched = serving.LlamaServingScheduler(fake, batch_size=1)
+    cases = [([], 1, None, "EmptyPrompt", None), ([VOCAB], 1, None, "TokenOutOfRange", (VOCAB, VOCAB)),
+             ([-1], 1, None, "TokenOutOfRange", (-1, VOCAB)), ([1] * 60, 5, None, "ContextLength", (65, 64)),
+             ([1], 2, serving.Sampling(0.0, np.zeros((2, VOCAB), np.float32)), "InvalidTemperature", None),
+             ([1], 2, serving.Sampling(float("nan"), np.zeros((2, VOCAB), np.float32)), "InvalidTemperature", None),
+             ([1], 2, serving.Sampling(1.0, np.zeros(3, np.float32)), "UniformTapeLength", (2 * VOCAB, 3)),
+             ([1], 2, serving.Sampling(1.0, None), "UniformTapeLength", (2 * VOCAB, 0)),
+             ([1], 1, serving.Sampling(1.0, np.ones(VOCAB, np.float32)), "InvalidUniform", (0, 0))]
+    for prompt, n, sampling, kind, numbers in cases:
+        with pytest.raises(serving.ServingError) as e:
+            sched.submit_ids(prompt, serving.GenerationConfig(n, sampling or serving.Sampling()))
+        assert e.value.kind == kind
+        if numbers:
+            assert (e.value.value, e.value.value2) == numbers
+    bad = np.zeros((1, VOCAB), np.float32)
+    bad[0, 17] = -0.5
+    with pytest.raises(serving.ServingError) as e:
+        sched.submit_ids([1], serving.GenerationConfig(1, serving.Sampling(1.0, bad)))
+    assert (e.value.kind, e.value.value) == ("InvalidUniform", 17)
+    assert sched.submit_ids([1], serving.GenerationConfig(1)) == 0      # no id was spent on the rejected ones
+    z = sched.submit_ids([1], serving.GenerationConfig(0))
+    assert sched.status(z) == "complete" and sched.result(z).generated_ids == []
+    for kw in (dict(batch_size=0), dict(batch_size=3, max_rows=2)):
+        with pytest.raises(serving.ServingError) as e:
+            serving.LlamaServingScheduler(fake, **kw)
+        assert e.value.kind == "EmptyBatch"
+    with pytest.raises(serving.ServingError):       # text needs a tokenizer
+        sched.submit_text("hello", serving.GenerationConfig(1))
+
+
+def test_gumbel_tape_rows_follow_the_generation_step():
+    rng = np.random.default_rng(3)
+    tape = rng.random((4, VOCAB), dtype=np.float32)
+    history, want = [5, 6], []
+    for step in range(4):
+        want.append(pick(fake_logits(history), 0.8, tape[step]))
+        history.append(want[-1])
+    assert want != alone([5, 6], 4)
+    fake = FakeSession()
+    sched = serving.LlamaServingScheduler(fake, batch_size=2)
+    g = sched.submit_ids([9], serving.GenerationConfig(4))
+    s = sched.submit_ids([5, 6], serving.GenerationConfig(4, serving.Sampling(0.8, tape)))
+    run_all(sched)
+    assert sched.result(s).generated_ids == want and sched.result(g).generated_ids == alone([9], 4)
+
+
+def test_remove_frees_the_row_and_unknown_ids_are_reported():
+    fake = FakeSession()
+    sched = serving.LlamaServingScheduler(fake, batch_size=1)
+    a = sched.submit_ids([1, 2], serving.GenerationConfig(5))
+    b = sched.submit_ids([3], serving.GenerationConfig(2))
+    sched.step()
+    assert sched.result(a) is None                  # not complete yet
+    assert sched.remove(a) and not sched.remove(a) and sched.status(a) is None
+    assert ("reset", 0) in fake.calls
+    run_all(sched)
+    assert sched.result(b).generated_ids == alone([3], 2) and sched.pending() == 0
+
+
+def test_prefix_cache_longest_match_extension_and_full_hit():
+    fake = FakeSession()
+    sched = serving.LlamaServingScheduler(fake, batch_size=1, prefix_max_entries=8, prefix_max_bytes=1 << 20)
+    base, longer = [1, 2, 3, 4], [1, 2, 3, 4, 5, 6]
+    a = sched.submit_ids(base, serving.GenerationConfig(3))
+    run_all(sched)
+    st = sched.prefix_stats()
+    assert (st["entries"], st["hits"], st["misses"], st["bytes"]) == (1, 0, 1, entry_bytes(base))
+    fake.calls.clear()
+    b = sched.submit_ids(base, serving.GenerationConfig(1))      # the whole prompt is cached: selection only
+    run_all(sched)
+    assert [c[0] for c in fake.calls if c[0] != "reset"] == ["restore", "select"]
+    fake.calls.clear()
+    c = sched.submit_ids(longer, serving.GenerationConfig(3))    # four cached positions, two prefilled
+    run_all(sched)
+    assert ("restore", 0, 4) in fake.calls and ("prefill", 0, 2) in fake.calls
+    d = sched.submit_ids([1, 2, 9], serving.GenerationConfig(2))  # shares two tokens with an entry but no whole entry
+    run_all(sched)
+    assert sched.result(a).generated_ids == alone(base, 3) and sched.result(b).generated_ids == alone(base, 1)
+    assert sched.result(c).generated_ids == alone(longer, 3) and sched.result(d).generated_ids == alone([1, 2, 9], 2)
+    st = sched.prefix_stats()
     assert (st["entries"], st["hits"], st["misses"]) == (3, 2, 2)
-    assert st["bytes"] == entry_bytes([1, 2]) + entry_bytes([1, 2, 3, 4]) + entry_bytes([9])
+    assert st["bytes"] == entry_bytes(base) + entry_bytes(longer) + entry_bytes([1, 2, 9])
 
 
-def test_eviction_is_least_recently_used_and_spares_referenced_entries():
-    c = serving._PrefixCache(2, 1 << 20)
-    c.insert([1], FakeSnapshot(1), logits())
-    c.insert([2], FakeSnapshot(1), logits())
-    c.longest([1, 5])                      # touches and leases [1]
-    assert c.insert([3], FakeSnapshot(1), logits())
-    assert set(c.entries) == {(1,), (3,)} and c.stats()["evictions"] == 1   # [2] was the oldest unreferenced
-    c.longest([3, 5])                      # both entries leased now
-    assert not c.insert([4], FakeSnapshot(1), logits())                    # nothing may be evicted
-    c.release((1,))
-    assert c.insert([4], FakeSnapshot(1), logits()) and set(c.entries) == {(3,), (4,)}
-    # re-inserting a key replaces it without eviction
-    before = c.stats()["evictions"]
-    assert c.insert([4], FakeSnapshot(1, 500), logits()) and c.stats()["evictions"] == before
-    assert c.stats()["bytes"] == entry_bytes([3]) + entry_bytes([4], 500)
+def test_prefix_cache_evicts_least_recently_used_under_both_budgets():
+    fake = FakeSession()
+    sched = serving.LlamaServingScheduler(fake, batch_size=1, prefix_max_entries=2, prefix_max_bytes=1 << 20)
+    for p in ([1], [2]):
+        sched.submit_ids(p, serving.GenerationConfig(1))
+    run_all(sched)
+    sched.submit_ids([1, 5], serving.GenerationConfig(1))        # touches [1]; its own entry evicts [2], the oldest
+    run_all(sched)
+    st = sched.prefix_stats()
+    assert (st["entries"], st["evictions"]) == (2, 1)
+    assert sorted(len(v) for v in fake.snapshots.values()) == [1, 2] and [1] in fake.snapshots.values()
+    sched.submit_ids([2], serving.GenerationConfig(1))           # [2] is gone: a miss
+    run_all(sched)
+    assert sched.prefix_stats()["misses"] == 3
+    # re-inserting a key replaces it without an eviction
+    before = sched.prefix_stats()
+    sched.invalidate_prefix_cache()
+    assert fake.snapshots == {}                                   # device copies are released with their entries
+    st = sched.prefix_stats()
+    assert (st["entries"], st["bytes"], st["generation"]) == (0, 0, before["generation"] + 1)
+    # byte budget: room for one entry only, and an entry larger than the whole budget is not kept
+    small = serving.LlamaServingScheduler(FakeSession(), batch_size=1, prefix_max_entries=8, prefix_max_bytes=1500)
+    for p in ([1], [2]):
+        small.submit_ids(p, serving.GenerationConfig(1))
+    run_all(small)
+    st = small.prefix_stats()
+    assert (st["entries"], st["evictions"], st["bytes"]) == (1, 1, entry_bytes([2]))
+    none = serving.LlamaServingScheduler(FakeSession(snapshot_bytes=4000), batch_size=1, prefix_max_entries=8, prefix_max_bytes=1500)
+    none.submit_ids([1], serving.GenerationConfig(1))
+    run_all(none)
+    assert none.prefix_stats()["entries"] == 0
+    off = serving.LlamaServingScheduler(FakeSession(), batch_size=1, prefix_max_entries=0, prefix_max_bytes=1 << 20)
+    off.submit_ids([1], serving.GenerationConfig(1))
+    run_all(off)
+    assert off.prefix_stats()["entries"] == 0 and off.session.snapshots == {}
 
 
-def test_budgets_and_invalidation():
-    assert not serving._PrefixCache(0, 1 << 20).insert([1], FakeSnapshot(1), logits())
-    assert not serving._PrefixCache(4, 0).insert([1], FakeSnapshot(1), logits())
-    c = serving._PrefixCache(4, 1500)
-    assert not c.insert([1], FakeSnapshot(1, 2000), logits())              # larger than the whole budget
-    assert c.insert([1], FakeSnapshot(1), logits())
-    assert c.insert([2], FakeSnapshot(1), logits()) and set(c.entries) == {(2,)}  # byte budget evicts
-    c.invalidate()
-    st = c.stats()
-    assert (st["entries"], st["bytes"], st["generation"]) == (0, 0, 1)
-    c.entries[(7,)] = serving._Entry(0, FakeSnapshot(1), logits(), 10, 0)  # an entry of the old generation
-    c.bytes = 10
-    assert c.longest([7, 8]) is None
-    st = c.stats()
-    assert (st["stale_rejections"], st["entries"], st["bytes"]) == (1, 0, 0)
+def test_a_failed_step_can_be_run_again_as_a_whole():
+    fake = FakeSession()
+    sched = serving.LlamaServingScheduler(fake, batch_size=2)
+    a = sched.submit_ids([1, 2], serving.GenerationConfig(4))
+    sched.step()
+    b = sched.submit_ids([3, 4, 5], serving.GenerationConfig(3))
+    fake.fail["decode"] = 9                                       # the decode launch of this step fails
+    with pytest.raises(serving.ServingError) as e:
+        sched.step()
+    assert (e.value.kind, e.value.value) == ("Session", 9)
+    assert sched.status(a) == "running" and sched.status(b) == "queued"   # b was un-admitted, its row reset
+    assert fake.rows[1] == []
+    fake.fail["prefill"] = 12
+    with pytest.raises(serving.ServingError) as e:
+        sched.step()
+    assert e.value.value == 12 and sched.status(b) == "queued"
+    run_all(sched)
+    assert sched.result(a).generated_ids == alone([1, 2], 4) and sched.result(b).generated_ids == alone([3, 4, 5], 3)
