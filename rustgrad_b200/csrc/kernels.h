@@ -90,6 +90,11 @@ struct GemvI8Args {
   uint8_t *pack_out = nullptr;
   const float *pack_w = nullptr;
   int pack_type = 0;
+  // Weights the NEXT kernel of the step will stream (up to three tensors, 16-byte aligned): once this
+  // launch has issued its own loads its producer warps ask L2 for them, so that the next kernel's
+  // first stages are L2 hits instead of a cold start of the HBM stream.
+  const uint8_t *next_w[3] = {nullptr, nullptr, nullptr};
+  size_t next_bytes[3] = {0, 0, 0};
 };
 bool qgemv_i8_supported(int k, int batch);
 size_t qgemv_i8_xq_bytes(int k);

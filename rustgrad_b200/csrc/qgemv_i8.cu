@@ -103,7 +103,11 @@ struct Params {
   uint8_t *pack_out;    // EPI_RESIDUAL / EPI_SWIGLU, batch 1: also write the new rows packed for the next GEMV
   const float *pack_w;  // norm weight folded into the packed output (nullable)
   int pack_q4;          // block type of the GEMV that will read pack_out: 1 Q4_0, 0 Q8_0
+  const uint8_t *pf[3];   // weights of the next kernel, asked into L2 once this CTA's own loads are issued
+  uint32_t pf_bytes[3];
 };
+
+constexpr uint32_t PF_CHUNK = 8192;  // bytes per L2 prefetch request
 
 // (layout of a packed activation vector in global memory: xq_side_offset / xq_ssq_offset in rg_device.cuh)
 
@@ -461,6 +465,15 @@ __global__ void __launch_bounds__(THREADS, 1)
         ++round;
       }
     }
+    if (lane == 0) trace_stamp(P.trace, 7, tr_first, tr_last);  // every load of this CTA issued
+    // every load of this CTA is issued: spend the rest of the kernel asking L2 for the next kernel's
+    // weights (constant data; a hint that nothing waits for), one slice per CTA
+#pragma unroll 1
+    for (int i = 0; i < 3; ++i) {
+      const uint32_t total = P.pf_bytes[i];
+      for (uint32_t off = (blockIdx.x * 32u + (uint32_t)lane) * PF_CHUNK; off < total; off += gridDim.x * 32u * PF_CHUNK)
+        l2_prefetch_bulk(P.pf[i] + off, min(PF_CHUNK, total - off));
+    }
     return;
   }
 
@@ -730,6 +743,7 @@ __global__ void __launch_bounds__(THREADS, 1)
   for (int u = 0; u < units; ++u) {
     const int nb = min(G::KC, P.kb - c * G::KC);
     mbar_wait_bounded(&full[stage], phase, dead, P.status);
+    if (u == 0 && ctid == 0) trace_stamp(P.trace, 6, tr_first, tr_last);  // first weight stage landed
     const uint32_t sw = smem_stage0 + (uint32_t)stage * (uint32_t)STAGE_BYTES;
     uint32_t aw = sw + lane_w_off + (uint32_t)warp * PAIRB;
     uint32_t as = sw + lane_s_off + (uint32_t)warp * PAIRB;
@@ -918,6 +932,11 @@ cudaError_t launch_t(const GemvI8Args &a, const LaunchCfg &cfg) {
   P.pack_q4 = a.pack_type == RG_TYPE_Q4_0 ? 1 : 0;
   P.xq_fix = a.xq_fix;
   P.xq_nfix = a.xq_fix ? a.xq_nfix : 0;
+  for (int i = 0; i < 3; ++i) {
+    const bool ok = a.next_w[i] && (reinterpret_cast<uintptr_t>(a.next_w[i]) & 15) == 0;
+    P.pf[i] = ok ? a.next_w[i] : nullptr;
+    P.pf_bytes[i] = ok ? (uint32_t)(a.next_bytes[i] > 0xFFFFFFF0u ? 0xFFFFFFF0u : a.next_bytes[i]) & ~15u : 0u;
+  }
   P.rows_per_cta = qgemv_i8_rows_per_cta(P.n_rows, cfg.sm_count, EPI == EPI_RESIDUAL && a.pack_out != nullptr);
   const int grid = (P.n_rows + P.rows_per_cta - 1) / P.rows_per_cta;
   const int S = 4 * a.batch;

@@ -30,6 +30,12 @@ __device__ __forceinline__ bool finite_f32(float v) { return fabsf(v) <= 3.40282
 // touches memory another kernel of the step writes, so completion stays transitive along the
 // chain; constant weights may be prefetched before it.
 // ---------------------------------------------------------------------------------------------
+// Hint that [p, p + bytes) will be read soon: the lines are brought into L2 and nothing waits for
+// them.  p and bytes are multiples of 16.
+__device__ __forceinline__ void l2_prefetch_bulk(const void *p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -13,6 +13,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <atomic>
 #include <map>
 #include <memory>
@@ -507,7 +508,20 @@ struct PackedIo {
   uint8_t *pack_out = nullptr;
   const float *pack_w = nullptr;
   int pack_type = 0;
+  // the packed tensors the next GEMV of the step streams (asked into L2 by this launch)
+  const DevTensor *const *next_w = nullptr;
+  int next_n = 0;
+  int next_lead = 0;  // the first next_lead tensors are read before the others
 };
+
+// How much of the next kernel's weights a GEMV launch asks into L2 (all tensors together).
+static size_t l2_prefetch_budget() {
+  static const size_t bytes = [] {
+    const char *e = getenv("RG_B200_L2_PREFETCH_MB");
+    return (size_t)(e ? atoi(e) : 40) << 20;
+  }();
+  return bytes;
+}
 
 static int32_t gemv_i8(rg_session *s, const DevTensor *const *w, int n, const float *x, int ldx, const int32_t *col_map,
                        const float *norm_w, int batch, int epi, float *y, int ldy, const LaunchCfg &L,
@@ -520,6 +534,22 @@ static int32_t gemv_i8(rg_session *s, const DevTensor *const *w, int n, const fl
   a.pack_out = io.pack_out;
   a.pack_w = io.pack_w;
   a.pack_type = io.pack_type;
+  {
+    // split the budget over the tensors in proportion (gate and up are consumed side by side)
+    size_t budget = l2_prefetch_budget(), total = 0;
+    for (int i = 0; i < io.next_n && i < 3; ++i) {
+      if (!io.next_w[i]->packed()) continue;
+      a.next_w[i] = io.next_w[i]->d;
+      if (i < io.next_lead) {  // read first: taken whole as far as the budget goes
+        a.next_bytes[i] = std::min(io.next_w[i]->nbytes, budget);
+        budget -= a.next_bytes[i];
+      } else {
+        total += io.next_w[i]->nbytes;
+      }
+    }
+    for (int i = io.next_lead; i < io.next_n && i < 3; ++i)
+      if (a.next_w[i]) a.next_bytes[i] = total <= budget ? io.next_w[i]->nbytes : (size_t)((double)io.next_w[i]->nbytes * budget / total);
+  }
   a.type = w[0]->type;
   a.nseg = n;
   for (int i = 0; i < n; ++i) {
@@ -572,8 +602,25 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
   for (int l = 0; l < c.n_layers; ++l) {
     const LayerW &W = s->layers[(size_t)l];
     const DevTensor *qkvw[3] = {&W.q, &W.k, &W.v};
+    const DevTensor *ow[1] = {&W.o};
+    const DevTensor *guw[2] = {&W.gate, &W.up};
+    const DevTensor *dw[1] = {&W.down};
+    const DevTensor *hw_next[1] = {s->head};
+    const DevTensor *qkv_next[3] = {nullptr, nullptr, nullptr};
+    if (l + 1 < c.n_layers) {
+      const LayerW &N = s->layers[(size_t)l + 1];
+      qkv_next[0] = &N.q;
+      qkv_next[1] = &N.k;
+      qkv_next[2] = &N.v;
+    }
     PackedIo qkv_io;
     qkv_io.site = SITE_QKV;
+    // the attention launch between this projection and the next reads little: ask for the output
+    // projection and, with what is left of the budget, the start of gate / up
+    const DevTensor *after_qkv[3] = {&W.o, &W.gate, &W.up};
+    qkv_io.next_w = after_qkv;
+    qkv_io.next_n = env_flag("RG_B200_PF_QKV_O_ONLY") ? 1 : 3;
+    qkv_io.next_lead = 1;
     if (pre && l > 0) {  // layer 0 reads the embedding row, which nothing packed
       qkv_io.xq = s->xq_x;
       qkv_io.xq_norm = true;
@@ -649,9 +696,10 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
       RG_LAUNCH(s, launch_attention(aa, L));
       if (s->family_mask & (1u << PROF_ATTN)) s->launches_in_step++;  // split + combine
     }
-    const DevTensor *ow[1] = {&W.o};
     PackedIo o_in;
     o_in.site = SITE_O;
+    o_in.next_w = guw;
+    o_in.next_n = 2;
     if (pre_attn) o_in.xq = s->xq_attn;
     if (tp) {
       if ((rc = gemv_i8(s, ow, 1, s->attn_f32, qw, nullptr, nullptr, ncols, EPI_STORE, s->tp_part[0], d, L, o_in))) return rc;
@@ -665,15 +713,23 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
       }
       if ((rc = gemv_i8(s, ow, 1, s->attn_f32, qw, nullptr, nullptr, ncols, EPI_RESIDUAL, s->x, d, L, io))) return rc;
     }
-    const DevTensor *guw[2] = {&W.gate, &W.up};
     PackedIo gu_io;
     gu_io.site = SITE_GATE_UP;
+    gu_io.next_w = dw;
+    gu_io.next_n = 1;
     if (pre) {
       gu_io.xq = s->xq_x;
       gu_io.xq_norm = true;
     }
     PackedIo down_in;  // the SwiGLU epilogue packs the blocks that lie inside one of its CTAs, the down projection the rest
     down_in.site = SITE_DOWN;
+    if (l + 1 < c.n_layers) {
+      down_in.next_w = qkv_next;
+      down_in.next_n = 3;
+    } else if (n_logit_cols > 0) {
+      down_in.next_w = hw_next;
+      down_in.next_n = 1;
+    }
     if (pre_attn && s->xq_h) {
       gu_io.pack_out = s->xq_h;
       gu_io.pack_type = W.down.type;
@@ -684,7 +740,6 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
     if ((rc = gemv_i8(s, guw, 2, s->x, d, nullptr, reinterpret_cast<const float *>(W.ffn_norm.d), ncols, EPI_SWIGLU, s->h_f32,
                       s->ffn_l, tp_lib ? plain : L, gu_io)))
       return rc;
-    const DevTensor *dw[1] = {&W.down};
     if (tp) {
       if ((rc = gemv_i8(s, dw, 1, s->h_f32, s->ffn_l, nullptr, nullptr, ncols, EPI_STORE, s->tp_part[1], d, L, down_in))) return rc;
       if ((rc = tp_reduce_add(s, ncols, 1))) return rc;
