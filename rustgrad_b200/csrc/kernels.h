@@ -158,6 +158,12 @@ struct TpFusedArgs {
   unsigned *epochs = nullptr;             // local, [2][TP_FUSED_CTAS], zero at start
   int rank = 0, world = 1, buffer = 0;
   unsigned poll_limit = 1u << 22;  // polls of a flag word before the wait gives up with DEV_TIMEOUT
+  // One column, n a multiple of 32: besides x, write the new residual row packed as the input of the
+  // integer GEMV that reads it next (block type pack_type, norm weight pack_w folded in, per-block
+  // sums of squares for the deferred RMSNorm): that GEMV's prologue is then a single bulk copy.
+  uint8_t *pack_out = nullptr;
+  const float *pack_w = nullptr;
+  int pack_type = 0;
 };
 cudaError_t launch_tp_allreduce_add(const TpFusedArgs &a, const LaunchCfg &cfg);
 

@@ -195,4 +195,42 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// One 32-element block of a packed activation vector (rg_device.cuh), lane = element: block fixed point
+// of `val`, digits, side words, and (ssq_out) the sum of squares `ssq` the caller reduced.  All 32 lanes call.
+__device__ __forceinline__ void pack_block_warp(float val, bool q4, uint8_t *xq, int kbo, int kb_all, int lane, bool ssq_out,
+                                                float ssq) {
+  float m = warp_max(fabsf(val));
+  if (__any_sync(0xffffffffu, !(fabsf(val) <= 3.0e38f))) m = __uint_as_float(0x7f800000u);  // keep NaN / inf visible
+  const uint32_t E = __float_as_uint(m) >> 23;
+  const uint32_t XBITS = q4 ? 25u : 29u;
+  float s = 0.0f;
+  int X = 0;
+  if (E >= 40u && E < 255u) {
+    s = __uint_as_float((E - XBITS) << 23);
+    X = __float2int_rn(val * __uint_as_float((254u + XBITS - E) << 23));
+  } else if (E == 255u) {
+    s = __uint_as_float(0x7fc00000u);
+    X = lane == 0 ? 1 : 0;
+  }
+  int t_lo = 0, t_hi = 0;
+  if (q4) {
+    int sum = X;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    t_lo = (sum & 0x1FF) << 7;
+    t_hi = sum >> 9;
+    const int partner = __shfl_xor_sync(0xffffffffu, X, 16);
+    X = lane < 16 ? X << 4 : X - (partner << 4);
+  }
+  const uint32_t Y = (uint32_t)X + 0x80808080u;
+  uint8_t *dst = xq + (size_t)kbo * 128 + ((lane & 15) >> 2) * 8 + (lane >> 4) * 4 + (lane & 3);
+#pragma unroll
+  for (int d = 0; d < 4; ++d) dst[d * 32] = (uint8_t)(((Y >> (8 * d)) & 0xFFu) ^ 0x80u);
+  if (lane == 0) {
+    *reinterpret_cast<float4 *>(xq + xq_side_offset(kb_all) + (size_t)kbo * 16) =
+        make_float4(s, __int_as_float(t_lo), s, __int_as_float(t_hi));
+    if (ssq_out) reinterpret_cast<float *>(xq + xq_ssq_offset(kb_all))[kbo] = ssq;
+  }
+}
+
 }  // namespace rg

@@ -440,7 +440,9 @@ static int32_t linear(rg_session *s, const DevTensor *const *w, int n, const voi
 
 // x += sum over ranks of the partial projection in buffer `which` (0: output projection, 1: down
 // projection).  Fused form: one kernel over NVLink peer memory; otherwise NCCL all-reduce + add.
-static int32_t tp_reduce_add(rg_session *s, int ncols, int which) {
+// pack_*: also leave the new residual row packed for the GEMV that reads it next (one column, peer-memory exchange only)
+static int32_t tp_reduce_add(rg_session *s, int ncols, int which, uint8_t *pack_out = nullptr, const float *pack_w = nullptr,
+                             int pack_type = 0) {
   const int d = s->cfg.d_model;
   std::string err;
   prof_mark(s, PROF_OTHER);
@@ -461,6 +463,9 @@ static int32_t tp_reduce_add(rg_session *s, int ncols, int which) {
     a.rank = s->tp_rank;
     a.world = s->tp_world;
     a.buffer = which;
+    a.pack_out = pack_out;
+    a.pack_w = pack_w;
+    a.pack_type = pack_type;
     RG_LAUNCH(s, launch_tp_allreduce_add(a, lcfg(s)));
     s->report.peer_reduce_launches++;
     return RG_OK;
@@ -593,7 +598,8 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
   // stream packed, with the next norm weight folded in, for the projection that reads it, whose
   // prologue is then a single bulk copy; the norm's scalar factor is applied to that projection's results.
   s->trace_next = 0;
-  const bool pre = ncols == 1 && !tp && s->xq_x && !env_flag("RG_B200_NO_PREPACK");
+  // (under tensor parallelism the peer-memory exchange kernel, which adds the residual, is that producer)
+  const bool pre = ncols == 1 && (!tp || s->tp_fused) && s->xq_x && !env_flag("RG_B200_NO_PREPACK");
   // likewise the one-launch attention packs its output for the output projection (any world size:
   // the heads are rank-local)
   const bool pre_attn = ncols == 1 && s->xq_attn && s->attn_counters && !env_flag("RG_B200_NO_PREPACK");
@@ -703,7 +709,8 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
     if (pre_attn) o_in.xq = s->xq_attn;
     if (tp) {
       if ((rc = gemv_i8(s, ow, 1, s->attn_f32, qw, nullptr, nullptr, ncols, EPI_STORE, s->tp_part[0], d, L, o_in))) return rc;
-      if ((rc = tp_reduce_add(s, ncols, 0))) return rc;
+      if ((rc = tp_reduce_add(s, ncols, 0, pre ? s->xq_x : nullptr, reinterpret_cast<const float *>(W.ffn_norm.d), W.gate.type)))
+        return rc;
     } else {
       PackedIo io = o_in;
       if (pre) {
@@ -742,7 +749,11 @@ static int32_t forward_small(rg_session *s, int ncols, int n_logit_cols, bool ad
       return rc;
     if (tp) {
       if ((rc = gemv_i8(s, dw, 1, s->h_f32, s->ffn_l, nullptr, nullptr, ncols, EPI_STORE, s->tp_part[1], d, L, down_in))) return rc;
-      if ((rc = tp_reduce_add(s, ncols, 1))) return rc;
+      const bool last = l + 1 == c.n_layers;
+      if ((rc = tp_reduce_add(s, ncols, 1, pre ? s->xq_x : nullptr,
+                              reinterpret_cast<const float *>(last ? s->output_norm.d : s->layers[(size_t)l + 1].attn_norm.d),
+                              last ? s->head->type : s->layers[(size_t)l + 1].q.type)))
+        return rc;
     } else {
       PackedIo io = down_in;
       if (pre) {  // read next by the following layer's q/k/v projection, or by the head after the last layer

@@ -16,6 +16,9 @@
 // exchange of a layer knows that every rank has finished reading the first buffer, so it may be
 // overwritten by the next layer.  No NCCL call, no separate add kernel; the kernel is an ordinary
 // launch and is captured in the decode graph like the others.
+#include <stdint.h>
+
+#include "../../include/rg_b200.h"
 #include "kernels.h"
 #include "rg_device.cuh"
 
@@ -27,6 +30,11 @@ constexpr int THREADS = 256;
 __device__ __forceinline__ float4 ld_peer(const float4 *p) {
   float4 v;
   asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_peer1(const float *p) {
+  float v;
+  asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
   return v;
 }
 __device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
@@ -69,6 +77,44 @@ __global__ void __launch_bounds__(THREADS) tp_allreduce_add_kernel(const TpFused
   }
   __syncthreads();
   if (s_dead) return;  // a rank never arrived: leave x untouched, the host sees the status
+  if (A.pack_out) {
+    // one column: a warp owns whole 32-element blocks (lane = element), so that it can also leave the
+    // row packed for the next integer GEMV, the same way a residual epilogue on one GPU does
+    const int warp = tid >> 5, lane = tid & 31, nblk = A.n >> 5;
+    const bool q4 = A.pack_type == RG_TYPE_Q4_0;
+    // every block of this warp is requested from every rank before the first sum: one NVLink round
+    // trip for the whole exchange
+    constexpr int STRIDE = TP_FUSED_CTAS * (THREADS / 32), UB = 4;
+    for (int kb0 = b * (THREADS / 32) + warp; kb0 < nblk; kb0 += UB * STRIDE) {
+      float p[UB][TP_FUSED_MAX_WORLD], resid[UB], w[UB];
+#pragma unroll
+      for (int u = 0; u < UB; ++u) {
+        const int e = (kb0 + u * STRIDE) * 32 + lane;
+        if (kb0 + u * STRIDE < nblk) {
+#pragma unroll
+          for (int r = 0; r < TP_FUSED_MAX_WORLD; ++r)
+            if (r < A.world) p[u][r] = ld_peer1(A.peer_partial[r] + e);
+          resid[u] = A.x[e];
+          w[u] = A.pack_w ? __ldg(A.pack_w + e) : 1.0f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UB; ++u) {
+        const int kb = kb0 + u * STRIDE;
+        if (kb < nblk) {
+          float sum = 0.0f;
+#pragma unroll
+          for (int r = 0; r < TP_FUSED_MAX_WORLD; ++r)
+            if (r < A.world) sum = __fadd_rn(sum, p[u][r]);  // rank order, as below
+          const float v = __fadd_rn(resid[u], sum);
+          A.x[kb * 32 + lane] = v;
+          const float ssq = warp_sum(__fmul_rn(v, v));
+          pack_block_warp(__fmul_rn(v, w[u]), q4, A.pack_out, kb, nblk, lane, true, ssq);
+        }
+      }
+    }
+    return;
+  }
   const int row4 = A.n / 4;
   const int total = A.cols * row4;
   for (int i = b * THREADS + tid; i < total; i += TP_FUSED_CTAS * THREADS) {
@@ -105,6 +151,9 @@ cudaError_t launch_tp_allreduce_add(const TpFusedArgs &a, const LaunchCfg &cfg) 
   count_launch(LC_TP_EXCHANGE);
   if (!a.x || !a.peer_partial || !a.peer_flags || !a.epochs || a.world < 2 || a.world > TP_FUSED_MAX_WORLD || a.n % 4 ||
       a.ldx % 4 || a.ldp % 4 || a.buffer < 0 || a.buffer > 1)
+    return cudaErrorInvalidValue;
+  if (a.pack_out && (a.cols != 1 || a.n % 32 || (reinterpret_cast<uintptr_t>(a.pack_out) & 127) ||
+                     (a.pack_type != RG_TYPE_Q4_0 && a.pack_type != RG_TYPE_Q8_0)))
     return cudaErrorInvalidValue;
   cudaLaunchConfig_t lc{};
   lc.gridDim = dim3(TP_FUSED_CTAS);
