@@ -136,6 +136,13 @@ uint64_t rg_b200_launch_count(const char *kernel);
  * written and whose poll limit is a few thousand polls.  The wait runs out, nothing faults or
  * hangs, and the session's next step returns RG_TIMEOUT and leaves the session poisoned. */
 int32_t rg_b200_test_expire_device_wait(rg_session *s);
+/* Development aid: with RG_B200_TRACE=1 in the environment at prepare, the kernels of a one- or
+ * two-column decode step stamp the global nanosecond timer at their phases (CTA started, grid
+ * dependency resolved, activations in shared memory, last weight stage consumed, first / last row
+ * group stored, first weight stage landed, all loads issued), first CTA in words 0-7 and last CTA in
+ * words 8-15 of each launch.  Copies the stamps of the last step (16 words per launch, launch order)
+ * and returns the number of launches copied; 0 when tracing is off. */
+int32_t rg_b200_debug_read_trace(rg_session *s, unsigned long long *out, int32_t max_launches);
 
 /* ---- GGUF container: replaces read_gguf / GgufFile (src/gguf/mod.rs:166-173,256-384,
  * src/gguf/reader.rs:8-301).  The bytes are borrowed and must outlive the handle. ---- */

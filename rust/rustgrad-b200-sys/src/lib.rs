@@ -3,7 +3,7 @@
 //!
 //! Every item mirrors a declaration of `include/rg_b200.h`, `include/rg_b200_tokenizer.h`,
 //! `include/rg_b200_workflow.h` or `include/rg_b200_serving.h`; the headers carry the documentation and, for each entry point, the
-//! rustgrad interface it stands in for.  All 92 exports are declared here.
+//! rustgrad interface it stands in for.  All 93 exports are declared here.
 #![allow(non_camel_case_types)]
 
 use core::ffi::{c_char, c_void};
@@ -285,6 +285,7 @@ unsafe extern "C" {
     pub fn rg_b200_test_fail_after(what: *const c_char, n: i32) -> i32;
     pub fn rg_b200_launch_count(kernel: *const c_char) -> u64;
     pub fn rg_b200_test_expire_device_wait(s: *mut rg_session) -> i32;
+    pub fn rg_b200_debug_read_trace(s: *mut rg_session, out: *mut u64, max_launches: i32) -> i32;
     pub fn rg_b200_gguf_open(bytes: *const u8, len: usize, out: *mut *mut rg_gguf) -> i32;
     pub fn rg_b200_gguf_close(g: *mut rg_gguf);
     pub fn rg_b200_gguf_tensor_count(g: *const rg_gguf) -> usize;

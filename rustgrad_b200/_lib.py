@@ -42,7 +42,7 @@ class Report(C.Structure):
 
 
 EXPORTS = [
-    "rg_b200_version", "rg_b200_status_string", "rg_b200_last_error", "rg_b200_test_fail_after", "rg_b200_test_expire_device_wait", "rg_b200_launch_count", "rg_b200_gguf_open",
+    "rg_b200_version", "rg_b200_status_string", "rg_b200_last_error", "rg_b200_test_fail_after", "rg_b200_test_expire_device_wait", "rg_b200_debug_read_trace", "rg_b200_launch_count", "rg_b200_gguf_open",
     "rg_b200_gguf_close", "rg_b200_gguf_tensor_count", "rg_b200_gguf_tensor_info", "rg_b200_gguf_llama_config",
     "rg_b200_plan_create", "rg_b200_plan_add_tensor", "rg_b200_plan_from_gguf", "rg_b200_plan_synth_tensor",
     "rg_b200_plan_tensor_nbytes", "rg_b200_plan_read_tensor", "rg_b200_plan_destroy", "rg_b200_session_prepare",
@@ -87,6 +87,7 @@ def load() -> C.CDLL:
     L.rg_b200_last_error.restype = C.c_char_p
     L.rg_b200_test_fail_after.argtypes = [C.c_char_p, C.c_int32]
     L.rg_b200_test_expire_device_wait.argtypes = [vp]
+    L.rg_b200_debug_read_trace.argtypes = [vp, C.POINTER(C.c_uint64), C.c_int32]
     L.rg_b200_launch_count.restype = C.c_uint64
     L.rg_b200_launch_count.argtypes = [C.c_char_p]
     L.rg_b200_gguf_open.argtypes = [u8p, C.c_size_t, C.POINTER(vp)]

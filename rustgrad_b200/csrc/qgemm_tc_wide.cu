@@ -1,5 +1,5 @@
 // Wide-tile variant of the tcgen05 GEMM for the single-operand modes (bf16 / f16) at more than 256 tokens:
-//   C[M][N] (f32) = X[M][K] (16-bit) * W[N][K]^T,  W in Q4_0 blocks  (BASELINE config 3).
+//   C[M][N] (f32) = X[M][K] (16-bit) * W[N][K]^T,  W in Q4_0 blocks  (the prefill GEMM workload: Q4_0 [14336,4096] and [4096,4096] weights, 128 to 2048 tokens).
 // One CTA computes 128 weight rows x 512 tokens: the dequantised A tile (K-major, 128-byte swizzle, in
 // SHARED memory) feeds two 256-column accumulators that together fill tensor memory, so each weight
 // block is expanded once per 512 tokens.  With all 512 TMEM columns taken by the accumulators the A

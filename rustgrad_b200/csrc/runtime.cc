@@ -2349,8 +2349,8 @@ int32_t rg_b200_decode_profile_projections(rg_session *s, const int32_t *first, 
   return decode_profile_impl(s, first, batch, steps, nullptr, nullptr, false, out_ms);
 }
 
-// Development aid, not part of the documented interface: copies the phase stamps of the last
-// small-batch step (RG_B200_TRACE=1 at prepare) to `out` (16 u64 per launch); returns the launch count.
+// Development aid: copies the phase stamps of the last small-batch step (RG_B200_TRACE=1 at prepare)
+// to `out` (16 u64 per launch); returns the launch count.
 int32_t rg_b200_debug_read_trace(rg_session *s, unsigned long long *out, int32_t max_launches) {
   if (!s || !out || !s->d_trace) return 0;
   cudaSetDevice(s->opt.device);
