@@ -192,6 +192,15 @@ int32_t rg_b200_reset_sequence(rg_session *s);
 /* prefill_ids (metal_generation.rs:913-1047): appends n prompt tokens to sequence `row`;
  * last_logits ([vocab], nullable) receives the logits of the final prompt token. */
 int32_t rg_b200_prefill(rg_session *s, int32_t row, const int32_t *ids, size_t n, float *last_logits);
+/* Several prompts in one pass: the batch prefill of LlamaBatchGenerator (src/models/transformer/
+ * batch.rs:177-325, batch_generation.rs:104-189) without its right padding.  Prompt i (lens[i] ids,
+ * the prompts laid end to end in `ids`) continues cache row rows[i] from that row's position; the
+ * rows must be distinct.  Chunks of up to 1024 columns are cut across the prompts, so short prompts
+ * share every weight tile.  last_logits (nullable) receives [n_rows, vocab], the logits after each
+ * prompt's last token; greedy (nullable) the token selected from them.  Everything is validated
+ * before any device work, and no row's position advances unless the whole call succeeded. */
+int32_t rg_b200_prefill_rows(rg_session *s, const int32_t *rows, const int32_t *ids, const size_t *lens, int32_t n_rows,
+                             float *last_logits, int32_t *greedy);
 /* run_token (metal_generation.rs:1123-1138) generalised to `batch` rows (batch.rs:140-162):
  * tokens[batch] in; logits [batch, vocab] and/or greedy ids [batch] out (either may be NULL).
  * Rows 0..batch-1 advance by one position only when the whole step succeeds. */

@@ -3,7 +3,7 @@
 //!
 //! Every item mirrors a declaration of `include/rg_b200.h`, `include/rg_b200_tokenizer.h`,
 //! `include/rg_b200_workflow.h` or `include/rg_b200_serving.h`; the headers carry the documentation and, for each entry point, the
-//! rustgrad interface it stands in for.  All 93 exports are declared here.
+//! rustgrad interface it stands in for.  All 94 exports are declared here.
 #![allow(non_camel_case_types)]
 
 use core::ffi::{c_char, c_void};
@@ -306,6 +306,7 @@ unsafe extern "C" {
     pub fn rg_b200_is_full(s: *const rg_session) -> i32;
     pub fn rg_b200_reset_sequence(s: *mut rg_session) -> i32;
     pub fn rg_b200_prefill(s: *mut rg_session, row: i32, ids: *const i32, n: usize, last_logits: *mut f32) -> i32;
+    pub fn rg_b200_prefill_rows(s: *mut rg_session, rows: *const i32, ids: *const i32, lens: *const usize, n_rows: i32, last_logits: *mut f32, greedy: *mut i32) -> i32;
     pub fn rg_b200_decode(s: *mut rg_session, tokens: *const i32, batch: i32, logits: *mut f32, greedy: *mut i32) -> i32;
     pub fn rg_b200_generate_greedy(s: *mut rg_session, prompt: *const i32, n_prompt: usize, max_new: usize, out: *mut i32, n_out: *mut usize, stopped: *mut i32) -> i32;
     pub fn rg_b200_decode_sampled(s: *mut rg_session, tokens: *const i32, batch: i32, temperature: f32, uniforms: *const f32, logits: *mut f32, ids: *mut i32) -> i32;

@@ -47,7 +47,7 @@ EXPORTS = [
     "rg_b200_plan_create", "rg_b200_plan_add_tensor", "rg_b200_plan_from_gguf", "rg_b200_plan_synth_tensor",
     "rg_b200_plan_tensor_nbytes", "rg_b200_plan_read_tensor", "rg_b200_plan_destroy", "rg_b200_session_prepare",
     "rg_b200_session_destroy", "rg_b200_position", "rg_b200_max_context", "rg_b200_vocab_size", "rg_b200_is_full",
-    "rg_b200_reset_sequence", "rg_b200_prefill", "rg_b200_decode", "rg_b200_generate_greedy", "rg_b200_decode_sampled", "rg_b200_generate_sampled", "rg_b200_decode_loop", "rg_b200_decode_profile", "rg_b200_decode_profile_in_step", "rg_b200_decode_profile_projections",
+    "rg_b200_reset_sequence", "rg_b200_prefill", "rg_b200_prefill_rows", "rg_b200_decode", "rg_b200_generate_greedy", "rg_b200_decode_sampled", "rg_b200_generate_sampled", "rg_b200_decode_loop", "rg_b200_decode_profile", "rg_b200_decode_profile_in_step", "rg_b200_decode_profile_projections",
     "rg_b200_report", "rg_b200_session_stream", "rg_b200_nccl_unique_id", "rg_b200_dequantize", "rg_b200_qmatmul",
     "rg_b200_row_gather", "rg_b200_qmatmul_bench", "rg_b200_qgemm", "rg_b200_attention_decode", "rg_b200_attention_decode_noalloc",
     "rg_b200_reset_row", "rg_b200_prefill_select", "rg_b200_decode_rows", "rg_b200_select", "rg_b200_kv_snapshot_create",
@@ -115,6 +115,7 @@ def load() -> C.CDLL:
     L.rg_b200_is_full.argtypes = [vp]
     L.rg_b200_reset_sequence.argtypes = [vp]
     L.rg_b200_prefill.argtypes = [vp, C.c_int32, i32p, C.c_size_t, f32p]
+    L.rg_b200_prefill_rows.argtypes = [vp, i32p, i32p, C.POINTER(C.c_size_t), C.c_int32, f32p, i32p]
     L.rg_b200_decode.argtypes = [vp, i32p, C.c_int32, f32p, i32p]
     L.rg_b200_generate_greedy.argtypes = [vp, i32p, C.c_size_t, C.c_size_t, i32p, C.POINTER(C.c_size_t), i32p]
     L.rg_b200_decode_sampled.argtypes = [vp, i32p, C.c_int32, C.c_float, f32p, f32p, i32p]

@@ -274,7 +274,11 @@ struct rg_session {
   float *d_uniforms = nullptr;  // [BMAX][vocab], allocated on first use
   const float *sample_temps = nullptr;  // per-column temperatures of a mixed step (device), else null
   float *d_temps = nullptr;             // [BMAX]
-  bool chunk_is_prompt = false;  // the columns of the current step are consecutive positions of one sequence
+  bool chunk_is_prompt = false;  // the columns of the current step are runs of consecutive positions (prompt_segments)
+  struct PromptSegment {
+    int col0, cols, seq, pos0;
+  };
+  std::vector<PromptSegment> prompt_segments;  // one run per sequence in the current prompt chunk
   // partial rotary lanes, q / k RMS norms or projection biases: such models take the general
   // q/k/v post-processing kernel and the three-launch attention on every path
   bool variant = false;
@@ -919,19 +923,22 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
     RG_LAUNCH(s, launch_rope_append(ra, L));
     if (s->chunk_is_prompt && prefill_attention_supported(s->heads_l, s->kv_l, hd)) {  // q and the caches are post-processed already
       // consecutive positions of one sequence: the tiled causal kernel reads each K / V row once per CTA
-      PrefillAttnArgs pa;
-      pa.q = s->q_rot;
-      pa.k_cache = ra.k_cache;
-      pa.v_cache = ra.v_cache;
-      pa.kv_f32 = s->kv_f32;
-      pa.cols = ncols;
-      pa.heads = s->heads_l;
-      pa.kv_heads = s->kv_l;
-      pa.ctx = s->ctx;
-      pa.seq = s->h_ctrl->seq[0];
-      pa.pos0 = s->h_ctrl->pos[0];
-      pa.out = s->attn_f32;
-      RG_LAUNCH(s, launch_attention_prefill(pa, L));
+      // (a chunk of several prompts holds one run per sequence: one launch per run)
+      for (const auto &seg : s->prompt_segments) {
+        PrefillAttnArgs pa;
+        pa.q = s->q_rot + (size_t)seg.col0 * qw;
+        pa.k_cache = ra.k_cache;
+        pa.v_cache = ra.v_cache;
+        pa.kv_f32 = s->kv_f32;
+        pa.cols = seg.cols;
+        pa.heads = s->heads_l;
+        pa.kv_heads = s->kv_l;
+        pa.ctx = s->ctx;
+        pa.seq = seg.seq;
+        pa.pos0 = seg.pos0;
+        pa.out = s->attn_f32 + (size_t)seg.col0 * qw;
+        RG_LAUNCH(s, launch_attention_prefill(pa, L));
+      }
     } else {
       AttnArgs aa;
       aa.q = s->q_rot;
@@ -971,7 +978,7 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
       if ((rc = tp_reduce_add(s, ncols, 1))) return rc;
     } else {
       prof_mark(s, PROF_OTHER);
-      RG_LAUNCH(s, launch_add_rows(s->x, d, s->tp_part[0], d, d, ncols, L));
+      RG_LAUNCH(s, launch_add_rows(s->x, d, s->tp_part[1], d, d, ncols, L));
     }
   }
   if (n_logit_cols > 0) {
@@ -985,10 +992,17 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
                         EPI_STORE, dst, ld, tp_lib ? plain : L)))
         return rc;
     } else {
-      // decode of many rows: logit column i is row i
+      // decode of many rows: logit column i is row i.  A chunk of several prompts wants the last
+      // column of each prompt instead: those rows are gathered first
       prof_mark(s, PROF_OTHER);
-      RG_LAUNCH(s, launch_rmsnorm16(s->x, d, reinterpret_cast<const float *>(s->output_norm.d), d, c.norm_eps, n_logit_cols, xop,
-                                    tp_lib ? plain : L));
+      const float *head_in = s->x;
+      if (s->chunk_is_prompt) {
+        RG_LAUNCH(s, launch_row_gather(RG_TYPE_F32, reinterpret_cast<const uint8_t *>(s->x), d, ctl->logit_cols, n_logit_cols,
+                                       s->partial, d, tp_lib ? plain : L));
+        head_in = s->partial;
+      }
+      RG_LAUNCH(s, launch_rmsnorm16(head_in, d, reinterpret_cast<const float *>(s->output_norm.d), d, c.norm_eps, n_logit_cols, xop,
+                                    (tp_lib && !s->chunk_is_prompt) ? plain : L));
       if ((rc = gemm_tc(s, *s->head, n_logit_cols, dst, ld, L))) return rc;
     }
     LaunchCfg am = L;
@@ -1907,6 +1921,7 @@ static int32_t prefill_impl(rg_session *s, int32_t row, const int32_t *ids, size
     h->step = 0;
     if ((rc = upload_ctrl(s))) return rc;
     s->chunk_is_prompt = !env_flag("RG_B200_SPLIT_ATTENTION");
+    s->prompt_segments.assign(1, {0, chunk, row, base + (int)done});
     rc = run_step(s, chunk, last ? 1 : 0, false, false);
     s->chunk_is_prompt = false;
     if (rc) return rc;
@@ -1923,6 +1938,97 @@ static int32_t prefill_impl(rg_session *s, int32_t row, const int32_t *ids, size
 
 int32_t rg_b200_prefill(rg_session *s, int32_t row, const int32_t *ids, size_t n, float *last_logits) {
   return prefill_impl(s, row, ids, n, last_logits, 1.0f, nullptr);
+}
+
+// Several prompts in one pass (the batch prefill of batch.rs:177-325, batch_generation.rs:104-189,
+// without its right padding: the chunk simply holds one run of columns per prompt).  Chunks of up
+// to 1024 columns are cut from the prompts laid end to end, so short prompts share every weight
+// tile; attention runs per prompt, and the last column of each prompt yields its logits.
+int32_t rg_b200_prefill_rows(rg_session *s, const int32_t *rows, const int32_t *ids, const size_t *lens, int32_t n_rows,
+                             float *last_logits, int32_t *greedy) {
+  int32_t rc = check_live(s);
+  if (rc) return rc;
+  if (!rows || !ids || !lens) return fail(RG_INVALID_ARGUMENT, "null argument");
+  if (n_rows < 1 || n_rows > s->max_batch) return fail(RG_INVALID_ARGUMENT, "row count out of range");
+  std::vector<char> seen((size_t)s->max_batch, 0);
+  size_t total = 0;
+  for (int r = 0; r < n_rows; ++r) {
+    if (rows[r] < 0 || rows[r] >= s->max_batch) return fail(RG_INVALID_ARGUMENT, "row out of range");
+    if (seen[(size_t)rows[r]]) return fail(RG_INVALID_ARGUMENT, "row " + std::to_string(rows[r]) + " listed twice");
+    seen[(size_t)rows[r]] = 1;
+    if (lens[r] == 0) return fail(RG_EMPTY_PROMPT, "empty token list for row " + std::to_string(rows[r]));
+    const int base = s->position[(size_t)rows[r]];
+    if ((size_t)base + lens[r] > (size_t)s->ctx)
+      return fail(RG_CONTEXT_EXHAUSTED, "row " + std::to_string(rows[r]) + ": position " + std::to_string(base) + " + " +
+                                            std::to_string(lens[r]) + " tokens exceeds " + std::to_string(s->ctx));
+    total += lens[r];
+  }
+  for (size_t i = 0; i < total; ++i)
+    if (ids[i] < 0 || ids[i] >= s->cfg.vocab) return fail(RG_TOKEN_OUT_OF_RANGE, "token " + std::to_string(ids[i]) + " at index " + std::to_string(i));
+  const size_t vocab = (size_t)s->cfg.vocab;
+  const bool shared = wide_path_ok(s) && !env_flag("RG_B200_SPLIT_ATTENTION");
+  if (!shared) {
+    // models that do not run on the tensor-core path: one prompt after the other, all or nothing
+    const std::vector<int32_t> before = s->position;
+    size_t off = 0;
+    for (int r = 0; r < n_rows; ++r) {
+      rc = prefill_impl(s, rows[r], ids + off, lens[r], last_logits ? last_logits + (size_t)r * vocab : nullptr, 1.0f, nullptr);
+      if (!rc && greedy) greedy[r] = s->h_ids[0];
+      if (rc) {
+        s->position = before;
+        return rc;
+      }
+      off += lens[r];
+    }
+    return RG_OK;
+  }
+  RG_CUDA(cudaSetDevice(s->opt.device));
+  s->sample_uniforms = nullptr;
+  RG_CUDA(cudaEventRecord(s->ev0, s->stream));
+  const int cap = prefill_attention_supported(s->heads_l, s->kv_l, s->cfg.head_dim) ? WMAX : SCOLS;
+  int r = 0;             // prompt the next column comes from
+  size_t taken = 0;      // tokens of prompt r already placed
+  size_t id_off = 0;     // index of prompt r's first token in ids
+  int first_done = 0;    // prompts finished before the current chunk
+  while (r < n_rows) {
+    Ctrl *h = s->h_ctrl;
+    s->prompt_segments.clear();
+    int cols = 0, n_logit = 0;
+    while (r < n_rows && cols < cap && n_logit < BMAX) {
+      const int base = s->position[(size_t)rows[r]];
+      const int take = (int)std::min<size_t>((size_t)(cap - cols), lens[r] - taken);
+      for (int i = 0; i < take; ++i) {
+        h->tokens[cols + i] = ids[id_off + taken + (size_t)i];
+        h->pos[cols + i] = base + (int)taken + i;
+        h->seq[cols + i] = rows[r];
+      }
+      s->prompt_segments.push_back({cols, take, rows[r], base + (int)taken});
+      cols += take;
+      taken += (size_t)take;
+      if (taken == lens[r]) {
+        h->logit_cols[n_logit++] = cols - 1;
+        id_off += lens[r];
+        taken = 0;
+        ++r;
+      }
+    }
+    h->step = 0;
+    if ((rc = upload_ctrl(s))) return rc;
+    s->chunk_is_prompt = true;
+    rc = run_step(s, cols, n_logit, false, false);
+    s->chunk_is_prompt = false;
+    if (rc) return rc;
+    // the pinned control block and the logits buffer are reused by the next chunk
+    rc = finish_step(s, n_logit, last_logits ? last_logits + (size_t)first_done * vocab : nullptr, last_logits ? n_logit : 0);
+    if (rc) return rc;
+    if (greedy) memcpy(greedy + first_done, s->h_ids, sizeof(int32_t) * (size_t)n_logit);
+    first_done += n_logit;
+  }
+  RG_CUDA(cudaEventRecord(s->ev1, s->stream));
+  RG_CUDA(cudaEventSynchronize(s->ev1));
+  cudaEventElapsedTime(&s->report.last_prefill_ms, s->ev0, s->ev1);
+  for (int i = 0; i < n_rows; ++i) s->position[(size_t)rows[i]] += (int)lens[i];  // commit only after the whole call succeeded
+  return RG_OK;
 }
 
 static int32_t decode_impl(rg_session *s, const int32_t *tokens, int32_t batch, float *logits, int32_t *greedy, float temperature,

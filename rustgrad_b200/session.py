@@ -265,6 +265,19 @@ class LlamaCudaSession:
         check(self._L.rg_b200_prefill(self._h, row, _i32(ids), ids.size, _f32(logits) if want_logits else None))
         return logits
 
+    def prefill_rows(self, prompts: dict, want_logits: bool = True):
+        """Several prompts in one pass: ``prompts`` maps cache row -> token ids.  Returns
+        (logits [n, vocab] in the dict's order or None, greedy ids [n])."""
+        rows = np.ascontiguousarray(list(prompts.keys()), dtype=np.int32)
+        lens = (C.c_size_t * len(rows))(*[len(p) for p in prompts.values()])
+        ids = np.ascontiguousarray(np.concatenate([np.asarray(p, dtype=np.int32) for p in prompts.values()]) if len(rows)
+                                   else np.zeros(0, np.int32), dtype=np.int32)
+        logits = np.empty((len(rows), self.vocab_size()), dtype=np.float32) if want_logits else None
+        greedy = np.empty(len(rows), dtype=np.int32)
+        check(self._L.rg_b200_prefill_rows(self._h, _i32(rows), _i32(ids), lens, len(rows),
+                                           _f32(logits) if want_logits else None, _i32(greedy)))
+        return logits, greedy
+
     def run_token(self, token: int) -> np.ndarray:
         logits, _ = self.decode([token], want_logits=True)
         return logits[0]

@@ -682,3 +682,66 @@ def test_incomplete_variant_families_are_refused():
         with pytest.raises(session.UnsupportedVariant):
             g.llama_config()
         g.close()
+
+
+def test_batched_prompt_prefill_matches_per_prompt_prefill(small_hd128, tiny):
+    """Several prompts in one pass (rg_b200_prefill_rows; src/models/transformer/batch.rs:177-325):
+    one chunk holding five prompts of very different lengths (logits of five arbitrary columns),
+    prompts cut across two chunks, a row that continues from cached positions, and a model that is
+    not on the tensor-core path; every prompt must see exactly what it sees alone, and the decode
+    step that follows must find every cache row in place."""
+    cfg, tensors = small_hd128
+    mk = lambda **kw: session.LlamaCudaPlan.from_tensors(  # noqa: E731
+        cfg, tensors, session.CudaSessionTarget(kv_f32=True, max_context=1100, **kw)).prepare()
+
+    def check(s, prompts, model_cfg, model_tensors, mode=O.MODE_FAST):
+        before = {r: s.position(r) for r in prompts}
+        logits, greedy = s.prefill_rows(prompts)
+        oracles = {}
+        for i, (row, p) in enumerate(prompts.items()):
+            o = oracles[row] = O.OracleModel(model_cfg, model_tensors, threads=4)
+            want = o.forward(p, mode)
+            assert_logits_close(logits[i], want)
+            assert int(greedy[i]) == O.select_greedy(want)
+            assert s.position(row) == before[row] + len(p)
+        return oracles, [int(g) for g in greedy]
+
+    s = mk(max_batch=5)
+    prompts = {2: synth.prompt_ids(cfg, 40, seed=1), 0: synth.prompt_ids(cfg, 7, seed=2), 4: synth.prompt_ids(cfg, 300, seed=3),
+               1: synth.prompt_ids(cfg, 1, seed=4), 3: synth.prompt_ids(cfg, 2, seed=5)}
+    before = session.launch_count("attn_prefill")
+    oracles, toks = check(s, prompts, cfg, tensors)
+    assert session.launch_count("attn_prefill") == before + 5 * cfg["n_layers"]   # one chunk, one attention launch per prompt
+    order = list(prompts)                                     # decode all five rows together: row r feeds its own token
+    by_row = {row: toks[i] for i, row in enumerate(order)}
+    logits, _ = s.decode([by_row[r] for r in range(5)], want_logits=True)
+    for r in range(5):
+        assert_logits_close(logits[r], oracles[r].forward([by_row[r]], O.MODE_FAST))
+    # 700 + 500 + 30 tokens: the second prompt is cut by the 1024-column chunk boundary
+    s = mk(max_batch=3)
+    check(s, {0: synth.prompt_ids(cfg, 700, seed=6), 1: synth.prompt_ids(cfg, 500, seed=7), 2: synth.prompt_ids(cfg, 30, seed=8)},
+          cfg, tensors)
+    # a row that already holds positions continues from them
+    s = mk(max_batch=2)
+    head, tail = synth.prompt_ids(cfg, 9, seed=9), synth.prompt_ids(cfg, 20, seed=10)
+    s.prefill_ids(head, row=1, want_logits=False)
+    logits, _ = s.prefill_rows({1: tail, 0: head})
+    o = O.OracleModel(cfg, tensors, threads=4)
+    assert_logits_close(logits[0], o.forward(np.concatenate([head, tail]), O.MODE_FAST))
+    # typed refusals leave every position as it was
+    for bad, err in (({0: head, 1: [cfg["vocab"]]}, session.TokenOutOfRange), ({0: head, 1: []}, session.EmptyPrompt),
+                     ({0: head, 1: synth.prompt_ids(cfg, 1100, seed=1)}, session.ContextExhausted)):
+        with pytest.raises(err):
+            s.prefill_rows(bad)
+        assert (s.position(0), s.position(1)) == (9, 29)
+    import ctypes as C
+    from rustgrad_b200 import _lib
+    rows = (C.c_int32 * 2)(0, 0)
+    lens = (C.c_size_t * 2)(1, 1)
+    ids = (C.c_int32 * 2)(1, 2)
+    assert _lib.load().rg_b200_prefill_rows(s._h, rows, ids, lens, 2, None, None) == 1   # a row listed twice
+    # a model with a dense projection (K = 688): the prompts run one after the other
+    tcfg, ttensors, tdata, _ = tiny
+    s = make_session(tdata, kv_f32=True, max_batch=3)
+    check(s, {1: synth.prompt_ids(tcfg, 12, seed=11), 0: synth.prompt_ids(tcfg, 5, seed=12), 2: synth.prompt_ids(tcfg, 20, seed=13)},
+          tcfg, ttensors, O.MODE_STRICT)
