@@ -9,8 +9,9 @@
  *    batch being rebuilt from snapshots at every step;
  *  - a prefix entry is taken when a prompt has been prefilled, as a device-to-device copy of the
  *    row's K/V; decode steps add no entries;
- *  - the decode columns of one step run as ONE launch sequence over all running rows; newly
- *    admitted prompts are prefilled one after the other in the same step.
+ *  - the decode columns of one step run as ONE launch sequence over all running rows; the greedy
+ *    prompts admitted in a step are prefilled together in one pass (rg_b200_prefill_rows), so short
+ *    prompts share every weight tile; sampled ones one after the other.
  * The scheduler only decides what runs: all device work goes through the verbs of rg_b200.h
  * (prefill_select, decode_rows, select, kv_snapshot_*, reset_row), reached through the table of
  * rg_serving_backend so that the policy can be driven without a device.
@@ -115,6 +116,10 @@ typedef struct rg_serving_backend {
   int32_t (*snapshot_create)(void *ctx, int32_t row, int32_t length, void **snapshot, size_t *bytes);
   int32_t (*snapshot_restore)(void *ctx, const void *snapshot, int32_t row);
   void (*snapshot_free)(void *ctx, void *snapshot);
+  /* Optional (may be NULL): several greedy prompts in one pass, rg_b200_prefill_rows.  Prompt i (lens[i]
+   * ids, laid end to end) continues cache row rows[i]; last_logits is [n, vocab], selected [n]. */
+  int32_t (*prefill_rows)(void *ctx, const int32_t *rows, const int32_t *ids, const size_t *lens, int32_t n, float *last_logits,
+                          int32_t *selected);
 } rg_serving_backend;
 
 /* LlamaServingScheduler::new (serving/mod.rs:371-406).  The session (and the tokenizer, nullable,

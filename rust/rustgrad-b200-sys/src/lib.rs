@@ -275,6 +275,7 @@ pub struct rg_serving_backend {
     pub snapshot_create: Option<unsafe extern "C" fn(ctx: *mut c_void, row: i32, length: i32, snapshot: *mut *mut c_void, bytes: *mut usize) -> i32>,
     pub snapshot_restore: Option<unsafe extern "C" fn(ctx: *mut c_void, snapshot: *const c_void, row: i32) -> i32>,
     pub snapshot_free: Option<unsafe extern "C" fn(ctx: *mut c_void, snapshot: *mut c_void)>,
+    pub prefill_rows: Option<unsafe extern "C" fn(ctx: *mut c_void, rows: *const i32, ids: *const i32, lens: *const usize, n: i32, last_logits: *mut f32, selected: *mut i32) -> i32>,
 }
 
 unsafe extern "C" {

@@ -192,6 +192,9 @@ int32_t be_snapshot_restore(void *c, const void *snap, int32_t row) {
   return rg_b200_kv_snapshot_restore((rg_session *)c, (const rg_kv_snapshot *)snap, row);
 }
 void be_snapshot_free(void *, void *snap) { rg_b200_kv_snapshot_free((rg_kv_snapshot *)snap); }
+int32_t be_prefill_rows(void *c, const int32_t *rows, const int32_t *ids, const size_t *lens, int32_t n, float *last, int32_t *sel) {
+  return rg_b200_prefill_rows((rg_session *)c, rows, ids, lens, n, last, sel);
+}
 
 int32_t encode_text(const rg_tokenizer *tok, const char *text, size_t len, Key *out, rg_serving_error *err) {
   rg_tok_error terr{};
@@ -244,6 +247,7 @@ int32_t rg_b200_scheduler_new(rg_session *session, const rg_tokenizer *tokenizer
   be.snapshot_create = be_snapshot_create;
   be.snapshot_restore = be_snapshot_restore;
   be.snapshot_free = be_snapshot_free;
+  be.prefill_rows = be_prefill_rows;
   return rg_b200_scheduler_new_with_backend(&be, tokenizer, options, out, err);
 }
 
@@ -395,11 +399,62 @@ int32_t rg_b200_scheduler_step(rg_scheduler *s, rg_token_event *events, size_t c
     return fail(err, RG_SERVING_SESSION, rc);
   };
   std::vector<float> last(vocab);
+  // greedy prompts admitted in this step wait here and are prefilled together
+  struct Deferred {
+    Request *r;
+    size_t cached;
+  };
+  std::vector<Deferred> deferred;
+  auto remember_prefix = [&](Request *r, const float *logits) -> int32_t {
+    if (!(s->prefixes.max_entries && s->prefixes.max_bytes)) return RG_OK;
+    void *handle = nullptr;
+    size_t bytes = 0;
+    if (int32_t rc = s->be.snapshot_create(s->be.ctx, r->row, (int32_t)r->prompt.size(), &handle, &bytes)) return rc;
+    auto snap = std::make_shared<Snapshot>(&s->be, handle, (int32_t)r->prompt.size(), bytes);
+    s->prefixes.insert(r->prompt, std::move(snap), logits, vocab);
+    return RG_OK;
+  };
+  auto flush = [&]() -> int32_t {
+    if (deferred.empty()) return RG_OK;
+    const int32_t n = (int32_t)deferred.size();
+    std::vector<int32_t> rows(n), ids, sel(n, -1);
+    std::vector<size_t> lens(n);
+    for (int32_t i = 0; i < n; ++i) {
+      const Deferred &d = deferred[i];
+      rows[i] = d.r->row;
+      lens[i] = d.r->prompt.size() - d.cached;
+      ids.insert(ids.end(), d.r->prompt.begin() + (ptrdiff_t)d.cached, d.r->prompt.end());
+    }
+    std::vector<float> logits((size_t)n * vocab);
+    int32_t rc = RG_OK;
+    if (n > 1 && s->be.prefill_rows) {
+      rc = s->be.prefill_rows(s->be.ctx, rows.data(), ids.data(), lens.data(), n, logits.data(), sel.data());
+    } else {
+      size_t off = 0;
+      for (int32_t i = 0; i < n && !rc; ++i) {
+        rc = s->be.prefill_select(s->be.ctx, rows[i], ids.data() + off, lens[i], 0.0f, nullptr, &logits[(size_t)i * vocab], &sel[i]);
+        off += lens[i];
+      }
+    }
+    for (int32_t i = 0; i < n && !rc; ++i) {
+      rc = remember_prefix(deferred[i].r, &logits[(size_t)i * vocab]);
+      chosen[deferred[i].r->id] = sel[i];
+    }
+    deferred.clear();
+    return rc;
+  };
   for (Request *r : selected) {
     if (r->has_pending) {
       decode_cols.push_back(r);
       continue;
     }
+    // a waiting prompt this one extends must be in the prefix cache before the lookup below
+    if (s->prefixes.max_entries && s->prefixes.max_bytes)
+      for (const Deferred &d : deferred)
+        if (d.r->prompt.size() <= r->prompt.size() && std::equal(d.r->prompt.begin(), d.r->prompt.end(), r->prompt.begin())) {
+          if (int32_t rc = flush()) return roll_back(rc);
+          break;
+        }
     // a new request: lean on the longest cached prefix, prefill what is left
     r->row = *s->free_rows.begin();
     s->free_rows.erase(s->free_rows.begin());
@@ -424,18 +479,17 @@ int32_t rg_b200_scheduler_step(rg_scheduler *s, rg_token_event *events, size_t c
       s->prefixes.release(held);
       if (rc) return roll_back(rc);
     }
+    if (r->greedy) {
+      deferred.push_back({r, cached});
+      continue;
+    }
     rc = s->be.prefill_select(s->be.ctx, r->row, r->prompt.data() + cached, r->prompt.size() - cached, r->temperature, tape,
                               last.data(), &token);
     if (rc) return roll_back(rc);
-    if (s->prefixes.max_entries && s->prefixes.max_bytes) {
-      void *handle = nullptr;
-      size_t bytes = 0;
-      if ((rc = s->be.snapshot_create(s->be.ctx, r->row, (int32_t)r->prompt.size(), &handle, &bytes))) return roll_back(rc);
-      auto snap = std::make_shared<Snapshot>(&s->be, handle, (int32_t)r->prompt.size(), bytes);
-      s->prefixes.insert(r->prompt, std::move(snap), last.data(), vocab);
-    }
+    if ((rc = remember_prefix(r, last.data()))) return roll_back(rc);
     chosen[r->id] = token;
   }
+  if (int32_t rc = flush()) return roll_back(rc);
   if (!decode_cols.empty()) {
     const int32_t n = (int32_t)decode_cols.size();
     std::vector<int32_t> rows(n), toks(n), ids(n);

@@ -59,12 +59,13 @@ _SELECT = C.CFUNCTYPE(C.c_int32, vp, f32p, C.c_float, f32p, i32p)
 _SNAP_CREATE = C.CFUNCTYPE(C.c_int32, vp, C.c_int32, C.c_int32, C.POINTER(vp), C.POINTER(C.c_size_t))
 _SNAP_RESTORE = C.CFUNCTYPE(C.c_int32, vp, vp, C.c_int32)
 _SNAP_FREE = C.CFUNCTYPE(None, vp, vp)
+_PREFILL_ROWS = C.CFUNCTYPE(C.c_int32, vp, i32p, i32p, C.POINTER(C.c_size_t), C.c_int32, f32p, i32p)
 
 
 class _Backend(C.Structure):
     _fields_ = [("ctx", vp), ("vocab", C.c_int32), ("max_context", C.c_int32), ("reset_row", _RESET),
                 ("prefill_select", _PREFILL), ("decode_rows", _DECODE), ("select", _SELECT), ("snapshot_create", _SNAP_CREATE),
-                ("snapshot_restore", _SNAP_RESTORE), ("snapshot_free", _SNAP_FREE)]
+                ("snapshot_restore", _SNAP_RESTORE), ("snapshot_free", _SNAP_FREE), ("prefill_rows", _PREFILL_ROWS)]
 
 
 def _L():
@@ -181,6 +182,10 @@ class ServingBackend:
     def snapshot_free(self, handle: int) -> None:
         pass
 
+    prefill_rows = None
+    """Optional: ``prefill_rows(rows, prompts, last_logits [n, vocab]) -> (status, ids)`` for several
+    greedy prompts in one pass; without it the scheduler prefills them one after the other."""
+
     def _table(self) -> _Backend:
         v = self.vocab
 
@@ -209,9 +214,21 @@ class ServingBackend:
             handle[0], nbytes[0] = h, b
             return rc
 
+        def prefill_rows(_, rows, ids, lens, n, last, sel):
+            prompts, off = [], 0
+            for i in range(n):
+                prompts.append([ids[off + j] for j in range(lens[i])])
+                off += lens[i]
+            rc, out = self.prefill_rows([rows[i] for i in range(n)], prompts, np.ctypeslib.as_array(last, shape=(n, v)))
+            for i, t in enumerate(out):
+                sel[i] = t
+            return rc
+
         self._keep = [_RESET(lambda _, row: self.reset_row(row)), _PREFILL(prefill), _DECODE(decode), _SELECT(select),
                       _SNAP_CREATE(snap_create), _SNAP_RESTORE(lambda _, h, row: self.snapshot_restore(h, row)),
                       _SNAP_FREE(lambda _, h: self.snapshot_free(h))]
+        if self.prefill_rows is not None:
+            self._keep.append(_PREFILL_ROWS(prefill_rows))
         return _Backend(None, self.vocab, self.max_context, *self._keep)
 
 

@@ -300,3 +300,54 @@ def test_a_failed_step_can_be_run_again_as_a_whole():
     assert e.value.value == 12 and sched.status(b) == "queued"
     run_all(sched)
     assert sched.result(a).generated_ids == alone([1, 2], 4) and sched.result(b).generated_ids == alone([3, 4, 5], 3)
+
+
+class BatchingSession(FakeSession):
+    """A back end that also offers the several-prompts-in-one-pass verb."""
+
+    def prefill_rows(self, rows, prompts, last_logits):
+        self.calls.append(("prefill_rows", tuple(rows), tuple(len(p) for p in prompts)))
+        rc = self._failing("prefill_rows")
+        if rc:
+            return rc, []
+        out = []
+        for i, (row, ids) in enumerate(zip(rows, prompts)):
+            self.rows.setdefault(row, []).extend(ids)
+            last_logits[i, :] = fake_logits(self.rows[row])
+            out.append(int(np.argmax(last_logits[i])))
+        return 0, out
+
+
+def test_greedy_prompts_admitted_together_are_prefilled_in_one_pass():
+    fake = BatchingSession()
+    sched = serving.LlamaServingScheduler(fake, batch_size=4, prefix_max_entries=8, prefix_max_bytes=1 << 20)
+    rng = np.random.default_rng(1)
+    tape = rng.random((3, VOCAB), dtype=np.float32)
+    prompts = [[1, 2, 3], [4, 5], [6, 7, 8, 9]]
+    ids = [sched.submit_ids(p, serving.GenerationConfig(3)) for p in prompts]
+    sampled = sched.submit_ids([9, 9], serving.GenerationConfig(3, serving.Sampling(0.9, tape)))
+    sched.step()
+    assert ("prefill_rows", (0, 1, 2), (3, 2, 4)) in fake.calls          # the three greedy prompts in one call
+    assert [c for c in fake.calls if c[0] == "prefill"] == [("prefill", 3, 2)]   # the sampled one alone
+    run_all(sched)
+    for rid, p in zip(ids, prompts):
+        assert sched.result(rid).generated_ids == alone(p, 3)
+    assert sched.prefix_stats()["entries"] == 4
+    # a prompt that extends one waiting in the same step still finds it in the prefix cache
+    fake.calls.clear()
+    a = sched.submit_ids([20, 21], serving.GenerationConfig(2))
+    b = sched.submit_ids([20, 21, 22], serving.GenerationConfig(2))
+    c = sched.submit_ids([30], serving.GenerationConfig(2))
+    sched.step()
+    assert ("restore", 1, 2) in fake.calls and sched.prefix_stats()["hits"] == 1
+    run_all(sched)
+    assert [sched.result(r).generated_ids for r in (a, b, c)] == [alone([20, 21], 2), alone([20, 21, 22], 2), alone([30], 2)]
+    # a failing pass un-admits all of its prompts
+    d = sched.submit_ids([40, 41], serving.GenerationConfig(1))
+    e = sched.submit_ids([42], serving.GenerationConfig(1))
+    fake.fail["prefill_rows"] = 9
+    with pytest.raises(serving.ServingError):
+        sched.step()
+    assert [sched.status(r) for r in (d, e)] == ["queued", "queued"]
+    run_all(sched)
+    assert sched.result(d).generated_ids == alone([40, 41], 1) and sched.result(e).generated_ids == alone([42], 1)
