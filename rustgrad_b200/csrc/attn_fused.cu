@@ -314,6 +314,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnA
       }
     }
     last_flag = last;
+    trace_stamp(trace, 4, tr_first, false);  // arrival counted
   }
   __syncthreads();
   if (!last_flag) return;
@@ -352,6 +353,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnA
   for (int j = 0; j < HPT; ++j)
     if (tid + j * THREADS < nh) hdr[tid + j * THREADS] = hreg[j];
   __syncthreads();
+  if (tid == 0 && kvh == 0 && c == 0) trace_stamp(trace, 10, true, false);  // span headers gathered (slot 10)
   if (warp < G) {
     const int gq = warp;
     float M = -INFINITY;
@@ -367,6 +369,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnA
     if (lane == 0) ml[gq * 2 + 1] = __frcp_rn(L);
   }
   __syncthreads();
+  if (tid == 0 && kvh == 0 && c == 0) trace_stamp(trace, 11, true, false);  // span weights ready (slot 11)
   for (int o = tid; o < nout; o += THREADS) {
     const int gq = o / (HD / 2), d = 2 * (o - gq * (HD / 2));
     const float *base = column(o);
@@ -389,6 +392,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnA
     const float o0 = __fmul_rn(a0, ml[gq * 2 + 1]), o1 = __fmul_rn(a1, ml[gq * 2 + 1]);
     dst[0] = o0;
     dst[1] = o1;
+    if (tid == 0 && kvh == 0 && c == 0) trace_stamp(trace, 12, true, false);  // first output pair stored (slot 12)
     if (A.pack_out) {
       // The sixteen lanes of a half-warp hold one 32-element block of the output projection's input
       // (lane j: elements 2j, 2j + 1): pack it as block fixed point for the integer GEMV (rg_device.cuh).

@@ -1134,7 +1134,8 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
     int32_t rc = linear(s, qkvw, 3, s->xn_pack, s->xn_f32, d, ncols, EPI_STORE, s->qkv, qkv_w);
     if (rc) return rc;
     prof_mark(s, PROF_ATTN);
-    if (gemv16 && s->attn_counters && !s->variant) {
+    if ((gemv16 || (ncols >= 3 && !s->chunk_is_prompt && !env_flag("RG_B200_SPLIT_ATTENTION_SMALL"))) && s->attn_counters &&
+        !s->variant) {
       // rows of distinct sequences: RoPE, cache append, split attention and the combine in one launch
       FusedAttnArgs fa;
       fa.qkv = s->qkv;
