@@ -205,8 +205,6 @@ static int32_t check_tensor(rg_plan *p, const std::string &name, int32_t type, u
     return fail(RG_SHAPE_MISMATCH, name + ": expected [" + std::to_string(slot->rows) + "," + std::to_string(slot->cols) +
                                        "], got [" + std::to_string(rows) + "," + std::to_string(cols) + "]");
   if (cols % (uint64_t)block_elements(type)) return fail(RG_SHAPE_MISMATCH, name + ": columns are not a multiple of the block size");
-  if ((type == RG_TYPE_Q4_K || type == RG_TYPE_Q6_K) && p->tp_world > 1)
-    return fail(RG_UNSUPPORTED_GEOMETRY, name + ": K-quant tensors are not sharded (single GPU only)");
   if (slot->t && slot->t->type >= 0) return fail(RG_INVALID_ARGUMENT, name + ": tensor bound twice");
   const uint64_t W = (uint64_t)p->tp_world, R = (uint64_t)p->tp_rank;
   *r0 = 0, *lr = rows, *c0 = 0, *lc = cols;
@@ -215,7 +213,9 @@ static int32_t check_tensor(rg_plan *p, const std::string &name, int32_t type, u
     *lr = rows / W;
     *r0 = R * *lr;
   } else if (W > 1 && slot->split == SPLIT_COLS) {
-    if (cols % (W * 32)) return fail(RG_UNSUPPORTED_GEOMETRY, name + ": columns do not split at block boundaries");
+    // a rank owns whole blocks of every row: 32 elements, or a 256-element K-quant super-block
+    if (cols % (W * (uint64_t)block_elements(type)))
+      return fail(RG_UNSUPPORTED_GEOMETRY, name + ": columns do not split at block boundaries");
     *lc = cols / W;
     *c0 = R * *lc;
   }

@@ -101,3 +101,63 @@ def test_tensor_parallel_matches_single_gpu_and_cpu_path(tmp_path, world):
     mp.spawn(worker, args=(world, free_port(), str(nccl_dir), False), nprocs=world, join=True)
     assert np.load(nccl_dir / "peer0.npy")[0] == 0
     assert np.abs(np.load(nccl_dir / "logits0.npy") - l0).max() <= 1e-4
+
+
+def kquant_tensors():
+    """Q4_K projections, Q6_K embedding / head / one down projection: random valid super-blocks."""
+    rng = np.random.default_rng(7)
+    tensors = {}
+    for name, rows, cols, is_norm in synth.tensor_inventory(CFG, tied_head=False):
+        if is_norm:
+            tensors[name] = (quant.F32, 1, cols, np.ones(cols, dtype=np.float32).view(np.uint8))
+        else:
+            kind = quant.Q6_K if name in ("token_embd.weight", "output.weight", "blk.0.ffn_down.weight") else quant.Q4_K
+            tensors[name] = (kind, rows, cols, quant.random_k_blocks(kind, rows * cols // 256, rng, scale=0.05))
+    return tensors
+
+
+def kquant_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    from rustgrad_b200 import session
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    box = [session.nccl_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    target = session.CudaSessionTarget(device=rank, kv_f32=True, tp_rank=rank, tp_world=world, nccl_id=box[0])
+    s = session.LlamaCudaPlan.from_tensors(CFG, kquant_tensors(), target).prepare()
+    logits = [s.prefill_ids(synth.prompt_ids(CFG, 11, seed=2))]
+    tok = int(np.argmax(logits[0]))
+    for _ in range(4):
+        lg, greedy = s.decode([tok], want_logits=True)
+        logits.append(lg[0])
+        tok = int(greedy[0])
+    np.save(os.path.join(out_dir, f"logits{rank}.npy"), np.stack(logits))
+    dist.barrier()
+    s.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_k_quant_tensors_shard_at_super_block_boundaries(tmp_path, world):
+    """Q4_K / Q6_K projections under tensor parallelism: rows split as for any type, the contracting
+    axis of attn_output / ffn_down at 256-element super-blocks (src/sharding.rs:642-667 on the block
+    geometry of src/gguf/tensor.rs:88-155)."""
+    import torch
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    from oracle import oracle as O
+    mp.spawn(kquant_worker, args=(world, free_port(), str(tmp_path)), nprocs=world, join=True)
+    l0 = np.load(tmp_path / "logits0.npy")
+    for r in range(1, world):
+        assert np.array_equal(l0, np.load(tmp_path / f"logits{r}.npy"))
+    oracle = O.OracleModel(CFG, kquant_tensors(), threads=4)
+    want = [oracle.forward(synth.prompt_ids(CFG, 11, seed=2))]
+    for _ in range(4):
+        want.append(oracle.forward([O.select_greedy(want[-1])]))
+    want = np.stack(want)
+    assert [int(np.argmax(r)) for r in l0] == [O.select_greedy(w) for w in want]
+    diff = np.abs(l0 - want).max()
+    assert diff <= 1e-2 and diff <= 1e-3 * np.abs(want).max() + 1e-6, (diff, np.abs(want).max())
