@@ -398,3 +398,144 @@ impl Drop for LlamaCudaPromptWorkflow {
         unsafe { rg_b200_workflow_close(self.raw) }
     }
 }
+
+/// `LlamaServingError` (serving/mod.rs:792-860): the kind (`serving_status::*`) with its numbers.
+#[derive(Clone, Copy, Debug, Eq, PartialEq)]
+pub struct LlamaCudaServingError {
+    pub kind: i32,
+    pub value: i64,
+    pub value2: i64,
+}
+
+impl fmt::Display for LlamaCudaServingError {
+    fn fmt(&self, f: &mut fmt::Formatter<'_>) -> fmt::Result {
+        write!(f, "serving status {} ({}, {})", self.kind, self.value, self.value2)
+    }
+}
+
+impl std::error::Error for LlamaCudaServingError {}
+
+/// `LlamaServingSampling` (serving/mod.rs:28-38).
+pub enum LlamaCudaServingSampling<'a> {
+    Greedy,
+    GumbelMax { temperature: f32, uniforms: &'a [f32] },
+}
+
+/// `LlamaTokenEvent` (serving/mod.rs:98-129).
+pub type LlamaCudaTokenEvent = rg_token_event;
+
+/// `LlamaServingResult` (serving/mod.rs:131-155), copied out of the scheduler.
+#[derive(Clone, Debug, Eq, PartialEq)]
+pub struct LlamaCudaServingResult {
+    pub request_id: u64,
+    pub prompt_ids: Vec<u32>,
+    pub generated_ids: Vec<u32>,
+    pub decoded: String,
+    pub stopped: bool,
+}
+
+/// Continuous batching with a prefix cache over one session (`LlamaServingScheduler`,
+/// serving/mod.rs:371-690).  The session must outlive the scheduler.
+pub struct LlamaCudaServingScheduler<'s> {
+    raw: *mut rg_scheduler,
+    batch_size: usize,
+    _session: core::marker::PhantomData<&'s mut LlamaCudaSession>,
+}
+
+impl<'s> LlamaCudaServingScheduler<'s> {
+    pub fn new(session: &'s mut LlamaCudaSession, batch_size: usize, prefix_max_entries: usize, prefix_max_bytes: usize,
+               stop_ids: &[i32]) -> Result<Self, LlamaCudaServingError> {
+        let options = rg_serving_options {
+            batch_size: batch_size as i32,
+            max_rows: 0,
+            prefix_max_entries,
+            prefix_max_bytes,
+            stop_ids: stop_ids.as_ptr(),
+            n_stop_ids: stop_ids.len(),
+            has_bos: 0,
+            bos_id: 0,
+        };
+        let mut raw = core::ptr::null_mut();
+        let mut err = rg_serving_error::default();
+        let rc = unsafe { rg_b200_scheduler_new(session.as_raw(), core::ptr::null(), &options, &mut raw, &mut err) };
+        if rc != 0 {
+            return Err(LlamaCudaServingError { kind: rc, value: err.value, value2: err.value2 });
+        }
+        Ok(Self { raw, batch_size, _session: core::marker::PhantomData })
+    }
+
+    /// `submit_ids` (serving/mod.rs:408-477): validated as a whole before it gets an id.
+    pub fn submit_ids(&mut self, prompt: &[i32], max_new_tokens: usize, sampling: LlamaCudaServingSampling<'_>) -> Result<u64, LlamaCudaServingError> {
+        let s = match sampling {
+            LlamaCudaServingSampling::Greedy => rg_serving_sampling { greedy: 1, temperature: 0.0, uniforms: core::ptr::null(), n_uniforms: 0 },
+            LlamaCudaServingSampling::GumbelMax { temperature, uniforms } => {
+                rg_serving_sampling { greedy: 0, temperature, uniforms: uniforms.as_ptr(), n_uniforms: uniforms.len() }
+            }
+        };
+        let (mut id, mut err) = (0u64, rg_serving_error::default());
+        let rc = unsafe { rg_b200_scheduler_submit_ids(self.raw, prompt.as_ptr(), prompt.len(), max_new_tokens, &s, &mut id, &mut err) };
+        if rc != 0 {
+            return Err(LlamaCudaServingError { kind: rc, value: err.value, value2: err.value2 });
+        }
+        Ok(id)
+    }
+
+    /// `step` (serving/mod.rs:557-690): one token for each of up to `batch_size` requests in arrival order.
+    pub fn step(&mut self) -> Result<Vec<LlamaCudaTokenEvent>, LlamaCudaServingError> {
+        let mut events = vec![rg_token_event::default(); self.batch_size];
+        let (mut n, mut err) = (0usize, rg_serving_error::default());
+        let rc = unsafe { rg_b200_scheduler_step(self.raw, events.as_mut_ptr(), events.len(), &mut n, &mut err) };
+        if rc != 0 {
+            return Err(LlamaCudaServingError { kind: rc, value: err.value, value2: err.value2 });
+        }
+        events.truncate(n);
+        Ok(events)
+    }
+
+    pub fn pending(&self) -> usize {
+        unsafe { rg_b200_scheduler_pending(self.raw) }
+    }
+
+    pub fn result(&self, request_id: u64) -> Option<LlamaCudaServingResult> {
+        let mut r = core::mem::MaybeUninit::<rg_serving_result>::zeroed();
+        if unsafe { rg_b200_scheduler_result(self.raw, request_id, r.as_mut_ptr()) } != 0 {
+            return None;
+        }
+        let r = unsafe { r.assume_init() };
+        let ids = |p: *const i32, n: usize| -> Vec<u32> {
+            if n == 0 { Vec::new() } else { unsafe { core::slice::from_raw_parts(p, n) }.iter().map(|&t| t as u32).collect() }
+        };
+        let decoded = if r.decoded_bytes == 0 {
+            String::new()
+        } else {
+            String::from_utf8_lossy(unsafe { core::slice::from_raw_parts(r.decoded as *const u8, r.decoded_bytes) }).into_owned()
+        };
+        Some(LlamaCudaServingResult {
+            request_id: r.request_id,
+            prompt_ids: ids(r.prompt_ids, r.n_prompt_ids),
+            generated_ids: ids(r.generated_ids, r.n_generated_ids),
+            decoded,
+            stopped: r.stopped != 0,
+        })
+    }
+
+    pub fn remove(&mut self, request_id: u64) -> bool {
+        unsafe { rg_b200_scheduler_remove(self.raw, request_id) == 0 }
+    }
+
+    pub fn prefix_stats(&self) -> rg_prefix_stats {
+        let mut st = rg_prefix_stats::default();
+        unsafe { rg_b200_scheduler_prefix_stats(self.raw, &mut st) };
+        st
+    }
+
+    pub fn invalidate_prefix_cache(&mut self) {
+        unsafe { rg_b200_scheduler_invalidate_prefix_cache(self.raw) }
+    }
+}
+
+impl Drop for LlamaCudaServingScheduler<'_> {
+    fn drop(&mut self) {
+        unsafe { rg_b200_scheduler_free(self.raw) }
+    }
+}
