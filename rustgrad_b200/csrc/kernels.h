@@ -164,7 +164,14 @@ struct TpFusedArgs {
   uint8_t *pack_out = nullptr;
   const float *pack_w = nullptr;
   int pack_type = 0;
+  // Push form (nullable: then every rank pulls the others' partials after a flag hand-shake): device
+  // array [world] of every rank's receive area, [2 buffers][world source ranks][TP_PUSH_COLS][ldp]
+  // 8-byte words {value, epoch}.  A thread stores its elements of the local partial into every peer's
+  // area (slot = own rank) and then polls its OWN area for the other ranks' words of this epoch: no
+  // flags, no fences, no load from a peer; one NVLink store latency per exchange.
+  float *const *peer_recv = nullptr;
 };
+constexpr int TP_PUSH_COLS = 32;  // columns an exchange in push form can carry
 cudaError_t launch_tp_allreduce_add(const TpFusedArgs &a, const LaunchCfg &cfg);
 
 // Dense (F32/F16) weight GEMV for tensors the block formats cannot hold (K % 32 != 0) or that a

@@ -318,6 +318,7 @@ struct rg_session {
   bool tp_fused = false;
   const float **tp_peer_part[2] = {nullptr, nullptr};  // device arrays [world]
   unsigned **tp_peer_flags = nullptr;                  // device array [world]
+  float **tp_peer_recv = nullptr;                      // device array [world]: receive areas of the push form (null: pull)
   unsigned *tp_epochs = nullptr;
   std::vector<void *> tp_ipc_opened;
   // one-launch decode attention (attn_fused.cu): arrival counters per (column, kv head); null = not used
@@ -470,6 +471,7 @@ static int32_t tp_reduce_add(rg_session *s, int ncols, int which, uint8_t *pack_
     a.pack_out = pack_out;
     a.pack_w = pack_w;
     a.pack_type = pack_type;
+    a.peer_recv = ncols <= TP_PUSH_COLS ? s->tp_peer_recv : nullptr;
     RG_LAUNCH(s, launch_tp_allreduce_add(a, lcfg(s)));
     s->report.peer_reduce_launches++;
     return RG_OK;
@@ -1031,7 +1033,10 @@ static int32_t tp_fused_setup(rg_session *s) {
   const int W = s->tp_world, d = s->cfg.d_model;
   if (W > TP_FUSED_MAX_WORLD || d % 4) return RG_OK;
   const size_t part_floats = (size_t)WMAX * d;
-  const size_t block_bytes = 2 * part_floats * sizeof(float) + TP_FUSED_FLAG_WORDS * sizeof(unsigned);
+  // two partial buffers, the flag words, then the receive area of the push form
+  const size_t recv_off = 2 * part_floats * sizeof(float) + ((TP_FUSED_FLAG_WORDS * sizeof(unsigned) + 255) & ~(size_t)255);
+  const size_t recv_floats = (size_t)2 * 2 * W * TP_PUSH_COLS * d;  // 8-byte words {value, epoch}
+  const size_t block_bytes = recv_off + recv_floats * sizeof(float);
   uint8_t *block = nullptr;
   float *xchg = nullptr;  // [16 floats of handle + 1 ok flag] * (1 + W)
   int32_t rc;
@@ -1079,16 +1084,22 @@ static int32_t tp_fused_setup(rg_session *s) {
   if (host[0] < (float)W - 0.5f) return RG_OK;  // some rank could not: everyone keeps the NCCL path
   std::vector<const float *> pa((size_t)W), pb((size_t)W);
   std::vector<unsigned *> pf((size_t)W);
+  std::vector<float *> pr((size_t)W);
   for (int r = 0; r < W; ++r) {
     pa[(size_t)r] = reinterpret_cast<const float *>(base[(size_t)r]);
     pb[(size_t)r] = reinterpret_cast<const float *>(base[(size_t)r]) + part_floats;
     pf[(size_t)r] = reinterpret_cast<unsigned *>(base[(size_t)r] + 2 * part_floats * sizeof(float));
+    pr[(size_t)r] = reinterpret_cast<float *>(base[(size_t)r] + recv_off);
   }
   const float **d_pa, **d_pb;
   unsigned **d_pf;
+  float **d_pr;
   if ((rc = dalloc(s, &d_pa, (size_t)W))) return rc;
   if ((rc = dalloc(s, &d_pb, (size_t)W))) return rc;
   if ((rc = dalloc(s, &d_pf, (size_t)W))) return rc;
+  if ((rc = dalloc(s, &d_pr, (size_t)W))) return rc;
+  RG_CUDA(cudaMemcpy(d_pr, pr.data(), sizeof(void *) * (size_t)W, cudaMemcpyHostToDevice));
+  s->tp_peer_recv = env_flag("RG_B200_TP_PULL") ? nullptr : d_pr;
   if ((rc = dalloc(s, &s->tp_epochs, (size_t)2 * TP_FUSED_CTAS))) return rc;
   RG_CUDA(cudaMemcpy(d_pa, pa.data(), sizeof(void *) * (size_t)W, cudaMemcpyHostToDevice));
   RG_CUDA(cudaMemcpy(d_pb, pb.data(), sizeof(void *) * (size_t)W, cudaMemcpyHostToDevice));

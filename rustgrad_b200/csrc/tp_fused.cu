@@ -59,6 +59,69 @@ __global__ void __launch_bounds__(THREADS) tp_allreduce_add_kernel(const TpFused
   }
   __syncthreads();
   const unsigned e = s_epoch;
+  if (A.peer_recv) {
+    // ---- push form: no flag hand-shake and no load from a peer.  Every element travels as an
+    // 8-byte word {value, epoch}, stored into the receive area of each peer (an 8-byte store is
+    // indivisible); the receiver polls its OWN memory until the word carries this exchange's epoch.
+    // One NVLink store latency per exchange; the same thread sends and later sums an element.
+    auto recv = [&](int r, int q) {  // receive area of rank r, slot of source rank q
+      return reinterpret_cast<uint2 *>(A.peer_recv[r]) + ((size_t)(A.buffer * A.world + q) * TP_PUSH_COLS) * (size_t)A.ldp;
+    };
+    const float *mine = A.peer_partial[A.rank];
+    auto poll = [&](const uint2 *p) {
+      for (unsigned i = 0; i < A.poll_limit; ++i) {
+        uint2 w;
+        asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(p) : "memory");
+        if (w.y == e) return __uint_as_float(w.x);
+        if (i > 256) __nanosleep(32);
+      }
+      atomicExch(status, DEV_TIMEOUT);  // a rank never arrived: the host sees the status and poisons the session
+      return 0.0f;
+    };
+    if (A.pack_out) {
+      const int warp = tid >> 5, lane = tid & 31, nblk = A.n >> 5;
+      const bool q4 = A.pack_type == RG_TYPE_Q4_0;
+      constexpr int STRIDE = TP_FUSED_CTAS * (THREADS / 32);
+      for (int kb = b * (THREADS / 32) + warp; kb < nblk; kb += STRIDE) {
+        const int idx = kb * 32 + lane;
+        const float v = mine[idx];
+        for (int r = 0; r < A.world; ++r)
+          if (r != A.rank)
+            asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(recv(r, A.rank) + idx), "r"(__float_as_uint(v)), "r"(e) : "memory");
+      }
+      for (int kb = b * (THREADS / 32) + warp; kb < nblk; kb += STRIDE) {
+        const int idx = kb * 32 + lane;
+        const float resid = A.x[idx];
+        const float w = A.pack_w ? __ldg(A.pack_w + idx) : 1.0f;
+        float sum = 0.0f;
+        for (int r = 0; r < A.world; ++r)  // rank order: every rank computes the identical value
+          sum = __fadd_rn(sum, r == A.rank ? mine[idx] : poll(recv(A.rank, r) + idx));
+        const float v = __fadd_rn(resid, sum);
+        A.x[idx] = v;
+        const float ssq = warp_sum(__fmul_rn(v, v));
+        pack_block_warp(__fmul_rn(v, w), q4, A.pack_out, kb, nblk, lane, true, ssq);
+      }
+      return;
+    }
+    const int total = A.cols * A.n;
+    for (int i = b * THREADS + tid; i < total; i += TP_FUSED_CTAS * THREADS) {
+      const int col = i / A.n, j = i - col * A.n;
+      const size_t idx = (size_t)col * A.ldp + j;
+      const float v = mine[idx];
+      for (int r = 0; r < A.world; ++r)
+        if (r != A.rank)
+          asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(recv(r, A.rank) + idx), "r"(__float_as_uint(v)), "r"(e) : "memory");
+    }
+    for (int i = b * THREADS + tid; i < total; i += TP_FUSED_CTAS * THREADS) {
+      const int col = i / A.n, j = i - col * A.n;
+      const size_t idx = (size_t)col * A.ldp + j;
+      float sum = 0.0f;
+      for (int r = 0; r < A.world; ++r) sum = __fadd_rn(sum, r == A.rank ? mine[idx] : poll(recv(A.rank, r) + idx));
+      float *dst = A.x + (size_t)col * A.ldx + j;
+      *dst = __fadd_rn(*dst, sum);
+    }
+    return;
+  }
   if (tid < A.world) {
     st_release_sys(A.peer_flags[tid] + slot + A.rank, e);  // tell rank `tid` that this rank's partial is ready
     const unsigned *mine = A.peer_flags[A.rank] + slot + tid;  // written by rank `tid`
@@ -124,7 +187,8 @@ __global__ void __launch_bounds__(THREADS) tp_allreduce_add_kernel(const TpFused
     float4 p[TP_FUSED_MAX_WORLD];
 #pragma unroll
     for (int r = 0; r < TP_FUSED_MAX_WORLD; ++r)
-      if (r < A.world) p[r] = ld_peer(reinterpret_cast<const float4 *>(A.peer_partial[r] + (size_t)col * A.ldp) + j);
+      if (r < A.world)
+        p[r] = ld_peer(reinterpret_cast<const float4 *>(A.peer_partial[r] + (size_t)col * A.ldp) + j);
     const float4 resid = *(reinterpret_cast<const float4 *>(A.x + (size_t)col * A.ldx) + j);
     float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
@@ -152,6 +216,7 @@ cudaError_t launch_tp_allreduce_add(const TpFusedArgs &a, const LaunchCfg &cfg) 
   if (!a.x || !a.peer_partial || !a.peer_flags || !a.epochs || a.world < 2 || a.world > TP_FUSED_MAX_WORLD || a.n % 4 ||
       a.ldx % 4 || a.ldp % 4 || a.buffer < 0 || a.buffer > 1)
     return cudaErrorInvalidValue;
+  if (a.peer_recv && a.cols > TP_PUSH_COLS) return cudaErrorInvalidValue;
   if (a.pack_out && (a.cols != 1 || a.n % 32 || (reinterpret_cast<uintptr_t>(a.pack_out) & 127) ||
                      (a.pack_type != RG_TYPE_Q4_0 && a.pack_type != RG_TYPE_Q8_0)))
     return cudaErrorInvalidValue;
