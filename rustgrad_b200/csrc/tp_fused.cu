@@ -68,15 +68,30 @@ __global__ void __launch_bounds__(THREADS) tp_allreduce_add_kernel(const TpFused
       return reinterpret_cast<uint2 *>(A.peer_recv[r]) + ((size_t)(A.buffer * A.world + q) * TP_PUSH_COLS) * (size_t)A.ldp;
     };
     const float *mine = A.peer_partial[A.rank];
-    auto poll = [&](const uint2 *p) {
-      for (unsigned i = 0; i < A.poll_limit; ++i) {
-        uint2 w;
-        asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(p) : "memory");
-        if (w.y == e) return __uint_as_float(w.x);
-        if (i > 256) __nanosleep(32);
+    // The words of all source ranks are requested together and looked at together: a poll round
+    // costs one trip to L2 whatever the world size.  Returns the sum in rank order (own rank from `own`).
+    auto gather_sum = [&](size_t idx, float own) {
+      const uint2 *src[TP_FUSED_MAX_WORLD];
+#pragma unroll
+      for (int r = 0; r < TP_FUSED_MAX_WORLD; ++r) src[r] = r < A.world && r != A.rank ? recv(A.rank, r) + idx : nullptr;
+      uint2 w[TP_FUSED_MAX_WORLD];
+      bool all = false;
+      for (unsigned i = 0; i < A.poll_limit && !all; ++i) {
+#pragma unroll
+        for (int r = 0; r < TP_FUSED_MAX_WORLD; ++r)
+          if (src[r]) asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(w[r].x), "=r"(w[r].y) : "l"(src[r]) : "memory");
+        all = true;
+#pragma unroll
+        for (int r = 0; r < TP_FUSED_MAX_WORLD; ++r)
+          if (src[r] && w[r].y != e) all = false;
+        if (!all && i > 256) __nanosleep(32);
       }
-      atomicExch(status, DEV_TIMEOUT);  // a rank never arrived: the host sees the status and poisons the session
-      return 0.0f;
+      if (!all) atomicExch(status, DEV_TIMEOUT);  // a rank never arrived: the host sees the status and poisons the session
+      float sum = 0.0f;
+#pragma unroll
+      for (int r = 0; r < TP_FUSED_MAX_WORLD; ++r)
+        if (r < A.world) sum = __fadd_rn(sum, r == A.rank ? own : (all ? __uint_as_float(w[r].x) : 0.0f));
+      return sum;
     };
     if (A.pack_out) {
       const int warp = tid >> 5, lane = tid & 31, nblk = A.n >> 5;
@@ -93,10 +108,7 @@ __global__ void __launch_bounds__(THREADS) tp_allreduce_add_kernel(const TpFused
         const int idx = kb * 32 + lane;
         const float resid = A.x[idx];
         const float w = A.pack_w ? __ldg(A.pack_w + idx) : 1.0f;
-        float sum = 0.0f;
-        for (int r = 0; r < A.world; ++r)  // rank order: every rank computes the identical value
-          sum = __fadd_rn(sum, r == A.rank ? mine[idx] : poll(recv(A.rank, r) + idx));
-        const float v = __fadd_rn(resid, sum);
+        const float v = __fadd_rn(resid, gather_sum((size_t)idx, mine[idx]));
         A.x[idx] = v;
         const float ssq = warp_sum(__fmul_rn(v, v));
         pack_block_warp(__fmul_rn(v, w), q4, A.pack_out, kb, nblk, lane, true, ssq);
@@ -115,10 +127,8 @@ __global__ void __launch_bounds__(THREADS) tp_allreduce_add_kernel(const TpFused
     for (int i = b * THREADS + tid; i < total; i += TP_FUSED_CTAS * THREADS) {
       const int col = i / A.n, j = i - col * A.n;
       const size_t idx = (size_t)col * A.ldp + j;
-      float sum = 0.0f;
-      for (int r = 0; r < A.world; ++r) sum = __fadd_rn(sum, r == A.rank ? mine[idx] : poll(recv(A.rank, r) + idx));
       float *dst = A.x + (size_t)col * A.ldx + j;
-      *dst = __fadd_rn(*dst, sum);
+      *dst = __fadd_rn(*dst, gather_sum(idx, mine[idx]));
     }
     return;
   }
