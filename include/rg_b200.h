@@ -251,6 +251,12 @@ int32_t rg_b200_report(const rg_session *s, rg_report *out);
 /* cudaStream_t the session launches on (for CUDA-event timing by the caller). */
 void *rg_b200_session_stream(const rg_session *s);
 
+/* The share of one tensor a tensor-parallel rank keeps (the rule rg_b200_plan_add_tensor applies):
+ * q / k / v, gate / up and the vocabulary head by output rows, attn_output / ffn_down along the
+ * contracting axis at whole blocks (32 elements, 256 for K-quants), everything else whole
+ * (src/sharding.rs:642-667).  Host arithmetic only. */
+int32_t rg_b200_tp_shard(const char *name, int32_t ggml_type, uint64_t rows, uint64_t cols, int32_t rank, int32_t world,
+                         uint64_t *row0, uint64_t *n_rows, uint64_t *col0, uint64_t *n_cols);
 /* ---- Tensor parallel plumbing (replaces CudaCollectiveGroup, src/collective.rs:322-345,441). ---- */
 int32_t rg_b200_nccl_unique_id(uint8_t out[128]);
 

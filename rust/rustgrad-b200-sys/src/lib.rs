@@ -3,7 +3,7 @@
 //!
 //! Every item mirrors a declaration of `include/rg_b200.h`, `include/rg_b200_tokenizer.h`,
 //! `include/rg_b200_workflow.h` or `include/rg_b200_serving.h`; the headers carry the documentation and, for each entry point, the
-//! rustgrad interface it stands in for.  All 94 exports are declared here.
+//! rustgrad interface it stands in for.  All 95 exports are declared here.
 #![allow(non_camel_case_types)]
 
 use core::ffi::{c_char, c_void};
@@ -319,6 +319,7 @@ unsafe extern "C" {
     pub fn rg_b200_report(s: *const rg_session, out: *mut rg_report) -> i32;
     pub fn rg_b200_session_stream(s: *const rg_session) -> *mut c_void;
     pub fn rg_b200_nccl_unique_id(out: *mut u8) -> i32;
+    pub fn rg_b200_tp_shard(name: *const c_char, ggml_type: i32, rows: u64, cols: u64, rank: i32, world: i32, row0: *mut u64, n_rows: *mut u64, col0: *mut u64, n_cols: *mut u64) -> i32;
     pub fn rg_b200_dequantize(device: i32, ggml_type: i32, bytes: *const u8, elements: usize, out: *mut f32) -> i32;
     pub fn rg_b200_qmatmul(device: i32, ggml_type: i32, weight: *const u8, n: u64, k: u64, activation: *const f32, m: u64, out: *mut f32) -> i32;
     pub fn rg_b200_row_gather(device: i32, ggml_type: i32, weight: *const u8, rows: u64, cols: u64, indices: *const i64, count: usize, out: *mut f32) -> i32;

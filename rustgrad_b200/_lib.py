@@ -48,7 +48,7 @@ EXPORTS = [
     "rg_b200_plan_tensor_nbytes", "rg_b200_plan_read_tensor", "rg_b200_plan_destroy", "rg_b200_session_prepare",
     "rg_b200_session_destroy", "rg_b200_position", "rg_b200_max_context", "rg_b200_vocab_size", "rg_b200_is_full",
     "rg_b200_reset_sequence", "rg_b200_prefill", "rg_b200_prefill_rows", "rg_b200_decode", "rg_b200_generate_greedy", "rg_b200_decode_sampled", "rg_b200_generate_sampled", "rg_b200_decode_loop", "rg_b200_decode_profile", "rg_b200_decode_profile_in_step", "rg_b200_decode_profile_projections",
-    "rg_b200_report", "rg_b200_session_stream", "rg_b200_nccl_unique_id", "rg_b200_dequantize", "rg_b200_qmatmul",
+    "rg_b200_report", "rg_b200_session_stream", "rg_b200_nccl_unique_id", "rg_b200_tp_shard", "rg_b200_dequantize", "rg_b200_qmatmul",
     "rg_b200_row_gather", "rg_b200_qmatmul_bench", "rg_b200_qgemm", "rg_b200_attention_decode", "rg_b200_attention_decode_noalloc",
     "rg_b200_reset_row", "rg_b200_prefill_select", "rg_b200_decode_rows", "rg_b200_select", "rg_b200_kv_snapshot_create",
     "rg_b200_kv_snapshot_length", "rg_b200_kv_snapshot_bytes", "rg_b200_kv_snapshot_restore", "rg_b200_kv_snapshot_free",
@@ -128,6 +128,7 @@ def load() -> C.CDLL:
     L.rg_b200_session_stream.restype = vp
     L.rg_b200_session_stream.argtypes = [vp]
     L.rg_b200_nccl_unique_id.argtypes = [u8p]
+    L.rg_b200_tp_shard.argtypes = [C.c_char_p, C.c_int32, C.c_uint64, C.c_uint64, C.c_int32, C.c_int32] + [C.POINTER(C.c_uint64)] * 4
     L.rg_b200_dequantize.argtypes = [C.c_int32, C.c_int32, u8p, C.c_size_t, f32p]
     L.rg_b200_qmatmul.argtypes = [C.c_int32, C.c_int32, u8p, C.c_uint64, C.c_uint64, f32p, C.c_uint64, f32p]
     L.rg_b200_row_gather.argtypes = [C.c_int32, C.c_int32, u8p, C.c_uint64, C.c_uint64, C.POINTER(C.c_int64),

@@ -153,6 +153,39 @@ struct rg_plan {
 
 namespace rg {
 
+// How a tensor is divided over tensor-parallel ranks, by name (Megatron split: the projections that
+// produce heads or hidden units by rows, the two that consume them along the contracting axis;
+// src/sharding.rs:642-667).
+static Split split_of(const std::string &name) {
+  auto ends = [&](const char *suffix) {
+    const size_t n = strlen(suffix);
+    return name.size() >= n && name.compare(name.size() - n, n, suffix) == 0;
+  };
+  if (name == "output.weight" || ends("attn_q.weight") || ends("attn_k.weight") || ends("attn_v.weight") ||
+      ends("ffn_gate.weight") || ends("ffn_up.weight"))
+    return SPLIT_ROWS;
+  if (ends("attn_output.weight") || ends("ffn_down.weight")) return SPLIT_COLS;
+  return SPLIT_NONE;
+}
+
+// The rank's share of a [rows, cols] tensor: whole rows, or whole blocks of every row.
+static int32_t shard_range(const std::string &name, int32_t type, uint64_t rows, uint64_t cols, Split split, uint64_t W, uint64_t R,
+                           uint64_t *r0, uint64_t *lr, uint64_t *c0, uint64_t *lc) {
+  *r0 = 0, *lr = rows, *c0 = 0, *lc = cols;
+  if (W > 1 && split == SPLIT_ROWS) {
+    if (rows % W) return fail(RG_UNSUPPORTED_GEOMETRY, name + ": rows do not divide by the tensor-parallel world size");
+    *lr = rows / W;
+    *r0 = R * *lr;
+  } else if (W > 1 && split == SPLIT_COLS) {
+    // a rank owns whole blocks of every row: 32 elements, or a 256-element K-quant super-block
+    if (cols % (W * (uint64_t)block_elements(type)))
+      return fail(RG_UNSUPPORTED_GEOMETRY, name + ": columns do not split at block boundaries");
+    *lc = cols / W;
+    *c0 = R * *lc;
+  }
+  return RG_OK;
+}
+
 static bool find_slot(rg_plan *p, const std::string &name, Slot *s) {
   const rg_llama_config &c = p->cfg;
   const uint64_t d = c.d_model, f = c.ffn_dim, qw = (uint64_t)c.n_heads * c.head_dim, kw = (uint64_t)c.n_kv_heads * c.head_dim;
@@ -165,7 +198,7 @@ static bool find_slot(rg_plan *p, const std::string &name, Slot *s) {
     return true;
   };
   if (name == "token_embd.weight") return set(&p->token_embd, c.vocab, d, false, SPLIT_NONE);
-  if (name == "output.weight") return set(&p->output, c.vocab, d, false, SPLIT_ROWS);
+  if (name == "output.weight") return set(&p->output, c.vocab, d, false, split_of(name));
   if (name == "output_norm.weight") return set(&p->output_norm, 1, d, true, SPLIT_NONE);
   if (name == "rope_freqs.weight") {
     s->ignored = true;
@@ -177,13 +210,13 @@ static bool find_slot(rg_plan *p, const std::string &name, Slot *s) {
   LayerW &L = p->layers[(size_t)layer];
   if (suffix == "attn_norm.weight") return set(&L.attn_norm, 1, d, true, SPLIT_NONE);
   if (suffix == "ffn_norm.weight") return set(&L.ffn_norm, 1, d, true, SPLIT_NONE);
-  if (suffix == "attn_q.weight") return set(&L.q, qw, d, false, SPLIT_ROWS);
-  if (suffix == "attn_k.weight") return set(&L.k, kw, d, false, SPLIT_ROWS);
-  if (suffix == "attn_v.weight") return set(&L.v, kw, d, false, SPLIT_ROWS);
-  if (suffix == "attn_output.weight") return set(&L.o, d, qw, false, SPLIT_COLS);
-  if (suffix == "ffn_gate.weight") return set(&L.gate, f, d, false, SPLIT_ROWS);
-  if (suffix == "ffn_up.weight") return set(&L.up, f, d, false, SPLIT_ROWS);
-  if (suffix == "ffn_down.weight") return set(&L.down, d, f, false, SPLIT_COLS);
+  if (suffix == "attn_q.weight") return set(&L.q, qw, d, false, split_of(name));
+  if (suffix == "attn_k.weight") return set(&L.k, kw, d, false, split_of(name));
+  if (suffix == "attn_v.weight") return set(&L.v, kw, d, false, split_of(name));
+  if (suffix == "attn_output.weight") return set(&L.o, d, qw, false, split_of(name));
+  if (suffix == "ffn_gate.weight") return set(&L.gate, f, d, false, split_of(name));
+  if (suffix == "ffn_up.weight") return set(&L.up, f, d, false, split_of(name));
+  if (suffix == "ffn_down.weight") return set(&L.down, d, f, false, split_of(name));
   // present only in the variant the configuration names (model.rs:427-449)
   const uint64_t hd = (uint64_t)c.head_dim;
   if (c.qk_norm && suffix == "attn_q_norm.weight") return set(&L.q_norm, 1, c.qk_norm == 1 ? hd : qw, true, SPLIT_NONE);
@@ -206,20 +239,7 @@ static int32_t check_tensor(rg_plan *p, const std::string &name, int32_t type, u
                                        "], got [" + std::to_string(rows) + "," + std::to_string(cols) + "]");
   if (cols % (uint64_t)block_elements(type)) return fail(RG_SHAPE_MISMATCH, name + ": columns are not a multiple of the block size");
   if (slot->t && slot->t->type >= 0) return fail(RG_INVALID_ARGUMENT, name + ": tensor bound twice");
-  const uint64_t W = (uint64_t)p->tp_world, R = (uint64_t)p->tp_rank;
-  *r0 = 0, *lr = rows, *c0 = 0, *lc = cols;
-  if (W > 1 && slot->split == SPLIT_ROWS) {
-    if (rows % W) return fail(RG_UNSUPPORTED_GEOMETRY, name + ": rows do not divide by the tensor-parallel world size");
-    *lr = rows / W;
-    *r0 = R * *lr;
-  } else if (W > 1 && slot->split == SPLIT_COLS) {
-    // a rank owns whole blocks of every row: 32 elements, or a 256-element K-quant super-block
-    if (cols % (W * (uint64_t)block_elements(type)))
-      return fail(RG_UNSUPPORTED_GEOMETRY, name + ": columns do not split at block boundaries");
-    *lc = cols / W;
-    *c0 = R * *lc;
-  }
-  return RG_OK;
+  return shard_range(name, type, rows, cols, slot->split, (uint64_t)p->tp_world, (uint64_t)p->tp_rank, r0, lr, c0, lc);
 }
 
 }  // namespace rg
@@ -1512,6 +1532,15 @@ int32_t rg_b200_plan_create(const rg_llama_config *c, const rg_options *o, rg_pl
   p->layers.resize((size_t)c->n_layers);
   *out = p.release();
   return RG_OK;
+}
+
+int32_t rg_b200_tp_shard(const char *name, int32_t type, uint64_t rows, uint64_t cols, int32_t rank, int32_t world, uint64_t *row0,
+                         uint64_t *n_rows, uint64_t *col0, uint64_t *n_cols) {
+  if (!name || !row0 || !n_rows || !col0 || !n_cols) return fail(RG_INVALID_ARGUMENT, "null argument");
+  if (world < 1 || rank < 0 || rank >= world) return fail(RG_INVALID_ARGUMENT, "rank out of range");
+  if (!block_elements(type)) return fail(RG_UNSUPPORTED_TYPE, std::string(name) + ": ggml type " + std::to_string(type) + " is not supported");
+  if (cols % (uint64_t)block_elements(type)) return fail(RG_SHAPE_MISMATCH, std::string(name) + ": columns are not a multiple of the block size");
+  return shard_range(name, type, rows, cols, split_of(name), (uint64_t)world, (uint64_t)rank, row0, n_rows, col0, n_cols);
 }
 
 int32_t rg_b200_plan_add_tensor(rg_plan *p, const char *name, int32_t type, uint64_t rows, uint64_t cols, const uint8_t *bytes,

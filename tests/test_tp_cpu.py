@@ -62,8 +62,23 @@ def test_two_rank_split_reproduces_the_unsharded_projection(tmp_path):
 
 
 def test_split_rejects_shapes_that_would_cut_a_block():
+    from rustgrad_b200 import session
     data = np.zeros(18 * 3 * 4, np.uint8)
-    with pytest.raises(ValueError):
+    with pytest.raises(session.UnsupportedGeometry):
         tp.shard("blk.0.ffn_down.weight", quant.Q4_0, 4, 96, data, 0, 2)   # 96 / 2 = 48: not whole blocks
-    with pytest.raises(ValueError):
+    with pytest.raises(session.UnsupportedGeometry):
         tp.shard("blk.0.attn_q.weight", quant.Q4_0, 3, 128, np.zeros(18 * 4 * 3, np.uint8), 0, 2)
+    with pytest.raises(session.UnsupportedGeometry):  # a K-quant super-block holds 256 elements: 512 / 4 cuts one
+        tp.shard_range("blk.0.attn_output.weight", quant.Q4_K, 8, 512, 0, 4)
+
+
+def test_split_ranges_by_name_and_type():
+    # rows for the projections that produce heads / hidden units and the head, the contracting axis for
+    # the two that consume them, everything else whole
+    assert tp.shard_range("blk.3.attn_k.weight", quant.Q8_0, 1024, 4096, 3, 8) == (384, 128, 0, 4096)
+    assert tp.shard_range("output.weight", quant.Q8_0, 128256, 4096, 1, 2) == (64128, 64128, 0, 4096)
+    assert tp.shard_range("blk.0.ffn_down.weight", quant.Q4_0, 8192, 28672, 5, 8) == (0, 8192, 17920, 3584)
+    assert tp.shard_range("blk.0.attn_output.weight", quant.Q4_K, 8, 1024, 1, 4) == (0, 8, 256, 256)
+    assert tp.shard_range("token_embd.weight", quant.Q8_0, 100, 64, 1, 2) == (0, 100, 0, 64)
+    assert tp.shard_range("blk.0.attn_norm.weight", quant.F32, 1, 64, 1, 2) == (0, 1, 0, 64)
+    assert tp.shard_range("blk.0.ffn_up.weight", quant.Q4_0, 96, 512, 0, 1) == (0, 96, 0, 512)
