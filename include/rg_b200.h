@@ -108,7 +108,7 @@ typedef struct {
   uint64_t kv_bytes;          /* KV cache bytes on this rank */
   uint64_t fallback_count;    /* always 0: there is no CPU or library fallback */
   float last_prefill_ms;      /* CUDA-event time of the last prefill call */
-  float last_decode_ms;       /* CUDA-event time of the last decode step */
+  float last_decode_ms;       /* last decode: host-clock time of the call (host-driven verbs), CUDA-event time per step (decode_loop) */
   uint64_t peer_reduce_launches; /* tensor-parallel partial sums done by the peer-memory kernel (0: NCCL path) */
 } rg_report;
 

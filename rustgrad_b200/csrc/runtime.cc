@@ -15,6 +15,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <chrono>
 #include <map>
 #include <memory>
 #include <string>
@@ -312,6 +313,7 @@ struct rg_session {
   std::vector<void *> owned;  // everything to cudaFree
   // pinned host staging
   Ctrl *h_ctrl = nullptr;
+  int32_t *h_result = nullptr;  // pinned: [status, pad x 3, ids / id history]
   int32_t *h_ids = nullptr;
   int *h_status = nullptr;
   float *h_logits = nullptr;
@@ -350,8 +352,7 @@ struct rg_session {
     for (void *p : tp_ipc_opened) cudaIpcCloseMemHandle(p);
     for (void *p : owned) cudaFree(p);
     if (h_ctrl) cudaFreeHost(h_ctrl);
-    if (h_ids) cudaFreeHost(h_ids);
-    if (h_status) cudaFreeHost(h_status);
+    if (h_result) cudaFreeHost(h_result);
     if (h_logits) cudaFreeHost(h_logits);
     if (ev0) cudaEventDestroy(ev0);
     if (ev1) cudaEventDestroy(ev1);
@@ -1357,10 +1358,11 @@ static int32_t upload_ctrl(rg_session *s) {
 
 // Reads back the status word and `n` greedy ids; maps device findings to typed statuses.
 static int32_t finish_step(rg_session *s, int n_ids, float *logits_out, int n_logit_rows) {
-  RG_CUDA(x_memcpy_async(s->h_status, s->d_status, sizeof(int), cudaMemcpyDeviceToHost, s->stream));
-  if (n_ids > 0) RG_CUDA(x_memcpy_async(s->h_ids, s->d_ids, sizeof(int32_t) * (size_t)n_ids, cudaMemcpyDeviceToHost, s->stream));
-  s->report.d2h_calls += 1 + (n_ids > 0);
-  s->report.d2h_bytes += sizeof(int) + sizeof(int32_t) * (size_t)n_ids;
+  // status word and ids lie side by side on both sides: one copy
+  const size_t res_bytes = sizeof(int32_t) * (n_ids > 0 ? 4 + (size_t)n_ids : 1);
+  RG_CUDA(x_memcpy_async(s->h_result, s->d_status, res_bytes, cudaMemcpyDeviceToHost, s->stream));
+  s->report.d2h_calls += 1;
+  s->report.d2h_bytes += res_bytes;
   if (logits_out && n_logit_rows > 0) {
     const size_t bytes = sizeof(float) * (size_t)n_logit_rows * (size_t)s->cfg.vocab;
     RG_CUDA(x_memcpy_async(s->h_logits, s->logits, bytes, cudaMemcpyDeviceToHost, s->stream));
@@ -1760,10 +1762,16 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
 #define RG_TRY(e)            \
   if ((rc = (e))) return rc;
   RG_TRY(dalloc(s.get(), &s->d_ctrl, 1));
-  RG_TRY(dalloc(s.get(), &s->d_ids, BMAX));
+  {
+    // status word and selected ids side by side: a host-driven step reads both back with one copy
+    int32_t *res = nullptr;
+    RG_TRY(dalloc(s.get(), &res, 4 + BMAX));
+    s->d_status = reinterpret_cast<int *>(res);
+    s->d_ids = res + 4;
+  }
   s->history_cap = 8192;
   RG_TRY(dalloc(s.get(), &s->d_history, (size_t)s->history_cap * BMAX));
-  RG_TRY(dalloc(s.get(), &s->d_status, 1));
+
   // per-column buffers are sized for the widest forward (a 1024-token prefill chunk)
   RG_TRY(dalloc(s.get(), &s->x, (size_t)WMAX * d));
   RG_TRY(dalloc(s.get(), &s->xn_f32, (size_t)MAXC * d));
@@ -1853,8 +1861,9 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   RG_CUDA(cudaMemsetAsync(s->d_status, 0, sizeof(int), s->stream));
   RG_CUDA(cudaMemsetAsync(s->d_ctrl, 0, sizeof(Ctrl), s->stream));
   RG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&s->h_ctrl), sizeof(Ctrl)));
-  RG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&s->h_ids), sizeof(int32_t) * (size_t)s->history_cap * BMAX));
-  RG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&s->h_status), sizeof(int)));
+  RG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&s->h_result), sizeof(int32_t) * (4 + (size_t)s->history_cap * BMAX)));
+  s->h_status = reinterpret_cast<int *>(s->h_result);  // same head as the device block: [status, pad x 3, ids ...]
+  s->h_ids = s->h_result + 4;
   RG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&s->h_logits), sizeof(float) * (size_t)BMAX * c.vocab));
   memset(s->h_ctrl, 0, sizeof(Ctrl));
   RG_CUDA(cudaStreamSynchronize(s->stream));
@@ -2096,13 +2105,13 @@ static int32_t decode_impl(rg_session *s, const int32_t *tokens, int32_t batch, 
     rg_session *s;
     ~Disarm() { s->sample_uniforms = nullptr; }
   } disarm{s};
-  RG_CUDA(cudaEventRecord(s->ev0, s->stream));
+  // (timed with the host clock: two event records and a query would cost a step several microseconds)
+  const auto t0 = std::chrono::steady_clock::now();
   if ((rc = upload_ctrl(s))) return rc;
   if ((rc = run_step(s, batch, batch, true, uniforms == nullptr))) return rc;  // the captured graph selects greedily
-  RG_CUDA(cudaEventRecord(s->ev1, s->stream));
   rc = finish_step(s, batch, logits, logits ? batch : 0);
   if (rc && rc != RG_NON_FINITE_LOGITS) return rc;
-  cudaEventElapsedTime(&s->report.last_decode_ms, s->ev0, s->ev1);
+  s->report.last_decode_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
   if (rc) return rc;  // non-finite logits: position unchanged (metal_generation.rs:892-898)
   if (greedy) memcpy(greedy, s->h_ids, sizeof(int32_t) * (size_t)batch);
   for (int i = 0; i < batch; ++i) s->position[(size_t)i] += 1;
@@ -2186,13 +2195,12 @@ int32_t rg_b200_decode_rows(rg_session *s, const int32_t *rows, const int32_t *t
     rg_session *s;
     ~Disarm() { s->sample_uniforms = nullptr, s->sample_temps = nullptr; }
   } disarm{s};
-  RG_CUDA(cudaEventRecord(s->ev0, s->stream));
+  const auto t0 = std::chrono::steady_clock::now();
   if ((rc = upload_ctrl(s))) return rc;
   if ((rc = run_step(s, n, n, true, s->sample_uniforms == nullptr))) return rc;
-  RG_CUDA(cudaEventRecord(s->ev1, s->stream));
   rc = finish_step(s, n, logits, logits ? n : 0);
   if (rc && rc != RG_NON_FINITE_LOGITS) return rc;
-  cudaEventElapsedTime(&s->report.last_decode_ms, s->ev0, s->ev1);
+  s->report.last_decode_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
   if (rc) return rc;
   if (ids) memcpy(ids, s->h_ids, sizeof(int32_t) * (size_t)n);
   for (int i = 0; i < n; ++i) s->position[(size_t)rows[i]] += 1;

@@ -285,6 +285,17 @@ class LlamaCudaSession:
     def decode(self, tokens, want_logits: bool = False, temperature: float | None = None, uniforms=None):
         """One step for ``len(tokens)`` rows.  With ``temperature`` and ``uniforms`` ([rows, vocab]) the ids are
         Gumbel-max samples (LlamaSampling::GumbelMax, generation.rs:10-19), otherwise greedy."""
+        if not want_logits and uniforms is None and len(tokens) <= 32:
+            # greedy ids only: reused ctypes arrays, no array objects per step
+            io = self.__dict__.get("_step_io")
+            if io is None:
+                io = self.__dict__["_step_io"] = ((C.c_int32 * 32)(), (C.c_int32 * 32)())
+            tin, tout = io
+            b = len(tokens)
+            for i in range(b):
+                tin[i] = int(tokens[i])
+            check(self._L.rg_b200_decode(self._h, tin, b, None, tout))
+            return None, np.array(tout[:b], dtype=np.int32)
         tokens = np.ascontiguousarray(tokens, dtype=np.int32)
         b = tokens.size
         logits = np.empty((b, self.vocab_size()), dtype=np.float32) if want_logits else None
