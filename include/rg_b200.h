@@ -126,7 +126,7 @@ const char *rg_b200_last_error(void);
  * fail-after-N knobs (src/cuda.rs:5895-5960).  Never makes the GPU itself fault. */
 int32_t rg_b200_test_fail_after(const char *what, int32_t n);
 /* How many launches of a kernel family this process has made: "qgemv_i8", "qgemv", "qgemm_tc",
- * "qgemm_tc_wide", "attn_fused", "attn_prefill", "attn_split", "tp_exchange", "kquant_gemv",
+ * "qgemm_tc_wide", "attn_fused", "attn_prefill" (both forms; "attn_prefill_tc" the tensor-core form alone), "attn_split", "tp_exchange", "kquant_gemv",
  * "dense_gemv"; UINT64_MAX for an unknown name.  Evidence for tests and reports of which kernel
  * served a call (the role of MetalDeviceRunReport's dispatch counts, src/runtime/metal/session.rs:145-185). */
 uint64_t rg_b200_launch_count(const char *kernel);

@@ -12,6 +12,7 @@
 // token, which is what makes a 2048-token prompt cheap.
 #include <cuda_fp16.h>
 #include <math.h>
+#include <stdlib.h>
 
 #include "../../include/rg_b200.h"
 #include "kernels.h"
@@ -252,7 +253,13 @@ cudaError_t launch_attention_prefill(const PrefillAttnArgs &a, const LaunchCfg &
   if (!prefill_attention_supported(a.heads, a.kv_heads, HD) || !a.q || !a.k_cache || !a.v_cache || !a.out || a.cols < 1 ||
       a.pos0 < 0 || a.pos0 + a.cols > a.ctx)
     return cudaErrorInvalidValue;
-  return a.kv_f32 ? launch_g<float>(a, cfg) : launch_g<__half>(a, cfg);
+  if (a.kv_f32) return launch_g<float>(a, cfg);
+  // f16 caches: K and V rows are exact tensor-core operands (attn_prefill_tc.cu)
+  static const bool simt = [] {
+    const char *v = getenv("RG_B200_PREFILL_ATTN_F32");
+    return v && *v && *v != '0';
+  }();
+  return simt ? launch_g<__half>(a, cfg) : launch_attention_prefill_tc(a, cfg);
 }
 
 }  // namespace rg

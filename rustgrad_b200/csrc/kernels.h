@@ -31,7 +31,7 @@ struct DeviceOnce {
 // Launch counters per kernel family (process-wide), so a test can prove which kernel served a call.
 enum LaunchCounter {
   LC_QGEMV_I8 = 0, LC_QGEMV, LC_QGEMM_TC, LC_QGEMM_TC_WIDE, LC_ATTN_FUSED, LC_ATTN_PREFILL, LC_ATTN_SPLIT, LC_TP_EXCHANGE,
-  LC_KQUANT_GEMV, LC_DENSE_GEMV, LC_COUNT
+  LC_KQUANT_GEMV, LC_DENSE_GEMV, LC_ATTN_PREFILL_TC, LC_COUNT
 };
 void count_launch(int which);
 
@@ -287,6 +287,8 @@ struct PrefillAttnArgs {
 };
 bool prefill_attention_supported(int heads, int kv_heads, int hd);
 cudaError_t launch_attention_prefill(const PrefillAttnArgs &a, const LaunchCfg &cfg);
+// Tensor-core form for f16 caches (attn_prefill_tc.cu); launch_attention_prefill dispatches to it.
+cudaError_t launch_attention_prefill_tc(const PrefillAttnArgs &a, const LaunchCfg &cfg);
 
 // Greedy selection per column with the reference's rules (generation.rs:260-287): lowest id wins
 // ties, any non-finite logit yields -1.  Also advances: next_tokens[c] = id, pos[c] += 1 when

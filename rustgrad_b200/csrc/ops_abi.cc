@@ -26,7 +26,7 @@ using namespace rg;
 
 extern "C" uint64_t rg_b200_launch_count(const char *kernel) {
   static const char *names[LC_COUNT] = {"qgemv_i8", "qgemv", "qgemm_tc", "qgemm_tc_wide", "attn_fused", "attn_prefill",
-                                        "attn_split", "tp_exchange", "kquant_gemv", "dense_gemv"};
+                                        "attn_split", "tp_exchange", "kquant_gemv", "dense_gemv", "attn_prefill_tc"};
   if (!kernel) return 0;
   for (int i = 0; i < LC_COUNT; ++i)
     if (!strcmp(kernel, names[i])) return g_launch_counts[i].load(std::memory_order_relaxed);

@@ -745,3 +745,26 @@ def test_batched_prompt_prefill_matches_per_prompt_prefill(small_hd128, tiny):
     s = make_session(tdata, kv_f32=True, max_batch=3)
     check(s, {1: synth.prompt_ids(tcfg, 12, seed=11), 0: synth.prompt_ids(tcfg, 5, seed=12), 2: synth.prompt_ids(tcfg, 20, seed=13)},
           tcfg, ttensors, O.MODE_STRICT)
+
+
+@pytest.mark.parametrize("heads,kv_heads", [(4, 1), (4, 2), (2, 2), (8, 1)])
+def test_prompt_attention_on_tensor_cores_with_f16_cache(heads, kv_heads):
+    """Prompt chunks of a session with the f16 cache run the tensor-core attention kernel
+    (attn_prefill_tc.cu): 1, 2, 4 and 8 query heads per kv head, a chunk whose last tile is ragged
+    (700 tokens), a second chunk that sees 1024 cached positions (1030 tokens), and the same prompt
+    through the f32 kernel; against the checker with an f16 cache."""
+    cfg = synth.scaled(synth.TINY, d_model=heads * 128, n_heads=heads, n_kv_heads=kv_heads, head_dim=128, ffn_dim=512, vocab=320,
+                       n_layers=2, rope_theta=500000.0, max_context=1100)
+    tensors = synth.build_tensors(cfg, seed=31, body_type=quant.Q8_0)
+    oracle = O.OracleModel(cfg, tensors, kv_f16=True, threads=4)
+    for n in (700, 1030):
+        prompt = synth.prompt_ids(cfg, n, seed=n)
+        s = session.LlamaCudaPlan.from_tensors(cfg, tensors, session.CudaSessionTarget(max_context=1100)).prepare()
+        before = session.launch_count("attn_prefill_tc")
+        got = s.prefill_ids(prompt)
+        assert session.launch_count("attn_prefill_tc") >= before + cfg["n_layers"]
+        oracle.reset()
+        want = oracle.forward(prompt, O.MODE_FAST)
+        assert_logits_close(got, want)
+        tok = O.select_greedy(want)
+        assert_logits_close(s.run_token(tok), oracle.forward([tok], O.MODE_FAST))   # the cache rows it left are the checker's
