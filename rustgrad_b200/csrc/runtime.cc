@@ -104,6 +104,9 @@ struct DevTensor {
 struct LayerW {
   DevTensor attn_norm, q, k, v, o, ffn_norm, gate, up, down;
   DevTensor q_norm, k_norm, q_bias, k_bias, v_bias;  // model variants only (f32 vectors)
+  // q, k, v (gate, up) lie one after the other in ONE allocation: the tensor-core path then runs
+  // them as a single GEMM over the stacked rows, which fills the SMs' waves better than 3 (2) launches
+  bool qkv_stacked = false, gu_stacked = false;
 };
 
 enum Split { SPLIT_NONE, SPLIT_ROWS, SPLIT_COLS };
@@ -901,9 +904,16 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
     prof_mark(s, PROF_OTHER);
     RG_LAUNCH(s, launch_rmsnorm16(s->x, d, reinterpret_cast<const float *>(W.attn_norm.d), d, c.norm_eps, ncols, xop,
                                   (tp_lib && l > 0) ? plain : L));
-    if ((rc = gemm_tc(s, W.q, ncols, s->qkv, qkv_w, L))) return rc;
-    if ((rc = gemm_tc(s, W.k, ncols, s->qkv + qw, qkv_w, L))) return rc;
-    if ((rc = gemm_tc(s, W.v, ncols, s->qkv + qw + kw, qkv_w, L))) return rc;
+    if (W.qkv_stacked && ncols > BMAX) {  // one GEMM over the stacked rows of q | k | v
+      DevTensor all = W.q;
+      all.rows = W.q.rows + W.k.rows + W.v.rows;
+      all.nbytes = W.q.nbytes + W.k.nbytes + W.v.nbytes;
+      if ((rc = gemm_tc(s, all, ncols, s->qkv, qkv_w, L))) return rc;
+    } else {
+      if ((rc = gemm_tc(s, W.q, ncols, s->qkv, qkv_w, L))) return rc;
+      if ((rc = gemm_tc(s, W.k, ncols, s->qkv + qw, qkv_w, L))) return rc;
+      if ((rc = gemm_tc(s, W.v, ncols, s->qkv + qw + kw, qkv_w, L))) return rc;
+    }
     prof_mark(s, PROF_ATTN);
     if (!s->chunk_is_prompt && ncols <= BMAX && s->attn_counters && !s->variant) {
       // a decode batch: RoPE, cache append, split attention and the combine in one launch
@@ -992,10 +1002,19 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
     prof_mark(s, PROF_OTHER);
     RG_LAUNCH(s, launch_rmsnorm16(s->x, d, reinterpret_cast<const float *>(W.ffn_norm.d), d, c.norm_eps, ncols, xop,
                                   tp_lib ? plain : L));
-    if ((rc = gemm_tc(s, W.gate, ncols, s->gate_f32, s->ffn_l, L))) return rc;
-    if ((rc = gemm_tc(s, W.up, ncols, s->up_f32, s->ffn_l, L))) return rc;
-    prof_mark(s, PROF_OTHER);
-    RG_LAUNCH(s, launch_swiglu16(s->gate_f32, s->up_f32, s->ffn_l, s->ffn_l, ncols, xop, L));
+    if (W.gu_stacked && ncols > BMAX) {  // one GEMM over gate | up: token rows of [gate, up] side by side
+      DevTensor all = W.gate;
+      all.rows = W.gate.rows + W.up.rows;
+      all.nbytes = W.gate.nbytes + W.up.nbytes;
+      if ((rc = gemm_tc(s, all, ncols, s->gate_f32, 2 * s->ffn_l, L))) return rc;
+      prof_mark(s, PROF_OTHER);
+      RG_LAUNCH(s, launch_swiglu16(s->gate_f32, s->gate_f32 + s->ffn_l, s->ffn_l, 2 * s->ffn_l, ncols, xop, L));
+    } else {
+      if ((rc = gemm_tc(s, W.gate, ncols, s->gate_f32, s->ffn_l, L))) return rc;
+      if ((rc = gemm_tc(s, W.up, ncols, s->up_f32, s->ffn_l, L))) return rc;
+      prof_mark(s, PROF_OTHER);
+      RG_LAUNCH(s, launch_swiglu16(s->gate_f32, s->up_f32, s->ffn_l, s->ffn_l, ncols, xop, L));
+    }
     if ((rc = gemm_tc(s, W.down, ncols, s->tp_part[1], d, L))) return rc;
     if (tp) {
       if ((rc = tp_reduce_add(s, ncols, 1))) return rc;
@@ -1789,8 +1808,9 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   }
   RG_TRY(dalloc(s.get(), &s->partial, (size_t)WMAX * d));
   s->tp_part[0] = s->tp_part[1] = s->partial;
-  RG_TRY(dalloc(s.get(), &s->gate_f32, (size_t)WMAX * s->ffn_l));
-  RG_TRY(dalloc(s.get(), &s->up_f32, (size_t)WMAX * s->ffn_l));
+  // one allocation: two [WMAX][ffn] halves, or (stacked gate|up GEMM) [tokens][2 ffn] rows
+  RG_TRY(dalloc(s.get(), &s->gate_f32, (size_t)2 * WMAX * s->ffn_l));
+  s->up_f32 = s->gate_f32 + (size_t)WMAX * s->ffn_l;
   RG_TRY(dalloc(s.get(), &s->h_f32, (size_t)MAXC * s->ffn_l));
   RG_TRY(dalloc(s.get(), &s->logits, (size_t)BMAX * c.vocab));
   RG_TRY(dalloc(s.get(), &s->logits_l, (size_t)BMAX * s->vocab_l));
@@ -1881,10 +1901,50 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   own(s->token_embd);
   own(s->output_norm);
   own(s->output);
-  for (auto &L : s->layers)
-    for (DevTensor *t : {&L.attn_norm, &L.q, &L.k, &L.v, &L.o, &L.ffn_norm, &L.gate, &L.up, &L.down, &L.q_norm, &L.k_norm, &L.q_bias,
-                         &L.k_bias, &L.v_bias})
-      own(*t);
+  // Tensors that one tensor-core GEMM can take together are copied into one allocation (device to
+  // device, once): same block type, same K, every part a whole number of 256-row tiles.
+  auto stack = [&](std::initializer_list<DevTensor *> parts) -> bool {
+    const DevTensor *first = *parts.begin();
+    size_t total = 0;
+    for (const DevTensor *t : parts) {
+      if (!t->packed() || t->type != first->type || t->cols != first->cols || t->rows % 256) return false;
+      total += t->nbytes;
+    }
+    uint8_t *block = nullptr;
+    if (x_malloc(reinterpret_cast<void **>(&block), total) != cudaSuccess) {
+      cudaGetLastError();
+      return false;  // not enough memory for the second copy during the move: the tensors stay where they are
+    }
+    size_t off = 0;
+    for (DevTensor *t : parts) {
+      if (cudaMemcpy(block + off, t->d, t->nbytes, cudaMemcpyDeviceToDevice) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(block);
+        return false;
+      }
+      off += t->nbytes;
+    }
+    off = 0;
+    for (DevTensor *t : parts) {
+      cudaFree(t->d);
+      t->d = block + off;
+      off += t->nbytes;
+    }
+    s->owned.push_back(block);
+    return true;
+  };
+  const bool stacking = wide_path_ok(s.get()) && !env_flag("RG_B200_NO_STACKED_GEMM");
+  for (auto &L : s->layers) {
+    if (stacking) {
+      L.qkv_stacked = stack({&L.q, &L.k, &L.v});
+      L.gu_stacked = stack({&L.gate, &L.up});
+    }
+    for (DevTensor *t : {&L.attn_norm, &L.o, &L.ffn_norm, &L.down, &L.q_norm, &L.k_norm, &L.q_bias, &L.k_bias, &L.v_bias}) own(*t);
+    if (!L.qkv_stacked)
+      for (DevTensor *t : {&L.q, &L.k, &L.v}) own(*t);
+    if (!L.gu_stacked)
+      for (DevTensor *t : {&L.gate, &L.up}) own(*t);
+  }
   p->consumed = true;
   s->position.assign((size_t)s->max_batch, 0);
   s->report.weight_bytes = s->weight_bytes;

@@ -694,12 +694,12 @@ def test_batched_prompt_prefill_matches_per_prompt_prefill(small_hd128, tiny):
     mk = lambda **kw: session.LlamaCudaPlan.from_tensors(  # noqa: E731
         cfg, tensors, session.CudaSessionTarget(kv_f32=True, max_context=1100, **kw)).prepare()
 
-    def check(s, prompts, model_cfg, model_tensors, mode=O.MODE_FAST):
+    def check(s, prompts, model_cfg, model_tensors, mode=O.MODE_FAST, kv_f16=False):
         before = {r: s.position(r) for r in prompts}
         logits, greedy = s.prefill_rows(prompts)
         oracles = {}
         for i, (row, p) in enumerate(prompts.items()):
-            o = oracles[row] = O.OracleModel(model_cfg, model_tensors, threads=4)
+            o = oracles[row] = O.OracleModel(model_cfg, model_tensors, kv_f16=kv_f16, threads=4)
             want = o.forward(p, mode)
             assert_logits_close(logits[i], want)
             assert int(greedy[i]) == O.select_greedy(want)
@@ -721,6 +721,12 @@ def test_batched_prompt_prefill_matches_per_prompt_prefill(small_hd128, tiny):
     s = mk(max_batch=3)
     check(s, {0: synth.prompt_ids(cfg, 700, seed=6), 1: synth.prompt_ids(cfg, 500, seed=7), 2: synth.prompt_ids(cfg, 30, seed=8)},
           cfg, tensors)
+    # the same with the f16 cache: every run of the chunk goes through the tensor-core attention kernel
+    s = session.LlamaCudaPlan.from_tensors(cfg, tensors, session.CudaSessionTarget(max_context=1100, max_batch=3)).prepare()
+    before = session.launch_count("attn_prefill_tc")
+    check(s, {2: synth.prompt_ids(cfg, 90, seed=14), 0: synth.prompt_ids(cfg, 33, seed=15), 1: synth.prompt_ids(cfg, 200, seed=16)},
+          cfg, tensors, kv_f16=True)
+    assert session.launch_count("attn_prefill_tc") == before + 3 * cfg["n_layers"]
     # a row that already holds positions continues from them
     s = mk(max_batch=2)
     head, tail = synth.prompt_ids(cfg, 9, seed=9), synth.prompt_ids(cfg, 20, seed=10)
