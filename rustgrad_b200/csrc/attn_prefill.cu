@@ -248,18 +248,26 @@ bool prefill_attention_supported(int heads, int kv_heads, int hd) {
   return g == 1 || g == 2 || g == 4 || g == 8;
 }
 
-cudaError_t launch_attention_prefill(const PrefillAttnArgs &a, const LaunchCfg &cfg) {
-  count_launch(LC_ATTN_PREFILL);
-  if (!prefill_attention_supported(a.heads, a.kv_heads, HD) || !a.q || !a.k_cache || !a.v_cache || !a.out || a.cols < 1 ||
-      a.pos0 < 0 || a.pos0 + a.cols > a.ctx)
-    return cudaErrorInvalidValue;
-  if (a.kv_f32) return launch_g<float>(a, cfg);
-  // f16 caches: K and V rows are exact tensor-core operands (attn_prefill_tc.cu)
+static bool prefill_simt_forced() {
   static const bool simt = [] {
     const char *v = getenv("RG_B200_PREFILL_ATTN_F32");
     return v && *v && *v != '0';
   }();
-  return simt ? launch_g<__half>(a, cfg) : launch_attention_prefill_tc(a, cfg);
+  return simt;
+}
+
+// f16 caches: K and V rows are exact tensor-core operands (attn_prefill_tc.cu)
+bool prefill_attention_uses_tc(const PrefillAttnArgs &a) { return !a.kv_f32 && !prefill_simt_forced(); }
+
+cudaError_t launch_attention_prefill(const PrefillAttnArgs &a, const LaunchCfg &cfg) {
+  count_launch(LC_ATTN_PREFILL);
+  const bool tc = prefill_attention_uses_tc(a);
+  if (!prefill_attention_supported(a.heads, a.kv_heads, HD) || !a.q || !a.k_cache || !a.v_cache || a.cols < 1 || a.pos0 < 0 ||
+      a.pos0 + a.cols > a.ctx)
+    return cudaErrorInvalidValue;
+  if (a.out16_hi ? (!tc || a.out16_ld < a.heads * HD || (a.out16_ld & 1)) : !a.out) return cudaErrorInvalidValue;
+  if (a.kv_f32) return launch_g<float>(a, cfg);
+  return tc ? launch_attention_prefill_tc(a, cfg) : launch_g<__half>(a, cfg);
 }
 
 }  // namespace rg

@@ -15,6 +15,7 @@
 //    fragment), again as hi + lo planes; V rows are exact f16, read transposed by ldmatrix.
 // Every f16 x f16 product is exact in the f32 accumulator, so what differs from the f32 kernel is
 // the order of the sums and the 2^-22 tail of q and p.
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math.h>
 #include <stdint.h>
@@ -53,6 +54,12 @@ __device__ __forceinline__ void split2(float x0, float x1, uint32_t &hi, uint32_
   const __half2 l = __floats2half2_rn(x0 - hf.x, x1 - hf.y);
   hi = *reinterpret_cast<const uint32_t *>(&h);
   lo = *reinterpret_cast<const uint32_t *>(&l);
+}
+
+// f32 -> f16 as the GEMM operand conversion does it: finite values beyond the f16 range saturate
+__device__ __forceinline__ __half f16_sat(float v) {
+  if (fabsf(v) > 65504.0f && fabsf(v) < __int_as_float(0x7f800000)) v = copysignf(65504.0f, v);
+  return __float2half_rn(v);
 }
 
 template <int G>
@@ -205,7 +212,28 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc_kernel(const PrefillA
     const int r = 16 * warp + g + 8 * h, head = r / TQ, tok = r - head * TQ;
     if (tok >= nq) continue;
     const float inv = __frcp_rn(l_run[h]);
-    float *dst = A.out + (size_t)(t0 + tok) * A.heads * HD + (size_t)(kvh * G + head) * HD + 2 * t;
+    const size_t col = (size_t)(kvh * G + head) * HD + 2 * t;
+    if (A.out16_hi) {  // the operand planes of the output projection, rounded as the f32 -> operand conversion rounds
+      const size_t at = (size_t)(t0 + tok) * A.out16_ld + col;
+      uint16_t *hi = static_cast<uint16_t *>(A.out16_hi) + at;
+      uint16_t *lo = A.out16_lo ? static_cast<uint16_t *>(A.out16_lo) + at : nullptr;
+#pragma unroll
+      for (int n = 0; n < HD / 8; ++n) {
+        const float v0 = __fmul_rn(o[n][2 * h], inv), v1 = __fmul_rn(o[n][2 * h + 1], inv);
+        if (A.out16_f16) {
+          const __half h0 = f16_sat(v0), h1 = f16_sat(v1);
+          *reinterpret_cast<uint32_t *>(hi + 8 * n) = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+          if (lo)
+            *reinterpret_cast<uint32_t *>(lo + 8 * n) = (uint32_t)__half_as_ushort(f16_sat(v0 - __half2float(h0))) |
+                                                         ((uint32_t)__half_as_ushort(f16_sat(v1 - __half2float(h1))) << 16);
+        } else {
+          *reinterpret_cast<uint32_t *>(hi + 8 * n) = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v0)) |
+                                                       ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v1)) << 16);
+        }
+      }
+      continue;
+    }
+    float *dst = A.out + (size_t)(t0 + tok) * A.heads * HD + col;
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n)
       *reinterpret_cast<float2 *>(dst + 8 * n) = make_float2(__fmul_rn(o[n][2 * h], inv), __fmul_rn(o[n][2 * h + 1], inv));

@@ -122,6 +122,7 @@ struct QGemmArgs {
   int ldc = 0;
   int splits = 1;
   size_t split_stride = 0;
+  bool accumulate = false;  // out += x . W^T (a projection whose result is added to the residual stream); splits must be 1
 };
 cudaError_t launch_qgemm_tc(const QGemmArgs &a, const LaunchCfg &cfg);
 // 128 x 512 tiles with the A operand in shared memory (qgemm_tc_wide.cu): single-operand modes, Q4_0, m > 256
@@ -284,7 +285,15 @@ struct PrefillAttnArgs {
   bool kv_f32 = false;
   int cols = 0, heads = 0, kv_heads = 0, ctx = 0, seq = 0, pos0 = 0;
   float *out = nullptr;
+  // Tensor-core form only: when out16_hi is set the result goes straight to the 16-bit operand planes of
+  // the output projection (row stride out16_ld elements; lo only with f16 operands, may be null) and
+  // `out` is not written.
+  void *out16_hi = nullptr, *out16_lo = nullptr;
+  int out16_ld = 0;
+  bool out16_f16 = false;
 };
+// True when launch_attention_prefill will take the tensor-core form for these arguments.
+bool prefill_attention_uses_tc(const PrefillAttnArgs &a);
 bool prefill_attention_supported(int heads, int kv_heads, int hd);
 cudaError_t launch_attention_prefill(const PrefillAttnArgs &a, const LaunchCfg &cfg);
 // Tensor-core form for f16 caches (attn_prefill_tc.cu); launch_attention_prefill dispatches to it.

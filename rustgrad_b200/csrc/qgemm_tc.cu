@@ -56,6 +56,7 @@ struct Params {
   int ldc;
   size_t split_stride;
   int *status;
+  int accumulate;  // out += result (the residual add of a projection); not with split-K
 };
 
 __device__ __forceinline__ void tma_tile_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
@@ -422,7 +423,10 @@ __global__ void __launch_bounds__(MAX_THREADS, 1)
 #pragma unroll
         for (int w = 0; w < 16; ++w) {
           const int tok = tok0 + c0 + w;
-          if (tok < P.m && orow < P.n) out[(size_t)tok * P.ldc + orow] = __uint_as_float(v[w]);
+          if (tok < P.m && orow < P.n) {
+            float *dst = out + (size_t)tok * P.ldc + orow;
+            *dst = P.accumulate ? __fadd_rn(*dst, __uint_as_float(v[w])) : __uint_as_float(v[w]);
+          }
         }
       }
     }
@@ -493,6 +497,8 @@ cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
   P.ldc = a.ldc;
   P.split_stride = a.split_stride;
   P.status = cfg.status;
+  P.accumulate = a.accumulate ? 1 : 0;
+  if (a.accumulate && splits > 1) return cudaErrorInvalidValue;
   constexpr size_t smem = 1024 + NS * NPL * (TN * KSTEP * 2) + RAW_NS * RT * TM * RAW_ROW + (3 * NS + 2 * RAW_NS + 1) * 8 + 16;
   static_assert(smem <= 227 * 1024, "tile configuration exceeds the shared memory of one SM");
   auto kernel = qgemm_tc_kernel<QT, TN, MODE, RT>;

@@ -32,6 +32,7 @@ struct Params {
   int ldc;
   size_t split_stride;
   int *status;
+  int accumulate;  // out += result (the residual add of a projection)
 };
 
 __device__ __forceinline__ void tma_tile_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
@@ -324,7 +325,10 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
         for (int w = 0; w < 16; ++w) {
           const int tok = tok0 + c0 + w;
-          if (tok < P.m && orow < P.n) out[(size_t)tok * P.ldc + orow] = __uint_as_float(v[w]);
+          if (tok < P.m && orow < P.n) {
+            float *dst = out + (size_t)tok * P.ldc + orow;
+            *dst = P.accumulate ? __fadd_rn(*dst, __uint_as_float(v[w])) : __uint_as_float(v[w]);
+          }
         }
       }
     }
@@ -395,6 +399,7 @@ cudaError_t launch_t(const QGemmArgs &a, const LaunchCfg &cfg) {
   P.ldc = a.ldc;
   P.split_stride = a.split_stride;
   P.status = cfg.status;
+  P.accumulate = a.accumulate ? 1 : 0;
   constexpr size_t smem =
       1024 + NS * NPL * (A_BYTES + TN * KSTEP * 2) + RAW_NS * TM * RAW_ROW + (3 * NS + 2 * RAW_NS + 1) * 8 + 16;
   static_assert(smem <= 227 * 1024, "tile configuration exceeds the shared memory of one SM");

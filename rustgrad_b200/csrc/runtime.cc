@@ -847,8 +847,9 @@ static Operand16 wide_operand(const rg_session *s) {
   return o;
 }
 
-static int32_t gemm_tc(rg_session *s, const DevTensor &w, int m, float *out, int ldc, const LaunchCfg &L) {
+static int32_t gemm_tc(rg_session *s, const DevTensor &w, int m, float *out, int ldc, const LaunchCfg &L, bool accumulate = false) {
   QGemmArgs a;
+  a.accumulate = accumulate;
   a.type = w.type;
   a.w = w.d;
   a.n = (int)w.rows;
@@ -871,6 +872,7 @@ static int32_t gemm_tc(rg_session *s, const DevTensor &w, int m, float *out, int
   while (splits > 1 && (size_t)splits * (size_t)m * (size_t)a.n > (size_t)BMAX * 2 * (size_t)s->sm_count * 256) --splits;  // never past the scratch
   splits = qgemm_effective_splits(a.k, splits);  // the launcher's own count: the reduction sums exactly the tiles it writes
   if (splits > 1) {
+    if (accumulate) return fail(RG_INVALID_ARGUMENT, "a split-K GEMM cannot add into its output");
     a.out = s->split_scratch;
     a.ldc = a.n;
     a.splits = splits;
@@ -915,6 +917,7 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
       if ((rc = gemm_tc(s, W.v, ncols, s->qkv + qw + kw, qkv_w, L))) return rc;
     }
     prof_mark(s, PROF_ATTN);
+    bool attn_in_operand = false;
     if (!s->chunk_is_prompt && ncols <= BMAX && s->attn_counters && !s->variant) {
       // a decode batch: RoPE, cache append, split attention and the combine in one launch
       FusedAttnArgs fa;
@@ -957,6 +960,7 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
     if (s->chunk_is_prompt && prefill_attention_supported(s->heads_l, s->kv_l, hd)) {  // q and the caches are post-processed already
       // consecutive positions of one sequence: the tiled causal kernel reads each K / V row once per CTA
       // (a chunk of several prompts holds one run per sequence: one launch per run)
+      bool to_operand = true;  // every run wrote the operand planes of the output projection itself
       for (const auto &seg : s->prompt_segments) {
         PrefillAttnArgs pa;
         pa.q = s->q_rot + (size_t)seg.col0 * qw;
@@ -970,8 +974,17 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
         pa.seq = seg.seq;
         pa.pos0 = seg.pos0;
         pa.out = s->attn_f32 + (size_t)seg.col0 * qw;
+        if (prefill_attention_uses_tc(pa)) {
+          pa.out16_hi = static_cast<uint16_t *>(xop.hi) + (size_t)seg.col0 * xop.ld;
+          pa.out16_lo = xop.lo ? static_cast<uint16_t *>(xop.lo) + (size_t)seg.col0 * xop.ld : nullptr;
+          pa.out16_ld = xop.ld;
+          pa.out16_f16 = xop.f16;
+        } else {
+          to_operand = false;
+        }
         RG_LAUNCH(s, launch_attention_prefill(pa, L));
       }
+      attn_in_operand = to_operand;
     } else {
       AttnArgs aa;
       aa.q = s->q_rot;
@@ -991,13 +1004,18 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
       if (s->family_mask & (1u << PROF_ATTN)) s->launches_in_step++;  // split + combine
     }
     }
-    RG_LAUNCH(s, launch_to16(s->attn_f32, qw, qw, ncols, xop, L));
-    if ((rc = gemm_tc(s, W.o, ncols, s->tp_part[0], d, L))) return rc;
-    if (tp) {
-      if ((rc = tp_reduce_add(s, ncols, 0))) return rc;
+    if (!attn_in_operand) RG_LAUNCH(s, launch_to16(s->attn_f32, qw, qw, ncols, xop, L));
+    const bool add_in_gemm = !tp && ncols > BMAX;  // one GPU, no K split: the projection adds into the residual stream itself
+    if (add_in_gemm) {
+      if ((rc = gemm_tc(s, W.o, ncols, s->x, d, L, true))) return rc;
     } else {
-      prof_mark(s, PROF_OTHER);
-      RG_LAUNCH(s, launch_add_rows(s->x, d, s->tp_part[0], d, d, ncols, L));
+      if ((rc = gemm_tc(s, W.o, ncols, s->tp_part[0], d, L))) return rc;
+      if (tp) {
+        if ((rc = tp_reduce_add(s, ncols, 0))) return rc;
+      } else {
+        prof_mark(s, PROF_OTHER);
+        RG_LAUNCH(s, launch_add_rows(s->x, d, s->tp_part[0], d, d, ncols, L));
+      }
     }
     prof_mark(s, PROF_OTHER);
     RG_LAUNCH(s, launch_rmsnorm16(s->x, d, reinterpret_cast<const float *>(W.ffn_norm.d), d, c.norm_eps, ncols, xop,
@@ -1015,12 +1033,16 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
       prof_mark(s, PROF_OTHER);
       RG_LAUNCH(s, launch_swiglu16(s->gate_f32, s->up_f32, s->ffn_l, s->ffn_l, ncols, xop, L));
     }
-    if ((rc = gemm_tc(s, W.down, ncols, s->tp_part[1], d, L))) return rc;
-    if (tp) {
-      if ((rc = tp_reduce_add(s, ncols, 1))) return rc;
+    if (add_in_gemm) {
+      if ((rc = gemm_tc(s, W.down, ncols, s->x, d, L, true))) return rc;
     } else {
-      prof_mark(s, PROF_OTHER);
-      RG_LAUNCH(s, launch_add_rows(s->x, d, s->tp_part[1], d, d, ncols, L));
+      if ((rc = gemm_tc(s, W.down, ncols, s->tp_part[1], d, L))) return rc;
+      if (tp) {
+        if ((rc = tp_reduce_add(s, ncols, 1))) return rc;
+      } else {
+        prof_mark(s, PROF_OTHER);
+        RG_LAUNCH(s, launch_add_rows(s->x, d, s->tp_part[1], d, d, ncols, L));
+      }
     }
   }
   if (n_logit_cols > 0) {
