@@ -127,7 +127,7 @@ const char *rg_b200_last_error(void);
 int32_t rg_b200_test_fail_after(const char *what, int32_t n);
 /* How many launches of a kernel family this process has made: "qgemv_i8", "qgemv", "qgemm_tc",
  * "qgemm_tc_wide", "attn_fused", "attn_prefill" (both forms; "attn_prefill_tc" the tensor-core form alone), "attn_split", "tp_exchange", "kquant_gemv",
- * "dense_gemv"; UINT64_MAX for an unknown name.  Evidence for tests and reports of which kernel
+ * "dense_gemv", "qgemv_rows" (the opt-in 3..16-row form, not counted under "qgemv"), "attn_decode_tc"; UINT64_MAX for an unknown name.  Evidence for tests and reports of which kernel
  * served a call (the role of MetalDeviceRunReport's dispatch counts, src/runtime/metal/session.rs:145-185). */
 uint64_t rg_b200_launch_count(const char *kernel);
 /* Test hook for the device-side time-out path (bounded waits that end in a status word, the
@@ -264,7 +264,7 @@ int32_t rg_b200_nccl_unique_id(uint8_t out[128]);
 /* QuantizedTensorData::dequantize_f32 (src/gguf/quantization/data.rs:415-428): bit-exact. */
 int32_t rg_b200_dequantize(int32_t device, int32_t ggml_type, const uint8_t *bytes, size_t elements, float *out);
 /* QuantizedMatmulPlan::execute (src/matmul/quantized.rs:126-182): activation f32 [m,k] x packed
- * or dense [n,k] -> f32 [m,n].  m <= 8 runs the decode GEMV, larger m the prefill path. */
+ * or dense [n,k] -> f32 [m,n], through the decode GEMVs in chunks of at most 8 activation rows. */
 int32_t rg_b200_qmatmul(int32_t device, int32_t ggml_type, const uint8_t *weight, uint64_t n, uint64_t k,
                         const float *activation, uint64_t m, float *out);
 /* QuantizedRowGatherPlan::execute (src/gguf/quantization/row_gather.rs:149-226). */
@@ -347,7 +347,7 @@ void rg_b200_kv_snapshot_free(rg_kv_snapshot *k);
 
 /* Device-resident operator benchmark: weight uploaded once, `iters` launches timed with CUDA
  * events on the library's stream; `rotate` distinct weight copies are cycled so that each launch
- * reads HBM rather than L2.  kernel_ms receives the mean time of one launch. */
+ * reads HBM rather than L2.  kernel_ms receives the mean time of one launch.  m in 1..8. */
 int32_t rg_b200_qmatmul_bench(int32_t device, int32_t ggml_type, const uint8_t *weight, uint64_t n, uint64_t k,
                               const float *activation, uint64_t m, int32_t rotate, int32_t iters,
                               int32_t warmup, float *out, float *kernel_ms);

@@ -16,7 +16,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = HERE / "build"
 LIB = HERE / "librg_b200.so"
-SOURCES = ["qgemv.cu", "qgemv_i8.cu", "qgemm_tc.cu", "qgemm_tc_wide.cu", "attn_fused.cu", "tp_fused.cu", "attn_prefill.cu", "attn_prefill_tc.cu", "ops.cu", "runtime.cc", "ops_abi.cc", "gguf.cc", "comm.cc", "tokenizer.cc", "workflow.cc", "serving.cc"]
+SOURCES = ["qgemv.cu", "qgemv_rows.cu", "qgemv_i8.cu", "qgemm_tc.cu", "qgemm_tc_wide.cu", "attn_fused.cu", "tp_fused.cu", "attn_prefill.cu", "attn_prefill_tc.cu", "attn_decode_tc.cu", "ops.cu", "runtime.cc", "ops_abi.cc", "gguf.cc", "comm.cc", "tokenizer.cc", "workflow.cc", "serving.cc"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function"]
 

@@ -31,7 +31,7 @@ struct DeviceOnce {
 // Launch counters per kernel family (process-wide), so a test can prove which kernel served a call.
 enum LaunchCounter {
   LC_QGEMV_I8 = 0, LC_QGEMV, LC_QGEMM_TC, LC_QGEMM_TC_WIDE, LC_ATTN_FUSED, LC_ATTN_PREFILL, LC_ATTN_SPLIT, LC_TP_EXCHANGE,
-  LC_KQUANT_GEMV, LC_DENSE_GEMV, LC_ATTN_PREFILL_TC, LC_COUNT
+  LC_KQUANT_GEMV, LC_DENSE_GEMV, LC_ATTN_PREFILL_TC, LC_QGEMV_ROWS, LC_ATTN_DECODE_TC, LC_COUNT
 };
 void count_launch(int which);
 
@@ -47,13 +47,25 @@ struct GemvArgs {
   int nseg = 1;
   int k = 0;               // multiple of 256
   const void *xpack = nullptr;
-  int batch = 1;           // 1..8
+  int batch = 1;           // 1..16
   int epi = EPI_STORE;
   float *y = nullptr;      // EPI_STORE: y[b*ldy + row] = v;  EPI_RESIDUAL: y[b*ldy + row] += v
   int ldy = 0;
   void *ypack = nullptr;   // EPI_SWIGLU: packed output with K' = seg_rows[0]
+  // Workspace of the K-split form of qgemv_rows.cu (optional; without it matrices with few rows run unsplit):
+  // partial tiles, and QGEMV_ROWS_MAX_TILES counters that are zero between launches.
+  float *split_scratch = nullptr;
+  size_t split_scratch_floats = 0;
+  unsigned *split_counters = nullptr;
 };
+constexpr int QGEMV_ROWS_MAX_TILES = 256;
 cudaError_t launch_qgemv(const GemvArgs &a, const LaunchCfg &cfg);
+// A second form for 3..16 batch rows on Q4_0 (qgemv_rows.cu: tall row tiles that share one copy of the
+// activations, K split over CTAs for matrices with few rows), behind RG_B200_ROWS_GEMV=1; launch_qgemv checks
+// the arguments and dispatches.
+bool qgemv_rows_enabled();
+bool qgemv_rows_applies(const GemvArgs &a);
+cudaError_t launch_qgemv_rows(const GemvArgs &a, const LaunchCfg &cfg);
 size_t xpack_bytes(int k, int batch);  // K rounded up to a whole 32-element block
 
 // Integer tensor-core GEMV for batch 1..2 with the activations packed (and optionally
@@ -246,6 +258,11 @@ constexpr int ATTN_SPAN = 128;  // context positions per CTA of the split kernel
 bool attention_supported(int heads, int kv_heads, int hd);  // hd in {64,128}, heads/kv_heads in {1,2,4,8}
 size_t attn_scratch_floats(int cols, int heads, int hd, int ctx);
 cudaError_t launch_attention(const AttnArgs &a, const LaunchCfg &cfg);
+// The same for f16 caches and head dimension 128 on the tensor cores, built for batches of rows
+// (attn_decode_tc.cu): per-warp cp.async rings keep the K / V stream going.  Two launches (spans, merge).
+bool attention_decode_tc_supported(const AttnArgs &a);
+size_t attention_decode_tc_scratch_floats(int sm_count, int heads, int kv_heads, int cols, int ctx);
+cudaError_t launch_attention_decode_tc(const AttnArgs &a, const LaunchCfg &cfg);
 
 // RoPE + KV append + split-context attention + combine in one launch (attn_fused.cu).  qkv rows are
 // the raw projections [cols, qw + 2*kw]; out is [cols, heads*hd] f32.  scratch holds

@@ -26,7 +26,7 @@ using namespace rg;
 
 extern "C" uint64_t rg_b200_launch_count(const char *kernel) {
   static const char *names[LC_COUNT] = {"qgemv_i8", "qgemv", "qgemm_tc", "qgemm_tc_wide", "attn_fused", "attn_prefill",
-                                        "attn_split", "tp_exchange", "kquant_gemv", "dense_gemv", "attn_prefill_tc"};
+                                        "attn_split", "tp_exchange", "kquant_gemv", "dense_gemv", "attn_prefill_tc", "qgemv_rows", "attn_decode_tc"};
   if (!kernel) return 0;
   for (int i = 0; i < LC_COUNT; ++i)
     if (!strcmp(kernel, names[i])) return g_launch_counts[i].load(std::memory_order_relaxed);
@@ -109,12 +109,31 @@ int32_t scan_scales(int32_t type, const uint8_t *bytes, size_t nbytes) {
   return RG_OK;
 }
 
-// Launches y[m,n] = x[m,k] . W[n,k]^T in column chunks of at most eight activation rows.
+// Workspace of the K-split row GEMV (qgemv_rows.cu): partial tiles and zeroed arrival counters.
+struct GemvWorkspace {
+  float *scratch = nullptr;
+  size_t floats = 0;
+  unsigned *counters = nullptr;
+};
+constexpr size_t GEMV_WS_FLOATS = (size_t)256 * 512 * 8;  // up to 256 units of 512 threads x 8 partial sums
+cudaError_t alloc_gemv_workspace(Scope *sc, GemvWorkspace *ws) {
+  cudaError_t e = sc->alloc(&ws->scratch, sizeof(float) * GEMV_WS_FLOATS);
+  if (e != cudaSuccess) return e;
+  if ((e = sc->alloc(&ws->counters, sizeof(unsigned) * QGEMV_ROWS_MAX_TILES)) != cudaSuccess) return e;
+  ws->floats = GEMV_WS_FLOATS;
+  return cudaMemsetAsync(ws->counters, 0, sizeof(unsigned) * QGEMV_ROWS_MAX_TILES, sc->stream);
+}
+
+// Activation rows one launch takes: 16 where the row GEMV is switched on and applies, else 8.
+int matmul_chunk(int32_t type, uint64_t k) { return (qgemv_rows_enabled() && type == RG_TYPE_Q4_0 && k % 256 == 0) ? 16 : 8; }
+
+// Launches y[m,n] = x[m,k] . W[n,k]^T in column chunks of at most matmul_chunk() activation rows.
 int32_t run_matmul(int32_t type, const uint8_t *d_w, uint64_t n, uint64_t k, const float *d_x, uint64_t m, float *d_y,
-                   void *d_pack, const LaunchCfg &cfg) {
+                   void *d_pack, const GemvWorkspace &ws, const LaunchCfg &cfg) {
   const bool packed = (type == RG_TYPE_Q4_0 || type == RG_TYPE_Q8_0);
-  for (uint64_t m0 = 0; m0 < m; m0 += 8) {
-    const int batch = (int)std::min<uint64_t>(8, m - m0);
+  const uint64_t chunk = (uint64_t)matmul_chunk(type, k);
+  for (uint64_t m0 = 0; m0 < m; m0 += chunk) {
+    const int batch = (int)std::min<uint64_t>(chunk, m - m0);
     if (packed && qgemv_i8_supported((int)k, batch)) {
       // batch 1..2: integer tensor-core kernel, packs the f32 activations in its own prologue
       GemvI8Args a;
@@ -143,6 +162,9 @@ int32_t run_matmul(int32_t type, const uint8_t *d_w, uint64_t n, uint64_t k, con
       a.epi = EPI_STORE;
       a.y = d_y + m0 * n;
       a.ldy = (int)n;
+      a.split_scratch = ws.scratch;
+      a.split_scratch_floats = ws.floats;
+      a.split_counters = ws.counters;
       OP_CUDA(launch_qgemv(a, cfg));
     } else {
       DenseGemvArgs a;
@@ -214,10 +236,12 @@ int32_t rg_b200_qmatmul(int32_t device, int32_t type, const uint8_t *weight, uin
   OP_CUDA(sc.alloc(&d_w, wbytes));
   OP_CUDA(sc.alloc(&d_x, sizeof(float) * m * k));
   OP_CUDA(sc.alloc(&d_y, sizeof(float) * m * n));
-  OP_CUDA(sc.alloc(&d_pack, xpack_bytes((int)k, 8)));
+  OP_CUDA(sc.alloc(&d_pack, xpack_bytes((int)k, 16)));
+  GemvWorkspace ws;
+  OP_CUDA(alloc_gemv_workspace(&sc, &ws));
   OP_CUDA(cudaMemcpyAsync(d_w, weight, wbytes, cudaMemcpyHostToDevice, sc.stream));
   OP_CUDA(cudaMemcpyAsync(d_x, activation, sizeof(float) * m * k, cudaMemcpyHostToDevice, sc.stream));
-  if ((rc = run_matmul(type, d_w, n, k, d_x, m, d_y, d_pack, cfg))) return rc;
+  if ((rc = run_matmul(type, d_w, n, k, d_x, m, d_y, d_pack, ws, cfg))) return rc;
   int status = 0;
   OP_CUDA(cudaMemcpyAsync(out, d_y, sizeof(float) * m * n, cudaMemcpyDeviceToHost, sc.stream));
   OP_CUDA(cudaMemcpyAsync(&status, d_status, sizeof(int), cudaMemcpyDeviceToHost, sc.stream));
@@ -375,7 +399,8 @@ int32_t rg_b200_attention_decode(int32_t device, const float *q, const void *key
 int32_t rg_b200_qmatmul_bench(int32_t device, int32_t type, const uint8_t *weight, uint64_t n, uint64_t k, const float *activation,
                               uint64_t m, int32_t rotate, int32_t iters, int32_t warmup, float *out, float *kernel_ms) {
   if (!weight || !activation || !kernel_ms) return fail(RG_INVALID_ARGUMENT, "null argument");
-  if (m < 1 || m > 8 || iters < 1 || rotate < 1) return fail(RG_INVALID_ARGUMENT, "m in 1..8, iters >= 1, rotate >= 1");
+  if (m < 1 || m > 16 || (m > 8 && matmul_chunk(type, k) < 16) || iters < 1 || rotate < 1)
+    return fail(RG_INVALID_ARGUMENT, "m in 1..8 (1..16 for Q4_0 with the row GEMV switched on), iters >= 1, rotate >= 1");
   size_t wbytes;
   int32_t rc = check_weight(type, n, k, &wbytes);
   if (rc) return rc;
@@ -409,6 +434,11 @@ int32_t rg_b200_qmatmul_bench(int32_t device, int32_t type, const uint8_t *weigh
   a.epi = EPI_STORE;
   a.y = d_y;
   a.ldy = (int)n;
+  GemvWorkspace ws;
+  OP_CUDA(alloc_gemv_workspace(&sc, &ws));
+  a.split_scratch = ws.scratch;
+  a.split_scratch_floats = ws.floats;
+  a.split_counters = ws.counters;
   // batch 1..2 runs the integer tensor-core kernel (activations packed by its prologue)
   const bool use_i8 = qgemv_i8_supported((int)k, (int)m);
   GemvI8Args a8;

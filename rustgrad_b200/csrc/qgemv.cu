@@ -499,13 +499,14 @@ cudaError_t launch_e(const GemvArgs &a, const LaunchCfg &cfg) {
 size_t xpack_bytes(int k, int batch) { return (size_t)((k + 31) / 32 * 32) * (size_t)batch * 4; }
 
 cudaError_t launch_qgemv(const GemvArgs &a, const LaunchCfg &cfg) {
-  count_launch(LC_QGEMV);
   if (a.k <= 0 || a.k % 256 || a.batch < 1 || a.batch > 16 || a.nseg < 1 || a.nseg > 3) return cudaErrorInvalidValue;
   if (a.epi == EPI_SWIGLU && (a.nseg != 2 || a.seg_rows[0] != a.seg_rows[1])) return cudaErrorInvalidValue;
   for (int i = 0; i + 1 < a.nseg; ++i)
     if (a.epi != EPI_SWIGLU && a.seg_rows[i] % BOXR) return cudaErrorInvalidValue;  // boxes may not straddle segments
   for (int i = 0; i < a.nseg; ++i)
     if ((reinterpret_cast<uintptr_t>(a.w[i]) & 15) != 0) return cudaErrorInvalidValue;
+  if (qgemv_rows_applies(a)) return launch_qgemv_rows(a, cfg);
+  count_launch(LC_QGEMV);
   // column tiles of four batch rows (hi and lo column each): 1, 2 or 4 tiles
   const int nt = a.batch > 8 ? 4 : a.batch > 4 ? 2 : 1;
   if (a.type == RG_TYPE_Q4_0)

@@ -307,7 +307,8 @@ struct rg_session {
   // q/k/v post-processing kernel and the three-launch attention on every path
   bool variant = false;
   int rope_dim = 0;  // rotary lanes per head (head_dim for the plain layer)
-  float *split_scratch = nullptr;  // K-split partial tiles of the tensor-core GEMM at small token counts
+  float *split_scratch = nullptr;  // K-split partial tiles of the tensor-core GEMM at small token counts and of the 3..16-row GEMV
+  unsigned *gemv_counters = nullptr;  // arrival counters of the K-split row GEMV, zero between launches
   void *xb = nullptr;  // 16-bit operand planes (hi, lo) of the tensor-core path: [2][WMAX][max(d, qw, ffn_l)]
   int gemm_mode = QGEMM_F16X3;
   int xb_ld = 0;
@@ -430,6 +431,9 @@ static int32_t linear(rg_session *s, const DevTensor *const *w, int n, const voi
     a.epi = epi;
     a.y = y;
     a.ldy = ldy;
+    a.split_scratch = s->split_scratch;
+    a.split_scratch_floats = s->split_scratch ? (size_t)BMAX * 2 * s->sm_count * 256 : 0;
+    a.split_counters = s->gemv_counters;
     RG_LAUNCH(s, launch_qgemv(a, lcfg(s)));
     return RG_OK;
   }
@@ -447,6 +451,9 @@ static int32_t linear(rg_session *s, const DevTensor *const *w, int n, const voi
       a.epi = epi;
       a.y = y + row0;
       a.ldy = ldy;
+      a.split_scratch = s->split_scratch;
+      a.split_scratch_floats = s->split_scratch ? (size_t)BMAX * 2 * s->sm_count * 256 : 0;
+      a.split_counters = s->gemv_counters;
       RG_LAUNCH(s, launch_qgemv(a, lcfg(s)));
     } else {
       DenseGemvArgs a;
@@ -518,6 +525,29 @@ static void rope_variant(const rg_session *s, const LayerW &W, RopeArgs *ra) {
   ra->q_bias = reinterpret_cast<const float *>(W.q_bias.d);
   ra->k_bias = reinterpret_cast<const float *>(W.k_bias.d);
   ra->v_bias = reinterpret_cast<const float *>(W.v_bias.d);
+}
+
+// Decode rows of distinct sequences on f16 caches: from nine rows on, the tensor-core attention with per-warp
+// cp.async rings (attn_decode_tc.cu) streams K / V faster than the one-launch kernel, whose CTAs load, score and
+// combine one after the other.  Measured on the 8B shape, attention ms per step, new against one-launch: 16 rows
+// 1.52 / 1.88 at context 2100 and 1.05 / 1.24 at 1024; 8 rows 0.99 / 1.05 at 2100 but 3 % behind in whole-job
+// throughput at contexts under 200; 4 rows 0.75 / 0.61.  So eight rows and fewer keep the one-launch kernel.
+static bool decode_tc_attention(const rg_session *s, int ncols) {
+  static const bool off = env_flag("RG_B200_NO_ATTN_DECODE_TC");
+  static const int min_cols = [] {
+    const char *v = getenv("RG_B200_ATTN_TC_MIN_COLS");
+    const int n = v ? atoi(v) : 0;
+    return n > 0 ? n : 9;
+  }();
+  if (off || s->chunk_is_prompt || ncols < min_cols || ncols > BMAX) return false;
+  AttnArgs a;
+  a.kv_f32 = s->kv_f32;
+  a.heads = s->heads_l;
+  a.kv_heads = s->kv_l;
+  a.hd = s->cfg.head_dim;
+  return attention_decode_tc_supported(a) &&
+         attention_decode_tc_scratch_floats(s->sm_count, s->heads_l, s->kv_l, ncols, s->ctx) <=
+             attn_scratch_floats(SCOLS, s->heads_l, s->cfg.head_dim, s->ctx);
 }
 
 // True when every projection of the model can run the integer tensor-core GEMV at this width.
@@ -918,7 +948,8 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
     }
     prof_mark(s, PROF_ATTN);
     bool attn_in_operand = false;
-    if (!s->chunk_is_prompt && ncols <= BMAX && s->attn_counters && !s->variant) {
+    const bool tc_attn = decode_tc_attention(s, ncols);
+    if (!tc_attn && !s->chunk_is_prompt && ncols <= BMAX && s->attn_counters && !s->variant) {
       // a decode batch: RoPE, cache append, split attention and the combine in one launch
       FusedAttnArgs fa;
       fa.qkv = s->qkv;
@@ -1000,7 +1031,11 @@ static int32_t forward_wide(rg_session *s, int ncols, int n_logit_cols, bool adv
       aa.col_pos = ctl->pos;
       aa.scratch = s->attn_scratch;
       aa.out_f32 = s->attn_f32;
-      RG_LAUNCH(s, launch_attention(aa, L));
+      if (tc_attn) {
+        RG_LAUNCH(s, launch_attention_decode_tc(aa, L));
+      } else {
+        RG_LAUNCH(s, launch_attention(aa, L));
+      }
       if (s->family_mask & (1u << PROF_ATTN)) s->launches_in_step++;  // split + combine
     }
     }
@@ -1207,8 +1242,9 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
     int32_t rc = linear(s, qkvw, 3, s->xn_pack, s->xn_f32, d, ncols, EPI_STORE, s->qkv, qkv_w);
     if (rc) return rc;
     prof_mark(s, PROF_ATTN);
-    if ((gemv16 || (ncols >= 3 && !s->chunk_is_prompt && !env_flag("RG_B200_SPLIT_ATTENTION_SMALL"))) && s->attn_counters &&
-        !s->variant) {
+    const bool tc_attn = decode_tc_attention(s, ncols);
+    if (!tc_attn && (gemv16 || (ncols >= 3 && !s->chunk_is_prompt && !env_flag("RG_B200_SPLIT_ATTENTION_SMALL"))) &&
+        s->attn_counters && !s->variant) {
       // rows of distinct sequences: RoPE, cache append, split attention and the combine in one launch
       FusedAttnArgs fa;
       fa.qkv = s->qkv;
@@ -1264,7 +1300,11 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
     aa.scratch = s->attn_scratch;
     aa.out_pack = s->attn_pack;
     aa.out_f32 = W.o.packed() ? nullptr : s->attn_f32;
-    RG_LAUNCH(s, launch_attention(aa, L));
+    if (tc_attn) {
+      RG_LAUNCH(s, launch_attention_decode_tc(aa, L));
+    } else {
+      RG_LAUNCH(s, launch_attention(aa, L));
+    }
     if (s->family_mask & (1u << PROF_ATTN)) s->launches_in_step++;  // split + combine
     }
     const DevTensor *ow[1] = {&W.o};
@@ -1841,6 +1881,8 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   RG_TRY(dalloc(s.get(), &raw, (size_t)2 * WMAX * s->xb_ld * 2));
   // splits <= 2 * SMs / tiles and rows <= tiles * rows_per_cta (256 with two row tiles per CTA)
   RG_TRY(dalloc(s.get(), &s->split_scratch, (size_t)BMAX * 2 * s->sm_count * 256));
+  RG_TRY(dalloc(s.get(), &s->gemv_counters, (size_t)QGEMV_ROWS_MAX_TILES));
+  RG_CUDA(cudaMemsetAsync(s->gemv_counters, 0, sizeof(unsigned) * QGEMV_ROWS_MAX_TILES, s->stream));
   s->gemm_mode = (s->opt.gemm_operand_mode >= 1 && s->opt.gemm_operand_mode <= 3) ? s->opt.gemm_operand_mode - 1 : QGEMM_F16X3;
   s->xb = raw;
   RG_TRY(dalloc(s.get(), &raw, xpack_bytes(d, MAXC)));

@@ -774,3 +774,32 @@ def test_prompt_attention_on_tensor_cores_with_f16_cache(heads, kv_heads):
         assert_logits_close(got, want)
         tok = O.select_greedy(want)
         assert_logits_close(s.run_token(tok), oracle.forward([tok], O.MODE_FAST))   # the cache rows it left are the checker's
+
+
+@pytest.mark.parametrize("heads,kv_heads", [(4, 1), (4, 2), (2, 2), (8, 1)])
+def test_batched_decode_attention_on_tensor_cores_with_f16_cache(heads, kv_heads):
+    """Nine or more rows decoding together on f16 caches run the tensor-core decode attention
+    (attn_decode_tc.cu): 1, 2, 4 and 8 query heads per kv head; rows at different positions, so spans end in
+    ragged 16-key tiles, some warps of a CTA get no tile, and long rows are cut into several spans; every
+    row against its own checker with an f16 cache, three steps."""
+    cfg = synth.scaled(synth.TINY, d_model=heads * 128, n_heads=heads, n_kv_heads=kv_heads, head_dim=128, ffn_dim=512, vocab=320,
+                       n_layers=2, rope_theta=500000.0, max_context=700)
+    tensors = synth.build_tensors(cfg, seed=33, body_type=quant.Q4_0)
+    for rows, lengths in ((9, (1, 15, 16, 17, 63, 64, 65, 130, 600)), (16, tuple(5 + 41 * r for r in range(16)))):
+        s = session.LlamaCudaPlan.from_tensors(cfg, tensors, session.CudaSessionTarget(max_context=700, max_batch=rows)).prepare()
+        oracles = [O.OracleModel(cfg, tensors, kv_f16=True, threads=2) for _ in range(rows)]
+        toks = []
+        for r in range(rows):
+            p = synth.prompt_ids(cfg, lengths[r], seed=200 + r)
+            s.prefill_ids(p, row=r)
+            toks.append(O.select_greedy(oracles[r].forward(p, O.MODE_FAST)))
+        before = session.launch_count("attn_decode_tc")
+        for _ in range(3):
+            logits, greedy = s.decode(toks, want_logits=True)
+            nxt = []
+            for r in range(rows):
+                w = oracles[r].forward([toks[r]], O.MODE_FAST)
+                assert_logits_close(logits[r], w)
+                nxt.append(O.select_greedy(w))
+            toks = nxt
+        assert session.launch_count("attn_decode_tc") >= before + cfg["n_layers"]  # later steps may replay a captured graph

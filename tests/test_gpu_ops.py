@@ -201,3 +201,37 @@ def test_decode_attention_rejects_unsupported_head_geometry():
     with pytest.raises(session.RgError) as e:
         session.attention_decode(q, kv, kv)
     assert e.value.status == 20
+
+
+def test_opt_in_row_gemv_matches_f64_blockwise_plan():
+    """The second 3..16-row GEMV (qgemv_rows.cu, switched on by RG_B200_ROWS_GEMV=1 when the library
+    loads, hence the child process): tall row tiles, K split over CTAs for matrices with few rows and
+    the in-order merge by the last CTA to arrive; 3..16 rows against the f64 blockwise plan."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import numpy as np
+from oracle import oracle as O
+from rustgrad_b200 import quant, session
+rng = np.random.default_rng(7)
+before = session.launch_count("qgemv_rows")
+for n, k in ((64, 256), (45, 512), (300, 1024), (1000, 4096), (4096, 4096), (37, 14336), (6144, 1024)):
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    data = quant.encode(quant.Q4_0, w)
+    dense = O.dequantize(quant.Q4_0, data, n * k).reshape(n, k)
+    wn = np.sqrt((dense.astype(np.float64) ** 2).sum(axis=1))
+    for m in (3, 4, 8, 11, 16):
+        x = rng.standard_normal((m, k)).astype(np.float32)
+        want = O.quantized_matmul(quant.Q4_0, data, n, k, x)
+        got = session.qmatmul(quant.Q4_0, data, n, k, x)
+        scale = np.sqrt((x.astype(np.float64) ** 2).sum(axis=1))[:, None] * wn[None, :]
+        err = np.abs(got.astype(np.float64) - want.astype(np.float64)) / (scale + 1e-30)
+        assert err.max() < 2e-6, (n, k, m, err.max())
+assert session.launch_count("qgemv_rows") == before + 7 * 5
+print("ok")
+'''
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, RG_B200_ROWS_GEMV="1", PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    r = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
