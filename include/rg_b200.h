@@ -264,7 +264,8 @@ int32_t rg_b200_nccl_unique_id(uint8_t out[128]);
 /* QuantizedTensorData::dequantize_f32 (src/gguf/quantization/data.rs:415-428): bit-exact. */
 int32_t rg_b200_dequantize(int32_t device, int32_t ggml_type, const uint8_t *bytes, size_t elements, float *out);
 /* QuantizedMatmulPlan::execute (src/matmul/quantized.rs:126-182): activation f32 [m,k] x packed
- * or dense [n,k] -> f32 [m,n], through the decode GEMVs in chunks of at most 8 activation rows. */
+ * or dense [n,k] -> f32 [m,n], through the decode GEMVs in chunks of at most 16 activation rows (8 for
+ * types other than Q4_0 / Q8_0). */
 int32_t rg_b200_qmatmul(int32_t device, int32_t ggml_type, const uint8_t *weight, uint64_t n, uint64_t k,
                         const float *activation, uint64_t m, float *out);
 /* QuantizedRowGatherPlan::execute (src/gguf/quantization/row_gather.rs:149-226). */
@@ -347,7 +348,7 @@ void rg_b200_kv_snapshot_free(rg_kv_snapshot *k);
 
 /* Device-resident operator benchmark: weight uploaded once, `iters` launches timed with CUDA
  * events on the library's stream; `rotate` distinct weight copies are cycled so that each launch
- * reads HBM rather than L2.  kernel_ms receives the mean time of one launch.  m in 1..8. */
+ * reads HBM rather than L2.  kernel_ms receives the mean time of one launch.  m in 1..16. */
 int32_t rg_b200_qmatmul_bench(int32_t device, int32_t ggml_type, const uint8_t *weight, uint64_t n, uint64_t k,
                               const float *activation, uint64_t m, int32_t rotate, int32_t iters,
                               int32_t warmup, float *out, float *kernel_ms);

@@ -124,8 +124,8 @@ cudaError_t alloc_gemv_workspace(Scope *sc, GemvWorkspace *ws) {
   return cudaMemsetAsync(ws->counters, 0, sizeof(unsigned) * QGEMV_ROWS_MAX_TILES, sc->stream);
 }
 
-// Activation rows one launch takes: 16 where the row GEMV is switched on and applies, else 8.
-int matmul_chunk(int32_t type, uint64_t k) { return (qgemv_rows_enabled() && type == RG_TYPE_Q4_0 && k % 256 == 0) ? 16 : 8; }
+// Activation rows one launch takes: 16 for the packed types (the f16-MMA GEMV), else 8.
+int matmul_chunk(int32_t type, uint64_t k) { return ((type == RG_TYPE_Q4_0 || type == RG_TYPE_Q8_0) && k % 256 == 0) ? 16 : 8; }
 
 // Launches y[m,n] = x[m,k] . W[n,k]^T in column chunks of at most matmul_chunk() activation rows.
 int32_t run_matmul(int32_t type, const uint8_t *d_w, uint64_t n, uint64_t k, const float *d_x, uint64_t m, float *d_y,
@@ -400,7 +400,7 @@ int32_t rg_b200_qmatmul_bench(int32_t device, int32_t type, const uint8_t *weigh
                               uint64_t m, int32_t rotate, int32_t iters, int32_t warmup, float *out, float *kernel_ms) {
   if (!weight || !activation || !kernel_ms) return fail(RG_INVALID_ARGUMENT, "null argument");
   if (m < 1 || m > 16 || (m > 8 && matmul_chunk(type, k) < 16) || iters < 1 || rotate < 1)
-    return fail(RG_INVALID_ARGUMENT, "m in 1..8 (1..16 for Q4_0 with the row GEMV switched on), iters >= 1, rotate >= 1");
+    return fail(RG_INVALID_ARGUMENT, "m in 1..16, iters >= 1, rotate >= 1");
   size_t wbytes;
   int32_t rc = check_weight(type, n, k, &wbytes);
   if (rc) return rc;

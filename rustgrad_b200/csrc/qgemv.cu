@@ -325,14 +325,11 @@ __global__ void __launch_bounds__(THREADS, 1)
           mma_16816(ce, ae[0][2], ae[1][2], ae[0][3], ae[1][3], xe[j].z, xe[j].w);
           mma_16816_zero(co, ao[0][0], ao[1][0], ao[0][1], ao[1][1], xo[j].x, xo[j].y);
           mma_16816(co, ao[0][2], ao[1][2], ao[0][3], ao[1][3], xo[j].z, xo[j].w);
-          acc[mt][j][0] = fmaf(de[0], ce[0], acc[mt][j][0]);
-          acc[mt][j][1] = fmaf(de[0], ce[1], acc[mt][j][1]);
-          acc[mt][j][2] = fmaf(de[1], ce[2], acc[mt][j][2]);
-          acc[mt][j][3] = fmaf(de[1], ce[3], acc[mt][j][3]);
-          acc[mt][j][0] = fmaf(dd[0], co[0], acc[mt][j][0]);
-          acc[mt][j][1] = fmaf(dd[0], co[1], acc[mt][j][1]);
-          acc[mt][j][2] = fmaf(dd[1], co[2], acc[mt][j][2]);
-          acc[mt][j][3] = fmaf(dd[1], co[3], acc[mt][j][3]);
+          // the block scales multiply two accumulator lanes at a time (packed f32x2 FMA)
+          ffma2_scale(acc[mt][j][0], acc[mt][j][1], de[0], ce[0], ce[1]);
+          ffma2_scale(acc[mt][j][2], acc[mt][j][3], de[1], ce[2], ce[3]);
+          ffma2_scale(acc[mt][j][0], acc[mt][j][1], dd[0], co[0], co[1]);
+          ffma2_scale(acc[mt][j][2], acc[mt][j][3], dd[1], co[2], co[3]);
         }
       }
     }

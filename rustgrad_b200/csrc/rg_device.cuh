@@ -106,6 +106,14 @@ __device__ __forceinline__ void mma_16816_zero(float (&d)[4], uint32_t a0, uint3
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(z));
 }
 
+// (a0, a1) += s * (c0, c1) as one packed f32x2 fused multiply-add: each half is rounded exactly like fmaf.
+__device__ __forceinline__ void ffma2_scale(float &a0, float &a1, float s, float c0, float c1) {
+  asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%0, %1};\n\tmov.b64 rb, {%2, %2};\n\tmov.b64 rc, {%3, %4};\n\t"
+      "fma.rn.f32x2 ra, rc, rb, ra;\n\tmov.b64 {%0, %1}, ra;\n\t}"
+      : "+f"(a0), "+f"(a1)
+      : "f"(s), "f"(c0), "f"(c1));
+}
+
 __device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
   uint32_t d;
   asm("sub.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));

@@ -78,7 +78,7 @@ def test_qmatmul_matches_f64_blockwise_plan(kind, n, k):
     w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
     data = quant.encode(kind, w)
     dense = O.dequantize(kind, data, n * k).reshape(n, k)
-    for m in (1, 2, 3, 4, 5, 8):
+    for m in (1, 2, 3, 4, 5, 8, 9, 13, 16):  # 9..16: four column tiles
         x = rng.standard_normal((m, k)).astype(np.float32)
         want = O.quantized_matmul(kind, data, n, k, x)
         got = session.qmatmul(kind, data, n, k, x)
@@ -143,10 +143,11 @@ def test_qmatmul_extreme_activations_keep_f32_precision():
     data = quant.encode(quant.Q4_0, w)
     dense = O.dequantize(quant.Q4_0, data, n * k).reshape(n, k)
     for scale in (1e-4, 1.0, 3e3):
-        x = (rng.standard_normal((2, k)) * scale).astype(np.float32)
-        got = session.qmatmul(quant.Q4_0, data, n, k, x)
-        want = O.quantized_matmul(quant.Q4_0, data, n, k, x)
-        assert rel_err(got, want, x, dense).max() < 4e-6, scale
+        for m in (2, 4, 12):  # integer kernel; f16-MMA kernel with one and with four column tiles
+            x = (rng.standard_normal((m, k)) * scale).astype(np.float32)
+            got = session.qmatmul(quant.Q4_0, data, n, k, x)
+            want = O.quantized_matmul(quant.Q4_0, data, n, k, x)
+            assert rel_err(got, want, x, dense).max() < 4e-6, (scale, m)
 
 
 def test_qmatmul_rejects_unsupported_geometry_and_types():
