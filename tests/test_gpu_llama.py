@@ -785,7 +785,9 @@ def test_batched_decode_attention_on_tensor_cores_with_f16_cache(heads, kv_heads
     cfg = synth.scaled(synth.TINY, d_model=heads * 128, n_heads=heads, n_kv_heads=kv_heads, head_dim=128, ffn_dim=512, vocab=320,
                        n_layers=2, rope_theta=500000.0, max_context=700)
     tensors = synth.build_tensors(cfg, seed=33, body_type=quant.Q4_0)
-    for rows, lengths in ((9, (1, 15, 16, 17, 63, 64, 65, 130, 600)), (16, tuple(5 + 41 * r for r in range(16)))):
+    # 9 and 16 rows: projections on the GEMV; 20 rows: projections on the tcgen05 GEMM, same attention kernel
+    for rows, lengths in ((9, (1, 15, 16, 17, 63, 64, 65, 130, 600)), (16, tuple(5 + 41 * r for r in range(16))),
+                          (20, tuple(3 + 29 * r for r in range(20)))):
         s = session.LlamaCudaPlan.from_tensors(cfg, tensors, session.CudaSessionTarget(max_context=700, max_batch=rows)).prepare()
         oracles = [O.OracleModel(cfg, tensors, kv_f16=True, threads=2) for _ in range(rows)]
         toks = []
