@@ -468,7 +468,7 @@ def main():
 
     peak, peak_kind = measured_peaks()
     gemv_bytes, gemv_launches = gemv_bytes_per_step(cfg, wl, n, B)
-    proj_kernel = ("qgemv_i8_kernel" if B <= 2 else "qgemv_kernel" if B <= 8 else "qgemm_tc_kernel") + " (all projection launches of a step)"
+    proj_kernel = ("qgemv_i8_kernel" if B <= 2 else "qgemv_kernel" if B <= 16 else "qgemm_tc_kernel") + " (all projection launches of a step)"
     gemv_ms = prof["gemv"]["ms_per_step"]
     achieved = gemv_bytes / (gemv_ms * 1e-3) / 1e9 if gemv_ms > 0 else None
     ms_per_step = gpu_ms / args.steps
