@@ -147,7 +147,11 @@ __global__ void rmsnorm_pack_kernel(const float *x, int ldx, const float *w, int
   }
   __syncthreads();
   const float inv = inv_s;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+  // gridDim.y CTAs share a column: each sums the whole row (in the same order, so they agree bit for bit)
+  // and writes its own slice
+  const int per = (d + (int)gridDim.y - 1) / (int)gridDim.y;
+  const int i0 = (int)blockIdx.y * per, i1 = min(d, i0 + per);
+  for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
     const float v = __fmul_rn(__fmul_rn(xr[i], inv), w[i]);
     if (xpack) xpack_store(xpack, 2 * cols, c, i, v);
     if (y) y[(size_t)c * ldy + i] = v;
@@ -177,7 +181,8 @@ __global__ void rope_append_kernel(const float *qkv, int heads, int kv_heads, in
   const float *row = qkv + (size_t)c * (qw + 2 * kw);
   const float *ct = cos_t + (size_t)pos * half, *st = sin_t + (size_t)pos * half;
   const int rot_items = (heads + kv_heads) * half;
-  for (int it = threadIdx.x; it < rot_items; it += blockDim.x) {
+  const int first = blockIdx.y * blockDim.x + threadIdx.x, step = blockDim.x * gridDim.y;  // gridDim.y CTAs share a column
+  for (int it = first; it < rot_items; it += step) {
     const int h = it / half, i = it - h * half;
     const float *src = row + (size_t)h * hd;  // q heads then k heads are contiguous in the row
     const float x1 = src[2 * i], x2 = src[2 * i + 1];
@@ -194,7 +199,7 @@ __global__ void rope_append_kernel(const float *qkv, int heads, int kv_heads, in
       dst[half + i] = to_kv<KV>(y2);
     }
   }
-  for (int it = threadIdx.x; it < kw; it += blockDim.x) {
+  for (int it = first; it < kw; it += step) {
     const int h = it / hd, j = it - h * hd;
     v_cache[(((size_t)seq * kv_heads + h) * ctx + pos) * hd + j] = to_kv<KV>(row[qw + kw + it]);
   }
@@ -915,8 +920,10 @@ cudaError_t launch_unpack(const void *xpack, int k, int batch, float *x, int ldx
 }
 cudaError_t launch_rmsnorm_pack(const float *x, int ldx, const float *w, int d, float eps, int cols, const int32_t *col_map,
                                 void *xpack, float *y, int ldy, const LaunchCfg &cfg) {
-  return launch(rmsnorm_pack_kernel, dim3(cols), dim3(512), 0, cfg, x, ldx, w, d, eps, cols, col_map, static_cast<__half *>(xpack),
-                y, ldy);
+  // few columns: four CTAs per column, so the slices are packed side by side instead of by one CTA
+  const unsigned parts = cols <= 64 && d >= 2048 ? 4u : 1u;
+  return launch(rmsnorm_pack_kernel, dim3((unsigned)cols, parts), dim3(512), 0, cfg, x, ldx, w, d, eps, cols, col_map,
+                static_cast<__half *>(xpack), y, ldy);
 }
 cudaError_t launch_rope_append(const RopeArgs &a, const LaunchCfg &cfg) {
   const int rope = a.rope_dim ? a.rope_dim : a.hd;
@@ -940,10 +947,11 @@ cudaError_t launch_rope_append(const RopeArgs &a, const LaunchCfg &cfg) {
     return launch(qkv_variant_kernel<__half>, dim3(a.cols), dim3(256), smem, cfg, a, static_cast<__half *>(a.k_cache),
                   static_cast<__half *>(a.v_cache));
   }
+  const dim3 grid((unsigned)a.cols, a.cols <= 64 ? 4u : 1u);  // few columns: four CTAs share one
   if (a.kv_f32)
-    return launch(rope_append_kernel<float>, dim3(a.cols), dim3(256), 0, cfg, a.qkv, a.heads, a.kv_heads, a.hd, a.ctx, a.col_seq,
+    return launch(rope_append_kernel<float>, grid, dim3(256), 0, cfg, a.qkv, a.heads, a.kv_heads, a.hd, a.ctx, a.col_seq,
                   a.col_pos, a.cos_t, a.sin_t, a.q_out, static_cast<float *>(a.k_cache), static_cast<float *>(a.v_cache));
-  return launch(rope_append_kernel<__half>, dim3(a.cols), dim3(256), 0, cfg, a.qkv, a.heads, a.kv_heads, a.hd, a.ctx, a.col_seq,
+  return launch(rope_append_kernel<__half>, grid, dim3(256), 0, cfg, a.qkv, a.heads, a.kv_heads, a.hd, a.ctx, a.col_seq,
                 a.col_pos, a.cos_t, a.sin_t, a.q_out, static_cast<__half *>(a.k_cache), static_cast<__half *>(a.v_cache));
 }
 size_t attn_scratch_floats(int cols, int heads, int hd, int ctx) {
