@@ -393,6 +393,11 @@ __global__ void __launch_bounds__(THREADS, 2) attn_fused_kernel(const FusedAttnA
     dst[0] = o0;
     dst[1] = o1;
     if (tid == 0 && kvh == 0 && c == 0) trace_stamp(trace, 12, true, false);  // first output pair stored (slot 12)
+    if (A.xpack_out) {
+      const int e = (kvh * G + gq) * HD + d;
+      xpack_store(static_cast<__half *>(A.xpack_out), 2 * A.cols, c, e, o0);
+      xpack_store(static_cast<__half *>(A.xpack_out), 2 * A.cols, c, e + 1, o1);
+    }
     if (A.pack_out) {
       // The sixteen lanes of a half-warp hold one 32-element block of the output projection's input
       // (lane j: elements 2j, 2j + 1): pack it as block fixed point for the integer GEMV (rg_device.cuh).

@@ -286,6 +286,8 @@ struct FusedAttnArgs {
   // projection (qgemv_i8_xq_bytes(heads * hd) bytes; pack_type = that projection's block type)
   uint8_t *pack_out = nullptr;
   int pack_type = 0;
+  // any cols: also leave the output as the packed activations (hi / lo f16 columns) of the f16-MMA GEMV
+  void *xpack_out = nullptr;
 };
 bool fused_attention_supported(int heads, int kv_heads, int hd);
 int fused_attn_per_head(int sm_count, int kv_heads, int cols);

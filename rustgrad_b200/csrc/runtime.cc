@@ -1264,9 +1264,8 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
       fa.max_splits = s->attn_max_splits;
       fa.counters = s->attn_counters;
       fa.out = s->attn_f32;
+      fa.xpack_out = s->attn_pack;  // the O projection's packed input comes out of the same launch
       RG_LAUNCH(s, launch_attention_fused(fa, L));
-      prof_mark(s, PROF_OTHER);
-      RG_LAUNCH(s, launch_pack(s->attn_f32, qw, qw, ncols, s->attn_pack, L));
     } else {
     RopeArgs ra;
     ra.qkv = s->qkv;
