@@ -527,17 +527,17 @@ static void rope_variant(const rg_session *s, const LayerW &W, RopeArgs *ra) {
   ra->v_bias = reinterpret_cast<const float *>(W.v_bias.d);
 }
 
-// Decode rows of distinct sequences on f16 caches: from nine rows on, the tensor-core attention with per-warp
+// Decode rows of distinct sequences on f16 caches: from eight rows on, the tensor-core attention with per-warp
 // cp.async rings (attn_decode_tc.cu) streams K / V faster than the one-launch kernel, whose CTAs load, score and
 // combine one after the other.  Measured on the 8B shape, attention ms per step, new against one-launch: 16 rows
-// 1.52 / 1.88 at context 2100 and 1.05 / 1.24 at 1024; 8 rows 0.99 / 1.05 at 2100 but 3 % behind in whole-job
-// throughput at contexts under 200; 4 rows 0.75 / 0.61.  So eight rows and fewer keep the one-launch kernel.
+// 1.52 / 1.88 at context 2100; 8 rows 0.63 / 0.72 at context 1024 and 0.43 / 0.45 at 200; 6 rows 0.59 / 0.57;
+// 4 rows 0.54 / 0.48.  So seven rows and fewer keep the one-launch kernel.
 static bool decode_tc_attention(const rg_session *s, int ncols) {
   static const bool off = env_flag("RG_B200_NO_ATTN_DECODE_TC");
   static const int min_cols = [] {
     const char *v = getenv("RG_B200_ATTN_TC_MIN_COLS");
     const int n = v ? atoi(v) : 0;
-    return n > 0 ? n : 9;
+    return n > 0 ? n : 8;
   }();
   if (off || s->chunk_is_prompt || ncols < min_cols || ncols > BMAX) return false;
   AttnArgs a;

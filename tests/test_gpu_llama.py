@@ -778,7 +778,7 @@ def test_prompt_attention_on_tensor_cores_with_f16_cache(heads, kv_heads):
 
 @pytest.mark.parametrize("heads,kv_heads", [(4, 1), (4, 2), (2, 2), (8, 1)])
 def test_batched_decode_attention_on_tensor_cores_with_f16_cache(heads, kv_heads):
-    """Nine or more rows decoding together on f16 caches run the tensor-core decode attention
+    """Eight or more rows decoding together on f16 caches run the tensor-core decode attention
     (attn_decode_tc.cu): 1, 2, 4 and 8 query heads per kv head; rows at different positions, so spans end in
     ragged 16-key tiles, some warps of a CTA get no tile, and long rows are cut into several spans; every
     row against its own checker with an f16 cache, three steps."""
