@@ -52,6 +52,19 @@ struct GemvArgs {
   float *y = nullptr;      // EPI_STORE: y[b*ldy + row] = v;  EPI_RESIDUAL: y[b*ldy + row] += v
   int ldy = 0;
   void *ypack = nullptr;   // EPI_SWIGLU: packed output with K' = seg_rows[0]
+  // Deferred RMSNorm between the GEMVs of a batch step (qgemv.cu only; the reference's rms_norm,
+  // src/models/transformer/layer.rs:423-443, with the scalar 1 / rms moved behind the linear map):
+  //  * producer side (EPI_RESIDUAL): besides y += v, the new rows times `pack_w` (the next norm's weight) are
+  //    left packed in `pack_next`, and every CTA leaves the sum of squares of its new rows per batch column in
+  //    ssq_out[cta * 16 + b];
+  //  * consumer side: the input `xpack` holds such un-normalised rows; the outputs are multiplied by
+  //    1 / sqrt(sum over the first ssq_n CTAs' sums / k + norm_eps) of their batch column.
+  void *pack_next = nullptr;
+  const float *pack_w = nullptr;
+  float *ssq_out = nullptr;
+  const float *ssq_in = nullptr;
+  int ssq_n = 0;
+  float norm_eps = 0.0f;
   // Workspace of the K-split form of qgemv_rows.cu (optional; without it matrices with few rows run unsplit):
   // partial tiles, and QGEMV_ROWS_MAX_TILES counters that are zero between launches.
   float *split_scratch = nullptr;
@@ -60,6 +73,7 @@ struct GemvArgs {
 };
 constexpr int QGEMV_ROWS_MAX_TILES = 256;
 cudaError_t launch_qgemv(const GemvArgs &a, const LaunchCfg &cfg);
+int qgemv_grid(int n_rows, int sm_count);  // CTAs launch_qgemv's own kernel uses for a matrix of n_rows rows
 // A second form for 3..16 batch rows on Q4_0 (qgemv_rows.cu: tall row tiles that share one copy of the
 // activations, K split over CTAs for matrices with few rows), behind RG_B200_ROWS_GEMV=1; launch_qgemv checks
 // the arguments and dispatches.

@@ -70,7 +70,15 @@ struct KParams {
   int rows_per_cta;
   int stages;
   int *status;
+  // deferred RMSNorm (see GemvArgs)
+  __half *pack_next;
+  const float *pack_w;
+  float *ssq_out;
+  const float *ssq_in;
+  int ssq_n;
+  float norm_eps;
 };
+constexpr int STATIC_SMEM = 2304;  // sq_s, inv_s, inv_bar below (rounded up)
 
 // Eight nibbles of one 32-bit word -> four half2 registers of exact integers (n - 8).
 // Low nibbles: (1024 | n) - 1032.  High nibbles stay in place: (1024 | 16 n) * (1/16) - 72, one
@@ -162,6 +170,10 @@ __global__ void __launch_bounds__(THREADS, 1)
   const int x_stage_bytes = G::KC * P.S * 64;
   const int stage_bytes = (W_STAGE_BYTES + x_stage_bytes + 127) & ~127;
 
+  __shared__ float sq_s[R][16];  // squares of the new residual rows of a group, per batch column
+  __shared__ float inv_s[16];    // 1 / rms of this launch's input, per batch column
+  __shared__ __align__(8) uint64_t inv_bar;
+
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r_begin = blockIdx.x * P.rows_per_cta;
   const int r_end = min(P.n_rows, r_begin + P.rows_per_cta);
@@ -175,6 +187,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], CW);
     }
+    mbar_init(&inv_bar, 1);
     *dead = 0;
     mbar_fence_init();
   }
@@ -228,6 +241,18 @@ __global__ void __launch_bounds__(THREADS, 1)
     pdl_wait();
     grp = 0, c = 0;
     for (int u = 0; u < pro; ++u, next()) issue(u, grp, c, false, true);
+    if (P.ssq_in) {
+      // 1 / rms of the input rows from the producers' per-CTA sums of squares: lane b + 16 h adds the CTAs
+      // h, h + 2, ...; even and odd halves meet in a fixed order.  The consumers need it at their first epilogue.
+      const int b = lane & 15;
+      float sum = 0.0f;
+#pragma unroll 8
+      for (int i = lane >> 4; i < P.ssq_n; i += 2) sum += __ldcg(P.ssq_in + i * 16 + b);
+      sum += __shfl_down_sync(0xffffffffu, sum, 16);
+      if (lane < 16) inv_s[lane] = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)(P.kb * 32)), P.norm_eps)));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&inv_bar);
+    }
     int stage = 0;
     uint32_t phase = 0;  // parity of the consumers' release being waited for
     for (int u = pro; u < units; ++u, next()) {
@@ -252,6 +277,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[mt][j][i] = 0.0f;
 
+  bool inv_ready = false;
+  float run_ssq = 0.0f;  // threads 0..15: sum of squares of this CTA's new residual rows, batch column tid
   // loop state kept incrementally: no integer division in the steady state
   int stage = 0, c = 0, grp = 0;
   uint32_t phase = 0;
@@ -351,28 +378,49 @@ __global__ void __launch_bounds__(THREADS, 1)
             acc[mt][j][hs * 2 + 1] = 0.0f;
           }
       asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+      if (P.ssq_in && !inv_ready) {
+        mbar_wait_bounded(&inv_bar, 0, dead, P.status);
+        inv_ready = true;
+      }
       const int vr0 = r_begin + grp * GROUP_ROWS;
       const int tid = threadIdx.x;
+      const bool fuse_norm = EPI == EPI_RESIDUAL && P.pack_next != nullptr;
       for (int idx = tid; idx < GROUP_ROWS * NB; idx += CW * 32) {
         const int row = idx / NB, b = idx - row * NB;
         const int vrow = vr0 + row;
-        if (vrow >= r_end || b >= P.batch) continue;
+        if (vrow >= r_end || b >= P.batch) {
+          if (fuse_norm) sq_s[row][b] = 0.0f;
+          continue;
+        }
         float v = 0.0f;
 #pragma unroll
         for (int w8 = 0; w8 < CW; ++w8) v += red[(w8 * R + row) * NB + b];
+        const float inv = P.ssq_in ? inv_s[b] : 1.0f;  // the input rows were packed without their 1 / rms
+        if (P.ssq_in) v = __fmul_rn(v, inv);
         if (EPI == EPI_STORE) {
           P.y[(size_t)b * P.ldy + vrow] = v;
         } else if (EPI == EPI_RESIDUAL) {
           float *dst = P.y + (size_t)b * P.ldy + vrow;
-          *dst = __fadd_rn(*dst, v);
+          const float nv = __fadd_rn(*dst, v);
+          *dst = nv;
+          if (fuse_norm) {  // the next norm's input: weight now, 1 / rms behind the next GEMV
+            xpack_store(P.pack_next, P.S, b, vrow, __fmul_rn(nv, P.pack_w[vrow]));
+            sq_s[row][b] = __fmul_rn(nv, nv);
+          }
         } else {
           float up = 0.0f;
 #pragma unroll
           for (int w8 = 0; w8 < CW; ++w8) up += red[(w8 * R + row + 16) * NB + b];
+          if (P.ssq_in) up = __fmul_rn(up, inv);
           xpack_store(P.ypack, P.S, b, vrow, swiglu(v, up));
         }
       }
       asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+      if (fuse_norm && tid < 16) {  // rows in order; the next write of sq_s comes after this thread's next barrier
+        float sum = 0.0f;
+        for (int row = 0; row < GROUP_ROWS; ++row) sum += sq_s[row][tid];
+        run_ssq += sum;
+      }
     }
     if (++c == n_chunks) {
       c = 0;
@@ -383,6 +431,8 @@ __global__ void __launch_bounds__(THREADS, 1)
       phase ^= 1u;
     }
   }
+  if (EPI == EPI_RESIDUAL && P.ssq_out && threadIdx.x < 16)
+    P.ssq_out[blockIdx.x * 16 + threadIdx.x] = (int)threadIdx.x < P.batch ? run_ssq : 0.0f;
 }
 
 // cuTensorMapEncodeTiled resolved through the runtime, so the library needs no link to libcuda.
@@ -439,6 +489,12 @@ cudaError_t launch_t(const GemvArgs &a, const LaunchCfg &cfg) {
   P.ldy = a.ldy;
   P.ypack = static_cast<__half *>(a.ypack);
   P.status = cfg.status;
+  P.pack_next = EPI == EPI_RESIDUAL ? static_cast<__half *>(a.pack_next) : nullptr;
+  P.pack_w = a.pack_w;
+  P.ssq_out = a.ssq_out;
+  P.ssq_in = a.ssq_in;
+  P.ssq_n = a.ssq_n;
+  P.norm_eps = a.norm_eps;
   const int sms = cfg.sm_count > 0 ? cfg.sm_count : 148;
   // rows are dealt out in box-height units so that no TMA box straddles two CTAs or two segments
   const int units = (P.n_rows + BOXR - 1) / BOXR;
@@ -446,7 +502,7 @@ cudaError_t launch_t(const GemvArgs &a, const LaunchCfg &cfg) {
   const int grid = (P.n_rows + P.rows_per_cta - 1) / P.rows_per_cta;
   const int stage_bytes = (R * G::RS + G::KC * P.S * 64 + 127) & ~127;
   const int fixed = 128 + CW * R * 4 * NT * 4;
-  int stages = (SMEM_LIMIT - fixed) / stage_bytes;
+  int stages = (SMEM_LIMIT - STATIC_SMEM - fixed) / stage_bytes;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages < 2) return cudaErrorInvalidConfiguration;
   P.stages = stages;
@@ -464,7 +520,7 @@ cudaError_t launch_t(const GemvArgs &a, const LaunchCfg &cfg) {
   static DeviceOnce attr_once;  // per instantiation and device
   bool *attr_flag = attr_once.slot();
   if (!attr_flag || !*attr_flag) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT - STATIC_SMEM);
     if (e != cudaSuccess) return e;
     if (attr_flag) *attr_flag = true;
   }
@@ -493,6 +549,13 @@ cudaError_t launch_e(const GemvArgs &a, const LaunchCfg &cfg) {
 
 }  // namespace
 
+int qgemv_grid(int n_rows, int sm_count) {
+  const int sms = sm_count > 0 ? sm_count : 148;
+  const int units = (n_rows + BOXR - 1) / BOXR;
+  const int rows_per_cta = ((units + sms - 1) / sms) * BOXR;
+  return (n_rows + rows_per_cta - 1) / rows_per_cta;
+}
+
 size_t xpack_bytes(int k, int batch) { return (size_t)((k + 31) / 32 * 32) * (size_t)batch * 4; }
 
 cudaError_t launch_qgemv(const GemvArgs &a, const LaunchCfg &cfg) {
@@ -502,7 +565,12 @@ cudaError_t launch_qgemv(const GemvArgs &a, const LaunchCfg &cfg) {
     if (a.epi != EPI_SWIGLU && a.seg_rows[i] % BOXR) return cudaErrorInvalidValue;  // boxes may not straddle segments
   for (int i = 0; i < a.nseg; ++i)
     if ((reinterpret_cast<uintptr_t>(a.w[i]) & 15) != 0) return cudaErrorInvalidValue;
-  if (qgemv_rows_applies(a)) return launch_qgemv_rows(a, cfg);
+  if (a.pack_next && (a.epi != EPI_RESIDUAL || !a.pack_w || !a.ssq_out)) return cudaErrorInvalidValue;
+  if (a.ssq_in && a.ssq_n < 1) return cudaErrorInvalidValue;
+  if (qgemv_rows_applies(a)) {
+    if (a.pack_next || a.ssq_in) return cudaErrorInvalidValue;  // the deferred norm lives in this file's kernel only
+    return launch_qgemv_rows(a, cfg);
+  }
   count_launch(LC_QGEMV);
   // column tiles of four batch rows (hi and lo column each): 1, 2 or 4 tiles
   const int nt = a.batch > 8 ? 4 : a.batch > 4 ? 2 : 1;

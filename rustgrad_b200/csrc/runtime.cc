@@ -309,6 +309,9 @@ struct rg_session {
   int rope_dim = 0;  // rotary lanes per head (head_dim for the plain layer)
   float *split_scratch = nullptr;  // K-split partial tiles of the tensor-core GEMM at small token counts and of the 3..16-row GEMV
   unsigned *gemv_counters = nullptr;  // arrival counters of the K-split row GEMV, zero between launches
+  // deferred RMSNorm of 3..16-row steps: per-CTA sums of squares left by the O (a) and down (b) projections
+  float *ssq_a = nullptr, *ssq_b = nullptr;
+  bool defer_norm_ok = false;
   void *xb = nullptr;  // 16-bit operand planes (hi, lo) of the tensor-core path: [2][WMAX][max(d, qw, ffn_l)]
   int gemm_mode = QGEMM_F16X3;
   int xb_ld = 0;
@@ -410,10 +413,20 @@ enum GemvSite { SITE_ANY = 0, SITE_QKV = 1, SITE_O = 2, SITE_GATE_UP = 3, SITE_D
 // at a time.
 static inline void prof_mark(rg_session *s, int kind) { s->cur_kind = kind; }
 
+// Deferred RMSNorm around a packed projection of a batch step (GemvArgs): the input rows come without their
+// 1 / rms (ssq_in), and / or the residual rows this projection completes leave packed for the next norm.
+struct NormFuse {
+  const float *ssq_in = nullptr;
+  int ssq_n = 0;
+  void *pack_next = nullptr;
+  const float *pack_w = nullptr;
+  float *ssq_out = nullptr;
+};
+
 // y = W x for one projection given as `n` row segments sharing K.  Packed segments of one type go
 // out as a single fused launch; dense ones run the dense kernel segment by segment.
 static int32_t linear(rg_session *s, const DevTensor *const *w, int n, const void *in_pack, const float *in_f32, int ld_in,
-                      int batch, int epi, float *y, int ldy) {
+                      int batch, int epi, float *y, int ldy, const NormFuse *nf = nullptr) {
   bool all_packed = true;
   for (int i = 0; i < n; ++i) all_packed = all_packed && w[i]->packed() && w[i]->type == w[0]->type;
   prof_mark(s, PROF_GEMV);
@@ -434,6 +447,14 @@ static int32_t linear(rg_session *s, const DevTensor *const *w, int n, const voi
     a.split_scratch = s->split_scratch;
     a.split_scratch_floats = s->split_scratch ? (size_t)BMAX * 2 * s->sm_count * 256 : 0;
     a.split_counters = s->gemv_counters;
+    if (nf) {
+      a.ssq_in = nf->ssq_in;
+      a.ssq_n = nf->ssq_n;
+      a.norm_eps = s->cfg.norm_eps;
+      a.pack_next = nf->pack_next;
+      a.pack_w = nf->pack_w;
+      a.ssq_out = nf->ssq_out;
+    }
     RG_LAUNCH(s, launch_qgemv(a, lcfg(s)));
     return RG_OK;
   }
@@ -454,8 +475,15 @@ static int32_t linear(rg_session *s, const DevTensor *const *w, int n, const voi
       a.split_scratch = s->split_scratch;
       a.split_scratch_floats = s->split_scratch ? (size_t)BMAX * 2 * s->sm_count * 256 : 0;
       a.split_counters = s->gemv_counters;
+      if (nf) {  // (pack_next needs the one-launch form: whole rows of the residual stream)
+        if (nf->pack_next) return fail(RG_INVALID_ARGUMENT, "deferred norm output on a segmented projection");
+        a.ssq_in = nf->ssq_in;
+        a.ssq_n = nf->ssq_n;
+        a.norm_eps = s->cfg.norm_eps;
+      }
       RG_LAUNCH(s, launch_qgemv(a, lcfg(s)));
     } else {
+      if (nf && (nf->ssq_in || nf->pack_next)) return fail(RG_INVALID_ARGUMENT, "deferred norm on a dense projection");
       DenseGemvArgs a;
       a.type = w[i]->type;
       a.w = w[i]->d;
@@ -1232,14 +1260,25 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
   first.pdl = false;  // follows a memcpy, not a kernel
   prof_mark(s, PROF_OTHER);
   RG_LAUNCH(s, launch_row_gather(s->token_embd.type, s->token_embd.d, d, ctl->tokens, ncols, s->x, d, first));
+  const bool defer = s->defer_norm_ok && ncols >= 3 && ncols <= 16;
+  const int ssq_n = qgemv_grid(d, s->sm_count);  // CTAs of a projection with d output rows
   for (int l = 0; l < c.n_layers; ++l) {
     const LayerW &W = s->layers[(size_t)l];
     const bool qkv_dense = !W.q.packed() || !W.k.packed() || !W.v.packed();
-    prof_mark(s, PROF_OTHER);
-    RG_LAUNCH(s, launch_rmsnorm_pack(s->x, d, reinterpret_cast<const float *>(W.attn_norm.d), d, c.norm_eps, ncols, nullptr,
-                                     s->xn_pack, qkv_dense ? s->xn_f32 : nullptr, d, L));
+    // 3..16 rows on packed weights: only the first norm of the step is a launch of its own; afterwards the O and
+    // down projections leave the new residual rows packed (times the next norm's weight) with their sums of
+    // squares, and the projection that consumes them applies 1 / rms to its outputs
+    NormFuse qkv_in;
+    if (defer && l > 0) {
+      qkv_in.ssq_in = s->ssq_b;
+      qkv_in.ssq_n = ssq_n;
+    } else {
+      prof_mark(s, PROF_OTHER);
+      RG_LAUNCH(s, launch_rmsnorm_pack(s->x, d, reinterpret_cast<const float *>(W.attn_norm.d), d, c.norm_eps, ncols, nullptr,
+                                       s->xn_pack, qkv_dense ? s->xn_f32 : nullptr, d, L));
+    }
     const DevTensor *qkvw[3] = {&W.q, &W.k, &W.v};
-    int32_t rc = linear(s, qkvw, 3, s->xn_pack, s->xn_f32, d, ncols, EPI_STORE, s->qkv, qkv_w);
+    int32_t rc = linear(s, qkvw, 3, s->xn_pack, s->xn_f32, d, ncols, EPI_STORE, s->qkv, qkv_w, &qkv_in);
     if (rc) return rc;
     prof_mark(s, PROF_ATTN);
     const bool tc_attn = decode_tc_attention(s, ncols);
@@ -1310,15 +1349,23 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
     if (s->tp_world > 1) {
       if ((rc = linear(s, ow, 1, s->attn_pack, s->attn_f32, qw, ncols, EPI_STORE, s->tp_part[0], d))) return rc;
       if ((rc = tp_reduce_add(s, ncols, 0))) return rc;
-    } else if ((rc = linear(s, ow, 1, s->attn_pack, s->attn_f32, qw, ncols, EPI_RESIDUAL, s->x, d))) {
-      return rc;
+    } else {
+      NormFuse o_out;
+      if (defer) {
+        o_out.pack_next = s->xn_pack;
+        o_out.pack_w = reinterpret_cast<const float *>(W.ffn_norm.d);
+        o_out.ssq_out = s->ssq_a;
+      }
+      if ((rc = linear(s, ow, 1, s->attn_pack, s->attn_f32, qw, ncols, EPI_RESIDUAL, s->x, d, &o_out))) return rc;
     }
     LaunchCfg after = L;
     if (s->tp_world > 1 && !s->tp_fused) after.pdl = false;
     const bool gu_dense = !W.gate.packed() || !W.up.packed() || W.gate.type != W.up.type;
-    prof_mark(s, PROF_OTHER);
-    RG_LAUNCH(s, launch_rmsnorm_pack(s->x, d, reinterpret_cast<const float *>(W.ffn_norm.d), d, c.norm_eps, ncols, nullptr,
-                                     s->xn_pack, gu_dense ? s->xn_f32 : nullptr, d, after));
+    if (!defer) {
+      prof_mark(s, PROF_OTHER);
+      RG_LAUNCH(s, launch_rmsnorm_pack(s->x, d, reinterpret_cast<const float *>(W.ffn_norm.d), d, c.norm_eps, ncols, nullptr,
+                                       s->xn_pack, gu_dense ? s->xn_f32 : nullptr, d, after));
+    }
     if (!gu_dense) {
       prof_mark(s, PROF_GEMV);
       GemvArgs a;
@@ -1332,6 +1379,11 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
       a.batch = ncols;
       a.epi = EPI_SWIGLU;
       a.ypack = s->h_pack;
+      if (defer) {
+        a.ssq_in = s->ssq_a;
+        a.ssq_n = ssq_n;
+        a.norm_eps = c.norm_eps;
+      }
       RG_LAUNCH(s, launch_qgemv(a, L));
       if (!W.down.packed()) RG_LAUNCH(s, launch_unpack(s->h_pack, s->ffn_l, ncols, s->h_f32, s->ffn_l, L));
     } else {
@@ -1344,8 +1396,14 @@ static int32_t forward(rg_session *s, int ncols, int n_logit_cols, bool advance)
     if (s->tp_world > 1) {
       if ((rc = linear(s, dw, 1, s->h_pack, s->h_f32, s->ffn_l, ncols, EPI_STORE, s->tp_part[1], d))) return rc;
       if ((rc = tp_reduce_add(s, ncols, 1))) return rc;
-    } else if ((rc = linear(s, dw, 1, s->h_pack, s->h_f32, s->ffn_l, ncols, EPI_RESIDUAL, s->x, d))) {
-      return rc;
+    } else {
+      NormFuse d_out;
+      if (defer && l + 1 < c.n_layers) {
+        d_out.pack_next = s->xn_pack;
+        d_out.pack_w = reinterpret_cast<const float *>(s->layers[(size_t)l + 1].attn_norm.d);
+        d_out.ssq_out = s->ssq_b;
+      }
+      if ((rc = linear(s, dw, 1, s->h_pack, s->h_f32, s->ffn_l, ncols, EPI_RESIDUAL, s->x, d, &d_out))) return rc;
     }
   }
   if (n_logit_cols > 0) {
@@ -1880,6 +1938,10 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   RG_TRY(dalloc(s.get(), &raw, (size_t)2 * WMAX * s->xb_ld * 2));
   // splits <= 2 * SMs / tiles and rows <= tiles * rows_per_cta (256 with two row tiles per CTA)
   RG_TRY(dalloc(s.get(), &s->split_scratch, (size_t)BMAX * 2 * s->sm_count * 256));
+  RG_TRY(dalloc(s.get(), &s->ssq_a, (size_t)256 * 16));
+  RG_TRY(dalloc(s.get(), &s->ssq_b, (size_t)256 * 16));
+  RG_CUDA(cudaMemsetAsync(s->ssq_a, 0, sizeof(float) * 256 * 16, s->stream));
+  RG_CUDA(cudaMemsetAsync(s->ssq_b, 0, sizeof(float) * 256 * 16, s->stream));
   RG_TRY(dalloc(s.get(), &s->gemv_counters, (size_t)QGEMV_ROWS_MAX_TILES));
   RG_CUDA(cudaMemsetAsync(s->gemv_counters, 0, sizeof(unsigned) * QGEMV_ROWS_MAX_TILES, s->stream));
   s->gemm_mode = (s->opt.gemm_operand_mode >= 1 && s->opt.gemm_operand_mode <= 3) ? s->opt.gemm_operand_mode - 1 : QGEMM_F16X3;
@@ -1953,6 +2015,14 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
 #undef RG_TRY
   // take ownership of the weights
   s->layers = p->layers;
+  {
+    bool ok = s->tp_world == 1 && s->sm_count <= 256 && !qgemv_rows_enabled() && !env_flag("RG_B200_NO_DEFERRED_NORM") &&
+              s->cfg.d_model % 256 == 0;
+    for (const LayerW &W : s->layers)
+      ok = ok && W.q.packed() && W.k.packed() && W.v.packed() && W.o.packed() && W.gate.packed() && W.up.packed() &&
+           W.down.packed() && W.gate.type == W.up.type;
+    s->defer_norm_ok = ok;
+  }
   s->token_embd = p->token_embd;
   s->output_norm = p->output_norm;
   s->output = p->output;
