@@ -511,6 +511,9 @@ def main():
         }
     if parity is not None:
         line["tp_parity"] = parity
+    if B > 16 and n == 1:
+        line["profile_note"] = ("the timed steps run as equal chunks of at most 16 rows; `roofline` and `profile_ms_per_step` "
+                                "describe ONE step over all rows on the 17..32-row path (RG_B200_WIDE_DECODE_ONE_STEP=1 times that)")
     if not args.no_cpu_baseline:
         tok_s, t_token, sample = cpu_reference_arm(args, wl, threads, prefill + args.warmup)
         line["cpu_baseline"] = {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}

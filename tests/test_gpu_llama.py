@@ -189,16 +189,17 @@ def test_tensor_core_path_for_long_prompts_and_wide_decode_batches():
 
 
 def test_twenty_rows_decode_on_the_tensor_core_path(monkeypatch):
-    """Decode batches of 17..32 rows (and, with the GEMV route switched off, 9..16) run the projections on
-    the tcgen05 GEMM with compensated f16 operands: logit bar and greedy ids against the checker."""
+    """Decode batches of 17..32 rows: by default cut into equal chunks of at most 16 rows that run the GEMV path
+    (20 rows = two steps of 10); with RG_B200_WIDE_DECODE_ONE_STEP=1 (and, with the GEMV route switched off,
+    for 9..16 rows) the projections run on the tcgen05 GEMM with compensated f16 operands.  Logit bar and
+    greedy ids against the checker for all three."""
     cfg = synth.scaled(synth.TINY, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn_dim=1024, vocab=640, n_layers=3,
                        rope_theta=500000.0, max_context=64)
     tensors = synth.build_tensors(cfg, seed=9, body_type=quant.Q4_0, embed_type=quant.Q8_0, head_type=quant.Q8_0,
                                   tied_head=False)
-    for rows, no_gemv16 in ((20, False), (12, True)):
-        if no_gemv16:
-            monkeypatch.setenv("RG_B200_NO_GEMV16", "1")
-        before = session.launch_count("qgemm_tc")
+    for rows, env, kernel in ((20, None, "qgemv"), (20, "RG_B200_WIDE_DECODE_ONE_STEP", "qgemm_tc"), (12, "RG_B200_NO_GEMV16", "qgemm_tc")):
+        if env:
+            monkeypatch.setenv(env, "1")
         s = session.LlamaCudaPlan.from_tensors(cfg, tensors, session.CudaSessionTarget(kv_f32=True, max_batch=rows,
                                                                                       max_context=64)).prepare()
         oracles = [O.OracleModel(cfg, tensors, threads=2) for _ in range(rows)]
@@ -207,6 +208,7 @@ def test_twenty_rows_decode_on_the_tensor_core_path(monkeypatch):
             p = synth.prompt_ids(cfg, 3 + r % 5, seed=70 + r)
             s.prefill_ids(p, row=r)
             toks.append(O.select_greedy(oracles[r].forward(p, O.MODE_FAST)))
+        before = {k: session.launch_count(k) for k in ("qgemv", "qgemm_tc")}
         differing = 0
         for _ in range(2):
             logits, greedy = s.decode(toks, want_logits=True)
@@ -217,9 +219,13 @@ def test_twenty_rows_decode_on_the_tensor_core_path(monkeypatch):
                 nxt.append(O.select_greedy(w))
                 differing += int(greedy[r]) != nxt[r]
             toks = nxt
-        print(f"{rows} rows on the tensor-core path: greedy ids differing from the checker: {differing}")
+        print(f"{rows} rows ({env or 'chunked'}): greedy ids differing from the checker: {differing}")
         assert differing == 0
-        assert session.launch_count("qgemm_tc") > before
+        assert session.launch_count(kernel) > before[kernel]
+        if kernel == "qgemv":
+            assert session.launch_count("qgemm_tc") == before["qgemm_tc"]
+        if env:
+            monkeypatch.delenv(env)
 
 
 def test_stop_on_eos_and_last_token_not_fed_back(tiny):
@@ -785,7 +791,7 @@ def test_batched_decode_attention_on_tensor_cores_with_f16_cache(heads, kv_heads
     cfg = synth.scaled(synth.TINY, d_model=heads * 128, n_heads=heads, n_kv_heads=kv_heads, head_dim=128, ffn_dim=512, vocab=320,
                        n_layers=2, rope_theta=500000.0, max_context=700)
     tensors = synth.build_tensors(cfg, seed=33, body_type=quant.Q4_0)
-    # 9 and 16 rows: projections on the GEMV; 20 rows: projections on the tcgen05 GEMM, same attention kernel
+    # 9 and 16 rows: one step; 20 rows: two steps of 10 rows
     for rows, lengths in ((9, (1, 15, 16, 17, 63, 64, 65, 130, 600)), (16, tuple(5 + 41 * r for r in range(16))),
                           (20, tuple(3 + 29 * r for r in range(20)))):
         s = session.LlamaCudaPlan.from_tensors(cfg, tensors, session.CudaSessionTarget(max_context=700, max_batch=rows)).prepare()
