@@ -203,7 +203,9 @@ int32_t rg_b200_prefill_rows(rg_session *s, const int32_t *rows, const int32_t *
                              float *last_logits, int32_t *greedy);
 /* run_token (metal_generation.rs:1123-1138) generalised to `batch` rows (batch.rs:140-162):
  * tokens[batch] in; logits [batch, vocab] and/or greedy ids [batch] out (either may be NULL).
- * Rows 0..batch-1 advance by one position only when the whole step succeeds. */
+ * Rows 0..batch-1 advance by one position only when the whole step succeeds.  The rows are independent
+ * sequences: on Q4_0 / Q8_0 weights a step of more than 16 rows runs as equal chunks of at most 16 rows (the
+ * same results; rg_b200_decode_rows and rg_b200_decode_loop likewise). */
 int32_t rg_b200_decode(rg_session *s, const int32_t *tokens, int32_t batch, float *logits, int32_t *greedy);
 /* generate_ids with greedy selection (generation.rs:106-160, metal_generation.rs:1052-1175):
  * requires a fresh sequence, prefill then one-token steps, stops on EOS/EOT, the last token is
@@ -226,7 +228,8 @@ int32_t rg_b200_generate_sampled(rg_session *s, const int32_t *prompt, size_t n_
 /* Device-resident greedy loop for rows 0..batch-1: `steps` replays of the decode graph with the
  * selected token fed back on the device (the device-greedy session of
  * metal_greedy_generation.rs:52-72).  first_tokens[batch] seeds it; out [steps, batch] (nullable)
- * receives the ids after the last step.  gpu_ms (nullable) is the CUDA-event time of the loop. */
+ * receives the ids after the last step.  gpu_ms (nullable) is the CUDA-event time of the loop (summed over
+ * the chunks of a batch beyond 16 rows, which run one after the other, each for all steps). */
 int32_t rg_b200_decode_loop(rg_session *s, const int32_t *first_tokens, int32_t batch, int32_t steps,
                             int32_t *out, float *gpu_ms);
 /* Profiling pass in the vocabulary of rustgrad's CUDA event recorder (src/cuda_profile.rs:15-60).
