@@ -312,6 +312,7 @@ struct rg_session {
   // deferred RMSNorm of 3..16-row steps: per-CTA sums of squares left by the O (a) and down (b) projections
   float *ssq_a = nullptr, *ssq_b = nullptr;
   bool defer_norm_ok = false;
+  bool packed_layers = false;  // one GPU and every layer tensor Q4_0 / Q8_0 with whole 256-element groups: the GEMV paths serve 3..16 rows
   void *xb = nullptr;  // 16-bit operand planes (hi, lo) of the tensor-core path: [2][WMAX][max(d, qw, ffn_l)]
   int gemm_mode = QGEMM_F16X3;
   int xb_ld = 0;
@@ -2016,12 +2017,12 @@ int32_t rg_b200_session_prepare(rg_plan *p, rg_session **out) {
   // take ownership of the weights
   s->layers = p->layers;
   {
-    bool ok = s->tp_world == 1 && s->sm_count <= 256 && !qgemv_rows_enabled() && !env_flag("RG_B200_NO_DEFERRED_NORM") &&
-              s->cfg.d_model % 256 == 0;
+    bool ok = s->tp_world == 1 && s->cfg.d_model % 256 == 0;
     for (const LayerW &W : s->layers)
       ok = ok && W.q.packed() && W.k.packed() && W.v.packed() && W.o.packed() && W.gate.packed() && W.up.packed() &&
            W.down.packed() && W.gate.type == W.up.type;
-    s->defer_norm_ok = ok;
+    s->packed_layers = ok;
+    s->defer_norm_ok = ok && s->sm_count <= 256 && !qgemv_rows_enabled() && !env_flag("RG_B200_NO_DEFERRED_NORM");
   }
   s->token_embd = p->token_embd;
   s->output_norm = p->output_norm;
@@ -2279,7 +2280,7 @@ int32_t rg_b200_prefill_rows(rg_session *s, const int32_t *rows, const int32_t *
 // tokens/s at 32 rows), so such a step is cut into equal chunks of at most 16 rows.  The rows are independent
 // sequences, so the result is the same; positions move only when every chunk has succeeded.
 static int decode_chunk_rows(const rg_session *s, int n) {
-  if (n <= 16 || !s->defer_norm_ok || env_flag("RG_B200_WIDE_DECODE_ONE_STEP")) return n;
+  if (n <= 16 || !s->packed_layers || env_flag("RG_B200_WIDE_DECODE_ONE_STEP")) return n;
   const int chunks = (n + 15) / 16;
   return (n + chunks - 1) / chunks;
 }
