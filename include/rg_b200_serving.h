@@ -45,7 +45,8 @@ typedef enum rg_serving_status {
   RG_SERVING_SESSION = 9,              /* a session verb failed: value = its rg_status; rg_b200_last_error has the text */
   RG_SERVING_TOKENIZER = 10,           /* value = rg_tok_status */
   RG_SERVING_INVALID_ARGUMENT = 11,
-  RG_SERVING_NOT_COMPLETE = 12         /* result asked of a request that has not finished */
+  RG_SERVING_NOT_COMPLETE = 12,        /* result asked of a request that has not finished */
+  RG_SERVING_ACTIVE_REQUESTS = 13      /* rebind of a scheduler that still has unfinished requests */
 } rg_serving_status;
 
 typedef struct rg_serving_error {
@@ -149,6 +150,17 @@ size_t rg_b200_scheduler_pending(const rg_scheduler *s);
 size_t rg_b200_scheduler_completed(const rg_scheduler *s, uint64_t *ids, size_t cap);
 void rg_b200_scheduler_prefix_stats(const rg_scheduler *s, rg_prefix_stats *out);
 void rg_b200_scheduler_invalidate_prefix_cache(rg_scheduler *s);
+/* LlamaServingScheduler::rebind (serving/mod.rs:528-547): an idle scheduler (no unfinished request, else
+ * RG_SERVING_ACTIVE_REQUESTS) takes another session and tokenizer.  When the session differs from the bound
+ * one (another object, vocabulary or context length; for a backend table also any other verb) every cached prefix is dropped -- its snapshots are freed
+ * through the OLD session -- before a new request can be admitted; *changed (nullable) is then 1, else 0.
+ * Finished requests keep their results.  The new session must hold as many cache rows as the scheduler was
+ * created with.  `options` (nullable) replaces the stop ids and the BOS rule; its other fields are ignored. */
+int32_t rg_b200_scheduler_rebind(rg_scheduler *s, rg_session *session, const rg_tokenizer *tokenizer,
+                                 const rg_serving_options *options, int32_t *changed, rg_serving_error *err);
+int32_t rg_b200_scheduler_rebind_with_backend(rg_scheduler *s, const rg_serving_backend *backend,
+                                              const rg_tokenizer *tokenizer, const rg_serving_options *options,
+                                              int32_t *changed, rg_serving_error *err);
 
 /* One step (serving/mod.rs:557-690): selects up to batch_size unfinished requests in arrival order,
  * admits the new ones (longest cached prefix, then a prefill of the rest), decodes one token for

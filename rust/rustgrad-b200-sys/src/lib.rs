@@ -3,7 +3,7 @@
 //!
 //! Every item mirrors a declaration of `include/rg_b200.h`, `include/rg_b200_tokenizer.h`,
 //! `include/rg_b200_workflow.h` or `include/rg_b200_serving.h`; the headers carry the documentation and, for each entry point, the
-//! rustgrad interface it stands in for.  All 95 exports are declared here.
+//! rustgrad interface it stands in for.  All 97 exports are declared here.
 #![allow(non_camel_case_types)]
 
 use core::ffi::{c_char, c_void};
@@ -381,4 +381,6 @@ unsafe extern "C" {
     pub fn rg_b200_scheduler_prefix_stats(s: *const rg_scheduler, out: *mut rg_prefix_stats);
     pub fn rg_b200_scheduler_invalidate_prefix_cache(s: *mut rg_scheduler);
     pub fn rg_b200_scheduler_step(s: *mut rg_scheduler, events: *mut rg_token_event, cap: usize, n_events: *mut usize, err: *mut rg_serving_error) -> i32;
+    pub fn rg_b200_scheduler_rebind(s: *mut rg_scheduler, session: *mut rg_session, tokenizer: *const rg_tokenizer, options: *const rg_serving_options, changed: *mut i32, err: *mut rg_serving_error) -> i32;
+    pub fn rg_b200_scheduler_rebind_with_backend(s: *mut rg_scheduler, backend: *const rg_serving_backend, tokenizer: *const rg_tokenizer, options: *const rg_serving_options, changed: *mut i32, err: *mut rg_serving_error) -> i32;
 }

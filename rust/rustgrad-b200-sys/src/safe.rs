@@ -532,6 +532,34 @@ impl<'s> LlamaCudaServingScheduler<'s> {
     pub fn invalidate_prefix_cache(&mut self) {
         unsafe { rg_b200_scheduler_invalidate_prefix_cache(self.raw) }
     }
+
+    /// `rebind` (serving/mod.rs:528-547): an idle scheduler takes another session; `Ok(true)` when it differs
+    /// from the bound one, in which case every cached prefix was dropped.  Kind 13 (`ActiveRequests`) while
+    /// requests are unfinished.  `stop_ids`, when given, replace the stop rule.
+    pub fn rebind<'n>(self, session: &'n mut LlamaCudaSession, stop_ids: Option<&[i32]>) -> Result<(LlamaCudaServingScheduler<'n>, bool), LlamaCudaServingError> {
+        let options = stop_ids.map(|ids| rg_serving_options {
+            batch_size: self.batch_size as i32,
+            max_rows: 0,
+            prefix_max_entries: 0,
+            prefix_max_bytes: 0,
+            stop_ids: ids.as_ptr(),
+            n_stop_ids: ids.len(),
+            has_bos: 0,
+            bos_id: 0,
+        });
+        let mut changed = 0i32;
+        let mut err = rg_serving_error::default();
+        let rc = unsafe {
+            rg_b200_scheduler_rebind(self.raw, session.as_raw(), core::ptr::null(),
+                                     options.as_ref().map_or(core::ptr::null(), |o| o as *const _), &mut changed, &mut err)
+        };
+        if rc != 0 {
+            return Err(LlamaCudaServingError { kind: rc, value: err.value, value2: err.value2 });
+        }
+        let rebound = LlamaCudaServingScheduler { raw: self.raw, batch_size: self.batch_size, _session: core::marker::PhantomData };
+        core::mem::forget(self);  // the handle lives on in `rebound`
+        Ok((rebound, changed != 0))
+    }
 }
 
 impl Drop for LlamaCudaServingScheduler<'_> {

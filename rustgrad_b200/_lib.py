@@ -65,7 +65,8 @@ EXPORTS = [
     "rg_b200_scheduler_new", "rg_b200_scheduler_new_with_backend", "rg_b200_scheduler_free", "rg_b200_scheduler_submit_ids",
     "rg_b200_scheduler_submit_text", "rg_b200_scheduler_submit_chat", "rg_b200_scheduler_status", "rg_b200_scheduler_result",
     "rg_b200_scheduler_remove", "rg_b200_scheduler_pending", "rg_b200_scheduler_completed", "rg_b200_scheduler_prefix_stats",
-    "rg_b200_scheduler_invalidate_prefix_cache", "rg_b200_scheduler_step",
+    "rg_b200_scheduler_invalidate_prefix_cache", "rg_b200_scheduler_step", "rg_b200_scheduler_rebind",
+    "rg_b200_scheduler_rebind_with_backend",
 ]
 
 _lib = None

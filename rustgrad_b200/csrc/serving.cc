@@ -233,9 +233,7 @@ int32_t rg_b200_scheduler_new_with_backend(const rg_serving_backend *backend, co
   return RG_SERVING_OK;
 }
 
-int32_t rg_b200_scheduler_new(rg_session *session, const rg_tokenizer *tokenizer, const rg_serving_options *options,
-                              rg_scheduler **out, rg_serving_error *err) {
-  if (!session) return fail(err, RG_SERVING_INVALID_ARGUMENT);
+static rg_serving_backend session_backend(rg_session *session) {
   rg_serving_backend be{};
   be.ctx = session;
   be.vocab = rg_b200_vocab_size(session);
@@ -248,7 +246,47 @@ int32_t rg_b200_scheduler_new(rg_session *session, const rg_tokenizer *tokenizer
   be.snapshot_restore = be_snapshot_restore;
   be.snapshot_free = be_snapshot_free;
   be.prefill_rows = be_prefill_rows;
+  return be;
+}
+
+int32_t rg_b200_scheduler_new(rg_session *session, const rg_tokenizer *tokenizer, const rg_serving_options *options,
+                              rg_scheduler **out, rg_serving_error *err) {
+  if (!session) return fail(err, RG_SERVING_INVALID_ARGUMENT);
+  const rg_serving_backend be = session_backend(session);
   return rg_b200_scheduler_new_with_backend(&be, tokenizer, options, out, err);
+}
+
+// serving/mod.rs:528-547.  The cached snapshots belong to the session that made them: they are destroyed
+// (through the table still in place) before the new table is taken.
+int32_t rg_b200_scheduler_rebind_with_backend(rg_scheduler *s, const rg_serving_backend *backend, const rg_tokenizer *tokenizer,
+                                              const rg_serving_options *o, int32_t *changed, rg_serving_error *err) {
+  if (!s || !backend) return fail(err, RG_SERVING_INVALID_ARGUMENT);
+  if (o && o->n_stop_ids && !o->stop_ids) return fail(err, RG_SERVING_INVALID_ARGUMENT);
+  if (rg_b200_scheduler_pending(s) != 0) return fail(err, RG_SERVING_ACTIVE_REQUESTS, (int64_t)rg_b200_scheduler_pending(s));
+  // the same session: the same object behind the same verbs
+  const bool differs = backend->ctx != s->be.ctx || backend->vocab != s->be.vocab || backend->max_context != s->be.max_context ||
+                       backend->reset_row != s->be.reset_row || backend->prefill_select != s->be.prefill_select ||
+                       backend->decode_rows != s->be.decode_rows || backend->select != s->be.select ||
+                       backend->snapshot_create != s->be.snapshot_create || backend->snapshot_restore != s->be.snapshot_restore ||
+                       backend->snapshot_free != s->be.snapshot_free || backend->prefill_rows != s->be.prefill_rows;
+  if (differs) s->prefixes.invalidate();
+  s->be = *backend;
+  s->tokenizer = tokenizer;
+  if (o) {
+    s->stop_ids.clear();
+    s->stop_ids.insert(o->stop_ids, o->stop_ids + o->n_stop_ids);
+    s->has_bos = o->has_bos != 0;
+    s->bos_id = o->bos_id;
+  }
+  if (changed) *changed = differs ? 1 : 0;
+  return RG_SERVING_OK;
+}
+
+int32_t rg_b200_scheduler_rebind(rg_scheduler *s, rg_session *session, const rg_tokenizer *tokenizer,
+                                 const rg_serving_options *options, int32_t *changed, rg_serving_error *err) {
+  if (!session) return fail(err, RG_SERVING_INVALID_ARGUMENT);
+  const rg_serving_backend be = session_backend(session);
+  return rg_b200_scheduler_rebind_with_backend(s, &be, tokenizer, options, changed, err);
 }
 
 void rg_b200_scheduler_free(rg_scheduler *s) {

@@ -1,7 +1,7 @@
 """Continuous batching with a prefix cache over one ``LlamaCudaSession``: the verbs of rustgrad's
 ``LlamaServingScheduler`` (src/models/transformer/serving/mod.rs:371-690) -- submit_ids /
 submit_text / submit_chat / status / result / remove / step / prefix_stats /
-invalidate_prefix_cache -- bound to the scheduler of ``include/rg_b200_serving.h``.
+invalidate_prefix_cache / rebind -- bound to the scheduler of ``include/rg_b200_serving.h``.
 
 The policy (arrival order, batch size, cache rows, prefix cache, admission checks) is compiled code
 in the library; this module only converts arguments and results.  ``ServingBackend`` lets a test
@@ -19,7 +19,7 @@ from . import _lib
 from .tokenizer import ROLES
 
 KINDS = ["Ok", "EmptyBatch", "EmptyPrompt", "ContextLength", "TokenOutOfRange", "InvalidTemperature", "UniformTapeLength",
-         "InvalidUniform", "UnknownRequest", "Session", "Tokenizer", "InvalidArgument", "NotComplete"]
+         "InvalidUniform", "UnknownRequest", "Session", "Tokenizer", "InvalidArgument", "NotComplete", "ActiveRequests"]
 STATUS = ["queued", "running", "complete"]
 f32p, i32p, vp = C.POINTER(C.c_float), C.POINTER(C.c_int32), C.c_void_p
 
@@ -93,6 +93,8 @@ def _L():
     L.rg_b200_scheduler_invalidate_prefix_cache.restype = None
     L.rg_b200_scheduler_invalidate_prefix_cache.argtypes = [vp]
     L.rg_b200_scheduler_step.argtypes = [vp, C.POINTER(_Event), C.c_size_t, C.POINTER(C.c_size_t), ep]
+    L.rg_b200_scheduler_rebind.argtypes = [vp, vp, vp, C.POINTER(_Options), C.POINTER(C.c_int32), ep]
+    L.rg_b200_scheduler_rebind_with_backend.argtypes = [vp, C.POINTER(_Backend), vp, C.POINTER(_Options), C.POINTER(C.c_int32), ep]
     L._serving_bound = True
     return L
 
@@ -187,6 +189,10 @@ class ServingBackend:
     greedy prompts in one pass; without it the scheduler prefills them one after the other."""
 
     def _table(self) -> _Backend:
+        # one table per object: the scheduler recognises a session by its verbs (rebind)
+        cached = getattr(self, "_table_cache", None)
+        if cached is not None:
+            return cached
         v = self.vocab
 
         def tape(p, n):
@@ -229,7 +235,8 @@ class ServingBackend:
                       _SNAP_FREE(lambda _, h: self.snapshot_free(h))]
         if self.prefill_rows is not None:
             self._keep.append(_PREFILL_ROWS(prefill_rows))
-        return _Backend(None, self.vocab, self.max_context, *self._keep)
+        self._table_cache = _Backend(None, self.vocab, self.max_context, *self._keep)
+        return self._table_cache
 
 
 class LlamaServingScheduler:
@@ -337,6 +344,30 @@ class LlamaServingScheduler:
 
     def invalidate_prefix_cache(self) -> None:
         self._lib.rg_b200_scheduler_invalidate_prefix_cache(self._h)
+
+    def rebind(self, session, tokenizer=None, stop_ids=None, bos_id: Optional[int] = None) -> bool:
+        """LlamaServingScheduler::rebind (serving/mod.rs:528-547): an idle scheduler takes another session
+        (or backend table) and tokenizer; True when the session differs, in which case every cached prefix
+        was dropped.  ``stop_ids`` (with ``bos_id``) replaces the stop rule when given."""
+        opts = None
+        if stop_ids is not None:
+            stops = np.array(sorted(int(t) for t in stop_ids), dtype=np.int32)
+            opts = _Options(self.batch_size, 0, 0, 0, stops.ctypes.data_as(i32p), stops.size, int(bos_id is not None), bos_id or 0)
+        changed, err = C.c_int32(), _Error()
+        tok = tokenizer._h if tokenizer is not None else None
+        if isinstance(session, ServingBackend):
+            table = session._table()
+            rc = self._lib.rg_b200_scheduler_rebind_with_backend(self._h, C.byref(table), tok, C.byref(opts) if opts else None,
+                                                                 C.byref(changed), C.byref(err))
+        else:
+            table = None
+            rc = self._lib.rg_b200_scheduler_rebind(self._h, session._h, tok, C.byref(opts) if opts else None,
+                                                    C.byref(changed), C.byref(err))
+        if rc:
+            _raise(rc, err)
+        # the callables of the old table stay alive until here: dropped prefixes were freed through them
+        self.session, self.tokenizer, self._table = session, tokenizer, table
+        return bool(changed.value)
 
     # ---- one step (serving/mod.rs:557-690) -----------------------------------------------------
     def step(self) -> list[TokenEvent]:

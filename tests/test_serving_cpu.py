@@ -351,3 +351,38 @@ def test_greedy_prompts_admitted_together_are_prefilled_in_one_pass():
     assert [sched.status(r) for r in (d, e)] == ["queued", "queued"]
     run_all(sched)
     assert sched.result(d).generated_ids == alone([40, 41], 1) and sched.result(e).generated_ids == alone([42], 1)
+
+
+def test_rebind_needs_an_idle_scheduler_and_drops_prefixes_only_for_another_session():
+    """LlamaServingScheduler::rebind (serving/mod.rs:528-547): refused while a request is unfinished; the same
+    session keeps the cached prefixes; another session drops them (freed through the session that made them)
+    and serves the next requests; finished results stay readable; new stop ids apply from then on."""
+    a, b = FakeSession(), FakeSession()
+    sched = serving.LlamaServingScheduler(a, batch_size=2, prefix_max_entries=8, prefix_max_bytes=1 << 20)
+    first = sched.submit_ids([1, 2, 3, 4], serving.GenerationConfig(3))
+    sched.step()
+    with pytest.raises(serving.ServingError) as e:
+        sched.rebind(b)
+    assert e.value.kind == "ActiveRequests" and e.value.value == 1
+    run_all(sched)
+    assert sched.prefix_stats()["entries"] == 1 and len(a.snapshots) == 1
+    # the same session: nothing is dropped, and the cached prefix still serves a hit
+    assert sched.rebind(a) is False
+    assert sched.prefix_stats()["entries"] == 1 and len(a.snapshots) == 1
+    again = sched.submit_ids([1, 2, 3, 4, 5], serving.GenerationConfig(2))
+    run_all(sched)
+    assert sched.prefix_stats()["hits"] == 1
+    assert sched.result(again).generated_ids == alone([1, 2, 3, 4, 5], 2)
+    # another session: every prefix goes, its snapshots are freed by the session that made them
+    held = len(a.snapshots)
+    assert held >= 1
+    assert sched.rebind(b, stop_ids=[next_token([9, 8, 7])]) is True
+    assert sched.prefix_stats()["entries"] == 0 and len(a.snapshots) == 0
+    assert sched.result(first).generated_ids == alone([1, 2, 3, 4], 3)  # finished results are kept
+    before = len(a.calls)
+    late = sched.submit_ids([9, 8, 7], serving.GenerationConfig(4))
+    run_all(sched)
+    assert len(a.calls) == before and any(c[0] == "prefill" for c in b.calls)  # only the new session works
+    r = sched.result(late)
+    assert r.generated_ids == alone([9, 8, 7], 4, stop=(next_token([9, 8, 7]),)) and r.stopped
+    assert sched.prefix_stats()["misses"] >= 1
