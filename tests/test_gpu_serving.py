@@ -227,3 +227,27 @@ def test_text_and_chat_requests_share_steps_and_decode_their_results():
         gen = alone(data, prompt, 6)
         cut = next((i + 1 for i, t in enumerate(gen) if t in stops), len(gen))
         assert r.generated_ids == gen[:cut] and r.decoded == check_tok.decode(gen[:cut])
+
+
+def test_rebind_moves_an_idle_scheduler_to_another_session(model):
+    """rebind (serving/mod.rs:528-547) over device sessions: the prefixes cached from the first session are
+    dropped (their device copies freed), and requests after the rebind run on the second session's weights."""
+    cfg, data = model
+    other = synth.gguf_bytes(cfg, synth.build_tensors(cfg, seed=3, body_type=quant.Q8_0))
+    a, b = make_session(data, max_batch=2, kv_f32=True), make_session(other, max_batch=2, kv_f32=True)
+    prompt = synth.prompt_ids(cfg, 9, seed=61)
+    sched = serving.LlamaServingScheduler(a, batch_size=2, prefix_max_entries=4, prefix_max_bytes=1 << 28)
+    first = sched.submit_ids(prompt, serving.GenerationConfig(5))
+    sched.step()
+    with pytest.raises(serving.ServingError) as e:
+        sched.rebind(b)
+    assert e.value.kind == "ActiveRequests"
+    run_all(sched)
+    assert sched.result(first).generated_ids == alone(data, prompt, 5)
+    assert sched.prefix_stats()["entries"] == 1
+    assert sched.rebind(a) is False and sched.prefix_stats()["entries"] == 1
+    assert sched.rebind(b) is True and sched.prefix_stats()["entries"] == 0
+    second = sched.submit_ids(prompt, serving.GenerationConfig(5))
+    run_all(sched)
+    assert sched.result(second).generated_ids == alone(other, prompt, 5)
+    assert sched.result(first).generated_ids == alone(data, prompt, 5)  # finished results are kept
