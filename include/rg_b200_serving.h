@@ -169,6 +169,62 @@ int32_t rg_b200_scheduler_rebind_with_backend(rg_scheduler *s, const rg_serving_
  * requests it had not reached keep their state. */
 int32_t rg_b200_scheduler_step(rg_scheduler *s, rg_token_event *events, size_t cap, size_t *n_events, rg_serving_error *err);
 
+/* ---- Fixed-size batch generation: LlamaBatchGenerator (src/models/transformer/batch_generation.rs:58-189) ----
+ * `batch_size` cache rows; every generate starts from empty rows, runs all prompts together (one batched
+ * prefill where the session offers it, then one decode launch sequence per step over the rows that have not
+ * stopped) and commits the rows' lengths only when every row, sample and decode succeeded.  The rows are
+ * independent: each produces exactly what it produces alone. */
+typedef struct rg_batch_generator rg_batch_generator;
+
+/* LlamaBatchGenerationError (batch_generation.rs:251-279). */
+typedef enum rg_batch_status {
+  RG_BATCH_OK = 0,
+  RG_BATCH_SESSION = 1,              /* a session verb failed (Model / non-finite logits): value = its rg_status */
+  RG_BATCH_INVALID_TEMPERATURE = 2,
+  RG_BATCH_TOKENIZER = 3,            /* value = rg_tok_status */
+  RG_BATCH_BATCH_SIZE = 4,           /* value = expected, value2 = actual */
+  RG_BATCH_EMPTY_PROMPT = 5,         /* row */
+  RG_BATCH_CONTEXT_OVERFLOW = 6,
+  RG_BATCH_CONTEXT_LENGTH = 7,       /* row; value = requested, value2 = maximum */
+  RG_BATCH_UNIFORM_TAPE_LENGTH = 8,  /* value = required, value2 = actual */
+  RG_BATCH_INVALID_UNIFORM = 9,      /* value = index of the first bad entry */
+  RG_BATCH_TOKEN_OUT_OF_RANGE = 10,  /* row; value = token, value2 = vocabulary */
+  RG_BATCH_INVALID_ARGUMENT = 11
+} rg_batch_status;
+
+typedef struct rg_batch_error {
+  int32_t kind;
+  int32_t row;
+  int64_t value, value2;
+} rg_batch_error;
+
+/* LlamaBatchGenerator::new.  Of `options` (nullable) the stop ids and the BOS rule are used.  The session
+ * (rows 0 .. batch_size-1 of it) and the tokenizer (nullable: no text in, decoded results empty) must outlive
+ * the generator. */
+int32_t rg_b200_batch_generator_new(rg_session *session, const rg_tokenizer *tokenizer, int32_t batch_size,
+                                    const rg_serving_options *options, rg_batch_generator **out, rg_batch_error *err);
+int32_t rg_b200_batch_generator_new_with_backend(const rg_serving_backend *backend, const rg_tokenizer *tokenizer,
+                                                 int32_t batch_size, const rg_serving_options *options,
+                                                 rg_batch_generator **out, rg_batch_error *err);
+void rg_b200_batch_generator_free(rg_batch_generator *g);
+/* cache_lengths: returns batch_size, writes at most cap committed row lengths.  clear: all rows empty. */
+size_t rg_b200_batch_generator_cache_lengths(const rg_batch_generator *g, size_t *lengths, size_t cap);
+void rg_b200_batch_generator_clear(rg_batch_generator *g);
+/* generate_ids (batch_generation.rs:104-189).  Prompt r is lens[r] ids of `ids` (laid end to end);
+ * n_prompts must equal batch_size.  Checks in the reference's order: batch size; per row empty prompt, context
+ * overflow, context length; token ids; the sampling (temperature, tape length, tape values) -- all before any
+ * device work.  Gumbel-max reads the [step, batch, vocabulary] row-major tape of `sampling`.  A row stops at a
+ * stop id (the stop token is reported, not fed back); the last generated token is never fed back.  On failure
+ * the committed lengths are the ones from before the call. */
+int32_t rg_b200_batch_generate_ids(rg_batch_generator *g, const int32_t *ids, const size_t *lens, size_t n_prompts,
+                                   size_t max_new_tokens, const rg_serving_sampling *sampling, rg_batch_error *err);
+/* generate_texts (batch_generation.rs:85-102): encodes every text, puts the BOS id in front when configured. */
+int32_t rg_b200_batch_generate_texts(rg_batch_generator *g, const char *const *texts, const size_t *text_bytes, size_t n_prompts,
+                                     size_t max_new_tokens, const rg_serving_sampling *sampling, rg_batch_error *err);
+/* Row `row` of the last successful generation (LlamaBatchSequence); request_id carries the row.  The pointers
+ * stay valid until the next generate or free.  RG_BATCH_INVALID_ARGUMENT when there is none. */
+int32_t rg_b200_batch_sequence(const rg_batch_generator *g, size_t row, rg_serving_result *out);
+
 #ifdef __cplusplus
 }
 #endif

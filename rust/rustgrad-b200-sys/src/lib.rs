@@ -3,7 +3,7 @@
 //!
 //! Every item mirrors a declaration of `include/rg_b200.h`, `include/rg_b200_tokenizer.h`,
 //! `include/rg_b200_workflow.h` or `include/rg_b200_serving.h`; the headers carry the documentation and, for each entry point, the
-//! rustgrad interface it stands in for.  All 97 exports are declared here.
+//! rustgrad interface it stands in for.  All 105 exports are declared here.
 #![allow(non_camel_case_types)]
 
 use core::ffi::{c_char, c_void};
@@ -193,6 +193,38 @@ pub mod serving_status {
     pub const TOKENIZER: i32 = 10;
     pub const INVALID_ARGUMENT: i32 = 11;
     pub const NOT_COMPLETE: i32 = 12;
+    pub const ACTIVE_REQUESTS: i32 = 13;
+}
+
+/// Opaque batch-generator handle of `include/rg_b200_serving.h` (`LlamaBatchGenerator`).
+#[repr(C)]
+pub struct rg_batch_generator {
+    _private: [u8; 0],
+}
+
+/// `rg_batch_status`: `LlamaBatchGenerationError` by kind.
+pub mod batch_status {
+    pub const OK: i32 = 0;
+    pub const SESSION: i32 = 1;
+    pub const INVALID_TEMPERATURE: i32 = 2;
+    pub const TOKENIZER: i32 = 3;
+    pub const BATCH_SIZE: i32 = 4;
+    pub const EMPTY_PROMPT: i32 = 5;
+    pub const CONTEXT_OVERFLOW: i32 = 6;
+    pub const CONTEXT_LENGTH: i32 = 7;
+    pub const UNIFORM_TAPE_LENGTH: i32 = 8;
+    pub const INVALID_UNIFORM: i32 = 9;
+    pub const TOKEN_OUT_OF_RANGE: i32 = 10;
+    pub const INVALID_ARGUMENT: i32 = 11;
+}
+
+#[repr(C)]
+#[derive(Clone, Copy, Debug, Default, PartialEq, Eq)]
+pub struct rg_batch_error {
+    pub kind: i32,
+    pub row: i32,
+    pub value: i64,
+    pub value2: i64,
 }
 
 #[repr(C)]
@@ -383,4 +415,12 @@ unsafe extern "C" {
     pub fn rg_b200_scheduler_step(s: *mut rg_scheduler, events: *mut rg_token_event, cap: usize, n_events: *mut usize, err: *mut rg_serving_error) -> i32;
     pub fn rg_b200_scheduler_rebind(s: *mut rg_scheduler, session: *mut rg_session, tokenizer: *const rg_tokenizer, options: *const rg_serving_options, changed: *mut i32, err: *mut rg_serving_error) -> i32;
     pub fn rg_b200_scheduler_rebind_with_backend(s: *mut rg_scheduler, backend: *const rg_serving_backend, tokenizer: *const rg_tokenizer, options: *const rg_serving_options, changed: *mut i32, err: *mut rg_serving_error) -> i32;
+    pub fn rg_b200_batch_generator_new(session: *mut rg_session, tokenizer: *const rg_tokenizer, batch_size: i32, options: *const rg_serving_options, out: *mut *mut rg_batch_generator, err: *mut rg_batch_error) -> i32;
+    pub fn rg_b200_batch_generator_new_with_backend(backend: *const rg_serving_backend, tokenizer: *const rg_tokenizer, batch_size: i32, options: *const rg_serving_options, out: *mut *mut rg_batch_generator, err: *mut rg_batch_error) -> i32;
+    pub fn rg_b200_batch_generator_free(g: *mut rg_batch_generator);
+    pub fn rg_b200_batch_generator_cache_lengths(g: *const rg_batch_generator, lengths: *mut usize, cap: usize) -> usize;
+    pub fn rg_b200_batch_generator_clear(g: *mut rg_batch_generator);
+    pub fn rg_b200_batch_generate_ids(g: *mut rg_batch_generator, ids: *const i32, lens: *const usize, n_prompts: usize, max_new_tokens: usize, sampling: *const rg_serving_sampling, err: *mut rg_batch_error) -> i32;
+    pub fn rg_b200_batch_generate_texts(g: *mut rg_batch_generator, texts: *const *const c_char, text_bytes: *const usize, n_prompts: usize, max_new_tokens: usize, sampling: *const rg_serving_sampling, err: *mut rg_batch_error) -> i32;
+    pub fn rg_b200_batch_sequence(g: *const rg_batch_generator, row: usize, out: *mut rg_serving_result) -> i32;
 }

@@ -562,6 +562,96 @@ impl<'s> LlamaCudaServingScheduler<'s> {
     }
 }
 
+/// `LlamaBatchGenerator` (batch_generation.rs:58-189) over rows `0 .. batch_size` of one session.
+pub struct LlamaCudaBatchGenerator<'s> {
+    raw: *mut rg_batch_generator,
+    batch_size: usize,
+    _session: core::marker::PhantomData<&'s mut LlamaCudaSession>,
+}
+
+/// `LlamaBatchGenerationError` by kind (`batch_status`), with the row and the numbers it carries.
+#[derive(Clone, Copy, Debug, Eq, PartialEq)]
+pub struct LlamaCudaBatchGenerationError {
+    pub kind: i32,
+    pub row: i32,
+    pub value: i64,
+    pub value2: i64,
+}
+
+impl<'s> LlamaCudaBatchGenerator<'s> {
+    pub fn new(session: &'s mut LlamaCudaSession, batch_size: usize, stop_ids: &[i32]) -> Result<Self, LlamaCudaBatchGenerationError> {
+        let options = rg_serving_options {
+            batch_size: batch_size as i32,
+            max_rows: 0,
+            prefix_max_entries: 0,
+            prefix_max_bytes: 0,
+            stop_ids: stop_ids.as_ptr(),
+            n_stop_ids: stop_ids.len(),
+            has_bos: 0,
+            bos_id: 0,
+        };
+        let mut raw = core::ptr::null_mut();
+        let mut err = rg_batch_error::default();
+        let rc = unsafe { rg_b200_batch_generator_new(session.as_raw(), core::ptr::null(), batch_size as i32, &options, &mut raw, &mut err) };
+        if rc != 0 {
+            return Err(LlamaCudaBatchGenerationError { kind: rc, row: err.row, value: err.value, value2: err.value2 });
+        }
+        Ok(Self { raw, batch_size, _session: core::marker::PhantomData })
+    }
+
+    pub fn cache_lengths(&self) -> Vec<usize> {
+        let mut out = vec![0usize; self.batch_size];
+        unsafe { rg_b200_batch_generator_cache_lengths(self.raw, out.as_mut_ptr(), out.len()) };
+        out
+    }
+
+    pub fn clear(&mut self) {
+        unsafe { rg_b200_batch_generator_clear(self.raw) }
+    }
+
+    /// `generate_ids` (batch_generation.rs:104-189); the Gumbel-max tape is `[step, batch, vocabulary]`.
+    pub fn generate_ids(&mut self, prompts: &[Vec<i32>], max_new_tokens: usize, sampling: LlamaCudaServingSampling<'_>)
+                        -> Result<Vec<LlamaCudaServingResult>, LlamaCudaBatchGenerationError> {
+        let flat: Vec<i32> = prompts.iter().flatten().copied().collect();
+        let lens: Vec<usize> = prompts.iter().map(|p| p.len()).collect();
+        let s = match sampling {
+            LlamaCudaServingSampling::Greedy => rg_serving_sampling { greedy: 1, temperature: 0.0, uniforms: core::ptr::null(), n_uniforms: 0 },
+            LlamaCudaServingSampling::GumbelMax { temperature, uniforms } => {
+                rg_serving_sampling { greedy: 0, temperature, uniforms: uniforms.as_ptr(), n_uniforms: uniforms.len() }
+            }
+        };
+        let mut err = rg_batch_error::default();
+        let rc = unsafe { rg_b200_batch_generate_ids(self.raw, flat.as_ptr(), lens.as_ptr(), prompts.len(), max_new_tokens, &s, &mut err) };
+        if rc != 0 {
+            return Err(LlamaCudaBatchGenerationError { kind: rc, row: err.row, value: err.value, value2: err.value2 });
+        }
+        let mut out = Vec::with_capacity(self.batch_size);
+        for row in 0..self.batch_size {
+            let mut r: rg_serving_result = unsafe { core::mem::zeroed() };
+            if unsafe { rg_b200_batch_sequence(self.raw, row, &mut r) } != 0 {
+                return Err(LlamaCudaBatchGenerationError { kind: batch_status::INVALID_ARGUMENT, row: row as i32, value: 0, value2: 0 });
+            }
+            let prompt = unsafe { core::slice::from_raw_parts(r.prompt_ids, r.n_prompt_ids) };
+            let generated = unsafe { core::slice::from_raw_parts(r.generated_ids, r.n_generated_ids) };
+            let text = unsafe { core::slice::from_raw_parts(r.decoded as *const u8, r.decoded_bytes) };
+            out.push(LlamaCudaServingResult {
+                request_id: r.request_id,
+                prompt_ids: prompt.iter().map(|&t| t as u32).collect(),
+                generated_ids: generated.iter().map(|&t| t as u32).collect(),
+                decoded: String::from_utf8_lossy(text).into_owned(),
+                stopped: r.stopped != 0,
+            });
+        }
+        Ok(out)
+    }
+}
+
+impl Drop for LlamaCudaBatchGenerator<'_> {
+    fn drop(&mut self) {
+        unsafe { rg_b200_batch_generator_free(self.raw) }
+    }
+}
+
 impl Drop for LlamaCudaServingScheduler<'_> {
     fn drop(&mut self) {
         unsafe { rg_b200_scheduler_free(self.raw) }

@@ -67,6 +67,9 @@ EXPORTS = [
     "rg_b200_scheduler_remove", "rg_b200_scheduler_pending", "rg_b200_scheduler_completed", "rg_b200_scheduler_prefix_stats",
     "rg_b200_scheduler_invalidate_prefix_cache", "rg_b200_scheduler_step", "rg_b200_scheduler_rebind",
     "rg_b200_scheduler_rebind_with_backend",
+    "rg_b200_batch_generator_new", "rg_b200_batch_generator_new_with_backend", "rg_b200_batch_generator_free",
+    "rg_b200_batch_generator_cache_lengths", "rg_b200_batch_generator_clear", "rg_b200_batch_generate_ids",
+    "rg_b200_batch_generate_texts", "rg_b200_batch_sequence",
 ]
 
 _lib = None

@@ -580,3 +580,233 @@ int32_t rg_b200_scheduler_step(rg_scheduler *s, rg_token_event *events, size_t c
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Fixed-size batch generation (src/models/transformer/batch_generation.rs:58-247) over the same
+// table of session verbs.
+// ---------------------------------------------------------------------------------------------
+struct rg_batch_generator {
+  rg_serving_backend be{};
+  const rg_tokenizer *tokenizer = nullptr;
+  int32_t batch = 0;
+  std::set<int32_t> stop_ids;
+  bool has_bos = false;
+  int32_t bos_id = 0;
+  std::vector<size_t> lengths;  // committed
+  struct Sequence {
+    std::vector<int32_t> prompt, generated;
+    std::string decoded;
+    bool stopped = false;
+  };
+  std::vector<Sequence> last;
+  bool has_result = false;
+};
+
+namespace {
+
+int32_t bfail(rg_batch_error *err, int32_t kind, int32_t row = 0, int64_t value = 0, int64_t value2 = 0) {
+  if (err) *err = rg_batch_error{kind, row, value, value2};
+  return kind;
+}
+
+// validate_sampling (batch_generation.rs:215-247)
+int32_t check_batch_sampling(const rg_serving_sampling *sp, size_t steps, size_t batch, size_t vocab, rg_batch_error *err) {
+  if (!sp || sp->greedy) return RG_BATCH_OK;
+  if (!std::isfinite(sp->temperature) || sp->temperature <= 0.0f) return bfail(err, RG_BATCH_INVALID_TEMPERATURE);
+  size_t required = 0;
+  if (__builtin_mul_overflow(steps, batch, &required) || __builtin_mul_overflow(required, vocab, &required))
+    return bfail(err, RG_BATCH_CONTEXT_OVERFLOW);
+  if (sp->n_uniforms < required || (required && !sp->uniforms))
+    return bfail(err, RG_BATCH_UNIFORM_TAPE_LENGTH, 0, (int64_t)required, (int64_t)(sp->uniforms ? sp->n_uniforms : 0));
+  for (size_t i = 0; i < required; ++i) {
+    const float u = sp->uniforms[i];
+    if (!std::isfinite(u) || u < 0.0f || u >= 1.0f) return bfail(err, RG_BATCH_INVALID_UNIFORM, 0, (int64_t)i);
+  }
+  return RG_BATCH_OK;
+}
+
+// finish (batch_generation.rs:192-213): the decoded text of every row; a tokenizer failure fails the call
+int32_t decode_rows_text(rg_batch_generator *g, std::vector<rg_batch_generator::Sequence> *seqs, rg_batch_error *err) {
+  for (auto &q : *seqs) {
+    q.decoded.clear();
+    if (!g->tokenizer) continue;
+    std::vector<uint32_t> gen(q.generated.begin(), q.generated.end());
+    rg_tok_error terr{};
+    size_t bytes = 0;
+    int32_t trc = rg_b200_tokenizer_decode(g->tokenizer, gen.data(), gen.size(), nullptr, 0, &bytes, &terr);
+    if (trc != RG_TOK_OK && !(trc == RG_TOK_INVALID_ARGUMENT && bytes > 0)) return bfail(err, RG_BATCH_TOKENIZER, 0, trc);
+    q.decoded.resize(bytes);
+    if (bytes && (trc = rg_b200_tokenizer_decode(g->tokenizer, gen.data(), gen.size(), &q.decoded[0], bytes, &bytes, &terr)) != RG_TOK_OK)
+      return bfail(err, RG_BATCH_TOKENIZER, 0, trc);
+  }
+  return RG_BATCH_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t rg_b200_batch_generator_new_with_backend(const rg_serving_backend *backend, const rg_tokenizer *tokenizer, int32_t batch_size,
+                                                 const rg_serving_options *o, rg_batch_generator **out, rg_batch_error *err) {
+  if (!backend || !out || batch_size < 1) return bfail(err, RG_BATCH_INVALID_ARGUMENT);
+  if (o && o->n_stop_ids && !o->stop_ids) return bfail(err, RG_BATCH_INVALID_ARGUMENT);
+  auto g = new rg_batch_generator();
+  g->be = *backend;
+  g->tokenizer = tokenizer;
+  g->batch = batch_size;
+  if (o) {
+    g->stop_ids.insert(o->stop_ids, o->stop_ids + o->n_stop_ids);
+    g->has_bos = o->has_bos != 0;
+    g->bos_id = o->bos_id;
+  }
+  g->lengths.assign((size_t)batch_size, 0);
+  *out = g;
+  return RG_BATCH_OK;
+}
+
+int32_t rg_b200_batch_generator_new(rg_session *session, const rg_tokenizer *tokenizer, int32_t batch_size,
+                                    const rg_serving_options *options, rg_batch_generator **out, rg_batch_error *err) {
+  if (!session) return bfail(err, RG_BATCH_INVALID_ARGUMENT);
+  const rg_serving_backend be = session_backend(session);
+  return rg_b200_batch_generator_new_with_backend(&be, tokenizer, batch_size, options, out, err);
+}
+
+void rg_b200_batch_generator_free(rg_batch_generator *g) { delete g; }
+
+size_t rg_b200_batch_generator_cache_lengths(const rg_batch_generator *g, size_t *lengths, size_t cap) {
+  if (!g) return 0;
+  for (size_t i = 0; i < g->lengths.size() && i < cap && lengths; ++i) lengths[i] = g->lengths[i];
+  return g->lengths.size();
+}
+
+void rg_b200_batch_generator_clear(rg_batch_generator *g) {
+  if (g) std::fill(g->lengths.begin(), g->lengths.end(), (size_t)0);
+}
+
+int32_t rg_b200_batch_generate_ids(rg_batch_generator *g, const int32_t *ids, const size_t *lens, size_t n_prompts,
+                                   size_t max_new, const rg_serving_sampling *sampling, rg_batch_error *err) {
+  if (!g || (n_prompts && (!lens || !ids))) return bfail(err, RG_BATCH_INVALID_ARGUMENT);
+  const size_t batch = (size_t)g->batch, vocab = (size_t)g->be.vocab, ctx = (size_t)g->be.max_context;
+  if (n_prompts != batch) return bfail(err, RG_BATCH_BATCH_SIZE, 0, (int64_t)batch, (int64_t)n_prompts);
+  for (size_t r = 0; r < batch; ++r) {
+    if (lens[r] == 0) return bfail(err, RG_BATCH_EMPTY_PROMPT, (int32_t)r);
+    size_t requested = 0;
+    if (__builtin_add_overflow(lens[r], max_new, &requested)) return bfail(err, RG_BATCH_CONTEXT_OVERFLOW);
+    if (requested > ctx) return bfail(err, RG_BATCH_CONTEXT_LENGTH, (int32_t)r, (int64_t)requested, (int64_t)ctx);
+  }
+  {
+    size_t off = 0;
+    for (size_t r = 0; r < batch; ++r)
+      for (size_t i = 0; i < lens[r]; ++i, ++off)
+        if (ids[off] < 0 || (size_t)ids[off] >= vocab) return bfail(err, RG_BATCH_TOKEN_OUT_OF_RANGE, (int32_t)r, ids[off], (int64_t)vocab);
+  }
+  int32_t rc = check_batch_sampling(sampling, max_new, batch, vocab, err);
+  if (rc) return rc;
+  const bool greedy = !sampling || sampling->greedy;
+  const float temperature = greedy ? 0.0f : sampling->temperature;
+
+  std::vector<rg_batch_generator::Sequence> seqs(batch);
+  {
+    size_t off = 0;
+    for (size_t r = 0; r < batch; ++r) {
+      seqs[r].prompt.assign(ids + off, ids + off + lens[r]);
+      off += lens[r];
+    }
+  }
+  auto commit = [&](const std::vector<size_t> &lengths) {
+    g->last = std::move(seqs);
+    g->has_result = true;
+    g->lengths = lengths;
+    return RG_BATCH_OK;
+  };
+  if (max_new == 0) {  // nothing runs and the cache stays as it is
+    if ((rc = decode_rows_text(g, &seqs, err))) return rc;
+    return commit(g->lengths);
+  }
+
+  // ---- staged generation: the rows start empty; nothing is committed before the end
+  std::vector<size_t> staged(batch, 0);
+  auto session_failed = [&](int32_t status) { return bfail(err, RG_BATCH_SESSION, 0, status); };
+  std::vector<int32_t> rows(batch), sel(batch, -1);
+  for (size_t r = 0; r < batch; ++r) {
+    rows[r] = (int32_t)r;
+    if ((rc = g->be.reset_row(g->be.ctx, (int32_t)r))) return session_failed(rc);
+  }
+  if (greedy && batch > 1 && g->be.prefill_rows) {
+    std::vector<float> logits(batch * vocab);
+    if ((rc = g->be.prefill_rows(g->be.ctx, rows.data(), ids, lens, (int32_t)batch, logits.data(), sel.data()))) return session_failed(rc);
+  } else {
+    std::vector<float> logits(vocab);
+    size_t off = 0;
+    for (size_t r = 0; r < batch; ++r) {
+      const float *tape = greedy ? nullptr : sampling->uniforms + r * vocab;  // step 0, row r
+      if ((rc = g->be.prefill_select(g->be.ctx, (int32_t)r, ids + off, lens[r], temperature, tape, logits.data(), &sel[r])))
+        return session_failed(rc);
+      off += lens[r];
+    }
+  }
+  for (size_t r = 0; r < batch; ++r) staged[r] = lens[r];
+  for (size_t step = 0; step < max_new; ++step) {
+    // the tokens selected for this step; rows that stop here do not feed theirs back
+    std::vector<int32_t> active, toks;
+    for (size_t r = 0; r < batch; ++r) {
+      if (seqs[r].stopped) continue;
+      seqs[r].generated.push_back(sel[r]);
+      seqs[r].stopped = g->stop_ids.count(sel[r]) != 0;
+      if (!seqs[r].stopped) {
+        active.push_back((int32_t)r);
+        toks.push_back(sel[r]);
+      }
+    }
+    if (step + 1 >= max_new || active.empty()) break;
+    const int32_t n = (int32_t)active.size();
+    std::vector<float> temps((size_t)n, temperature), tape;
+    if (!greedy) {
+      tape.resize((size_t)n * vocab);
+      for (int32_t i = 0; i < n; ++i)
+        memcpy(&tape[(size_t)i * vocab], sampling->uniforms + ((step + 1) * batch + (size_t)active[(size_t)i]) * vocab, vocab * sizeof(float));
+    }
+    std::vector<int32_t> out((size_t)n, -1);
+    if ((rc = g->be.decode_rows(g->be.ctx, active.data(), toks.data(), n, temps.data(), greedy ? nullptr : tape.data(), out.data())))
+      return session_failed(rc);
+    for (int32_t i = 0; i < n; ++i) {
+      sel[(size_t)active[(size_t)i]] = out[(size_t)i];
+      staged[(size_t)active[(size_t)i]] += 1;
+    }
+  }
+  if ((rc = decode_rows_text(g, &seqs, err))) return rc;
+  return commit(staged);
+}
+
+int32_t rg_b200_batch_generate_texts(rg_batch_generator *g, const char *const *texts, const size_t *text_bytes, size_t n_prompts,
+                                     size_t max_new, const rg_serving_sampling *sampling, rg_batch_error *err) {
+  if (!g || (n_prompts && (!texts || !text_bytes))) return bfail(err, RG_BATCH_INVALID_ARGUMENT);
+  if (!g->tokenizer) return bfail(err, RG_BATCH_TOKENIZER, 0, RG_TOK_INVALID_ARGUMENT);
+  std::vector<int32_t> flat;
+  std::vector<size_t> lens;
+  for (size_t r = 0; r < n_prompts; ++r) {
+    Key ids;
+    if (g->has_bos) ids.push_back(g->bos_id);
+    rg_serving_error serr{};
+    if (encode_text(g->tokenizer, texts[r], text_bytes[r], &ids, &serr)) return bfail(err, RG_BATCH_TOKENIZER, (int32_t)r, serr.value);
+    lens.push_back(ids.size());
+    flat.insert(flat.end(), ids.begin(), ids.end());
+  }
+  return rg_b200_batch_generate_ids(g, flat.data(), lens.data(), n_prompts, max_new, sampling, err);
+}
+
+int32_t rg_b200_batch_sequence(const rg_batch_generator *g, size_t row, rg_serving_result *out) {
+  if (!g || !out || !g->has_result || row >= g->last.size()) return RG_BATCH_INVALID_ARGUMENT;
+  const auto &q = g->last[row];
+  out->request_id = row;
+  out->prompt_ids = q.prompt.data();
+  out->n_prompt_ids = q.prompt.size();
+  out->generated_ids = q.generated.data();
+  out->n_generated_ids = q.generated.size();
+  out->decoded = q.decoded.c_str();
+  out->decoded_bytes = q.decoded.size();
+  out->stopped = q.stopped ? 1 : 0;
+  return RG_BATCH_OK;
+}
+
+}  // extern "C"

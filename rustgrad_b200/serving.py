@@ -48,6 +48,10 @@ class _Result(C.Structure):
                 ("n_generated_ids", C.c_size_t), ("decoded", C.c_char_p), ("decoded_bytes", C.c_size_t), ("stopped", C.c_int32)]
 
 
+class _BatchError(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("row", C.c_int32), ("value", C.c_int64), ("value2", C.c_int64)]
+
+
 class _Stats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("entries", "bytes", "hits", "misses", "stale_rejections", "evictions", "generation")]
 
@@ -95,6 +99,19 @@ def _L():
     L.rg_b200_scheduler_step.argtypes = [vp, C.POINTER(_Event), C.c_size_t, C.POINTER(C.c_size_t), ep]
     L.rg_b200_scheduler_rebind.argtypes = [vp, vp, vp, C.POINTER(_Options), C.POINTER(C.c_int32), ep]
     L.rg_b200_scheduler_rebind_with_backend.argtypes = [vp, C.POINTER(_Backend), vp, C.POINTER(_Options), C.POINTER(C.c_int32), ep]
+    bep = C.POINTER(_BatchError)
+    L.rg_b200_batch_generator_new.argtypes = [vp, vp, C.c_int32, C.POINTER(_Options), C.POINTER(vp), bep]
+    L.rg_b200_batch_generator_new_with_backend.argtypes = [C.POINTER(_Backend), vp, C.c_int32, C.POINTER(_Options), C.POINTER(vp), bep]
+    L.rg_b200_batch_generator_free.restype = None
+    L.rg_b200_batch_generator_free.argtypes = [vp]
+    L.rg_b200_batch_generator_cache_lengths.restype = C.c_size_t
+    L.rg_b200_batch_generator_cache_lengths.argtypes = [vp, C.POINTER(C.c_size_t), C.c_size_t]
+    L.rg_b200_batch_generator_clear.restype = None
+    L.rg_b200_batch_generator_clear.argtypes = [vp]
+    L.rg_b200_batch_generate_ids.argtypes = [vp, i32p, C.POINTER(C.c_size_t), C.c_size_t, C.c_size_t, C.POINTER(_Sampling), bep]
+    L.rg_b200_batch_generate_texts.argtypes = [vp, C.POINTER(C.c_char_p), C.POINTER(C.c_size_t), C.c_size_t, C.c_size_t,
+                                               C.POINTER(_Sampling), bep]
+    L.rg_b200_batch_sequence.argtypes = [vp, C.c_size_t, C.POINTER(_Result)]
     L._serving_bound = True
     return L
 
@@ -377,3 +394,94 @@ class LlamaServingScheduler:
             _raise(rc, err)
         return [TokenEvent(e.request_id, e.arrival_order, e.generation_step, e.token_id, bool(e.stopped), bool(e.complete))
                 for e in events[: n.value]]
+
+
+BATCH_KINDS = ["Ok", "Session", "InvalidTemperature", "Tokenizer", "BatchSize", "EmptyPrompt", "ContextOverflow", "ContextLength",
+               "UniformTapeLength", "InvalidUniform", "TokenOutOfRange", "InvalidArgument"]
+
+
+class BatchGenerationError(Exception):
+    """LlamaBatchGenerationError (batch_generation.rs:251-279) by kind, with the row and the numbers it carries."""
+
+    def __init__(self, kind, row=0, value=0, value2=0, text=""):
+        super().__init__(f"{kind} row={row} value={value} value2={value2} {text}".strip())
+        self.kind, self.row, self.value, self.value2, self.text = kind, row, value, value2, text
+
+
+def _raise_batch(rc: int, err: _BatchError):
+    text = _lib.load().rg_b200_last_error().decode(errors="replace") if rc == 1 else ""
+    raise BatchGenerationError(BATCH_KINDS[rc] if 0 <= rc < len(BATCH_KINDS) else str(rc), err.row, err.value, err.value2, text)
+
+
+class LlamaBatchGenerator:
+    """LlamaBatchGenerator (src/models/transformer/batch_generation.rs:58-189) over a session (rows
+    0 .. batch_size-1) or a ``ServingBackend`` table: every generate starts from empty rows, runs all prompts
+    together and commits the row lengths only when everything succeeded.  ``sampling.uniforms`` is the
+    row-major [step, batch, vocabulary] tape."""
+
+    def __init__(self, session, tokenizer=None, batch_size: int = 1, stop_ids=(), bos_id: Optional[int] = None):
+        self._lib = _L()
+        self.session, self.tokenizer, self.batch_size = session, tokenizer, batch_size
+        stops = np.array(sorted(int(t) for t in stop_ids), dtype=np.int32)
+        opts = _Options(batch_size, 0, 0, 0, stops.ctypes.data_as(i32p), stops.size, int(bos_id is not None), bos_id or 0)
+        self._h, err = vp(), _BatchError()
+        tok = tokenizer._h if tokenizer is not None else None
+        if isinstance(session, ServingBackend):
+            self._table = session._table()
+            rc = self._lib.rg_b200_batch_generator_new_with_backend(C.byref(self._table), tok, batch_size, C.byref(opts),
+                                                                    C.byref(self._h), C.byref(err))
+        else:
+            rc = self._lib.rg_b200_batch_generator_new(session._h, tok, batch_size, C.byref(opts), C.byref(self._h), C.byref(err))
+        if rc:
+            self._h = None
+            _raise_batch(rc, err)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.rg_b200_batch_generator_free(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def cache_lengths(self) -> list:
+        out = (C.c_size_t * self.batch_size)()
+        n = self._lib.rg_b200_batch_generator_cache_lengths(self._h, out, self.batch_size)
+        return [out[i] for i in range(n)]
+
+    def clear(self) -> None:
+        self._lib.rg_b200_batch_generator_clear(self._h)
+
+    def _sequences(self):
+        out = []
+        for row in range(self.batch_size):
+            r = _Result()
+            if self._lib.rg_b200_batch_sequence(self._h, row, C.byref(r)):
+                raise BatchGenerationError("InvalidArgument", row)
+            out.append(ServingResult(r.request_id, [r.prompt_ids[i] for i in range(r.n_prompt_ids)],
+                                     [r.generated_ids[i] for i in range(r.n_generated_ids)],
+                                     C.string_at(r.decoded, r.decoded_bytes).decode("utf-8", "replace"), bool(r.stopped)))
+        return out
+
+    def generate_ids(self, prompts, max_new_tokens: int, sampling: Optional[Sampling] = None):
+        prompts = [[int(t) for t in p] for p in prompts]
+        flat = np.ascontiguousarray([t for p in prompts for t in p], dtype=np.int32)
+        lens = (C.c_size_t * max(len(prompts), 1))(*[len(p) for p in prompts])
+        sp, _keep = LlamaServingScheduler._sampling(GenerationConfig(max_new_tokens, sampling or Sampling()))
+        err = _BatchError()
+        rc = self._lib.rg_b200_batch_generate_ids(self._h, flat.ctypes.data_as(i32p), lens, len(prompts), max_new_tokens,
+                                                  C.byref(sp), C.byref(err))
+        if rc:
+            _raise_batch(rc, err)
+        return self._sequences()
+
+    def generate_texts(self, prompts, max_new_tokens: int, sampling: Optional[Sampling] = None):
+        raw = [p.encode("utf-8") for p in prompts]
+        strs = (C.c_char_p * max(len(raw), 1))(*raw)
+        lens = (C.c_size_t * max(len(raw), 1))(*[len(r) for r in raw])
+        sp, _keep = LlamaServingScheduler._sampling(GenerationConfig(max_new_tokens, sampling or Sampling()))
+        err = _BatchError()
+        rc = self._lib.rg_b200_batch_generate_texts(self._h, strs, lens, len(raw), max_new_tokens, C.byref(sp), C.byref(err))
+        if rc:
+            _raise_batch(rc, err)
+        return self._sequences()
+

@@ -61,7 +61,7 @@ def test_repr_c_structs_list_the_c_fields_in_order():
                          ("rg_b200_workflow.h", "rg_prompt_output"), ("rg_b200_serving.h", "rg_serving_error"),
                          ("rg_b200_serving.h", "rg_serving_options"), ("rg_b200_serving.h", "rg_serving_sampling"),
                          ("rg_b200_serving.h", "rg_token_event"), ("rg_b200_serving.h", "rg_serving_result"),
-                         ("rg_b200_serving.h", "rg_prefix_stats")):
+                         ("rg_b200_serving.h", "rg_prefix_stats"), ("rg_b200_serving.h", "rg_batch_error")):
         assert c_struct_fields(header, name) == rust_struct_fields(name), name
 
 
