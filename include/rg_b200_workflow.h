@@ -67,6 +67,49 @@ const int32_t *rg_b200_workflow_generated_ids(const rg_workflow *w);
 const char *rg_b200_workflow_decoded(const rg_workflow *w);          /* decoded_bytes bytes, also NUL-terminated */
 const char *rg_b200_workflow_rendered_prompt(const rg_workflow *w);  /* rendered_bytes bytes, also NUL-terminated */
 
+/* ---- LlamaConversation (src/models/transformer/conversation.rs:29-85): a transcript over one workflow. ----
+ * send() renders the committed history plus the new user message through the chat template, generates
+ * greedily from position 0 and appends the user and the assistant message only when everything succeeded. */
+typedef struct rg_conversation rg_conversation;
+
+/* LlamaConversationError. */
+enum {
+  RG_CONVERSATION_OK = 0,
+  RG_CONVERSATION_EMPTY_INPUT = 1,
+  RG_CONVERSATION_CHAT = 2,            /* template / tokenizer / message bound: *detail = rg_tok_status */
+  RG_CONVERSATION_GENERATION = 3,      /* the generation failed: *detail = rg_status */
+  RG_CONVERSATION_INVALID_ARGUMENT = 4
+};
+
+/* The workflow verbs a turn is made of; rg_b200_conversation_new binds them to an rg_workflow, a test supplies
+ * its own.  generate_chat has the contract of rg_b200_workflow_generate_chat; decoded returns the
+ * decoded_bytes bytes of the last request. */
+typedef struct rg_chat_backend {
+  void *ctx;
+  int32_t (*generate_chat)(void *ctx, const int32_t *roles, const char *const *contents, const size_t *content_len,
+                           size_t n_messages, size_t max_new_tokens, rg_text_callback on_text, void *user, rg_prompt_output *out);
+  const char *(*decoded)(void *ctx);
+} rg_chat_backend;
+
+/* LlamaPromptWorkflow::conversation (workflow.rs:136-139).  The workflow must outlive the conversation, and
+ * requests made on the workflow in between do not disturb the transcript (every turn starts from position 0). */
+int32_t rg_b200_conversation_new(rg_workflow *w, rg_conversation **out);
+int32_t rg_b200_conversation_new_with_backend(const rg_chat_backend *backend, rg_conversation **out);
+void rg_b200_conversation_free(rg_conversation *c);
+/* history(): messages committed so far (user, assistant, user, ...); the content pointer stays valid until the
+ * next send or reset. */
+size_t rg_b200_conversation_history_len(const rg_conversation *c);
+int32_t rg_b200_conversation_message(const rg_conversation *c, size_t index, int32_t *role, const char **content, size_t *content_len);
+/* cache_len(): positions the last successful turn left in the cache (its prompt and all but the last generated
+ * id); reset(): empty transcript, cache length 0. */
+size_t rg_b200_conversation_cache_len(const rg_conversation *c);
+void rg_b200_conversation_reset(rg_conversation *c);
+/* send (conversation.rs:58-84): message bound, then empty input, then render + generate on the staged transcript.
+ * `out` and the workflow's accessors describe the turn's generation; on any failure the transcript and the
+ * cache length are what they were.  detail (nullable) receives the status named above. */
+int32_t rg_b200_conversation_send(rg_conversation *c, const char *content, size_t content_len, size_t max_new_tokens,
+                                  rg_text_callback on_text, void *user, rg_prompt_output *out, int32_t *detail);
+
 #ifdef __cplusplus
 }
 #endif

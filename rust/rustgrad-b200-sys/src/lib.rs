@@ -3,7 +3,7 @@
 //!
 //! Every item mirrors a declaration of `include/rg_b200.h`, `include/rg_b200_tokenizer.h`,
 //! `include/rg_b200_workflow.h` or `include/rg_b200_serving.h`; the headers carry the documentation and, for each entry point, the
-//! rustgrad interface it stands in for.  All 105 exports are declared here.
+//! rustgrad interface it stands in for.  All 113 exports are declared here.
 #![allow(non_camel_case_types)]
 
 use core::ffi::{c_char, c_void};
@@ -171,6 +171,30 @@ pub struct rg_prompt_output {
 
 /// `rg_text_callback`: one call per generated token (`token_id = -1` for the final flush).
 pub type rg_text_callback = unsafe extern "C" fn(user: *mut c_void, token_id: i32, text: *const c_char, text_len: usize);
+
+/// Opaque conversation handle of `include/rg_b200_workflow.h` (`LlamaConversation`).
+#[repr(C)]
+pub struct rg_conversation {
+    _private: [u8; 0],
+}
+
+/// The workflow verbs a conversation turn is made of (`rg_chat_backend`).
+#[repr(C)]
+#[derive(Clone, Copy)]
+pub struct rg_chat_backend {
+    pub ctx: *mut c_void,
+    pub generate_chat: Option<unsafe extern "C" fn(ctx: *mut c_void, roles: *const i32, contents: *const *const c_char, content_len: *const usize, n_messages: usize, max_new_tokens: usize, on_text: Option<rg_text_callback>, user: *mut c_void, out: *mut rg_prompt_output) -> i32>,
+    pub decoded: Option<unsafe extern "C" fn(ctx: *mut c_void) -> *const c_char>,
+}
+
+/// `LlamaConversationError` by kind.
+pub mod conversation_status {
+    pub const OK: i32 = 0;
+    pub const EMPTY_INPUT: i32 = 1;
+    pub const CHAT: i32 = 2;
+    pub const GENERATION: i32 = 3;
+    pub const INVALID_ARGUMENT: i32 = 4;
+}
 
 /// Opaque scheduler handle of `include/rg_b200_serving.h`.
 #[repr(C)]
@@ -397,6 +421,14 @@ unsafe extern "C" {
     pub fn rg_b200_workflow_generated_ids(w: *const rg_workflow) -> *const i32;
     pub fn rg_b200_workflow_decoded(w: *const rg_workflow) -> *const c_char;
     pub fn rg_b200_workflow_rendered_prompt(w: *const rg_workflow) -> *const c_char;
+    pub fn rg_b200_conversation_new(w: *mut rg_workflow, out: *mut *mut rg_conversation) -> i32;
+    pub fn rg_b200_conversation_new_with_backend(backend: *const rg_chat_backend, out: *mut *mut rg_conversation) -> i32;
+    pub fn rg_b200_conversation_free(c: *mut rg_conversation);
+    pub fn rg_b200_conversation_history_len(c: *const rg_conversation) -> usize;
+    pub fn rg_b200_conversation_message(c: *const rg_conversation, index: usize, role: *mut i32, content: *mut *const c_char, content_len: *mut usize) -> i32;
+    pub fn rg_b200_conversation_cache_len(c: *const rg_conversation) -> usize;
+    pub fn rg_b200_conversation_reset(c: *mut rg_conversation);
+    pub fn rg_b200_conversation_send(c: *mut rg_conversation, content: *const c_char, content_len: usize, max_new_tokens: usize, on_text: Option<rg_text_callback>, user: *mut c_void, out: *mut rg_prompt_output, detail: *mut i32) -> i32;
 
     // ---- include/rg_b200_serving.h
     pub fn rg_b200_scheduler_new(session: *mut rg_session, tokenizer: *const rg_tokenizer, options: *const rg_serving_options, out: *mut *mut rg_scheduler, err: *mut rg_serving_error) -> i32;

@@ -214,3 +214,115 @@ const char *rg_b200_workflow_decoded(const rg_workflow *w) { return w ? w->decod
 const char *rg_b200_workflow_rendered_prompt(const rg_workflow *w) { return w ? w->rendered.c_str() : nullptr; }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// LlamaConversation (src/models/transformer/conversation.rs:29-85)
+// ---------------------------------------------------------------------------------------------
+struct rg_conversation {
+  rg_chat_backend be{};
+  std::vector<int32_t> roles;
+  std::vector<std::string> contents;
+  size_t cache_len = 0;
+};
+
+namespace {
+
+const size_t CONVERSATION_MESSAGE_BYTES = 1024 * 1024;  // LlamaChatMessage::new (chat.rs:45-55)
+
+int32_t wf_generate_chat(void *ctx, const int32_t *roles, const char *const *contents, const size_t *content_len, size_t n,
+                         size_t max_new, rg_text_callback on_text, void *user, rg_prompt_output *out) {
+  return rg_b200_workflow_generate_chat(static_cast<rg_workflow *>(ctx), roles, contents, content_len, n, max_new, on_text, user, out);
+}
+const char *wf_decoded(void *ctx) { return rg_b200_workflow_decoded(static_cast<rg_workflow *>(ctx)); }
+
+}  // namespace
+
+extern "C" {
+
+int32_t rg_b200_conversation_new_with_backend(const rg_chat_backend *backend, rg_conversation **out) {
+  if (!backend || !backend->generate_chat || !backend->decoded || !out) return RG_CONVERSATION_INVALID_ARGUMENT;
+  auto c = new rg_conversation();
+  c->be = *backend;
+  *out = c;
+  return RG_CONVERSATION_OK;
+}
+
+int32_t rg_b200_conversation_new(rg_workflow *w, rg_conversation **out) {
+  if (!w) return RG_CONVERSATION_INVALID_ARGUMENT;
+  rg_chat_backend be{};
+  be.ctx = w;
+  be.generate_chat = wf_generate_chat;
+  be.decoded = wf_decoded;
+  return rg_b200_conversation_new_with_backend(&be, out);
+}
+
+void rg_b200_conversation_free(rg_conversation *c) { delete c; }
+
+size_t rg_b200_conversation_history_len(const rg_conversation *c) { return c ? c->roles.size() : 0; }
+
+int32_t rg_b200_conversation_message(const rg_conversation *c, size_t index, int32_t *role, const char **content, size_t *content_len) {
+  if (!c || index >= c->roles.size()) return RG_CONVERSATION_INVALID_ARGUMENT;
+  if (role) *role = c->roles[index];
+  if (content) *content = c->contents[index].c_str();
+  if (content_len) *content_len = c->contents[index].size();
+  return RG_CONVERSATION_OK;
+}
+
+size_t rg_b200_conversation_cache_len(const rg_conversation *c) { return c ? c->cache_len : 0; }
+
+void rg_b200_conversation_reset(rg_conversation *c) {
+  if (!c) return;
+  c->roles.clear();
+  c->contents.clear();
+  c->cache_len = 0;
+}
+
+int32_t rg_b200_conversation_send(rg_conversation *c, const char *content, size_t content_len, size_t max_new_tokens,
+                                  rg_text_callback on_text, void *user, rg_prompt_output *out, int32_t *detail) {
+  if (detail) *detail = 0;
+  if (!c || (content_len && !content)) return RG_CONVERSATION_INVALID_ARGUMENT;
+  if (content_len > CONVERSATION_MESSAGE_BYTES) {
+    if (detail) *detail = RG_TOK_MESSAGE_TOO_LONG;
+    return RG_CONVERSATION_CHAT;
+  }
+  if (content_len == 0) return RG_CONVERSATION_EMPTY_INPUT;
+  // the staged transcript: committed history + the new user message
+  const size_t n = c->roles.size() + 1;
+  std::vector<int32_t> roles(c->roles);
+  roles.push_back(RG_CHAT_USER);
+  std::vector<const char *> ptrs(n);
+  std::vector<size_t> lens(n);
+  for (size_t i = 0; i + 1 < n; ++i) {
+    ptrs[i] = c->contents[i].data();
+    lens[i] = c->contents[i].size();
+  }
+  ptrs[n - 1] = content;
+  lens[n - 1] = content_len;
+  rg_prompt_output local{};
+  rg_prompt_output *o = out ? out : &local;
+  const int32_t rc = c->be.generate_chat(c->be.ctx, roles.data(), ptrs.data(), lens.data(), n, max_new_tokens, on_text, user, o);
+  if (rc != RG_OK) {
+    if (o->tokenizer_status) {
+      if (detail) *detail = o->tokenizer_status;
+      return RG_CONVERSATION_CHAT;
+    }
+    if (detail) *detail = rc;
+    return RG_CONVERSATION_GENERATION;
+  }
+  if (o->decoded_bytes > CONVERSATION_MESSAGE_BYTES) {  // the assistant message is bounded like any other
+    if (detail) *detail = RG_TOK_MESSAGE_TOO_LONG;
+    return RG_CONVERSATION_CHAT;
+  }
+  const char *text = c->be.decoded(c->be.ctx);
+  std::string assistant(text ? text : "", text ? o->decoded_bytes : 0);
+  c->roles.push_back(RG_CHAT_USER);
+  c->contents.emplace_back(content, content_len);
+  c->roles.push_back(RG_CHAT_ASSISTANT);
+  c->contents.push_back(std::move(assistant));
+  // a generation of no tokens returns before any cache work (generation.rs:127-134)
+  if (o->n_generated_ids > 0) c->cache_len = o->n_prompt_ids + o->n_generated_ids - 1;
+  return RG_CONVERSATION_OK;
+}
+
+}  // extern "C"
+

@@ -25,6 +25,13 @@ class _Output(C.Structure):
 
 
 _CALLBACK = C.CFUNCTYPE(None, C.c_void_p, C.c_int32, C.POINTER(C.c_char), C.c_size_t)
+_GENERATE_CHAT = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_char_p), C.POINTER(C.c_size_t), C.c_size_t,
+                             C.c_size_t, _CALLBACK, C.c_void_p, C.POINTER(_Output))
+_DECODED = C.CFUNCTYPE(C.c_void_p, C.c_void_p)
+
+
+class _ChatBackend(C.Structure):
+    _fields_ = [("ctx", C.c_void_p), ("generate_chat", _GENERATE_CHAT), ("decoded", _DECODED)]
 
 
 def _L():
@@ -47,6 +54,20 @@ def _L():
         for name in ("rg_b200_workflow_decoded", "rg_b200_workflow_rendered_prompt"):
             getattr(L, name).restype = C.POINTER(C.c_char)
             getattr(L, name).argtypes = [vp]
+        L.rg_b200_conversation_new.argtypes = [vp, C.POINTER(vp)]
+        L.rg_b200_conversation_new_with_backend.argtypes = [C.POINTER(_ChatBackend), C.POINTER(vp)]
+        L.rg_b200_conversation_free.restype = None
+        L.rg_b200_conversation_free.argtypes = [vp]
+        L.rg_b200_conversation_history_len.restype = C.c_size_t
+        L.rg_b200_conversation_history_len.argtypes = [vp]
+        L.rg_b200_conversation_message.argtypes = [vp, C.c_size_t, C.POINTER(C.c_int32), C.POINTER(C.POINTER(C.c_char)),
+                                                   C.POINTER(C.c_size_t)]
+        L.rg_b200_conversation_cache_len.restype = C.c_size_t
+        L.rg_b200_conversation_cache_len.argtypes = [vp]
+        L.rg_b200_conversation_reset.restype = None
+        L.rg_b200_conversation_reset.argtypes = [vp]
+        L.rg_b200_conversation_send.argtypes = [vp, C.c_char_p, C.c_size_t, C.c_size_t, _CALLBACK, vp, C.POINTER(_Output),
+                                                C.POINTER(C.c_int32)]
         L._workflow_bound = True
     return L
 
@@ -129,6 +150,10 @@ class LlamaPromptWorkflow:
         rc = _L().rg_b200_workflow_generate_text(self._h, raw, len(raw), max_new_tokens, cb, None, C.byref(out))
         return self._finish(rc, out)
 
+    def conversation(self) -> "LlamaConversation":
+        """LlamaPromptWorkflow::conversation (workflow.rs:136-139): a stateful transcript over this workflow."""
+        return LlamaConversation(self)
+
     def generate_chat(self, messages: Iterable[tuple[str, str]], max_new_tokens: int,
                       on_text: Optional[Callable[[int, str], None]] = None) -> LlamaPromptOutput:
         """LlamaPromptWorkflow::generate_chat: (role, content) messages through the checked template."""
@@ -142,3 +167,103 @@ class LlamaPromptWorkflow:
         cb = self._callback(on_text)
         rc = _L().rg_b200_workflow_generate_chat(self._h, roles, strs, lens, n, max_new_tokens, cb, None, C.byref(out))
         return self._finish(rc, out)
+
+
+ROLE_NAMES = {v: k for k, v in ROLES.items()}
+CONVERSATION_KINDS = ["Ok", "EmptyInput", "Chat", "Generation", "InvalidArgument"]
+
+
+class ConversationError(Exception):
+    """LlamaConversationError (conversation.rs:86-91): ``EmptyInput``, ``Chat`` (detail = tokenizer status)
+    or ``Generation`` (detail = session status)."""
+
+    def __init__(self, kind: str, detail: int = 0, text: str = ""):
+        super().__init__(f"{kind}: {detail}" + (f" ({text})" if text else ""))
+        self.kind, self.detail, self.text = kind, detail, text
+
+
+@dataclass
+class LlamaConversationTurn:
+    """LlamaConversationTurn (conversation.rs:9-27)."""
+    user: tuple
+    assistant: tuple
+    generation: LlamaGeneration
+
+
+class ChatBackend:
+    """The workflow verbs of a turn as Python callables, for driving the compiled transcript logic without a
+    device.  ``generate_chat(messages, max_new_tokens)`` returns ``(status, tokenizer_status, n_prompt_ids,
+    generated_ids, decoded, stopped)``."""
+
+    def generate_chat(self, messages, max_new_tokens):
+        raise NotImplementedError
+
+    def _table(self) -> _ChatBackend:
+        def generate(_ctx, roles, contents, lens, n, max_new, _cb, _user, out):
+            msgs = [(ROLE_NAMES[roles[i]], C.string_at(contents[i], lens[i]).decode("utf-8")) for i in range(n)]
+            rc, tok, n_prompt, generated, decoded, stopped = self.generate_chat(msgs, max_new)
+            self._last = decoded.encode("utf-8")
+            self._generated = list(generated)
+            out[0] = _Output(n_prompt, len(generated), len(self._last), 0, int(stopped), tok)
+            return rc
+
+        def decoded(_ctx):
+            self._buf = C.create_string_buffer(self._last)
+            return C.addressof(self._buf)
+
+        self._keep = (_GENERATE_CHAT(generate), _DECODED(decoded))
+        return _ChatBackend(None, *self._keep)
+
+
+class LlamaConversation:
+    """LlamaConversation (conversation.rs:29-85): the transcript lives in the library; ``send`` renders the
+    committed history plus the new user message, generates greedily and commits both messages on success."""
+
+    def __init__(self, workflow):
+        self._workflow = workflow
+        self._h = C.c_void_p()
+        if isinstance(workflow, ChatBackend):
+            self._table = workflow._table()
+            rc = _L().rg_b200_conversation_new_with_backend(C.byref(self._table), C.byref(self._h))
+        else:
+            rc = _L().rg_b200_conversation_new(workflow._h, C.byref(self._h))
+        if rc:
+            self._h = None
+            raise ConversationError(CONVERSATION_KINDS[rc])
+
+    def close(self):
+        if getattr(self, "_h", None):
+            _L().rg_b200_conversation_free(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def history(self) -> list:
+        L, out = _L(), []
+        for i in range(L.rg_b200_conversation_history_len(self._h)):
+            role, text, n = C.c_int32(), C.POINTER(C.c_char)(), C.c_size_t()
+            L.rg_b200_conversation_message(self._h, i, C.byref(role), C.byref(text), C.byref(n))
+            out.append((ROLE_NAMES[role.value], C.string_at(text, n.value).decode("utf-8")))
+        return out
+
+    def cache_len(self) -> int:
+        return _L().rg_b200_conversation_cache_len(self._h)
+
+    def reset(self) -> None:
+        _L().rg_b200_conversation_reset(self._h)
+
+    def send(self, content: str, max_new_tokens: int, on_text: Optional[Callable[[int, str], None]] = None) -> LlamaConversationTurn:
+        raw = content.encode("utf-8")
+        out, detail = _Output(), C.c_int32()
+        cb = LlamaPromptWorkflow._callback(on_text)
+        rc = _L().rg_b200_conversation_send(self._h, raw, len(raw), max_new_tokens, cb, None, C.byref(out), C.byref(detail))
+        if rc:
+            text = _L().rg_b200_last_error().decode(errors="replace") if rc in (2, 3) else ""
+            raise ConversationError(CONVERSATION_KINDS[rc] if rc < len(CONVERSATION_KINDS) else str(rc), detail.value, text)
+        user, assistant = self.history()[-2:]
+        if isinstance(self._workflow, ChatBackend):
+            gen = LlamaGeneration([], list(self._workflow._generated), assistant[1], bool(out.stopped))
+        else:
+            gen = self._workflow._finish(0, out).generation
+        return LlamaConversationTurn(user, assistant, gen)
+
