@@ -130,6 +130,18 @@ int32_t rg_b200_test_fail_after(const char *what, int32_t n);
  * "dense_gemv", "qgemv_rows" (the opt-in 3..16-row form, not counted under "qgemv"), "attn_decode_tc"; UINT64_MAX for an unknown name.  Evidence for tests and reports of which kernel
  * served a call (the role of MetalDeviceRunReport's dispatch counts, src/runtime/metal/session.rs:145-185). */
 uint64_t rg_b200_launch_count(const char *kernel);
+/* What a session on CUDA ordinal `device` would run on (the role of MetalDeviceInfo,
+ * src/runtime/metal/dispatch.rs:33-40, reached through LlamaMetalSession::device_info): name, SM count, compute
+ * capability and the memory sizes the kernels are laid out for.  RG_CUDA_ERROR when there is no such device. */
+typedef struct {
+  char name[128];                  /* NUL-terminated */
+  int32_t sm_count;
+  int32_t cc_major, cc_minor;
+  uint64_t total_memory_bytes;
+  uint64_t l2_bytes;
+  uint64_t shared_memory_per_block; /* opt-in maximum of dynamic shared memory per block */
+} rg_device_info;
+int32_t rg_b200_device_info(int32_t device, rg_device_info *out);
 /* Test hook for the device-side time-out path (bounded waits that end in a status word, the
  * stand-in for rustgrad's unprovable-completion rule, src/runtime/cuda_graph.rs:542-546): enqueues
  * on the session's stream one launch of the partial-sum exchange kernel whose peer flag is never

@@ -3,7 +3,7 @@
 //!
 //! Every item mirrors a declaration of `include/rg_b200.h`, `include/rg_b200_tokenizer.h`,
 //! `include/rg_b200_workflow.h` or `include/rg_b200_serving.h`; the headers carry the documentation and, for each entry point, the
-//! rustgrad interface it stands in for.  All 113 exports are declared here.
+//! rustgrad interface it stands in for.  All 114 exports are declared here.
 #![allow(non_camel_case_types)]
 
 use core::ffi::{c_char, c_void};
@@ -171,6 +171,19 @@ pub struct rg_prompt_output {
 
 /// `rg_text_callback`: one call per generated token (`token_id = -1` for the final flush).
 pub type rg_text_callback = unsafe extern "C" fn(user: *mut c_void, token_id: i32, text: *const c_char, text_len: usize);
+
+/// `rg_device_info`: what a session on a CUDA ordinal would run on.
+#[repr(C)]
+#[derive(Clone, Copy)]
+pub struct rg_device_info {
+    pub name: [c_char; 128],
+    pub sm_count: i32,
+    pub cc_major: i32,
+    pub cc_minor: i32,
+    pub total_memory_bytes: u64,
+    pub l2_bytes: u64,
+    pub shared_memory_per_block: u64,
+}
 
 /// Opaque conversation handle of `include/rg_b200_workflow.h` (`LlamaConversation`).
 #[repr(C)]
@@ -341,6 +354,7 @@ unsafe extern "C" {
     pub fn rg_b200_last_error() -> *const c_char;
     pub fn rg_b200_test_fail_after(what: *const c_char, n: i32) -> i32;
     pub fn rg_b200_launch_count(kernel: *const c_char) -> u64;
+    pub fn rg_b200_device_info(device: i32, out: *mut rg_device_info) -> i32;
     pub fn rg_b200_test_expire_device_wait(s: *mut rg_session) -> i32;
     pub fn rg_b200_debug_read_trace(s: *mut rg_session, out: *mut u64, max_launches: i32) -> i32;
     pub fn rg_b200_gguf_open(bytes: *const u8, len: usize, out: *mut *mut rg_gguf) -> i32;

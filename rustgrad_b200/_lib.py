@@ -72,7 +72,7 @@ EXPORTS = [
     "rg_b200_batch_generate_texts", "rg_b200_batch_sequence",
     "rg_b200_conversation_new", "rg_b200_conversation_new_with_backend", "rg_b200_conversation_free",
     "rg_b200_conversation_history_len", "rg_b200_conversation_message", "rg_b200_conversation_cache_len",
-    "rg_b200_conversation_reset", "rg_b200_conversation_send",
+    "rg_b200_conversation_reset", "rg_b200_conversation_send", "rg_b200_device_info",
 ]
 
 _lib = None

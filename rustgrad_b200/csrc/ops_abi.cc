@@ -33,6 +33,28 @@ extern "C" uint64_t rg_b200_launch_count(const char *kernel) {
   return ~0ull;
 }
 
+extern "C" int32_t rg_b200_device_info(int32_t device, rg_device_info *out) {
+  if (!out || device < 0) {
+    g_last_error = "null output or negative device";
+    return RG_INVALID_ARGUMENT;
+  }
+  cudaDeviceProp p{};
+  const cudaError_t e = cudaGetDeviceProperties(&p, device);
+  if (e != cudaSuccess) {
+    g_last_error = std::string("cudaGetDeviceProperties: ") + cudaGetErrorString(e);
+    return RG_CUDA_ERROR;
+  }
+  memset(out, 0, sizeof(*out));
+  strncpy(out->name, p.name, sizeof(out->name) - 1);
+  out->sm_count = p.multiProcessorCount;
+  out->cc_major = p.major;
+  out->cc_minor = p.minor;
+  out->total_memory_bytes = (uint64_t)p.totalGlobalMem;
+  out->l2_bytes = (uint64_t)p.l2CacheSize;
+  out->shared_memory_per_block = (uint64_t)p.sharedMemPerBlockOptin;
+  return RG_OK;
+}
+
 namespace {
 
 int32_t fail(int32_t status, const std::string &why) {

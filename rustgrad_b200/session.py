@@ -363,6 +363,22 @@ class LlamaCudaSession:
         check(self._L.rg_b200_test_expire_device_wait(self._h))
 
 
+class _DeviceInfo(C.Structure):
+    _fields_ = [("name", C.c_char * 128), ("sm_count", C.c_int32), ("cc_major", C.c_int32), ("cc_minor", C.c_int32),
+                ("total_memory_bytes", C.c_uint64), ("l2_bytes", C.c_uint64), ("shared_memory_per_block", C.c_uint64)]
+
+
+def device_info(device: int = 0) -> dict:
+    """What a session on CUDA ordinal ``device`` would run on (rg_b200_device_info); raises when there is none."""
+    L = _lib.load()
+    L.rg_b200_device_info.argtypes = [C.c_int32, C.POINTER(_DeviceInfo)]
+    info = _DeviceInfo()
+    check(L.rg_b200_device_info(device, C.byref(info)))
+    return {"name": info.name.decode(errors="replace"), "sm_count": info.sm_count, "compute_capability": (info.cc_major, info.cc_minor),
+            "total_memory_bytes": info.total_memory_bytes, "l2_bytes": info.l2_bytes,
+            "shared_memory_per_block": info.shared_memory_per_block}
+
+
 def launch_count(kernel: str) -> int:
     """Launches of a kernel family made by this process so far (see rg_b200_launch_count)."""
     n = _lib.load().rg_b200_launch_count(kernel.encode())

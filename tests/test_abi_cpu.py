@@ -182,3 +182,15 @@ def test_stop_ids_follow_the_tokenizer_rule():
     g = session.GgufFile(build(md, tensors))
     with pytest.raises(session.MissingMetadata):
         g.llama_config()
+
+
+def test_device_info_is_a_typed_error_without_a_device():
+    """No GPU here: the verb must say so (RG_CUDA_ERROR with the driver's words), never invent a device."""
+    import torch
+    if torch.cuda.is_available():
+        info = session.device_info(0)
+        assert info["sm_count"] > 0 and info["name"]
+        return
+    with pytest.raises(session.RgError) as e:
+        session.device_info(0)
+    assert e.value.status == 9 and "cuda" in str(e.value).lower()

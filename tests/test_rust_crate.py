@@ -57,6 +57,7 @@ def rust_struct_fields(name):
 
 def test_repr_c_structs_list_the_c_fields_in_order():
     for header, name in (("rg_b200.h", "rg_llama_config"), ("rg_b200.h", "rg_options"), ("rg_b200.h", "rg_report"),
+                         ("rg_b200.h", "rg_device_info"),
                          ("rg_b200_tokenizer.h", "rg_tok_config"), ("rg_b200_tokenizer.h", "rg_tok_error"),
                          ("rg_b200_workflow.h", "rg_prompt_output"), ("rg_b200_serving.h", "rg_serving_error"),
                          ("rg_b200_serving.h", "rg_serving_options"), ("rg_b200_serving.h", "rg_serving_sampling"),
